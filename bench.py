@@ -1,0 +1,323 @@
+#!/usr/bin/env python3
+"""Benchmark of the JANG quantized decode hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # CUDA arm (this repo)
+    python bench.py --impl reference --gpus N --steps K --warmup W   # reference's CPU path
+
+Workload (N=1): BASELINE config 2, the dense Llama-shaped decoder's batch-1
+decode weight stream — per layer q/k/v/o 4096x4096 @8-bit, gate/up 11008x4096
+@2-bit, down 4096x11008 @2-bit, 32 layers, lm_head 32000x4096 @6-bit, group 64,
+bf16 sidecars — i.e. the 225 quantized mat-vecs of one decoded token
+(3.74 GB of algorithmic bytes, far larger than L2, so no flush is needed).
+One step = one pass over all 225 matrices.  Weights are random N(0, 0.02)
+quantized on the GPU by this repo's quantizer; activations are N(0,1).
+Attention, norms and sampling are outside the path and are not run.
+
+metric: achieved GB/s = algorithmic bytes / time.  `value` has inputs resident
+in HBM and replays a CUDA graph; `e2e` goes through GemvPlan.run_host() with
+pinned host activations in and the logits row out every step.
+For N>1 the dense stack is replicated (weak scaling, no collective on this part
+of the path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS, HIDDEN, INTER, VOCAB, GS = 32, 4096, 11008, 32000, 64
+METRIC, UNIT = "jang_qgemv_hbm_gbs", "GB/s"
+
+
+def stack_spec():
+    """(name, N, K, bits) of every quantized matrix one decoded token streams."""
+    spec = []
+    for l in range(LAYERS):
+        for p in ("q", "k", "v", "o"):
+            spec.append((f"layers.{l}.self_attn.{p}_proj", HIDDEN, HIDDEN, 8))
+        spec.append((f"layers.{l}.mlp.gate_proj", INTER, HIDDEN, 2))
+        spec.append((f"layers.{l}.mlp.up_proj", INTER, HIDDEN, 2))
+        spec.append((f"layers.{l}.mlp.down_proj", HIDDEN, INTER, 2))
+    spec.append(("lm_head", VOCAB, HIDDEN, 6))
+    return spec
+
+
+def alg_bytes(N, K, bits, gs=GS, m=1, sidecar=2):
+    return N * K * bits // 8 + N * (K // gs) * 2 * sidecar + m * K * 2 + m * N * 2
+
+
+CONFIG = {"workload": "config2 dense decoder, batch-1 decode weight stream: 225 qGEMVs/token "
+                      "(32x[q,k,v,o 4096x4096@8b; gate,up 11008x4096@2b; down 4096x11008@2b] + lm_head 32000x4096@6b), "
+                      "group 64, bf16",
+          "matrices": 225, "bytes_per_step": sum(alg_bytes(n, k, b) for _, n, k, b in stack_spec()),
+          "l2": "working set 3.7 GB per step >> 126 MB L2, no flush needed", "parallelism": "replicated"}
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the reference's numpy path (dequantize_affine_numpy(...) @ x), restated in
+# oracle/jang_oracle.py, on all host threads, on a bounded sample of the workload
+# --------------------------------------------------------------------------------------
+def cpu_sample_setup():
+    from oracle import jang_oracle as jo
+    rng = np.random.default_rng(0)
+    sample = []
+    for name, N, K, bits in (("q_proj", HIDDEN, HIDDEN, 8), ("gate_proj", INTER, HIDDEN, 2),
+                             ("lm_head[:4096]", 4096, HIDDEN, 6)):
+        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+        packed, s, b = jo.quantize_affine(w, bits, GS, src_dtype="bf16")
+        x = jo.round_to(rng.standard_normal((1, K)).astype(np.float32), "bf16")
+        sample.append((name, packed, s, b, x, bits, N, K))
+    return sample
+
+
+def cpu_sample_step(sample, threads):
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import jang_oracle as jo
+
+    def part(args):
+        packed, s, b, x, bits = args
+        return jo.qmatmul(x, packed, s, b, bits, GS, acc=np.float32)
+
+    jobs = []
+    for _, packed, s, b, x, bits, N, K in sample:
+        chunk = (N + threads - 1) // threads
+        for r0 in range(0, N, chunk):
+            jobs.append((packed[r0:r0 + chunk], s[r0:r0 + chunk], b[r0:r0 + chunk], x, bits))
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(part, jobs))
+    return sum(alg_bytes(N, K, bits) for _, _, _, _, _, bits, N, K in sample)
+
+
+def cpu_baseline(steps=2, warmup=1):
+    threads = os.cpu_count() or 1
+    sample = cpu_sample_setup()
+    for _ in range(warmup):
+        cpu_sample_step(sample, threads)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(steps):
+        nbytes += cpu_sample_step(sample, threads)
+    dt = time.perf_counter() - t0
+    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": "per step: one q_proj 4096x4096@8b + one gate_proj 11008x4096@2b + 4096 rows of lm_head@6b "
+                      "(dequantize + f32 mat-vec, numpy restatement of jang_tools/affine.py:445-463)",
+            "ms_per_step": dt / steps * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = cpu_sample_setup()
+    for _ in range(max(args.warmup, 0)):
+        cpu_sample_step(sample, threads)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(args.steps):
+        nbytes += cpu_sample_step(sample, threads)
+    dt = time.perf_counter() - t0
+    v = nbytes / dt / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": CONFIG,
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": "per step: one q_proj 4096x4096@8b + one gate_proj 11008x4096@2b + 4096 rows "
+                                       "of lm_head@6b, numpy dequantize + f32 mat-vec on all host threads"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# clocks sampling (read-only NVML)
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index):
+        self.samples, self.reasons, self._stop = [], set(), threading.Event()
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80, "sw_power_cap": 0x4}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.nv is not None:
+            self.t.join(timeout=1)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------
+# CUDA arm
+# --------------------------------------------------------------------------------------
+def build_stack(device):
+    import torch
+    import jangq_b200 as jq
+    linears = []
+    for i, (name, N, K, bits) in enumerate(stack_spec()):
+        g = torch.Generator(device=device)
+        g.manual_seed(1000 + i)
+        w = (torch.randn((N, K), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        linears.append(jq.JANGLinear.from_float(w, bits=bits, group_size=GS))
+        del w
+    return linears
+
+
+def run_cuda(args):
+    import torch
+    import torch.distributed as dist
+    import jangq_b200 as jq
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the CUDA arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    linears = build_stack(device)
+    plan = jq.GemvPlan(linears, m=1, dtype=torch.bfloat16, device=device)
+    g = torch.Generator(device=device)
+    g.manual_seed(7)
+    for buf in plan._xbuf.values():
+        buf.copy_(torch.randn(buf.shape, generator=g, device=device).to(torch.bfloat16))
+    for k, hb in plan._host_in.items():
+        hb.copy_(plan._xbuf[k].cpu())
+    plan.capture()
+
+    W, K = max(args.warmup, 3), args.steps
+    for _ in range(W):
+        plan.run()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        ev0.record()
+        for _ in range(K):
+            plan.run()
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    bytes_step = plan.algorithmic_bytes
+    value = world * bytes_step * K / (ms * 1e-3) / 1e9
+
+    # end to end through the public API with host buffers
+    for _ in range(3):
+        plan.run_host()
+    barrier()
+    t0 = time.perf_counter()
+    ev0.record()
+    for _ in range(K):
+        plan.run_host()
+    ev1.record()
+    barrier()
+    e2e_ms = max(ev0.elapsed_time(ev1), (time.perf_counter() - t0) * 1e3)
+    t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e = world * bytes_step * K / (e2e_ms * 1e-3) / 1e9
+
+    jq._lib.check(jq._lib.load().jq_device_status())
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        per_gpu = value / world
+        traffic = None
+        try:
+            traffic = json.load(open(os.path.join(ROOT, "profiles", "qgemv_traffic.json"))).get("dram_bytes_per_step")
+        except Exception:
+            pass
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic", "config": CONFIG,
+                "tokens_per_s_weight_stream_bound": world * K / (ms * 1e-3),
+                "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
+                             "frac": per_gpu / peak,
+                             "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650",
+                             "traffic": traffic, "kernel": "qgemv_mma_kernel (225 launches per step, averaged)"},
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": plan.h2d_bytes,
+                        "d2h_bytes_per_step": plan.d2h_bytes, "ms_per_step": e2e_ms / K},
+                "gpu_launches": plan.launches_per_run * K, "clocks": clk.summary()}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

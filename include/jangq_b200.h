@@ -1,0 +1,112 @@
+/*
+ * jangq_b200 — C ABI of the B200 (sm_100a) implementation of JANG's affine
+ * mixed-bit quantized-inference path.
+ *
+ * The reference (jjang-ai/jangq) has no FFI of its own: its operator boundary
+ * is the MLX Python op signature plus the tensor layout contract
+ * (FORMAT.md:57-91, docs/adoption/PORTING.md:62-116).  Each entry point below
+ * names the reference call it stands in for.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer valid on the device of `stream`;
+ *   - every call only enqueues work on `stream` (a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream) and returns without syncing;
+ *   - the caller owns every buffer, including workspaces; nothing here
+ *     allocates device memory;
+ *   - return value: JQ_OK or a JQ_E* status; jq_last_error() gives the detail
+ *     for the calling thread;
+ *   - tensor layout: codes uint32 [rows, K*bits/32] row-major, LSB-first
+ *     bitstream per row; scales/biases [rows, K/group_size];
+ *     dequant = code*scale + bias; bits in {2,3,4,5,6,8}; group_size in
+ *     {32,64,128}; K % group_size == 0; K*bits % 32 == 0.
+ */
+#ifndef JANGQ_B200_H
+#define JANGQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JQ_OK            0
+#define JQ_EINVAL        1   /* bad shape, alignment, dtype or null pointer   */
+#define JQ_EUNSUPPORTED  2   /* bits / group_size / size outside the kernels  */
+#define JQ_EWORKSPACE    3   /* caller workspace too small                    */
+#define JQ_ECUDA         4   /* a CUDA runtime call failed (see last error)   */
+#define JQ_ETIMEOUT      5   /* a bounded device-side wait ran out            */
+
+#define JQ_F32   0
+#define JQ_F16   1
+#define JQ_BF16  2
+
+/* jq_quantize flags */
+#define JQ_QUANT_F16_TINY_GUARD  1  /* numpy-mirror floor on |scale| for f16 sidecars
+                                       (jang_tools/affine.py:46-51); MLX itself has none */
+
+typedef void* jq_stream_t;
+
+int         jq_version(void);
+const char* jq_status_string(int status);
+const char* jq_last_error(void);
+
+/* K1. Affine group quantizer: stands in for mx.quantize(w, group_size, bits)
+ * (jang_tools/convert.py:602-645,1533-1554) and its numpy mirror
+ * quantize_native_affine_numpy (jang_tools/affine.py:193-276).
+ * w [rows,K] of w_dtype; codes are bit-exact with the reference for the same
+ * source dtype; scales/biases are written in sidecar_dtype. */
+int jq_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size,
+                int sidecar_dtype, int flags, uint32_t* codes, void* scales, void* biases,
+                jq_stream_t stream);
+
+/* K1b. Zero-point round-to-nearest quantizer, the converter's fallback when MLX
+ * is missing: quantize_tensor(method="rtn") (jang_tools/quantize.py:211-289,
+ * caller convert.py:1564-1592).  Sidecars are float16 as in the reference. */
+int jq_quantize_rtn(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size,
+                    int sidecar_dtype, uint32_t* codes, void* scales, void* biases,
+                    jq_stream_t stream);
+
+/* Dequantizer: mx.dequantize / dequantize_affine_numpy (jang_tools/affine.py:445-463,
+ * loader.py:469).  out [rows,K] of out_dtype; float32 output is bit-exact with the
+ * reference (product and sum rounded separately). */
+int jq_dequantize(const uint32_t* codes, const void* scales, const void* biases, int sidecar_dtype,
+                  int64_t rows, int64_t K, int bits, int group_size, void* out, int out_dtype,
+                  jq_stream_t stream);
+
+/* K2. Decode-shaped quantized mat-vec: mx.quantized_matmul(x, W, scales, biases,
+ * transpose=True, group_size, bits) for few activation rows
+ * (jang_tools/jangrt/linear.py:41-45, dots3/ops.py:44-52; qmv arithmetic
+ * dsv41/metal_decode.py:201-234).  y[M,N] = x[M,K] . deq(W)[N,K]^T, f32 accumulate.
+ * M <= JQ_QGEMV_MAX_M; x and y are row-major with leading dimensions ldx / ldy
+ * (elements).  x_dtype/y_dtype: JQ_BF16 or JQ_F16 (same type for both). */
+#define JQ_QGEMV_MAX_M 16
+int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes,
+             const void* scales, const void* biases, int sidecar_dtype, int64_t N, int64_t K,
+             int bits, int group_size, void* y, int y_dtype, int64_t ldy, jq_stream_t stream);
+
+/* One launch over several independent matrices (for example q/k/v, or gate/up,
+ * of one decoder layer, each with its own bit width): the same arithmetic as
+ * jq_qgemv per entry.  `descs` is a HOST array, copied into the launch. */
+typedef struct JqGemvDesc {
+    const void*     x;       /* [M, K] activations, leading dimension ldx        */
+    const uint32_t* codes;   /* [N, K*bits/32]                                   */
+    const void*     scales;  /* [N, K/group_size]                                */
+    const void*     biases;
+    void*           y;       /* [M, N], leading dimension ldy                    */
+    int64_t         N, K, ldx, ldy;
+    int32_t         bits, group_size;
+} JqGemvDesc;
+#define JQ_QGEMV_MAX_BATCH 8
+int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype,
+                     int sidecar_dtype, jq_stream_t stream);
+
+/* Reads the device-side status word (synchronises the device).  JQ_ETIMEOUT when a
+ * kernel's bounded wait on a copy in flight ran out since the library was loaded.
+ * No counterpart in the reference: its Metal path has no device-side waits. */
+int jq_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JANGQ_B200_H */

@@ -1,0 +1,150 @@
+"""Torch-facing ops with the signatures of the MLX calls the reference makes.
+
+    quantize          <-> mx.quantize            (jang_tools/convert.py:602-645,1533-1554)
+    dequantize        <-> mx.dequantize          (jang_tools/loader.py:469, affine.py:445-463)
+    quantized_matmul  <-> mx.quantized_matmul    (jang_tools/jangrt/linear.py:41-45)
+
+Tensors live on the current CUDA device; work is enqueued on the current
+torch stream.  Packed codes are returned as torch.int32 holding the same bits
+as MLX's uint32 (torch has few uint32 kernels); uint32 inputs are accepted.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import JangqError
+
+ALLOWED_BITS = (2, 3, 4, 5, 6, 8)
+ALLOWED_GROUP_SIZES = (32, 64, 128)
+
+
+def _as_i32(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype == torch.int32:
+        return t
+    if t.dtype == torch.uint32:
+        return t.view(torch.int32)
+    raise JangqError(_lib.JQ_EINVAL, f"packed codes must be uint32/int32, got {t.dtype}")
+
+
+def _check_triple(wq, scales, biases, bits, group_size):
+    if bits not in ALLOWED_BITS:
+        raise JangqError(_lib.JQ_EUNSUPPORTED, f"unsupported bits={bits}")
+    if group_size not in ALLOWED_GROUP_SIZES:
+        raise JangqError(_lib.JQ_EUNSUPPORTED, f"unsupported group_size={group_size}")
+    K = wq.shape[-1] * 32 // bits
+    if wq.shape[-1] * 32 % bits or K % group_size:
+        raise JangqError(_lib.JQ_EINVAL, f"packed width {wq.shape[-1]} does not match bits={bits}, "
+                                         f"group_size={group_size}")
+    if scales.shape != biases.shape or scales.dtype != biases.dtype:
+        raise JangqError(_lib.JQ_EINVAL, "scales and biases must share shape and dtype")
+    if tuple(scales.shape) != tuple(wq.shape[:-1]) + (K // group_size,):
+        raise JangqError(_lib.JQ_EINVAL, f"scales shape {tuple(scales.shape)} does not match codes "
+                                         f"{tuple(wq.shape)} at bits={bits}, group_size={group_size}")
+    return K
+
+
+def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dtype: torch.dtype | None = None,
+             f16_tiny_guard: bool = False, mode: str = "affine"):
+    """Affine group quantization along the last axis -> (wq, scales, biases).
+
+    The source dtype of `w` (float32/float16/bfloat16) is the arithmetic's input
+    precision, exactly as for mx.quantize; the converter feeds float16
+    (convert.py:1550).  Sidecars default to the source dtype.  mode="rtn" runs the
+    converter's zero-point fallback instead (quantize.py:211-289, float16 sidecars).
+    """
+    dev = _lib.require_cuda(w)
+    lib = _lib.load()
+    if w.dim() < 2:
+        raise JangqError(_lib.JQ_EINVAL, f"affine quantization expects a matrix, got {tuple(w.shape)}")
+    K = w.shape[-1]
+    lead = tuple(w.shape[:-1])
+    w2 = w.reshape(-1, K).contiguous()
+    rows = w2.shape[0]
+    if mode == "rtn" and sidecar_dtype is None:
+        sidecar_dtype = torch.float16
+    sdt = sidecar_dtype or w.dtype
+    if bits not in ALLOWED_BITS or group_size not in ALLOWED_GROUP_SIZES or K % group_size or (K * bits) % 32:
+        # let the library produce the precise message
+        pass
+    wq = torch.empty((rows, max(K * bits // 32, 0)), dtype=torch.int32, device=dev)
+    G = K // group_size if group_size in ALLOWED_GROUP_SIZES else 0
+    scales = torch.empty((rows, G), dtype=sdt, device=dev)
+    biases = torch.empty((rows, G), dtype=sdt, device=dev)
+    with torch.cuda.device(dev):
+        if mode == "affine":
+            flags = _lib.JQ_QUANT_F16_TINY_GUARD if f16_tiny_guard else 0
+            _lib.check(lib.jq_quantize(w2.data_ptr(), _lib.dtype_id(w2.dtype), rows, K, bits, group_size,
+                                       _lib.dtype_id(sdt), flags, wq.data_ptr(), scales.data_ptr(),
+                                       biases.data_ptr(), _lib.stream_ptr(dev)))
+        elif mode == "rtn":
+            _lib.check(lib.jq_quantize_rtn(w2.data_ptr(), _lib.dtype_id(w2.dtype), rows, K, bits, group_size,
+                                           _lib.dtype_id(sdt), wq.data_ptr(), scales.data_ptr(),
+                                           biases.data_ptr(), _lib.stream_ptr(dev)))
+        else:
+            raise JangqError(_lib.JQ_EINVAL, f"unknown quantize mode {mode!r}")
+    return wq.reshape(lead + (wq.shape[-1],)), scales.reshape(lead + (G,)), biases.reshape(lead + (G,))
+
+
+def dequantize(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64, bits: int = 4,
+               dtype: torch.dtype | None = None) -> torch.Tensor:
+    """code*scale + bias -> [.., K] in `dtype` (default: the sidecar dtype, as mx.dequantize)."""
+    dev = _lib.require_cuda(wq, scales, biases)
+    lib = _lib.load()
+    wq = _as_i32(wq)
+    K = _check_triple(wq, scales, biases, bits, group_size)
+    lead = tuple(wq.shape[:-1])
+    wq2, s2, b2 = wq.reshape(-1, wq.shape[-1]).contiguous(), scales.reshape(-1, scales.shape[-1]).contiguous(), \
+        biases.reshape(-1, biases.shape[-1]).contiguous()
+    rows = wq2.shape[0]
+    out = torch.empty((rows, K), dtype=dtype or scales.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_dequantize(wq2.data_ptr(), s2.data_ptr(), b2.data_ptr(), _lib.dtype_id(s2.dtype), rows, K,
+                                     bits, group_size, out.data_ptr(), _lib.dtype_id(out.dtype),
+                                     _lib.stream_ptr(dev)))
+    return out.reshape(lead + (K,))
+
+
+def _qgemv(x2: torch.Tensor, wq, scales, biases, K, bits, group_size, out: torch.Tensor):
+    lib = _lib.load()
+    dev = x2.device
+    M, N = x2.shape[0], wq.shape[0]
+    _lib.check(lib.jq_qgemv(x2.data_ptr(), _lib.dtype_id(x2.dtype), M, x2.stride(0), wq.data_ptr(), scales.data_ptr(),
+                            biases.data_ptr(), _lib.dtype_id(scales.dtype), N, K, bits, group_size, out.data_ptr(),
+                            _lib.dtype_id(out.dtype), out.stride(0), _lib.stream_ptr(dev)))
+
+
+def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
+                     transpose: bool = True, group_size: int = 64, bits: int = 4) -> torch.Tensor:
+    """y[.., N] = x[.., K] . deq(w)[N, K]^T with float32 accumulation, output in x's dtype.
+
+    Few rows (decode) run the bandwidth-bound mat-vec kernel; many rows (prefill)
+    run the tensor-core GEMM.  Only transpose=True (weights stored [N, K], the only
+    form the reference uses) is provided.
+    """
+    if not transpose:
+        raise JangqError(_lib.JQ_EUNSUPPORTED, "quantized_matmul: only transpose=True is provided")
+    dev = _lib.require_cuda(x, w, scales, biases)
+    w = _as_i32(w)
+    if w.dim() != 2:
+        raise JangqError(_lib.JQ_EINVAL, f"weight must be 2-D [N, K*bits/32], got {tuple(w.shape)}")
+    K = _check_triple(w, scales, biases, bits, group_size)
+    if x.shape[-1] != K:
+        raise JangqError(_lib.JQ_EINVAL, f"x has {x.shape[-1]} features, weight expects {K}")
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise JangqError(_lib.JQ_EINVAL, f"activations must be bfloat16 or float16, got {x.dtype}")
+    lead = tuple(x.shape[:-1])
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M, N = x2.shape[0], w.shape[0]
+    w, scales, biases = w.contiguous(), scales.contiguous(), biases.contiguous()
+    out = torch.empty((M, N), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        if M <= _lib.QGEMV_MAX_M:
+            if M > 0:
+                _qgemv(x2, w, scales, biases, K, bits, group_size, out)
+        else:
+            from .gemm import qgemm
+            qgemm(x2, w, scales, biases, K, bits, group_size, out)
+    return out.reshape(lead + (N,))

@@ -1,0 +1,101 @@
+"""Graph-captured decode plans.
+
+The reference found real decode to be dispatch-bound, not bandwidth-bound
+(jang_tools/dsv41/DECODE_DSPARK_METHODS.md:90-93) and fused its dispatches by
+hand.  On CUDA the same effect comes from capturing the launches of a decode
+step once and replaying them: `GemvPlan` captures one jq_qgemv per linear on a
+private stream into a CUDA graph; `run()` replays it, `run_host()` adds the
+host->device copy of the step's activations and the device->host copy of the
+last output.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from . import _lib
+from .linear import JANGLinear
+
+
+class GemvPlan:
+    """A fixed sequence of quantized mat-vecs (one per linear), batch `m` rows.
+
+    Every linear has its own input row buffer `x[i]` ([m, in_features]) and
+    output buffer `y[i]`; the caller (or `run_host`) fills the inputs.
+    """
+
+    def __init__(self, linears: Sequence[JANGLinear], m: int = 1, dtype: torch.dtype = torch.bfloat16,
+                 device=None, share_inputs: bool = True):
+        if m < 1 or m > _lib.QGEMV_MAX_M:
+            raise _lib.JangqError(_lib.JQ_EINVAL, f"GemvPlan takes 1..{_lib.QGEMV_MAX_M} rows")
+        self.linears = list(linears)
+        self.m, self.dtype = m, dtype
+        self.device = torch.device(device if device is not None else self.linears[0].weight.device)
+        # one input buffer per distinct in_features when sharing (a real decoder reuses the hidden state)
+        self._xbuf = {}
+        self.x, self.y = [], []
+        for lin in self.linears:
+            key = lin.in_features if share_inputs else len(self.x)
+            if key not in self._xbuf:
+                self._xbuf[key] = torch.zeros((m, lin.in_features), dtype=dtype, device=self.device)
+            self.x.append(self._xbuf[key])
+            self.y.append(torch.empty((m, lin.out_features), dtype=dtype, device=self.device))
+        self.algorithmic_bytes = sum(self.bytes_of(lin, m) for lin in self.linears)
+        self.launches_per_run = sum((m + 7) // 8 for _ in self.linears)
+        self._graph = None
+        self._host_in = {k: torch.zeros(v.shape, dtype=dtype).pin_memory() for k, v in self._xbuf.items()}
+        self._host_out = torch.zeros(self.y[-1].shape, dtype=dtype).pin_memory()
+
+    @staticmethod
+    def bytes_of(lin: JANGLinear, m: int) -> int:
+        """Algorithmic bytes of one mat-vec: codes + sidecars + activations in + out."""
+        n, k = lin.out_features, lin.in_features
+        e = lin.scales.element_size()
+        return n * k * lin.bits // 8 + n * (k // lin.group_size) * 2 * e + m * k * 2 + m * n * 2
+
+    def _enqueue(self):
+        from .ops import _qgemv
+        for lin, x, y in zip(self.linears, self.x, self.y):
+            _qgemv(x, lin.weight, lin.scales, lin.biases, lin.in_features, lin.bits, lin.group_size, y)
+
+    def capture(self):
+        """Record the launches into a CUDA graph (call once, before run())."""
+        with torch.cuda.device(self.device):
+            s = torch.cuda.Stream(self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                self._enqueue()            # warm-up outside capture (sets function attributes)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue()
+            self._graph = g
+        return self
+
+    def run(self):
+        """Replay on the current stream (falls back to direct launches before capture())."""
+        if self._graph is None:
+            self._enqueue()
+        else:
+            self._graph.replay()
+        return self.y
+
+    def run_host(self, host_inputs: dict | None = None) -> torch.Tensor:
+        """One step from host memory: pinned inputs -> device, replay, last output -> pinned host."""
+        src = host_inputs if host_inputs is not None else self._host_in
+        for k, buf in self._xbuf.items():
+            buf.copy_(src[k], non_blocking=True)
+        self.run()
+        self._host_out.copy_(self.y[-1], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self._host_out
+
+    @property
+    def h2d_bytes(self) -> int:
+        return sum(v.numel() * v.element_size() for v in self._xbuf.values())
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self._host_out.numel() * self._host_out.element_size()

@@ -1,0 +1,326 @@
+"""CPU oracle for the JANG affine quantized-inference path.
+
+TEST INFRASTRUCTURE ONLY.  This module is a numpy restatement of the
+reference's algorithm; it exists so that tests, the smoke check and the
+bench's CPU-baseline leg can check (and time) the CUDA path against it.
+The product package never imports it: the product path has no CPU fallback
+and fails loudly when the CUDA library is missing.
+
+Parity status: the quantizer, packer and dequantizer are pinned against
+the reference's own numpy code (jang-tools/jang_tools/affine.py, pack.py,
+quantize.py, imported when the reference tree is mounted) and against the
+reference's MLX-generated golden vector
+(jang-runtime/Tests/JANGCoreMetalTests/fixtures/matmul_4bit_64x128.safetensors);
+see tests/golden/make_golden.py and tests/test_oracle_golden.py.  The
+matmul and gather_qmm arithmetic lives in the un-vendored third-party
+packages mlx 0.31.2 / mlx-lm 0.31.3 (jang-tools/uv.lock:910-962); it is
+restated from the reference's decoder (affine.py:445-463), its in-repo
+transcription of the MLX qmv order (dsv41/metal_decode.py:201-234) and the
+golden vector's y_ref.  The plain softmax-top-k router lives in mlx-lm
+only: parity unpinned for that one function.
+
+Every function cites the reference lines it follows (paths are relative
+to the reference project's root).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+ALLOWED_BITS = (2, 3, 4, 5, 6, 8)          # jang_tools/affine.py:210
+ALLOWED_GROUP_SIZES = (32, 64, 128)        # jang_tools/affine.py:27
+
+# smallest normal float16, the mirror-only scale floor (affine.py:43)
+_FP16_TINY = np.float32(np.finfo(np.float16).smallest_normal)
+
+
+# --------------------------------------------------------------------------
+# dtype helpers (bf16 by hand so that the oracle needs numpy only)
+# --------------------------------------------------------------------------
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round float32 to bfloat16 (round-to-nearest-even), return uint16 bits."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    rounded = (u + (0x7FFF + ((u >> 16) & 1))) >> 16
+    rounded = np.where(nan, (u >> 16) | 0x0040, rounded)
+    return rounded.astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (np.asarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def round_to(x: np.ndarray, dtype: str) -> np.ndarray:
+    """Return float32 values rounded to `dtype` ('f32' | 'f16' | 'bf16')."""
+    x = np.asarray(x, dtype=np.float32)
+    if dtype == "f32":
+        return x
+    if dtype == "f16":
+        with np.errstate(over="ignore"):
+            return x.astype(np.float16).astype(np.float32)
+    if dtype == "bf16":
+        return bf16_bits_to_f32(f32_to_bf16_bits(x)).reshape(x.shape)
+    raise ValueError(f"unknown dtype {dtype!r}")
+
+
+# --------------------------------------------------------------------------
+# a1: bit packing  (jang_tools/pack.py:12-82 pack, :85-149 unpack)
+# --------------------------------------------------------------------------
+def pack_rows(codes: np.ndarray, bits: int) -> np.ndarray:
+    """LSB-first bitstream per row, viewed as little-endian uint32 words.
+
+    Code j of a row occupies bits [j*bits, j*bits+bits) of that row's stream
+    (pack.py:28-82); rows are packed independently and the stream is re-viewed
+    as uint32 [rows, K*bits/32] (affine.py:256-265).
+    """
+    codes = np.asarray(codes, dtype=np.uint8)
+    rows, K = codes.shape
+    if (K * bits) % 32:
+        raise ValueError(f"packed row is not uint32-aligned: columns={K}, bits={bits}")
+    shifts = np.arange(bits, dtype=np.uint8)
+    bitplane = ((codes[:, :, None] >> shifts) & 1).astype(np.uint8)
+    stream = np.packbits(bitplane.reshape(rows, K * bits), axis=1, bitorder="little")
+    return np.ascontiguousarray(stream).view("<u4").reshape(rows, K * bits // 32)
+
+
+def unpack_rows(packed: np.ndarray, bits: int, K: int | None = None) -> np.ndarray:
+    """Inverse of pack_rows -> uint8 [rows, K] (pack.py:85-149, vectorised for
+    every width; the reference's 3/5/6-bit branch is a per-element loop)."""
+    packed = np.ascontiguousarray(packed, dtype="<u4")
+    rows, words = packed.shape
+    if K is None:
+        K = words * 32 // bits
+    stream = np.unpackbits(packed.view(np.uint8).reshape(rows, words * 4), axis=1,
+                           bitorder="little")
+    bitplane = stream[:, : K * bits].reshape(rows, K, bits)
+    weights = (1 << np.arange(bits)).astype(np.uint8)
+    return (bitplane * weights).sum(axis=2, dtype=np.uint8)
+
+
+# --------------------------------------------------------------------------
+# a2: affine group quantizer (jang_tools/affine.py:193-276, mirror of MLX
+#     affine_quantize; converter call sites convert.py:602-645,1533-1554)
+# --------------------------------------------------------------------------
+def quantize_affine_codes(w: np.ndarray, bits: int, group_size: int, src_dtype: str = "f16",
+                          sidecar_dtype: str | None = None, f16_tiny_guard: bool = False):
+    """Return (codes uint8 [rows,K], scales f32 [rows,K/gs], biases f32 [rows,K/gs]).
+
+    Scales/biases are float32 arrays holding values already rounded to
+    `sidecar_dtype` (default: the source dtype, affine.py:254-255).  The source
+    is first rounded to `src_dtype` (affine.py:212 casts to float16; the MLX
+    kernel itself takes f32/f16/bf16 and the golden vector was made from f32).
+    `f16_tiny_guard` reproduces the numpy mirror's `_to_f16_nonzero`
+    (affine.py:46-51), which MLX does not do; it only matters for f16 sidecars.
+    """
+    if bits not in ALLOWED_BITS:
+        raise ValueError(f"unsupported native affine bits={bits}")
+    if group_size not in ALLOWED_GROUP_SIZES:
+        raise ValueError(f"unsupported affine group_size={group_size}")
+    w = np.asarray(w)
+    if w.ndim != 2:
+        raise ValueError(f"affine quantization expects a 2D matrix, got {w.shape}")
+    rows, K = w.shape
+    if K % group_size:
+        raise ValueError(f"input dimension {K} is not divisible by group_size={group_size}")
+    if (K * bits) % 32:
+        raise ValueError(f"packed row is not uint32-aligned: columns={K}, bits={bits}")
+    sidecar_dtype = sidecar_dtype or src_dtype
+    G = K // group_size
+    bins = np.float32((1 << bits) - 1)
+    g = round_to(w, src_dtype).reshape(rows, G, group_size)          # affine.py:212,227-229
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        lo = g.min(axis=-1)                                          # :230
+        hi = np.maximum(g.max(axis=-1), np.float32(0.0))             # :233 (max seeded with 0)
+        scale = np.maximum((hi - lo) / bins, np.float32(1e-7))       # :234
+        dom_lo = np.abs(lo) > np.abs(hi)                             # :235
+        scale = np.where(dom_lo, scale, -scale)                      # :236
+        edge = np.where(dom_lo, lo, hi)                              # :237
+        q0 = np.rint(edge / scale)                                   # :238 (half-to-even)
+        at_zero = q0 == 0                                            # :239
+        refined = np.where(at_zero, scale, edge / np.where(at_zero, np.float32(1), q0))
+        scale = refined.astype(np.float32)                           # :240-246
+        bias = np.where(at_zero, np.float32(0.0), edge).astype(np.float32)   # :247
+        q = np.minimum(np.rint((g - bias[..., None]) / scale[..., None]), bins)  # :248-250
+    codes = np.nan_to_num(q, nan=0.0).clip(0, float(bins)).astype(np.uint8)
+    s = scale
+    if f16_tiny_guard and sidecar_dtype == "f16":                    # affine.py:46-51
+        s = np.where(np.abs(s) < _FP16_TINY,
+                     np.copysign(_FP16_TINY, np.where(s == 0, np.float32(1.0), s)), s)
+    return (codes.reshape(rows, K), round_to(s, sidecar_dtype).reshape(rows, G),
+            round_to(bias, sidecar_dtype).reshape(rows, G))
+
+
+def quantize_affine(w, bits, group_size, src_dtype="f16", sidecar_dtype=None, f16_tiny_guard=False):
+    """(packed uint32 [rows, K*bits/32], scales, biases) — see quantize_affine_codes."""
+    codes, s, b = quantize_affine_codes(w, bits, group_size, src_dtype, sidecar_dtype, f16_tiny_guard)
+    return pack_rows(codes, bits), s, b
+
+
+# --------------------------------------------------------------------------
+# a3: RTN zero-point quantizer, the converter's no-MLX fallback
+#     (jang_tools/quantize.py:127-208 else-branch, :211-289; convert.py:1564-1592)
+# --------------------------------------------------------------------------
+def quantize_rtn_codes(w: np.ndarray, bits: int, group_size: int = 64):
+    """Return (codes, scales, biases) with f16-rounded sidecars held in float32.
+
+    Blocks are consecutive `group_size` runs of the flattened [rows, K] tensor
+    (quantize.py:238-256), identical to per-row groups when K % group_size == 0.
+    """
+    w = np.asarray(w, dtype=np.float32)
+    rows, K = w.shape
+    if K % group_size:
+        raise ValueError("K must be a multiple of group_size")
+    L = np.float32((1 << bits) - 1)
+    blk = w.reshape(-1, group_size)
+    wmin = blk.min(axis=1)                                           # quantize.py:148-149
+    wmax = blk.max(axis=1)
+    const = wmax == wmin                                             # :152
+    rng = wmax - wmin                                                # :193-194
+    rng[const] = 1.0
+    scale = (rng / L).astype(np.float32)                             # :196
+    zero = np.clip(np.round(-wmin / scale), 0, L)                    # :197-198
+    q = np.clip(np.round(blk / scale[:, None] + zero[:, None]), 0, L).astype(np.uint8)  # :200-201
+    scale[const] = 1.0                                               # :203-205
+    zero[const] = 0.0
+    q[const] = 0
+    scales = round_to(scale, "f16")                                  # :278
+    biases = round_to((-scale * zero).astype(np.float32), "f16")     # :279
+    G = K // group_size
+    return q.reshape(rows, K), scales.reshape(rows, G), biases.reshape(rows, G)
+
+
+def quantize_rtn(w, bits, group_size=64):
+    codes, s, b = quantize_rtn_codes(w, bits, group_size)
+    return pack_rows(codes, bits), s, b
+
+
+# --------------------------------------------------------------------------
+# a4: dequantizer (jang_tools/affine.py:445-463; docs/adoption/PORTING.md:80-116)
+# --------------------------------------------------------------------------
+def dequantize_affine(packed, scales, biases, bits: int, group_size: int) -> np.ndarray:
+    """W[i,j] = code[i,j]*scales[i,j//gs] + biases[i,j//gs] in float32, the
+    product and the sum rounded separately (numpy: two float32 operations)."""
+    packed = np.asarray(packed)
+    rows = packed.shape[0]
+    K = packed.shape[1] * 32 // bits
+    codes = unpack_rows(packed, bits, K).astype(np.float32).reshape(rows, K // group_size, group_size)
+    s = np.asarray(scales, dtype=np.float32)[..., None]
+    b = np.asarray(biases, dtype=np.float32)[..., None]
+    return (codes * s + b).reshape(rows, K)
+
+
+# --------------------------------------------------------------------------
+# a5/a6: quantized matmul  y = x . deq(W)^T
+#   arithmetic: affine.py:457-463 + JangV2QuantMatmul.metal:50-70 (dequant then
+#   f32 dot); MLX qmv order transcribed at dsv41/metal_decode.py:201-234
+# --------------------------------------------------------------------------
+def qmatmul(x, packed, scales, biases, bits: int, group_size: int, acc=np.float64) -> np.ndarray:
+    """Y[M,N] = X[M,K] . deq(W)[N,K]^T, accumulated in `acc`, returned as f32."""
+    W = dequantize_affine(packed, scales, biases, bits, group_size)
+    x = np.atleast_2d(np.asarray(x, dtype=np.float32))
+    return (x.astype(acc) @ W.astype(acc).T).astype(np.float32)
+
+
+def qmatmul_group_order(x, packed, scales, biases, bits: int, group_size: int) -> np.ndarray:
+    """Same product in the MLX qmv order: per group s*sum(q*x) + b*sum(x), f32
+    (dsv41/metal_decode.py:201-234).  Small shapes only."""
+    packed = np.asarray(packed)
+    N = packed.shape[0]
+    K = packed.shape[1] * 32 // bits
+    G = K // group_size
+    q = unpack_rows(packed, bits, K).astype(np.float32).reshape(N, G, group_size)
+    x = np.atleast_2d(np.asarray(x, dtype=np.float32)).reshape(-1, G, group_size)
+    qx = np.einsum("ngk,mgk->mng", q, x).astype(np.float32)
+    sx = x.sum(axis=-1, dtype=np.float32)
+    s = np.asarray(scales, dtype=np.float32)
+    b = np.asarray(biases, dtype=np.float32)
+    return (qx * s[None] + sx[:, None, :] * b[None]).sum(axis=-1, dtype=np.float32)
+
+
+# --------------------------------------------------------------------------
+# a9: router.  Plain softmax top-k lives in mlx-lm (un-vendored): parity
+#     unpinned.  The normalisation form follows dots3/ops.py:159-162.
+# --------------------------------------------------------------------------
+def route_softmax_topk(logits: np.ndarray, k: int, renorm: bool = True, scale: float = 1.0):
+    """(idx int32 [T,k], w f32 [T,k]); ties go to the lower expert id
+    (dsv41/metal_decode.py:1141), experts are listed by descending score."""
+    z = np.asarray(logits, dtype=np.float32)
+    z = z - z.max(axis=-1, keepdims=True)
+    p = np.exp(z)
+    p = p / p.sum(axis=-1, keepdims=True, dtype=np.float32)
+    idx = np.argsort(-p, axis=-1, kind="stable")[:, :k]
+    w = np.take_along_axis(p, idx, axis=-1)
+    if renorm:
+        w = w / (w.sum(axis=-1, keepdims=True, dtype=np.float32) + np.float32(1e-20))
+    return idx.astype(np.int32), (w * np.float32(scale)).astype(np.float32)
+
+
+# --------------------------------------------------------------------------
+# a7: routed MoE (gather_qmm semantics)
+#   naive loop: dots3/ops_selftest.py:18-27; layer logic dsv41/model.py:1206-1245
+#   and dots3/ops.py:195-223
+# --------------------------------------------------------------------------
+def moe_sort(idx: np.ndarray, num_experts: int):
+    """order = stable argsort of the flat expert ids, inv = argsort(order),
+    offsets[e] = first sorted row of expert e (dsv41/model.py:1207-1212)."""
+    flat = np.asarray(idx).reshape(-1)
+    order = np.argsort(flat, kind="stable").astype(np.int32)
+    inv = np.argsort(order, kind="stable").astype(np.int32)
+    counts = np.bincount(flat, minlength=num_experts)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    return order, inv, offsets
+
+
+def gather_qmm(x, packed, scales, biases, rhs_indices, bits, group_size, lhs_indices=None):
+    """y[r] = x[lhs[r]] . deq(W[rhs[r]])^T  (dots3/ops.py:168-192 call shape).
+    x [R0,K]; packed [E,N,Kp]; rhs_indices [R]; lhs_indices [R] or None (identity)."""
+    x = np.asarray(x, dtype=np.float32)
+    rhs = np.asarray(rhs_indices).reshape(-1)
+    lhs = np.arange(rhs.size) if lhs_indices is None else np.asarray(lhs_indices).reshape(-1)
+    E, N, _ = np.asarray(packed).shape
+    out = np.zeros((rhs.size, N), np.float32)
+    for e in np.unique(rhs):
+        rowsel = np.nonzero(rhs == e)[0]
+        W = dequantize_affine(packed[e], scales[e], biases[e], bits, group_size)
+        out[rowsel] = (x[lhs[rowsel]].astype(np.float64) @ W.astype(np.float64).T).astype(np.float32)
+    return out
+
+
+def _silu(g):
+    return g / (1.0 + np.exp(-g))
+
+
+def moe_layer(x, idx, w, gate, up, down, *, swiglu_limit: float = 0.0, act_dtype: str = "bf16",
+              shared=None) -> np.ndarray:
+    """Routed-expert SwiGLU layer, float32 result [T,D].
+
+    gate/up/down are tuples (packed[E,N,Kp], scales, biases, bits, group_size).
+    Follows dsv41/model.py:1214-1245: gate/up in the activation dtype -> f32,
+    optional clamp, h = silu(g)*u*w[t,k] (weight applied before down), h cast to
+    the activation dtype, down, f32 sum over the k slots, plus an optional shared
+    expert `shared` = (gate, up, down) of 2-D triples (model.py:1237-1245).
+    """
+    x = round_to(x, act_dtype)
+    T, D = x.shape
+    k = idx.shape[1]
+    flat = np.asarray(idx).reshape(-1)
+    lhs = np.repeat(np.arange(T), k)
+    g = round_to(gather_qmm(x, *gate[:3], flat, gate[3], gate[4], lhs), act_dtype)
+    u = round_to(gather_qmm(x, *up[:3], flat, up[3], up[4], lhs), act_dtype)
+    if swiglu_limit > 0:
+        u = np.clip(u, -swiglu_limit, swiglu_limit)
+        g = np.minimum(g, swiglu_limit)
+    h = (_silu(g.astype(np.float32)) * u).astype(np.float32)
+    h = h * np.asarray(w, dtype=np.float32).reshape(-1)[:, None]
+    h = round_to(h, act_dtype)
+    y = round_to(gather_qmm(h, *down[:3], flat, down[3], down[4]), act_dtype)
+    out = y.reshape(T, k, D).sum(axis=1, dtype=np.float32)
+    if shared is not None:
+        sg, su, sd = shared
+        g2 = round_to(qmatmul(x, *sg), act_dtype)
+        u2 = round_to(qmatmul(x, *su), act_dtype)
+        if swiglu_limit > 0:
+            u2 = np.clip(u2, -swiglu_limit, swiglu_limit)
+            g2 = np.minimum(g2, swiglu_limit)
+        h2 = round_to((_silu(g2) * u2).astype(np.float32), act_dtype)
+        out = out + round_to(qmatmul(h2, *sd), act_dtype)
+    return out.astype(np.float32)

@@ -1,0 +1,127 @@
+"""GPU parity of the decode mat-vec (jq_qgemv through quantized_matmul) against
+the CPU oracle.  Tolerance (BASELINE north star): max |y-ref| / max|ref| <= 1e-2
+and cosine >= 0.9999; the tensor-core path is additionally held to an
+elementwise bound of one output rounding step plus 2e-3 of max|ref|."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import jangq_b200 as jq
+from jangq_b200 import _lib
+from oracle import jang_oracle as jo
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def make_case(N, K, bits, gs, M, dtype, seed=0):
+    rng = np.random.default_rng(seed)
+    w = torch.from_numpy((rng.standard_normal((N, K)) * 0.02).astype(np.float32)).to(DEV).to(dtype)
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(DEV).to(dtype)
+    wq, s, b = jq.quantize(w, gs, bits)
+    return x, wq, s, b
+
+
+def reference(x, wq, s, b, bits, gs):
+    return jo.qmatmul(x.float().cpu().numpy(), wq.cpu().numpy().view(np.uint32), s.float().cpu().numpy(),
+                      b.float().cpu().numpy(), bits, gs)
+
+
+def check(y, ref, dtype, tight=True):
+    y = y.float().cpu().numpy()
+    scale = np.abs(ref).max()
+    assert np.abs(y - ref).max() / scale <= 1e-2
+    cos = float((y * ref).sum() / (np.linalg.norm(y) * np.linalg.norm(ref)))
+    assert cos >= 0.9999
+    if tight:
+        ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+        assert np.all(np.abs(y - ref) <= ulp * np.abs(ref) + 2e-3 * scale)
+
+
+@pytest.mark.parametrize("M", (1, 3, 8, 13))
+@pytest.mark.parametrize("gs", (64, 128))
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+def test_qgemv_bf16(bits, gs, M):
+    x, wq, s, b = make_case(176, 2048, bits, gs, M, torch.bfloat16, seed=bits + gs + M)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
+    assert y.shape == (M, 176) and y.dtype == torch.bfloat16
+    check(y, reference(x, wq, s, b, bits, gs), torch.bfloat16)
+
+
+@pytest.mark.parametrize("bits", (2, 3, 4, 6, 8))
+def test_qgemv_f16(bits):
+    x, wq, s, b = make_case(96, 1024, bits, 64, 2, torch.float16, seed=bits)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=bits)
+    check(y, reference(x, wq, s, b, bits, 64), torch.float16)
+
+
+@pytest.mark.parametrize("N,K", ((50, 1472), (1, 64), (17, 11008), (333, 768), (16, 8192)))
+@pytest.mark.parametrize("bits", (2, 3, 4, 6, 8))
+def test_qgemv_ragged_shapes(bits, N, K):
+    """Row counts that are not a multiple of the 16-row tile, K that is not a
+    multiple of the stage length, single-group rows; 3-bit rows whose pitch is not
+    16-byte aligned take the general kernel."""
+    x, wq, s, b = make_case(N, K, bits, 64, 2, torch.bfloat16, seed=N + K)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=bits)
+    check(y, reference(x, wq, s, b, bits, 64), torch.bfloat16)
+
+
+@pytest.mark.parametrize("bits", (2, 4, 5, 8))
+def test_qgemv_group32_general_kernel(bits):
+    x, wq, s, b = make_case(40, 512, bits, 32, 3, torch.bfloat16, seed=9)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=32, bits=bits)
+    check(y, reference(x, wq, s, b, bits, 32), torch.bfloat16)
+
+
+def test_qgemv_mixed_sidecar_dtype_general_kernel():
+    x, wq, s, b = make_case(64, 512, 4, 64, 1, torch.bfloat16, seed=4)
+    s16, b16 = s.to(torch.float16), b.to(torch.float16)
+    y = jq.quantized_matmul(x, wq, s16, b16, group_size=64, bits=4)
+    check(y, reference(x, wq, s16, b16, 4, 64), torch.bfloat16)
+
+
+def test_qgemv_config1_full_size():
+    """BASELINE config 1: y = W.x for the 4096x4096 4-bit group-64 tensor, batch 1."""
+    x, wq, s, b = make_case(4096, 4096, 4, 64, 1, torch.bfloat16, seed=0)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=4)
+    check(y, reference(x, wq, s, b, 4, 64), torch.bfloat16)
+    # linearity in x at full size: W.(2x) == 2 W.x exactly (power-of-two scaling)
+    y2 = jq.quantized_matmul(x * 2, wq, s, b, group_size=64, bits=4)
+    assert torch.equal(y2, y * 2)
+
+
+def test_qgemv_leading_dimensions_and_canaries():
+    """Call the C ABI directly with ldx/ldy larger than the row length; the
+    padding must come back untouched."""
+    lib = _lib.load()
+    N, K, M, bits, gs = 70, 1024, 3, 4, 64
+    x, wq, s, b = make_case(N, K, bits, gs, M, torch.bfloat16, seed=21)
+    ldx, ldy = K + 64, N + 10
+    xp = torch.full((M, ldx), 7.0, dtype=torch.bfloat16, device=DEV)
+    xp[:, :K] = x
+    yp = torch.full((M + 1, ldy), -3.0, dtype=torch.bfloat16, device=DEV)
+    rc = lib.jq_qgemv(xp.data_ptr(), _lib.JQ_BF16, M, ldx, wq.data_ptr(), s.data_ptr(), b.data_ptr(), _lib.JQ_BF16,
+                      N, K, bits, gs, yp.data_ptr(), _lib.JQ_BF16, ldy, _lib.stream_ptr())
+    _lib.check(rc)
+    torch.cuda.synchronize()
+    check(yp[:M, :N], reference(x, wq, s, b, bits, gs), torch.bfloat16)
+    assert bool((yp[:M, N:] == -3.0).all()) and bool((yp[M] == -3.0).all())
+
+
+def test_general_kernel_matches_on_standard_shape():
+    x, wq, s, b = make_case(128, 1024, 6, 64, 4, torch.bfloat16, seed=6)
+    ref = reference(x, wq, s, b, 6, 64)
+    os.environ["JANGQ_FORCE_SIMPLE_GEMV"] = "1"
+    try:
+        y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=6)
+    finally:
+        os.environ.pop("JANGQ_FORCE_SIMPLE_GEMV")
+    check(y, ref, torch.bfloat16)
+
+
+def test_device_status_clean():
+    torch.cuda.synchronize()
+    assert _lib.load().jq_device_status() == 0

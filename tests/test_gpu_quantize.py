@@ -1,0 +1,166 @@
+"""GPU parity of the affine quantizer, the RTN fallback and the dequantizer
+against the CPU oracle and the reference-made golden vectors.  Integer outputs
+(packed codes) and the stored sidecars must be bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import jangq_b200 as jq
+from oracle import jang_oracle as jo
+
+pytestmark = pytest.mark.gpu
+
+BITS = (2, 3, 4, 5, 6, 8)
+GSS = (32, 64, 128)
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def to_np_u32(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+def f32(t):
+    return t.float().cpu().numpy()
+
+
+def adversarial(rng, rows, K, gs):
+    w = (rng.standard_normal((rows, K)) * 0.02).astype(np.float32)
+    g = w.reshape(rows, K // gs, gs)
+    g[0, 0] = 0.0
+    g[1, 0] = 0.0371
+    g[2, 0] = -0.0371
+    g[3, 0] = np.abs(g[3, 0])
+    g[4, 0] = -np.abs(g[4, 0])
+    g[5, 0, 7] = 3.5
+    g[6, 0, 3] = -3.5
+    g[7, -1] = np.linspace(-1.0, 1.0, gs)
+    g[8, -1] = np.arange(gs) * 0.5
+    g[9, -1] = np.concatenate([[0.0, 0.5, 1.5, 3.0], np.zeros(gs - 4)])
+    g[10, -1] = np.where(np.arange(gs) % 2 == 0, 0.0, -0.0)
+    g[11, -1] = 1e-9 * rng.standard_normal(gs)
+    g[12, -1] = np.arange(gs) - gs / 2 + 0.5            # many exact .5 ties after scaling
+    return g.reshape(rows, K)
+
+
+@pytest.mark.parametrize("gs", GSS)
+@pytest.mark.parametrize("bits", BITS)
+def test_golden_reference_vectors(golden_dir, bits, gs):
+    z = np.load(os.path.join(golden_dir, "affine_ref.npz"))
+    key = f"b{bits}_g{gs}"
+    w = torch.from_numpy(z[key + "_w"]).to(dev())
+    wq, s, b = jq.quantize(w, gs, bits, f16_tiny_guard=True)
+    assert np.array_equal(to_np_u32(wq), z[key + "_packed"])
+    assert np.array_equal(s.cpu().numpy(), z[key + "_scales"])
+    assert np.array_equal(b.cpu().numpy(), z[key + "_biases"])
+    deq = jq.dequantize(wq, s, b, gs, bits, dtype=torch.float32)
+    assert np.array_equal(deq.cpu().numpy(), z[key + "_deq"])
+
+
+def test_mlx_golden_vector(golden_dir):
+    z = np.load(os.path.join(golden_dir, "mlx_matmul_4bit_64x128.npz"))
+    rng = np.random.default_rng(int(z["seed"]))
+    W = rng.standard_normal((128, 64)).astype(np.float32)
+    x = rng.standard_normal((64,)).astype(np.float16)
+    wq, s, b = jq.quantize(torch.from_numpy(W).to(dev()), 64, 4, sidecar_dtype=torch.float16)
+    assert np.array_equal(to_np_u32(wq), z["packed"])
+    assert np.array_equal(s.cpu().numpy(), z["scales"])
+    assert np.array_equal(b.cpu().numpy(), z["biases"])
+    y = jq.quantized_matmul(torch.from_numpy(x).to(dev())[None, :], wq, s, b, group_size=64, bits=4)[0]
+    y = y.float().cpu().numpy()
+    y_ref = z["y_ref"]
+    # tolerance of the reference's own consumer of this vector (QuantizedMatmul4Tests.swift:83-84);
+    # the output here is float16, hence the extra half-ulp term
+    assert np.all(np.abs(y - y_ref) < 1e-2 + 2.0 ** -11 * np.abs(y_ref))
+
+
+@pytest.mark.parametrize("src", ("bf16", "f16", "f32"))
+@pytest.mark.parametrize("gs", GSS)
+@pytest.mark.parametrize("bits", BITS)
+def test_affine_bit_exact_vs_oracle(bits, gs, src):
+    rng = np.random.default_rng(bits * 1000 + gs)
+    w = adversarial(rng, 48, 1280, gs)
+    wt = torch.from_numpy(w).to(dev()).to(TORCH_DT[src])
+    wq, s, b = jq.quantize(wt, gs, bits)
+    pk, so, bo = jo.quantize_affine(f32(wt), bits, gs, src_dtype=src)
+    assert np.array_equal(to_np_u32(wq), pk)
+    assert np.array_equal(f32(s), so)
+    assert np.array_equal(f32(b), bo)
+    assert s.dtype == TORCH_DT[src]
+
+
+@pytest.mark.parametrize("bits", (2, 3, 4, 6, 8))
+def test_rtn_golden(golden_dir, bits):
+    z = np.load(os.path.join(golden_dir, "rtn_ref.npz"))
+    wq, s, b = jq.quantize(torch.from_numpy(z["w"]).to(dev()), 64, bits, mode="rtn")
+    assert np.array_equal(to_np_u32(wq), z[f"b{bits}_packed"])
+    assert np.array_equal(s.cpu().numpy(), z[f"b{bits}_scales"])
+    assert np.array_equal(b.cpu().numpy(), z[f"b{bits}_biases"])
+
+
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+def test_rtn_vs_oracle(bits):
+    rng = np.random.default_rng(5 + bits)
+    w = (rng.standard_normal((40, 768)) * 0.02).astype(np.float32)
+    w[3, 64:128] = -0.125
+    wq, s, b = jq.quantize(torch.from_numpy(w).to(dev()), 64, bits, mode="rtn")
+    pk, so, bo = jo.quantize_rtn(w, bits, 64)
+    assert np.array_equal(to_np_u32(wq), pk)
+    assert np.array_equal(f32(s), so) and np.array_equal(f32(b), bo)
+
+
+def test_config1_full_size_bit_exact():
+    """BASELINE config 1: 4096x4096 N(0,0.02) seed 0, 4-bit, group 64, bf16."""
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((4096, 4096)) * 0.02).astype(np.float32)
+    wt = torch.from_numpy(w).to(dev()).to(torch.bfloat16)
+    wq, s, b = jq.quantize(wt, 64, 4)
+    pk, so, bo = jo.quantize_affine(f32(wt), 4, 64, src_dtype="bf16")
+    assert np.array_equal(to_np_u32(wq), pk)
+    assert np.array_equal(f32(s), so) and np.array_equal(f32(b), bo)
+    # round trip: every weight is reproduced to within half a quantization step (+ sidecar rounding)
+    deq = jq.dequantize(wq, s, b, 64, 4, dtype=torch.float32)
+    err = (deq - wt.float()).abs().reshape(4096, 64, 64)
+    step = s.float().abs()[..., None]
+    slack = 2.0 ** -8 * (15 * step + b.float().abs()[..., None])     # bf16 rounding of the stored sidecars
+    assert bool((err <= 0.5 * step + slack).all())
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_dequantize_dtypes(bits):
+    rng = np.random.default_rng(11)
+    w = torch.from_numpy((rng.standard_normal((32, 512)) * 0.02).astype(np.float32)).to(dev()).to(torch.bfloat16)
+    wq, s, b = jq.quantize(w, 64, bits)
+    ref = jo.dequantize_affine(to_np_u32(wq), f32(s), f32(b), bits, 64)
+    assert np.array_equal(jq.dequantize(wq, s, b, 64, bits, dtype=torch.float32).cpu().numpy(), ref)
+    assert np.array_equal(f32(jq.dequantize(wq, s, b, 64, bits)), jo.round_to(ref, "bf16"))
+    assert np.array_equal(f32(jq.dequantize(wq, s, b, 64, bits, dtype=torch.float16)), jo.round_to(ref, "f16"))
+
+
+def test_stacked_experts_and_empty():
+    rng = np.random.default_rng(2)
+    w = torch.from_numpy((rng.standard_normal((3, 16, 256)) * 0.02).astype(np.float32)).to(dev()).to(torch.float16)
+    wq, s, b = jq.quantize(w, 64, 3)
+    assert wq.shape == (3, 16, 24) and s.shape == (3, 16, 4)
+    pk, so, bo = jo.quantize_affine(f32(w).reshape(48, 256), 3, 64, src_dtype="f16")
+    assert np.array_equal(to_np_u32(wq).reshape(48, 24), pk)
+    e = torch.empty((0, 128), dtype=torch.bfloat16, device=dev())
+    wq, s, b = jq.quantize(e, 64, 4)
+    assert wq.shape == (0, 16) and s.shape == (0, 2)
+
+
+def test_shape_errors():
+    w = torch.zeros((4, 100), dtype=torch.float16, device=dev())
+    with pytest.raises(jq.JangqError, match="not divisible by group_size"):
+        jq.quantize(w, 64, 4)
+    with pytest.raises(jq.JangqError):
+        jq.quantize(torch.zeros((4, 128), dtype=torch.float16, device=dev()), 64, 7)
+    with pytest.raises(jq.JangqError):
+        jq.quantize(torch.zeros((4, 128), dtype=torch.float16, device=dev()), 48, 4)
+    with pytest.raises(jq.JangqError, match="uint32-aligned"):
+        jq.quantize(torch.zeros((4, 32), dtype=torch.float16, device=dev()), 32, 3)
