@@ -1,0 +1,131 @@
+"""Single-op micro-benchmark with an HBM-resident working set.
+
+    python -m jangq_b200.microbench --op qgemv --N 4096 --K 4096 --bits 4 --gs 64 --M 1
+    python -m jangq_b200.microbench --op quantize --N 8192 --K 8192 --bits 4
+    python -m jangq_b200.microbench --sweep qgemv        # BASELINE config-4 small-M sweep
+
+Distinct copies of the weights are rotated so that the bytes touched between
+two uses of the same copy exceed `--rotate-mb` (default 512 MB, 4x the L2), and
+the launches are replayed from a CUDA graph.  Prints one JSON line per case
+with achieved GB/s (algorithmic bytes / time) or TFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _lib, ops
+
+
+def _time_graph(fn, iters: int, warmup: int = 3) -> float:
+    """Median milliseconds of one fn() call sequence, replayed from a CUDA graph."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bytes_w(N, K, bits, gs, e=2):
+    return N * K * bits // 8 + N * (K // gs) * 2 * e
+
+
+def bench_qgemv(N, K, bits, gs, M, iters, rotate_mb, dtype=torch.bfloat16):
+    dev = torch.device("cuda")
+    per = bytes_w(N, K, bits, gs)
+    copies = max(2, min(64, int(rotate_mb * 2 ** 20 // per) + 1))
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    w = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(dtype)
+    wq, s, b = ops.quantize(w, gs, bits)
+    del w
+    ws = [(wq.clone(), s.clone(), b.clone()) for _ in range(copies)]
+    x = torch.randn((M, K), generator=g, device=dev).to(dtype)
+    y = torch.empty((M, N), dtype=dtype, device=dev)
+
+    def fn():
+        for wq_, s_, b_ in ws:
+            ops._qgemv(x, wq_, s_, b_, K, bits, gs, y)
+
+    ms = _time_graph(fn, iters) / copies
+    alg = per + M * K * 2 + M * N * 2
+    return {"op": "qgemv", "N": N, "K": K, "bits": bits, "gs": gs, "M": M, "us": ms * 1e3,
+            "GBps": alg / (ms * 1e-3) / 1e9, "bytes": alg, "copies": copies}
+
+
+def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="quantize"):
+    dev = torch.device("cuda")
+    per = N * K * 2
+    copies = max(2, min(16, int(rotate_mb * 2 ** 20 // per) + 1))
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    wsrc = [(torch.randn((N, K), generator=g, device=dev) * 0.02).to(dtype) for _ in range(copies)]
+    if op == "quantize":
+        def fn():
+            for w in wsrc:
+                ops.quantize(w, gs, bits)
+        alg = per + bytes_w(N, K, bits, gs)
+    else:
+        trip = [ops.quantize(w, gs, bits) for w in wsrc]
+        del wsrc
+
+        def fn():
+            for wq, s, b in trip:
+                ops.dequantize(wq, s, b, gs, bits)
+        alg = per + bytes_w(N, K, bits, gs)
+    ms = _time_graph(fn, iters) / copies
+    return {"op": op, "N": N, "K": K, "bits": bits, "gs": gs, "us": ms * 1e3, "GBps": alg / (ms * 1e-3) / 1e9,
+            "bytes": alg, "copies": copies}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="qgemv", choices=("qgemv", "quantize", "dequantize"))
+    ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small"))
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--gs", type=int, default=64)
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--rotate-mb", type=float, default=512.0)
+    a = ap.parse_args()
+    _lib.load()
+    if a.sweep:
+        Ks = (2048, 4096, 8192) if a.sweep == "qgemv" else (4096,)
+        Ns = (4096, 14336, 28672) if a.sweep == "qgemv" else (4096, 14336)
+        for K in Ks:
+            for N in Ns:
+                for bits in (2, 3, 4, 6, 8):
+                    for gs in (64, 128):
+                        for M in (1, 8):
+                            print(json.dumps(bench_qgemv(N, K, bits, gs, M, a.iters, a.rotate_mb)), flush=True)
+        return
+    if a.op == "qgemv":
+        print(json.dumps(bench_qgemv(a.N, a.K, a.bits, a.gs, a.M, a.iters, a.rotate_mb)))
+    else:
+        print(json.dumps(bench_quantize(a.N, a.K, a.bits, a.gs, a.iters, a.rotate_mb, op=a.op)))
+    _lib.check(_lib.load().jq_device_status())
+
+
+if __name__ == "__main__":
+    main()
