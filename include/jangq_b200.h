@@ -85,6 +85,20 @@ int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t*
              const void* scales, const void* biases, int sidecar_dtype, int64_t N, int64_t K,
              int bits, int group_size, void* y, int y_dtype, int64_t ldy, jq_stream_t stream);
 
+/* Same as jq_qgemv with launch flags.
+ * JQ_GEMV_STATIC_WEIGHTS: the caller guarantees that codes/scales/biases are not written
+ * by earlier work on `stream`.  The kernel is then launched with programmatic stream
+ * serialization: it may start, and prefetch its weights, while the previous kernel on
+ * the stream is still running, and reads x / writes y only after that kernel has
+ * completed.  This is what hides launch latency between the many small mat-vecs of a
+ * decode step (the reference measured its decode as dispatch-bound,
+ * jang_tools/dsv41/DECODE_DSPARK_METHODS.md:90-93). */
+#define JQ_GEMV_STATIC_WEIGHTS 1
+int jq_qgemv_ex(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes,
+                const void* scales, const void* biases, int sidecar_dtype, int64_t N, int64_t K,
+                int bits, int group_size, void* y, int y_dtype, int64_t ldy, int flags,
+                jq_stream_t stream);
+
 /* One launch over several independent matrices (for example q/k/v, or gate/up,
  * of one decoder layer, each with its own bit width): the same arithmetic as
  * jq_qgemv per entry.  `descs` is a HOST array, copied into the launch. */

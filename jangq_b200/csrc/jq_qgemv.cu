@@ -4,11 +4,15 @@
 //     N*K*bits/8 (codes) + N*(K/gs)*2*sizeof(sidecar) + M*K*2 + M*N*2.
 //
 // Structure (one CTA = 16*MT weight rows x all of K, 4 warps):
-//   * every warp is its own producer and consumer: it bulk-copies (cp.async.bulk
-//     + mbarrier complete_tx) a stage = 16*MT row segments of `kt` codes plus the M
-//     activation row segments of the same k-range into private shared-memory
-//     buffers, 2-3 stages deep, so no cross-warp handshake exists until the final
-//     reduction; warp w owns stages w, w+4, ...;  scales/biases of a stage are
+//   * every warp is its own producer and consumer: with 128-bit cp.async copies
+//     (every lane one 16-byte chunk, 8 lanes per 128-byte row segment) it streams a
+//     stage = 16*MT row segments of `kt` codes plus the M activation row segments of
+//     the same k-range into private shared-memory buffers, 2-3 stages deep, so no
+//     cross-warp handshake exists until the final reduction; warp w owns stages
+//     w, w+4, ...  (one bulk-copy instruction moves a single row segment and is
+//     issued by one lane at a time, which made ~33 of them per stage cost more
+//     issue slots than the stage's arithmetic; per-lane cp.async costs ~10
+//     instructions per stage);  scales/biases of a stage are
 //     fetched one stage ahead with 8-byte loads and parked in shared memory as the
 //     f32 pair (s*POST, b - OFFSET*s);
 //   * codes are dequantized in registers straight into m16n8k16 MMA A operands
@@ -27,7 +31,7 @@
 
 namespace jq {
 
-__device__ int g_timeout_flag = 0;   // set when a bounded mbarrier wait ran out
+__device__ int g_timeout_flag = 0;   // set by any kernel whose bounded wait ran out
 
 struct GemvArgs {
     const void* x;
@@ -36,7 +40,8 @@ struct GemvArgs {
     const void* biases;
     void* y;
     int64_t N, K, ldx, ldy;
-    int M, kt, G, nbuf;
+    int M, G, nbuf;
+    int pdl;      // launched with programmatic stream serialization (weights are static)
 };
 
 constexpr int GEMV_WARPS = 4;
@@ -44,154 +49,166 @@ constexpr int GEMV_MAX_NBUF = 3;
 
 __host__ __device__ inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
-// shared-memory row padding (words) that keeps the per-lane unit loads conflict-free
-__host__ __device__ constexpr int gemv_row_pad(int bits) {
-    return bits == 2 ? 4 : bits == 6 ? 12 : bits == 8 ? 16 : 8;
-}
-
-// bytes of one stage buffer: codes, activations (M rows + one zero chunk), sidecar
-// float2 pairs (row stride NG+1), group sums X
-__host__ __device__ inline int gemv_stage_bytes(int kt, int bits, int gs, int M, int mt) {
-    const int ng = kt / gs;
-    return 16 * mt * (kt * bits / 8 + 4 * gemv_row_pad(bits)) + M * (kt * 2 + 16) + 32 + 16 * mt * (ng + 1) * 8 +
-           ng * 8;
-}
+// Compile-time geometry of one stage buffer (per warp, per pipeline slot).
+template <int BITS, int GS, int MT> struct GemvGeom {
+    static constexpr int KT = (BITS <= 4 || GS == 128) ? 512 : 256;   // codes per row and stage
+    static constexpr int ROWS = 16 * MT;
+    // row padding (words) that keeps the per-lane unit loads free of bank conflicts
+    static constexpr int PAD = BITS == 2 ? 4 : BITS == 6 ? 12 : BITS == 8 ? 16 : 8;
+    static constexpr int RS = KT * BITS / 32 + PAD;      // code row stride, words
+    static constexpr int XS = KT + 8;                    // activation row stride, elements
+    static constexpr int NG = KT / GS;                   // groups per stage (4 or 8)
+    static constexpr int NQ = NG / 4;                    // 8-byte sidecar quads per row
+    static constexpr int NGP = NG + 1;                   // padded sidecar row stride, float2
+    static constexpr int Z_OFF = ROWS * RS * 4;          // 32 zero bytes (B operand of lanes g >= M)
+    static constexpr int SC_OFF = Z_OFF + 32;            // float2 (s*POST, b - OFFSET*s) [ROWS][NGP]
+    static constexpr int XSUM_OFF = SC_OFF + ROWS * NGP * 8;   // float X[NG][8]
+    static constexpr int X_OFF = XSUM_OFF + NG * 8 * 4;  // activations [M][XS]
+    __host__ __device__ static constexpr int stage_bytes(int M) { return X_OFF + M * XS * 2; }
+};
 
 template <typename AT, int BITS, int GS, int MT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 qgemv_mma_kernel(const GemvArgs a) {
     using A = Act<AT>;
     using F = Fields<AT, BITS>;
+    using Geo = GemvGeom<BITS, GS, MT>;
     constexpr int NW = GEMV_WARPS;
     static_assert(NW == 4, "the final reduction maps the 4 warps onto the 4 accumulator slots");
     constexpr int BPG = GS / 64;            // 64-code k-blocks per quantization group
     constexpr int UW = Unit<BITS>::WORDS;
-    constexpr int ROWS = 16 * MT;
+    constexpr int ROWS = Geo::ROWS, KT = Geo::KT, RS = Geo::RS, XS = Geo::XS, NG = Geo::NG, NQ = Geo::NQ,
+                  NGP = Geo::NGP;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
     const int64_t n0 = (int64_t)blockIdx.x * ROWS;
     const int rows_valid = (int)min((int64_t)ROWS, a.N - n0);
-    const int K = (int)a.K, kt = a.kt, G = a.G, M = a.M, nbuf = a.nbuf;
-    const int nst = (K + kt - 1) / kt;
-    const int RS = kt * BITS / 32 + gemv_row_pad(BITS);   // code row stride, words
-    const int XS = kt + 8;                   // activation row stride, elements
-    const int NG = kt / GS;                  // groups per full stage (a multiple of 4)
-    const int NQ = NG / 4;                   // 8-byte sidecar quads per row and stage
-    const int NGP = NG + 1;                  // padded sidecar row stride (float2 units)
-    const int stage_bytes = gemv_stage_bytes(kt, BITS, GS, M, MT);
-    const int x_off = ROWS * RS * 4;
-    const int z_off = x_off + M * XS * 2;    // 32 zero bytes: the B operand of lanes with g >= M
-    const int sc_off = z_off + 32;
-    const int xs_off = sc_off + ROWS * NGP * 8;
-    const int64_t rowwords = a.K * BITS / 32;
-    uint8_t* mybuf = smem + 128 + (size_t)warp * nbuf * stage_bytes;
-    uint64_t* mybar = bars + warp * GEMV_MAX_NBUF;
+    const int K = (int)a.K, G = a.G, M = a.M, nbuf = a.nbuf;
+    const int nst = (K + KT - 1) / KT;
+    const int stage_bytes = Geo::stage_bytes(M);
+    const int64_t rowbytes = a.K * BITS / 8;
+    uint8_t* mybuf = smem + (size_t)warp * nbuf * stage_bytes;
     const uint16_t* xs16 = reinterpret_cast<const uint16_t*>(a.x);
     const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(a.scales);
     const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(a.biases);
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < NW * GEMV_MAX_NBUF; ++i) mbar_init(bars + i, 1);
-        mbar_fence_init();
-    }
     if (lane < 8)
-        for (int b = 0; b < nbuf; ++b) reinterpret_cast<uint32_t*>(mybuf + (size_t)b * stage_bytes + z_off)[lane] = 0u;
-    __syncthreads();
+        for (int b = 0; b < nbuf; ++b)
+            reinterpret_cast<uint32_t*>(mybuf + (size_t)b * stage_bytes + Geo::Z_OFF)[lane] = 0u;
 
-    // stage `st` -> buffer b: ROWS code row segments + M activation row segments
-    auto issue = [&](int st, int b) {
-        const int k0 = st * kt;
-        const int kc = min(kt, K - k0);
-        const uint32_t segbytes = (uint32_t)(kc * BITS / 8);
-        uint8_t* buf = mybuf + (size_t)b * stage_bytes;
-        if (lane == 0) mbar_expect_tx(mybar + b, segbytes * (uint32_t)rows_valid + (uint32_t)(M * kc * 2));
-        __syncwarp();
-#pragma unroll
-        for (int r = 0; r < MT; ++r) {
-            const int row = lane + 32 * r;
-            if (row < ROWS && row < rows_valid)
-                bulk_g2s(buf + row * RS * 4, a.codes + (n0 + row) * rowwords + (int64_t)k0 * BITS / 32, segbytes,
-                         mybar + b);
+    // ---- stage copies: 16 bytes per lane and instruction -------------------------------------
+    // LPR lanes share a code row (the smallest power of two covering its chunks), so one
+    // instruction covers 32/LPR rows and the per-iteration address update is two adds.
+    const uint8_t* code_base = reinterpret_cast<const uint8_t*>(a.codes) + n0 * rowbytes;
+    auto issue_codes = [&](int st, int b) {
+        if (st < nst) {
+            const int k0 = st * KT;
+            const int kc = min(KT, K - k0);
+            uint8_t* buf = mybuf + (size_t)b * stage_bytes;
+            const int cpr = kc * BITS / 128;                          // 16-byte chunks per code row
+            const int lpr = cpr <= 4 ? 4 : cpr <= 8 ? 8 : cpr <= 16 ? 16 : 32;
+            const int col = lane & (lpr - 1), rpi = 32 / lpr;
+            if (col < cpr) {
+                int row = lane / lpr;
+                const uint8_t* src = code_base + (int64_t)row * rowbytes + (int64_t)k0 * BITS / 8 + col * 16;
+                uint8_t* dst = buf + row * (RS * 4) + col * 16;
+                for (; row < rows_valid; row += rpi) {
+                    cp_async16(dst, src);
+                    src += (int64_t)rpi * rowbytes;
+                    dst += rpi * (RS * 4);
+                }
+            }
         }
-        if (lane >= 32 - M)   // the last M lanes also fetch the activation rows
-            bulk_g2s(buf + x_off + (lane - (32 - M)) * XS * 2, xs16 + (int64_t)(lane - (32 - M)) * a.ldx + k0,
-                     (uint32_t)(kc * 2), mybar + b);
+    };
+    auto issue_x = [&](int st, int b) {
+        if (st < nst) {
+            const int k0 = st * KT;
+            const int kc = min(KT, K - k0);
+            uint8_t* buf = mybuf + (size_t)b * stage_bytes;
+            const int cpx = kc / 8;                                    // chunks per activation row (32 or 64)
+            for (int m = 0; m < M; ++m)
+                for (int c = lane; c < cpx; c += 32)
+                    cp_async16(buf + Geo::X_OFF + (m * XS + c * 8) * 2, xs16 + (int64_t)m * a.ldx + k0 + c * 8);
+        }
     };
 
-    // sidecars of stage `st`: pair index -> (row, quad of 4 groups), one 8-byte load each
-    constexpr int SCP = (ROWS * 2 + 31) / 32;      // pairs per lane at most (NQ <= 2)
+    // ---- sidecars of a stage: pair index -> (row, quad of 4 groups), one 8-byte load each -----
+    constexpr int SCP = (ROWS * NQ + 31) / 32;     // pairs per lane
     uint2 sv[SCP], bv[SCP];
     auto fetch_sc = [&](int st) {
 #pragma unroll
         for (int i = 0; i < SCP; ++i) {
             const int pr = lane + 32 * i;
-            const int row = pr / NQ, quad = pr - row * NQ;
+            const int row = pr / NQ, quad = pr % NQ;
             const int grp = st * NG + quad * 4;
             sv[i] = make_uint2(0u, 0u);
             bv[i] = make_uint2(0u, 0u);
             if (pr < ROWS * NQ && grp < G) {
-                const int64_t grow = min(n0 + row, a.N - 1);
-                sv[i] = __ldg(reinterpret_cast<const uint2*>(sc16 + grow * G + grp));
-                bv[i] = __ldg(reinterpret_cast<const uint2*>(bi16 + grow * G + grp));
+                const int64_t off = min(n0 + row, a.N - 1) * G + grp;
+                sv[i] = __ldg(reinterpret_cast<const uint2*>(sc16 + off));
+                bv[i] = __ldg(reinterpret_cast<const uint2*>(bi16 + off));
             }
         }
     };
-    auto store_sc = [&](int b) {
+    auto store_sc = [&](uint8_t* buf) {
 #pragma unroll
         for (int i = 0; i < SCP; ++i) {
             const int pr = lane + 32 * i;
-            const int row = pr / NQ, quad = pr - row * NQ;
+            const int row = pr / NQ, quad = pr % NQ;
             if (pr < ROWS * NQ) {
-                float2* dst = reinterpret_cast<float2*>(mybuf + (size_t)b * stage_bytes + sc_off) + row * NGP + quad * 4;
-                const uint32_t sw[2] = {sv[i].x, sv[i].y}, bw[2] = {bv[i].x, bv[i].y};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float s = (j & 1) ? A::hi_f32(sw[j >> 1]) : A::lo_f32(sw[j >> 1]);
-                    const float bb = (j & 1) ? A::hi_f32(bw[j >> 1]) : A::lo_f32(bw[j >> 1]);
-                    dst[j] = make_float2(s * F::POST, fmaf(-F::OFFSET, s, bb));
-                }
+                float2* dst = reinterpret_cast<float2*>(buf + Geo::SC_OFF) + row * NGP + quad * 4;
+                const float s0 = A::lo_f32(sv[i].x), s1 = A::hi_f32(sv[i].x), s2 = A::lo_f32(sv[i].y),
+                            s3 = A::hi_f32(sv[i].y);
+                dst[0] = make_float2(s0 * F::POST, fmaf(-F::OFFSET, s0, A::lo_f32(bv[i].x)));
+                dst[1] = make_float2(s1 * F::POST, fmaf(-F::OFFSET, s1, A::hi_f32(bv[i].x)));
+                dst[2] = make_float2(s2 * F::POST, fmaf(-F::OFFSET, s2, A::lo_f32(bv[i].y)));
+                dst[3] = make_float2(s3 * F::POST, fmaf(-F::OFFSET, s3, A::hi_f32(bv[i].y)));
             }
         }
     };
 
-    // start streaming before anything else
+    // Start streaming the weights before anything else.  Under programmatic dependent launch
+    // this kernel may begin while its predecessor in the stream still runs: weights and
+    // sidecars (static by contract) are prefetched at once, the activations only after
+    // griddepcontrol.wait, and the successor is allowed to start launching immediately.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < GEMV_MAX_NBUF; ++i) {
-        const int st = warp + i * NW;
-        if (i < nbuf && st < nst) issue(st, i);
-    }
+    for (int i = 0; i < GEMV_MAX_NBUF; ++i)
+        if (i < nbuf) issue_codes(warp + i * NW, i);
     fetch_sc(warp);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < GEMV_MAX_NBUF; ++i)
+        if (i < nbuf) {
+            issue_x(warp + i * NW, i);
+            cp_async_commit();
+        }
 
     float acc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-    const uint32_t ones[4] = {A::ONES, A::ONES, A::ONES, A::ONES};
-    const bool simt_x = (M <= 2);
 
     int it = 0;
     for (int st = warp; st < nst; st += NW, ++it) {
         const int b = it % nbuf;
-        const uint32_t parity = (uint32_t)(it / nbuf) & 1u;
-        const int k0 = st * kt;
-        const int kc = min(kt, K - k0);
+        const int kc = min(KT, K - st * KT);
         const int nblk = kc >> 6;
         uint8_t* buf = mybuf + (size_t)b * stage_bytes;
-        store_sc(b);
+        store_sc(buf);
         if (st + NW < nst) fetch_sc(st + NW);
-        if (!mbar_wait(mybar + b, parity)) {
-            atomicExch(&g_timeout_flag, 1);
-            break;
-        }
-        float* Xs = reinterpret_cast<float*>(buf + xs_off);     // [NG][2] group sums for m = 0, 1
-        if (simt_x) {
-            // lane l sums the 16 activations of chunk l; GS/16 adjacent lanes make a group
+        if (nbuf == 3) cp_async_wait<2>(); else cp_async_wait<1>();   // this stage's copies have landed
+        __syncwarp();
+
+        // ---- X[grp][m] = sum of the group's activations -----------------------------------------
+        float* Xs = reinterpret_cast<float*>(buf + Geo::XSUM_OFF);
+        if (M <= 2) {
+            // SIMT: lane l sums the 16 activations of chunk l; GS/16 adjacent lanes make a group
             for (int m = 0; m < M; ++m) {
                 float sum = 0.f;
                 if (lane * 16 < kc) {
-                    const uint4* xp = reinterpret_cast<const uint4*>(buf + x_off + (m * XS + lane * 16) * 2);
+                    const uint4* xp = reinterpret_cast<const uint4*>(buf + Geo::X_OFF + (m * XS + lane * 16) * 2);
                     const uint4 v0 = xp[0], v1 = xp[1];
                     const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                     float s0 = 0.f, s1 = 0.f;
@@ -201,24 +218,44 @@ qgemv_mma_kernel(const GemvArgs a) {
                 }
 #pragma unroll
                 for (int d = 1; d < GS / 16; d <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
-                if ((lane & (GS / 16 - 1)) == 0 && lane * 16 < kc) Xs[(lane * 16 / GS) * 2 + m] = sum;
+                if ((lane & (GS / 16 - 1)) == 0 && lane * 16 < kc) Xs[(lane * 16 / GS) * 8 + m] = sum;
+            }
+        } else {
+            // tensor cores: the activations are the A operand (row = m, 8 consecutive k per lane), B is
+            // all ones, so every column of C holds the row sums; rows g and g+8 carry two k-chunks
+            const uint16_t* xa = (g < M) ? reinterpret_cast<const uint16_t*>(buf + Geo::X_OFF) + g * XS + tig * 8
+                                         : reinterpret_cast<const uint16_t*>(buf + Geo::Z_OFF);
+            const int xa_step = (g < M) ? 32 : 0;
+            const int ngrp = kc / GS;
+            for (int grp = 0; grp < ngrp; ++grp) {
+                float c[4];
+#pragma unroll
+                for (int i = 0; i < GS / 32; ++i) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xa + (grp * (GS / 32) + i) * xa_step);
+                    const uint32_t af[4] = {v.x, v.y, v.z, v.w};
+                    if (i == 0) A::mma0(c, af, A::ONES, A::ONES); else A::mma(c, af, A::ONES, A::ONES);
+                }
+                if (tig == 0) Xs[grp * 8 + g] = c[0] + c[2];
             }
         }
         __syncwarp();
-        const uint32_t* codes_s = reinterpret_cast<const uint32_t*>(buf);
-        const uint16_t* xrow = (g < M) ? reinterpret_cast<const uint16_t*>(buf + x_off) + g * XS + tig * 16
-                                       : reinterpret_cast<const uint16_t*>(buf + z_off);
+
+        // ---- main loop over the stage's 64-code k-blocks ------------------------------------------
+        const uint32_t* c_lo = reinterpret_cast<const uint32_t*>(buf) + g * RS;
+        const uint16_t* xrow = (g < M) ? reinterpret_cast<const uint16_t*>(buf + Geo::X_OFF) + g * XS + tig * 16
+                                       : reinterpret_cast<const uint16_t*>(buf + Geo::Z_OFF);
         const int xstep = (g < M) ? 64 : 0;
-        const float2* scs = reinterpret_cast<const float2*>(buf + sc_off);
-        float cg[MT][F::PASSES][4], xc[4];
-        xc[0] = xc[1] = xc[2] = xc[3] = 0.f;
+        const float2* pt = reinterpret_cast<const float2*>(buf + Geo::SC_OFF) + g * NGP;
+        const float* xsum = Xs + 2 * tig;
+        float cg[MT][F::PASSES][4];
         for (int blk = 0; blk < nblk; ++blk) {
             uint32_t xr[8];
             {
-                const uint4* xp = reinterpret_cast<const uint4*>(xrow + blk * xstep);
+                const uint4* xp = reinterpret_cast<const uint4*>(xrow);
                 const uint4 v0 = xp[0], v1 = xp[1];
                 xr[0] = v0.x; xr[1] = v0.y; xr[2] = v0.z; xr[3] = v0.w;
                 xr[4] = v1.x; xr[5] = v1.y; xr[6] = v1.z; xr[7] = v1.w;
+                xrow += xstep;
             }
             const bool first = (blk % BPG) == 0;
             uint32_t bb[4][2];
@@ -226,17 +263,11 @@ qgemv_mma_kernel(const GemvArgs a) {
             bb[1][0] = make_b<BITS, 1, 0>(xr); bb[1][1] = make_b<BITS, 1, 1>(xr);
             bb[2][0] = make_b<BITS, 2, 0>(xr); bb[2][1] = make_b<BITS, 2, 1>(xr);
             bb[3][0] = make_b<BITS, 3, 0>(xr); bb[3][1] = make_b<BITS, 3, 1>(xr);
-            if (!simt_x) {
-                if (first) A::mma0(xc, ones, bb[0][0], bb[0][1]); else A::mma(xc, ones, bb[0][0], bb[0][1]);
-                A::mma(xc, ones, bb[1][0], bb[1][1]);
-                A::mma(xc, ones, bb[2][0], bb[2][1]);
-                A::mma(xc, ones, bb[3][0], bb[3][1]);
-            }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 uint32_t ulo[UW], uhi[UW];
-                load_unit<BITS>(codes_s + (mt * 16 + g) * RS, blk, tig, ulo);
-                load_unit<BITS>(codes_s + (mt * 16 + g + 8) * RS, blk, tig, uhi);
+                load_unit<BITS>(c_lo + mt * 16 * RS, blk, tig, ulo);
+                load_unit<BITS>(c_lo + (mt * 16 + 8) * RS, blk, tig, uhi);
 #define JQ_STEP(T)                                                                                   \
     {                                                                                                \
         {                                                                                            \
@@ -256,37 +287,34 @@ qgemv_mma_kernel(const GemvArgs a) {
 #undef JQ_STEP
             }
             if (blk % BPG == BPG - 1) {
-                const int gl = blk / BPG;
-                float x0, x1;
-                if (simt_x) {
-                    const float2 xv = *reinterpret_cast<const float2*>(Xs + gl * 2);
-                    x0 = xv.x; x1 = xv.y;
-                } else {
-                    x0 = xc[0]; x1 = xc[1];
-                }
+                const float2 xv = *reinterpret_cast<const float2*>(xsum);
+                xsum += 8;
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    const float2 pt_lo = scs[(mt * 16 + g) * NGP + gl], pt_hi = scs[(mt * 16 + g + 8) * NGP + gl];
+                    const float2 pt_lo = pt[mt * 16 * NGP], pt_hi = pt[(mt * 16 + 8) * NGP];
                     float c[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         c[i] = cg[mt][0][i];
                         if constexpr (F::PASSES == 2) c[i] = fmaf(16.f, cg[mt][F::PASSES - 1][i], c[i]);
                     }
-                    acc[mt][0] = fmaf(pt_lo.x, c[0], fmaf(pt_lo.y, x0, acc[mt][0]));
-                    acc[mt][1] = fmaf(pt_lo.x, c[1], fmaf(pt_lo.y, x1, acc[mt][1]));
-                    acc[mt][2] = fmaf(pt_hi.x, c[2], fmaf(pt_hi.y, x0, acc[mt][2]));
-                    acc[mt][3] = fmaf(pt_hi.x, c[3], fmaf(pt_hi.y, x1, acc[mt][3]));
+                    acc[mt][0] = fmaf(pt_lo.x, c[0], fmaf(pt_lo.y, xv.x, acc[mt][0]));
+                    acc[mt][1] = fmaf(pt_lo.x, c[1], fmaf(pt_lo.y, xv.y, acc[mt][1]));
+                    acc[mt][2] = fmaf(pt_hi.x, c[2], fmaf(pt_hi.y, xv.x, acc[mt][2]));
+                    acc[mt][3] = fmaf(pt_hi.x, c[3], fmaf(pt_hi.y, xv.y, acc[mt][3]));
                 }
+                ++pt;
             }
         }
         __syncwarp();
-        const int nxt = st + nbuf * NW;
-        if (nxt < nst) issue(nxt, b);
+        issue_codes(st + nbuf * NW, b);
+        issue_x(st + nbuf * NW, b);
+        cp_async_commit();     // always one group per iteration so that the group count stays uniform
     }
+    cp_async_wait<0>();
 
     __syncthreads();   // every warp is done with its buffers
-    float* red = reinterpret_cast<float*>(smem + 128);
+    float* red = reinterpret_cast<float*>(smem);   // overlays the (now idle) stage buffers
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -375,16 +403,11 @@ static bool force_simple() {
 
 template <typename AT, int BITS, int GS, int MT>
 static int launch_mma_mt(GemvArgs a, cudaStream_t st, bool* launched) {
+    using Geo = GemvGeom<BITS, GS, MT>;
     *launched = false;
-    // stage length: 512 codes (256 for wide codes with 64-groups), shorter for short rows so
-    // that every warp still gets a stage; the sidecar quads need kt/GS to be a multiple of 4
-    int kt = (BITS <= 4 || GS == 128) ? 512 : 256;
-    const int kt_min = (GS == 128) ? 512 : 256;
-    while (a.K / kt < GEMV_WARPS && kt > kt_min) kt >>= 1;
-    a.kt = kt;
-    const int sb = gemv_stage_bytes(kt, BITS, GS, a.M, MT);
+    const int sb = Geo::stage_bytes(a.M);
     a.nbuf = (GEMV_WARPS * 3 * sb <= 72 * 1024) ? 3 : 2;
-    const size_t smem = 128 + (size_t)GEMV_WARPS * a.nbuf * sb;
+    const size_t smem = (size_t)GEMV_WARPS * a.nbuf * sb;
     if (smem > 200 * 1024) return JQ_OK;   // does not fit: general kernel
     static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
     int dev = 0;
@@ -395,9 +418,19 @@ static int launch_mma_mt(GemvArgs a, cudaStream_t st, bool* launched) {
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const unsigned grid = (unsigned)((a.N + 16 * MT - 1) / (16 * MT));
-    qgemv_mma_kernel<AT, BITS, GS, MT><<<grid, GEMV_WARPS * 32, smem, st>>>(a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GEMV_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_mma_kernel<AT, BITS, GS, MT>, a));
     *launched = true;
-    return check_launch("qgemv");
+    return JQ_OK;
 }
 
 template <typename AT, int BITS, int GS>
@@ -410,7 +443,7 @@ static int launch_mma(const GemvArgs& a, cudaStream_t st, bool* launched) {
 
 int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
                    const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int gs, void* y,
-                   int y_dtype, int64_t ldy, cudaStream_t st) {
+                   int y_dtype, int64_t ldy, int flags, cudaStream_t st) {
     int rc = check_quant_shape(N, K, bits, gs);
     if (rc != JQ_OK) return rc;
     JQ_REQUIRE(valid_dtype(x_dtype) && valid_dtype(sidecar_dtype) && valid_dtype(y_dtype), JQ_EINVAL, "bad dtype");
@@ -433,6 +466,7 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
         a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy;
         a.M = (int)((M - m0) < 8 ? (M - m0) : 8);
         a.G = (int)(K / gs);
+        a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
         bool launched = false;
         if (fast) {
 #define JQ_GEMV_CASE(B, GSZ)                                                                     \
@@ -446,7 +480,7 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
 #undef JQ_GEMV_CASE
         }
         if (!launched) {
-            a.kt = 0; a.nbuf = 0;
+            a.nbuf = 0;
             const unsigned grid = (unsigned)((N + 3) / 4);
             JQ_DISPATCH_BITS(bits, B,
                 (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(a, x_dtype, sidecar_dtype, y_dtype, gs)))
@@ -465,7 +499,14 @@ int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t*
              const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
              int y_dtype, int64_t ldy, jq_stream_t stream) {
     return jq::qgemv_dispatch(x, x_dtype, M, ldx, codes, scales, biases, sidecar_dtype, N, K, bits, group_size, y,
-                              y_dtype, ldy, (cudaStream_t)stream);
+                              y_dtype, ldy, 0, (cudaStream_t)stream);
+}
+
+int jq_qgemv_ex(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
+                const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
+                int y_dtype, int64_t ldy, int flags, jq_stream_t stream) {
+    return jq::qgemv_dispatch(x, x_dtype, M, ldx, codes, scales, biases, sidecar_dtype, N, K, bits, group_size, y,
+                              y_dtype, ldy, flags, (cudaStream_t)stream);
 }
 
 int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype, int sidecar_dtype,
@@ -475,7 +516,7 @@ int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtyp
     for (int i = 0; i < count; ++i) {
         const JqGemvDesc& d = descs[i];
         int rc = jq::qgemv_dispatch(d.x, act_dtype, M, d.ldx, d.codes, d.scales, d.biases, sidecar_dtype, d.N, d.K,
-                                    d.bits, d.group_size, d.y, act_dtype, d.ldy, (cudaStream_t)stream);
+                                    d.bits, d.group_size, d.y, act_dtype, d.ldy, 0, (cudaStream_t)stream);
         if (rc != JQ_OK) return rc;
     }
     return JQ_OK;

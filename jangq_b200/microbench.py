@@ -49,7 +49,7 @@ def bytes_w(N, K, bits, gs, e=2):
     return N * K * bits // 8 + N * (K // gs) * 2 * e
 
 
-def bench_qgemv(N, K, bits, gs, M, iters, rotate_mb, dtype=torch.bfloat16):
+def bench_qgemv(N, K, bits, gs, M, iters, rotate_mb, dtype=torch.bfloat16, flags=0):
     dev = torch.device("cuda")
     per = bytes_w(N, K, bits, gs)
     copies = max(2, min(64, int(rotate_mb * 2 ** 20 // per) + 1))
@@ -64,7 +64,7 @@ def bench_qgemv(N, K, bits, gs, M, iters, rotate_mb, dtype=torch.bfloat16):
 
     def fn():
         for wq_, s_, b_ in ws:
-            ops._qgemv(x, wq_, s_, b_, K, bits, gs, y)
+            ops._qgemv(x, wq_, s_, b_, K, bits, gs, y, flags)
 
     ms = _time_graph(fn, iters) / copies
     alg = per + M * K * 2 + M * N * 2
@@ -108,8 +108,10 @@ def main():
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--rotate-mb", type=float, default=512.0)
+    ap.add_argument("--pdl", action="store_true", help="launch with JQ_GEMV_STATIC_WEIGHTS (overlapped launches)")
     a = ap.parse_args()
     _lib.load()
+    flags = _lib.JQ_GEMV_STATIC_WEIGHTS if a.pdl else 0
     if a.sweep:
         Ks = (2048, 4096, 8192) if a.sweep == "qgemv" else (4096,)
         Ns = (4096, 14336, 28672) if a.sweep == "qgemv" else (4096, 14336)
@@ -118,10 +120,10 @@ def main():
                 for bits in (2, 3, 4, 6, 8):
                     for gs in (64, 128):
                         for M in (1, 8):
-                            print(json.dumps(bench_qgemv(N, K, bits, gs, M, a.iters, a.rotate_mb)), flush=True)
+                            print(json.dumps(bench_qgemv(N, K, bits, gs, M, a.iters, a.rotate_mb, flags=flags)), flush=True)
         return
     if a.op == "qgemv":
-        print(json.dumps(bench_qgemv(a.N, a.K, a.bits, a.gs, a.M, a.iters, a.rotate_mb)))
+        print(json.dumps(bench_qgemv(a.N, a.K, a.bits, a.gs, a.M, a.iters, a.rotate_mb, flags=flags)))
     else:
         print(json.dumps(bench_quantize(a.N, a.K, a.bits, a.gs, a.iters, a.rotate_mb, op=a.op)))
     _lib.check(_lib.load().jq_device_status())

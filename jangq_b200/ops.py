@@ -105,13 +105,14 @@ def dequantize(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, gro
     return out.reshape(lead + (K,))
 
 
-def _qgemv(x2: torch.Tensor, wq, scales, biases, K, bits, group_size, out: torch.Tensor):
+def _qgemv(x2: torch.Tensor, wq, scales, biases, K, bits, group_size, out: torch.Tensor, flags: int = 0):
     lib = _lib.load()
     dev = x2.device
     M, N = x2.shape[0], wq.shape[0]
-    _lib.check(lib.jq_qgemv(x2.data_ptr(), _lib.dtype_id(x2.dtype), M, x2.stride(0), wq.data_ptr(), scales.data_ptr(),
-                            biases.data_ptr(), _lib.dtype_id(scales.dtype), N, K, bits, group_size, out.data_ptr(),
-                            _lib.dtype_id(out.dtype), out.stride(0), _lib.stream_ptr(dev)))
+    _lib.check(lib.jq_qgemv_ex(x2.data_ptr(), _lib.dtype_id(x2.dtype), M, x2.stride(0), wq.data_ptr(),
+                               scales.data_ptr(), biases.data_ptr(), _lib.dtype_id(scales.dtype), N, K, bits,
+                               group_size, out.data_ptr(), _lib.dtype_id(out.dtype), out.stride(0), flags,
+                               _lib.stream_ptr(dev)))
 
 
 def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,

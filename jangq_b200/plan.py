@@ -26,11 +26,13 @@ class GemvPlan:
     """
 
     def __init__(self, linears: Sequence[JANGLinear], m: int = 1, dtype: torch.dtype = torch.bfloat16,
-                 device=None, share_inputs: bool = True):
+                 device=None, share_inputs: bool = True, static_weights: bool = True):
         if m < 1 or m > _lib.QGEMV_MAX_M:
             raise _lib.JangqError(_lib.JQ_EINVAL, f"GemvPlan takes 1..{_lib.QGEMV_MAX_M} rows")
         self.linears = list(linears)
         self.m, self.dtype = m, dtype
+        # the plan's weights are fixed once it exists, so launches may overlap their predecessors
+        self.static_weights = static_weights
         self.device = torch.device(device if device is not None else self.linears[0].weight.device)
         # one input buffer per distinct in_features when sharing (a real decoder reuses the hidden state)
         self._xbuf = {}
@@ -57,7 +59,8 @@ class GemvPlan:
     def _enqueue(self):
         from .ops import _qgemv
         for lin, x, y in zip(self.linears, self.x, self.y):
-            _qgemv(x, lin.weight, lin.scales, lin.biases, lin.in_features, lin.bits, lin.group_size, y)
+            _qgemv(x, lin.weight, lin.scales, lin.biases, lin.in_features, lin.bits, lin.group_size, y,
+                   _lib.JQ_GEMV_STATIC_WEIGHTS if self.static_weights else 0)
 
     def capture(self):
         """Record the launches into a CUDA graph (call once, before run())."""

@@ -125,3 +125,28 @@ def test_general_kernel_matches_on_standard_shape():
 def test_device_status_clean():
     torch.cuda.synchronize()
     assert _lib.load().jq_device_status() == 0
+
+
+def test_static_weights_overlapped_launches_keep_stream_order():
+    """JQ_GEMV_STATIC_WEIGHTS lets a launch start before its predecessor has finished; the
+    activations it reads (the predecessor's output) must still be the finished ones."""
+    from jangq_b200.ops import _qgemv
+    N = 1024
+    lins = []
+    for i in range(4):
+        _, wq, s, b = make_case(N, N, (2, 4, 6, 8)[i], 64, 1, torch.bfloat16, seed=40 + i)
+        lins.append((wq, s * 8, b * 8, (2, 4, 6, 8)[i]))      # gain ~1 so that the chain neither dies nor blows up
+    x0 = torch.randn((1, N), device=DEV).to(torch.bfloat16)
+
+    def chain(flags):
+        bufs = [x0] + [torch.empty((1, N), dtype=torch.bfloat16, device=DEV) for _ in range(8)]
+        for rep in range(8):
+            wq, s, b, bits = lins[rep % 4]
+            _qgemv(bufs[rep], wq, s, b, N, bits, 64, bufs[rep + 1], flags)
+        torch.cuda.synchronize()
+        return bufs[-1]
+
+    ref = chain(0)
+    for _ in range(5):
+        assert torch.equal(chain(_lib.JQ_GEMV_STATIC_WEIGHTS), ref)
+    assert float(ref.float().abs().max()) > 0
