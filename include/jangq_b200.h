@@ -115,6 +115,16 @@ typedef struct JqGemvDesc {
 int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype,
                      int sidecar_dtype, jq_stream_t stream);
 
+/* K3. Prefill-shaped quantized GEMM: the same mx.quantized_matmul call with many
+ * activation rows (MLX switches from qmv to its tiled qmm there; the reference's only
+ * statement of that kernel is the tile shape at jang_tools/jangh/kernels.py:34,273-277).
+ * Y[M,N] = X[M,K] . deq(W)[N,K]^T on tcgen05 tensor cores: the weights are dequantized to
+ * the activation type (one rounding) tile by tile in shared memory, f32 accumulation in
+ * tensor memory.  Needs K % 64 == 0 and x/scales/biases/y of the same 16-bit type. */
+int jq_qgemm(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes,
+             const void* scales, const void* biases, int sidecar_dtype, int64_t N, int64_t K,
+             int bits, int group_size, void* y, int y_dtype, int64_t ldy, jq_stream_t stream);
+
 /* Reads the device-side status word (synchronises the device).  JQ_ETIMEOUT when a
  * kernel's bounded wait on a copy in flight ran out since the library was loaded.
  * No counterpart in the reference: its Metal path has no device-side waits. */

@@ -48,6 +48,7 @@ SIGNATURES = {
     "jq_dequantize": (C.c_int, [_p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _p]),
     "jq_qgemv": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_ex": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _i32, _p]),
+    "jq_qgemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_batched": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _p]),
     "jq_device_status": (C.c_int, []),
 }

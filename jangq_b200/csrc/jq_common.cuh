@@ -43,6 +43,10 @@ int check_quant_shape(int64_t rows, int64_t K, int bits, int group_size);
 // cached per-device attributes (SM count); mutex-guarded, filled on first use
 int sm_count();
 
+// device address of the library's status word on the current device (nullptr on failure);
+// kernels with bounded waits set it to 1 when a wait runs out, jq_device_status() reads it
+int* status_word();
+
 // ---- device-side scalar conversion -------------------------------------------
 template <typename T> struct Elt;
 template <> struct Elt<float> {

@@ -1,0 +1,438 @@
+// K3: prefill-shaped quantized GEMM  Y[M,N] = X[M,K] . deq(W)[N,K]^T  on the 5th-generation
+// tensor cores (tcgen05.mma, accumulator in tensor memory).
+//
+// Bound: dense bf16/f16 tensor throughput for large M; 2*M*N*K flops per launch.
+//
+// One CTA computes a 128 (M) x BN (N) tile of Y.  Warp roles:
+//   warp 0        TMA producer: one elected lane copies the 128 x 64 activation tile of every
+//                 k-block into a 128-byte-swizzled shared-memory stage (cp.async.bulk.tensor);
+//   warp 1        allocates BN columns of tensor memory; one elected lane issues the MMAs
+//                 (4 x tcgen05.mma M=128, N=BN, K=16 per k-block) and commits their completion to
+//                 the mbarriers that free the stages;
+//   warps 2..     dequantizers, one weight row per thread: packed codes -> registers -> exact
+//                 q (16-bit float) -> fma(q, scale, bias) rounded once to the activation type ->
+//                 the K-major, 128-byte-swizzled B tile in shared memory (the layout TMA would
+//                 have produced), then fence.proxy.async + mbarrier arrive; afterwards the same
+//                 warps run the epilogue: tcgen05.ld the accumulator, convert, store Y.
+// Every mbarrier wait is bounded; a wait that runs out sets the library's status word and the
+// CTA leaves through the common exit (tensor memory is always released).
+//
+// Numerics: the B operand is the dequantized weight rounded to the activation type (what
+// MLX's qmm feeds its matrix units), products are accumulated in f32.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "jq_mma.cuh"
+
+namespace jq {
+
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_SA = 4;     // activation stages
+constexpr int GEMM_SB = 3;     // dequantized-weight stages
+
+struct GemmArgs {
+    const uint32_t* codes;
+    const void* scales;
+    const void* biases;
+    void* y;
+    int64_t M, N, K, ldy;
+    int gs, G;
+    int y_vec_ok;    // rows of y are 16-byte aligned
+    int* status;     // device status word, set to 1 when a bounded wait ran out
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on `bar` once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 2-D tiled TMA load (no multicast): coordinates {x = innermost (k), y = row}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 64 16-bit
+// elements (128 bytes), 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
+}
+
+template <typename AT> __host__ __device__ constexpr uint32_t umma_fmt();
+template <> __host__ __device__ constexpr uint32_t umma_fmt<__nv_bfloat16>() { return 1u; }
+template <> __host__ __device__ constexpr uint32_t umma_fmt<__half>() { return 0u; }
+
+template <typename AT, int BN>
+__host__ __device__ constexpr uint32_t umma_idesc() {
+    return (1u << 4) /* D = f32 */ | (umma_fmt<AT>() << 7) | (umma_fmt<AT>() << 10) | ((uint32_t)(BN >> 3) << 17) |
+           ((uint32_t)(GEMM_BM >> 4) << 24);             // A and B both K-major, no negate, dense
+}
+
+// ---- packed 16-bit float helpers --------------------------------------------------------------------
+template <typename AT> struct P2;
+template <> struct P2<__nv_bfloat16> {
+    __device__ static __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+        uint32_t r;
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+        return r;
+    }
+};
+template <> struct P2<__half> {
+    __device__ static __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+        uint32_t r;
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+        return r;
+    }
+};
+
+// 32 bits of a row's code stream starting at bit A (negative A: zero-filled below bit 0)
+template <int NWORDS, int A>
+__device__ __forceinline__ uint32_t stream_at(const uint32_t (&u)[NWORDS]) {
+    if constexpr (A < 0) return u[0] << (-A);
+    else if constexpr (A % 32 == 0) return u[A / 32];
+    else if constexpr (A / 32 + 1 < NWORDS) return __funnelshift_r(u[A / 32], u[A / 32 + 1], A % 32);
+    else return u[A / 32] >> (A % 32);
+}
+
+// Weights J and J+1 of a 64-code unit: rn(q*s + bias) in the activation type, packed.
+// sp2 = (s', s') with s' = s * 2^-TGT, b2 = (bias, bias); s/bias are the same values in f32.
+template <typename AT, int BITS, int J>
+__device__ __forceinline__ uint32_t dequant_pair(const uint32_t (&u)[2 * BITS], uint32_t sp2, uint32_t b2, float s,
+                                                 float bias) {
+    if constexpr (BITS <= Act<AT>::MANT) {
+        constexpr int TGT = Act<AT>::MANT - BITS;
+        constexpr uint32_t MASK = (((1u << BITS) - 1u) << TGT) * 0x00010001u;
+        const uint32_t lo = stream_at<2 * BITS, J * BITS - TGT>(u);
+        const uint32_t hi = stream_at<2 * BITS, (J + 1) * BITS - TGT>(u);
+        const uint32_t v = and_or(prmt(lo, hi, 0x5410), MASK, Act<AT>::MAGIC);   // 2^MANT + q*2^TGT, twice
+        const uint32_t q2 = P2<AT>::sub(v, Act<AT>::MAGIC);                       // q * 2^TGT, exact
+        return P2<AT>::fma(q2, sp2, b2);                                          // one rounding
+    } else {
+        // codes wider than the mantissa (8-bit with bf16): exact q in f32 through the 2^23 trick
+        static_assert(BITS == 8, "only 8-bit codes take the f32 route");
+        const uint32_t word = u[J / 4];
+        const float q0 = __uint_as_float(prmt(word, 0x4B000000u, 0x7540u | (uint32_t)(J % 4))) - 8388608.0f;
+        const float q1 = __uint_as_float(prmt(word, 0x4B000000u, 0x7540u | (uint32_t)(J % 4 + 1))) - 8388608.0f;
+        return Act<AT>::pack_hi(fmaf(q0, s, bias), fmaf(q1, s, bias));
+    }
+}
+
+// codes 8C .. 8C+7 -> one 16-byte chunk of the B tile
+template <typename AT, int BITS, int C>
+__device__ __forceinline__ uint4 dequant_chunk(const uint32_t (&u)[2 * BITS], uint32_t sp2, uint32_t b2, float s,
+                                               float bias) {
+    return make_uint4(dequant_pair<AT, BITS, 8 * C + 0>(u, sp2, b2, s, bias),
+                      dequant_pair<AT, BITS, 8 * C + 2>(u, sp2, b2, s, bias),
+                      dequant_pair<AT, BITS, 8 * C + 4>(u, sp2, b2, s, bias),
+                      dequant_pair<AT, BITS, 8 * C + 6>(u, sp2, b2, s, bias));
+}
+
+template <typename AT, int BITS, int BN>
+__global__ void __launch_bounds__(64 + BN)
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
+    using A = Act<AT>;
+    constexpr int NDW = BN / 32;                        // dequantizer warps
+    constexpr int A_STAGE = GEMM_BM * GEMM_BK * 2;      // 16 KB
+    constexpr int B_STAGE = BN * GEMM_BK * 2;
+    constexpr int UW = 2 * BITS;                        // words of one row's 64 codes
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the dynamic shared-memory base is only guaranteed 16-byte aligned: realign to 1024
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + GEMM_SA * A_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + GEMM_SB * B_STAGE);
+    uint64_t* xfull = bars;                  // [SA]
+    uint64_t* xempty = bars + GEMM_SA;       // [SA]
+    uint64_t* bfull = bars + 2 * GEMM_SA;    // [SB]
+    uint64_t* bempty = bfull + GEMM_SB;      // [SB]
+    uint64_t* accfull = bempty + GEMM_SB;    // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t n0 = (int64_t)blockIdx.x * BN, m0 = (int64_t)blockIdx.y * GEMM_BM;
+    const int nkb = (int)(a.K / GEMM_BK);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < GEMM_SA; ++i) { mbar_init(xfull + i, 1); mbar_init(xempty + i, 1); }
+        for (int i = 0; i < GEMM_SB; ++i) { mbar_init(bfull + i, NDW); mbar_init(bempty + i, 1); }
+        mbar_init(accfull, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % GEMM_SA;
+                if (kb >= GEMM_SA) ok = mbar_wait(xempty + s, (uint32_t)((kb / GEMM_SA) - 1) & 1u, 1u << 18);
+                if (!ok) break;
+                mbar_expect_tx(xfull + s, A_STAGE);
+                tma_load_2d(sA + s * A_STAGE, &xmap, kb * GEMM_BK, (int)m0, xfull + s);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc<AT, BN>();
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % GEMM_SA, t = kb % GEMM_SB;
+                ok = mbar_wait(xfull + s, (uint32_t)(kb / GEMM_SA) & 1u, 1u << 18) &&
+                     mbar_wait(bfull + t, (uint32_t)(kb / GEMM_SB) & 1u, 1u << 18);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sA + s * A_STAGE), b_addr = smem_u32(sB + t * B_STAGE);
+#pragma unroll
+                for (int k = 0; k < GEMM_BK / 16; ++k)
+                    umma_f16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(xempty + s);
+                umma_commit(bempty + t);
+            }
+            if (ok) umma_commit(accfull);
+        }
+    } else {
+        // ---------------- dequantizers: one weight row per thread ----------------
+        const int r = (warp - 2) * 32 + lane;                 // row within the tile
+        const int64_t n = min(n0 + r, a.N - 1);               // rows past N are computed but never stored
+        const uint32_t* crow = a.codes + n * (a.K * BITS / 32);
+        const uint16_t* srow = reinterpret_cast<const uint16_t*>(a.scales) + n * a.G;
+        const uint16_t* brow = reinterpret_cast<const uint16_t*>(a.biases) + n * a.G;
+        const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+        const uint32_t sw = (uint32_t)(r & 7);
+        const int gs = a.gs;
+        uint32_t cur[UW], nxt[UW];
+#pragma unroll
+        for (int i = 0; i < UW; ++i) cur[i] = __ldg(crow + i);
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int t = kb % GEMM_SB;
+            if (kb + 1 < nkb) {
+#pragma unroll
+                for (int i = 0; i < UW; ++i) nxt[i] = __ldg(crow + (kb + 1) * UW + i);
+            }
+            // scale / bias of the (up to two) groups this k-block touches
+            const int k0 = kb * GEMM_BK;
+            const int g0 = k0 / gs, g1 = (k0 + 32) / gs;
+            const uint16_t s0h = __ldg(srow + g0), b0h = __ldg(brow + g0);
+            const uint16_t s1h = __ldg(srow + g1), b1h = __ldg(brow + g1);
+            constexpr int TGTC = (BITS <= A::MANT) ? A::MANT - BITS : 0;
+            constexpr float POST = 1.0f / (float)(1 << TGTC);
+            const float s0 = A::to_f32(s0h), s1 = A::to_f32(s1h), bias0 = A::to_f32(b0h), bias1 = A::to_f32(b1h);
+            // s * 2^-TGT is exact (power-of-two scaling) unless it underflows the 16-bit type
+            const uint32_t sp0 = A::pack_hi(s0 * POST, s0 * POST), sp1 = A::pack_hi(s1 * POST, s1 * POST);
+            const uint32_t bb0 = (uint32_t)b0h * 0x00010001u, bb1 = (uint32_t)b1h * 0x00010001u;
+            if (kb >= GEMM_SB) {
+                // warp-uniform outcome, so that no lane is left behind at the __syncwarp below
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(bempty + t, (uint32_t)((kb / GEMM_SB) - 1) & 1u, 1u << 18));
+                if (!ok) break;
+            }
+            uint8_t* dst = sB + t * B_STAGE + row_off;
+#define JQ_CHUNK(C, SP, BB, S, BI) \
+    *reinterpret_cast<uint4*>(dst + (((uint32_t)(C) ^ sw) << 4)) = dequant_chunk<AT, BITS, C>(cur, SP, BB, S, BI);
+            JQ_CHUNK(0, sp0, bb0, s0, bias0) JQ_CHUNK(1, sp0, bb0, s0, bias0)
+            JQ_CHUNK(2, sp0, bb0, s0, bias0) JQ_CHUNK(3, sp0, bb0, s0, bias0)
+            JQ_CHUNK(4, sp1, bb1, s1, bias1) JQ_CHUNK(5, sp1, bb1, s1, bias1)
+            JQ_CHUNK(6, sp1, bb1, s1, bias1) JQ_CHUNK(7, sp1, bb1, s1, bias1)
+#undef JQ_CHUNK
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bfull + t);
+#pragma unroll
+            for (int i = 0; i < UW; ++i) cur[i] = nxt[i];
+        }
+
+        // ---------------- epilogue: TMEM -> registers -> Y ----------------
+        if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(accfull, 0, 1u << 18));
+        if (ok) {
+            tc_fence_after();
+            const int q = warp & 3;                               // TMEM lane quarter this warp may read
+            const int half = (warp - 2) / 4;                      // BN = 256: two warps per quarter split the columns
+            constexpr int COLS_PER_WARP = BN / (NDW / 4);
+            const int64_t m = m0 + q * 32 + lane;
+            uint16_t* yrow = reinterpret_cast<uint16_t*>(a.y) + m * a.ldy + n0;
+#pragma unroll 1
+            for (int c0 = half * COLS_PER_WARP; c0 < (half + 1) * COLS_PER_WARP; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (m < a.M) {
+                    if (a.y_vec_ok && n0 + c0 + 32 <= a.N) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 o;
+                            o.x = A::pack_hi(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                            o.y = A::pack_hi(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                            o.z = A::pack_hi(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                            o.w = A::pack_hi(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                            *reinterpret_cast<uint4*>(yrow + c0 + 8 * j) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c0 + j < a.N) yrow[c0 + j] = A::from_f32(__uint_as_float(v[j]));
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(a.status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, BN);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+template <typename AT, int BITS, int BN>
+static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, cudaStream_t st) {
+    constexpr size_t smem = 1024 + GEMM_SA * GEMM_BM * GEMM_BK * 2 + GEMM_SB * BN * GEMM_BK * 2 + 256;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    JQ_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)((a.M + GEMM_BM - 1) / GEMM_BM));
+    qgemm_tc_kernel<AT, BITS, BN><<<grid, 64 + BN, smem, st>>>(xmap, a);
+    return check_launch("qgemm");
+}
+
+int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
+                   const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int gs, void* y,
+                   int y_dtype, int64_t ldy, cudaStream_t st) {
+    int rc = check_quant_shape(N, K, bits, gs);
+    if (rc != JQ_OK) return rc;
+    JQ_REQUIRE(M >= 0, JQ_EINVAL, "negative M");
+    if (M == 0 || N == 0) return JQ_OK;
+    JQ_REQUIRE(K > 0, JQ_EINVAL, "K must be positive");
+    JQ_REQUIRE(x && codes && scales && biases && y, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(x_dtype == JQ_BF16 || x_dtype == JQ_F16, JQ_EINVAL, "qgemm activations must be bf16 or f16");
+    JQ_REQUIRE(sidecar_dtype == x_dtype && y_dtype == x_dtype, JQ_EUNSUPPORTED,
+               "qgemm needs scales/biases and the output in the activation dtype");
+    JQ_REQUIRE(K % GEMM_BK == 0, JQ_EUNSUPPORTED, "qgemm needs K to be a multiple of 64, got %lld", (long long)K);
+    JQ_REQUIRE(aligned(x, 16) && ldx % 8 == 0 && ldx >= K, JQ_EINVAL, "x must be 16-byte aligned with ldx %% 8 == 0");
+    JQ_REQUIRE(ldy >= N, JQ_EINVAL, "ldy too small");
+    JQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), JQ_EUNSUPPORTED, "dimension too large");
+    EncodeTiledFn enc = encode_tiled_fn();
+    JQ_REQUIRE(enc != nullptr, JQ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+
+    CUtensorMap xmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {GEMM_BK, GEMM_BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&xmap, x_dtype == JQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                      const_cast<void*>(x), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    JQ_REQUIRE(cr == CUDA_SUCCESS, JQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+
+    GemmArgs a;
+    a.codes = codes; a.scales = scales; a.biases = biases; a.y = y;
+    a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.gs = gs; a.G = (int)(K / gs);
+    a.y_vec_ok = (aligned(y, 16) && ldy % 8 == 0) ? 1 : 0;
+    a.status = status_word();
+    JQ_REQUIRE(a.status != nullptr, JQ_ECUDA, "could not locate the device status word");
+#define JQ_GEMM_CASE(B)                                                                                  \
+    if (bits == B)                                                                                       \
+        return x_dtype == JQ_BF16 ? launch_gemm<__nv_bfloat16, B, 128>(xmap, a, st)                      \
+                                  : launch_gemm<__half, B, 128>(xmap, a, st);
+    JQ_GEMM_CASE(2) JQ_GEMM_CASE(3) JQ_GEMM_CASE(4) JQ_GEMM_CASE(5) JQ_GEMM_CASE(6) JQ_GEMM_CASE(8)
+#undef JQ_GEMM_CASE
+    return fail(JQ_EUNSUPPORTED, "bits=%d", bits);
+}
+
+}  // namespace jq
+
+extern "C" {
+
+int jq_qgemm(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
+             const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
+             int y_dtype, int64_t ldy, jq_stream_t stream) {
+    return jq::qgemm_dispatch(x, x_dtype, M, ldx, codes, scales, biases, sidecar_dtype, N, K, bits, group_size, y,
+                              y_dtype, ldy, (cudaStream_t)stream);
+}
+
+}  // extern "C"

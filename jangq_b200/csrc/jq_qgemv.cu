@@ -396,6 +396,18 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
     }
 }
 
+int* status_word() {
+    static int* cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_timeout_flag) != cudaSuccess) return nullptr;
+        cached[dev] = static_cast<int*>(p);
+    }
+    return cached[dev];
+}
+
 static bool force_simple() {
     const char* e = getenv("JANGQ_FORCE_SIMPLE_GEMV");
     return e && e[0] == '1';
