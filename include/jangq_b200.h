@@ -125,6 +125,67 @@ int jq_qgemm(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t*
              const void* scales, const void* biases, int sidecar_dtype, int64_t N, int64_t K,
              int bits, int group_size, void* y, int y_dtype, int64_t ldy, jq_stream_t stream);
 
+/* ---- K4: routed-MoE gather_qmm --------------------------------------------------------
+ * Stands in for mx.gather_qmm(x, W[E,out,packed], scales, biases, rhs_indices, ...) and the
+ * sort-by-expert layer logic around it (jang_tools/dots3/ops.py:168-223,
+ * dsv41/model.py:847-857,1206-1245; fused decode dsv41/metal_decode.py:334-497).
+ * Expert weights are addressed through DEVICE arrays of per-expert device pointers
+ * (codes_tab/scales_tab/biases_tab, num_experts entries) so that every expert may have its
+ * own bit width: bits_tab (device int32[num_experts], or NULL when all experts share `bits`)
+ * makes a launch skip the experts whose width is not `bits`; call once per distinct width. */
+#define JQ_MOE_TILE_M 128
+
+/* Upper bound of the number of row tiles jq_moe_sort can emit (sizes tile_expert/tile_row0). */
+size_t jq_moe_sort_max_tiles(int64_t n_pairs, int num_experts, int tile_m);
+
+/* Stable sort of the n_pairs = T*k (token, slot) pairs by expert id (dsv41/model.py:1207-1212:
+ * order = argsort(flat idx), inv = argsort(order)).  Experts outside
+ * [expert_base, expert_base + num_experts) (another rank's, under expert parallelism) are dropped:
+ * inv = -1.  expert_offsets[num_experts + 1]; expert_offsets[num_experts] = kept pairs.  Also emits
+ * the tile list of the grouped GEMM: tile t covers sorted rows tile_row0[t] .. of expert
+ * tile_expert[t]; *num_tiles tiles.  All outputs are device arrays; nothing syncs. */
+int jq_moe_sort(const int32_t* topk_idx, int64_t n_pairs, int num_experts, int expert_base,
+                int32_t* order, int32_t* inv, int32_t* expert_offsets, int tile_m,
+                int32_t* tile_expert, int32_t* tile_row0, int32_t* num_tiles, jq_stream_t stream);
+
+/* dst[p, :] = src[order[p] / div, :] for p < min(*count, max_rows): the activation gather
+ * x[order // topk] of dsv41/model.py:1210.  16-bit rows, 16-byte aligned. */
+int jq_gather_rows(const void* src, int64_t src_ld, const int32_t* order, const int32_t* count,
+                   int div, void* dst, int64_t dst_ld, int64_t cols, int64_t max_rows, int dtype,
+                   jq_stream_t stream);
+
+/* Grouped quantized GEMM over the expert-sorted rows (gather_qmm with sorted_indices=True):
+ * y_sorted[p, :] = x_sorted[p, :] . deq(W[expert of row p])^T, on the tcgen05 tensor cores. */
+int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx,
+                const int32_t* expert_offsets, const int32_t* tile_expert, const int32_t* tile_row0,
+                const int32_t* num_tiles, int64_t max_tiles, const uint32_t* const* codes_tab,
+                const void* const* scales_tab, const void* const* biases_tab, const int32_t* bits_tab,
+                int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y_sorted,
+                int64_t ldy, jq_stream_t stream);
+
+/* h = silu(min(g, limit)) * clip(u, +-limit) * weights[pair] (dsv41/model.py:1216-1226; limit <= 0:
+ * no clamp; weights NULL: 1).  pair = order[p] when order != NULL else p; rows p < *count when
+ * count != NULL else p < max_rows. */
+int jq_moe_swiglu(const void* gate, const void* up, int64_t ld_in, const float* weights,
+                  const int32_t* order, const int32_t* count, void* h, int64_t ld_out, int64_t cols,
+                  int64_t max_rows, float limit, int dtype, jq_stream_t stream);
+
+/* out[t, :] = sum over the k slots, in slot order, f32: (weights ? weights[t*k+j] : 1) *
+ * y[inv ? inv[t*k+j] : t*k+j, :] (dsv41/model.py:1230-1234, dots3/ops.py:223); slots with
+ * inv < 0 are skipped.  Writes out (activation dtype) or, when out_f32 != NULL, f32 [T, D]. */
+int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T,
+                   int k, int64_t D, void* out, int64_t ldo, float* out_f32, int dtype,
+                   jq_stream_t stream);
+
+/* Unsorted gather mat-vec for few pairs (the reference's path below its sort threshold of 64,
+ * dsv41/model.py:1206, and its fused decode kernels): y[p, :] = deq(W[pair_expert[p]]) .
+ * x[p / x_div, :], p < pairs.  Pairs whose expert is outside [0, num_experts) are skipped. */
+int jq_gather_qgemv(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert,
+                    int64_t pairs, const uint32_t* const* codes_tab, const void* const* scales_tab,
+                    const void* const* biases_tab, const int32_t* bits_tab, int num_experts,
+                    int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
+                    int64_t ldy, jq_stream_t stream);
+
 /* Reads the device-side status word (synchronises the device).  JQ_ETIMEOUT when a
  * kernel's bounded wait on a copy in flight ran out since the library was loaded.
  * No counterpart in the reference: its Metal path has no device-side waits. */

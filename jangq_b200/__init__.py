@@ -6,7 +6,8 @@ kernels).  The op names follow the MLX calls the reference makes.
 from ._lib import JangqError
 from .linear import JANGLinear
 from .ops import ALLOWED_BITS, ALLOWED_GROUP_SIZES, dequantize, quantize, quantized_matmul
+from .moe import ExpertBank, gather_qmm, moe_layer, route_softmax_topk
 from .plan import GemvPlan
 
 __all__ = ["JangqError", "ALLOWED_BITS", "ALLOWED_GROUP_SIZES", "quantize", "dequantize", "quantized_matmul",
-           "JANGLinear", "GemvPlan"]
+           "JANGLinear", "GemvPlan", "ExpertBank", "gather_qmm", "moe_layer", "route_softmax_topk"]

@@ -20,6 +20,7 @@ JQ_QUANT_F16_TINY_GUARD = 1
 JQ_GEMV_STATIC_WEIGHTS = 1
 QGEMV_MAX_M = 16
 QGEMV_MAX_BATCH = 8
+MOE_TILE_M = 128
 
 _DTYPE_ID = {torch.float32: JQ_F32, torch.float16: JQ_F16, torch.bfloat16: JQ_BF16}
 
@@ -51,6 +52,15 @@ SIGNATURES = {
     "jq_qgemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_batched": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _p]),
     "jq_device_status": (C.c_int, []),
+    "jq_moe_sort_max_tiles": (C.c_size_t, [_i64, _i32, _i32]),
+    "jq_moe_sort": (C.c_int, [_p, _i64, _i32, _i32, _p, _p, _p, _i32, _p, _p, _p, _p]),
+    "jq_gather_rows": (C.c_int, [_p, _i64, _p, _p, _i32, _p, _i64, _i64, _i64, _i32, _p]),
+    "jq_moe_gemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _i32, _i64, _i64, _i32, _i32,
+                              _p, _i64, _p]),
+    "jq_moe_swiglu": (C.c_int, [_p, _p, _i64, _p, _p, _p, _p, _i64, _i64, _i64, C.c_float, _i32, _p]),
+    "jq_moe_combine": (C.c_int, [_p, _i64, _p, _p, _i64, _i32, _i64, _p, _i64, _p, _i32, _p]),
+    "jq_gather_qgemv": (C.c_int, [_p, _i32, _i64, _i32, _p, _i64, _p, _p, _p, _p, _i32, _i32, _i64, _i64, _i32, _i32,
+                                  _p, _i64, _p]),
 }
 
 _lock = threading.Lock()

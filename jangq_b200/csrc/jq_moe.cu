@@ -1,0 +1,232 @@
+// K4 support kernels for the routed-MoE path: stable sort of (token, slot) pairs by expert,
+// row gather, SwiGLU with routing weight, and the top-k combine.  The matmuls themselves are the
+// grouped mode of the tensor-core GEMM (jq_qgemm.cu) and the gather mode of the mat-vec
+// (jq_qgemv.cu).  All of these are small, bandwidth-bound index/elementwise kernels.
+#include "jq_mma.cuh"
+
+namespace jq {
+
+constexpr int SORT_THREADS = 1024;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+
+// Stable counting sort of n = T*k expert ids, one CTA.
+//   order[p]  = flat pair index (t*k + j) of the p-th pair in expert order (ties: ascending index)
+//   inv[i]    = position of pair i in `order`, or -1 when its expert is outside [base, base+E)
+//   offsets[e]= first position of local expert e, offsets[E] = number of kept pairs
+//   tiles: for every local expert, ceil(count/tile_m) tiles (expert id, first sorted row); *num_tiles
+// Shared memory: (SORT_WARPS + 1) * (E + 1) counters.
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_kernel(const int32_t* __restrict__ idx, int n, int E, int base, int32_t* __restrict__ order,
+                int32_t* __restrict__ inv, int32_t* __restrict__ offsets, int tile_m, int32_t* __restrict__ tile_expert,
+                int32_t* __restrict__ tile_row0, int32_t* __restrict__ num_tiles) {
+    extern __shared__ int32_t sm[];
+    const int EB = E + 1;                           // bucket E collects dropped pairs
+    int32_t* cnt = sm;                              // [SORT_WARPS][EB] per-chunk counts, then running positions
+    int32_t* start = sm + SORT_WARPS * EB;          // [EB] exclusive scan over experts
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < (SORT_WARPS + 1) * EB; i += SORT_THREADS) sm[i] = 0;
+    __syncthreads();
+    // chunk of this warp: a contiguous range whose length is a multiple of 32
+    const int per = ((n + SORT_WARPS - 1) / SORT_WARPS + 31) / 32 * 32;
+    const int lo = min(n, warp * per), hi = min(n, lo + per);
+    auto bucket = [&](int i) -> int {
+        const int e = idx[i] - base;
+        return (e >= 0 && e < E) ? e : E;
+    };
+    // pass 1: per-chunk histogram
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const bool act = i < hi;
+        const int b = act ? bucket(i) : -1;
+        const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
+        if (act && (peers & ((1u << lane) - 1u)) == 0) cnt[warp * EB + b] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    // totals per bucket and exclusive scan over buckets (thread 0 .. E: serial scan is fine for E <= 1024)
+    for (int b = threadIdx.x; b < EB; b += SORT_THREADS) {
+        int tot = 0;
+        for (int w = 0; w < SORT_WARPS; ++w) tot += cnt[w * EB + b];
+        start[b] = tot;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, tiles = 0;
+        for (int b = 0; b < EB; ++b) {
+            const int c = start[b];
+            start[b] = run;
+            if (b < E) {
+                offsets[b] = run;
+                for (int r = 0; r < c; r += tile_m) {
+                    tile_expert[tiles] = b;
+                    tile_row0[tiles] = run + r;
+                    ++tiles;
+                }
+            }
+            run += c;
+        }
+        offsets[E] = start[E];
+        *num_tiles = tiles;
+    }
+    __syncthreads();
+    // per-chunk base positions: start[b] + counts of earlier chunks
+    for (int b = threadIdx.x; b < EB; b += SORT_THREADS) {
+        int run = start[b];
+        for (int w = 0; w < SORT_WARPS; ++w) {
+            const int c = cnt[w * EB + b];
+            cnt[w * EB + b] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    // pass 2: stable placement
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const bool act = i < hi;
+        const int b = act ? bucket(i) : -1;
+        const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        int pos = 0;
+        if (act) pos = cnt[warp * EB + b] + rank;
+        __syncwarp();
+        if (act && rank == 0) cnt[warp * EB + b] += __popc(peers);
+        __syncwarp();
+        if (act) {
+            if (b < E) {
+                order[pos] = i;
+                inv[i] = pos;
+            } else {
+                inv[i] = -1;
+            }
+        }
+    }
+}
+
+// dst[p, :] = src[order[p] / div, :] for p < *count (16-byte vectors; cols*2 % 16 == 0)
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, int64_t src_ld_vec, const int32_t* __restrict__ order,
+                                   const int32_t* __restrict__ count, int div, uint4* __restrict__ dst,
+                                   int64_t dst_ld_vec, int cols_vec, int max_rows) {
+    const int n = min(*count, max_rows);
+    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+        const int64_t s = order[p] / div;
+        for (int c = threadIdx.x; c < cols_vec; c += blockDim.x) dst[p * dst_ld_vec + c] = __ldg(src + s * src_ld_vec + c);
+    }
+}
+
+// h[p, i] = silu(min(g, lim)) * clip(u, -lim, lim) * w[pair(p)]   (dsv41/model.py:1216-1226)
+// pair(p) = order[p] when `order` is given (sorted rows), else p.  lim <= 0 disables the clamp.
+template <typename AT>
+__global__ void swiglu_kernel(const AT* __restrict__ g, const AT* __restrict__ u, int64_t ld_in,
+                              const float* __restrict__ w, const int32_t* __restrict__ order,
+                              const int32_t* __restrict__ count, AT* __restrict__ h, int64_t ld_out, int cols, int max_rows,
+                              float lim) {
+    const int n = count ? min(*count, max_rows) : max_rows;
+    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+        const float wt = w ? w[order ? order[p] : p] : 1.0f;
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            float gv = Elt<AT>::to_f32(g[p * ld_in + c]), uv = Elt<AT>::to_f32(u[p * ld_in + c]);
+            if (lim > 0.f) {
+                gv = fminf(gv, lim);
+                uv = fminf(fmaxf(uv, -lim), lim);
+            }
+            const float s = gv / (1.0f + __expf(-gv));
+            h[p * ld_out + c] = Elt<AT>::from_f32(s * uv * wt);
+        }
+    }
+}
+
+// out[t, :] = sum_j (w ? w[t*k+j] : 1) * y[inv ? inv[t*k+j] : t*k+j, :]  in f32, slots in order
+// (dsv41/model.py:1230-1234); pairs with inv < 0 (experts of another rank) are skipped.
+template <typename AT>
+__global__ void combine_kernel(const AT* __restrict__ y, int64_t ldy, const int32_t* __restrict__ inv,
+                               const float* __restrict__ w, int T, int k, int D, AT* __restrict__ out, int64_t ldo,
+                               float* __restrict__ out_f32) {
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            float acc = 0.f;
+            for (int j = 0; j < k; ++j) {
+                const int p = inv ? inv[t * k + j] : t * k + j;
+                if (p >= 0) acc = fmaf(w ? w[t * k + j] : 1.0f, Elt<AT>::to_f32(y[(int64_t)p * ldy + c]), acc);
+            }
+            if (out_f32) out_f32[(int64_t)t * D + c] = acc;
+            else out[(int64_t)t * ldo + c] = Elt<AT>::from_f32(acc);
+        }
+    }
+}
+
+}  // namespace jq
+
+extern "C" {
+
+size_t jq_moe_sort_max_tiles(int64_t n_pairs, int num_experts, int tile_m) {
+    if (n_pairs < 0 || num_experts < 0 || tile_m <= 0) return 0;
+    return (size_t)(n_pairs / tile_m + num_experts);
+}
+
+int jq_moe_sort(const int32_t* topk_idx, int64_t n_pairs, int num_experts, int expert_base, int32_t* order,
+                int32_t* inv, int32_t* expert_offsets, int tile_m, int32_t* tile_expert, int32_t* tile_row0,
+                int32_t* num_tiles, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(n_pairs >= 0 && n_pairs < (1ll << 30), JQ_EINVAL, "bad pair count %lld", (long long)n_pairs);
+    JQ_REQUIRE(num_experts > 0 && num_experts <= 4096, JQ_EUNSUPPORTED, "num_experts must be in 1..4096");
+    JQ_REQUIRE(tile_m > 0, JQ_EINVAL, "tile_m must be positive");
+    JQ_REQUIRE(order && inv && expert_offsets && tile_expert && tile_row0 && num_tiles, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(n_pairs == 0 || topk_idx, JQ_EINVAL, "null pointer");
+    const size_t smem = (size_t)(SORT_WARPS + 1) * (num_experts + 1) * sizeof(int32_t);
+    JQ_REQUIRE(smem <= 200 * 1024, JQ_EUNSUPPORTED, "too many experts for the single-CTA sort");
+    static bool attr_done[64] = {};
+    int dev = 0;
+    JQ_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        JQ_CUDA_OK(cudaFuncSetAttribute(moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    moe_sort_kernel<<<1, SORT_THREADS, smem, (cudaStream_t)stream>>>(topk_idx, (int)n_pairs, num_experts, expert_base,
+                                                                      order, inv, expert_offsets, tile_m, tile_expert,
+                                                                      tile_row0, num_tiles);
+    return check_launch("moe_sort");
+}
+
+int jq_gather_rows(const void* src, int64_t src_ld, const int32_t* order, const int32_t* count, int div, void* dst,
+                   int64_t dst_ld, int64_t cols, int64_t max_rows, int dtype, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(dtype == JQ_BF16 || dtype == JQ_F16, JQ_EINVAL, "gather_rows takes 16-bit rows");
+    JQ_REQUIRE(div > 0 && cols >= 0 && max_rows >= 0, JQ_EINVAL, "bad argument");
+    if (max_rows == 0 || cols == 0) return JQ_OK;
+    JQ_REQUIRE(src && dst && order && count, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(cols % 8 == 0 && src_ld % 8 == 0 && dst_ld % 8 == 0 && aligned(src, 16) && aligned(dst, 16), JQ_EINVAL,
+               "gather_rows needs 16-byte aligned rows");
+    const int blocks = (int)(max_rows < 4 * 148 ? max_rows : 4 * 148);
+    gather_rows_kernel<<<blocks, 128, 0, (cudaStream_t)stream>>>((const uint4*)src, src_ld / 8, order, count, div,
+                                                                  (uint4*)dst, dst_ld / 8, (int)(cols / 8), (int)max_rows);
+    return check_launch("gather_rows");
+}
+
+int jq_moe_swiglu(const void* gate, const void* up, int64_t ld_in, const float* weights, const int32_t* order,
+                  const int32_t* count, void* h, int64_t ld_out, int64_t cols, int64_t max_rows, float limit, int dtype,
+                  jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(max_rows >= 0 && cols >= 0, JQ_EINVAL, "bad argument");
+    if (max_rows == 0 || cols == 0) return JQ_OK;
+    JQ_REQUIRE(gate && up && h, JQ_EINVAL, "null pointer");
+    const int blocks = (int)(max_rows < 8 * 148 ? max_rows : 8 * 148);
+    JQ_DISPATCH_DTYPE16(dtype, T,
+        (swiglu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gate, (const T*)up, ld_in, weights, order,
+                                                                     count, (T*)h, ld_out, (int)cols, (int)max_rows, limit)))
+    return check_launch("moe_swiglu");
+}
+
+int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T, int k, int64_t D,
+                   void* out, int64_t ldo, float* out_f32, int dtype, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(T >= 0 && k > 0 && D >= 0, JQ_EINVAL, "bad argument");
+    if (T == 0 || D == 0) return JQ_OK;
+    JQ_REQUIRE(y && (out || out_f32), JQ_EINVAL, "null pointer");
+    const int blocks = (int)(T < 8 * 148 ? T : 8 * 148);
+    JQ_DISPATCH_DTYPE16(dtype, A,
+        (combine_kernel<A><<<blocks, 256, 0, (cudaStream_t)stream>>>((const A*)y, ldy, inv, weights, (int)T, k, (int)D,
+                                                                      (A*)out, ldo, out_f32)))
+    return check_launch("moe_combine");
+}
+
+}  // extern "C"

@@ -42,6 +42,16 @@ struct GemmArgs {
     int gs, G;
     int y_vec_ok;    // rows of y are 16-byte aligned
     int* status;     // device status word, set to 1 when a bounded wait ran out
+    // grouped mode (routed experts): blockIdx.y indexes a tile list built by jq_moe_sort; rows are the
+    // expert-sorted (token, slot) pairs, weights come from per-expert pointer tables
+    const int32_t* tile_expert;
+    const int32_t* tile_row0;
+    const int32_t* num_tiles;
+    const int32_t* expert_offsets;
+    const uint32_t* const* codes_tab;
+    const void* const* scales_tab;
+    const void* const* biases_tab;
+    const int32_t* bits_tab;       // optional per-expert bit width: tiles of other widths exit
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
@@ -206,7 +216,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t n0 = (int64_t)blockIdx.x * BN, m0 = (int64_t)blockIdx.y * GEMM_BM;
+    const int64_t n0 = (int64_t)blockIdx.x * BN;
+    int64_t m0 = (int64_t)blockIdx.y * GEMM_BM, m_end = a.M;
+    const uint32_t* codes_g = a.codes;
+    const void* scales_g = a.scales;
+    const void* biases_g = a.biases;
+    if (a.tile_expert) {
+        // uniform for the whole CTA, before any barrier or tensor-memory allocation
+        if ((int)blockIdx.y >= *a.num_tiles) return;
+        const int e = a.tile_expert[blockIdx.y];
+        if (a.bits_tab && a.bits_tab[e] != BITS) return;
+        m0 = a.tile_row0[blockIdx.y];
+        m_end = a.expert_offsets[e + 1];
+        codes_g = a.codes_tab[e];
+        scales_g = a.scales_tab[e];
+        biases_g = a.biases_tab[e];
+    }
     const int nkb = (int)(a.K / GEMM_BK);
 
     if (threadIdx.x == 0) {
@@ -257,9 +282,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         // ---------------- dequantizers: one weight row per thread ----------------
         const int r = (warp - 2) * 32 + lane;                 // row within the tile
         const int64_t n = min(n0 + r, a.N - 1);               // rows past N are computed but never stored
-        const uint32_t* crow = a.codes + n * (a.K * BITS / 32);
-        const uint16_t* srow = reinterpret_cast<const uint16_t*>(a.scales) + n * a.G;
-        const uint16_t* brow = reinterpret_cast<const uint16_t*>(a.biases) + n * a.G;
+        const uint32_t* crow = codes_g + n * (a.K * BITS / 32);
+        const uint16_t* srow = reinterpret_cast<const uint16_t*>(scales_g) + n * a.G;
+        const uint16_t* brow = reinterpret_cast<const uint16_t*>(biases_g) + n * a.G;
         const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
         const uint32_t sw = (uint32_t)(r & 7);
         const int gs = a.gs;
@@ -316,7 +341,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
             for (int c0 = half * COLS_PER_WARP; c0 < (half + 1) * COLS_PER_WARP; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-                if (m < a.M) {
+                if (m < m_end) {
                     if (a.y_vec_ok && n0 + c0 + 32 <= a.N) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -364,7 +389,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 template <typename AT, int BITS, int BN>
-static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, int64_t m_tiles, cudaStream_t st) {
     constexpr size_t smem = 1024 + GEMM_SA * GEMM_BM * GEMM_BK * 2 + GEMM_SB * BN * GEMM_BK * 2 + 256;
     static bool attr_done[64] = {};
     int dev = 0;
@@ -374,20 +399,30 @@ static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, cudaStream_t 
                                         (int)smem));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)((a.M + GEMM_BM - 1) / GEMM_BM));
+    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)m_tiles);
     qgemm_tc_kernel<AT, BITS, BN><<<grid, 64 + BN, smem, st>>>(xmap, a);
     return check_launch("qgemm");
 }
 
+struct GroupedArgs {
+    const int32_t *tile_expert, *tile_row0, *num_tiles, *expert_offsets, *bits_tab;
+    const uint32_t* const* codes_tab;
+    const void* const* scales_tab;
+    const void* const* biases_tab;
+    int64_t max_tiles;
+};
+
+// Dense when grp == nullptr (codes/scales/biases of one matrix); grouped otherwise (x holds the M
+// expert-sorted rows, the weight pointers come from the tables).
 int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
                    const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int gs, void* y,
-                   int y_dtype, int64_t ldy, cudaStream_t st) {
+                   int y_dtype, int64_t ldy, const GroupedArgs* grp, cudaStream_t st) {
     int rc = check_quant_shape(N, K, bits, gs);
     if (rc != JQ_OK) return rc;
     JQ_REQUIRE(M >= 0, JQ_EINVAL, "negative M");
     if (M == 0 || N == 0) return JQ_OK;
     JQ_REQUIRE(K > 0, JQ_EINVAL, "K must be positive");
-    JQ_REQUIRE(x && codes && scales && biases && y, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(x && y && (grp || (codes && scales && biases)), JQ_EINVAL, "null pointer");
     JQ_REQUIRE(x_dtype == JQ_BF16 || x_dtype == JQ_F16, JQ_EINVAL, "qgemm activations must be bf16 or f16");
     JQ_REQUIRE(sidecar_dtype == x_dtype && y_dtype == x_dtype, JQ_EUNSUPPORTED,
                "qgemm needs scales/biases and the output in the activation dtype");
@@ -415,10 +450,21 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     a.y_vec_ok = (aligned(y, 16) && ldy % 8 == 0) ? 1 : 0;
     a.status = status_word();
     JQ_REQUIRE(a.status != nullptr, JQ_ECUDA, "could not locate the device status word");
+    a.tile_expert = grp ? grp->tile_expert : nullptr;
+    a.tile_row0 = grp ? grp->tile_row0 : nullptr;
+    a.num_tiles = grp ? grp->num_tiles : nullptr;
+    a.expert_offsets = grp ? grp->expert_offsets : nullptr;
+    a.codes_tab = grp ? grp->codes_tab : nullptr;
+    a.scales_tab = grp ? grp->scales_tab : nullptr;
+    a.biases_tab = grp ? grp->biases_tab : nullptr;
+    a.bits_tab = grp ? grp->bits_tab : nullptr;
+    const int64_t m_tiles = grp ? grp->max_tiles : (M + GEMM_BM - 1) / GEMM_BM;
+    if (m_tiles == 0) return JQ_OK;
+    JQ_REQUIRE(m_tiles < 65536, JQ_EUNSUPPORTED, "too many row tiles for one launch (%lld)", (long long)m_tiles);
 #define JQ_GEMM_CASE(B)                                                                                  \
     if (bits == B)                                                                                       \
-        return x_dtype == JQ_BF16 ? launch_gemm<__nv_bfloat16, B, 128>(xmap, a, st)                      \
-                                  : launch_gemm<__half, B, 128>(xmap, a, st);
+        return x_dtype == JQ_BF16 ? launch_gemm<__nv_bfloat16, B, 128>(xmap, a, m_tiles, st)                      \
+                                  : launch_gemm<__half, B, 128>(xmap, a, m_tiles, st);
     JQ_GEMM_CASE(2) JQ_GEMM_CASE(3) JQ_GEMM_CASE(4) JQ_GEMM_CASE(5) JQ_GEMM_CASE(6) JQ_GEMM_CASE(8)
 #undef JQ_GEMM_CASE
     return fail(JQ_EUNSUPPORTED, "bits=%d", bits);
@@ -432,7 +478,24 @@ int jq_qgemm(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t*
              const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
              int y_dtype, int64_t ldy, jq_stream_t stream) {
     return jq::qgemm_dispatch(x, x_dtype, M, ldx, codes, scales, biases, sidecar_dtype, N, K, bits, group_size, y,
-                              y_dtype, ldy, (cudaStream_t)stream);
+                              y_dtype, ldy, nullptr, (cudaStream_t)stream);
+}
+
+int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx, const int32_t* expert_offsets,
+                const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* num_tiles, int64_t max_tiles,
+                const uint32_t* const* codes_tab, const void* const* scales_tab, const void* const* biases_tab,
+                const int32_t* bits_tab, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size,
+                void* y_sorted, int64_t ldy, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(expert_offsets && tile_expert && tile_row0 && num_tiles && codes_tab && scales_tab && biases_tab,
+               JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(max_tiles >= 0, JQ_EINVAL, "negative max_tiles");
+    GroupedArgs g;
+    g.tile_expert = tile_expert; g.tile_row0 = tile_row0; g.num_tiles = num_tiles; g.expert_offsets = expert_offsets;
+    g.bits_tab = bits_tab; g.codes_tab = codes_tab; g.scales_tab = scales_tab; g.biases_tab = biases_tab;
+    g.max_tiles = max_tiles;
+    return qgemm_dispatch(x_sorted, act_dtype, max_rows, ldx, nullptr, nullptr, nullptr, sidecar_dtype, N, K, bits,
+                          group_size, y_sorted, act_dtype, ldy, &g, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -42,6 +42,14 @@ struct GemvArgs {
     int64_t N, K, ldx, ldy;
     int M, G, nbuf;
     int pdl;      // launched with programmatic stream serialization (weights are static)
+    // gather mode (routed experts, decode): blockIdx.y = (token, slot) pair p, expert e = pair_expert[p];
+    // weights come from per-expert pointer tables, x row = p / x_div, y row = p, M = 1
+    const int32_t* pair_expert;
+    const uint32_t* const* codes_tab;
+    const void* const* scales_tab;
+    const void* const* biases_tab;
+    const int32_t* bits_tab;      // optional: experts whose width differs from the launch's are skipped
+    int x_div, num_experts;
 };
 
 constexpr int GEMV_WARPS = 4;
@@ -93,6 +101,19 @@ qgemv_mma_kernel(const GemvArgs a) {
     const uint16_t* xs16 = reinterpret_cast<const uint16_t*>(a.x);
     const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(a.scales);
     const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(a.biases);
+    const uint32_t* codes_g = a.codes;
+    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
+    if (a.pair_expert) {
+        const int p = blockIdx.y;
+        const int e = a.pair_expert[p];
+        if (e < 0 || e >= a.num_experts) return;                      // expert of another rank
+        if (a.bits_tab && a.bits_tab[e] != BITS) return;              // handled by the launch of its own width
+        codes_g = a.codes_tab[e];
+        sc16 = reinterpret_cast<const uint16_t*>(a.scales_tab[e]);
+        bi16 = reinterpret_cast<const uint16_t*>(a.biases_tab[e]);
+        xs16 += (int64_t)(p / a.x_div) * a.ldx;
+        y16 += (int64_t)p * a.ldy;
+    }
 
     if (lane < 8)
         for (int b = 0; b < nbuf; ++b)
@@ -101,7 +122,7 @@ qgemv_mma_kernel(const GemvArgs a) {
     // ---- stage copies: 16 bytes per lane and instruction -------------------------------------
     // LPR lanes share a code row (the smallest power of two covering its chunks), so one
     // instruction covers 32/LPR rows and the per-iteration address update is two adds.
-    const uint8_t* code_base = reinterpret_cast<const uint8_t*>(a.codes) + n0 * rowbytes;
+    const uint8_t* code_base = reinterpret_cast<const uint8_t*>(codes_g) + n0 * rowbytes;
     auto issue_codes = [&](int st, int b) {
         if (st < nst) {
             const int k0 = st * KT;
@@ -329,7 +350,7 @@ qgemv_mma_kernel(const GemvArgs a) {
             for (int w = 0; w < NW; ++w) v += red[((w * MT + mt) * 4 + i) * 32 + lane];
             const int row = mt * 16 + g + ((i & 2) ? 8 : 0), m = 2 * tig + (i & 1);
             if (row < rows_valid && m < M)
-                reinterpret_cast<uint16_t*>(a.y)[(int64_t)m * a.ldy + n0 + row] = A::from_f32(v);
+                y16[(int64_t)m * a.ldy + n0 + row] = A::from_f32(v);
         }
     }
 }
@@ -353,7 +374,22 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
     const int64_t n = (int64_t)blockIdx.x * 4 + warp;
     if (n >= a.N) return;
     const int64_t rowwords = a.K * BITS / 32;
-    const uint32_t* row = a.codes + n * rowwords;
+    const uint32_t* codes_g = a.codes;
+    const void* scales_g = a.scales;
+    const void* biases_g = a.biases;
+    int64_t x_row0 = 0, y_row0 = 0;
+    if (a.pair_expert) {
+        const int p = blockIdx.y;
+        const int e = a.pair_expert[p];
+        if (e < 0 || e >= a.num_experts) return;
+        if (a.bits_tab && a.bits_tab[e] != BITS) return;
+        codes_g = a.codes_tab[e];
+        scales_g = a.scales_tab[e];
+        biases_g = a.biases_tab[e];
+        x_row0 = p / a.x_div;
+        y_row0 = p;
+    }
+    const uint32_t* row = codes_g + n * rowwords;
     const int64_t n_oct = a.K / 8;
     float acc[8];
 #pragma unroll
@@ -368,8 +404,8 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
         const unsigned long long bitsv =
             ((unsigned long long)__funnelshift_r(c1, c2, sh) << 32) | __funnelshift_r(c0, c1, sh);
         const int64_t grp = (oct * 8) / gs;
-        const float s = ld_any(a.scales, n * a.G + grp, sc_dtype);
-        const float bs = ld_any(a.biases, n * a.G + grp, sc_dtype);
+        const float s = ld_any(scales_g, n * a.G + grp, sc_dtype);
+        const float bs = ld_any(biases_g, n * a.G + grp, sc_dtype);
         float q[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) q[j] = (float)((uint32_t)(bitsv >> (j * BITS)) & ((1u << BITS) - 1u));
@@ -379,7 +415,7 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
                 float qx = 0.f, sx = 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const float xv = ld_any(a.x, (int64_t)m * a.ldx + oct * 8 + j, x_dtype);
+                    const float xv = ld_any(a.x, (x_row0 + m) * a.ldx + oct * 8 + j, x_dtype);
                     qx = fmaf(q[j], xv, qx);
                     sx += xv;
                 }
@@ -392,7 +428,7 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
         float v = acc[m];
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
-        if (lane == 0 && m < a.M) st_any(a.y, (int64_t)m * a.ldy + n, y_dtype, v);
+        if (lane == 0 && m < a.M) st_any(a.y, (y_row0 + m) * a.ldy + n, y_dtype, v);
     }
 }
 
@@ -414,7 +450,7 @@ static bool force_simple() {
 }
 
 template <typename AT, int BITS, int GS, int MT>
-static int launch_mma_mt(GemvArgs a, cudaStream_t st, bool* launched) {
+static int launch_mma_mt(GemvArgs a, int pairs, cudaStream_t st, bool* launched) {
     using Geo = GemvGeom<BITS, GS, MT>;
     *launched = false;
     const int sb = Geo::stage_bytes(a.M);
@@ -431,7 +467,7 @@ static int launch_mma_mt(GemvArgs a, cudaStream_t st, bool* launched) {
     }
     const unsigned grid = (unsigned)((a.N + 16 * MT - 1) / (16 * MT));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
+    cfg.gridDim = dim3(grid, (unsigned)pairs);
     cfg.blockDim = dim3(GEMV_WARPS * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -446,11 +482,11 @@ static int launch_mma_mt(GemvArgs a, cudaStream_t st, bool* launched) {
 }
 
 template <typename AT, int BITS, int GS>
-static int launch_mma(const GemvArgs& a, cudaStream_t st, bool* launched) {
+static int launch_mma(const GemvArgs& a, int pairs, cudaStream_t st, bool* launched) {
     // 32-row tiles halve the per-weight cost of the activation operand; use them once
     // they still give every SM at least two CTAs
-    if (a.N >= (int64_t)32 * 2 * sm_count()) return launch_mma_mt<AT, BITS, GS, 2>(a, st, launched);
-    return launch_mma_mt<AT, BITS, GS, 1>(a, st, launched);
+    if (a.N * pairs >= (int64_t)32 * 2 * sm_count()) return launch_mma_mt<AT, BITS, GS, 2>(a, pairs, st, launched);
+    return launch_mma_mt<AT, BITS, GS, 1>(a, pairs, st, launched);
 }
 
 int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
@@ -479,12 +515,14 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
         a.M = (int)((M - m0) < 8 ? (M - m0) : 8);
         a.G = (int)(K / gs);
         a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
+        a.pair_expert = nullptr; a.codes_tab = nullptr; a.scales_tab = nullptr; a.biases_tab = nullptr;
+        a.bits_tab = nullptr; a.x_div = 1; a.num_experts = 0;
         bool launched = false;
         if (fast) {
 #define JQ_GEMV_CASE(B, GSZ)                                                                     \
     if (bits == B && gs == GSZ) {                                                                \
-        rc = (x_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, st, &launched)          \
-                                  : launch_mma<__half, B, GSZ>(a, st, &launched);                \
+        rc = (x_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, 1, st, &launched)          \
+                                  : launch_mma<__half, B, GSZ>(a, 1, st, &launched);                \
         if (rc != JQ_OK) return rc;                                                              \
     }
             JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(6, 64) JQ_GEMV_CASE(8, 64)
@@ -503,9 +541,64 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     return JQ_OK;
 }
 
+// Routed-expert mat-vec for few (token, slot) pairs: y[p] = deq(W[expert[p]]) . x[p / x_div].
+int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert,
+                          int64_t pairs, const uint32_t* const* codes_tab, const void* const* scales_tab,
+                          const void* const* biases_tab, const int32_t* bits_tab, int num_experts, int sidecar_dtype,
+                          int64_t N, int64_t K, int bits, int gs, void* y, int64_t ldy, cudaStream_t st) {
+    int rc = check_quant_shape(N, K, bits, gs);
+    if (rc != JQ_OK) return rc;
+    JQ_REQUIRE(valid_dtype(act_dtype) && valid_dtype(sidecar_dtype), JQ_EINVAL, "bad dtype");
+    JQ_REQUIRE(pairs >= 0 && pairs < 65536, JQ_EINVAL, "gather mat-vec takes fewer than 65536 pairs, got %lld",
+               (long long)pairs);
+    if (pairs == 0 || N == 0) return JQ_OK;
+    JQ_REQUIRE(K > 0 && x_div > 0 && num_experts > 0, JQ_EINVAL, "bad argument");
+    JQ_REQUIRE(x && pair_expert && codes_tab && scales_tab && biases_tab && y, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(ldx >= K && ldy >= N, JQ_EINVAL, "leading dimension too small");
+    JQ_REQUIRE(N < (1ll << 31) && K < (1ll << 31), JQ_EUNSUPPORTED, "dimension too large");
+    GemvArgs a;
+    a.x = x; a.codes = nullptr; a.scales = nullptr; a.biases = nullptr; a.y = y;
+    a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.M = 1; a.G = (int)(K / gs); a.nbuf = 0; a.pdl = 0;
+    a.pair_expert = pair_expert; a.codes_tab = codes_tab; a.scales_tab = scales_tab; a.biases_tab = biases_tab;
+    a.bits_tab = bits_tab; a.x_div = x_div; a.num_experts = num_experts;
+    // the per-expert base pointers are not known on the host: the fast path relies on the caller's
+    // promise (checked for the row pitch here) that every expert tensor is 16-byte aligned
+    const bool fast = !force_simple() && (gs == 64 || gs == 128) && act_dtype != JQ_F32 && sidecar_dtype == act_dtype &&
+                      ((K * bits / 8) % 16 == 0) && aligned(x, 16) && (ldx % 8 == 0) && ((K / gs) % 4 == 0) && bits != 5;
+    bool launched = false;
+    if (fast) {
+#define JQ_GEMV_CASE(B, GSZ)                                                                          \
+    if (bits == B && gs == GSZ) {                                                                     \
+        rc = (act_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, (int)pairs, st, &launched) \
+                                    : launch_mma<__half, B, GSZ>(a, (int)pairs, st, &launched);       \
+        if (rc != JQ_OK) return rc;                                                                   \
+    }
+        JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(6, 64) JQ_GEMV_CASE(8, 64)
+        JQ_GEMV_CASE(2, 128) JQ_GEMV_CASE(3, 128) JQ_GEMV_CASE(4, 128) JQ_GEMV_CASE(6, 128) JQ_GEMV_CASE(8, 128)
+#undef JQ_GEMV_CASE
+    }
+    if (!launched) {
+        dim3 grid((unsigned)((N + 3) / 4), (unsigned)pairs);
+        JQ_DISPATCH_BITS(bits, B,
+            (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(a, act_dtype, sidecar_dtype, act_dtype, gs)))
+        rc = check_launch("gather qgemv (general)");
+        if (rc != JQ_OK) return rc;
+    }
+    return JQ_OK;
+}
+
 }  // namespace jq
 
 extern "C" {
+
+int jq_gather_qgemv(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert, int64_t pairs,
+                    const uint32_t* const* codes_tab, const void* const* scales_tab, const void* const* biases_tab,
+                    const int32_t* bits_tab, int num_experts, int sidecar_dtype, int64_t N, int64_t K, int bits,
+                    int group_size, void* y, int64_t ldy, jq_stream_t stream) {
+    return jq::gather_qgemv_dispatch(x, act_dtype, ldx, x_div, pair_expert, pairs, codes_tab, scales_tab, biases_tab,
+                                     bits_tab, num_experts, sidecar_dtype, N, K, bits, group_size, y, ldy,
+                                     (cudaStream_t)stream);
+}
 
 int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
              const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,

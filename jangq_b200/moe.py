@@ -1,0 +1,287 @@
+"""Routed mixture-of-experts over quantized experts.
+
+    ExpertBank        the stacked-expert weight holder (SwitchProj, jang_tools/dsv41/model.py:847-857),
+                      optionally with a different bit width per expert
+    gather_qmm        <-> mx.gather_qmm call shape of jang_tools/dots3/ops.py:168-192
+    route_softmax_topk  softmax -> top-k -> renormalise (dots3/ops.py:159-162 normalisation)
+    moe_layer         the layer logic of dsv41/model.py:1206-1245 (sort by expert above 64 pairs,
+                      SwiGLU with optional clamp, routing weight applied before down, f32 sum over
+                      slots, optional shared expert)
+
+Every matmul runs in libjangq_b200.so: the tensor-core grouped GEMM over expert-sorted rows, or
+the gather mat-vec below the sort threshold.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from . import _lib, ops
+from ._lib import JangqError
+
+SORT_THRESHOLD = 64      # pairs; dsv41/model.py:1206 (n * topk >= 64), mlx-lm SwitchGLU indices.size >= 64
+
+
+class ExpertBank:
+    """Quantized weights of E experts for one projection: y = deq(W[e]) . x.
+
+    Uniform: `weight` int32/uint32 [E, N, K*bits/32], `scales`/`biases` [E, N, K/gs], one
+    (bits, group_size) for all experts (the reference's layout).  Mixed: `from_experts` takes one
+    (wq, scales, biases, bits) tuple per expert.  Device pointer tables are built once.
+    """
+
+    def __init__(self, weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bits: int,
+                 group_size: int = 64):
+        dev = _lib.require_cuda(weight, scales, biases)
+        weight = ops._as_i32(weight).contiguous()
+        scales, biases = scales.contiguous(), biases.contiguous()
+        if weight.dim() != 3:
+            raise JangqError(_lib.JQ_EINVAL, f"stacked expert weight must be [E, N, K*bits/32], got {tuple(weight.shape)}")
+        self.K = ops._check_triple(weight, scales, biases, bits, group_size)
+        self.E, self.N = weight.shape[0], weight.shape[1]
+        self.group_size = group_size
+        self.device, self.sidecar_dtype = dev, scales.dtype
+        self._keep = [weight, scales, biases]
+        self.weight, self.scales, self.biases = weight, scales, biases
+        self.expert_bits = [bits] * self.E
+        self._build_tables([weight[e] for e in range(self.E)], [scales[e] for e in range(self.E)],
+                           [biases[e] for e in range(self.E)])
+
+    @classmethod
+    def from_experts(cls, experts: Sequence[tuple], group_size: int = 64) -> "ExpertBank":
+        """experts[e] = (wq [N, K*bits_e/32], scales [N, K/gs], biases, bits_e): per-expert widths."""
+        self = cls.__new__(cls)
+        ws, ss, bs, bits = [], [], [], []
+        for wq, s, b, nb in experts:
+            wq = ops._as_i32(wq).contiguous()
+            K = ops._check_triple(wq, s, b, nb, group_size)
+            ws.append(wq), ss.append(s.contiguous()), bs.append(b.contiguous()), bits.append(int(nb))
+            if len(ws) == 1:
+                self.K, self.N = K, wq.shape[0]
+            elif K != self.K or wq.shape[0] != self.N:
+                raise JangqError(_lib.JQ_EINVAL, "all experts of a bank must share [N, K]")
+        self.E, self.group_size = len(ws), group_size
+        self.device = _lib.require_cuda(*ws, *ss, *bs)
+        self.sidecar_dtype = ss[0].dtype
+        self._keep = [ws, ss, bs]
+        self.weight = self.scales = self.biases = None
+        self.expert_bits = bits
+        self._build_tables(ws, ss, bs)
+        return self
+
+    def _build_tables(self, ws, ss, bs):
+        for t in ws + ss + bs:
+            if t.data_ptr() % 16:
+                raise JangqError(_lib.JQ_EINVAL, "expert tensors must be 16-byte aligned")
+        dev = self.device
+        self.codes_tab = torch.tensor([t.data_ptr() for t in ws], dtype=torch.int64, device=dev)
+        self.scales_tab = torch.tensor([t.data_ptr() for t in ss], dtype=torch.int64, device=dev)
+        self.biases_tab = torch.tensor([t.data_ptr() for t in bs], dtype=torch.int64, device=dev)
+        self.distinct_bits = sorted(set(self.expert_bits))
+        self.bits_tab = (torch.tensor(self.expert_bits, dtype=torch.int32, device=dev)
+                         if len(self.distinct_bits) > 1 else None)
+
+    def slice(self, e0: int, e1: int) -> "ExpertBank":
+        """Experts [e0, e1) as their own bank (expert-parallel shard), sharing storage."""
+        if self.weight is not None:
+            return ExpertBank(self.weight[e0:e1], self.scales[e0:e1], self.biases[e0:e1], self.expert_bits[0],
+                              self.group_size)
+        ws, ss, bs = self._keep
+        return ExpertBank.from_experts([(ws[e], ss[e], bs[e], self.expert_bits[e]) for e in range(e0, e1)],
+                                       self.group_size)
+
+    def _sidecars_as(self, dtype):
+        """The kernels take sidecars in the activation dtype (converted once, then cached)."""
+        if self.sidecar_dtype == dtype:
+            return self
+        cache = self.__dict__.setdefault("_converted", {})
+        if dtype not in cache:
+            if self.weight is not None:
+                cache[dtype] = ExpertBank(self.weight, self.scales.to(dtype), self.biases.to(dtype),
+                                          self.expert_bits[0], self.group_size)
+            else:
+                ws, ss, bs = self._keep
+                cache[dtype] = ExpertBank.from_experts([(w, s.to(dtype), b.to(dtype), nb) for w, s, b, nb in
+                                                        zip(ws, ss, bs, self.expert_bits)], self.group_size)
+        return cache[dtype]
+
+
+class SortedPairs:
+    """Result of jq_moe_sort for one routing decision; reused by gate, up and down."""
+
+    def __init__(self, idx_flat: torch.Tensor, num_experts: int, expert_base: int = 0):
+        lib = _lib.load()
+        dev = idx_flat.device
+        n = idx_flat.numel()
+        self.n, self.E = n, num_experts
+        self.max_tiles = int(lib.jq_moe_sort_max_tiles(n, num_experts, _lib.MOE_TILE_M))
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.order = torch.empty(max(n, 1), **i32)
+        self.inv = torch.empty(max(n, 1), **i32)
+        self.offsets = torch.empty(num_experts + 1, **i32)
+        self.tile_expert = torch.empty(max(self.max_tiles, 1), **i32)
+        self.tile_row0 = torch.empty(max(self.max_tiles, 1), **i32)
+        self.num_tiles = torch.empty(1, **i32)
+        _lib.check(lib.jq_moe_sort(idx_flat.data_ptr(), n, num_experts, expert_base, self.order.data_ptr(),
+                                   self.inv.data_ptr(), self.offsets.data_ptr(), _lib.MOE_TILE_M,
+                                   self.tile_expert.data_ptr(), self.tile_row0.data_ptr(), self.num_tiles.data_ptr(),
+                                   _lib.stream_ptr(dev)))
+        self.count_ptr = self.offsets.data_ptr() + 4 * num_experts      # device address of the kept-pair count
+
+
+def _gather_rows(src: torch.Tensor, sp: SortedPairs, div: int) -> torch.Tensor:
+    lib = _lib.load()
+    dst = torch.empty((max(sp.n, 1), src.shape[1]), dtype=src.dtype, device=src.device)
+    _lib.check(lib.jq_gather_rows(src.data_ptr(), src.stride(0), sp.order.data_ptr(), sp.count_ptr, div, dst.data_ptr(),
+                                  dst.stride(0), src.shape[1], sp.n, _lib.dtype_id(src.dtype), _lib.stream_ptr(src.device)))
+    return dst
+
+
+def _moe_gemm(x_sorted: torch.Tensor, sp: SortedPairs, bank: ExpertBank) -> torch.Tensor:
+    lib = _lib.load()
+    bank = bank._sidecars_as(x_sorted.dtype)
+    y = torch.empty((x_sorted.shape[0], bank.N), dtype=x_sorted.dtype, device=x_sorted.device)
+    for bits in bank.distinct_bits:
+        _lib.check(lib.jq_moe_gemm(x_sorted.data_ptr(), _lib.dtype_id(x_sorted.dtype), sp.n, x_sorted.stride(0),
+                                   sp.offsets.data_ptr(), sp.tile_expert.data_ptr(), sp.tile_row0.data_ptr(),
+                                   sp.num_tiles.data_ptr(), sp.max_tiles, bank.codes_tab.data_ptr(),
+                                   bank.scales_tab.data_ptr(), bank.biases_tab.data_ptr(),
+                                   bank.bits_tab.data_ptr() if bank.bits_tab is not None else None,
+                                   _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
+                                   y.data_ptr(), y.stride(0), _lib.stream_ptr(x_sorted.device)))
+    return y
+
+
+def _gather_qgemv(x: torch.Tensor, x_div: int, pair_expert: torch.Tensor, bank: ExpertBank) -> torch.Tensor:
+    lib = _lib.load()
+    bank = bank._sidecars_as(x.dtype)
+    P = pair_expert.numel()
+    y = torch.zeros((P, bank.N), dtype=x.dtype, device=x.device)
+    for bits in bank.distinct_bits:
+        _lib.check(lib.jq_gather_qgemv(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), x_div, pair_expert.data_ptr(),
+                                       P, bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
+                                       bank.biases_tab.data_ptr(),
+                                       bank.bits_tab.data_ptr() if bank.bits_tab is not None else None, bank.E,
+                                       _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
+                                       y.data_ptr(), y.stride(0), _lib.stream_ptr(x.device)))
+    return y
+
+
+def gather_qmm(x: torch.Tensor, w, scales: torch.Tensor | None = None, biases: torch.Tensor | None = None,
+               rhs_indices: torch.Tensor | None = None, lhs_indices: torch.Tensor | None = None,
+               transpose: bool = True, group_size: int = 64, bits: int = 4, sorted_indices: bool = False) -> torch.Tensor:
+    """y[r] = x[lhs[r]] . deq(w[rhs[r]])^T for stacked experts w [E, N, K*bits/32] (or an ExpertBank).
+
+    x is [R0, K] (singleton middle dims are squeezed); rhs_indices [R] or [T, k]; lhs_indices [R]
+    or None, in which case row r of x is used when R0 == R, and row r // k when rhs is [T, k] with
+    R0 == T (MLX broadcasts the batch dims the same way).  As in the reference
+    (dots3/ops.py:175-176) sorted_indices=True needs lhs_indices.  Returns [R, N].
+    """
+    if not transpose:
+        raise JangqError(_lib.JQ_EUNSUPPORTED, "gather_qmm: only transpose=True is provided")
+    if rhs_indices is None:
+        raise JangqError(_lib.JQ_EINVAL, "gather_qmm needs rhs_indices")
+    if sorted_indices and lhs_indices is None:
+        raise ValueError("sorted_indices=True requires lhs_indices")
+    bank = w if isinstance(w, ExpertBank) else ExpertBank(w, scales, biases, bits, group_size)
+    dev = _lib.require_cuda(x, rhs_indices)
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.dtype not in (torch.bfloat16, torch.float16):
+        raise JangqError(_lib.JQ_EINVAL, f"activations must be bfloat16 or float16, got {x2.dtype}")
+    if x2.shape[1] != bank.K:
+        raise JangqError(_lib.JQ_EINVAL, f"x has {x2.shape[1]} features, experts expect {bank.K}")
+    k = rhs_indices.shape[-1] if rhs_indices.dim() == 2 else 1
+    rhs = rhs_indices.reshape(-1).to(torch.int32).contiguous()
+    R = rhs.numel()
+    if lhs_indices is not None:
+        lhs = lhs_indices.reshape(-1).to(torch.int64)
+        if lhs.numel() != R:
+            raise JangqError(_lib.JQ_EINVAL, "lhs_indices and rhs_indices differ in length")
+        x2, x_div = x2.index_select(0, lhs), 1
+    elif x2.shape[0] == R:
+        x_div = 1
+    elif rhs_indices.dim() == 2 and x2.shape[0] == rhs_indices.shape[0]:
+        x_div = k
+    else:
+        raise JangqError(_lib.JQ_EINVAL, f"cannot match {x2.shape[0]} rows of x with {R} indices")
+    x2 = x2.contiguous()
+    with torch.cuda.device(dev):
+        if R < SORT_THRESHOLD:
+            return _gather_qgemv(x2, x_div, rhs, bank)
+        sp = SortedPairs(rhs, bank.E)
+        xs = _gather_rows(x2, sp, x_div)
+        ys = _moe_gemm(xs, sp, bank)
+        return ys.index_select(0, sp.inv.to(torch.int64))
+
+
+def route_softmax_topk(logits: torch.Tensor, k: int, renorm: bool = True, scale: float = 1.0):
+    """(idx int32 [T, k], w float32 [T, k]): softmax over experts in f32, top-k by score (ties to
+    the lower id, as jang_tools/dsv41/metal_decode.py:1141), w / (sum w + 1e-20) * scale."""
+    p = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(p, k, dim=-1, sorted=True)
+    if renorm:
+        w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
+    return idx.to(torch.int32), (w * scale).float()
+
+
+def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertBank, up: ExpertBank,
+              down: ExpertBank, swiglu_limit: float = 0.0, shared=None, expert_base: int = 0,
+              out_f32: bool = False) -> torch.Tensor:
+    """Routed SwiGLU experts: out[t] = sum_j down_e( silu(gate_e x_t) * up_e x_t * w[t, j] ), e = idx[t, j].
+
+    x [T, H] bf16/f16; idx [T, k] int; w [T, k] f32.  Follows dsv41/model.py:1206-1245.  With
+    `expert_base` the banks hold experts [expert_base, expert_base + E) only and the other
+    pairs contribute nothing (expert parallelism).  `shared` = (gate, up, down) JANGLinear-like
+    modules of an always-on expert, added in f32.  Returns [T, H] in x.dtype (f32 if out_f32).
+    """
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, idx, w)
+    T, H = x.shape
+    k = idx.shape[1]
+    P = T * k
+    idx32 = idx.reshape(-1).to(torch.int32).contiguous()
+    wf = w.reshape(-1).float().contiguous()
+    x = x.contiguous()
+    dt = _lib.dtype_id(x.dtype)
+    st = _lib.stream_ptr(dev)
+    I = gate.N
+    with torch.cuda.device(dev):
+        if P >= SORT_THRESHOLD:
+            sp = SortedPairs(idx32, gate.E, expert_base)
+            xs = _gather_rows(x, sp, k)
+            g = _moe_gemm(xs, sp, gate)
+            u = _moe_gemm(xs, sp, up)
+            h = torch.empty((max(P, 1), I), dtype=x.dtype, device=dev)
+            _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), sp.order.data_ptr(),
+                                         sp.count_ptr, h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
+            y = _moe_gemm(h, sp, down)
+            inv_ptr = sp.inv.data_ptr()
+        else:
+            local = idx32 - expert_base if expert_base else idx32
+            g = _gather_qgemv(x, k, local, gate)
+            u = _gather_qgemv(x, k, local, up)
+            h = torch.empty((P, I), dtype=x.dtype, device=dev)
+            _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), None, None,
+                                         h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
+            y = _gather_qgemv(h, 1, local, down)
+            # pairs of other ranks' experts were skipped by the kernels: mask them in the combine
+            inv = torch.where((local >= 0) & (local < gate.E), torch.arange(P, device=dev, dtype=torch.int32),
+                              torch.full((P,), -1, device=dev, dtype=torch.int32))
+            inv_ptr = inv.data_ptr()
+        need_f32 = out_f32 or shared is not None
+        acc = torch.empty((T, H), dtype=torch.float32, device=dev) if need_f32 else None
+        out = None if need_f32 else torch.empty((T, H), dtype=x.dtype, device=dev)
+        _lib.check(lib.jq_moe_combine(y.data_ptr(), y.stride(0), inv_ptr, None, T, k, H,
+                                      out.data_ptr() if out is not None else None, H,
+                                      acc.data_ptr() if acc is not None else None, dt, st))
+        if shared is not None:
+            sg, su, sd = shared
+            g2, u2 = sg(x).float(), su(x).float()
+            if swiglu_limit > 0:
+                u2 = u2.clamp(-swiglu_limit, swiglu_limit)
+                g2 = g2.clamp(max=swiglu_limit)
+            acc = acc + sd((torch.nn.functional.silu(g2) * u2).to(x.dtype)).float()
+        if need_f32:
+            return acc if out_f32 else acc.to(x.dtype)
+        return out

@@ -1,0 +1,183 @@
+"""GPU parity of the routed-MoE path (sort, gather, grouped GEMM, SwiGLU, combine, gather
+mat-vec) against the CPU oracle.  Index outputs are bit-exact; floating-point outputs are held to
+max |y-ref| / max|ref| <= 1e-2 and cosine >= 0.9999 (BASELINE north star)."""
+import numpy as np
+import pytest
+import torch
+
+import jangq_b200 as jq
+from jangq_b200 import _lib
+from jangq_b200.moe import SORT_THRESHOLD, SortedPairs
+from oracle import jang_oracle as jo
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def close(y, ref):
+    y = np.asarray(y, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert np.abs(y - ref).max() / np.abs(ref).max() <= 1e-2
+    assert float((y * ref).sum() / (np.linalg.norm(y) * np.linalg.norm(ref))) >= 0.9999
+
+
+def make_bank(E, N, K, bits, gs, seed, dtype=torch.bfloat16):
+    rng = np.random.default_rng(seed)
+    w = torch.from_numpy((rng.standard_normal((E, N, K)) * 0.05).astype(np.float32)).to(DEV).to(dtype)
+    wq, s, b = jq.quantize(w, gs, bits)
+    return jq.ExpertBank(wq, s, b, bits, gs), (wq.cpu().numpy().view(np.uint32), s.float().cpu().numpy(),
+                                               b.float().cpu().numpy(), bits, gs)
+
+
+@pytest.mark.parametrize("n,E,base", ((0, 4, 0), (1, 4, 0), (37, 8, 0), (4096, 128, 0), (16384, 128, 0), (40960, 512, 0),
+                                      (5000, 16, 16), (3000, 64, 128)))
+def test_sort_matches_stable_argsort(n, E, base):
+    rng = np.random.default_rng(n + E)
+    total = E if base == 0 else 4 * E + base
+    idx = rng.integers(0, total, n).astype(np.int32)
+    sp = SortedPairs(torch.from_numpy(idx).to(DEV), E, base)
+    torch.cuda.synchronize()
+    local = idx - base
+    keep = (local >= 0) & (local < E)
+    order_ref = np.argsort(np.where(keep, local, E), kind="stable").astype(np.int32)[: keep.sum()]
+    off_ref = np.concatenate([[0], np.cumsum(np.bincount(local[keep], minlength=E))]).astype(np.int32)
+    kept = int(sp.offsets[E])
+    assert kept == keep.sum()
+    assert np.array_equal(sp.offsets.cpu().numpy(), off_ref)
+    assert np.array_equal(sp.order.cpu().numpy()[:kept], order_ref)
+    inv = sp.inv.cpu().numpy()[:n]
+    inv_ref = np.full(n, -1, np.int32)
+    inv_ref[order_ref] = np.arange(kept, dtype=np.int32)
+    assert np.array_equal(inv, inv_ref)
+    # tile list: every expert's rows are covered by ceil(count / 128) tiles in order
+    nt = int(sp.num_tiles)
+    te, tr = sp.tile_expert.cpu().numpy()[:nt], sp.tile_row0.cpu().numpy()[:nt]
+    exp_te, exp_tr = [], []
+    for e in range(E):
+        for r in range(off_ref[e], off_ref[e + 1], 128):
+            exp_te.append(e), exp_tr.append(r)
+    assert nt == len(exp_te) <= sp.max_tiles
+    assert np.array_equal(te, np.array(exp_te, np.int32)) and np.array_equal(tr, np.array(exp_tr, np.int32))
+
+
+@pytest.mark.parametrize("R", (8, 63, 64, 300))
+@pytest.mark.parametrize("bits", (2, 4, 6))
+def test_gather_qmm_both_paths(bits, R):
+    """Below and above the sort threshold (the reference's ops_selftest sweeps T across it)."""
+    E, N, K = 8, 96, 256
+    bank, (pk, s, b, _, gs) = make_bank(E, N, K, bits, 64, seed=bits)
+    rng = np.random.default_rng(R)
+    x = torch.from_numpy(rng.standard_normal((R, K)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    rhs = torch.from_numpy(rng.integers(0, E, R).astype(np.int32)).to(DEV)
+    y = jq.gather_qmm(x, bank, rhs_indices=rhs)
+    ref = jo.gather_qmm(x.float().cpu().numpy(), pk, s, b, rhs.cpu().numpy(), bits, gs)
+    assert (R >= SORT_THRESHOLD) == (R >= 64)
+    close(y.float().cpu().numpy(), ref)
+    # the MLX call shape: stacked tensors + lhs_indices
+    lhs = torch.from_numpy(rng.integers(0, R, R).astype(np.int32)).to(DEV)
+    y2 = jq.gather_qmm(x, bank.weight, bank.scales, bank.biases, rhs_indices=rhs, lhs_indices=lhs, group_size=64,
+                       bits=bits)
+    ref2 = jo.gather_qmm(x.float().cpu().numpy(), pk, s, b, rhs.cpu().numpy(), bits, gs, lhs.cpu().numpy())
+    close(y2.float().cpu().numpy(), ref2)
+
+
+def test_gather_qmm_sorted_flag_needs_lhs():
+    bank, _ = make_bank(2, 16, 64, 4, 64, seed=0)
+    x = torch.zeros((4, 64), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        jq.gather_qmm(x, bank, rhs_indices=torch.zeros(4, dtype=torch.int32, device=DEV), sorted_indices=True)
+
+
+@pytest.mark.parametrize("T", (1, 7, 8, 64, 300))
+def test_moe_layer_vs_oracle(T):
+    """E=16 experts, top-4, H=256, I=128: decode path (T*k < 64) and sorted tensor-core path."""
+    E, k, H, I = 16, 4, 256, 128
+    gate, qg = make_bank(E, I, H, 2, 64, seed=1)
+    up, qu = make_bank(E, I, H, 2, 64, seed=2)
+    down, qd = make_bank(E, H, I, 3, 64, seed=3)
+    rng = np.random.default_rng(T)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    logits = torch.from_numpy(rng.standard_normal((T, E)).astype(np.float32)).to(DEV)
+    idx, w = jq.route_softmax_topk(logits, k)
+    idx_ref, w_ref = jo.route_softmax_topk(logits.cpu().numpy(), k)
+    assert np.array_equal(idx.cpu().numpy(), idx_ref)
+    assert np.allclose(w.cpu().numpy(), w_ref, rtol=1e-5, atol=1e-7)
+    out = jq.moe_layer(x, idx, w, gate, up, down)
+    ref = jo.moe_layer(x.float().cpu().numpy(), idx_ref, w.cpu().numpy(), qg, qu, qd, act_dtype="bf16")
+    close(out.float().cpu().numpy(), ref)
+    # clamp variant (dsv41 swiglu_limit)
+    out2 = jq.moe_layer(x, idx, w, gate, up, down, swiglu_limit=0.5)
+    ref2 = jo.moe_layer(x.float().cpu().numpy(), idx_ref, w.cpu().numpy(), qg, qu, qd, swiglu_limit=0.5, act_dtype="bf16")
+    close(out2.float().cpu().numpy(), ref2)
+
+
+def test_moe_layer_zero_token_experts_and_skew():
+    """All tokens routed to two experts: the other experts get no tile; one expert gets several."""
+    E, k, H, I, T = 8, 2, 128, 64, 400
+    gate, qg = make_bank(E, I, H, 4, 64, seed=11)
+    up, qu = make_bank(E, I, H, 4, 64, seed=12)
+    down, qd = make_bank(E, H, I, 4, 64, seed=13)
+    rng = np.random.default_rng(0)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    idx = torch.tensor([[5, 2]] * T, dtype=torch.int32, device=DEV)
+    w = torch.from_numpy(rng.random((T, k)).astype(np.float32)).to(DEV)
+    out = jq.moe_layer(x, idx, w, gate, up, down)
+    ref = jo.moe_layer(x.float().cpu().numpy(), idx.cpu().numpy(), w.cpu().numpy(), qg, qu, qd, act_dtype="bf16")
+    close(out.float().cpu().numpy(), ref)
+
+
+def test_moe_mixed_bit_widths_per_expert():
+    """Each expert with its own width (2/3/4/6/8): one launch per distinct width."""
+    E, k, H, I, T = 5, 2, 128, 64, 96
+    widths = (2, 3, 4, 6, 8)
+    rng = np.random.default_rng(9)
+
+    def mixed(N, K, seed):
+        experts, ref = [], []
+        for e in range(E):
+            w = torch.from_numpy((np.random.default_rng(seed + e).standard_normal((N, K)) * 0.05).astype(np.float32))
+            wq, s, b = jq.quantize(w.to(DEV).to(torch.bfloat16), 64, widths[e])
+            experts.append((wq, s, b, widths[e]))
+            ref.append(jo.dequantize_affine(wq.cpu().numpy().view(np.uint32), s.float().cpu().numpy(),
+                                            b.float().cpu().numpy(), widths[e], 64))
+        return jq.ExpertBank.from_experts(experts), np.stack(ref)
+
+    gate, Wg = mixed(I, H, 100)
+    up, Wu = mixed(I, H, 200)
+    down, Wd = mixed(H, I, 300)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    idx = torch.from_numpy(rng.integers(0, E, (T, k)).astype(np.int32)).to(DEV)
+    w = torch.from_numpy(rng.random((T, k)).astype(np.float32)).to(DEV)
+    for sl in (slice(0, T), slice(0, 5)):          # sorted path and decode path
+        out = jq.moe_layer(x[sl], idx[sl], w[sl], gate, up, down).float().cpu().numpy()
+        xn, idn, wn = x[sl].float().cpu().numpy(), idx[sl].cpu().numpy(), w[sl].cpu().numpy()
+        ref = np.zeros_like(out)
+        for t in range(xn.shape[0]):
+            for j in range(k):
+                e = int(idn[t, j])
+                g = jo.round_to(xn[t] @ Wg[e].T, "bf16")
+                u = jo.round_to(xn[t] @ Wu[e].T, "bf16")
+                h = jo.round_to((g / (1 + np.exp(-g))) * u * wn[t, j], "bf16")
+                ref[t] += jo.round_to(h @ Wd[e].T, "bf16")
+        close(out, ref)
+
+
+def test_moe_expert_parallel_shards_sum_to_full():
+    """Experts split over 4 'ranks' (expert_base): the partial outputs add up to the full layer."""
+    E, k, H, I = 16, 4, 128, 64
+    gate, _ = make_bank(E, I, H, 2, 64, seed=21)
+    up, _ = make_bank(E, I, H, 2, 64, seed=22)
+    down, _ = make_bank(E, H, I, 2, 64, seed=23)
+    rng = np.random.default_rng(3)
+    for T in (3, 200):
+        x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+        idx, w = jq.route_softmax_topk(torch.from_numpy(rng.standard_normal((T, E)).astype(np.float32)).to(DEV), k)
+        full = jq.moe_layer(x, idx, w, gate, up, down, out_f32=True)
+        parts = sum(jq.moe_layer(x, idx, w, gate.slice(e0, e0 + 4), up.slice(e0, e0 + 4), down.slice(e0, e0 + 4),
+                                 expert_base=e0, out_f32=True) for e0 in range(0, E, 4))
+        assert float((full - parts).abs().max()) <= 1e-5 * float(full.abs().max()) + 1e-6
+
+
+def test_device_status_clean_after_moe():
+    torch.cuda.synchronize()
+    assert _lib.load().jq_device_status() == 0
