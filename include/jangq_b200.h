@@ -163,6 +163,25 @@ int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t l
                 int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y_sorted,
                 int64_t ldy, jq_stream_t stream);
 
+/* jq_moe_gemm without any workspace.  No counterpart in the reference (MLX allocates inside
+ * gather_qmm); it exists for callers that must not allocate device memory on the request path:
+ * a serving process that gave its whole device budget to weight and KV-cache arenas at start-up
+ * (a late allocation there can fail, fragment the pool, or stall the device), or a host runtime
+ * that calls this library as a plug-in and does not lend its allocator to plug-ins.
+ * The tile list that jq_moe_gemm reads from caller buffers is rebuilt here from expert_offsets
+ * into a fixed array inside the library (about 12 KB per device, held until the process exits).
+ * Limits: num_experts <= 1024 and max_rows <= 65536, otherwise JQ_EUNSUPPORTED.
+ * The first call on a device looks the array's device address up; make that call during
+ * start-up, before any stream capture.  All calls share the one array and every call rewrites
+ * it, so two calls whose kernels may overlap on the GPU (different streams) race: serialise them.
+ * Same inputs and outputs as jq_moe_gemm otherwise; it calls no cudaMalloc/cudaFree. */
+int jq_moe_gemm_static(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx,
+                       const int32_t* expert_offsets, int num_experts,
+                       const uint32_t* const* codes_tab, const void* const* scales_tab,
+                       const void* const* biases_tab, const int32_t* bits_tab, int sidecar_dtype,
+                       int64_t N, int64_t K, int bits, int group_size, void* y_sorted, int64_t ldy,
+                       jq_stream_t stream);
+
 /* h = silu(min(g, limit)) * clip(u, +-limit) * weights[pair] (dsv41/model.py:1216-1226; limit <= 0:
  * no clamp; weights NULL: 1).  pair = order[p] when order != NULL else p; rows p < *count when
  * count != NULL else p < max_rows. */

@@ -470,9 +470,87 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     return fail(JQ_EUNSUPPORTED, "bits=%d", bits);
 }
 
+// ---- allocation-free grouped GEMM ------------------------------------------------------------------
+// The grouped GEMM walks a tile list (expert id and first row of every 128-row tile, plus their
+// count).  jq_moe_gemm gets that list from buffers the caller allocated for jq_moe_sort; the variant
+// below rebuilds it from expert_offsets into this fixed array instead, so the call needs no
+// workspace at all.  Every device that loads the library holds the array (about 12 KB) until exit.
+constexpr int STATIC_MAX_EXPERTS = 1024;
+constexpr int64_t STATIC_MAX_ROWS = 65536;
+constexpr int STATIC_MAX_TILES = (int)(STATIC_MAX_ROWS / GEMM_BM) + STATIC_MAX_EXPERTS;
+constexpr int STATIC_HDR = 64;     // word 0 = number of tiles; the lists start 256 bytes in
+static __device__ __align__(256) int32_t g_static_tiles[STATIC_HDR + 2 * STATIC_MAX_TILES];
+
+// One thread rewrites the whole list on every call (count first reset, then the tiles), so nothing
+// of an earlier call survives into this one.
+__global__ void build_tiles_kernel(const int32_t* __restrict__ offsets, int E, int tile_m, int32_t* __restrict__ out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int32_t* tile_expert = out + STATIC_HDR;
+    int32_t* tile_row0 = out + STATIC_HDR + STATIC_MAX_TILES;
+    int tiles = 0;
+    out[0] = 0;
+    for (int e = 0; e < E; ++e) {
+        const int lo = offsets[e], hi = offsets[e + 1];
+        for (int r = lo; r < hi && tiles < STATIC_MAX_TILES; r += tile_m) {
+            tile_expert[tiles] = e;
+            tile_row0[tiles] = r;
+            ++tiles;
+        }
+    }
+    out[0] = tiles;
+}
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// host-side handle, never a device address, so it is resolved with cudaGetSymbolAddress once per
+// device (with that device current) and the pointer is what the kernels receive.
+static int static_tiles_ptr(int32_t** out) {
+    static int32_t* cached[64] = {};
+    int dev = 0;
+    JQ_CUDA_OK(cudaGetDevice(&dev));
+    JQ_REQUIRE(dev >= 0 && dev < 64, JQ_EUNSUPPORTED, "device ordinal %d out of range", dev);
+    if (!cached[dev]) {
+        int32_t* p = nullptr;
+        JQ_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_static_tiles));
+        JQ_REQUIRE(p != nullptr, JQ_ECUDA, "cudaGetSymbolAddress returned a null address");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return JQ_OK;
+}
+
 }  // namespace jq
 
 extern "C" {
+
+int jq_moe_gemm_static(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx,
+                       const int32_t* expert_offsets, int num_experts, const uint32_t* const* codes_tab,
+                       const void* const* scales_tab, const void* const* biases_tab, const int32_t* bits_tab,
+                       int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y_sorted, int64_t ldy,
+                       jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(expert_offsets && codes_tab && scales_tab && biases_tab, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(num_experts > 0 && num_experts <= STATIC_MAX_EXPERTS, JQ_EUNSUPPORTED,
+               "jq_moe_gemm_static holds tile lists for at most %d experts, got %d", STATIC_MAX_EXPERTS, num_experts);
+    JQ_REQUIRE(max_rows >= 0 && max_rows <= STATIC_MAX_ROWS, JQ_EUNSUPPORTED,
+               "jq_moe_gemm_static holds tile lists for at most %lld rows, got %lld", (long long)STATIC_MAX_ROWS,
+               (long long)max_rows);
+    if (max_rows == 0 || N == 0) return JQ_OK;
+    int32_t* tiles = nullptr;
+    int rc = static_tiles_ptr(&tiles);
+    if (rc != JQ_OK) return rc;
+    build_tiles_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(expert_offsets, num_experts, GEMM_BM, tiles);
+    rc = check_launch("build_tiles");
+    if (rc != JQ_OK) return rc;
+    GroupedArgs g;
+    g.tile_expert = tiles + STATIC_HDR;
+    g.tile_row0 = tiles + STATIC_HDR + STATIC_MAX_TILES;
+    g.num_tiles = tiles;
+    g.expert_offsets = expert_offsets;
+    g.bits_tab = bits_tab; g.codes_tab = codes_tab; g.scales_tab = scales_tab; g.biases_tab = biases_tab;
+    g.max_tiles = max_rows / GEMM_BM + num_experts;
+    return qgemm_dispatch(x_sorted, act_dtype, max_rows, ldx, nullptr, nullptr, nullptr, sidecar_dtype, N, K, bits,
+                          group_size, y_sorted, act_dtype, ldy, &g, (cudaStream_t)stream);
+}
 
 int jq_qgemm(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
              const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
