@@ -265,10 +265,8 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
             _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), None, None,
                                          h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
             y = _gather_qgemv(h, 1, local, down)
-            # pairs of other ranks' experts were skipped by the kernels: mask them in the combine
-            inv = torch.where((local >= 0) & (local < gate.E), torch.arange(P, device=dev, dtype=torch.int32),
-                              torch.full((P,), -1, device=dev, dtype=torch.int32))
-            inv_ptr = inv.data_ptr()
+            # pairs of other ranks' experts were skipped by the kernels and their rows stay zero
+            inv_ptr = None
         need_f32 = out_f32 or shared is not None
         acc = torch.empty((T, H), dtype=torch.float32, device=dev) if need_f32 else None
         out = None if need_f32 else torch.empty((T, H), dtype=x.dtype, device=dev)
