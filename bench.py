@@ -272,6 +272,10 @@ def run_cuda(args):
     e2e_ms = float(t.item())
     e2e = world * bytes_step * K / (e2e_ms * 1e-3) / 1e9
 
+    moe_res = None
+    if not args.no_moe:
+        moe_res = run_moe(args, device, world, rank, barrier)
+
     jq._lib.check(jq._lib.load().jq_device_status())
 
     if rank == 0:
@@ -298,11 +302,77 @@ def run_cuda(args):
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": plan.h2d_bytes,
                         "d2h_bytes_per_step": plan.d2h_bytes, "ms_per_step": e2e_ms / K},
                 "gpu_launches": plan.launches_per_run * K, "clocks": clk.summary()}
+        if moe_res is not None:
+            line["moe_decode"] = moe_res
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_moe(args, device, world, rank, barrier):
+    """BASELINE config 3, batch-1 decode per GPU through the quantized hot path (attention
+    projections 6-bit, router, top-8 of 128 experts 2-bit), experts sharded over the ranks;
+    aggregate tokens/s = world tokens per step / step time (weak scaling: one token per GPU)."""
+    import torch
+    import torch.distributed as dist
+    from jangq_b200.stacks import MoEDecodeStack
+    stack = MoEDecodeStack(device=device, rank=rank, world=world)
+    g = torch.Generator(device=device)
+    g.manual_seed(11 + rank)
+    x = torch.randn((1, stack.H), generator=g, device=device).to(torch.bfloat16)
+    out = stack.step(x)                                   # eager warm-up (sets function attributes)
+    torch.cuda.synchronize()
+    graph = None
+    try:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            stack.step(x)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            out = stack.step(x)
+        graph = gr
+    except Exception as e:                                # capture of the collectives not available: run eagerly
+        if rank == 0:
+            print(f"# MoE step not captured ({type(e).__name__}: {e}); timing eager launches", file=sys.stderr)
+        torch.cuda.synchronize()
+
+    def one():
+        if graph is not None:
+            graph.replay()
+        else:
+            stack.step(x)
+
+    W, K = max(args.warmup, 3), args.steps
+    for _ in range(W):
+        one()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        one()
+    ev1.record()
+    barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / K
+    finite = bool(torch.isfinite(out.float()).all())
+    peak = 6464.6
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        pass
+    gbs = stack.bytes_per_token / (ms * 1e-3) / 1e9
+    return {"tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
+            "per_gpu_GBps": gbs, "hbm_frac": gbs / peak, "graph": graph is not None, "finite": finite,
+            "workload": "config3 MoE stack, batch-1 decode per GPU: 48 layers x [q,k,v,o @6b + bf16 router + top-8 of "
+                        "128 experts (768x2048 gate/up, 2048x768 down) @2b], group 64; experts sharded E/N per GPU, "
+                        "tokens all-gathered and partial sums reduce-scattered (NCCL) per layer; attention core not run"}
 
 
 def main():
@@ -312,6 +382,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-moe", action="store_true", help="skip the config-3 MoE decode measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

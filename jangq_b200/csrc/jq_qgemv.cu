@@ -52,7 +52,6 @@ struct GemvArgs {
     int x_div, num_experts;
 };
 
-constexpr int GEMV_WARPS = 4;
 constexpr int GEMV_MAX_NBUF = 3;
 
 __host__ __device__ inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -75,14 +74,13 @@ template <int BITS, int GS, int MT> struct GemvGeom {
     __host__ __device__ static constexpr int stage_bytes(int M) { return X_OFF + M * XS * 2; }
 };
 
-template <typename AT, int BITS, int GS, int MT>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+template <typename AT, int BITS, int GS, int MT, int NW>
+__global__ void __launch_bounds__(NW * 32)
 qgemv_mma_kernel(const GemvArgs a) {
     using A = Act<AT>;
     using F = Fields<AT, BITS>;
     using Geo = GemvGeom<BITS, GS, MT>;
-    constexpr int NW = GEMV_WARPS;
-    static_assert(NW == 4, "the final reduction maps the 4 warps onto the 4 accumulator slots");
+    static_assert(NW == 4 || NW == 8, "4 or 8 warps split K");
     constexpr int BPG = GS / 64;            // 64-code k-blocks per quantization group
     constexpr int UW = Unit<BITS>::WORDS;
     constexpr int ROWS = Geo::ROWS, KT = Geo::KT, RS = Geo::RS, XS = Geo::XS, NG = Geo::NG, NQ = Geo::NQ,
@@ -269,6 +267,7 @@ qgemv_mma_kernel(const GemvArgs a) {
         const float2* pt = reinterpret_cast<const float2*>(buf + Geo::SC_OFF) + g * NGP;
         const float* xsum = Xs + 2 * tig;
         float cg[MT][F::PASSES][4];
+#pragma unroll 2
         for (int blk = 0; blk < nblk; ++blk) {
             uint32_t xr[8];
             {
@@ -341,8 +340,8 @@ qgemv_mma_kernel(const GemvArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) red[((warp * MT + mt) * 4 + i) * 32 + lane] = acc[mt][i];
     __syncthreads();
-    {
-        const int i = threadIdx.x >> 5;    // 4 warps <-> the 4 accumulator slots
+    if (warp < 4) {
+        const int i = warp;                // warps 0..3 <-> the 4 accumulator slots
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             float v = 0.f;
@@ -449,26 +448,26 @@ static bool force_simple() {
     return e && e[0] == '1';
 }
 
-template <typename AT, int BITS, int GS, int MT>
-static int launch_mma_mt(GemvArgs a, int pairs, cudaStream_t st, bool* launched) {
+template <typename AT, int BITS, int GS, int MT, int NW>
+static int launch_mma_cfg(GemvArgs a, int pairs, int nbuf, cudaStream_t st, bool* launched) {
     using Geo = GemvGeom<BITS, GS, MT>;
     *launched = false;
     const int sb = Geo::stage_bytes(a.M);
-    a.nbuf = (GEMV_WARPS * 3 * sb <= 72 * 1024) ? 3 : 2;
-    const size_t smem = (size_t)GEMV_WARPS * a.nbuf * sb;
+    a.nbuf = nbuf;
+    const size_t smem = (size_t)NW * a.nbuf * sb;
     if (smem > 200 * 1024) return JQ_OK;   // does not fit: general kernel
     static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_mma_kernel<AT, BITS, GS, MT>,
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_mma_kernel<AT, BITS, GS, MT, NW>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     const unsigned grid = (unsigned)((a.N + 16 * MT - 1) / (16 * MT));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, (unsigned)pairs);
-    cfg.blockDim = dim3(GEMV_WARPS * 32);
+    cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -476,17 +475,44 @@ static int launch_mma_mt(GemvArgs a, int pairs, cudaStream_t st, bool* launched)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_mma_kernel<AT, BITS, GS, MT>, a));
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_mma_kernel<AT, BITS, GS, MT, NW>, a));
     *launched = true;
     return JQ_OK;
 }
 
+// Shape heuristics.  The kernel is latency-bound per warp, so what matters is how many warps
+// the grid puts on every SM and how many stages each of them walks in sequence:
+//   * 32-row tiles (MT=2) halve the per-weight cost of the activation operand; they pay off for
+//     medium grids (4 to 12 sixteen-row tiles per SM);
+//   * a small grid (at most ~2 tiles per SM) with long rows splits K over 8 warps instead of 4;
+//   * two pipeline stages keep shared memory small (more resident CTAs); a third one only pays when
+//     each warp walks many stages in sequence (8 warps, very long rows).
+// The thresholds come from a sweep over the decode shapes of the BASELINE configurations.
 template <typename AT, int BITS, int GS>
 static int launch_mma(const GemvArgs& a, int pairs, cudaStream_t st, bool* launched) {
-    // 32-row tiles halve the per-weight cost of the activation operand; use them once
-    // they still give every SM at least two CTAs
-    if (a.N * pairs >= (int64_t)32 * 2 * sm_count()) return launch_mma_mt<AT, BITS, GS, 2>(a, pairs, st, launched);
-    return launch_mma_mt<AT, BITS, GS, 1>(a, pairs, st, launched);
+    const int sms = sm_count();
+    const int64_t tiles16 = (a.N + 15) / 16 * pairs;
+    constexpr int KT = GemvGeom<BITS, GS, 1>::KT;
+    const int nst = (int)((a.K + KT - 1) / KT);
+    int mt = (tiles16 >= (int64_t)4 * sms && tiles16 < (int64_t)12 * sms) ? 2 : 1;
+    int nw = (mt == 1 && tiles16 <= (int64_t)2 * sms && nst >= 16) ? 8 : 4;
+    if (const char* e = getenv("JANGQ_GEMV_MT")) {            // tuning knobs for experiments
+        if (e[0] == '1') mt = 1;
+        if (e[0] == '2') mt = 2;
+    }
+    if (const char* e = getenv("JANGQ_GEMV_NW")) {
+        if (e[0] == '4') nw = 4;
+        if (e[0] == '8') nw = 8;
+    }
+    if (mt == 2) nw = 4;
+    const int sb = mt == 2 ? GemvGeom<BITS, GS, 2>::stage_bytes(a.M) : GemvGeom<BITS, GS, 1>::stage_bytes(a.M);
+    int nbuf = (nw == 8 && nst >= 20 && nw * 3 * sb <= 200 * 1024) ? 3 : 2;
+    if (const char* e = getenv("JANGQ_GEMV_NBUF")) {
+        if (e[0] == '2' || e[0] == '3') nbuf = e[0] - '0';
+    }
+    if (mt == 2) return launch_mma_cfg<AT, BITS, GS, 2, 4>(a, pairs, nbuf, st, launched);
+    if (nw == 8) return launch_mma_cfg<AT, BITS, GS, 1, 8>(a, pairs, nbuf, st, launched);
+    return launch_mma_cfg<AT, BITS, GS, 1, 4>(a, pairs, nbuf, st, launched);
 }
 
 int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,

@@ -30,6 +30,14 @@ class JANGLinear(nn.Module):
         self.register_buffer("biases", torch.zeros((out_features, in_features // group_size), dtype=dtype,
                                                    device=device))
         self.register_buffer("bias", torch.zeros((out_features,), dtype=dtype, device=device) if bias else None)
+        # set by freeze(): the weights will not be written any more, so decode launches may overlap
+        # their predecessor on the stream (JQ_GEMV_STATIC_WEIGHTS)
+        self.static_weights = False
+
+    def freeze(self):
+        """Declare the quantized weights final (call after loading, with the device idle)."""
+        self.static_weights = True
+        return self
 
     @classmethod
     def from_float(cls, w: torch.Tensor, bits: int = 4, group_size: int = 64, bias: torch.Tensor | None = None):
@@ -45,7 +53,7 @@ class JANGLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = ops.quantized_matmul(x, self.weight, self.scales, self.biases, transpose=True,
-                                 group_size=self.group_size, bits=self.bits)
+                                 group_size=self.group_size, bits=self.bits, static_weights=self.static_weights)
         return y if self.bias is None else y + self.bias
 
     def extra_repr(self) -> str:

@@ -116,12 +116,14 @@ def _qgemv(x2: torch.Tensor, wq, scales, biases, K, bits, group_size, out: torch
 
 
 def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
-                     transpose: bool = True, group_size: int = 64, bits: int = 4) -> torch.Tensor:
+                     transpose: bool = True, group_size: int = 64, bits: int = 4,
+                     static_weights: bool = False) -> torch.Tensor:
     """y[.., N] = x[.., K] . deq(w)[N, K]^T with float32 accumulation, output in x's dtype.
 
     Few rows (decode) run the bandwidth-bound mat-vec kernel; many rows (prefill)
     run the tensor-core GEMM.  Only transpose=True (weights stored [N, K], the only
-    form the reference uses) is provided.
+    form the reference uses) is provided.  static_weights=True promises that w/scales/biases are
+    not written by earlier work on the stream, which lets the decode kernel overlap its predecessor.
     """
     if not transpose:
         raise JangqError(_lib.JQ_EUNSUPPORTED, "quantized_matmul: only transpose=True is provided")
@@ -144,7 +146,8 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, bia
     with torch.cuda.device(dev):
         if M <= _lib.QGEMV_MAX_M:
             if M > 0:
-                _qgemv(x2, w, scales, biases, K, bits, group_size, out)
+                _qgemv(x2, w, scales, biases, K, bits, group_size, out,
+                       _lib.JQ_GEMV_STATIC_WEIGHTS if static_weights else 0)
         else:
             from .gemm import qgemm
             qgemm(x2, w, scales, biases, K, bits, group_size, out)

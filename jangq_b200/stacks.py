@@ -1,0 +1,88 @@
+"""Synthetic random-init weight stacks with the shapes of the BASELINE configurations, for
+benchmarks and smoke tests.  Only the quantized hot path is modelled: attention's softmax(QK)V,
+norms, RoPE and sampling are outside it, so the attention block is its four projections with the
+query projection's output standing in for the attention result.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import moe, moe_ep
+from .linear import JANGLinear
+
+
+def _rand_linear(out_f, in_f, bits, gs, device, seed):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = (torch.randn((out_f, in_f), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    return JANGLinear.from_float(w, bits=bits, group_size=gs)
+
+
+def _rand_bank(E, out_f, in_f, bits, gs, device, seed):
+    from .ops import quantize
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = (torch.randn((E, out_f, in_f), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    wq, s, b = quantize(w, gs, bits)
+    return moe.ExpertBank(wq, s, b, bits, gs)
+
+
+class MoEDecodeStack:
+    """BASELINE config 3 (default arguments): 48 layers, hidden 2048, 32 query / 4 KV heads of 128,
+    128 experts of SwiGLU intermediate 768, top-8 softmax routing, experts 2-bit, attention 6-bit,
+    group 64.  With world > 1 the experts are sharded E/world per rank (expert parallelism); the
+    attention projections and the router are replicated."""
+
+    def __init__(self, layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, inter=768, topk=8,
+                 expert_bits=2, attn_bits=6, gs=64, device="cuda", rank=0, world=1, seed=0, group=None):
+        self.L, self.H, self.E, self.I, self.k = layers, hidden, experts, inter, topk
+        self.world, self.rank, self.group = world, rank, group
+        self.e_local = experts // world
+        self.base = rank * self.e_local
+        dq, dkv = q_heads * head_dim, kv_heads * head_dim
+        self.layers = []
+        for l in range(layers):
+            s0 = seed + 1000 * l
+            lay = {
+                "q": _rand_linear(dq, hidden, attn_bits, gs, device, s0 + 1),
+                "k": _rand_linear(dkv, hidden, attn_bits, gs, device, s0 + 2),
+                "v": _rand_linear(dkv, hidden, attn_bits, gs, device, s0 + 3),
+                "o": _rand_linear(hidden, dq, attn_bits, gs, device, s0 + 4),
+                "router": (torch.randn((experts, hidden), device=device,
+                                       generator=torch.Generator(device=device).manual_seed(s0 + 5)) * 0.02).to(torch.bfloat16),
+                "gate": _rand_bank(self.e_local, inter, hidden, expert_bits, gs, device, s0 + 10 + rank),
+                "up": _rand_bank(self.e_local, inter, hidden, expert_bits, gs, device, s0 + 30 + rank),
+                "down": _rand_bank(self.e_local, hidden, inter, expert_bits, gs, device, s0 + 50 + rank),
+            }
+            self.layers.append(lay)
+        torch.cuda.synchronize(device)
+        for lay in self.layers:
+            for n in "qkvo":
+                lay[n].freeze()
+        e = 2
+        attn = sum(moe_bytes(lin) for lin in (self.layers[0][n] for n in "qkvo"))
+        per_expert = 3 * (inter * hidden * expert_bits // 8 + (inter * hidden // gs) * 2 * e)
+        self.bytes_per_token = layers * (attn + topk * per_expert + experts * hidden * 2)
+
+    def step(self, x: torch.Tensor) -> torch.Tensor:
+        """One token per row of x ([T, H] bf16) through every layer's quantized matmuls."""
+        for lay in self.layers:
+            q = lay["q"](x)
+            lay["k"](x)
+            lay["v"](x)
+            x = torch.nn.functional.rms_norm(x + lay["o"](q), (self.H,))
+            logits = torch.matmul(x, lay["router"].t()).float()
+            idx, w = moe.route_softmax_topk(logits, self.k)
+            if self.world == 1:
+                y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True)
+            else:
+                y = moe_ep.gathered_tokens(x, idx, w, moe_ep.partial_experts_fn(lay["gate"], lay["up"], lay["down"],
+                                                                                self.base), group=self.group)
+            x = torch.nn.functional.rms_norm(x + y.to(x.dtype), (self.H,))
+        return x
+
+
+def moe_bytes(lin: JANGLinear) -> int:
+    n, k = lin.out_features, lin.in_features
+    return n * k * lin.bits // 8 + n * (k // lin.group_size) * 2 * lin.scales.element_size()
