@@ -30,8 +30,8 @@ namespace jq {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_SA = 4;     // activation stages
-constexpr int GEMM_SB = 3;     // dequantized-weight stages
+constexpr int GEMM_SA = 3;     // activation stages
+constexpr int GEMM_SB = 2;     // dequantized-weight stages
 
 struct GemmArgs {
     const uint32_t* codes;
@@ -193,21 +193,30 @@ __device__ __forceinline__ uint4 dequant_chunk(const uint32_t (&u)[2 * BITS], ui
                       dequant_pair<AT, BITS, 8 * C + 6>(u, sp2, b2, s, bias));
 }
 
-template <typename AT, int BITS, int BN>
-__global__ void __launch_bounds__(64 + BN)
+template <typename AT, int BITS, int BN, int DPR>
+__global__ void __launch_bounds__(64 + BN * DPR)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     using A = Act<AT>;
-    constexpr int NDW = BN / 32;                        // dequantizer warps
+    constexpr int NDW = BN / 32 * DPR;                  // dequantizer warps (DPR threads share a weight row)
+    constexpr int NDT = NDW * 32;
     constexpr int A_STAGE = GEMM_BM * GEMM_BK * 2;      // 16 KB
     constexpr int B_STAGE = BN * GEMM_BK * 2;
     constexpr int UW = 2 * BITS;                        // words of one row's 64 codes
+    // packed codes are staged through shared memory, CKB k-blocks at a time, so that the global
+    // reads are coalesced 16-byte chunks (8+ lanes per row) instead of one sector per thread
+    constexpr int CKB = BITS == 2 ? 8 : (BITS == 8 ? 2 : 4);
+    constexpr int RB = CKB * 8 * BITS;                  // bytes per row and code stage (96..192)
+    constexpr int RBP = RB + 16;                        // padded pitch: conflict-free row reads
+    constexpr int CPR = RB / 16;                        // 16-byte chunks per row
+    constexpr int C_STAGE = BN * RBP;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // the dynamic shared-memory base is only guaranteed 16-byte aligned: realign to 1024
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
     uint8_t* sB = smem + GEMM_SA * A_STAGE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + GEMM_SB * B_STAGE);
+    uint8_t* sC = sB + GEMM_SB * B_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sC + 2 * C_STAGE);
     uint64_t* xfull = bars;                  // [SA]
     uint64_t* xempty = bars + GEMM_SA;       // [SA]
     uint64_t* bfull = bars + 2 * GEMM_SA;    // [SB]
@@ -280,65 +289,189 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         }
     } else {
         // ---------------- dequantizers: one weight row per thread ----------------
-        const int r = (warp - 2) * 32 + lane;                 // row within the tile
+        const int dt = threadIdx.x - 64;                      // 0 .. NDT-1
+        const int r = dt % BN;                                // row within the tile
+        const int half = dt / BN;                             // DPR = 2: which 32 codes of the k-block (warp-uniform)
         const int64_t n = min(n0 + r, a.N - 1);               // rows past N are computed but never stored
-        const uint32_t* crow = codes_g + n * (a.K * BITS / 32);
+        const int64_t rowbytes = a.K * BITS / 8;
+        const uint8_t* cbytes = reinterpret_cast<const uint8_t*>(codes_g);
         const uint16_t* srow = reinterpret_cast<const uint16_t*>(scales_g) + n * a.G;
         const uint16_t* brow = reinterpret_cast<const uint16_t*>(biases_g) + n * a.G;
         const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
         const uint32_t sw = (uint32_t)(r & 7);
         const int gs = a.gs;
-        uint32_t cur[UW], nxt[UW];
-#pragma unroll
-        for (int i = 0; i < UW; ++i) cur[i] = __ldg(crow + i);
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int t = kb % GEMM_SB;
-            if (kb + 1 < nkb) {
-#pragma unroll
-                for (int i = 0; i < UW; ++i) nxt[i] = __ldg(crow + (kb + 1) * UW + i);
+        const int nstage = (nkb + CKB - 1) / CKB;
+
+        // all dequantizer threads copy code stage `st` together: consecutive lanes take consecutive
+        // 16-byte chunks of a row; always one commit so that group counting stays uniform
+        auto issue_codes = [&](int st, int buf) {
+            if (st < nstage) {
+                const int64_t off = (int64_t)st * RB;
+                const int rem = (int)min((int64_t)RB, rowbytes - off);
+                uint8_t* dstb = sC + buf * C_STAGE;
+                for (int c = dt; c < BN * CPR; c += NDT) {
+                    const int row = c / CPR, col = c - row * CPR;
+                    if (col * 16 < rem)
+                        cp_async16(dstb + row * RBP + col * 16,
+                                   cbytes + min(n0 + row, a.N - 1) * rowbytes + off + col * 16);
+                }
             }
-            // scale / bias of the (up to two) groups this k-block touches
-            const int k0 = kb * GEMM_BK;
-            const int g0 = k0 / gs, g1 = (k0 + 32) / gs;
-            const uint16_t s0h = __ldg(srow + g0), b0h = __ldg(brow + g0);
-            const uint16_t s1h = __ldg(srow + g1), b1h = __ldg(brow + g1);
-            constexpr int TGTC = (BITS <= A::MANT) ? A::MANT - BITS : 0;
-            constexpr float POST = 1.0f / (float)(1 << TGTC);
-            const float s0 = A::to_f32(s0h), s1 = A::to_f32(s1h), bias0 = A::to_f32(b0h), bias1 = A::to_f32(b1h);
-            // s * 2^-TGT is exact (power-of-two scaling) unless it underflows the 16-bit type
-            const uint32_t sp0 = A::pack_hi(s0 * POST, s0 * POST), sp1 = A::pack_hi(s1 * POST, s1 * POST);
-            const uint32_t bb0 = (uint32_t)b0h * 0x00010001u, bb1 = (uint32_t)b1h * 0x00010001u;
-            if (kb >= GEMM_SB) {
-                // warp-uniform outcome, so that no lane is left behind at the __syncwarp below
-                ok = __all_sync(0xFFFFFFFFu, mbar_wait(bempty + t, (uint32_t)((kb / GEMM_SB) - 1) & 1u, 1u << 18));
-                if (!ok) break;
+            cp_async_commit();
+        };
+
+        // Scales and biases: one vector load per code stage (CKB consecutive groups of this row) when
+        // the row is suitably aligned and groups are 64 or 128 wide; otherwise scalar loads per k-block.
+        // Either way they are fetched one step ahead of their use.
+        constexpr int SCW = CKB / 2;                          // 32-bit words holding CKB 16-bit sidecars
+        const int gpk_shift = (gs == 128) ? 1 : 0;            // k-blocks per group: 1 (gs 64) or 2 (gs 128)
+        const bool sc_vec = (gs >= 64) && (a.G % (CKB >> gpk_shift) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(srow) | reinterpret_cast<uintptr_t>(brow)) % (2 * CKB) == 0) &&
+                            ((a.G * 2) % (2 * CKB) == 0);
+        uint32_t scw[SCW], bcw[SCW], scn[SCW], bcn[SCW];
+#pragma unroll
+        for (int i = 0; i < SCW; ++i) scw[i] = bcw[i] = scn[i] = bcn[i] = 0u;
+        auto load_sc_stage = [&](int st, uint32_t (&so)[SCW], uint32_t (&bo)[SCW]) {
+            // groups of stage st: first = st*CKB >> gpk_shift, count = CKB >> gpk_shift (a multiple of 2 words when vec)
+            const int gfirst = (st * CKB) >> gpk_shift;
+            const int cnt = CKB >> gpk_shift;
+            if (gfirst + cnt <= a.G) {
+                const uint32_t* sp = reinterpret_cast<const uint32_t*>(srow + gfirst);
+                const uint32_t* bp = reinterpret_cast<const uint32_t*>(brow + gfirst);
+                if (cnt == 8) {
+                    const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sp)), bv = __ldg(reinterpret_cast<const uint4*>(bp));
+                    so[0] = sv.x; if (SCW > 1) so[1 % SCW] = sv.y; if (SCW > 2) { so[2 % SCW] = sv.z; so[3 % SCW] = sv.w; }
+                    bo[0] = bv.x; if (SCW > 1) bo[1 % SCW] = bv.y; if (SCW > 2) { bo[2 % SCW] = bv.z; bo[3 % SCW] = bv.w; }
+                } else if (cnt == 4) {
+                    const uint2 sv = __ldg(reinterpret_cast<const uint2*>(sp)), bv = __ldg(reinterpret_cast<const uint2*>(bp));
+                    so[0] = sv.x; if (SCW > 1) so[1 % SCW] = sv.y;
+                    bo[0] = bv.x; if (SCW > 1) bo[1 % SCW] = bv.y;
+                } else if (cnt == 2) {
+                    so[0] = __ldg(sp); bo[0] = __ldg(bp);
+                } else {                                       // cnt == 1
+                    so[0] = __ldg(srow + gfirst); bo[0] = __ldg(brow + gfirst);
+                }
+            } else {                                           // ragged last stage: element loads
+#pragma unroll
+                for (int i = 0; i < CKB; ++i) {
+                    const int gi = gfirst + i;
+                    if (i < cnt && gi < a.G) {
+                        const uint32_t sv = __ldg(srow + gi), bv = __ldg(brow + gi);
+                        if (i & 1) { so[i / 2] |= sv << 16; bo[i / 2] |= bv << 16; }
+                        else { so[i / 2] = sv; bo[i / 2] = bv; }
+                    }
+                }
             }
-            uint8_t* dst = sB + t * B_STAGE + row_off;
+        };
+        uint16_t s0h = 0, b0h = 0, s1h = 0, b1h = 0, s0n = 0, b0n = 0, s1n = 0, b1n = 0;
+        if (sc_vec) {
+            load_sc_stage(0, scw, bcw);
+        } else {
+            s0h = __ldg(srow); b0h = __ldg(brow);
+            s1h = s0h; b1h = b0h;
+            if (gs == 32) { s1h = __ldg(srow + 1); b1h = __ldg(brow + 1); }
+        }
+        issue_codes(0, 0);
+        // After a timed-out wait the warp keeps walking the loops (copies and the named barrier
+        // only), so that no other dequantizer warp is left waiting at the barrier.
+        for (int st = 0; st < nstage; ++st) {
+            cp_async_wait<0>();
+            asm volatile("bar.sync 1, %0;" ::"n"(NDT) : "memory");  // stage st landed; stage st-1 fully consumed
+            issue_codes(st + 1, (st + 1) & 1);
+            if (sc_vec && st + 1 < nstage) load_sc_stage(st + 1, scn, bcn);
+            const uint8_t* crow = sC + (st & 1) * C_STAGE + r * RBP;
+#pragma unroll
+            for (int kbi = 0; kbi < CKB; ++kbi) {
+                const int kb = st * CKB + kbi;
+                if (kb >= nkb) break;
+                const int t = kb % GEMM_SB;
+                uint32_t cur[UW];
+                if constexpr (DPR == 1) {
+                    if constexpr ((8 * BITS) % 16 == 0) {
+                        const uint4* cp = reinterpret_cast<const uint4*>(crow + kbi * 8 * BITS);
+#pragma unroll
+                        for (int i = 0; i < UW / 4; ++i) {
+                            const uint4 v = cp[i];
+                            cur[4 * i] = v.x; cur[4 * i + 1] = v.y; cur[4 * i + 2] = v.z; cur[4 * i + 3] = v.w;
+                        }
+                    } else {
+                        const uint2* cp = reinterpret_cast<const uint2*>(crow + kbi * 8 * BITS);
+#pragma unroll
+                        for (int i = 0; i < UW / 2; ++i) {
+                            const uint2 v = cp[i];
+                            cur[2 * i] = v.x; cur[2 * i + 1] = v.y;
+                        }
+                    }
+                } else {
+                    // this thread's 32 codes are BITS whole words; the other half stays zero
+                    const uint32_t* cp = reinterpret_cast<const uint32_t*>(crow + kbi * 8 * BITS) + half * BITS;
+#pragma unroll
+                    for (int i = 0; i < UW; ++i) cur[i] = 0u;
+                    if (half == 0) {
+#pragma unroll
+                        for (int i = 0; i < BITS; ++i) cur[i] = cp[i];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < BITS; ++i) cur[BITS + i] = cp[i];
+                    }
+                }
+                if (sc_vec) {
+                    const int gi = kbi >> gpk_shift;                      // group within the stage (static after unrolling)
+                    const uint32_t swd = scw[gi / 2], bwd = bcw[gi / 2];
+                    s0h = (uint16_t)((gi & 1) ? (swd >> 16) : (swd & 0xFFFFu));
+                    b0h = (uint16_t)((gi & 1) ? (bwd >> 16) : (bwd & 0xFFFFu));
+                    s1h = s0h; b1h = b0h;
+                } else if (kb + 1 < nkb) {        // scalar path: sidecars of the next k-block
+                    const int k1 = (kb + 1) * GEMM_BK;
+                    const int g0 = k1 / gs;
+                    s0n = __ldg(srow + g0); b0n = __ldg(brow + g0);
+                    s1n = s0n; b1n = b0n;
+                    if (gs == 32) { s1n = __ldg(srow + g0 + 1); b1n = __ldg(brow + g0 + 1); }
+                }
+                constexpr int TGTC = (BITS <= A::MANT) ? A::MANT - BITS : 0;
+                constexpr float POST = 1.0f / (float)(1 << TGTC);
+                const float s0 = A::to_f32(s0h), s1 = A::to_f32(s1h), bias0 = A::to_f32(b0h), bias1 = A::to_f32(b1h);
+                // s * 2^-TGT is exact (power-of-two scaling) unless it underflows the 16-bit type
+                const uint32_t sp0 = A::pack_hi(s0 * POST, s0 * POST), sp1 = A::pack_hi(s1 * POST, s1 * POST);
+                const uint32_t bb0 = (uint32_t)b0h * 0x00010001u, bb1 = (uint32_t)b1h * 0x00010001u;
+                if (ok && kb >= GEMM_SB)   // warp-uniform outcome
+                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(bempty + t, (uint32_t)((kb / GEMM_SB) - 1) & 1u, 1u << 18));
+                if (ok) {
+                    uint8_t* dst = sB + t * B_STAGE + row_off;
 #define JQ_CHUNK(C, SP, BB, S, BI) \
     *reinterpret_cast<uint4*>(dst + (((uint32_t)(C) ^ sw) << 4)) = dequant_chunk<AT, BITS, C>(cur, SP, BB, S, BI);
-            JQ_CHUNK(0, sp0, bb0, s0, bias0) JQ_CHUNK(1, sp0, bb0, s0, bias0)
-            JQ_CHUNK(2, sp0, bb0, s0, bias0) JQ_CHUNK(3, sp0, bb0, s0, bias0)
-            JQ_CHUNK(4, sp1, bb1, s1, bias1) JQ_CHUNK(5, sp1, bb1, s1, bias1)
-            JQ_CHUNK(6, sp1, bb1, s1, bias1) JQ_CHUNK(7, sp1, bb1, s1, bias1)
+                    if (DPR == 1 || half == 0) {
+                        JQ_CHUNK(0, sp0, bb0, s0, bias0) JQ_CHUNK(1, sp0, bb0, s0, bias0)
+                        JQ_CHUNK(2, sp0, bb0, s0, bias0) JQ_CHUNK(3, sp0, bb0, s0, bias0)
+                    }
+                    if (DPR == 1 || half == 1) {
+                        JQ_CHUNK(4, sp1, bb1, s1, bias1) JQ_CHUNK(5, sp1, bb1, s1, bias1)
+                        JQ_CHUNK(6, sp1, bb1, s1, bias1) JQ_CHUNK(7, sp1, bb1, s1, bias1)
+                    }
 #undef JQ_CHUNK
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bfull + t);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bfull + t);
+                }
+                if (!sc_vec) { s0h = s0n; b0h = b0n; s1h = s1n; b1h = b1n; }
+            }
+            if (sc_vec) {
 #pragma unroll
-            for (int i = 0; i < UW; ++i) cur[i] = nxt[i];
+                for (int i = 0; i < SCW; ++i) { scw[i] = scn[i]; bcw[i] = bcn[i]; }
+            }
         }
+        cp_async_wait<0>();
 
         // ---------------- epilogue: TMEM -> registers -> Y ----------------
         if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(accfull, 0, 1u << 18));
         if (ok) {
             tc_fence_after();
             const int q = warp & 3;                               // TMEM lane quarter this warp may read
-            const int half = (warp - 2) / 4;                      // BN = 256: two warps per quarter split the columns
+            const int part = (warp - 2) / 4;                      // the NDW/4 warps of a quarter split the columns
             constexpr int COLS_PER_WARP = BN / (NDW / 4);
             const int64_t m = m0 + q * 32 + lane;
             uint16_t* yrow = reinterpret_cast<uint16_t*>(a.y) + m * a.ldy + n0;
 #pragma unroll 1
-            for (int c0 = half * COLS_PER_WARP; c0 < (half + 1) * COLS_PER_WARP; c0 += 32) {
+            for (int c0 = part * COLS_PER_WARP; c0 < (part + 1) * COLS_PER_WARP; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 if (m < m_end) {
@@ -388,19 +521,21 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-template <typename AT, int BITS, int BN>
+template <typename AT, int BITS, int BN, int DPR>
 static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, int64_t m_tiles, cudaStream_t st) {
-    constexpr size_t smem = 1024 + GEMM_SA * GEMM_BM * GEMM_BK * 2 + GEMM_SB * BN * GEMM_BK * 2 + 256;
+    constexpr int CKB = BITS == 2 ? 8 : (BITS == 8 ? 2 : 4);
+    constexpr size_t smem = 1024 + GEMM_SA * GEMM_BM * GEMM_BK * 2 + GEMM_SB * BN * GEMM_BK * 2 +
+                            2 * BN * (CKB * 8 * BITS + 16) + 256;
     static bool attr_done[64] = {};
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN, DPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)m_tiles);
-    qgemm_tc_kernel<AT, BITS, BN><<<grid, 64 + BN, smem, st>>>(xmap, a);
+    qgemm_tc_kernel<AT, BITS, BN, DPR><<<grid, 64 + BN * DPR, smem, st>>>(xmap, a);
     return check_launch("qgemm");
 }
 
@@ -427,6 +562,10 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     JQ_REQUIRE(sidecar_dtype == x_dtype && y_dtype == x_dtype, JQ_EUNSUPPORTED,
                "qgemm needs scales/biases and the output in the activation dtype");
     JQ_REQUIRE(K % GEMM_BK == 0, JQ_EUNSUPPORTED, "qgemm needs K to be a multiple of 64, got %lld", (long long)K);
+    JQ_REQUIRE((K * bits / 8) % 16 == 0, JQ_EUNSUPPORTED,
+               "qgemm needs packed rows of a multiple of 16 bytes (K %% 128 == 0 for odd widths), got K=%lld bits=%d",
+               (long long)K, bits);
+    JQ_REQUIRE(grp || aligned(codes, 16), JQ_EINVAL, "codes must be 16-byte aligned");
     JQ_REQUIRE(aligned(x, 16) && ldx % 8 == 0 && ldx >= K, JQ_EINVAL, "x must be 16-byte aligned with ldx %% 8 == 0");
     JQ_REQUIRE(ldy >= N, JQ_EINVAL, "ldy too small");
     JQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), JQ_EUNSUPPORTED, "dimension too large");
@@ -461,10 +600,15 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     const int64_t m_tiles = grp ? grp->max_tiles : (M + GEMM_BM - 1) / GEMM_BM;
     if (m_tiles == 0) return JQ_OK;
     JQ_REQUIRE(m_tiles < 65536, JQ_EUNSUPPORTED, "too many row tiles for one launch (%lld)", (long long)m_tiles);
+    // 256-wide tiles reuse every activation tile twice as often; narrow outputs keep 128
+    const bool wide = N >= 256 && !getenv("JANGQ_GEMM_BN128");
 #define JQ_GEMM_CASE(B)                                                                                  \
-    if (bits == B)                                                                                       \
-        return x_dtype == JQ_BF16 ? launch_gemm<__nv_bfloat16, B, 128>(xmap, a, m_tiles, st)                      \
-                                  : launch_gemm<__half, B, 128>(xmap, a, m_tiles, st);
+    if (bits == B) {                                                                                     \
+        if (x_dtype == JQ_BF16)                                                                          \
+            return wide ? launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st)                    \
+                        : launch_gemm<__nv_bfloat16, B, 128, 1>(xmap, a, m_tiles, st);                   \
+        return launch_gemm<__half, B, 128, 1>(xmap, a, m_tiles, st);                                     \
+    }
     JQ_GEMM_CASE(2) JQ_GEMM_CASE(3) JQ_GEMM_CASE(4) JQ_GEMM_CASE(5) JQ_GEMM_CASE(6) JQ_GEMM_CASE(8)
 #undef JQ_GEMM_CASE
     return fail(JQ_EUNSUPPORTED, "bits=%d", bits);

@@ -72,6 +72,28 @@ def bench_qgemv(N, K, bits, gs, M, iters, rotate_mb, dtype=torch.bfloat16, flags
             "GBps": alg / (ms * 1e-3) / 1e9, "bytes": alg, "copies": copies}
 
 
+def bench_qgemm(N, K, bits, gs, M, iters, dtype=torch.bfloat16):
+    """Prefill GEMM: TFLOP/s = 2*M*N*K / time (activations and weights stay L2/HBM resident as they fall)."""
+    from .gemm import qgemm
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    w = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(dtype)
+    wq, s, b = ops.quantize(w, gs, bits)
+    del w
+    x = torch.randn((M, K), generator=g, device=dev).to(dtype)
+    y = torch.empty((M, N), dtype=dtype, device=dev)
+    reps = 4
+
+    def fn():
+        for _ in range(reps):
+            qgemm(x, wq, s, b, K, bits, gs, y)
+
+    ms = _time_graph(fn, iters) / reps
+    return {"op": "qgemm", "M": M, "N": N, "K": K, "bits": bits, "gs": gs, "us": ms * 1e3,
+            "TFLOPs": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+
+
 def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="quantize"):
     dev = torch.device("cuda")
     per = N * K * 2
@@ -99,8 +121,8 @@ def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="q
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="qgemv", choices=("qgemv", "quantize", "dequantize"))
-    ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small"))
+    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "dequantize"))
+    ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small", "qgemm"))
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--bits", type=int, default=4)
@@ -112,6 +134,12 @@ def main():
     a = ap.parse_args()
     _lib.load()
     flags = _lib.JQ_GEMV_STATIC_WEIGHTS if a.pdl else 0
+    if a.sweep == "qgemm":
+        for N in (4096, 14336):
+            for bits in (2, 4, 8):
+                for M in (64, 512, 4096):
+                    print(json.dumps(bench_qgemm(N, 4096, bits, 64, M, a.iters)), flush=True)
+        return
     if a.sweep:
         Ks = (2048, 4096, 8192) if a.sweep == "qgemv" else (4096,)
         Ns = (4096, 14336, 28672) if a.sweep == "qgemv" else (4096, 14336)
@@ -124,6 +152,8 @@ def main():
         return
     if a.op == "qgemv":
         print(json.dumps(bench_qgemv(a.N, a.K, a.bits, a.gs, a.M, a.iters, a.rotate_mb, flags=flags)))
+    elif a.op == "qgemm":
+        print(json.dumps(bench_qgemm(a.N, a.K, a.bits, a.gs, a.M, a.iters)))
     else:
         print(json.dumps(bench_quantize(a.N, a.K, a.bits, a.gs, a.iters, a.rotate_mb, op=a.op)))
     _lib.check(_lib.load().jq_device_status())

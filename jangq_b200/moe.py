@@ -82,6 +82,11 @@ class ExpertBank:
         self.bits_tab = (torch.tensor(self.expert_bits, dtype=torch.int32, device=dev)
                          if len(self.distinct_bits) > 1 else None)
 
+    @property
+    def gemm_ok(self) -> bool:
+        """Shapes the tensor-core grouped GEMM takes: K a multiple of 64, packed rows of 16-byte multiples."""
+        return self.K % 64 == 0 and all((self.K * b // 8) % 16 == 0 for b in self.distinct_bits)
+
     def slice(self, e0: int, e1: int) -> "ExpertBank":
         """Experts [e0, e1) as their own bank (expert-parallel shard), sharing storage."""
         if self.weight is not None:
@@ -207,7 +212,7 @@ def gather_qmm(x: torch.Tensor, w, scales: torch.Tensor | None = None, biases: t
         raise JangqError(_lib.JQ_EINVAL, f"cannot match {x2.shape[0]} rows of x with {R} indices")
     x2 = x2.contiguous()
     with torch.cuda.device(dev):
-        if R < SORT_THRESHOLD:
+        if R < SORT_THRESHOLD or not bank.gemm_ok:
             return _gather_qgemv(x2, x_div, rhs, bank)
         sp = SortedPairs(rhs, bank.E)
         xs = _gather_rows(x2, sp, x_div)
@@ -247,7 +252,7 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
     st = _lib.stream_ptr(dev)
     I = gate.N
     with torch.cuda.device(dev):
-        if P >= SORT_THRESHOLD:
+        if P >= SORT_THRESHOLD and gate.gemm_ok and up.gemm_ok and down.gemm_ok:
             sp = SortedPairs(idx32, gate.E, expert_base)
             xs = _gather_rows(x, sp, k)
             g = _moe_gemm(xs, sp, gate)

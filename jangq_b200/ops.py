@@ -148,7 +148,13 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, bia
             if M > 0:
                 _qgemv(x2, w, scales, biases, K, bits, group_size, out,
                        _lib.JQ_GEMV_STATIC_WEIGHTS if static_weights else 0)
-        else:
+        elif K % 64 == 0 and (K * bits // 8) % 16 == 0:
             from .gemm import qgemm
             qgemm(x2, w, scales, biases, K, bits, group_size, out)
+        else:
+            # row lengths the tensor-core kernel does not take (K not a multiple of 64, or packed
+            # rows that are not a multiple of 16 bytes): the general mat-vec kernel, 16 rows at a time
+            for m0 in range(0, M, _lib.QGEMV_MAX_M):
+                _qgemv(x2[m0:m0 + _lib.QGEMV_MAX_M], w, scales, biases, K, bits, group_size,
+                       out[m0:m0 + _lib.QGEMV_MAX_M])
     return out.reshape(lead + (N,))

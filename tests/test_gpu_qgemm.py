@@ -91,10 +91,20 @@ def test_qgemm_matches_qgemv_rows():
     assert float(err) < 1e-2
 
 
-def test_qgemm_rejects_unsupported():
-    x, wq, s, b = make_case(32, 64, 96, 4, 32, torch.bfloat16, seed=1)     # K % 64 != 0
-    with pytest.raises(jq.JangqError, match="multiple of 64"):
-        jq.quantized_matmul(x, wq, s, b, group_size=32, bits=4)
+def test_qgemm_unsupported_row_lengths():
+    """K % 64 != 0, or packed rows that are not a multiple of 16 bytes: the C entry point refuses,
+    quantized_matmul falls back to the general mat-vec kernel and stays correct."""
+    lib = _lib.load()
+    for K, bits, gs in ((96, 4, 32), (64, 3, 64)):
+        x, wq, s, b = make_case(40, 64, K, bits, gs, torch.bfloat16, seed=K)
+        y = torch.empty((40, 64), dtype=torch.bfloat16, device=DEV)
+        rc = lib.jq_qgemm(x.data_ptr(), _lib.JQ_BF16, 40, K, wq.data_ptr(), s.data_ptr(), b.data_ptr(), _lib.JQ_BF16,
+                          64, K, bits, gs, y.data_ptr(), _lib.JQ_BF16, 64, _lib.stream_ptr())
+        assert rc == _lib.JQ_EUNSUPPORTED
+        y = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
+        ref = jo.qmatmul(x.float().cpu().numpy(), wq.cpu().numpy().view(np.uint32), s.float().cpu().numpy(),
+                         b.float().cpu().numpy(), bits, gs)
+        assert np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max() <= 1e-2
 
 
 def test_device_status_clean_after_gemm():
