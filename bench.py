@@ -288,7 +288,7 @@ def run_cuda(args):
         per_gpu = value / world
         traffic = None
         try:
-            traffic = json.load(open(os.path.join(ROOT, "profiles", "qgemv_traffic.json"))).get("dram_bytes_per_step")
+            traffic = json.load(open(os.path.join(ROOT, "profiles", "qgemv_traffic.json"))).get("dram_bytes_per_step_scaled")
         except Exception:
             pass
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -298,7 +298,9 @@ def run_cuda(args):
                 "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                              "frac": per_gpu / peak,
                              "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650",
-                             "traffic": traffic, "kernel": "qgemv_mma_kernel (225 launches per step, averaged)"},
+                             "traffic": traffic, "traffic_note": "bytes per 225-launch step, scaled from two ncu captures in which "
+                             "per-launch DRAM bytes equalled the algorithmic bytes (profiles/bench_launch_list.md)",
+                             "kernel": "qgemv_mma_kernel (225 launches per step, averaged)"},
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": plan.h2d_bytes,
                         "d2h_bytes_per_step": plan.d2h_bytes, "ms_per_step": e2e_ms / K},
                 "gpu_launches": plan.launches_per_run * K, "clocks": clk.summary()}
