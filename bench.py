@@ -369,8 +369,30 @@ def run_moe(args, device, world, rank, barrier):
         peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
     except Exception:
         pass
+    # routed-expert block over a 2048-token prefill batch per GPU (sorted grouped-GEMM path)
+    Tp = 2048
+    xp = torch.randn((Tp, stack.H), generator=g, device=device).to(torch.bfloat16)
+    nl = min(4, stack.L)
+    for l in range(nl):
+        stack.prefill_layer(xp, l)
+    barrier()
+    ev0.record()
+    for _ in range(3):
+        for l in range(nl):
+            stack.prefill_layer(xp, l)
+    ev1.record()
+    barrier()
+    tp = torch.tensor([ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tp, op=dist.ReduceOp.MAX)
+    ms_layer = float(tp.item()) / (3 * nl)
+    flops_layer = 2.0 * Tp * stack.k * 3 * stack.I * stack.H
+    prefill = {"tokens_per_gpu": Tp, "ms_per_layer": ms_layer, "tok_s_per_layer": world * Tp / (ms_layer * 1e-3),
+               "expert_TFLOPs_per_gpu": flops_layer / (ms_layer * 1e-3) / 1e12,
+               "note": "router + sort + gather + gate/up/down grouped GEMMs + SwiGLU + combine of one layer; "
+                       "N>1: all-to-all dispatch/combine of the rank's 2048 tokens (host-synchronised split sizes)"}
     gbs = stack.bytes_per_token / (ms * 1e-3) / 1e9
-    return {"tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
+    return {"prefill": prefill, "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
             "per_gpu_GBps": gbs, "hbm_frac": gbs / peak, "graph": graph is not None, "finite": finite,
             "workload": "config3 MoE stack, batch-1 decode per GPU: 48 layers x [q,k,v,o @6b + bf16 router + top-8 of "
                         "128 experts (768x2048 gate/up, 2048x768 down) @2b], group 64; experts sharded E/N per GPU, "

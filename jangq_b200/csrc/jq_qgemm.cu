@@ -602,10 +602,12 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     JQ_REQUIRE(m_tiles < 65536, JQ_EUNSUPPORTED, "too many row tiles for one launch (%lld)", (long long)m_tiles);
     // 256-wide tiles reuse every activation tile twice as often; narrow outputs keep 128
     const bool wide = N >= 256 && !getenv("JANGQ_GEMM_BN128");
+    const bool dpr2 = getenv("JANGQ_GEMM_DPR2") != nullptr;      // tuning knob: two dequantizer threads per row
 #define JQ_GEMM_CASE(B)                                                                                  \
     if (bits == B) {                                                                                     \
         if (x_dtype == JQ_BF16)                                                                          \
-            return wide ? launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st)                    \
+            return wide ? (dpr2 ? launch_gemm<__nv_bfloat16, B, 256, 2>(xmap, a, m_tiles, st)            \
+                                : launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st))           \
                         : launch_gemm<__nv_bfloat16, B, 128, 1>(xmap, a, m_tiles, st);                   \
         return launch_gemm<__half, B, 128, 1>(xmap, a, m_tiles, st);                                     \
     }

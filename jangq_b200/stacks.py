@@ -83,6 +83,19 @@ class MoEDecodeStack:
         return x
 
 
+    def prefill_layer(self, x: torch.Tensor, layer: int = 0) -> torch.Tensor:
+        """The routed-expert block of one layer over many tokens (sorted tensor-core path); with
+        world > 1 the tokens of this rank are dispatched to the expert owners and combined back."""
+        lay = self.layers[layer]
+        logits = torch.matmul(x, lay["router"].t()).float()
+        idx, w = moe.route_softmax_topk(logits, self.k)
+        if self.world == 1:
+            return moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"])
+        y = moe_ep.dispatch_combine(x, idx, w, self.E, moe_ep.local_experts_fn(lay["gate"], lay["up"], lay["down"]),
+                                    group=self.group)
+        return y.to(x.dtype)
+
+
 def moe_bytes(lin: JANGLinear) -> int:
     n, k = lin.out_features, lin.in_features
     return n * k * lin.bits // 8 + n * (k // lin.group_size) * 2 * lin.scales.element_size()
