@@ -28,29 +28,11 @@
 #include <cstdlib>
 
 #include "jq_mma.cuh"
+#include "jq_qgemv.cuh"
 
 namespace jq {
 
 __device__ int g_timeout_flag = 0;   // set by any kernel whose bounded wait ran out
-
-struct GemvArgs {
-    const void* x;
-    const uint32_t* codes;
-    const void* scales;
-    const void* biases;
-    void* y;
-    int64_t N, K, ldx, ldy;
-    int M, G, nbuf;
-    int pdl;      // launched with programmatic stream serialization (weights are static)
-    // gather mode (routed experts, decode): blockIdx.y = (token, slot) pair p, expert e = pair_expert[p];
-    // weights come from per-expert pointer tables, x row = p / x_div, y row = p, M = 1
-    const int32_t* pair_expert;
-    const uint32_t* const* codes_tab;
-    const void* const* scales_tab;
-    const void* const* biases_tab;
-    const int32_t* bits_tab;      // optional: experts whose width differs from the launch's are skipped
-    int x_div, num_experts;
-};
 
 constexpr int GEMV_MAX_NBUF = 3;
 
@@ -81,8 +63,6 @@ qgemv_mma_kernel(const GemvArgs a) {
     using F = Fields<AT, BITS>;
     using Geo = GemvGeom<BITS, GS, MT>;
     static_assert(NW == 4 || NW == 8, "4 or 8 warps split K");
-    constexpr int BPG = GS / 64;            // 64-code k-blocks per quantization group
-    constexpr int UW = Unit<BITS>::WORDS;
     constexpr int ROWS = Geo::ROWS, KT = Geo::KT, RS = Geo::RS, XS = Geo::XS, NG = Geo::NG, NQ = Geo::NQ,
                   NGP = Geo::NGP;
 
@@ -266,66 +246,7 @@ qgemv_mma_kernel(const GemvArgs a) {
         const int xstep = (g < M) ? 64 : 0;
         const float2* pt = reinterpret_cast<const float2*>(buf + Geo::SC_OFF) + g * NGP;
         const float* xsum = Xs + 2 * tig;
-        float cg[MT][F::PASSES][4];
-#pragma unroll 2
-        for (int blk = 0; blk < nblk; ++blk) {
-            uint32_t xr[8];
-            {
-                const uint4* xp = reinterpret_cast<const uint4*>(xrow);
-                const uint4 v0 = xp[0], v1 = xp[1];
-                xr[0] = v0.x; xr[1] = v0.y; xr[2] = v0.z; xr[3] = v0.w;
-                xr[4] = v1.x; xr[5] = v1.y; xr[6] = v1.z; xr[7] = v1.w;
-                xrow += xstep;
-            }
-            const bool first = (blk % BPG) == 0;
-            uint32_t bb[4][2];
-            bb[0][0] = make_b<BITS, 0, 0>(xr); bb[0][1] = make_b<BITS, 0, 1>(xr);
-            bb[1][0] = make_b<BITS, 1, 0>(xr); bb[1][1] = make_b<BITS, 1, 1>(xr);
-            bb[2][0] = make_b<BITS, 2, 0>(xr); bb[2][1] = make_b<BITS, 2, 1>(xr);
-            bb[3][0] = make_b<BITS, 3, 0>(xr); bb[3][1] = make_b<BITS, 3, 1>(xr);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                uint32_t ulo[UW], uhi[UW];
-                load_unit<BITS>(c_lo + mt * 16 * RS, blk, tig, ulo);
-                load_unit<BITS>(c_lo + (mt * 16 + 8) * RS, blk, tig, uhi);
-#define JQ_STEP(T)                                                                                   \
-    {                                                                                                \
-        {                                                                                            \
-            const uint32_t af[4] = {make_a<AT, BITS, T, 0, 0>(ulo), make_a<AT, BITS, T, 0, 0>(uhi),  \
-                                    make_a<AT, BITS, T, 1, 0>(ulo), make_a<AT, BITS, T, 1, 0>(uhi)}; \
-            if (T == 0 && first) A::mma0(cg[mt][0], af, bb[T][0], bb[T][1]);                         \
-            else A::mma(cg[mt][0], af, bb[T][0], bb[T][1]);                                          \
-        }                                                                                            \
-        if constexpr (F::PASSES == 2) {                                                              \
-            const uint32_t af[4] = {make_a<AT, BITS, T, 0, 1>(ulo), make_a<AT, BITS, T, 0, 1>(uhi),  \
-                                    make_a<AT, BITS, T, 1, 1>(ulo), make_a<AT, BITS, T, 1, 1>(uhi)}; \
-            if (T == 0 && first) A::mma0(cg[mt][F::PASSES - 1], af, bb[T][0], bb[T][1]);             \
-            else A::mma(cg[mt][F::PASSES - 1], af, bb[T][0], bb[T][1]);                              \
-        }                                                                                            \
-    }
-                JQ_STEP(0) JQ_STEP(1) JQ_STEP(2) JQ_STEP(3)
-#undef JQ_STEP
-            }
-            if (blk % BPG == BPG - 1) {
-                const float2 xv = *reinterpret_cast<const float2*>(xsum);
-                xsum += 8;
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const float2 pt_lo = pt[mt * 16 * NGP], pt_hi = pt[(mt * 16 + 8) * NGP];
-                    float c[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        c[i] = cg[mt][0][i];
-                        if constexpr (F::PASSES == 2) c[i] = fmaf(16.f, cg[mt][F::PASSES - 1][i], c[i]);
-                    }
-                    acc[mt][0] = fmaf(pt_lo.x, c[0], fmaf(pt_lo.y, xv.x, acc[mt][0]));
-                    acc[mt][1] = fmaf(pt_lo.x, c[1], fmaf(pt_lo.y, xv.y, acc[mt][1]));
-                    acc[mt][2] = fmaf(pt_hi.x, c[2], fmaf(pt_hi.y, xv.x, acc[mt][2]));
-                    acc[mt][3] = fmaf(pt_hi.x, c[3], fmaf(pt_hi.y, xv.y, acc[mt][3]));
-                }
-                ++pt;
-            }
-        }
+        gemv_stage_blocks<AT, BITS, GS, MT>(c_lo, RS, xrow, xstep, pt, NGP, xsum, nblk, tig, acc);
         __syncwarp();
         issue_codes(st + nbuf * NW, b);
         issue_x(st + nbuf * NW, b);
@@ -448,6 +369,19 @@ static bool force_simple() {
     return e && e[0] == '1';
 }
 
+// JANGQ_GEMV_KERNEL selects the fast-path kernel: unset = per-width default, "tc" = tensor-memory
+// kernel wherever the shape fits it, "mma" = the warp-MMA kernel of this file, "row" = the
+// row-parallel cluster kernel.
+// A tuning and comparison knob.
+static int gemv_kernel_choice() {
+    const char* e = getenv("JANGQ_GEMV_KERNEL");
+    if (!e) return 0;
+    if (e[0] == 'm') return 1;
+    if (e[0] == 'r') return 2;
+    if (e[0] == 't') return 3;      // tensor-memory kernel for every width it supports
+    return 0;
+}
+
 template <typename AT, int BITS, int GS, int MT, int NW>
 static int launch_mma_cfg(GemvArgs a, int pairs, int nbuf, cudaStream_t st, bool* launched) {
     using Geo = GemvGeom<BITS, GS, MT>;
@@ -542,9 +476,19 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
         a.G = (int)(K / gs);
         a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
         a.pair_expert = nullptr; a.codes_tab = nullptr; a.scales_tab = nullptr; a.biases_tab = nullptr;
-        a.bits_tab = nullptr; a.x_div = 1; a.num_experts = 0;
+        a.bits_tab = nullptr; a.x_div = 1; a.num_experts = 0; a.ksplit = 1; a.nbuf = 0; a.status = nullptr;
         bool launched = false;
-        if (fast) {
+        const int kern = gemv_kernel_choice();
+        // measured on B200: the tensor-memory kernel wins for 4- and 8-bit codes, the warp-MMA kernel for 2-bit
+        if (fast && (kern == 3 || (kern == 0 && bits != 2))) {
+            rc = launch_tc_kernel(a, x_dtype, bits, gs, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (fast && kern == 2) {
+            rc = launch_row_kernel(a, x_dtype, bits, gs, 1, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (fast && !launched) {
 #define JQ_GEMV_CASE(B, GSZ)                                                                     \
     if (bits == B && gs == GSZ) {                                                                \
         rc = (x_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, 1, st, &launched)          \
@@ -586,13 +530,17 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
     a.x = x; a.codes = nullptr; a.scales = nullptr; a.biases = nullptr; a.y = y;
     a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.M = 1; a.G = (int)(K / gs); a.nbuf = 0; a.pdl = 0;
     a.pair_expert = pair_expert; a.codes_tab = codes_tab; a.scales_tab = scales_tab; a.biases_tab = biases_tab;
-    a.bits_tab = bits_tab; a.x_div = x_div; a.num_experts = num_experts;
+    a.bits_tab = bits_tab; a.x_div = x_div; a.num_experts = num_experts; a.ksplit = 1; a.status = nullptr;
     // the per-expert base pointers are not known on the host: the fast path relies on the caller's
     // promise (checked for the row pitch here) that every expert tensor is 16-byte aligned
     const bool fast = !force_simple() && (gs == 64 || gs == 128) && act_dtype != JQ_F32 && sidecar_dtype == act_dtype &&
                       ((K * bits / 8) % 16 == 0) && aligned(x, 16) && (ldx % 8 == 0) && ((K / gs) % 4 == 0) && bits != 5;
     bool launched = false;
-    if (fast) {
+    if (fast && gemv_kernel_choice() == 2) {
+        rc = launch_row_kernel(a, act_dtype, bits, gs, (int)pairs, st, &launched);
+        if (rc != JQ_OK) return rc;
+    }
+    if (fast && !launched) {
 #define JQ_GEMV_CASE(B, GSZ)                                                                          \
     if (bits == B && gs == GSZ) {                                                                     \
         rc = (act_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, (int)pairs, st, &launched) \

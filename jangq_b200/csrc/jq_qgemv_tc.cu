@@ -1,0 +1,658 @@
+// K2 on the 5th-generation tensor cores: decode-shaped quantized mat-vec
+//     y[M,N] = x[M,K] . deq(W)[N,K]^T,  M <= 8,
+// with the packed codes fed to tcgen05.mma as unsigned 8-bit integers and the activations as
+// signed 8-bit limbs.
+//
+// Bound: HBM bandwidth.  Algorithmic bytes per launch =
+//     N*K*bits/8 (codes) + N*(K/gs)*2*2 (scales, biases) + M*K*2 + M*N*2.
+//
+// Arithmetic.  Per quantization group g and activation row m the activations become fixed
+// point with a shared power-of-two exponent,  x[k] ~ e(g,m) * xi[k],  |xi| <= 2^22, and xi is
+// written as three signed 8-bit limbs  xi = l0 + 256*l1 + 65536*l2.  bf16/f16 values within
+// 2^-14 of the group's largest magnitude are represented exactly, smaller ones are rounded
+// to e(g,m) (2^-22 of the group maximum): f32-accumulation grade.  The tensor core computes the
+// exact integer sums  D_l[row] = sum_k q[row,k] * l_l[k]  (|D| < 2^23, s32 accumulator), and
+// per group   acc[row,m] += e * ( s * (D0 + 256*D1 + 65536*D2) + b * sum_k xi[k] ),
+// which is  sum_k (s*q + b) * x[k]  up to the rounding of x described above.
+//
+// Structure.  One CTA owns 128 weight rows (one per lane of tensor memory) and a K slice; a
+// cluster of `ksplit` CTAs covers all of K and rank 0 adds the partial sums through
+// distributed shared memory.  Warp roles:
+//   warp  0     TMA producer: one lane streams 128-row x 128-byte boxes of packed codes
+//               (cp.async.bulk.tensor, 128-byte swizzle) into a ring of 16 KB stages;
+//   warp  1     allocates tensor memory; one lane issues the MMAs: per 128-k tile four
+//               tcgen05.mma.kind::i8 (M=128, N=16 or 32, K=32).  8-bit codes are the A operand as
+//               they arrive (the stage is the K-major, swizzled A tile); narrower codes come from
+//               tensor memory.  B (the limbs, prepared once per CTA) is 128-byte-swizzled
+//               shared memory;
+//   warps 2-5   epilogue, one weight row per thread: prefetch the row's scales/biases with
+//               cp.async, tcgen05.ld the group sums of a tile, scale, accumulate in registers;
+//   warps 6-13  (2- and 4-bit) unpackers, one weight row per thread: read the row's packed
+//               bytes of a tile from the stage, expand them to one byte per code in registers and
+//               tcgen05.st them as the A operand of the tile.
+// The order of the 16 codes inside every 16-byte unit of A is whatever is cheapest to unpack;
+// the limbs of x are written in the same order.
+// Every mbarrier wait is bounded: a wait that runs out sets the library's status word and the
+// CTA runs on to the common exit without waiting again.
+#include <cstdlib>
+
+#include "jq_mma.cuh"
+#include "jq_qgemv.cuh"
+#include "jq_tc.cuh"
+
+namespace jq {
+
+namespace tcv {
+
+// Optional cycle accounting of the waits of every role (compiled in with -DJQ_TC_PROFILE only).
+#ifdef JQ_TC_PROFILE
+__device__ unsigned long long g_tc_prof[32];
+#define JQ_PROF_DECL(v) long long v = clock64()
+#define JQ_PROF_ADD(cond, idx, t0) do { if (cond) atomicAdd(&g_tc_prof[idx], (unsigned long long)(clock64() - (t0))); } while (0)
+#else
+#define JQ_PROF_DECL(v) do { } while (0)
+#define JQ_PROF_ADD(cond, idx, t0) do { } while (0)
+#endif
+
+constexpr int ROWS = 128;        // weight rows per CTA
+constexpr int TK = 128;          // k per tile = bytes of one A row per tile
+constexpr int NS = 4;            // stages of packed codes (128 rows x 128 bytes)
+constexpr int STAGE_BYTES = ROWS * 128;
+constexpr int NTA = 4;           // unpacked A tiles in tensor memory (32 columns each)
+constexpr int A_COLS = NTA * 32;
+constexpr int D_COLS = 128;      // accumulator ring
+constexpr int TMEM_COLS = A_COLS + D_COLS;
+constexpr int SQ = 8;            // sidecar quads (4 groups) in flight per row
+constexpr int W_EPI = 2, W_MMA2 = 6, W_UNP = 7;   // warp 0 producer, 1 and 6 MMA issuers, 2-5 epilogue, 7-14 unpackers
+constexpr uint32_t POLLS = 1u << 18;
+__host__ __device__ constexpr int threads_for(int bits) { return bits == 8 ? 7 * 32 : 15 * 32; }
+
+__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* own, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(own)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// Position p of a 16-byte unit of the A operand holds code PERM(p) of the unit.
+template <int BITS> __host__ __device__ constexpr int perm(int p) {
+    if (BITS == 2) return (p & 3) * 4 + (p >> 2);                       // register j = codes j, j+4, j+8, j+12
+    if (BITS == 4) return (p & 8) + ((p & 4) ? 1 : 0) + 2 * (p & 3);    // word w: even codes, then odd codes
+    return p;
+}
+
+// shared-memory map (offsets from a 1024-byte aligned base)
+struct Map {
+    int tab, red, sc, b, raw, total;
+};
+__host__ __device__ inline Map make_map(int ncol, int slice_tiles, int slice_groups) {
+    Map m;
+    // [0, 512): 32 mbarriers and the tensor-memory slot
+    m.tab = 512;                                       // float2 (e, sum xi) [slice_groups][8]
+    m.red = m.tab + slice_groups * 64;                 // f32 [128][8]
+    m.sc = m.red + ROWS * 8 * 4;                       // [SQ][128] cells of 16 bytes (scale quad, bias quad)
+    m.b = (m.sc + SQ * ROWS * 16 + 1023) / 1024 * 1024;   // limbs: slice_tiles tiles of ncol rows x 128 bytes
+    m.raw = m.b + slice_tiles * ncol * 128;            // NS stages, 1024-byte aligned
+    m.total = m.raw + NS * STAGE_BYTES;
+    return m;
+}
+
+// inverse of perm(): position of code j inside its 16-byte unit
+template <int BITS> __host__ __device__ constexpr int inv_perm(int j) {
+    if (BITS == 2) return (j >> 2) + 4 * (j & 3);
+    if (BITS == 4) return (j & 8) + 4 * (j & 1) + ((j >> 1) & 3);
+    return j;
+}
+
+template <typename AT, int BITS, int GS, int NCOL>
+__global__ void __launch_bounds__(threads_for(BITS), 2)
+qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
+    using A = Act<AT>;
+    constexpr int THREADS = threads_for(BITS);
+    constexpr int PREP = W_MMA2 * 32;          // threads that prepare the activations (warps 0..5)
+    constexpr int PREP_SYNC = W_UNP * 32;      // ... and the second MMA warp waits for them
+    constexpr int TILE_B = TK * BITS / 8;      // packed bytes of one row and tile (32, 64 or 128)
+    constexpr int TPS = 128 / TILE_B;          // tiles per stage (4, 2 or 1)
+    constexpr int GPT = TK / GS;               // groups per tile (2 or 1)
+    constexpr int KPG = GS / 32;               // MMAs per group (2 or 4)
+    constexpr int TPQ = 4 * GS / TK;           // tiles per sidecar quad (2 or 4)
+    constexpr int DW = GPT * NCOL;             // accumulator columns of one tile
+    constexpr int DC = BITS == 8 ? TMEM_COLS : D_COLS;   // 8-bit codes need no A tiles in tensor memory
+    constexpr int R = (DC / DW) < 4 ? (DC / DW) : 4;   // ring of tiles: A slot and accumulator of tile t = t % R
+    constexpr int EB = R >= 4 ? 2 : 1;         // tiles per epilogue batch
+    constexpr int MMAX = NCOL == 16 ? 5 : 8;
+    static_assert(R >= NS || BITS != 8, "the producer of 8-bit stages relies on R >= NS");
+    static_assert(TPQ % EB == 0, "an epilogue batch stays inside one sidecar quad");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = a.ksplit;
+    const int rb = blockIdx.x / S;
+    const int cr = blockIdx.x - rb * S;                  // rank in the cluster (cluster shape (S,1,1))
+    const int M = a.M, G = a.G;
+    const int nquads = G / 4;                            // K in units of 4 groups
+    const int q_begin = (int)((int64_t)cr * nquads / S), q_end = (int)((int64_t)(cr + 1) * nquads / S);
+    const int sq_max = (nquads + S - 1) / S;             // longest slice of the cluster, quads
+    const int nq = q_end - q_begin;                      // this CTA's slice
+    const int ntiles = nq * TPQ;
+    const int nstages = (ntiles + TPS - 1) / TPS;
+    const int t_begin = q_begin * TPQ;                   // first tile of the slice (global tile index)
+    const int k_begin = t_begin * TK;
+    const int64_t n0 = (int64_t)rb * ROWS;
+
+    const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4);
+    uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* raw_empty = raw_full + NS;
+    uint64_t* a_full = raw_empty + NS;                   // [R]
+    uint64_t* d_full = a_full + 4;                       // [R]
+    uint64_t* d_empty = d_full + 4;                      // [R]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 4);
+    float2* tab = reinterpret_cast<float2*>(smem + mp.tab);
+    float* red = reinterpret_cast<float*>(smem + mp.red);
+    uint8_t* sc_ring = smem + mp.sc;
+    uint8_t* sB = smem + mp.b;
+    uint8_t* sRaw = smem + mp.raw;
+
+    const uint16_t* xs16 = reinterpret_cast<const uint16_t*>(a.x);
+    const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(a.scales);
+    const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(a.biases);
+    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
+
+    // ---- set-up: barriers, tensor memory, first weight copies (static data) -----------------------------
+    JQ_PROF_DECL(t_start);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    auto produce = [&](int st) {       // one lane: stage st of the slice
+        const int s = st % NS;
+        mbar_expect_tx(raw_full + s, STAGE_BYTES);
+        tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, &wmap, t_begin * TILE_B + st * 128, (int)n0, raw_full + s);
+    };
+    if (tid == 0) {
+        for (int i = 0; i < NS; ++i) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 8); }
+        for (int i = 0; i < 4; ++i) { mbar_init(a_full + i, 4); mbar_init(d_full + i, 1); mbar_init(d_empty + i, 4); }
+        mbar_fence_init();
+        for (int st = 0; st < NS && st < nstages; ++st) produce(st);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + (BITS == 8 ? 0 : A_COLS);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // tensor-memory lane quarter = warp id mod 4
+    bool ok = true;
+    JQ_PROF_ADD(tid == 0, 0, t_start);                 // 0: set-up
+
+    float acc[MMAX];
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) acc[m] = 0.f;
+    const int row = (warp & 3) * 32 + lane;              // epilogue and unpacker threads: own weight row
+
+    if (warp >= W_UNP) {
+        if constexpr (BITS != 8) {
+            // ---------------- unpackers: packed codes -> one byte per code -> tensor memory ----------------
+            // They depend on the weights only, so they start before the activations are ready.
+            JQ_PROF_DECL(t_roles);
+            static_assert(BITS == 2 || BITS == 4 || BITS == 8, "widths of this kernel");
+            constexpr int NCH = TILE_B / 16;                          // 16-byte chunks of one row and tile
+            const int half = (warp - W_UNP) >> 2;                     // tiles of a stage alternate between two warp sets
+            const uint32_t row_off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+            for (int st = 0; st < nstages && ok; ++st) {
+                const int s = st % NS;
+                JQ_PROF_DECL(t0);
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(raw_full + s, (uint32_t)(st / NS) & 1u, POLLS));
+                JQ_PROF_ADD(warp == W_UNP && lane == 0, 9, t0);       // 9: unpacker waits for packed codes
+                if (!ok) break;
+                const uint8_t* rowp = sRaw + (size_t)s * STAGE_BYTES + row_off;
+#pragma unroll
+                for (int t2 = 0; t2 < TPS / 2; ++t2) {
+                    const int tt = 2 * t2 + half;
+                    const int t = st * TPS + tt;
+                    if (t >= ntiles) break;
+                    const int ri = t % R;
+                    uint32_t v[32];
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const uint4 w = *reinterpret_cast<const uint4*>(
+                            rowp + (((uint32_t)(tt * NCH + i) ^ (uint32_t)(row & 7)) << 4));
+                        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if constexpr (BITS == 4) {
+                                v[8 * i + 2 * j] = ws[j] & 0x0F0F0F0Fu;
+                                v[8 * i + 2 * j + 1] = (ws[j] >> 4) & 0x0F0F0F0Fu;
+                            } else {
+                                v[16 * i + 4 * j] = ws[j] & 0x03030303u;
+                                v[16 * i + 4 * j + 1] = (ws[j] >> 2) & 0x03030303u;
+                                v[16 * i + 4 * j + 2] = (ws[j] >> 4) & 0x03030303u;
+                                v[16 * i + 4 * j + 3] = (ws[j] >> 6) & 0x03030303u;
+                            }
+                        }
+                    }
+                    JQ_PROF_DECL(t1);
+                    if (t >= R) {      // the MMAs of tile t - R have read this A slot
+                        ok = __all_sync(0xFFFFFFFFu, mbar_wait(d_full + ri, (uint32_t)((t / R) - 1) & 1u, POLLS));
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    JQ_PROF_ADD(warp == W_UNP && lane == 0, 10, t1);  // 10: unpacker waits for a free A tile
+                    JQ_PROF_DECL(t_st);
+                    tmem_st32(tmem_a + lane_base + (uint32_t)(ri * 32), v);
+                    tmem_st_wait();
+                    JQ_PROF_ADD(warp == W_UNP && lane == 0, 11, t_st);  // 11: tensor-memory store
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(a_full + ri);
+                }
+                __syncwarp();                                         // every lane has read its row of the stage
+                if (lane == 0) mbar_arrive(raw_empty + s);
+            }
+            JQ_PROF_ADD(warp == W_UNP && lane == 0, 12, t_roles);     // 12: unpacker loop, total
+        }
+    } else {
+        // ---- warps 0..5: activations of the slice -> limbs (B operand) + per-group (e, sum xi) ----------------
+        const int64_t n_row = min(n0 + row, a.N - 1);
+        auto issue_sc = [&](int j) {                     // epilogue threads: sidecar quad j of the own row
+            if (j < nq) {
+                uint8_t* cell = sc_ring + ((size_t)(j % SQ) * ROWS + row) * 16;
+                const int64_t off = n_row * G + (int64_t)(q_begin + j) * 4;
+                cp_async8(cell, sc16 + off);
+                cp_async8(cell + 8, bi16 + off);
+            }
+            cp_async_commit();
+        };
+        if (warp >= W_EPI && warp < W_MMA2) {
+#pragma unroll
+            for (int i = 0; i < SQ - 1; ++i) issue_sc(i);
+        }
+        if (warp < W_MMA2) {   // rows of B that carry no limb are zero (independent of the activations)
+            const int zq = (NCOL - 3 * M) * 8;               // 16-byte chunks per tile, fewer than PREP
+            if (tid < zq) {
+                const int n = 3 * M + (tid >> 3), c = tid & 7;
+                uint8_t* p0 = sB + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4);
+                for (int t = 0; t < ntiles; ++t)
+                    *reinterpret_cast<uint4*>(p0 + (size_t)t * (NCOL * 128)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        JQ_PROF_DECL(t_prep);
+        {
+            // eight consecutive activations per lane; GS/8 adjacent lanes form a quantization group.
+            // The loads of all PF rounds are issued together, so their latency is paid once.
+            constexpr int LPG = GS / 8;
+            constexpr int PF = 3;
+            const int per_row = ntiles * (TK / 8);
+            const int items = M * per_row;                   // a multiple of 32
+            for (int base0 = warp * 32; base0 < items && warp < W_MMA2; base0 += PREP * PF) {
+                uint4 rawv[PF];
+#pragma unroll
+                for (int i = 0; i < PF; ++i) {
+                    const int it = base0 + i * PREP + lane;
+                    if (it < items) {
+                        const int m = it / per_row;
+                        rawv[i] = *reinterpret_cast<const uint4*>(xs16 + (int64_t)m * a.ldx + k_begin + (it - m * per_row) * 8);
+                    }
+                }
+#ifdef JQ_TC_PROFILE
+                { uint32_t sink; asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(rawv[0].x)); (void)sink; }
+                JQ_PROF_ADD(tid == 0 && base0 == 0, 16, t_prep);   // 16: first activation load has arrived
+#endif
+#pragma unroll
+                for (int i = 0; i < PF; ++i) {
+                    const int it = base0 + i * PREP + lane;
+                    if (it >= items) break;                  // warp-uniform: items is a multiple of 32
+                    const int m = it / per_row;
+                    const int ko = it - m * per_row;         // octet of the slice
+                    const uint32_t w[4] = {rawv[i].x, rawv[i].y, rawv[i].z, rawv[i].w};
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { v[2 * j] = A::lo_f32(w[j]); v[2 * j + 1] = A::hi_f32(w[j]); }
+                    uint32_t amax = 0u;                      // largest magnitude, as bits (NaN/inf sort highest)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) amax = max(amax, __float_as_uint(v[j]) & 0x7FFFFFFFu);
+#pragma unroll
+                    for (int d = 1; d < LPG; d <<= 1) amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+                    uint32_t eb = amax >> 23;
+                    const bool finite = eb != 255u;
+                    eb = max(eb, 21u);
+                    const float scale = __uint_as_float((275u - eb) << 23);      // 2^(21 - E)
+                    float e = __uint_as_float((eb - 21u) << 23);                 // 2^(E - 21)
+                    if (!finite) e = __uint_as_float(0x7FC00000u);               // non-finite input -> NaN output
+                    int xi[8];
+                    int sum = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { xi[j] = __float2int_rn(v[j] * scale); sum += xi[j]; }
+#pragma unroll
+                    for (int d = 1; d < LPG; d <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+                    const int u = ko >> 1, hf = ko & 1;      // 16-code unit of the slice, which half of it
+                    const int t = u >> 3, c = u & 7;         // tile of the slice, 16-byte chunk of its 128-byte row
+                    uint8_t* tile = sB + (size_t)t * (NCOL * 128);
+                    int l0[8], l1[8], l2[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int r1 = (xi[j] + 128) >> 8;
+                        l0[j] = xi[j] & 255; l1[j] = r1 & 255; l2[j] = ((r1 + 128) >> 8) & 255;
+                    }
+                    auto put = [&](int n, const int (&b)[8]) {
+                        // element j of this half is code 8*hf + j of the unit; position inv_perm(8*hf + j)
+                        uint8_t* dst = tile + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4);
+                        if constexpr (BITS == 8) {           // positions 8*hf .. 8*hf+7: two words
+                            *reinterpret_cast<uint2*>(dst + 8 * hf) =
+                                make_uint2(b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24, b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24);
+                        } else if constexpr (BITS == 4) {    // even codes, then odd codes, in the same 8 bytes
+                            *reinterpret_cast<uint2*>(dst + 8 * hf) =
+                                make_uint2(b[0] | b[2] << 8 | b[4] << 16 | b[6] << 24, b[1] | b[3] << 8 | b[5] << 16 | b[7] << 24);
+                        } else {                             // code j -> byte (j >> 2) of word (j & 3): bytes 2*hf, 2*hf+1 of all words
+                            uint16_t* d16 = reinterpret_cast<uint16_t*>(dst) + hf;
+                            d16[0] = (uint16_t)(b[0] | b[4] << 8);
+                            d16[2] = (uint16_t)(b[1] | b[5] << 8);
+                            d16[4] = (uint16_t)(b[2] | b[6] << 8);
+                            d16[6] = (uint16_t)(b[3] | b[7] << 8);
+                        }
+                    };
+                    put(3 * m, l0);
+                    put(3 * m + 1, l1);
+                    put(3 * m + 2, l2);
+                    if ((ko & (LPG - 1)) == 0) tab[(ko / LPG) * 8 + m] = make_float2(e, (float)sum);
+                }
+            }
+        }
+        JQ_PROF_ADD(tid == 0, 17, t_prep);                 // 17: own limbs written
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes of B -> tensor-core reads
+        asm volatile("bar.sync 1, %0;" ::"n"(PREP_SYNC) : "memory");
+        JQ_PROF_ADD(tid == 0, 1, t_prep);                  // 1: activation limbs
+        JQ_PROF_DECL(t_roles);
+
+        if (warp == 0) {
+            // ---------------- TMA producer (the first NS stages are already in flight) ----------------
+            if (lane == 0) {
+                for (int st = NS; st < nstages; ++st) {
+                    JQ_PROF_DECL(t0);
+                    if constexpr (BITS == 8)    // stage = tile: free once the MMAs of tile st - NS have completed
+                        ok = mbar_wait(d_full + (st - NS) % R, (uint32_t)((st - NS) / R) & 1u, POLLS);
+                    else
+                        ok = mbar_wait(raw_empty + st % NS, (uint32_t)((st / NS) - 1) & 1u, POLLS);
+                    JQ_PROF_ADD(true, 2, t0);                  // 2: producer waits for a free stage
+                    if (!ok) break;
+                    produce(st);
+                }
+                JQ_PROF_ADD(true, 13, t_roles);                // 13: producer role, total
+            }
+        } else if (warp == 1 || warp == W_MMA2) {
+            // ---------------- MMA issuers: warp 1 takes the even tiles, warp 6 the odd ones ----------------
+            // (issuing one tcgen05.mma costs its thread ~50 cycles, more than the tensor core needs for it)
+            if (lane == 0) {
+                constexpr uint32_t idesc = umma_idesc_i8(NCOL);
+                const uint32_t b_addr = smem_u32(sB), raw_addr = smem_u32(sRaw);
+                for (int t = (warp == 1 ? 0 : 1); t < ntiles && ok; t += 2) {
+                    const int ri = t % R, s = t % NS;
+                    JQ_PROF_DECL(t0);
+                    if constexpr (BITS == 8) ok = mbar_wait(raw_full + s, (uint32_t)(t / NS) & 1u, POLLS);
+                    else ok = mbar_wait(a_full + ri, (uint32_t)(t / R) & 1u, POLLS);
+                    JQ_PROF_ADD(warp == 1, 3, t0);             // 3: MMA waits for its A operand
+                    JQ_PROF_DECL(t1);
+                    if (ok && t >= R) ok = mbar_wait(d_empty + ri, (uint32_t)((t / R) - 1) & 1u, POLLS);
+                    JQ_PROF_ADD(warp == 1, 4, t1);             // 4: MMA waits for a free accumulator
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint32_t dcol = tmem_d + (uint32_t)(ri * DW + (kk / KPG) * NCOL);
+                        const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)t * (NCOL * 128) + kk * 32);
+                        if constexpr (BITS == 8)
+                            umma_i8_ss(dcol, umma_desc_sw128(raw_addr + (uint32_t)s * STAGE_BYTES + kk * 32), bdesc, idesc,
+                                       (kk % KPG) ? 1u : 0u);
+                        else
+                            umma_i8_ts(dcol, tmem_a + (uint32_t)(ri * 32 + kk * 8), bdesc, idesc, (kk % KPG) ? 1u : 0u);
+                    }
+                    umma_commit(d_full + ri);      // also what frees the tile's A operand (stage or tensor-memory slot)
+                }
+                JQ_PROF_ADD(warp == 1, 5, t_roles);            // 5: MMA loop, total
+            }
+        } else {
+            // ---------------- epilogue: one weight row per thread, EB tiles per step ----------------
+            for (int j = 0; j < nq && ok; ++j) {
+                JQ_PROF_DECL(t0);
+                issue_sc(j + SQ - 1);
+                cp_async_wait<SQ - 1>();                              // quad j of this row has landed
+                JQ_PROF_ADD(warp == W_EPI && lane == 0, 6, t0);       // 6: epilogue waits for sidecars
+                const uint4 cell = *reinterpret_cast<const uint4*>(sc_ring + ((size_t)(j % SQ) * ROWS + row) * 16);
+                const uint32_t sw[2] = {cell.x, cell.y}, bw[2] = {cell.z, cell.w};
+#pragma unroll
+                for (int tb = 0; tb < TPQ / EB; ++tb) {
+                    const int t0i = j * TPQ + tb * EB;                // first tile of the batch
+                    JQ_PROF_DECL(t1);
+#pragma unroll
+                    for (int i = 0; i < EB; ++i)
+                        if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(d_full + (t0i + i) % R, (uint32_t)((t0i + i) / R) & 1u, POLLS));
+                    JQ_PROF_ADD(warp == W_EPI && lane == 0, 7, t1);   // 7: epilogue waits for sums
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (NCOL == 16 && M == 1) {
+                        // three columns per group: load every group of the batch, then one wait
+                        uint32_t d4[EB * GPT][4];
+#pragma unroll
+                        for (int i = 0; i < EB; ++i)
+#pragma unroll
+                            for (int gi = 0; gi < GPT; ++gi)
+                                tmem_ld4_nowait(tmem_d + lane_base + (uint32_t)(((t0i + i) % R) * DW + gi * NCOL), d4[i * GPT + gi]);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane < EB) mbar_arrive(d_empty + (t0i + lane) % R);
+#pragma unroll
+                        for (int i = 0; i < EB * GPT; ++i) {
+                            const int gq = tb * EB * GPT + i;         // group of the quad
+                            const float s = (gq & 1) ? A::hi_f32(sw[gq >> 1]) : A::lo_f32(sw[gq >> 1]);
+                            const float bs = (gq & 1) ? A::hi_f32(bw[gq >> 1]) : A::lo_f32(bw[gq >> 1]);
+                            const float2 es = tab[(j * 4 + gq) * 8];
+                            const float f = fmaf((float)(int)d4[i][2], 65536.f, fmaf((float)(int)d4[i][1], 256.f, (float)(int)d4[i][0]));
+                            acc[0] = fmaf(es.x, fmaf(s, f, bs * es.y), acc[0]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < EB; ++i) {
+#pragma unroll
+                            for (int gi = 0; gi < GPT; ++gi) {
+                                uint32_t dv[NCOL];
+                                const uint32_t dcol = tmem_d + lane_base + (uint32_t)(((t0i + i) % R) * DW + gi * NCOL);
+                                if constexpr (NCOL == 16) tmem_ld16(dcol, dv); else tmem_ld32(dcol, dv);
+                                const int gq = (tb * EB + i) * GPT + gi;
+                                const float s = (gq & 1) ? A::hi_f32(sw[gq >> 1]) : A::lo_f32(sw[gq >> 1]);
+                                const float bs = (gq & 1) ? A::hi_f32(bw[gq >> 1]) : A::lo_f32(bw[gq >> 1]);
+#pragma unroll
+                                for (int m = 0; m < MMAX; ++m) {
+                                    if (m < M) {
+                                        const float2 es = tab[(j * 4 + gq) * 8 + m];
+                                        const float f = fmaf((float)(int)dv[3 * m + 2], 65536.f,
+                                                             fmaf((float)(int)dv[3 * m + 1], 256.f, (float)(int)dv[3 * m]));
+                                        acc[m] = fmaf(es.x, fmaf(s, f, bs * es.y), acc[m]);
+                                    }
+                                }
+                            }
+                        }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane < EB) mbar_arrive(d_empty + (t0i + lane) % R);
+                    }
+                }
+            }
+            cp_async_wait<0>();
+            JQ_PROF_ADD(warp == W_EPI && lane == 0, 8, t_roles);      // 8: epilogue loop, total
+        }
+    }
+    if (!ok) atomicExch(a.status, 1);
+
+    // ---- results: direct store, or partial sums to rank 0 through distributed shared memory -----------------
+    const bool epi = warp >= W_EPI && warp < W_MMA2;
+    if (S == 1) {
+        if (epi && n0 + row < a.N) {
+#pragma unroll
+            for (int m = 0; m < MMAX; ++m)
+                if (m < M) y16[(int64_t)m * a.ldy + n0 + row] = A::from_f32(acc[m]);
+        }
+    } else {
+        if (epi) {
+#pragma unroll
+            for (int m = 0; m < MMAX; ++m) red[row * 8 + m] = acc[m];
+        }
+        cluster_sync_all();
+        if (cr == 0) {
+            for (int idx = tid; idx < ROWS * M; idx += THREADS) {
+                const int m = idx / ROWS, rr = idx - m * ROWS;
+                float v = red[rr * 8 + m];
+                for (int s = 1; s < S; ++s) v += ld_cluster_f32(red + rr * 8 + m, (uint32_t)s);
+                if (n0 + rr < a.N) y16[(int64_t)m * a.ldy + n0 + rr] = A::from_f32(v);
+            }
+        }
+        cluster_sync_all();    // peers keep their shared memory alive until rank 0 has read it
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    JQ_PROF_ADD(tid == 0, 14, t_start);                           // 14: whole CTA
+#ifdef JQ_TC_PROFILE
+    if (tid == 0) atomicAdd(&g_tc_prof[15], 1ull);                 // 15: CTA count
+#endif
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return (e && e[0] >= '0' && e[0] <= '9') ? atoi(e) : dflt;
+}
+
+template <typename AT, int BITS, int GS, int NCOL>
+static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, cudaStream_t st, bool* launched) {
+    constexpr int TPQ = 4 * GS / TK;
+    const int nquads = a.G / 4;
+    const int sq_max = (nquads + S - 1) / S;
+    const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4);
+    const int smem = mp.total + 1024;
+    if (smem > 227 * 1024) return JQ_OK;
+    static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
+    int dev = 0;
+    JQ_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_tc_kernel<AT, BITS, GS, NCOL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        227 * 1024));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    a.ksplit = S;
+    a.status = status_word();
+    JQ_REQUIRE(a.status != nullptr, JQ_ECUDA, "could not locate the device status word");
+    const unsigned row_blocks = (unsigned)((a.N + ROWS - 1) / ROWS);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(row_blocks * (unsigned)S);
+    cfg.blockDim = dim3(threads_for(BITS));
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (S > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)S;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (a.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_tc_kernel<AT, BITS, GS, NCOL>, wmap, a));
+    *launched = true;
+    return JQ_OK;
+}
+
+// Cluster size.  The grid is row_blocks * S CTAs, at most two per SM.  The launch is HBM-bound as a
+// whole, so an SM may carry up to ~1.5x its fair share of tiles before it becomes the critical path;
+// every wave of CTAs adds a fixed start-up (barriers, tensor-memory allocation, first-byte latency)
+// counted in tiles.  The smallest S with the lowest modelled time wins.
+template <typename AT, int BITS, int GS, int NCOL>
+static int launch_shape(const CUtensorMap& wmap, const GemvArgs& a, cudaStream_t st, bool* launched) {
+    constexpr int TPQ = 4 * GS / TK;
+    const int sms = sm_count();
+    const int nquads = a.G / 4;
+    const int64_t row_blocks = (a.N + ROWS - 1) / ROWS;
+    const double startup = (double)env_int("JANGQ_TC_STARTUP", 6);
+    const double fair = (double)row_blocks * nquads * TPQ / sms;
+    int best = 0;
+    double best_cost = 0;
+    for (int S = 1; S <= 8 && S <= nquads; ++S) {
+        const int sq_max = (nquads + S - 1) / S;
+        const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4);
+        if (mp.total + 1024 > 227 * 1024) continue;
+        const int per_sm = (mp.total + 2048 <= 113 * 1024) ? 2 : 1;
+        const int64_t ctas = row_blocks * S;
+        const int64_t waves = (ctas + (int64_t)per_sm * sms - 1) / ((int64_t)per_sm * sms);
+        const double busiest = (double)((ctas + sms - 1) / sms) * sq_max * TPQ / 1.5;
+        const double cost = (busiest > fair ? busiest : fair) + startup * (double)waves;
+        if (best == 0 || cost < best_cost - 1e-9) { best = S; best_cost = cost; }
+    }
+    best = env_int("JANGQ_TC_S", best);
+    if (best < 1 || best > 8 || best > nquads) return JQ_OK;
+    return launch_cfg<AT, BITS, GS, NCOL>(wmap, a, best, st, launched);
+}
+
+}  // namespace tcv
+
+#ifdef JQ_TC_PROFILE
+extern "C" int jq_tc_profile_read(unsigned long long* out, int reset) {
+    if (cudaMemcpyFromSymbol(out, tcv::g_tc_prof, sizeof(tcv::g_tc_prof)) != cudaSuccess) return 1;
+    if (reset) {
+        unsigned long long z[32] = {};
+        if (cudaMemcpyToSymbol(tcv::g_tc_prof, z, sizeof(z)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#endif
+
+// Dense mat-vec on the tensor-memory kernel; *launched stays false when the shape does not fit it.
+int launch_tc_kernel(const GemvArgs& a, int act_dtype, int bits, int gs, cudaStream_t st, bool* launched) {
+    *launched = false;
+    const int64_t rowbytes = a.K * bits / 8;
+    if (!(bits == 2 || bits == 4 || bits == 8) || a.K % tcv::TK != 0 || a.G % 4 != 0 || a.M > 8 || rowbytes < 128)
+        return JQ_OK;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return JQ_OK;
+    // the packed codes as a [N][rowbytes] byte matrix; a box is 128 rows x 128 bytes, 128-byte swizzled;
+    // rows past N and bytes past the row end read as zero
+    CUtensorMap wmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)rowbytes, (cuuint64_t)a.N};
+    const cuuint64_t gstride[1] = {(cuuint64_t)rowbytes};
+    const cuuint32_t box[2] = {128, (cuuint32_t)tcv::ROWS};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.codes), gdim, gstride, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    JQ_REQUIRE(cr == CUDA_SUCCESS, JQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+    int rc = JQ_OK;
+#define JQ_TC_CASE(B, GSZ)                                                                                    \
+    if (bits == B && gs == GSZ) {                                                                             \
+        if (act_dtype == JQ_BF16)                                                                             \
+            rc = a.M <= 5 ? tcv::launch_shape<__nv_bfloat16, B, GSZ, 16>(wmap, a, st, launched)               \
+                          : tcv::launch_shape<__nv_bfloat16, B, GSZ, 32>(wmap, a, st, launched);              \
+        else                                                                                                  \
+            rc = a.M <= 5 ? tcv::launch_shape<__half, B, GSZ, 16>(wmap, a, st, launched)                      \
+                          : tcv::launch_shape<__half, B, GSZ, 32>(wmap, a, st, launched);                     \
+    }
+    JQ_TC_CASE(2, 64) JQ_TC_CASE(4, 64) JQ_TC_CASE(8, 64) JQ_TC_CASE(2, 128) JQ_TC_CASE(4, 128) JQ_TC_CASE(8, 128)
+#undef JQ_TC_CASE
+    return rc;
+}
+
+}  // namespace jq
