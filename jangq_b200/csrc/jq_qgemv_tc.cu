@@ -19,15 +19,18 @@
 // cluster of `ksplit` CTAs covers all of K and rank 0 adds the partial sums through
 // distributed shared memory.  Warp roles:
 //   warp  0     TMA producer: one lane streams 128-row x 128-byte boxes of packed codes
-//               (cp.async.bulk.tensor, 128-byte swizzle) into a ring of 16 KB stages;
-//   warp  1     allocates tensor memory; one lane issues the MMAs: per 128-k tile four
+//               (cp.async.bulk.tensor, 128-byte swizzle) into a ring of 16 KB stages; when the
+//               whole K slice fits the ring it is in flight before the activations exist;
+//   warps 1-2   MMA issuers (even / odd tiles; issuing one tcgen05.mma costs its thread ~50
+//               cycles, more than the tensor core needs for it): per 128-k tile four
 //               tcgen05.mma.kind::i8 (M=128, N=16 or 32, K=32).  8-bit codes are the A operand as
 //               they arrive (the stage is the K-major, swizzled A tile); narrower codes come from
 //               tensor memory.  B (the limbs, prepared once per CTA) is 128-byte-swizzled
-//               shared memory;
-//   warps 2-5   epilogue, one weight row per thread: prefetch the row's scales/biases with
-//               cp.async, tcgen05.ld the group sums of a tile, scale, accumulate in registers;
-//   warps 6-13  (2- and 4-bit) unpackers, one weight row per thread: read the row's packed
+//               shared memory.  Warp 1 also owns the tensor-memory allocation;
+//   warps 3-10  epilogue in two sets that alternate pairs of tiles, one weight row per thread:
+//               prefetch the row's scales/biases with cp.async, tcgen05.ld the group sums,
+//               scale, accumulate in registers;
+//   warps 11-18 (2- and 4-bit) unpackers, one weight row per thread: read the row's packed
 //               bytes of a tile from the stage, expand them to one byte per code in registers and
 //               tcgen05.st them as the A operand of the tile.
 // The order of the 16 codes inside every 16-byte unit of A is whatever is cheapest to unpack;
@@ -56,16 +59,12 @@ __device__ unsigned long long g_tc_prof[32];
 
 constexpr int ROWS = 128;        // weight rows per CTA
 constexpr int TK = 128;          // k per tile = bytes of one A row per tile
-constexpr int NS = 4;            // stages of packed codes (128 rows x 128 bytes)
-constexpr int STAGE_BYTES = ROWS * 128;
-constexpr int NTA = 4;           // unpacked A tiles in tensor memory (32 columns each)
-constexpr int A_COLS = NTA * 32;
-constexpr int D_COLS = 128;      // accumulator ring
-constexpr int TMEM_COLS = A_COLS + D_COLS;
-constexpr int SQ = 8;            // sidecar quads (4 groups) in flight per row
-constexpr int W_EPI = 2, W_MMA2 = 6, W_UNP = 7;   // warp 0 producer, 1 and 6 MMA issuers, 2-5 epilogue, 7-14 unpackers
+constexpr int MAXNS = 12;        // most stages of packed codes
+constexpr int BOX_BYTES = ROWS * 128;   // one TMA box: 128 rows x 128 bytes
+constexpr int SQ = 4;            // sidecar quads (4 groups) in flight per row and epilogue set
+constexpr int W_MMA = 1, W_EPI = 3, W_UNP = 11;
 constexpr uint32_t POLLS = 1u << 18;
-__host__ __device__ constexpr int threads_for(int bits) { return bits == 8 ? 7 * 32 : 15 * 32; }
+__host__ __device__ constexpr int threads_for(int bits) { return bits == 8 ? W_UNP * 32 : (W_UNP + 8) * 32; }
 
 __device__ __forceinline__ void cp_async8(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -81,61 +80,57 @@ __device__ __forceinline__ float ld_cluster_f32(const float* own, uint32_t rank)
     return v;
 }
 
-// Position p of a 16-byte unit of the A operand holds code PERM(p) of the unit.
-template <int BITS> __host__ __device__ constexpr int perm(int p) {
-    if (BITS == 2) return (p & 3) * 4 + (p >> 2);                       // register j = codes j, j+4, j+8, j+12
-    if (BITS == 4) return (p & 8) + ((p & 4) ? 1 : 0) + 2 * (p & 3);    // word w: even codes, then odd codes
-    return p;
-}
+// Ring of tiles in tensor memory: tile t uses A slot (narrow codes) and accumulator t % R.
+template <int BITS, int GS, int NCOL> struct Ring {
+    static constexpr int GPT = TK / GS;                    // groups per tile (2 or 1)
+    static constexpr int DW = GPT * NCOL;                  // accumulator columns of one tile
+    static constexpr int R = (256 / DW) < 8 ? (256 / DW) : 8;
+    static constexpr int RP = R / 2;                       // ... handled in pairs of tiles: ring of RP pairs
+    static constexpr int A_COLS = BITS == 8 ? 0 : R * 32;  // 8-bit codes are read from shared memory
+    // a stage of packed codes: one box (4 or 2 tiles of narrow codes) or, for 8-bit codes, two boxes = one pair
+    static constexpr int STAGE_BYTES = BITS == 8 ? 2 * BOX_BYTES : BOX_BYTES;
+    static constexpr int MAX_STAGES = BITS == 8 ? MAXNS / 2 : MAXNS;
+    static constexpr int NEED = A_COLS + R * DW;
+    static constexpr int TMEM_COLS = NEED <= 128 ? 128 : NEED <= 256 ? 256 : 512;
+};
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 struct Map {
     int tab, red, sc, b, raw, total;
 };
-__host__ __device__ inline Map make_map(int ncol, int slice_tiles, int slice_groups) {
+__host__ __device__ inline Map make_map(int ncol, int slice_tiles, int slice_groups, int ns, int stage_bytes) {
     Map m;
-    // [0, 512): 32 mbarriers and the tensor-memory slot
+    // [0, 512): mbarriers and the tensor-memory slot
     m.tab = 512;                                       // float2 (e, sum xi) [slice_groups][8]
-    m.red = m.tab + slice_groups * 64;                 // f32 [128][8]
-    m.sc = m.red + ROWS * 8 * 4;                       // [SQ][128] cells of 16 bytes (scale quad, bias quad)
-    m.b = (m.sc + SQ * ROWS * 16 + 1023) / 1024 * 1024;   // limbs: slice_tiles tiles of ncol rows x 128 bytes
-    m.raw = m.b + slice_tiles * ncol * 128;            // NS stages, 1024-byte aligned
-    m.total = m.raw + NS * STAGE_BYTES;
+    m.red = m.tab + slice_groups * 64;                 // f32 [2][128][8]
+    m.sc = m.red + 2 * ROWS * 8 * 4;                   // [2 sets][SQ][128] cells of 16 bytes (scale quad, bias quad)
+    m.b = (m.sc + 2 * SQ * ROWS * 16 + 1023) / 1024 * 1024;   // limbs: slice_tiles tiles of ncol rows x 128 bytes
+    m.raw = m.b + slice_tiles * ncol * 128;            // ns stages, 1024-byte aligned
+    m.total = m.raw + ns * stage_bytes;
     return m;
 }
 
-// inverse of perm(): position of code j inside its 16-byte unit
-template <int BITS> __host__ __device__ constexpr int inv_perm(int j) {
-    if (BITS == 2) return (j >> 2) + 4 * (j & 3);
-    if (BITS == 4) return (j & 8) + 4 * (j & 1) + ((j >> 1) & 3);
-    return j;
-}
-
 template <typename AT, int BITS, int GS, int NCOL>
-__global__ void __launch_bounds__(threads_for(BITS), 2)
+__global__ void __launch_bounds__(threads_for(BITS), BITS == 8 ? 2 : 1)
 qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
     using A = Act<AT>;
+    using RG = Ring<BITS, GS, NCOL>;
     constexpr int THREADS = threads_for(BITS);
-    constexpr int PREP = W_MMA2 * 32;          // threads that prepare the activations (warps 0..5)
-    constexpr int PREP_SYNC = W_UNP * 32;      // ... and the second MMA warp waits for them
+    constexpr int PREP = W_UNP * 32;           // warps 0..10 prepare the activations
     constexpr int TILE_B = TK * BITS / 8;      // packed bytes of one row and tile (32, 64 or 128)
-    constexpr int TPS = 128 / TILE_B;          // tiles per stage (4, 2 or 1)
-    constexpr int GPT = TK / GS;               // groups per tile (2 or 1)
+    constexpr int TPS = BITS == 8 ? 2 : 128 / TILE_B;   // tiles per stage (4, 2 or 2)
+    constexpr int STAGE_BYTES = RG::STAGE_BYTES;
+    constexpr int GPT = RG::GPT;
     constexpr int KPG = GS / 32;               // MMAs per group (2 or 4)
     constexpr int TPQ = 4 * GS / TK;           // tiles per sidecar quad (2 or 4)
-    constexpr int DW = GPT * NCOL;             // accumulator columns of one tile
-    constexpr int DC = BITS == 8 ? TMEM_COLS : D_COLS;   // 8-bit codes need no A tiles in tensor memory
-    constexpr int R = (DC / DW) < 4 ? (DC / DW) : 4;   // ring of tiles: A slot and accumulator of tile t = t % R
-    constexpr int EB = R >= 4 ? 2 : 1;         // tiles per epilogue batch
+    constexpr int DW = RG::DW, RP = RG::RP;
     constexpr int MMAX = NCOL == 16 ? 5 : 8;
-    static_assert(R >= NS || BITS != 8, "the producer of 8-bit stages relies on R >= NS");
-    static_assert(TPQ % EB == 0, "an epilogue batch stays inside one sidecar quad");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int S = a.ksplit;
+    const int S = a.ksplit, NS = a.nbuf;
     const int rb = blockIdx.x / S;
     const int cr = blockIdx.x - rb * S;                  // rank in the cluster (cluster shape (S,1,1))
     const int M = a.M, G = a.G;
@@ -143,19 +138,19 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
     const int q_begin = (int)((int64_t)cr * nquads / S), q_end = (int)((int64_t)(cr + 1) * nquads / S);
     const int sq_max = (nquads + S - 1) / S;             // longest slice of the cluster, quads
     const int nq = q_end - q_begin;                      // this CTA's slice
-    const int ntiles = nq * TPQ;
+    const int ntiles = nq * TPQ;                         // even
     const int nstages = (ntiles + TPS - 1) / TPS;
     const int t_begin = q_begin * TPQ;                   // first tile of the slice (global tile index)
     const int k_begin = t_begin * TK;
     const int64_t n0 = (int64_t)rb * ROWS;
 
-    const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4);
-    uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);
-    uint64_t* raw_empty = raw_full + NS;
-    uint64_t* a_full = raw_empty + NS;                   // [R]
-    uint64_t* d_full = a_full + 4;                       // [R]
-    uint64_t* d_empty = d_full + 4;                      // [R]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 4);
+    const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4, NS, STAGE_BYTES);
+    uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);      // [MAXNS]
+    uint64_t* raw_empty = raw_full + MAXNS;                      // [MAXNS]
+    uint64_t* a_full = raw_empty + MAXNS;                        // [8]
+    uint64_t* d_full = a_full + 8;                               // [8]
+    uint64_t* d_empty = d_full + 8;                              // [8]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 8);
     float2* tab = reinterpret_cast<float2*>(smem + mp.tab);
     float* red = reinterpret_cast<float*>(smem + mp.red);
     uint8_t* sc_ring = smem + mp.sc;
@@ -173,20 +168,25 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
     auto produce = [&](int st) {       // one lane: stage st of the slice
         const int s = st % NS;
         mbar_expect_tx(raw_full + s, STAGE_BYTES);
-        tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, &wmap, t_begin * TILE_B + st * 128, (int)n0, raw_full + s);
+        if constexpr (BITS == 8) {
+            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, &wmap, (t_begin + 2 * st) * 128, (int)n0, raw_full + s);
+            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES + BOX_BYTES, &wmap, (t_begin + 2 * st + 1) * 128, (int)n0, raw_full + s);
+        } else {
+            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, &wmap, t_begin * TILE_B + st * 128, (int)n0, raw_full + s);
+        }
     };
     if (tid == 0) {
-        for (int i = 0; i < NS; ++i) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 8); }
-        for (int i = 0; i < 4; ++i) { mbar_init(a_full + i, 4); mbar_init(d_full + i, 1); mbar_init(d_empty + i, 4); }
+        for (int i = 0; i < MAXNS; ++i) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, BITS == 8 ? 1 : 8); }
+        for (int i = 0; i < 8; ++i) { mbar_init(a_full + i, 8); mbar_init(d_full + i, 1); mbar_init(d_empty + i, 4); }
         mbar_fence_init();
         for (int st = 0; st < NS && st < nstages; ++st) produce(st);
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == W_MMA) tmem_alloc(tmem_slot, RG::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + (BITS == 8 ? 0 : A_COLS);
+    const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + RG::A_COLS;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // tensor-memory lane quarter = warp id mod 4
     bool ok = true;
     JQ_PROF_ADD(tid == 0, 0, t_start);                 // 0: set-up
@@ -195,6 +195,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
 #pragma unroll
     for (int m = 0; m < MMAX; ++m) acc[m] = 0.f;
     const int row = (warp & 3) * 32 + lane;              // epilogue and unpacker threads: own weight row
+    const int eset = (warp - W_EPI) >> 2;                // epilogue set (0 or 1) of warps 3..10
 
     if (warp >= W_UNP) {
         if constexpr (BITS != 8) {
@@ -208,7 +209,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
             for (int st = 0; st < nstages && ok; ++st) {
                 const int s = st % NS;
                 JQ_PROF_DECL(t0);
-                ok = __all_sync(0xFFFFFFFFu, mbar_wait(raw_full + s, (uint32_t)(st / NS) & 1u, POLLS));
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(raw_full + s, (uint32_t)(st / NS) & 1u, POLLS));
                 JQ_PROF_ADD(warp == W_UNP && lane == 0, 9, t0);       // 9: unpacker waits for packed codes
                 if (!ok) break;
                 const uint8_t* rowp = sRaw + (size_t)s * STAGE_BYTES + row_off;
@@ -217,7 +218,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
                     const int tt = 2 * t2 + half;
                     const int t = st * TPS + tt;
                     if (t >= ntiles) break;
-                    const int ri = t % R;
+                    const int pr = t >> 1, pi = pr % RP;                 // pair of tiles and its ring slot
                     uint32_t v[32];
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
@@ -238,19 +239,17 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
                         }
                     }
                     JQ_PROF_DECL(t1);
-                    if (t >= R) {      // the MMAs of tile t - R have read this A slot
-                        ok = __all_sync(0xFFFFFFFFu, mbar_wait(d_full + ri, (uint32_t)((t / R) - 1) & 1u, POLLS));
+                    if (pr >= RP) {    // the MMAs of pair pr - RP have read this A slot
+                        ok = __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(d_full + pi, (uint32_t)((pr / RP) - 1) & 1u, POLLS));
                         if (!ok) break;
                         tc_fence_after();
                     }
                     JQ_PROF_ADD(warp == W_UNP && lane == 0, 10, t1);  // 10: unpacker waits for a free A tile
-                    JQ_PROF_DECL(t_st);
-                    tmem_st32(tmem_a + lane_base + (uint32_t)(ri * 32), v);
+                    tmem_st32(tmem_a + lane_base + (uint32_t)((2 * pi + (t & 1)) * 32), v);
                     tmem_st_wait();
-                    JQ_PROF_ADD(warp == W_UNP && lane == 0, 11, t_st);  // 11: tensor-memory store
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(a_full + ri);
+                    if (lane == 0) mbar_arrive(a_full + pi);
                 }
                 __syncwarp();                                         // every lane has read its row of the stage
                 if (lane == 0) mbar_arrive(raw_empty + s);
@@ -258,22 +257,28 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
             JQ_PROF_ADD(warp == W_UNP && lane == 0, 12, t_roles);     // 12: unpacker loop, total
         }
     } else {
-        // ---- warps 0..5: activations of the slice -> limbs (B operand) + per-group (e, sum xi) ----------------
+        // ---- warps 0..10: activations of the slice -> limbs (B operand) + per-group (e, sum xi) ---------------
+        // epilogue threads: i-th pair of tiles of set `eset` is pair 2i + eset of the slice; its sidecars are
+        // quad 2i + eset (groups of 64: one pair per quad) or quad i (groups of 128: two pairs per quad)
+        const int npairs = ntiles / 2;
+        const int my_pairs = warp >= W_EPI ? (npairs - eset + 1) / 2 : 0;
         const int64_t n_row = min(n0 + row, a.N - 1);
-        auto issue_sc = [&](int j) {                     // epilogue threads: sidecar quad j of the own row
-            if (j < nq) {
-                uint8_t* cell = sc_ring + ((size_t)(j % SQ) * ROWS + row) * 16;
-                const int64_t off = n_row * G + (int64_t)(q_begin + j) * 4;
+        uint8_t* my_sc = sc_ring + (size_t)(eset & 1) * SQ * ROWS * 16;
+        auto issue_sc = [&](int i) {
+            if (i < my_pairs) {
+                uint8_t* cell = my_sc + ((size_t)(i % SQ) * ROWS + row) * 16;
+                const int quad = GS == 64 ? 2 * i + eset : i;
+                const int64_t off = n_row * G + (int64_t)(q_begin + quad) * 4;
                 cp_async8(cell, sc16 + off);
                 cp_async8(cell + 8, bi16 + off);
             }
             cp_async_commit();
         };
-        if (warp >= W_EPI && warp < W_MMA2) {
+        if (warp >= W_EPI) {
 #pragma unroll
             for (int i = 0; i < SQ - 1; ++i) issue_sc(i);
         }
-        if (warp < W_MMA2) {   // rows of B that carry no limb are zero (independent of the activations)
+        {   // rows of B that carry no limb are zero (independent of the activations)
             const int zq = (NCOL - 3 * M) * 8;               // 16-byte chunks per tile, fewer than PREP
             if (tid < zq) {
                 const int n = 3 * M + (tid >> 3), c = tid & 7;
@@ -288,10 +293,10 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
             // eight consecutive activations per lane; GS/8 adjacent lanes form a quantization group.
             // The loads of all PF rounds are issued together, so their latency is paid once.
             constexpr int LPG = GS / 8;
-            constexpr int PF = 3;
+            constexpr int PF = 2;
             const int per_row = ntiles * (TK / 8);
             const int items = M * per_row;                   // a multiple of 32
-            for (int base0 = warp * 32; base0 < items && warp < W_MMA2; base0 += PREP * PF) {
+            for (int base0 = warp * 32; base0 < items; base0 += PREP * PF) {
                 uint4 rawv[PF];
 #pragma unroll
                 for (int i = 0; i < PF; ++i) {
@@ -341,16 +346,18 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
                         const int r1 = (xi[j] + 128) >> 8;
                         l0[j] = xi[j] & 255; l1[j] = r1 & 255; l2[j] = ((r1 + 128) >> 8) & 255;
                     }
+                    // The order of the 16 codes inside a 16-byte unit of A is whatever is cheapest to unpack:
+                    // 8-bit: natural; 4-bit: per 8 codes the even ones, then the odd ones; 2-bit: code j of
+                    // the unit is byte j >> 2 of word j & 3.  The limbs follow the same order.
                     auto put = [&](int n, const int (&b)[8]) {
-                        // element j of this half is code 8*hf + j of the unit; position inv_perm(8*hf + j)
                         uint8_t* dst = tile + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4);
-                        if constexpr (BITS == 8) {           // positions 8*hf .. 8*hf+7: two words
+                        if constexpr (BITS == 8) {
                             *reinterpret_cast<uint2*>(dst + 8 * hf) =
                                 make_uint2(b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24, b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24);
-                        } else if constexpr (BITS == 4) {    // even codes, then odd codes, in the same 8 bytes
+                        } else if constexpr (BITS == 4) {
                             *reinterpret_cast<uint2*>(dst + 8 * hf) =
                                 make_uint2(b[0] | b[2] << 8 | b[4] << 16 | b[6] << 24, b[1] | b[3] << 8 | b[5] << 16 | b[7] << 24);
-                        } else {                             // code j -> byte (j >> 2) of word (j & 3): bytes 2*hf, 2*hf+1 of all words
+                        } else {
                             uint16_t* d16 = reinterpret_cast<uint16_t*>(dst) + hf;
                             d16[0] = (uint16_t)(b[0] | b[4] << 8);
                             d16[2] = (uint16_t)(b[1] | b[5] << 8);
@@ -365,9 +372,8 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
                 }
             }
         }
-        JQ_PROF_ADD(tid == 0, 17, t_prep);                 // 17: own limbs written
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes of B -> tensor-core reads
-        asm volatile("bar.sync 1, %0;" ::"n"(PREP_SYNC) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(PREP) : "memory");
         JQ_PROF_ADD(tid == 0, 1, t_prep);                  // 1: activation limbs
         JQ_PROF_DECL(t_roles);
 
@@ -376,131 +382,145 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
             if (lane == 0) {
                 for (int st = NS; st < nstages; ++st) {
                     JQ_PROF_DECL(t0);
-                    if constexpr (BITS == 8)    // stage = tile: free once the MMAs of tile st - NS have completed
-                        ok = mbar_wait(d_full + (st - NS) % R, (uint32_t)((st - NS) / R) & 1u, POLLS);
-                    else
-                        ok = mbar_wait(raw_empty + st % NS, (uint32_t)((st / NS) - 1) & 1u, POLLS);
+                    ok = mbar_wait_relaxed(raw_empty + st % NS, (uint32_t)((st / NS) - 1) & 1u, POLLS);
                     JQ_PROF_ADD(true, 2, t0);                  // 2: producer waits for a free stage
                     if (!ok) break;
                     produce(st);
                 }
-                JQ_PROF_ADD(true, 13, t_roles);                // 13: producer role, total
             }
-        } else if (warp == 1 || warp == W_MMA2) {
-            // ---------------- MMA issuers: warp 1 takes the even tiles, warp 6 the odd ones ----------------
-            // (issuing one tcgen05.mma costs its thread ~50 cycles, more than the tensor core needs for it)
+        } else if (warp < W_EPI) {
+            // ---------------- MMA issuers: warp 1 takes the even pairs of tiles, warp 2 the odd ones ----------------
             if (lane == 0) {
                 constexpr uint32_t idesc = umma_idesc_i8(NCOL);
-                const uint32_t b_addr = smem_u32(sB), raw_addr = smem_u32(sRaw);
-                for (int t = (warp == 1 ? 0 : 1); t < ntiles && ok; t += 2) {
-                    const int ri = t % R, s = t % NS;
+                const uint32_t b_lo0 = umma_desc_sw128_lo(smem_u32(sB)), raw_lo0 = umma_desc_sw128_lo(smem_u32(sRaw));
+                const int npairs_ = ntiles / 2;
+                for (int pr = warp - W_MMA; pr < npairs_ && ok; pr += 2) {
+                    const int pi = pr % RP, s = pr % NS;
                     JQ_PROF_DECL(t0);
-                    if constexpr (BITS == 8) ok = mbar_wait(raw_full + s, (uint32_t)(t / NS) & 1u, POLLS);
-                    else ok = mbar_wait(a_full + ri, (uint32_t)(t / R) & 1u, POLLS);
-                    JQ_PROF_ADD(warp == 1, 3, t0);             // 3: MMA waits for its A operand
+                    if constexpr (BITS == 8) ok = mbar_wait(raw_full + s, (uint32_t)(pr / NS) & 1u, POLLS);
+                    else ok = mbar_wait(a_full + pi, (uint32_t)(pr / RP) & 1u, POLLS);
+                    JQ_PROF_ADD(warp == W_MMA, 3, t0);         // 3: MMA waits for its A operand
                     JQ_PROF_DECL(t1);
-                    if (ok && t >= R) ok = mbar_wait(d_empty + ri, (uint32_t)((t / R) - 1) & 1u, POLLS);
-                    JQ_PROF_ADD(warp == 1, 4, t1);             // 4: MMA waits for a free accumulator
+                    if (ok && pr >= RP) ok = mbar_wait(d_empty + pi, (uint32_t)((pr / RP) - 1) & 1u, POLLS);
+                    JQ_PROF_ADD(warp == W_MMA, 4, t1);         // 4: MMA waits for a free accumulator
                     if (!ok) break;
                     tc_fence_after();
+                    // descriptors: one 32-bit add per operand and MMA (the issuing thread is the scarce resource)
+                    const uint32_t d0 = tmem_d + (uint32_t)(2 * pi * DW);
+                    const uint32_t b_lo = b_lo0 + (uint32_t)(2 * pr) * (uint32_t)(NCOL * 128 >> 4);
+                    const uint32_t a_lo = raw_lo0 + (uint32_t)s * (uint32_t)(STAGE_BYTES >> 4);
+                    const uint32_t a_tm = tmem_a + (uint32_t)(2 * pi * 32);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint32_t dcol = tmem_d + (uint32_t)(ri * DW + (kk / KPG) * NCOL);
-                        const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)t * (NCOL * 128) + kk * 32);
-                        if constexpr (BITS == 8)
-                            umma_i8_ss(dcol, umma_desc_sw128(raw_addr + (uint32_t)s * STAGE_BYTES + kk * 32), bdesc, idesc,
-                                       (kk % KPG) ? 1u : 0u);
-                        else
-                            umma_i8_ts(dcol, tmem_a + (uint32_t)(ri * 32 + kk * 8), bdesc, idesc, (kk % KPG) ? 1u : 0u);
+                    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint32_t dcol = d0 + (uint32_t)(j * DW + (kk / KPG) * NCOL);
+                            const uint64_t bdesc = umma_desc_join(b_lo + (uint32_t)((j * NCOL * 128 + kk * 32) >> 4));
+                            if constexpr (BITS == 8)
+                                umma_i8_ss(dcol, umma_desc_join(a_lo + (uint32_t)((j * BOX_BYTES + kk * 32) >> 4)), bdesc, idesc,
+                                           (kk % KPG) ? 1u : 0u);
+                            else
+                                umma_i8_ts(dcol, a_tm + (uint32_t)(j * 32 + kk * 8), bdesc, idesc, (kk % KPG) ? 1u : 0u);
+                        }
                     }
-                    umma_commit(d_full + ri);      // also what frees the tile's A operand (stage or tensor-memory slot)
+                    umma_commit(d_full + pi);      // sums ready; for narrow codes also: the A slots are free again
+                    if constexpr (BITS == 8) { if (pr + NS < npairs_) umma_commit(raw_empty + s); }   // the stage is free again
                 }
-                JQ_PROF_ADD(warp == 1, 5, t_roles);            // 5: MMA loop, total
+                JQ_PROF_ADD(warp == W_MMA, 5, t_roles);        // 5: MMA loop, total
             }
         } else {
-            // ---------------- epilogue: one weight row per thread, EB tiles per step ----------------
-            for (int j = 0; j < nq && ok; ++j) {
+            // ---------------- epilogue: one weight row per thread, two tiles per step ----------------
+            for (int i = 0; i < my_pairs && ok; ++i) {
                 JQ_PROF_DECL(t0);
-                issue_sc(j + SQ - 1);
-                cp_async_wait<SQ - 1>();                              // quad j of this row has landed
+                issue_sc(i + SQ - 1);
+                cp_async_wait<SQ - 1>();                              // sidecars of this pair have landed
                 JQ_PROF_ADD(warp == W_EPI && lane == 0, 6, t0);       // 6: epilogue waits for sidecars
-                const uint4 cell = *reinterpret_cast<const uint4*>(sc_ring + ((size_t)(j % SQ) * ROWS + row) * 16);
+                const uint4 cell = *reinterpret_cast<const uint4*>(my_sc + ((size_t)(i % SQ) * ROWS + row) * 16);
                 const uint32_t sw[2] = {cell.x, cell.y}, bw[2] = {cell.z, cell.w};
+                const int pair = 2 * i + eset;
+                const int t0i = 2 * pair;                             // first tile of the pair
+                const int g0 = t0i * GPT;                             // its first group (of the slice)
+                const int gq0 = GS == 64 ? 0 : 2 * (pair & 1);        // ... and that group's place in the sidecar quad
+                JQ_PROF_DECL(t1);
+                const int pi = pair % RP;
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(d_full + pi, (uint32_t)(pair / RP) & 1u, POLLS));
+                JQ_PROF_ADD(warp == W_EPI && lane == 0, 7, t1);       // 7: epilogue waits for sums
+                if (!ok) break;
+                tc_fence_after();
+                if (NCOL == 16 && M == 1) {
+                    // three columns per group: load every group of the pair, then one wait
+                    uint32_t d4[2 * GPT][4];
 #pragma unroll
-                for (int tb = 0; tb < TPQ / EB; ++tb) {
-                    const int t0i = j * TPQ + tb * EB;                // first tile of the batch
-                    JQ_PROF_DECL(t1);
+                    for (int j = 0; j < 2; ++j)
 #pragma unroll
-                    for (int i = 0; i < EB; ++i)
-                        if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(d_full + (t0i + i) % R, (uint32_t)((t0i + i) / R) & 1u, POLLS));
-                    JQ_PROF_ADD(warp == W_EPI && lane == 0, 7, t1);   // 7: epilogue waits for sums
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (NCOL == 16 && M == 1) {
-                        // three columns per group: load every group of the batch, then one wait
-                        uint32_t d4[EB * GPT][4];
+                        for (int gi = 0; gi < GPT; ++gi)
+                            tmem_ld4_nowait(tmem_d + lane_base + (uint32_t)((2 * pi + j) * DW + gi * NCOL), d4[j * GPT + gi]);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(d_empty + pi);
 #pragma unroll
-                        for (int i = 0; i < EB; ++i)
+                    for (int j = 0; j < 2 * GPT; ++j) {
+                        const int gq = gq0 + j;                       // group of the quad
+                        const float s = (gq & 1) ? A::hi_f32(sw[gq >> 1]) : A::lo_f32(sw[gq >> 1]);
+                        const float bs = (gq & 1) ? A::hi_f32(bw[gq >> 1]) : A::lo_f32(bw[gq >> 1]);
+                        const float2 es = tab[(g0 + j) * 8];
+                        const float f = fmaf((float)(int)d4[j][2], 65536.f, fmaf((float)(int)d4[j][1], 256.f, (float)(int)d4[j][0]));
+                        acc[0] = fmaf(es.x, fmaf(s, f, bs * es.y), acc[0]);
+                    }
+                } else {
 #pragma unroll
-                            for (int gi = 0; gi < GPT; ++gi)
-                                tmem_ld4_nowait(tmem_d + lane_base + (uint32_t)(((t0i + i) % R) * DW + gi * NCOL), d4[i * GPT + gi]);
-                        tmem_ld_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane < EB) mbar_arrive(d_empty + (t0i + lane) % R);
+                    for (int j = 0; j < 2; ++j) {
 #pragma unroll
-                        for (int i = 0; i < EB * GPT; ++i) {
-                            const int gq = tb * EB * GPT + i;         // group of the quad
+                        for (int gi = 0; gi < GPT; ++gi) {
+                            uint32_t dv[NCOL];
+                            const uint32_t dcol = tmem_d + lane_base + (uint32_t)((2 * pi + j) * DW + gi * NCOL);
+                            if constexpr (NCOL == 16) tmem_ld16(dcol, dv); else tmem_ld32(dcol, dv);
+                            const int gq = gq0 + j * GPT + gi;
                             const float s = (gq & 1) ? A::hi_f32(sw[gq >> 1]) : A::lo_f32(sw[gq >> 1]);
                             const float bs = (gq & 1) ? A::hi_f32(bw[gq >> 1]) : A::lo_f32(bw[gq >> 1]);
-                            const float2 es = tab[(j * 4 + gq) * 8];
-                            const float f = fmaf((float)(int)d4[i][2], 65536.f, fmaf((float)(int)d4[i][1], 256.f, (float)(int)d4[i][0]));
-                            acc[0] = fmaf(es.x, fmaf(s, f, bs * es.y), acc[0]);
-                        }
-                    } else {
 #pragma unroll
-                        for (int i = 0; i < EB; ++i) {
-#pragma unroll
-                            for (int gi = 0; gi < GPT; ++gi) {
-                                uint32_t dv[NCOL];
-                                const uint32_t dcol = tmem_d + lane_base + (uint32_t)(((t0i + i) % R) * DW + gi * NCOL);
-                                if constexpr (NCOL == 16) tmem_ld16(dcol, dv); else tmem_ld32(dcol, dv);
-                                const int gq = (tb * EB + i) * GPT + gi;
-                                const float s = (gq & 1) ? A::hi_f32(sw[gq >> 1]) : A::lo_f32(sw[gq >> 1]);
-                                const float bs = (gq & 1) ? A::hi_f32(bw[gq >> 1]) : A::lo_f32(bw[gq >> 1]);
-#pragma unroll
-                                for (int m = 0; m < MMAX; ++m) {
-                                    if (m < M) {
-                                        const float2 es = tab[(j * 4 + gq) * 8 + m];
-                                        const float f = fmaf((float)(int)dv[3 * m + 2], 65536.f,
-                                                             fmaf((float)(int)dv[3 * m + 1], 256.f, (float)(int)dv[3 * m]));
-                                        acc[m] = fmaf(es.x, fmaf(s, f, bs * es.y), acc[m]);
-                                    }
+                            for (int m = 0; m < MMAX; ++m) {
+                                if (m < M) {
+                                    const float2 es = tab[(g0 + j * GPT + gi) * 8 + m];
+                                    const float f = fmaf((float)(int)dv[3 * m + 2], 65536.f,
+                                                         fmaf((float)(int)dv[3 * m + 1], 256.f, (float)(int)dv[3 * m]));
+                                    acc[m] = fmaf(es.x, fmaf(s, f, bs * es.y), acc[m]);
                                 }
                             }
                         }
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane < EB) mbar_arrive(d_empty + (t0i + lane) % R);
                     }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(d_empty + pi);
                 }
             }
             cp_async_wait<0>();
             JQ_PROF_ADD(warp == W_EPI && lane == 0, 8, t_roles);      // 8: epilogue loop, total
+            // the two sets add their partial sums: set 1 -> shared memory -> set 0
+            if (eset == 1) {
+#pragma unroll
+                for (int m = 0; m < MMAX; ++m) red[(ROWS + row) * 8 + m] = acc[m];
+            }
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            if (eset == 0) {
+#pragma unroll
+                for (int m = 0; m < MMAX; ++m) acc[m] += red[(ROWS + row) * 8 + m];
+            }
         }
     }
     if (!ok) atomicExch(a.status, 1);
 
     // ---- results: direct store, or partial sums to rank 0 through distributed shared memory -----------------
-    const bool epi = warp >= W_EPI && warp < W_MMA2;
+    const bool owner = warp >= W_EPI && warp < W_EPI + 4;             // set 0 holds the CTA's sums
     if (S == 1) {
-        if (epi && n0 + row < a.N) {
+        if (owner && n0 + row < a.N) {
 #pragma unroll
             for (int m = 0; m < MMAX; ++m)
                 if (m < M) y16[(int64_t)m * a.ldy + n0 + row] = A::from_f32(acc[m]);
         }
     } else {
-        if (epi) {
+        if (owner) {
 #pragma unroll
             for (int m = 0; m < MMAX; ++m) red[row * 8 + m] = acc[m];
         }
@@ -517,9 +537,9 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == W_MMA) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc(tmem_base, RG::TMEM_COLS);
     }
     JQ_PROF_ADD(tid == 0, 14, t_start);                           // 14: whole CTA
 #ifdef JQ_TC_PROFILE
@@ -533,11 +553,11 @@ static int env_int(const char* name, int dflt) {
 }
 
 template <typename AT, int BITS, int GS, int NCOL>
-static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, cudaStream_t st, bool* launched) {
+static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, int ns, cudaStream_t st, bool* launched) {
     constexpr int TPQ = 4 * GS / TK;
     const int nquads = a.G / 4;
     const int sq_max = (nquads + S - 1) / S;
-    const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4);
+    const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4, ns, Ring<BITS, GS, NCOL>::STAGE_BYTES);
     const int smem = mp.total + 1024;
     if (smem > 227 * 1024) return JQ_OK;
     static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
@@ -549,6 +569,7 @@ static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, cudaStream_t s
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     a.ksplit = S;
+    a.nbuf = ns;
     a.status = status_word();
     JQ_REQUIRE(a.status != nullptr, JQ_ECUDA, "could not locate the device status word");
     const unsigned row_blocks = (unsigned)((a.N + ROWS - 1) / ROWS);
@@ -578,34 +599,44 @@ static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, cudaStream_t s
     return JQ_OK;
 }
 
-// Cluster size.  The grid is row_blocks * S CTAs, at most two per SM.  The launch is HBM-bound as a
-// whole, so an SM may carry up to ~1.5x its fair share of tiles before it becomes the critical path;
-// every wave of CTAs adds a fixed start-up (barriers, tensor-memory allocation, first-byte latency)
-// counted in tiles.  The smallest S with the lowest modelled time wins.
+// Cluster size and ring depth.
+//   * Few row blocks (at most one CTA per SM): the largest S <= 8 that still gives every SM at most one
+//     CTA; the ring then holds the CTA's whole K slice where it fits, so that all of the matrix is in
+//     flight before the activations arrive (the launch may overlap its predecessor).
+//   * Many row blocks: S grows only until the limbs of a slice fit beside a deep ring; CTAs run in waves.
 template <typename AT, int BITS, int GS, int NCOL>
 static int launch_shape(const CUtensorMap& wmap, const GemvArgs& a, cudaStream_t st, bool* launched) {
     constexpr int TPQ = 4 * GS / TK;
+    using RG = Ring<BITS, GS, NCOL>;
+    constexpr int TPS = BITS == 8 ? 2 : 8 / BITS;          // tiles per stage
     const int sms = sm_count();
     const int nquads = a.G / 4;
     const int64_t row_blocks = (a.N + ROWS - 1) / ROWS;
-    const double startup = (double)env_int("JANGQ_TC_STARTUP", 6);
-    const double fair = (double)row_blocks * nquads * TPQ / sms;
-    int best = 0;
-    double best_cost = 0;
-    for (int S = 1; S <= 8 && S <= nquads; ++S) {
-        const int sq_max = (nquads + S - 1) / S;
-        const Map mp = make_map(NCOL, sq_max * TPQ, sq_max * 4);
-        if (mp.total + 1024 > 227 * 1024) continue;
-        const int per_sm = (mp.total + 2048 <= 113 * 1024) ? 2 : 1;
-        const int64_t ctas = row_blocks * S;
-        const int64_t waves = (ctas + (int64_t)per_sm * sms - 1) / ((int64_t)per_sm * sms);
-        const double busiest = (double)((ctas + sms - 1) / sms) * sq_max * TPQ / 1.5;
-        const double cost = (busiest > fair ? busiest : fair) + startup * (double)waves;
-        if (best == 0 || cost < best_cost - 1e-9) { best = S; best_cost = cost; }
+    int S = 1;
+    if (row_blocks <= sms) {
+        while (S < 8 && S < nquads && row_blocks * (S + 1) <= sms) ++S;
     }
-    best = env_int("JANGQ_TC_S", best);
-    if (best < 1 || best > 8 || best > nquads) return JQ_OK;
-    return launch_cfg<AT, BITS, GS, NCOL>(wmap, a, best, st, launched);
+    auto fit_ns = [&](int s_) {
+        const int sq_max = (nquads + s_ - 1) / s_;
+        const int want = (sq_max * TPQ + TPS - 1) / TPS;      // stages of the longest slice
+        int ns = want < RG::MAX_STAGES ? want : RG::MAX_STAGES;
+        if (BITS == 8 && (ns & 1)) ++ns;                      // see below: even rings only
+        if (ns < 2) ns = 2;
+        while (ns > 2 && make_map(NCOL, sq_max * TPQ, sq_max * 4, ns, RG::STAGE_BYTES).total + 1024 > 227 * 1024) --ns;
+        // 8-bit codes: a stage holds one pair of tiles and the two MMA warps take alternate pairs.  With an
+        // even ring every stage barrier is waited on by one warp only, phase after phase; with an odd ring a
+        // warp that runs ahead would test a parity two phases away and read a stage that is still in flight.
+        if (BITS == 8 && (ns & 1)) --ns;
+        return ns;
+    };
+    // the limbs of a long slice can crowd out the ring: split K further while fewer than 4 stages fit
+    while (S < 8 && S < nquads && fit_ns(S) * RG::STAGE_BYTES < 4 * BOX_BYTES &&
+           make_map(NCOL, ((nquads + S - 1) / S) * TPQ, 0, 4, BOX_BYTES).total + 1024 > 227 * 1024) ++S;
+    S = env_int("JANGQ_TC_S", S);
+    if (S < 1 || S > 8 || S > nquads) return JQ_OK;
+    int ns = env_int("JANGQ_TC_NS", fit_ns(S));
+    if (ns < 2 || ns > RG::MAX_STAGES || (BITS == 8 && (ns & 1))) return JQ_OK;
+    return launch_cfg<AT, BITS, GS, NCOL>(wmap, a, S, ns, st, launched);
 }
 
 }  // namespace tcv

@@ -77,6 +77,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 EncodeTiledFn encode_tiled_fn();
 
+// The same descriptor split into its 32-bit halves: the high half is constant, the low half is
+// (address >> 4) | leading-byte-offset field, so moving inside a tile is one 32-bit add of (bytes >> 4).
+__device__ __forceinline__ uint32_t umma_desc_sw128_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
+constexpr uint32_t UMMA_DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint64_t umma_desc_join(uint32_t lo) { return ((uint64_t)UMMA_DESC_SW128_HI << 32) | lo; }
+
 // Integer MMA with the A operand in tensor memory: D[128 x N] (s32) (+)= A[128 x 32] (u8, one row
 // per TMEM lane, 8 columns of 4 bytes) . B[N x 32]^T (s8, K-major in shared memory).
 __device__ __forceinline__ void umma_i8_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
@@ -99,6 +105,25 @@ __device__ __forceinline__ void umma_i8_ss(uint32_t tmem_d, uint64_t adesc, uint
 // instruction descriptor of the calls above: D s32, A unsigned 8-bit, B signed 8-bit, both K-major, M = 128
 __host__ __device__ constexpr uint32_t umma_idesc_i8(int n) {
     return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+// Bounded wait that sleeps between polls: for warps whose wake-up latency matters less than the
+// issue slots a hot polling loop takes from the MMA-issuing warps of the same SM.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t max_polls) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < max_polls; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        __nanosleep(64);
+    }
+    return false;
 }
 
 // registers -> tensor memory: lane (base + threadIdx%32), 32 consecutive columns
