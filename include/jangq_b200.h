@@ -114,6 +114,11 @@ typedef struct JqGemvDesc {
 #define JQ_QGEMV_MAX_BATCH 8
 int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype,
                      int sidecar_dtype, jq_stream_t stream);
+/* The same with the flags of jq_qgemv_ex.  Consecutive entries that share x, ldx, K, bits and
+ * group_size (at most 4 at a time) go out as one launch whose grid is the concatenation of
+ * their row blocks; other entries are launched one after the other. */
+int jq_qgemv_batched_ex(const JqGemvDesc* descs, int count, int64_t M, int act_dtype,
+                        int sidecar_dtype, int flags, jq_stream_t stream);
 
 /* K3. Prefill-shaped quantized GEMM: the same mx.quantized_matmul call with many
  * activation rows (MLX switches from qmv to its tiled qmm there; the reference's only

@@ -51,6 +51,7 @@ SIGNATURES = {
     "jq_qgemv_ex": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _i32, _p]),
     "jq_qgemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_batched": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _p]),
+    "jq_qgemv_batched_ex": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _i32, _p]),
     "jq_device_status": (C.c_int, []),
     "jq_moe_sort_max_tiles": (C.c_size_t, [_i64, _i32, _i32]),
     "jq_moe_sort": (C.c_int, [_p, _i64, _i32, _i32, _p, _p, _p, _i32, _p, _p, _p, _p]),

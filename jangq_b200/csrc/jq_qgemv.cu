@@ -22,7 +22,9 @@
 //     with X = sum of x over the group,   acc += (s*POST) * C + (b - OFFSET*s) * X ;
 //     X comes from a per-stage SIMT pre-pass when M <= 2 and from an extra MMA with
 //     an all-ones A operand otherwise;
-//   * the four warps' partial sums are added through shared memory.
+//   * the four warps' partial sums are added through shared memory;
+//   * a launch may cover several matrices that share x (GemvBatch): the grid is the concatenation of
+//     their row tiles.
 // The general fallback kernel (any alignment, group size 32, 5-bit, mixed dtypes)
 // is a plain one-warp-per-row SIMT loop with a shuffle reduction.
 #include <cstdlib>
@@ -58,7 +60,7 @@ template <int BITS, int GS, int MT> struct GemvGeom {
 
 template <typename AT, int BITS, int GS, int MT, int NW>
 __global__ void __launch_bounds__(NW * 32)
-qgemv_mma_kernel(const GemvArgs a) {
+qgemv_mma_kernel(const GemvArgs a, const GemvBatch bt) {
     using A = Act<AT>;
     using F = Fields<AT, BITS>;
     using Geo = GemvGeom<BITS, GS, MT>;
@@ -69,18 +71,22 @@ qgemv_mma_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
-    const int64_t n0 = (int64_t)blockIdx.x * ROWS;
-    const int rows_valid = (int)min((int64_t)ROWS, a.N - n0);
     const int K = (int)a.K, G = a.G, M = a.M, nbuf = a.nbuf;
     const int nst = (K + KT - 1) / KT;
     const int stage_bytes = Geo::stage_bytes(M);
     const int64_t rowbytes = a.K * BITS / 8;
     uint8_t* mybuf = smem + (size_t)warp * nbuf * stage_bytes;
     const uint16_t* xs16 = reinterpret_cast<const uint16_t*>(a.x);
-    const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(a.scales);
-    const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(a.biases);
-    const uint32_t* codes_g = a.codes;
-    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
+    // which matrix of the fused launch this block belongs to (gather mode: always the tables below)
+    int mi = 0, blk0 = 0;
+    while (mi + 1 < bt.count && (int)blockIdx.x >= bt.blk_end[mi]) { blk0 = bt.blk_end[mi]; ++mi; }
+    const int64_t N = bt.N[mi], ldy = bt.ldy[mi];
+    const int64_t n0 = (int64_t)((int)blockIdx.x - blk0) * ROWS;
+    const int rows_valid = (int)min((int64_t)ROWS, N - n0);
+    const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(bt.scales[mi]);
+    const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(bt.biases[mi]);
+    const uint32_t* codes_g = bt.codes[mi];
+    uint16_t* y16 = reinterpret_cast<uint16_t*>(bt.y[mi]);
     if (a.pair_expert) {
         const int p = blockIdx.y;
         const int e = a.pair_expert[p];
@@ -90,7 +96,7 @@ qgemv_mma_kernel(const GemvArgs a) {
         sc16 = reinterpret_cast<const uint16_t*>(a.scales_tab[e]);
         bi16 = reinterpret_cast<const uint16_t*>(a.biases_tab[e]);
         xs16 += (int64_t)(p / a.x_div) * a.ldx;
-        y16 += (int64_t)p * a.ldy;
+        y16 += (int64_t)p * ldy;
     }
 
     if (lane < 8)
@@ -145,7 +151,7 @@ qgemv_mma_kernel(const GemvArgs a) {
             sv[i] = make_uint2(0u, 0u);
             bv[i] = make_uint2(0u, 0u);
             if (pr < ROWS * NQ && grp < G) {
-                const int64_t off = min(n0 + row, a.N - 1) * G + grp;
+                const int64_t off = min(n0 + row, N - 1) * G + grp;
                 sv[i] = __ldg(reinterpret_cast<const uint2*>(sc16 + off));
                 bv[i] = __ldg(reinterpret_cast<const uint2*>(bi16 + off));
             }
@@ -270,7 +276,7 @@ qgemv_mma_kernel(const GemvArgs a) {
             for (int w = 0; w < NW; ++w) v += red[((w * MT + mt) * 4 + i) * 32 + lane];
             const int row = mt * 16 + g + ((i & 2) ? 8 : 0), m = 2 * tig + (i & 1);
             if (row < rows_valid && m < M)
-                y16[(int64_t)m * a.ldy + n0 + row] = A::from_f32(v);
+                y16[(int64_t)m * ldy + n0 + row] = A::from_f32(v);
         }
     }
 }
@@ -370,20 +376,18 @@ static bool force_simple() {
 }
 
 // JANGQ_GEMV_KERNEL selects the fast-path kernel: unset = per-width default, "tc" = tensor-memory
-// kernel wherever the shape fits it, "mma" = the warp-MMA kernel of this file, "row" = the
-// row-parallel cluster kernel.
-// A tuning and comparison knob.
+// kernel wherever the shape fits it, "mma" = the warp-MMA kernel of this file.  A tuning and
+// comparison knob.
 static int gemv_kernel_choice() {
     const char* e = getenv("JANGQ_GEMV_KERNEL");
     if (!e) return 0;
     if (e[0] == 'm') return 1;
-    if (e[0] == 'r') return 2;
-    if (e[0] == 't') return 3;      // tensor-memory kernel for every width it supports
+    if (e[0] == 't') return 3;
     return 0;
 }
 
 template <typename AT, int BITS, int GS, int MT, int NW>
-static int launch_mma_cfg(GemvArgs a, int pairs, int nbuf, cudaStream_t st, bool* launched) {
+static int launch_mma_cfg(GemvArgs a, GemvBatch bt, int pairs, int nbuf, cudaStream_t st, bool* launched) {
     using Geo = GemvGeom<BITS, GS, MT>;
     *launched = false;
     const int sb = Geo::stage_bytes(a.M);
@@ -398,9 +402,13 @@ static int launch_mma_cfg(GemvArgs a, int pairs, int nbuf, cudaStream_t st, bool
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    const unsigned grid = (unsigned)((a.N + 16 * MT - 1) / (16 * MT));
+    int64_t grid = 0;
+    for (int i = 0; i < bt.count; ++i) {
+        grid += (bt.N[i] + 16 * MT - 1) / (16 * MT);
+        bt.blk_end[i] = (int)grid;
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid, (unsigned)pairs);
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)pairs);
     cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -409,7 +417,7 @@ static int launch_mma_cfg(GemvArgs a, int pairs, int nbuf, cudaStream_t st, bool
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_mma_kernel<AT, BITS, GS, MT, NW>, a));
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_mma_kernel<AT, BITS, GS, MT, NW>, a, bt));
     *launched = true;
     return JQ_OK;
 }
@@ -423,9 +431,11 @@ static int launch_mma_cfg(GemvArgs a, int pairs, int nbuf, cudaStream_t st, bool
 //     each warp walks many stages in sequence (8 warps, very long rows).
 // The thresholds come from a sweep over the decode shapes of the BASELINE configurations.
 template <typename AT, int BITS, int GS>
-static int launch_mma(const GemvArgs& a, int pairs, cudaStream_t st, bool* launched) {
+static int launch_mma(const GemvArgs& a, const GemvBatch& bt, int pairs, cudaStream_t st, bool* launched) {
     const int sms = sm_count();
-    const int64_t tiles16 = (a.N + 15) / 16 * pairs;
+    int64_t tiles16 = 0;
+    for (int i = 0; i < bt.count; ++i) tiles16 += (bt.N[i] + 15) / 16;
+    tiles16 *= pairs;
     constexpr int KT = GemvGeom<BITS, GS, 1>::KT;
     const int nst = (int)((a.K + KT - 1) / KT);
     int mt = (tiles16 >= (int64_t)4 * sms && tiles16 < (int64_t)12 * sms) ? 2 : 1;
@@ -444,71 +454,112 @@ static int launch_mma(const GemvArgs& a, int pairs, cudaStream_t st, bool* launc
     if (const char* e = getenv("JANGQ_GEMV_NBUF")) {
         if (e[0] == '2' || e[0] == '3') nbuf = e[0] - '0';
     }
-    if (mt == 2) return launch_mma_cfg<AT, BITS, GS, 2, 4>(a, pairs, nbuf, st, launched);
-    if (nw == 8) return launch_mma_cfg<AT, BITS, GS, 1, 8>(a, pairs, nbuf, st, launched);
-    return launch_mma_cfg<AT, BITS, GS, 1, 4>(a, pairs, nbuf, st, launched);
+    if (mt == 2) return launch_mma_cfg<AT, BITS, GS, 2, 4>(a, bt, pairs, nbuf, st, launched);
+    if (nw == 8) return launch_mma_cfg<AT, BITS, GS, 1, 8>(a, bt, pairs, nbuf, st, launched);
+    return launch_mma_cfg<AT, BITS, GS, 1, 4>(a, bt, pairs, nbuf, st, launched);
+}
+
+static int launch_mma_any(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, int pairs,
+                          cudaStream_t st, bool* launched) {
+    int rc = JQ_OK;
+#define JQ_GEMV_CASE(B, GSZ)                                                                      \
+    if (bits == B && gs == GSZ) {                                                                 \
+        rc = (act_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, bt, pairs, st, launched) \
+                                    : launch_mma<__half, B, GSZ>(a, bt, pairs, st, launched);      \
+    }
+    JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(6, 64) JQ_GEMV_CASE(8, 64)
+    JQ_GEMV_CASE(2, 128) JQ_GEMV_CASE(3, 128) JQ_GEMV_CASE(4, 128) JQ_GEMV_CASE(6, 128) JQ_GEMV_CASE(8, 128)
+#undef JQ_GEMV_CASE
+    return rc;
+}
+
+// One or several matrices that share x: count entries of (codes, scales, biases, y, N, ldy).  Entries
+// that qualify for a fast kernel go out as ONE launch; the general kernel takes them one by one.
+struct GemvItems {
+    int count;
+    const uint32_t* codes[GEMV_MAX_FUSE];
+    const void* scales[GEMV_MAX_FUSE];
+    const void* biases[GEMV_MAX_FUSE];
+    void* y[GEMV_MAX_FUSE];
+    int64_t N[GEMV_MAX_FUSE], ldy[GEMV_MAX_FUSE];
+};
+
+int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, const GemvItems& it, int sidecar_dtype,
+                         int64_t K, int bits, int gs, int y_dtype, int flags, cudaStream_t st) {
+    JQ_REQUIRE(it.count >= 1 && it.count <= GEMV_MAX_FUSE, JQ_EINVAL, "bad item count %d", it.count);
+    JQ_REQUIRE(valid_dtype(x_dtype) && valid_dtype(sidecar_dtype) && valid_dtype(y_dtype), JQ_EINVAL, "bad dtype");
+    JQ_REQUIRE(M >= 0 && M <= JQ_QGEMV_MAX_M, JQ_EINVAL, "qgemv takes 0 <= M <= %d rows, got %lld", JQ_QGEMV_MAX_M,
+               (long long)M);
+    bool fast = !force_simple() && (gs == 64 || gs == 128) && x_dtype != JQ_F32 && sidecar_dtype == x_dtype &&
+                y_dtype == x_dtype && ((K * bits / 8) % 16 == 0) && aligned(x, 16) && (ldx % 8 == 0) &&
+                (gs > 0 && (K / gs) % 4 == 0) && bits != 5;
+    GemvItems live = {};      // entries with rows to compute
+    for (int i = 0; i < it.count; ++i) {
+        int rc = check_quant_shape(it.N[i], K, bits, gs);
+        if (rc != JQ_OK) return rc;
+        if (M == 0 || it.N[i] == 0) continue;
+        JQ_REQUIRE(K > 0, JQ_EINVAL, "K must be positive");
+        JQ_REQUIRE(x && it.codes[i] && it.scales[i] && it.biases[i] && it.y[i], JQ_EINVAL, "null pointer");
+        JQ_REQUIRE(ldx >= K && it.ldy[i] >= it.N[i], JQ_EINVAL, "leading dimension too small");
+        JQ_REQUIRE(it.N[i] < (1ll << 31) && K < (1ll << 31), JQ_EUNSUPPORTED, "dimension too large");
+        fast = fast && aligned(it.codes[i], 16) && aligned(it.scales[i], 8) && aligned(it.biases[i], 8);
+        const int j = live.count++;
+        live.codes[j] = it.codes[i]; live.scales[j] = it.scales[i]; live.biases[j] = it.biases[i];
+        live.y[j] = it.y[i]; live.N[j] = it.N[i]; live.ldy[j] = it.ldy[i];
+    }
+    if (live.count == 0) return JQ_OK;
+    const int kern = gemv_kernel_choice();
+    for (int64_t m0 = 0; m0 < M; m0 += 8) {
+        GemvArgs a = {};
+        a.x = (const char*)x + m0 * ldx * dtype_size(x_dtype);
+        a.K = K; a.ldx = ldx;
+        a.M = (int)((M - m0) < 8 ? (M - m0) : 8);
+        a.G = (int)(K / gs);
+        a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
+        a.x_div = 1; a.ksplit = 1;
+        GemvBatch bt = {};
+        bt.count = live.count;
+        for (int i = 0; i < live.count; ++i) {
+            bt.codes[i] = live.codes[i]; bt.scales[i] = live.scales[i]; bt.biases[i] = live.biases[i];
+            bt.y[i] = (char*)live.y[i] + m0 * live.ldy[i] * dtype_size(y_dtype);
+            bt.N[i] = live.N[i]; bt.ldy[i] = live.ldy[i];
+        }
+        a.codes = bt.codes[0]; a.scales = bt.scales[0]; a.biases = bt.biases[0]; a.y = bt.y[0];
+        a.N = bt.N[0]; a.ldy = bt.ldy[0];
+        bool launched = false;
+        int rc = JQ_OK;
+        // measured on B200: the tensor-memory kernel wins for 4- and 8-bit codes, the warp-MMA kernel for 2-bit
+        if (fast && (kern == 3 || (kern == 0 && bits != 2))) {
+            rc = launch_tc_kernel(a, bt, x_dtype, bits, gs, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (fast && !launched) {
+            rc = launch_mma_any(a, bt, x_dtype, bits, gs, 1, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (!launched) {
+            for (int i = 0; i < bt.count; ++i) {
+                GemvArgs s1 = a;
+                s1.codes = bt.codes[i]; s1.scales = bt.scales[i]; s1.biases = bt.biases[i]; s1.y = bt.y[i];
+                s1.N = bt.N[i]; s1.ldy = bt.ldy[i]; s1.nbuf = 0;
+                const unsigned grid = (unsigned)((s1.N + 3) / 4);
+                JQ_DISPATCH_BITS(bits, B,
+                    (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(s1, x_dtype, sidecar_dtype, y_dtype, gs)))
+                rc = check_launch("qgemv (general)");
+                if (rc != JQ_OK) return rc;
+            }
+        }
+    }
+    return JQ_OK;
 }
 
 int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,
                    const void* biases, int sidecar_dtype, int64_t N, int64_t K, int bits, int gs, void* y,
                    int y_dtype, int64_t ldy, int flags, cudaStream_t st) {
-    int rc = check_quant_shape(N, K, bits, gs);
-    if (rc != JQ_OK) return rc;
-    JQ_REQUIRE(valid_dtype(x_dtype) && valid_dtype(sidecar_dtype) && valid_dtype(y_dtype), JQ_EINVAL, "bad dtype");
-    JQ_REQUIRE(M >= 0 && M <= JQ_QGEMV_MAX_M, JQ_EINVAL, "qgemv takes 0 <= M <= %d rows, got %lld", JQ_QGEMV_MAX_M,
-               (long long)M);
-    if (M == 0 || N == 0) return JQ_OK;
-    JQ_REQUIRE(K > 0, JQ_EINVAL, "K must be positive");
-    JQ_REQUIRE(x && codes && scales && biases && y, JQ_EINVAL, "null pointer");
-    JQ_REQUIRE(ldx >= K && ldy >= N, JQ_EINVAL, "leading dimension too small");
-    JQ_REQUIRE(N < (1ll << 31) && K < (1ll << 31), JQ_EUNSUPPORTED, "dimension too large");
-
-    const bool fast = !force_simple() && (gs == 64 || gs == 128) && x_dtype != JQ_F32 && sidecar_dtype == x_dtype &&
-                      y_dtype == x_dtype && aligned(codes, 16) && ((K * bits / 8) % 16 == 0) && aligned(x, 16) &&
-                      (ldx % 8 == 0) && aligned(scales, 8) && aligned(biases, 8) && ((K / gs) % 4 == 0);
-    for (int64_t m0 = 0; m0 < M; m0 += 8) {
-        GemvArgs a;
-        a.x = (const char*)x + m0 * ldx * dtype_size(x_dtype);
-        a.codes = codes; a.scales = scales; a.biases = biases;
-        a.y = (char*)y + m0 * ldy * dtype_size(y_dtype);
-        a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy;
-        a.M = (int)((M - m0) < 8 ? (M - m0) : 8);
-        a.G = (int)(K / gs);
-        a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
-        a.pair_expert = nullptr; a.codes_tab = nullptr; a.scales_tab = nullptr; a.biases_tab = nullptr;
-        a.bits_tab = nullptr; a.x_div = 1; a.num_experts = 0; a.ksplit = 1; a.nbuf = 0; a.status = nullptr;
-        bool launched = false;
-        const int kern = gemv_kernel_choice();
-        // measured on B200: the tensor-memory kernel wins for 4- and 8-bit codes, the warp-MMA kernel for 2-bit
-        if (fast && (kern == 3 || (kern == 0 && bits != 2))) {
-            rc = launch_tc_kernel(a, x_dtype, bits, gs, st, &launched);
-            if (rc != JQ_OK) return rc;
-        }
-        if (fast && kern == 2) {
-            rc = launch_row_kernel(a, x_dtype, bits, gs, 1, st, &launched);
-            if (rc != JQ_OK) return rc;
-        }
-        if (fast && !launched) {
-#define JQ_GEMV_CASE(B, GSZ)                                                                     \
-    if (bits == B && gs == GSZ) {                                                                \
-        rc = (x_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, 1, st, &launched)          \
-                                  : launch_mma<__half, B, GSZ>(a, 1, st, &launched);                \
-        if (rc != JQ_OK) return rc;                                                              \
-    }
-            JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(6, 64) JQ_GEMV_CASE(8, 64)
-            JQ_GEMV_CASE(2, 128) JQ_GEMV_CASE(3, 128) JQ_GEMV_CASE(4, 128) JQ_GEMV_CASE(6, 128) JQ_GEMV_CASE(8, 128)
-#undef JQ_GEMV_CASE
-        }
-        if (!launched) {
-            a.nbuf = 0;
-            const unsigned grid = (unsigned)((N + 3) / 4);
-            JQ_DISPATCH_BITS(bits, B,
-                (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(a, x_dtype, sidecar_dtype, y_dtype, gs)))
-            rc = check_launch("qgemv (general)");
-            if (rc != JQ_OK) return rc;
-        }
-    }
-    return JQ_OK;
+    GemvItems it = {};
+    it.count = 1;
+    it.codes[0] = codes; it.scales[0] = scales; it.biases[0] = biases; it.y[0] = y; it.N[0] = N; it.ldy[0] = ldy;
+    return qgemv_dispatch_items(x, x_dtype, M, ldx, it, sidecar_dtype, K, bits, gs, y_dtype, flags, st);
 }
 
 // Routed-expert mat-vec for few (token, slot) pairs: y[p] = deq(W[expert[p]]) . x[p / x_div].
@@ -526,30 +577,21 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
     JQ_REQUIRE(x && pair_expert && codes_tab && scales_tab && biases_tab && y, JQ_EINVAL, "null pointer");
     JQ_REQUIRE(ldx >= K && ldy >= N, JQ_EINVAL, "leading dimension too small");
     JQ_REQUIRE(N < (1ll << 31) && K < (1ll << 31), JQ_EUNSUPPORTED, "dimension too large");
-    GemvArgs a;
-    a.x = x; a.codes = nullptr; a.scales = nullptr; a.biases = nullptr; a.y = y;
-    a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.M = 1; a.G = (int)(K / gs); a.nbuf = 0; a.pdl = 0;
+    GemvArgs a = {};
+    a.x = x; a.y = y;
+    a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.M = 1; a.G = (int)(K / gs);
     a.pair_expert = pair_expert; a.codes_tab = codes_tab; a.scales_tab = scales_tab; a.biases_tab = biases_tab;
-    a.bits_tab = bits_tab; a.x_div = x_div; a.num_experts = num_experts; a.ksplit = 1; a.status = nullptr;
+    a.bits_tab = bits_tab; a.x_div = x_div; a.num_experts = num_experts; a.ksplit = 1;
+    GemvBatch bt = {};        // one entry: row count and output of every pair's matrix
+    bt.count = 1; bt.y[0] = y; bt.N[0] = N; bt.ldy[0] = ldy;
     // the per-expert base pointers are not known on the host: the fast path relies on the caller's
     // promise (checked for the row pitch here) that every expert tensor is 16-byte aligned
     const bool fast = !force_simple() && (gs == 64 || gs == 128) && act_dtype != JQ_F32 && sidecar_dtype == act_dtype &&
                       ((K * bits / 8) % 16 == 0) && aligned(x, 16) && (ldx % 8 == 0) && ((K / gs) % 4 == 0) && bits != 5;
     bool launched = false;
-    if (fast && gemv_kernel_choice() == 2) {
-        rc = launch_row_kernel(a, act_dtype, bits, gs, (int)pairs, st, &launched);
+    if (fast) {
+        rc = launch_mma_any(a, bt, act_dtype, bits, gs, (int)pairs, st, &launched);
         if (rc != JQ_OK) return rc;
-    }
-    if (fast && !launched) {
-#define JQ_GEMV_CASE(B, GSZ)                                                                          \
-    if (bits == B && gs == GSZ) {                                                                     \
-        rc = (act_dtype == JQ_BF16) ? launch_mma<__nv_bfloat16, B, GSZ>(a, (int)pairs, st, &launched) \
-                                    : launch_mma<__half, B, GSZ>(a, (int)pairs, st, &launched);       \
-        if (rc != JQ_OK) return rc;                                                                   \
-    }
-        JQ_GEMV_CASE(2, 64) JQ_GEMV_CASE(3, 64) JQ_GEMV_CASE(4, 64) JQ_GEMV_CASE(6, 64) JQ_GEMV_CASE(8, 64)
-        JQ_GEMV_CASE(2, 128) JQ_GEMV_CASE(3, 128) JQ_GEMV_CASE(4, 128) JQ_GEMV_CASE(6, 128) JQ_GEMV_CASE(8, 128)
-#undef JQ_GEMV_CASE
     }
     if (!launched) {
         dim3 grid((unsigned)((N + 3) / 4), (unsigned)pairs);
@@ -557,6 +599,33 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
             (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(a, act_dtype, sidecar_dtype, act_dtype, gs)))
         rc = check_launch("gather qgemv (general)");
         if (rc != JQ_OK) return rc;
+    }
+    return JQ_OK;
+}
+
+// Fused form of several mat-vecs: consecutive entries that share x, K, the bit width and the group size
+// become one launch (at most GEMV_MAX_FUSE matrices each).
+int qgemv_dispatch_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype, int sidecar_dtype, int flags,
+                           cudaStream_t st) {
+    JQ_REQUIRE(count >= 0 && count <= JQ_QGEMV_MAX_BATCH, JQ_EINVAL, "count must be in [0, %d]", JQ_QGEMV_MAX_BATCH);
+    JQ_REQUIRE(count == 0 || descs, JQ_EINVAL, "null descriptor table");
+    int i = 0;
+    while (i < count) {
+        const JqGemvDesc& d0 = descs[i];
+        GemvItems it = {};
+        int j = i;
+        while (j < count && it.count < GEMV_MAX_FUSE) {
+            const JqGemvDesc& d = descs[j];
+            if (d.x != d0.x || d.ldx != d0.ldx || d.K != d0.K || d.bits != d0.bits || d.group_size != d0.group_size) break;
+            const int k = it.count++;
+            it.codes[k] = d.codes; it.scales[k] = d.scales; it.biases[k] = d.biases; it.y[k] = d.y;
+            it.N[k] = d.N; it.ldy[k] = d.ldy;
+            ++j;
+        }
+        int rc = qgemv_dispatch_items(d0.x, act_dtype, M, d0.ldx, it, sidecar_dtype, d0.K, d0.bits, d0.group_size,
+                                      act_dtype, flags, st);
+        if (rc != JQ_OK) return rc;
+        i = j;
     }
     return JQ_OK;
 }
@@ -590,15 +659,12 @@ int jq_qgemv_ex(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32
 
 int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype, int sidecar_dtype,
                      jq_stream_t stream) {
-    JQ_REQUIRE(count >= 0 && count <= JQ_QGEMV_MAX_BATCH, JQ_EINVAL, "count must be in [0, %d]", JQ_QGEMV_MAX_BATCH);
-    JQ_REQUIRE(count == 0 || descs, JQ_EINVAL, "null descriptor table");
-    for (int i = 0; i < count; ++i) {
-        const JqGemvDesc& d = descs[i];
-        int rc = jq::qgemv_dispatch(d.x, act_dtype, M, d.ldx, d.codes, d.scales, d.biases, sidecar_dtype, d.N, d.K,
-                                    d.bits, d.group_size, d.y, act_dtype, d.ldy, 0, (cudaStream_t)stream);
-        if (rc != JQ_OK) return rc;
-    }
-    return JQ_OK;
+    return jq::qgemv_dispatch_batched(descs, count, M, act_dtype, sidecar_dtype, 0, (cudaStream_t)stream);
+}
+
+int jq_qgemv_batched_ex(const JqGemvDesc* descs, int count, int64_t M, int act_dtype, int sidecar_dtype, int flags,
+                        jq_stream_t stream) {
+    return jq::qgemv_dispatch_batched(descs, count, M, act_dtype, sidecar_dtype, flags, (cudaStream_t)stream);
 }
 
 int jq_device_status(void) {

@@ -1,4 +1,4 @@
-// Argument block and inner loop shared by the mat-vec kernels (jq_qgemv.cu, jq_qgemv_row.cu).
+// Argument blocks and inner loop shared by the mat-vec kernels (jq_qgemv.cu, jq_qgemv_tc.cu).
 #pragma once
 
 #include "jq_mma.cuh"
@@ -22,10 +22,23 @@ struct GemvArgs {
     const void* const* biases_tab;
     const int32_t* bits_tab;      // optional: experts whose width differs from the launch's are skipped
     int x_div, num_experts;
-    int ksplit;   // cluster kernels: CTAs of a cluster that split K
+    int ksplit;   // tensor-memory kernel: CTAs of a cluster that split K
     int* status;  // device status word, set to 1 when a bounded wait ran out (tensor-memory kernel)
 };
 
+// Matrices of one fused launch: they share the activations (x, ldx), K, the bit width and the group
+// size, and differ in weights, output and row count (q/k/v or gate/up of one decoder layer).  The grid
+// is the concatenation of their row blocks; blk_end[i] is the first block after matrix i.
+constexpr int GEMV_MAX_FUSE = 4;
+struct GemvBatch {
+    const uint32_t* codes[GEMV_MAX_FUSE];
+    const void* scales[GEMV_MAX_FUSE];
+    const void* biases[GEMV_MAX_FUSE];
+    void* y[GEMV_MAX_FUSE];
+    int64_t N[GEMV_MAX_FUSE], ldy[GEMV_MAX_FUSE];
+    int blk_end[GEMV_MAX_FUSE];
+    int count;
+};
 
 // One pipeline stage of one warp: nblk k-blocks of 64 codes for 16*MT weight rows.
 //   codes : this lane's first row (row g of the tile) in the staged codes, row stride RS words
@@ -106,11 +119,9 @@ __device__ __forceinline__ void gemv_stage_blocks(const uint32_t* __restrict__ c
     }
 }
 
-// row-parallel kernel with cluster split-K (jq_qgemv_row.cu); *launched = false when the shape does
-// not fit it and the caller should use the K-split kernel instead
-int launch_row_kernel(const GemvArgs& a, int act_dtype, int bits, int gs, int pairs, cudaStream_t st, bool* launched);
-
-// tensor-memory kernel (jq_qgemv_tc.cu), dense mat-vec only; same convention for *launched
-int launch_tc_kernel(const GemvArgs& a, int act_dtype, int bits, int gs, cudaStream_t st, bool* launched);
+// tensor-memory kernel (jq_qgemv_tc.cu), dense mat-vecs only; *launched stays false when the shape does
+// not fit it and the caller should use the warp-MMA kernel instead
+int launch_tc_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
+                     bool* launched);
 
 }  // namespace jq

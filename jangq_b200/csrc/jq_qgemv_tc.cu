@@ -94,6 +94,11 @@ template <int BITS, int GS, int NCOL> struct Ring {
     static constexpr int TMEM_COLS = NEED <= 128 ? 128 : NEED <= 256 ? 256 : 512;
 };
 
+// tensor maps of the matrices of one (possibly fused) launch
+struct TcMaps {
+    CUtensorMap m[GEMV_MAX_FUSE];
+};
+
 // shared-memory map (offsets from a 1024-byte aligned base)
 struct Map {
     int tab, red, sc, b, raw, total;
@@ -112,7 +117,7 @@ __host__ __device__ inline Map make_map(int ncol, int slice_tiles, int slice_gro
 
 template <typename AT, int BITS, int GS, int NCOL>
 __global__ void __launch_bounds__(threads_for(BITS), BITS == 8 ? 2 : 1)
-qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
+qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const GemvBatch bt) {
     using A = Act<AT>;
     using RG = Ring<BITS, GS, NCOL>;
     constexpr int THREADS = threads_for(BITS);
@@ -131,8 +136,13 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = a.ksplit, NS = a.nbuf;
-    const int rb = blockIdx.x / S;
-    const int cr = blockIdx.x - rb * S;                  // rank in the cluster (cluster shape (S,1,1))
+    const int rbg = blockIdx.x / S;                      // row block of the launch
+    const int cr = blockIdx.x - rbg * S;                 // rank in the cluster (cluster shape (S,1,1))
+    int mi = 0, blk0 = 0;                                // matrix of a fused launch, its first row block
+    while (mi + 1 < bt.count && rbg >= bt.blk_end[mi]) { blk0 = bt.blk_end[mi]; ++mi; }
+    const int rb = rbg - blk0;
+    const int64_t N = bt.N[mi], ldy = bt.ldy[mi];
+    const CUtensorMap* wmap = &maps.m[mi];
     const int M = a.M, G = a.G;
     const int nquads = G / 4;                            // K in units of 4 groups
     const int q_begin = (int)((int64_t)cr * nquads / S), q_end = (int)((int64_t)(cr + 1) * nquads / S);
@@ -158,9 +168,9 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
     uint8_t* sRaw = smem + mp.raw;
 
     const uint16_t* xs16 = reinterpret_cast<const uint16_t*>(a.x);
-    const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(a.scales);
-    const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(a.biases);
-    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
+    const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(bt.scales[mi]);
+    const uint16_t* bi16 = reinterpret_cast<const uint16_t*>(bt.biases[mi]);
+    uint16_t* y16 = reinterpret_cast<uint16_t*>(bt.y[mi]);
 
     // ---- set-up: barriers, tensor memory, first weight copies (static data) -----------------------------
     JQ_PROF_DECL(t_start);
@@ -169,10 +179,10 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
         const int s = st % NS;
         mbar_expect_tx(raw_full + s, STAGE_BYTES);
         if constexpr (BITS == 8) {
-            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, &wmap, (t_begin + 2 * st) * 128, (int)n0, raw_full + s);
-            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES + BOX_BYTES, &wmap, (t_begin + 2 * st + 1) * 128, (int)n0, raw_full + s);
+            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, wmap, (t_begin + 2 * st) * 128, (int)n0, raw_full + s);
+            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES + BOX_BYTES, wmap, (t_begin + 2 * st + 1) * 128, (int)n0, raw_full + s);
         } else {
-            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, &wmap, t_begin * TILE_B + st * 128, (int)n0, raw_full + s);
+            tma_load_2d(sRaw + (size_t)s * STAGE_BYTES, wmap, t_begin * TILE_B + st * 128, (int)n0, raw_full + s);
         }
     };
     if (tid == 0) {
@@ -262,7 +272,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
         // quad 2i + eset (groups of 64: one pair per quad) or quad i (groups of 128: two pairs per quad)
         const int npairs = ntiles / 2;
         const int my_pairs = warp >= W_EPI ? (npairs - eset + 1) / 2 : 0;
-        const int64_t n_row = min(n0 + row, a.N - 1);
+        const int64_t n_row = min(n0 + row, N - 1);
         uint8_t* my_sc = sc_ring + (size_t)(eset & 1) * SQ * ROWS * 16;
         auto issue_sc = [&](int i) {
             if (i < my_pairs) {
@@ -514,10 +524,10 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
     // ---- results: direct store, or partial sums to rank 0 through distributed shared memory -----------------
     const bool owner = warp >= W_EPI && warp < W_EPI + 4;             // set 0 holds the CTA's sums
     if (S == 1) {
-        if (owner && n0 + row < a.N) {
+        if (owner && n0 + row < N) {
 #pragma unroll
             for (int m = 0; m < MMAX; ++m)
-                if (m < M) y16[(int64_t)m * a.ldy + n0 + row] = A::from_f32(acc[m]);
+                if (m < M) y16[(int64_t)m * ldy + n0 + row] = A::from_f32(acc[m]);
         }
     } else {
         if (owner) {
@@ -530,7 +540,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a) {
                 const int m = idx / ROWS, rr = idx - m * ROWS;
                 float v = red[rr * 8 + m];
                 for (int s = 1; s < S; ++s) v += ld_cluster_f32(red + rr * 8 + m, (uint32_t)s);
-                if (n0 + rr < a.N) y16[(int64_t)m * a.ldy + n0 + rr] = A::from_f32(v);
+                if (n0 + rr < N) y16[(int64_t)m * ldy + n0 + rr] = A::from_f32(v);
             }
         }
         cluster_sync_all();    // peers keep their shared memory alive until rank 0 has read it
@@ -553,7 +563,7 @@ static int env_int(const char* name, int dflt) {
 }
 
 template <typename AT, int BITS, int GS, int NCOL>
-static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, int ns, cudaStream_t st, bool* launched) {
+static int launch_cfg(const TcMaps& maps, GemvArgs a, GemvBatch bt, int S, int ns, cudaStream_t st, bool* launched) {
     constexpr int TPQ = 4 * GS / TK;
     const int nquads = a.G / 4;
     const int sq_max = (nquads + S - 1) / S;
@@ -572,9 +582,13 @@ static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, int ns, cudaSt
     a.nbuf = ns;
     a.status = status_word();
     JQ_REQUIRE(a.status != nullptr, JQ_ECUDA, "could not locate the device status word");
-    const unsigned row_blocks = (unsigned)((a.N + ROWS - 1) / ROWS);
+    int64_t row_blocks = 0;
+    for (int i = 0; i < bt.count; ++i) {
+        row_blocks += (bt.N[i] + ROWS - 1) / ROWS;
+        bt.blk_end[i] = (int)row_blocks;
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(row_blocks * (unsigned)S);
+    cfg.gridDim = dim3((unsigned)row_blocks * (unsigned)S);
     cfg.blockDim = dim3(threads_for(BITS));
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
@@ -594,7 +608,7 @@ static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, int ns, cudaSt
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_tc_kernel<AT, BITS, GS, NCOL>, wmap, a));
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_tc_kernel<AT, BITS, GS, NCOL>, maps, a, bt));
     *launched = true;
     return JQ_OK;
 }
@@ -605,13 +619,14 @@ static int launch_cfg(const CUtensorMap& wmap, GemvArgs a, int S, int ns, cudaSt
 //     flight before the activations arrive (the launch may overlap its predecessor).
 //   * Many row blocks: S grows only until the limbs of a slice fit beside a deep ring; CTAs run in waves.
 template <typename AT, int BITS, int GS, int NCOL>
-static int launch_shape(const CUtensorMap& wmap, const GemvArgs& a, cudaStream_t st, bool* launched) {
+static int launch_shape(const TcMaps& maps, const GemvArgs& a, const GemvBatch& bt, cudaStream_t st, bool* launched) {
     constexpr int TPQ = 4 * GS / TK;
     using RG = Ring<BITS, GS, NCOL>;
     constexpr int TPS = BITS == 8 ? 2 : 8 / BITS;          // tiles per stage
     const int sms = sm_count();
     const int nquads = a.G / 4;
-    const int64_t row_blocks = (a.N + ROWS - 1) / ROWS;
+    int64_t row_blocks = 0;
+    for (int i = 0; i < bt.count; ++i) row_blocks += (bt.N[i] + ROWS - 1) / ROWS;
     int S = 1;
     if (row_blocks <= sms) {
         while (S < 8 && S < nquads && row_blocks * (S + 1) <= sms) ++S;
@@ -636,7 +651,7 @@ static int launch_shape(const CUtensorMap& wmap, const GemvArgs& a, cudaStream_t
     if (S < 1 || S > 8 || S > nquads) return JQ_OK;
     int ns = env_int("JANGQ_TC_NS", fit_ns(S));
     if (ns < 2 || ns > RG::MAX_STAGES || (BITS == 8 && (ns & 1))) return JQ_OK;
-    return launch_cfg<AT, BITS, GS, NCOL>(wmap, a, S, ns, st, launched);
+    return launch_cfg<AT, BITS, GS, NCOL>(maps, a, bt, S, ns, st, launched);
 }
 
 }  // namespace tcv
@@ -652,34 +667,40 @@ extern "C" int jq_tc_profile_read(unsigned long long* out, int reset) {
 }
 #endif
 
-// Dense mat-vec on the tensor-memory kernel; *launched stays false when the shape does not fit it.
-int launch_tc_kernel(const GemvArgs& a, int act_dtype, int bits, int gs, cudaStream_t st, bool* launched) {
+// Dense mat-vecs (one launch for all matrices of `bt`) on the tensor-memory kernel; *launched stays
+// false when the shape does not fit it.
+int launch_tc_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
+                     bool* launched) {
     *launched = false;
     const int64_t rowbytes = a.K * bits / 8;
     if (!(bits == 2 || bits == 4 || bits == 8) || a.K % tcv::TK != 0 || a.G % 4 != 0 || a.M > 8 || rowbytes < 128)
         return JQ_OK;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return JQ_OK;
-    // the packed codes as a [N][rowbytes] byte matrix; a box is 128 rows x 128 bytes, 128-byte swizzled;
-    // rows past N and bytes past the row end read as zero
-    CUtensorMap wmap;
-    const cuuint64_t gdim[2] = {(cuuint64_t)rowbytes, (cuuint64_t)a.N};
-    const cuuint64_t gstride[1] = {(cuuint64_t)rowbytes};
-    const cuuint32_t box[2] = {128, (cuuint32_t)tcv::ROWS};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.codes), gdim, gstride, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    JQ_REQUIRE(cr == CUDA_SUCCESS, JQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+    // the packed codes of every matrix as a [N][rowbytes] byte matrix; a box is 128 rows x 128 bytes,
+    // 128-byte swizzled; rows past N and bytes past the row end read as zero
+    tcv::TcMaps maps;
+    for (int i = 0; i < GEMV_MAX_FUSE; ++i) {
+        const int src = i < bt.count ? i : 0;      // unused slots repeat the first map
+        const cuuint64_t gdim[2] = {(cuuint64_t)rowbytes, (cuuint64_t)bt.N[src]};
+        const cuuint64_t gstride[1] = {(cuuint64_t)rowbytes};
+        const cuuint32_t box[2] = {128, (cuuint32_t)tcv::ROWS};
+        const cuuint32_t estr[2] = {1, 1};
+        if (i >= bt.count) { maps.m[i] = maps.m[0]; continue; }
+        CUresult cr = enc(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(bt.codes[src]), gdim,
+                          gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        JQ_REQUIRE(cr == CUDA_SUCCESS, JQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+    }
     int rc = JQ_OK;
 #define JQ_TC_CASE(B, GSZ)                                                                                    \
     if (bits == B && gs == GSZ) {                                                                             \
         if (act_dtype == JQ_BF16)                                                                             \
-            rc = a.M <= 5 ? tcv::launch_shape<__nv_bfloat16, B, GSZ, 16>(wmap, a, st, launched)               \
-                          : tcv::launch_shape<__nv_bfloat16, B, GSZ, 32>(wmap, a, st, launched);              \
+            rc = a.M <= 5 ? tcv::launch_shape<__nv_bfloat16, B, GSZ, 16>(maps, a, bt, st, launched)           \
+                          : tcv::launch_shape<__nv_bfloat16, B, GSZ, 32>(maps, a, bt, st, launched);          \
         else                                                                                                  \
-            rc = a.M <= 5 ? tcv::launch_shape<__half, B, GSZ, 16>(wmap, a, st, launched)                      \
-                          : tcv::launch_shape<__half, B, GSZ, 32>(wmap, a, st, launched);                     \
+            rc = a.M <= 5 ? tcv::launch_shape<__half, B, GSZ, 16>(maps, a, bt, st, launched)                  \
+                          : tcv::launch_shape<__half, B, GSZ, 32>(maps, a, bt, st, launched);                 \
     }
     JQ_TC_CASE(2, 64) JQ_TC_CASE(4, 64) JQ_TC_CASE(8, 64) JQ_TC_CASE(2, 128) JQ_TC_CASE(4, 128) JQ_TC_CASE(8, 128)
 #undef JQ_TC_CASE

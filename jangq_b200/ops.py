@@ -115,6 +115,31 @@ def _qgemv(x2: torch.Tensor, wq, scales, biases, K, bits, group_size, out: torch
                                _lib.stream_ptr(dev)))
 
 
+def qgemv_fused(x2: torch.Tensor, linears, outs, flags: int = 0):
+    """Mat-vecs of several weight matrices over the same activations x2 [M <= 16, K]: one C call, and
+    one kernel launch for every run of up to four matrices that share K, the bit width and the group
+    size (q/k/v, or gate/up, of a decoder layer).  `linears` are objects with weight/scales/biases/
+    bits/group_size/in_features (JANGLinear), `outs` the output tensors [M, N_i]."""
+    lib = _lib.load()
+    n = len(linears)
+    if n == 0:
+        return
+    if n > _lib.QGEMV_MAX_BATCH:
+        for i in range(0, n, _lib.QGEMV_MAX_BATCH):
+            qgemv_fused(x2, linears[i:i + _lib.QGEMV_MAX_BATCH], outs[i:i + _lib.QGEMV_MAX_BATCH], flags)
+        return
+    descs = (_lib.JqGemvDesc * n)()
+    for d, lin, out in zip(descs, linears, outs):
+        if lin.scales.dtype != linears[0].scales.dtype or out.dtype != x2.dtype:
+            raise JangqError(_lib.JQ_EINVAL, "qgemv_fused: one sidecar dtype, outputs in the activation dtype")
+        d.x, d.codes, d.scales, d.biases, d.y = (x2.data_ptr(), lin.weight.data_ptr(), lin.scales.data_ptr(),
+                                                 lin.biases.data_ptr(), out.data_ptr())
+        d.N, d.K, d.ldx, d.ldy = lin.weight.shape[0], lin.in_features, x2.stride(0), out.stride(0)
+        d.bits, d.group_size = lin.bits, lin.group_size
+    _lib.check(lib.jq_qgemv_batched_ex(descs, n, x2.shape[0], _lib.dtype_id(x2.dtype),
+                                       _lib.dtype_id(linears[0].scales.dtype), flags, _lib.stream_ptr(x2.device)))
+
+
 def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
                      transpose: bool = True, group_size: int = 64, bits: int = 4,
                      static_weights: bool = False) -> torch.Tensor:

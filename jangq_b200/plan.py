@@ -3,10 +3,13 @@
 The reference found real decode to be dispatch-bound, not bandwidth-bound
 (jang_tools/dsv41/DECODE_DSPARK_METHODS.md:90-93) and fused its dispatches by
 hand.  On CUDA the same effect comes from capturing the launches of a decode
-step once and replaying them: `GemvPlan` captures one jq_qgemv per linear on a
-private stream into a CUDA graph; `run()` replays it, `run_host()` adds the
+step once and replaying them: `GemvPlan` captures the mat-vecs of its linears on
+a private stream into a CUDA graph; `run()` replays it, `run_host()` adds the
 host->device copy of the step's activations and the device->host copy of the
-last output.
+last output.  Linears named in one inner list of `groups` read the same
+activations (q/k/v, or gate/up, of a decoder layer) and go out through
+jq_qgemv_batched_ex, which makes one launch of every run that shares K, the
+bit width and the group size.
 """
 from __future__ import annotations
 
@@ -26,7 +29,8 @@ class GemvPlan:
     """
 
     def __init__(self, linears: Sequence[JANGLinear], m: int = 1, dtype: torch.dtype = torch.bfloat16,
-                 device=None, share_inputs: bool = True, static_weights: bool = True):
+                 device=None, share_inputs: bool = True, static_weights: bool = True,
+                 groups: Sequence[Sequence[int]] | None = None):
         if m < 1 or m > _lib.QGEMV_MAX_M:
             raise _lib.JangqError(_lib.JQ_EINVAL, f"GemvPlan takes 1..{_lib.QGEMV_MAX_M} rows")
         self.linears = list(linears)
@@ -44,7 +48,14 @@ class GemvPlan:
             self.x.append(self._xbuf[key])
             self.y.append(torch.empty((m, lin.out_features), dtype=dtype, device=self.device))
         self.algorithmic_bytes = sum(self.bytes_of(lin, m) for lin in self.linears)
-        self.launches_per_run = sum((m + 7) // 8 for _ in self.linears)
+        # groups: lists of indices into `linears` whose members share an input; default: every linear alone
+        self.groups = [list(g) for g in groups] if groups is not None else [[i] for i in range(len(self.linears))]
+        if sorted(i for g in self.groups for i in g) != list(range(len(self.linears))):
+            raise _lib.JangqError(_lib.JQ_EINVAL, "groups must name every linear exactly once")
+        for g in self.groups:
+            if any(self.x[i] is not self.x[g[0]] for i in g):
+                raise _lib.JangqError(_lib.JQ_EINVAL, "the linears of a group must read the same input buffer")
+        self.launches_per_run = sum(self._launches_of(g) for g in self.groups) * ((m + 7) // 8)
         self._graph = None
         self._host_in = {k: torch.zeros(v.shape, dtype=dtype).pin_memory() for k, v in self._xbuf.items()}
         self._host_out = torch.zeros(self.y[-1].shape, dtype=dtype).pin_memory()
@@ -56,11 +67,22 @@ class GemvPlan:
         e = lin.scales.element_size()
         return n * k * lin.bits // 8 + n * (k // lin.group_size) * 2 * e + m * k * 2 + m * n * 2
 
+    def _launches_of(self, group) -> int:
+        """Kernel launches of one group: runs of up to 4 consecutive members with equal (K, bits, group size)."""
+        n, run, prev = 0, 0, None
+        for i in group:
+            lin = self.linears[i]
+            key = (lin.in_features, lin.bits, lin.group_size)
+            if key != prev or run == 4:
+                n, run, prev = n + 1, 0, key
+            run += 1
+        return n
+
     def _enqueue(self):
-        from .ops import _qgemv
-        for lin, x, y in zip(self.linears, self.x, self.y):
-            _qgemv(x, lin.weight, lin.scales, lin.biases, lin.in_features, lin.bits, lin.group_size, y,
-                   _lib.JQ_GEMV_STATIC_WEIGHTS if self.static_weights else 0)
+        from .ops import qgemv_fused
+        flags = _lib.JQ_GEMV_STATIC_WEIGHTS if self.static_weights else 0
+        for g in self.groups:
+            qgemv_fused(self.x[g[0]], [self.linears[i] for i in g], [self.y[i] for i in g], flags)
 
     def capture(self):
         """Record the launches into a CUDA graph (call once, before run())."""

@@ -150,3 +150,71 @@ def test_static_weights_overlapped_launches_keep_stream_order():
     for _ in range(5):
         assert torch.equal(chain(_lib.JQ_GEMV_STATIC_WEIGHTS), ref)
     assert float(ref.float().abs().max()) > 0
+
+
+# ---- fused launches (jq_qgemv_batched_ex): several matrices over the same activations -----------------------
+@pytest.mark.parametrize("M", (1, 3))
+@pytest.mark.parametrize("bits", (2, 4, 6, 8))
+def test_fused_matches_oracle_and_single_calls(bits, M):
+    """q/k/v-like: three matrices of different row counts (one ragged) in one call; every output must
+    match the oracle and agree with the single-matrix call to an output rounding step (the split of K over
+    clusters and warps, hence the f32 summation order, depends on the size of the launch)."""
+    from jangq_b200.ops import qgemv_fused
+    K, gs = 1024, 64
+    x = None
+    lins, refs = [], []
+    for i, N in enumerate((384, 200, 128)):
+        xi, wq, s, b = make_case(N, K, bits, gs, M, torch.bfloat16, seed=10 + i)
+        x = xi if x is None else x
+        lin = jq.JANGLinear(K, N, bits, gs, dtype=torch.bfloat16, device=DEV)
+        lin.weight.copy_(wq); lin.scales.copy_(s); lin.biases.copy_(b)
+        lins.append(lin)
+        refs.append(reference(x, wq, s, b, bits, gs))
+    outs = [torch.full((M, l.out_features), float("nan"), dtype=torch.bfloat16, device=DEV) for l in lins]
+    qgemv_fused(x, lins, outs)
+    torch.cuda.synchronize()
+    for lin, out, ref in zip(lins, outs, refs):
+        check(out, ref, torch.bfloat16)
+        single = jq.quantized_matmul(x, lin.weight, lin.scales, lin.biases, group_size=gs, bits=bits)
+        assert (single.float() - out.float()).abs().max() <= 2.0 ** -7 * out.float().abs().max()
+
+
+def test_fused_mixed_widths_split_into_runs():
+    """Entries whose width or K differ cannot share a launch: the call must still compute all of them."""
+    from jangq_b200.ops import qgemv_fused
+    gs, M = 64, 1
+    lins, refs, x = [], [], None
+    for i, (N, bits) in enumerate(((256, 8), (256, 8), (192, 2), (128, 4), (128, 4))):
+        xi, wq, s, b = make_case(N, 512, bits, gs, M, torch.bfloat16, seed=30 + i)
+        x = xi if x is None else x
+        lin = jq.JANGLinear(512, N, bits, gs, dtype=torch.bfloat16, device=DEV)
+        lin.weight.copy_(wq); lin.scales.copy_(s); lin.biases.copy_(b)
+        lins.append(lin)
+        refs.append(reference(x, wq, s, b, bits, gs))
+    outs = [torch.empty((M, l.out_features), dtype=torch.bfloat16, device=DEV) for l in lins]
+    qgemv_fused(x, lins, outs, _lib.JQ_GEMV_STATIC_WEIGHTS)
+    torch.cuda.synchronize()
+    for out, ref in zip(outs, refs):
+        check(out, ref, torch.bfloat16)
+
+
+def test_plan_groups_fuse_and_match_ungrouped():
+    """GemvPlan with groups (q/k/v fused, o alone) replays to the outputs of the ungrouped plan (to one
+    output rounding step: the summation order depends on the launch size)."""
+    torch.manual_seed(3)
+    lins = [jq.JANGLinear.from_float((torch.randn(n, 1024, device=DEV) * 0.02).to(torch.bfloat16), bits=b, group_size=64)
+            for n, b in ((256, 8), (256, 8), (128, 8), (256, 8), (512, 2), (512, 2))]
+    xin = torch.randn(1, 1024, device=DEV).to(torch.bfloat16)
+    plans = [jq.GemvPlan(lins, m=1, device=DEV), jq.GemvPlan(lins, m=1, device=DEV, groups=[[0, 1, 2], [3], [4, 5]])]
+    assert plans[0].launches_per_run == 6 and plans[1].launches_per_run == 3
+    outs = []
+    for p in plans:
+        for buf in p._xbuf.values():
+            buf.copy_(xin)
+        p.capture()
+        p.run()
+        torch.cuda.synchronize()
+        outs.append([y.clone() for y in p.y])
+    for a, b in zip(*outs):
+        assert (a.float() - b.float()).abs().max() <= 2.0 ** -7 * a.float().abs().max()
+    _lib.check(_lib.load().jq_device_status())
