@@ -36,8 +36,6 @@ namespace jq {
 
 __device__ int g_timeout_flag = 0;   // set by any kernel whose bounded wait ran out
 
-constexpr int GEMV_MAX_NBUF = 3;
-
 __host__ __device__ inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
 // Compile-time geometry of one stage buffer (per warp, per pipeline slot).
@@ -376,12 +374,13 @@ static bool force_simple() {
 }
 
 // JANGQ_GEMV_KERNEL selects the fast-path kernel: unset = per-width default, "tc" = tensor-memory
-// kernel wherever the shape fits it, "mma" = the warp-MMA kernel of this file.  A tuning and
-// comparison knob.
+// kernel wherever the shape fits it, "imma" = integer warp-MMA kernel wherever it fits, "mma" = the
+// warp-MMA kernel of this file.  A tuning and comparison knob.
 static int gemv_kernel_choice() {
     const char* e = getenv("JANGQ_GEMV_KERNEL");
     if (!e) return 0;
     if (e[0] == 'm') return 1;
+    if (e[0] == 'i') return 2;      // integer warp-MMA kernel wherever the shape fits it
     if (e[0] == 't') return 3;
     return 0;
 }
@@ -528,8 +527,22 @@ int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, con
         a.N = bt.N[0]; a.ldy = bt.ldy[0];
         bool launched = false;
         int rc = JQ_OK;
-        // measured on B200: the tensor-memory kernel wins for 4- and 8-bit codes, the warp-MMA kernel for 2-bit
-        if (fast && (kern == 3 || (kern == 0 && bits != 2))) {
+        // Measured choice on B200 (CUDA events, overlapped launches, working set >> L2):
+        //   8-bit: tensor-memory kernel, except launches of at most ~6K rows with M <= 2, where the integer
+        //          warp-MMA kernel has the lower fixed latency (4096x4096: 6.4 us vs 7.7 us);
+        //   4-bit: tensor-memory kernel;
+        //   2-bit: integer warp-MMA kernel for M <= 2 once the grid fills the machine (>= 2 row tiles of 16
+        //          per SM: 11008x4096 8.3 us vs 8.8 us), else the bf16 warp-MMA kernel;
+        //   3/6-bit, M > 2 with 2-bit: bf16 warp-MMA kernel.
+        int64_t rows = 0;
+        for (int i = 0; i < bt.count; ++i) rows += bt.N[i];
+        const bool small8 = bits == 8 && a.M <= 2 && rows <= 6144;
+        const bool big2 = bits == 2 && a.M <= 2 && rows >= (int64_t)32 * sm_count() && K <= 8192;
+        if (fast && (kern == 2 || (kern == 0 && (small8 || big2)))) {
+            rc = launch_imma_kernel(a, bt, x_dtype, bits, gs, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (fast && !launched && (kern == 3 || (kern == 0 && bits != 2))) {
             rc = launch_tc_kernel(a, bt, x_dtype, bits, gs, st, &launched);
             if (rc != JQ_OK) return rc;
         }

@@ -119,6 +119,12 @@ __device__ __forceinline__ void gemv_stage_blocks(const uint32_t* __restrict__ c
     }
 }
 
+constexpr int GEMV_MAX_NBUF = 3;   // deepest per-warp stage pipeline of the warp-MMA kernels
+
+// integer warp-MMA kernel (jq_qgemv_imma.cu), dense mat-vecs with at most 2 activation rows; same convention
+int launch_imma_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
+                       bool* launched);
+
 // tensor-memory kernel (jq_qgemv_tc.cu), dense mat-vecs only; *launched stays false when the shape does
 // not fit it and the caller should use the warp-MMA kernel instead
 int launch_tc_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,

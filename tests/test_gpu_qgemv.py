@@ -218,3 +218,31 @@ def test_plan_groups_fuse_and_match_ungrouped():
     for a, b in zip(*outs):
         assert (a.float() - b.float()).abs().max() <= 2.0 ** -7 * a.float().abs().max()
     _lib.check(_lib.load().jq_device_status())
+
+
+# ---- every fast kernel, selected explicitly ------------------------------------------------------------------
+@pytest.mark.parametrize("kernel", ("tc", "imma", "mma"))
+@pytest.mark.parametrize("bits,N,K,M", ((8, 4096, 4096, 1), (2, 5000, 4096, 1), (4, 300, 11008, 2), (8, 130, 2048, 2),
+                                        (2, 96, 512, 1), (4, 4100, 1024, 1)))
+def test_each_kernel_against_oracle(monkeypatch, kernel, bits, N, K, M):
+    """The dispatcher picks a kernel per shape from measurements; JANGQ_GEMV_KERNEL forces one (where the
+    shape fits it), so every kernel is checked on shapes it would not get by default: ragged row blocks,
+    K split over clusters, rows longer than one ring."""
+    monkeypatch.setenv("JANGQ_GEMV_KERNEL", kernel)
+    x, wq, s, b = make_case(N, K, bits, 64, M, torch.bfloat16, seed=bits + N + M)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=bits)
+    check(y, reference(x, wq, s, b, bits, 64), torch.bfloat16)
+    _lib.check(_lib.load().jq_device_status())
+
+
+def test_nonfinite_activation_poisons_only_its_outputs(monkeypatch):
+    """An infinite activation must not turn into a finite garbage value: the integer kernels mark the group's
+    exponent NaN, so every output row of that activation row is NaN, the other activation row is untouched."""
+    for kernel in ("tc", "imma"):
+        monkeypatch.setenv("JANGQ_GEMV_KERNEL", kernel)
+        x, wq, s, b = make_case(256, 1024, 8, 64, 2, torch.bfloat16, seed=5)
+        ref = reference(x, wq, s, b, 8, 64)
+        x[1, 77] = float("inf")
+        y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=8).float().cpu().numpy()
+        assert np.all(np.isnan(y[1]))
+        assert np.abs(y[0] - ref[0]).max() <= 1e-2 * np.abs(ref[0]).max()
