@@ -210,6 +210,37 @@ int jq_gather_qgemv(const void* x, int act_dtype, int64_t ldx, int x_div, const 
                     int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
                     int64_t ldy, jq_stream_t stream);
 
+/* The same over two expert banks of equal shape that read the same rows of x (gate and up of the
+ * routed SwiGLU experts, dsv41/model.py:1216-1220) in one launch: y[p] from the first tables, y2[p]
+ * from the second (all four second-bank arguments NULL: one bank).  flags as for jq_qgemv_ex. */
+int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert,
+                     int64_t pairs, const uint32_t* const* codes_tab, const void* const* scales_tab,
+                     const void* const* biases_tab, const uint32_t* const* codes_tab2,
+                     const void* const* scales_tab2, const void* const* biases_tab2,
+                     const int32_t* bits_tab, int num_experts, int sidecar_dtype, int64_t N, int64_t K,
+                     int bits, int group_size, void* y, void* y2, int64_t ldy, int flags,
+                     jq_stream_t stream);
+
+/* Router of the few-token (decode) path, one launch: logits = x . router_w^T (f32 accumulation,
+ * rounded to the activation type), softmax over the experts in f32, the k largest scores with ties
+ * to the lower expert id (jang_tools/dsv41/metal_decode.py:1141), weights p / (sum p + 1e-20) * scale
+ * when renorm != 0, else p * scale (dots3/ops.py:149-162).  x [T, H] and router_w [num_experts, H]
+ * are of the activation type; idx_out int32 [T, k], w_out f32 [T, k].  num_experts <= 1024.
+ * counters: T device int32 that are zero when the call starts; the call leaves them zero (the CTAs of a
+ * token count themselves in and the last one selects).  logits_ws: T*num_experts floats of scratch. */
+int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H, const void* router_w,
+                 int num_experts, int k, int renorm, float scale, int32_t* idx_out, float* w_out,
+                 int32_t* counters, float* logits_ws, jq_stream_t stream);
+
+/* out[t, :] = v / sqrt(mean(v^2) + eps) with v = x[t, :] + sum_{j<k} y[t*k + j, :], f32 arithmetic,
+ * activation type out; y is f32 when y_f32 != NULL (then k = 1), else of the activation type.  With k > 1
+ * it is also the unweighted combine of the routed experts' k slot rows (their routing weights are applied
+ * before the down projection, dsv41/model.py:1222-1226).  No counterpart in the reference's quantized
+ * path: it is the residual + norm glue between the quantized blocks of the synthetic decode stacks
+ * (jangq_b200/stacks.py), one launch instead of several.  H <= 4096. */
+int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k, int64_t T, int64_t H,
+                        float eps, void* out, int act_dtype, jq_stream_t stream);
+
 /* Reads the device-side status word (synchronises the device).  JQ_ETIMEOUT when a
  * kernel's bounded wait on a copy in flight ran out since the library was loaded.
  * No counterpart in the reference: its Metal path has no device-side waits. */

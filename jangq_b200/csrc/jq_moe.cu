@@ -6,6 +6,29 @@
 
 namespace jq {
 
+// The small kernels of the few-token path are launched with programmatic stream serialization: their CTAs
+// may be scheduled while the predecessor still runs, and they touch memory only after griddepcontrol.wait
+// (which returns once the predecessor has completed and flushed), so the launch latency of a chain of
+// tiny dependent kernels overlaps.  The instruction is a no-op for a launch without the attribute.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 constexpr int SORT_THREADS = 1024;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 
@@ -120,6 +143,7 @@ __global__ void swiglu_kernel(const AT* __restrict__ g, const AT* __restrict__ u
                               const float* __restrict__ w, const int32_t* __restrict__ order,
                               const int32_t* __restrict__ count, AT* __restrict__ h, int64_t ld_out, int cols, int max_rows,
                               float lim) {
+    pdl_enter();
     const int n = count ? min(*count, max_rows) : max_rows;
     for (int p = blockIdx.x; p < n; p += gridDim.x) {
         const float wt = w ? w[order ? order[p] : p] : 1.0f;
@@ -154,9 +178,181 @@ __global__ void combine_kernel(const AT* __restrict__ y, int64_t ldy, const int3
     }
 }
 
+
+// Router for few tokens (decode): logits[e] = x . Wr[e] in f32, rounded to the activation type (what
+// x @ Wr^T returns there), softmax over the experts in f32, the k largest scores (ties to the lower
+// id), w = p / (sum p + 1e-20) * scale  (dots3/ops.py:149-162; the plain softmax-top-k of the mlx-lm
+// switch layers).  One CTA per token; warps split the experts, warp 0 selects.
+constexpr int ROUTE_MAX_E = 1024;
+template <typename AT>
+__global__ void __launch_bounds__(256)
+route_kernel(const AT* __restrict__ x, int64_t ldx, const AT* __restrict__ wr, int H, int E, int k, int renorm,
+             float scale, int32_t* __restrict__ idx_out, float* __restrict__ w_out, float* __restrict__ ws_logits,
+             int* __restrict__ ws_count) {
+    // grid (T, ceil(E / 8)): warp w of CTA (t, b) computes the logit of expert 8b + w; the CTA that finishes
+    // last for its token (a counter, no waiting) runs the selection over all E logits
+    __shared__ float p[ROUTE_MAX_E];
+    __shared__ int is_last;
+    pdl_enter();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * 8 + warp;
+    if (e < E) {
+        const AT* xr = x + (int64_t)t * ldx;
+        const AT* wrow = wr + (int64_t)e * H;
+        float acc = 0.f;
+        for (int c = lane * 8; c < H; c += 256) {          // H % 8 == 0, 16-byte loads
+            const uint4 xv = *reinterpret_cast<const uint4*>(xr + c);
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + c));
+            const AT* xa = reinterpret_cast<const AT*>(&xv);
+            const AT* wa = reinterpret_cast<const AT*>(&wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(Elt<AT>::to_f32(xa[j]), Elt<AT>::to_f32(wa[j]), acc);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
+        if (lane == 0) ws_logits[(int64_t)t * E + e] = Elt<AT>::to_f32(Elt<AT>::from_f32(acc));
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(ws_count + t, 1);
+        is_last = prev == (int)gridDim.y - 1;
+        if (is_last) ws_count[t] = 0;                      // left at zero for the next call
+    }
+    __syncthreads();
+    if (!is_last || warp != 0) return;
+    __threadfence();
+    for (int i = lane; i < E; i += 32) p[i] = __ldcg(ws_logits + (int64_t)t * E + i);
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int i = lane; i < E; i += 32) mx = fmaxf(mx, p[i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float v = __expf(p[i] - mx);
+        p[i] = v;
+        sum += v;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+    const float inv_sum = 1.0f / sum;
+    __syncwarp();
+    float top_sum = 0.f, my_w = 0.f;
+    int my_idx = 0;
+    for (int j = 0; j < k; ++j) {
+        float bv = -1.f;
+        int bi = 0x7FFFFFFF;
+        for (int i = lane; i < E; i += 32) {
+            const float v = p[i];
+            if (v > bv) { bv = v; bi = i; }                // ascending i: the first maximum is the lowest id
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, d);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, d);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) p[bi] = -1.f;                       // taken
+        __syncwarp();
+        const float pv = bv * inv_sum;
+        top_sum += pv;
+        if (lane == j % 32) { my_w = pv; my_idx = bi; }
+        if (j % 32 == 31 || j == k - 1) {                  // flush this batch of (up to 32) selections
+            const int j0 = j - (j % 32);
+            if (lane <= j - j0) {
+                idx_out[(int64_t)t * k + j0 + lane] = my_idx;
+                w_out[(int64_t)t * k + j0 + lane] = my_w;  // raw p: normalised below
+            }
+        }
+    }
+    __syncwarp();
+    const float norm = renorm ? scale / (top_sum + 1e-20f) : scale;
+    for (int j = lane; j < k; j += 32) w_out[(int64_t)t * k + j] *= norm;
+}
+
+// out[t, :] = rms_norm(x[t, :] + sum_j y[t*k + j, :]) without weight, in f32: v / sqrt(mean(v^2) + eps), rounded
+// to the activation type; the k rows are added in slot order (k = 1: a plain residual).  Glue of the
+// synthetic decode stacks (residual + norm between the quantized blocks; with k > 1 also the unweighted
+// combine of the routed experts, whose routing weights were applied before the down projection); y is
+// f32 (y_f32 != NULL, k = 1) or of the activation type.
+template <typename AT>
+__global__ void __launch_bounds__(1024)
+residual_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, const float* __restrict__ y_f32, int k, int H,
+                        float eps, AT* __restrict__ out) {
+    __shared__ float part[32];
+    pdl_enter();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int PER = 4;                               // columns per thread held in registers (H <= 4096)
+    float v[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * 1024;
+        v[i] = 0.f;
+        if (c < H) {
+            float a = Elt<AT>::to_f32(x[(int64_t)t * H + c]);
+            if (y_f32) a += y_f32[(int64_t)t * H + c];
+            else
+                for (int j = 0; j < k; ++j) a += Elt<AT>::to_f32(y[((int64_t)t * k + j) * H + c]);
+            v[i] = a;
+            ss = fmaf(a, a, ss);
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) tot += part[i];
+    const float r = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = threadIdx.x + i * 1024;
+        if (c < H) out[(int64_t)t * H + c] = Elt<AT>::from_f32(v[i] * r);
+    }
+}
+
 }  // namespace jq
 
 extern "C" {
+
+int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H, const void* router_w, int num_experts,
+                 int k, int renorm, float scale, int32_t* idx_out, float* w_out, int32_t* counters, float* logits_ws,
+                 jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(T >= 0 && H > 0 && H % 8 == 0, JQ_EINVAL, "jq_moe_route needs H %% 8 == 0");
+    JQ_REQUIRE(num_experts > 0 && num_experts <= ROUTE_MAX_E, JQ_EUNSUPPORTED, "jq_moe_route takes at most %d experts",
+               ROUTE_MAX_E);
+    JQ_REQUIRE(k > 0 && k <= num_experts, JQ_EINVAL, "k must be in [1, num_experts]");
+    if (T == 0) return JQ_OK;
+    JQ_REQUIRE(x && router_w && idx_out && w_out && counters && logits_ws, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(ldx >= H && ldx % 8 == 0 && aligned(x, 16) && aligned(router_w, 16), JQ_EINVAL,
+               "x and the router weights must be 16-byte aligned with ldx %% 8 == 0");
+    JQ_REQUIRE(T <= 65535, JQ_EUNSUPPORTED, "jq_moe_route is the few-token path");
+    const dim3 grid((unsigned)T, (unsigned)((num_experts + 7) / 8));
+    JQ_DISPATCH_DTYPE16(act_dtype, AT,
+        JQ_CUDA_OK(launch_pdl(route_kernel<AT>, grid, dim3(256), 0, (cudaStream_t)stream, (const AT*)x, ldx,
+                              (const AT*)router_w, (int)H, num_experts, k, renorm, scale, idx_out, w_out, logits_ws,
+                              (int*)counters)))
+    return JQ_OK;
+}
+
+int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k, int64_t T, int64_t H, float eps, void* out,
+                        int act_dtype, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(T >= 0 && H > 0 && H <= 4096, JQ_EUNSUPPORTED, "jq_residual_rmsnorm takes rows of at most 4096 elements");
+    if (T == 0) return JQ_OK;
+    JQ_REQUIRE(x && out && (y || y_f32), JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(k >= 1 && (y_f32 == nullptr || k == 1), JQ_EINVAL, "k >= 1; an f32 addend is a single row");
+    JQ_REQUIRE(T <= 65535, JQ_EUNSUPPORTED, "at most 65535 rows");
+    JQ_DISPATCH_DTYPE16(act_dtype, AT,
+        JQ_CUDA_OK(launch_pdl(residual_rmsnorm_kernel<AT>, dim3((unsigned)T), dim3(1024), 0, (cudaStream_t)stream,
+                              (const AT*)x, (const AT*)y, y_f32, k, (int)H, eps, (AT*)out)))
+    return JQ_OK;
+}
+
 
 size_t jq_moe_sort_max_tiles(int64_t n_pairs, int num_experts, int tile_m) {
     if (n_pairs < 0 || num_experts < 0 || tile_m <= 0) return 0;
@@ -211,9 +407,9 @@ int jq_moe_swiglu(const void* gate, const void* up, int64_t ld_in, const float* 
     JQ_REQUIRE(gate && up && h, JQ_EINVAL, "null pointer");
     const int blocks = (int)(max_rows < 8 * 148 ? max_rows : 8 * 148);
     JQ_DISPATCH_DTYPE16(dtype, T,
-        (swiglu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gate, (const T*)up, ld_in, weights, order,
-                                                                     count, (T*)h, ld_out, (int)cols, (int)max_rows, limit)))
-    return check_launch("moe_swiglu");
+        JQ_CUDA_OK(launch_pdl(swiglu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gate,
+                              (const T*)up, ld_in, weights, order, count, (T*)h, ld_out, (int)cols, (int)max_rows, limit)))
+    return JQ_OK;
 }
 
 int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T, int k, int64_t D,

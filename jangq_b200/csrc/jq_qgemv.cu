@@ -86,14 +86,18 @@ qgemv_mma_kernel(const GemvArgs a, const GemvBatch bt) {
     const uint32_t* codes_g = bt.codes[mi];
     uint16_t* y16 = reinterpret_cast<uint16_t*>(bt.y[mi]);
     if (a.pair_expert) {
+        // the pair list is itself an output of the predecessor (the router): nothing is read before it is done
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int p = blockIdx.y;
         const int e = a.pair_expert[p];
         if (e < 0 || e >= a.num_experts) return;                      // expert of another rank
         if (a.bits_tab && a.bits_tab[e] != BITS) return;              // handled by the launch of its own width
-        codes_g = a.codes_tab[e];
-        sc16 = reinterpret_cast<const uint16_t*>(a.scales_tab[e]);
-        bi16 = reinterpret_cast<const uint16_t*>(a.biases_tab[e]);
+        const bool second = blockIdx.z != 0;                         // gate | up in one launch
+        codes_g = (second ? a.codes_tab2 : a.codes_tab)[e];
+        sc16 = reinterpret_cast<const uint16_t*>((second ? a.scales_tab2 : a.scales_tab)[e]);
+        bi16 = reinterpret_cast<const uint16_t*>((second ? a.biases_tab2 : a.biases_tab)[e]);
         xs16 += (int64_t)(p / a.x_div) * a.ldx;
+        if (second) y16 = reinterpret_cast<uint16_t*>(a.y2);
         y16 += (int64_t)p * ldy;
     }
 
@@ -307,9 +311,10 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
         const int e = a.pair_expert[p];
         if (e < 0 || e >= a.num_experts) return;
         if (a.bits_tab && a.bits_tab[e] != BITS) return;
-        codes_g = a.codes_tab[e];
-        scales_g = a.scales_tab[e];
-        biases_g = a.biases_tab[e];
+        const bool second = blockIdx.z != 0;
+        codes_g = (second ? a.codes_tab2 : a.codes_tab)[e];
+        scales_g = (second ? a.scales_tab2 : a.scales_tab)[e];
+        biases_g = (second ? a.biases_tab2 : a.biases_tab)[e];
         x_row0 = p / a.x_div;
         y_row0 = p;
     }
@@ -352,7 +357,8 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
         float v = acc[m];
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
-        if (lane == 0 && m < a.M) st_any(a.y, (y_row0 + m) * a.ldy + n, y_dtype, v);
+        if (lane == 0 && m < a.M)
+            st_any((a.pair_expert && blockIdx.z != 0) ? a.y2 : a.y, (y_row0 + m) * a.ldy + n, y_dtype, v);
     }
 }
 
@@ -387,6 +393,7 @@ static int gemv_kernel_choice() {
 
 template <typename AT, int BITS, int GS, int MT, int NW>
 static int launch_mma_cfg(GemvArgs a, GemvBatch bt, int pairs, int nbuf, cudaStream_t st, bool* launched) {
+    const unsigned banks = (a.pair_expert && a.codes_tab2) ? 2u : 1u;
     using Geo = GemvGeom<BITS, GS, MT>;
     *launched = false;
     const int sb = Geo::stage_bytes(a.M);
@@ -407,7 +414,7 @@ static int launch_mma_cfg(GemvArgs a, GemvBatch bt, int pairs, int nbuf, cudaStr
         bt.blk_end[i] = (int)grid;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid, (unsigned)pairs);
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)pairs, banks);
     cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -579,7 +586,9 @@ int qgemv_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
 int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert,
                           int64_t pairs, const uint32_t* const* codes_tab, const void* const* scales_tab,
                           const void* const* biases_tab, const int32_t* bits_tab, int num_experts, int sidecar_dtype,
-                          int64_t N, int64_t K, int bits, int gs, void* y, int64_t ldy, cudaStream_t st) {
+                          int64_t N, int64_t K, int bits, int gs, void* y, int64_t ldy, cudaStream_t st,
+                          const uint32_t* const* codes_tab2 = nullptr, const void* const* scales_tab2 = nullptr,
+                          const void* const* biases_tab2 = nullptr, void* y2 = nullptr, int flags = 0) {
     int rc = check_quant_shape(N, K, bits, gs);
     if (rc != JQ_OK) return rc;
     JQ_REQUIRE(valid_dtype(act_dtype) && valid_dtype(sidecar_dtype), JQ_EINVAL, "bad dtype");
@@ -595,6 +604,10 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
     a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.M = 1; a.G = (int)(K / gs);
     a.pair_expert = pair_expert; a.codes_tab = codes_tab; a.scales_tab = scales_tab; a.biases_tab = biases_tab;
     a.bits_tab = bits_tab; a.x_div = x_div; a.num_experts = num_experts; a.ksplit = 1;
+    JQ_REQUIRE((codes_tab2 == nullptr) == (y2 == nullptr) && (codes_tab2 == nullptr || (scales_tab2 && biases_tab2)), JQ_EINVAL,
+               "the second bank needs its three tables and its output");
+    a.codes_tab2 = codes_tab2; a.scales_tab2 = scales_tab2; a.biases_tab2 = biases_tab2; a.y2 = y2;
+    a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
     GemvBatch bt = {};        // one entry: row count and output of every pair's matrix
     bt.count = 1; bt.y[0] = y; bt.N[0] = N; bt.ldy[0] = ldy;
     // the per-expert base pointers are not known on the host: the fast path relies on the caller's
@@ -607,7 +620,7 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
         if (rc != JQ_OK) return rc;
     }
     if (!launched) {
-        dim3 grid((unsigned)((N + 3) / 4), (unsigned)pairs);
+        dim3 grid((unsigned)((N + 3) / 4), (unsigned)pairs, codes_tab2 ? 2u : 1u);
         JQ_DISPATCH_BITS(bits, B,
             (qgemv_simple_kernel<B><<<grid, 128, 0, st>>>(a, act_dtype, sidecar_dtype, act_dtype, gs)))
         rc = check_launch("gather qgemv (general)");
@@ -654,6 +667,16 @@ int jq_gather_qgemv(const void* x, int act_dtype, int64_t ldx, int x_div, const 
     return jq::gather_qgemv_dispatch(x, act_dtype, ldx, x_div, pair_expert, pairs, codes_tab, scales_tab, biases_tab,
                                      bits_tab, num_experts, sidecar_dtype, N, K, bits, group_size, y, ldy,
                                      (cudaStream_t)stream);
+}
+
+int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert, int64_t pairs,
+                     const uint32_t* const* codes_tab, const void* const* scales_tab, const void* const* biases_tab,
+                     const uint32_t* const* codes_tab2, const void* const* scales_tab2, const void* const* biases_tab2,
+                     const int32_t* bits_tab, int num_experts, int sidecar_dtype, int64_t N, int64_t K, int bits,
+                     int group_size, void* y, void* y2, int64_t ldy, int flags, jq_stream_t stream) {
+    return jq::gather_qgemv_dispatch(x, act_dtype, ldx, x_div, pair_expert, pairs, codes_tab, scales_tab, biases_tab,
+                                     bits_tab, num_experts, sidecar_dtype, N, K, bits, group_size, y, ldy,
+                                     (cudaStream_t)stream, codes_tab2, scales_tab2, biases_tab2, y2, flags);
 }
 
 int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,

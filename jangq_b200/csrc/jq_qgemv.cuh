@@ -22,6 +22,11 @@ struct GemvArgs {
     const void* const* biases_tab;
     const int32_t* bits_tab;      // optional: experts whose width differs from the launch's are skipped
     int x_div, num_experts;
+    // optional second bank (gridDim.z == 2, blockIdx.z == 1): same shapes, own tables and output y2
+    const uint32_t* const* codes_tab2;
+    const void* const* scales_tab2;
+    const void* const* biases_tab2;
+    void* y2;
     int ksplit;   // tensor-memory kernel: CTAs of a cluster that split K
     int* status;  // device status word, set to 1 when a bounded wait ran out (tensor-memory kernel)
 };

@@ -453,7 +453,7 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                 const int gq0 = GS == 64 ? 0 : 2 * (pair & 1);        // ... and that group's place in the sidecar quad
                 JQ_PROF_DECL(t1);
                 const int pi = pair % RP;
-                ok = __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(d_full + pi, (uint32_t)(pair / RP) & 1u, POLLS));
+                ok = mbar_wait_warp(d_full + pi, (uint32_t)(pair / RP) & 1u, POLLS, true);   // one lane polls
                 JQ_PROF_ADD(warp == W_EPI && lane == 0, 7, t1);       // 7: epilogue waits for sums
                 if (!ok) break;
                 tc_fence_after();

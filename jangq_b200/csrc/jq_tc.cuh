@@ -126,6 +126,16 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Warp-wide bounded wait: lane 0 polls, the outcome is broadcast (32 lanes polling the same mbarrier
+// only multiply the shared-memory traffic of the spin).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t max_polls, bool relaxed) {
+    int okv = 1;
+    if ((threadIdx.x & 31) == 0) okv = relaxed ? mbar_wait_relaxed(bar, parity, max_polls) : mbar_wait(bar, parity, max_polls);
+    okv = __shfl_sync(0xFFFFFFFFu, okv, 0);
+    __syncwarp();      // orders the other lanes' reads after lane 0's acquire
+    return okv != 0;
+}
+
 // registers -> tensor memory: lane (base + threadIdx%32), 32 consecutive columns
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(

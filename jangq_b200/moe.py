@@ -158,19 +158,45 @@ def _moe_gemm(x_sorted: torch.Tensor, sp: SortedPairs, bank: ExpertBank) -> torc
     return y
 
 
-def _gather_qgemv(x: torch.Tensor, x_div: int, pair_expert: torch.Tensor, bank: ExpertBank) -> torch.Tensor:
+def _gather_qgemv(x: torch.Tensor, x_div: int, pair_expert: torch.Tensor, bank: ExpertBank,
+                  may_skip: bool = True, flags: int = 0) -> torch.Tensor:
+    """y[p] = deq(W[pair_expert[p]]) . x[p // x_div].  Pairs whose expert is not in the bank are skipped by
+    the kernel; their rows are zero (may_skip=False: the caller knows every pair is local, no memset)."""
     lib = _lib.load()
     bank = bank._sidecars_as(x.dtype)
     P = pair_expert.numel()
-    y = torch.zeros((P, bank.N), dtype=x.dtype, device=x.device)
+    alloc = torch.zeros if (may_skip or len(bank.distinct_bits) > 1) else torch.empty
+    y = alloc((P, bank.N), dtype=x.dtype, device=x.device)
     for bits in bank.distinct_bits:
-        _lib.check(lib.jq_gather_qgemv(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), x_div, pair_expert.data_ptr(),
-                                       P, bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
-                                       bank.biases_tab.data_ptr(),
-                                       bank.bits_tab.data_ptr() if bank.bits_tab is not None else None, bank.E,
-                                       _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
-                                       y.data_ptr(), y.stride(0), _lib.stream_ptr(x.device)))
+        _lib.check(lib.jq_gather_qgemv2(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), x_div, pair_expert.data_ptr(),
+                                        P, bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
+                                        bank.biases_tab.data_ptr(), None, None, None,
+                                        bank.bits_tab.data_ptr() if bank.bits_tab is not None else None, bank.E,
+                                        _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
+                                        y.data_ptr(), None, y.stride(0), flags, _lib.stream_ptr(x.device)))
     return y
+
+
+def _gather_qgemv_pair(x: torch.Tensor, x_div: int, pair_expert: torch.Tensor, bank_a: ExpertBank, bank_b: ExpertBank,
+                       may_skip: bool = True, flags: int = 0):
+    """Two banks of equal shape and width (gate, up) over the same rows of x in one launch."""
+    same = (bank_a.N == bank_b.N and bank_a.K == bank_b.K and bank_a.group_size == bank_b.group_size and
+            bank_a.E == bank_b.E and bank_a.bits_tab is None and bank_b.bits_tab is None and
+            bank_a.distinct_bits == bank_b.distinct_bits and len(bank_a.distinct_bits) == 1)
+    if not same:
+        return (_gather_qgemv(x, x_div, pair_expert, bank_a, may_skip, flags),
+                _gather_qgemv(x, x_div, pair_expert, bank_b, may_skip, flags))
+    lib = _lib.load()
+    a, b = bank_a._sidecars_as(x.dtype), bank_b._sidecars_as(x.dtype)
+    P = pair_expert.numel()
+    alloc = torch.zeros if may_skip else torch.empty
+    y = alloc((2, P, a.N), dtype=x.dtype, device=x.device)
+    _lib.check(lib.jq_gather_qgemv2(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), x_div, pair_expert.data_ptr(), P,
+                                    a.codes_tab.data_ptr(), a.scales_tab.data_ptr(), a.biases_tab.data_ptr(),
+                                    b.codes_tab.data_ptr(), b.scales_tab.data_ptr(), b.biases_tab.data_ptr(), None, a.E,
+                                    _lib.dtype_id(a.sidecar_dtype), a.N, a.K, a.distinct_bits[0], a.group_size,
+                                    y[0].data_ptr(), y[1].data_ptr(), y.stride(1), flags, _lib.stream_ptr(x.device)))
+    return y[0], y[1]
 
 
 def gather_qmm(x: torch.Tensor, w, scales: torch.Tensor | None = None, biases: torch.Tensor | None = None,
@@ -230,15 +256,77 @@ def route_softmax_topk(logits: torch.Tensor, k: int, renorm: bool = True, scale:
     return idx.to(torch.int32), (w * scale).float()
 
 
+def route_from_hidden(x: torch.Tensor, router_w: torch.Tensor, k: int, renorm: bool = True, scale: float = 1.0):
+    """route_softmax_topk(x @ router_w.T, k) in one launch for few tokens: (idx int32 [T, k], w f32 [T, k]).
+    x [T, H] and router_w [E, H] share a 16-bit dtype; E <= 1024."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, router_w)
+    if x.dtype != router_w.dtype or x.dtype not in (torch.bfloat16, torch.float16):
+        raise JangqError(_lib.JQ_EINVAL, "route_from_hidden: x and router_w must share a 16-bit dtype")
+    T, H = x.shape
+    E = router_w.shape[0]
+    x, router_w = x.contiguous(), router_w.contiguous()
+    idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+    w = torch.empty((T, k), dtype=torch.float32, device=dev)
+    cnt, ws = _route_workspace(dev, T, E)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_moe_route(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), T, H, router_w.data_ptr(), E, k,
+                                    1 if renorm else 0, float(scale), idx.data_ptr(), w.data_ptr(), cnt.data_ptr(),
+                                    ws.data_ptr(), _lib.stream_ptr(dev)))
+    return idx, w
+
+
+_ROUTE_WS = {}
+
+
+def _route_workspace(dev, T: int, E: int):
+    """(counters, logits scratch) of the router kernel, kept per device: calls on one stream follow each
+    other, and the kernel leaves the counters at zero."""
+    key = (dev.type, dev.index)
+    cnt, ws = _ROUTE_WS.get(key, (None, None))
+    if cnt is None or cnt.numel() < T:
+        cnt = torch.zeros(max(T, 1024), dtype=torch.int32, device=dev)
+    if ws is None or ws.numel() < T * E:
+        ws = torch.empty(max(T * E, 1 << 16), dtype=torch.float32, device=dev)
+    _ROUTE_WS[key] = (cnt, ws)
+    return cnt, ws
+
+
+def residual_rmsnorm(x: torch.Tensor, y: torch.Tensor, eps: float | None = None, k: int = 1) -> torch.Tensor:
+    """rms_norm(x + y) without weight, f32 arithmetic, one launch; y [T, H] may be f32 or x's dtype, or
+    (k > 1, x's dtype) the [T*k, H] slot rows of the routed experts, which are summed in slot order.  Glue of
+    the synthetic decode stacks, not part of the reference's quantized path."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, y)
+    T, H = x.shape
+    x, y = x.contiguous(), y.contiguous()
+    if y.shape != (T * k, H):
+        raise JangqError(_lib.JQ_EINVAL, f"residual_rmsnorm: y must be [{T * k}, {H}], got {tuple(y.shape)}")
+    if eps is None:
+        eps = torch.finfo(x.dtype).eps
+    out = torch.empty_like(x)
+    yf = y.dtype == torch.float32
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_residual_rmsnorm(x.data_ptr(), None if yf else y.data_ptr(), y.data_ptr() if yf else None, k, T, H,
+                                           float(eps), out.data_ptr(), _lib.dtype_id(x.dtype), _lib.stream_ptr(dev)))
+    return out
+
+
 def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertBank, up: ExpertBank,
               down: ExpertBank, swiglu_limit: float = 0.0, shared=None, expert_base: int = 0,
-              out_f32: bool = False) -> torch.Tensor:
+              out_f32: bool = False, all_local: bool | None = None, return_slots: bool = False,
+              static_weights: bool = False) -> torch.Tensor:
     """Routed SwiGLU experts: out[t] = sum_j down_e( silu(gate_e x_t) * up_e x_t * w[t, j] ), e = idx[t, j].
 
     x [T, H] bf16/f16; idx [T, k] int; w [T, k] f32.  Follows dsv41/model.py:1206-1245.  With
     `expert_base` the banks hold experts [expert_base, expert_base + E) only and the other
     pairs contribute nothing (expert parallelism).  `shared` = (gate, up, down) JANGLinear-like
     modules of an always-on expert, added in f32.  Returns [T, H] in x.dtype (f32 if out_f32).
+    all_local=True is the caller's promise that every idx is an expert of these banks (single-rank
+    decode), which saves the zero-fill of the rows skipped pairs would leave untouched.  return_slots=True
+    (few-token path only) returns the [T*k, H] rows before the combine, for a caller that fuses the sum.
+    static_weights=True promises that the expert weights are not written by earlier work on the stream, so
+    the few-token mat-vecs may prefetch them while their predecessor still runs.
     """
     lib = _lib.load()
     dev = _lib.require_cuda(x, idx, w)
@@ -264,12 +352,15 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
             inv_ptr = sp.inv.data_ptr()
         else:
             local = idx32 - expert_base if expert_base else idx32
-            g = _gather_qgemv(x, k, local, gate)
-            u = _gather_qgemv(x, k, local, up)
+            may_skip = all_local is not True
+            flags = _lib.JQ_GEMV_STATIC_WEIGHTS if static_weights else 0
+            g, u = _gather_qgemv_pair(x, k, local, gate, up, may_skip, flags)
             h = torch.empty((P, I), dtype=x.dtype, device=dev)
             _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), None, None,
                                          h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
-            y = _gather_qgemv(h, 1, local, down)
+            y = _gather_qgemv(h, 1, local, down, may_skip, flags)
+            if return_slots and shared is None:
+                return y        # [T*k, H]: the caller sums the k rows of a token (routing weights already applied)
             # pairs of other ranks' experts were skipped by the kernels and their rows stay zero
             inv_ptr = None
         need_f32 = out_f32 or shared is not None

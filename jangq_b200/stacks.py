@@ -67,19 +67,30 @@ class MoEDecodeStack:
 
     def step(self, x: torch.Tensor) -> torch.Tensor:
         """One token per row of x ([T, H] bf16) through every layer's quantized matmuls."""
+        from .ops import qgemv_fused
+        T = x.shape[0]
         for lay in self.layers:
-            q = lay["q"](x)
-            lay["k"](x)
-            lay["v"](x)
-            x = torch.nn.functional.rms_norm(x + lay["o"](q), (self.H,))
-            logits = torch.matmul(x, lay["router"].t()).float()
-            idx, w = moe.route_softmax_topk(logits, self.k)
+            if T <= 16:     # q/k/v read the same activations: one fused launch
+                outs = [torch.empty((T, lay[n].out_features), dtype=x.dtype, device=x.device) for n in "qkv"]
+                qgemv_fused(x, [lay[n] for n in "qkv"], outs, 1)
+                q = outs[0]
+            else:
+                q = lay["q"](x)
+                lay["k"](x)
+                lay["v"](x)
+            x = moe.residual_rmsnorm(x, lay["o"](q))
+            idx, w = moe.route_from_hidden(x, lay["router"], self.k)
+            if self.world == 1 and T * self.k < moe.SORT_THRESHOLD:
+                y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], all_local=True, return_slots=True,
+                                  static_weights=True)
+                x = moe.residual_rmsnorm(x, y, k=self.k)     # combine + residual + norm in one launch
+                continue
             if self.world == 1:
-                y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True)
+                y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True, all_local=True)
             else:
                 y = moe_ep.gathered_tokens(x, idx, w, moe_ep.partial_experts_fn(lay["gate"], lay["up"], lay["down"],
                                                                                 self.base), group=self.group)
-            x = torch.nn.functional.rms_norm(x + y.to(x.dtype), (self.H,))
+            x = moe.residual_rmsnorm(x, y)
         return x
 
 

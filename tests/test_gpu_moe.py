@@ -178,6 +178,79 @@ def test_moe_expert_parallel_shards_sum_to_full():
         assert float((full - parts).abs().max()) <= 1e-5 * float(full.abs().max()) + 1e-6
 
 
+@pytest.mark.parametrize("T,E,k,H", ((1, 128, 8, 2048), (3, 16, 4, 256), (5, 1000, 32, 512), (2, 40, 40, 128)))
+def test_route_from_hidden_matches_unfused_router(T, E, k, H):
+    """The one-launch router against x @ W^T (activation-type logits) -> oracle softmax-top-k: same experts
+    (up to swaps between scores closer than the accumulation error of the logits), same weights."""
+    from jangq_b200.moe import route_from_hidden
+    rng = np.random.default_rng(T + E)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    wr = torch.from_numpy((rng.standard_normal((E, H)) * 0.05).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    idx, w = route_from_hidden(x, wr, k)
+    logits = (x.float() @ wr.float().t()).to(torch.bfloat16).float().cpu().numpy()
+    idx_ref, w_ref = jo.route_softmax_topk(logits, k)
+    idx, w = idx.cpu().numpy(), w.cpu().numpy()
+    assert idx.shape == (T, k) and w.shape == (T, k)
+    for t in range(T):
+        assert len(set(idx[t].tolist())) == k and idx[t].min() >= 0 and idx[t].max() < E
+        # same set of experts unless the k-th and (k+1)-th logits are within one rounding step of each other
+        srt = np.sort(logits[t])[::-1]
+        gap = srt[k - 1] - srt[k] if k < E else 1.0
+        if gap > 2.0 ** -7 * max(1.0, abs(srt[k - 1])):
+            assert set(idx[t].tolist()) == set(idx_ref[t].tolist())
+            order = {e: i for i, e in enumerate(idx_ref[t].tolist())}
+            wr_sorted = np.array([w_ref[t][order[e]] for e in idx[t].tolist()])
+            assert np.allclose(w[t], wr_sorted, rtol=2e-2, atol=1e-6)
+        assert abs(w[t].sum() - 1.0) < 1e-4
+        assert np.all(np.diff(w[t]) <= 1e-7)          # scores come out in descending order
+
+
+def test_residual_rmsnorm_matches_torch():
+    from jangq_b200.moe import residual_rmsnorm
+    torch.manual_seed(0)
+    x = torch.randn(5, 2048, device=DEV).to(torch.bfloat16)
+    for y in (torch.randn(5, 2048, device=DEV), torch.randn(5, 2048, device=DEV).to(torch.bfloat16)):
+        out = residual_rmsnorm(x, y)
+        v = x.float() + y.float()
+        ref = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + torch.finfo(torch.bfloat16).eps)
+        assert out.dtype == torch.bfloat16
+        assert (out.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max()
+    # k slot rows per token (the unweighted combine of the routed experts), H not a multiple of 1024
+    xs = torch.randn(3, 1536, device=DEV).to(torch.bfloat16)
+    ys = torch.randn(3 * 8, 1536, device=DEV).to(torch.bfloat16)
+    out = residual_rmsnorm(xs, ys, k=8)
+    v = xs.float() + ys.float().view(3, 8, 1536).sum(1)
+    ref = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + torch.finfo(torch.bfloat16).eps)
+    assert (out.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max()
+
+
+@pytest.mark.parametrize("bits", (2, 6))
+def test_gather_pair_equals_two_single_gathers(bits):
+    """gate and up in one launch (jq_gather_qgemv2) are bit-identical to two launches."""
+    from jangq_b200.moe import _gather_qgemv, _gather_qgemv_pair
+    E, I, H, P = 8, 192, 512, 6
+    gate, _ = make_bank(E, I, H, bits, 64, seed=21)
+    up, _ = make_bank(E, I, H, bits, 64, seed=22)
+    rng = np.random.default_rng(1)
+    x = torch.from_numpy(rng.standard_normal((3, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    pe = torch.tensor([0, 7, 3, 3, 9, 1], dtype=torch.int32, device=DEV)     # 9: not in the bank, skipped
+    g2, u2 = _gather_qgemv_pair(x, 2, pe, gate, up)
+    g1, u1 = _gather_qgemv(x, 2, pe, gate), _gather_qgemv(x, 2, pe, up)
+    assert torch.equal(g1, g2) and torch.equal(u1, u2)
+    assert torch.count_nonzero(g2[4]) == 0 and torch.count_nonzero(u2[4]) == 0
+    assert P == pe.numel()
+
+
+def test_decode_stack_step_is_finite_and_deterministic():
+    from jangq_b200.stacks import MoEDecodeStack
+    st = MoEDecodeStack(layers=2, hidden=512, q_heads=4, kv_heads=2, head_dim=128, experts=16, inter=256, topk=4,
+                        device=DEV)
+    x = torch.randn(1, 512, device=DEV, generator=torch.Generator(device=DEV).manual_seed(0)).to(torch.bfloat16)
+    a, b = st.step(x), st.step(x)
+    assert torch.isfinite(a.float()).all() and torch.equal(a, b)
+    _lib.check(_lib.load().jq_device_status())
+
+
 def test_device_status_clean_after_moe():
     torch.cuda.synchronize()
     assert _lib.load().jq_device_status() == 0
