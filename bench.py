@@ -334,8 +334,9 @@ def run_moe(args, device, world, rank, barrier):
     from jangq_b200.stacks import MoEDecodeStack
     stack = MoEDecodeStack(device=device, rank=rank, world=world)
     g = torch.Generator(device=device)
-    g.manual_seed(11 + rank)
-    x = torch.randn((1, stack.H), generator=g, device=device).to(torch.bfloat16)
+    g.manual_seed(11)
+    # one token per GPU and step; with N > 1 every rank carries the rows of all N tokens (same seed everywhere)
+    x = torch.randn((world, stack.H), generator=g, device=device).to(torch.bfloat16)
     out = stack.step(x)                                   # eager warm-up (sets function attributes)
     torch.cuda.synchronize()
     graph = None
@@ -408,7 +409,8 @@ def run_moe(args, device, world, rank, barrier):
             "per_gpu_GBps": gbs, "hbm_frac": gbs / peak, "graph": graph is not None, "finite": finite,
             "workload": "config3 MoE stack, batch-1 decode per GPU: 48 layers x [q,k,v,o @6b + bf16 router + top-8 of "
                         "128 experts (768x2048 gate/up, 2048x768 down) @2b], group 64; experts sharded E/N per GPU, "
-                        "tokens all-gathered and partial sums reduce-scattered (NCCL) per layer; attention core not run"}
+                        "N>1: every rank runs the replicated dense blocks on the N tokens of the step, its own experts on "
+                        "them, one NCCL all-reduce of the partial sums per layer; attention core not run"}
 
 
 def main():

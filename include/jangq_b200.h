@@ -203,7 +203,7 @@ int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* 
 
 /* Unsorted gather mat-vec for few pairs (the reference's path below its sort threshold of 64,
  * dsv41/model.py:1206, and its fused decode kernels): y[p, :] = deq(W[pair_expert[p]]) .
- * x[p / x_div, :], p < pairs.  Pairs whose expert is outside [0, num_experts) are skipped. */
+ * x[p / x_div, :], p < pairs.  Pairs whose expert is outside [0, num_experts) get a zero row. */
 int jq_gather_qgemv(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert,
                     int64_t pairs, const uint32_t* const* codes_tab, const void* const* scales_tab,
                     const void* const* biases_tab, const int32_t* bits_tab, int num_experts,
@@ -212,13 +212,16 @@ int jq_gather_qgemv(const void* x, int act_dtype, int64_t ldx, int x_div, const 
 
 /* The same over two expert banks of equal shape that read the same rows of x (gate and up of the
  * routed SwiGLU experts, dsv41/model.py:1216-1220) in one launch: y[p] from the first tables, y2[p]
- * from the second (all four second-bank arguments NULL: one bank).  flags as for jq_qgemv_ex. */
+ * from the second (all four second-bank arguments NULL: one bank).  pair_expert holds global expert ids
+ * and the tables describe the experts [expert_base, expert_base + num_experts) (expert parallelism).
+ * Pairs of other experts get a zero row here and in jq_gather_qgemv (the caller need not clear y).
+ * flags as for jq_qgemv_ex. */
 int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const int32_t* pair_expert,
                      int64_t pairs, const uint32_t* const* codes_tab, const void* const* scales_tab,
                      const void* const* biases_tab, const uint32_t* const* codes_tab2,
                      const void* const* scales_tab2, const void* const* biases_tab2,
                      const int32_t* bits_tab, int num_experts, int sidecar_dtype, int64_t N, int64_t K,
-                     int bits, int group_size, void* y, void* y2, int64_t ldy, int flags,
+                     int bits, int group_size, void* y, void* y2, int64_t ldy, int expert_base, int flags,
                      jq_stream_t stream);
 
 /* Router of the few-token (decode) path, one launch: logits = x . router_w^T (f32 accumulation,

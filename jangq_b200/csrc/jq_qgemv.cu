@@ -89,10 +89,14 @@ qgemv_mma_kernel(const GemvArgs a, const GemvBatch bt) {
         // the pair list is itself an output of the predecessor (the router): nothing is read before it is done
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int p = blockIdx.y;
-        const int e = a.pair_expert[p];
-        if (e < 0 || e >= a.num_experts) return;                      // expert of another rank
-        if (a.bits_tab && a.bits_tab[e] != BITS) return;              // handled by the launch of its own width
+        const int e = a.pair_expert[p] - a.expert_base;
         const bool second = blockIdx.z != 0;                         // gate | up in one launch
+        if (e < 0 || e >= a.num_experts) {                            // expert of another rank: the pair's row is zero
+            uint16_t* yz = reinterpret_cast<uint16_t*>(second ? a.y2 : bt.y[0]) + (int64_t)p * ldy + n0;
+            for (int r = threadIdx.x; r < rows_valid; r += blockDim.x) yz[r] = 0;
+            return;
+        }
+        if (a.bits_tab && a.bits_tab[e] != BITS) return;              // handled by the launch of its own width
         codes_g = (second ? a.codes_tab2 : a.codes_tab)[e];
         sc16 = reinterpret_cast<const uint16_t*>((second ? a.scales_tab2 : a.scales_tab)[e]);
         bi16 = reinterpret_cast<const uint16_t*>((second ? a.biases_tab2 : a.biases_tab)[e]);
@@ -308,10 +312,14 @@ qgemv_simple_kernel(const GemvArgs a, int x_dtype, int sc_dtype, int y_dtype, in
     int64_t x_row0 = 0, y_row0 = 0;
     if (a.pair_expert) {
         const int p = blockIdx.y;
-        const int e = a.pair_expert[p];
-        if (e < 0 || e >= a.num_experts) return;
-        if (a.bits_tab && a.bits_tab[e] != BITS) return;
+        const int e = a.pair_expert[p] - a.expert_base;
         const bool second = blockIdx.z != 0;
+        if (e < 0 || e >= a.num_experts) {                            // expert of another rank: zero output
+            if (lane == 0)
+                for (int m = 0; m < a.M; ++m) st_any(second ? a.y2 : a.y, (int64_t)(p + m) * a.ldy + n, y_dtype, 0.f);
+            return;
+        }
+        if (a.bits_tab && a.bits_tab[e] != BITS) return;
         codes_g = (second ? a.codes_tab2 : a.codes_tab)[e];
         scales_g = (second ? a.scales_tab2 : a.scales_tab)[e];
         biases_g = (second ? a.biases_tab2 : a.biases_tab)[e];
@@ -588,7 +596,8 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
                           const void* const* biases_tab, const int32_t* bits_tab, int num_experts, int sidecar_dtype,
                           int64_t N, int64_t K, int bits, int gs, void* y, int64_t ldy, cudaStream_t st,
                           const uint32_t* const* codes_tab2 = nullptr, const void* const* scales_tab2 = nullptr,
-                          const void* const* biases_tab2 = nullptr, void* y2 = nullptr, int flags = 0) {
+                          const void* const* biases_tab2 = nullptr, void* y2 = nullptr, int flags = 0,
+                          int expert_base = 0) {
     int rc = check_quant_shape(N, K, bits, gs);
     if (rc != JQ_OK) return rc;
     JQ_REQUIRE(valid_dtype(act_dtype) && valid_dtype(sidecar_dtype), JQ_EINVAL, "bad dtype");
@@ -608,6 +617,7 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
                "the second bank needs its three tables and its output");
     a.codes_tab2 = codes_tab2; a.scales_tab2 = scales_tab2; a.biases_tab2 = biases_tab2; a.y2 = y2;
     a.pdl = (flags & JQ_GEMV_STATIC_WEIGHTS) ? 1 : 0;
+    a.expert_base = expert_base;
     GemvBatch bt = {};        // one entry: row count and output of every pair's matrix
     bt.count = 1; bt.y[0] = y; bt.N[0] = N; bt.ldy[0] = ldy;
     // the per-expert base pointers are not known on the host: the fast path relies on the caller's
@@ -673,10 +683,10 @@ int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const
                      const uint32_t* const* codes_tab, const void* const* scales_tab, const void* const* biases_tab,
                      const uint32_t* const* codes_tab2, const void* const* scales_tab2, const void* const* biases_tab2,
                      const int32_t* bits_tab, int num_experts, int sidecar_dtype, int64_t N, int64_t K, int bits,
-                     int group_size, void* y, void* y2, int64_t ldy, int flags, jq_stream_t stream) {
+                     int group_size, void* y, void* y2, int64_t ldy, int expert_base, int flags, jq_stream_t stream) {
     return jq::gather_qgemv_dispatch(x, act_dtype, ldx, x_div, pair_expert, pairs, codes_tab, scales_tab, biases_tab,
                                      bits_tab, num_experts, sidecar_dtype, N, K, bits, group_size, y, ldy,
-                                     (cudaStream_t)stream, codes_tab2, scales_tab2, biases_tab2, y2, flags);
+                                     (cudaStream_t)stream, codes_tab2, scales_tab2, biases_tab2, y2, flags, expert_base);
 }
 
 int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,

@@ -22,6 +22,7 @@ struct GemvArgs {
     const void* const* biases_tab;
     const int32_t* bits_tab;      // optional: experts whose width differs from the launch's are skipped
     int x_div, num_experts;
+    int expert_base;              // pair_expert holds global ids; this bank owns [expert_base, expert_base + num_experts)
     // optional second bank (gridDim.z == 2, blockIdx.z == 1): same shapes, own tables and output y2
     const uint32_t* const* codes_tab2;
     const void* const* scales_tab2;

@@ -159,43 +159,42 @@ def _moe_gemm(x_sorted: torch.Tensor, sp: SortedPairs, bank: ExpertBank) -> torc
 
 
 def _gather_qgemv(x: torch.Tensor, x_div: int, pair_expert: torch.Tensor, bank: ExpertBank,
-                  may_skip: bool = True, flags: int = 0) -> torch.Tensor:
-    """y[p] = deq(W[pair_expert[p]]) . x[p // x_div].  Pairs whose expert is not in the bank are skipped by
-    the kernel; their rows are zero (may_skip=False: the caller knows every pair is local, no memset)."""
+                  flags: int = 0, expert_base: int = 0) -> torch.Tensor:
+    """y[p] = deq(W[pair_expert[p] - expert_base]) . x[p // x_div].  Pairs whose expert is not in the bank
+    get a zero row (written by the kernel)."""
     lib = _lib.load()
     bank = bank._sidecars_as(x.dtype)
     P = pair_expert.numel()
-    alloc = torch.zeros if (may_skip or len(bank.distinct_bits) > 1) else torch.empty
-    y = alloc((P, bank.N), dtype=x.dtype, device=x.device)
+    y = torch.empty((P, bank.N), dtype=x.dtype, device=x.device)
     for bits in bank.distinct_bits:
         _lib.check(lib.jq_gather_qgemv2(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), x_div, pair_expert.data_ptr(),
                                         P, bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
                                         bank.biases_tab.data_ptr(), None, None, None,
                                         bank.bits_tab.data_ptr() if bank.bits_tab is not None else None, bank.E,
                                         _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
-                                        y.data_ptr(), None, y.stride(0), flags, _lib.stream_ptr(x.device)))
+                                        y.data_ptr(), None, y.stride(0), expert_base, flags, _lib.stream_ptr(x.device)))
     return y
 
 
 def _gather_qgemv_pair(x: torch.Tensor, x_div: int, pair_expert: torch.Tensor, bank_a: ExpertBank, bank_b: ExpertBank,
-                       may_skip: bool = True, flags: int = 0):
+                       flags: int = 0, expert_base: int = 0):
     """Two banks of equal shape and width (gate, up) over the same rows of x in one launch."""
     same = (bank_a.N == bank_b.N and bank_a.K == bank_b.K and bank_a.group_size == bank_b.group_size and
             bank_a.E == bank_b.E and bank_a.bits_tab is None and bank_b.bits_tab is None and
             bank_a.distinct_bits == bank_b.distinct_bits and len(bank_a.distinct_bits) == 1)
     if not same:
-        return (_gather_qgemv(x, x_div, pair_expert, bank_a, may_skip, flags),
-                _gather_qgemv(x, x_div, pair_expert, bank_b, may_skip, flags))
+        return (_gather_qgemv(x, x_div, pair_expert, bank_a, flags, expert_base),
+                _gather_qgemv(x, x_div, pair_expert, bank_b, flags, expert_base))
     lib = _lib.load()
     a, b = bank_a._sidecars_as(x.dtype), bank_b._sidecars_as(x.dtype)
     P = pair_expert.numel()
-    alloc = torch.zeros if may_skip else torch.empty
-    y = alloc((2, P, a.N), dtype=x.dtype, device=x.device)
+    y = torch.empty((2, P, a.N), dtype=x.dtype, device=x.device)
     _lib.check(lib.jq_gather_qgemv2(x.data_ptr(), _lib.dtype_id(x.dtype), x.stride(0), x_div, pair_expert.data_ptr(), P,
                                     a.codes_tab.data_ptr(), a.scales_tab.data_ptr(), a.biases_tab.data_ptr(),
                                     b.codes_tab.data_ptr(), b.scales_tab.data_ptr(), b.biases_tab.data_ptr(), None, a.E,
                                     _lib.dtype_id(a.sidecar_dtype), a.N, a.K, a.distinct_bits[0], a.group_size,
-                                    y[0].data_ptr(), y[1].data_ptr(), y.stride(1), flags, _lib.stream_ptr(x.device)))
+                                    y[0].data_ptr(), y[1].data_ptr(), y.stride(1), expert_base, flags,
+                                    _lib.stream_ptr(x.device)))
     return y[0], y[1]
 
 
@@ -315,18 +314,19 @@ def residual_rmsnorm(x: torch.Tensor, y: torch.Tensor, eps: float | None = None,
 def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertBank, up: ExpertBank,
               down: ExpertBank, swiglu_limit: float = 0.0, shared=None, expert_base: int = 0,
               out_f32: bool = False, all_local: bool | None = None, return_slots: bool = False,
-              static_weights: bool = False) -> torch.Tensor:
+              static_weights: bool = False, few_token_path: bool | None = None) -> torch.Tensor:
     """Routed SwiGLU experts: out[t] = sum_j down_e( silu(gate_e x_t) * up_e x_t * w[t, j] ), e = idx[t, j].
 
     x [T, H] bf16/f16; idx [T, k] int; w [T, k] f32.  Follows dsv41/model.py:1206-1245.  With
     `expert_base` the banks hold experts [expert_base, expert_base + E) only and the other
     pairs contribute nothing (expert parallelism).  `shared` = (gate, up, down) JANGLinear-like
     modules of an always-on expert, added in f32.  Returns [T, H] in x.dtype (f32 if out_f32).
-    all_local=True is the caller's promise that every idx is an expert of these banks (single-rank
-    decode), which saves the zero-fill of the rows skipped pairs would leave untouched.  return_slots=True
+    all_local is accepted for compatibility and ignored (the kernels zero the rows of skipped pairs
+    themselves).  return_slots=True
     (few-token path only) returns the [T*k, H] rows before the combine, for a caller that fuses the sum.
     static_weights=True promises that the expert weights are not written by earlier work on the stream, so
-    the few-token mat-vecs may prefetch them while their predecessor still runs.
+    the few-token mat-vecs may prefetch them while their predecessor still runs.  few_token_path forces
+    (True) or forbids (False) the unsorted gather mat-vec path; default: below 64 pairs, as the reference.
     """
     lib = _lib.load()
     dev = _lib.require_cuda(x, idx, w)
@@ -340,7 +340,8 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
     st = _lib.stream_ptr(dev)
     I = gate.N
     with torch.cuda.device(dev):
-        if P >= SORT_THRESHOLD and gate.gemm_ok and up.gemm_ok and down.gemm_ok:
+        use_sorted = P >= SORT_THRESHOLD if few_token_path is None else not few_token_path
+        if use_sorted and gate.gemm_ok and up.gemm_ok and down.gemm_ok:
             sp = SortedPairs(idx32, gate.E, expert_base)
             xs = _gather_rows(x, sp, k)
             g = _moe_gemm(xs, sp, gate)
@@ -351,14 +352,12 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
             y = _moe_gemm(h, sp, down)
             inv_ptr = sp.inv.data_ptr()
         else:
-            local = idx32 - expert_base if expert_base else idx32
-            may_skip = all_local is not True
             flags = _lib.JQ_GEMV_STATIC_WEIGHTS if static_weights else 0
-            g, u = _gather_qgemv_pair(x, k, local, gate, up, may_skip, flags)
+            g, u = _gather_qgemv_pair(x, k, idx32, gate, up, flags, expert_base)
             h = torch.empty((P, I), dtype=x.dtype, device=dev)
             _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), None, None,
                                          h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
-            y = _gather_qgemv(h, 1, local, down, may_skip, flags)
+            y = _gather_qgemv(h, 1, idx32, down, flags, expert_base)
             if return_slots and shared is None:
                 return y        # [T*k, H]: the caller sums the k rows of a token (routing weights already applied)
             # pairs of other ranks' experts were skipped by the kernels and their rows stay zero

@@ -32,12 +32,18 @@ class MoEDecodeStack:
     """BASELINE config 3 (default arguments): 48 layers, hidden 2048, 32 query / 4 KV heads of 128,
     128 experts of SwiGLU intermediate 768, top-8 softmax routing, experts 2-bit, attention 6-bit,
     group 64.  With world > 1 the experts are sharded E/world per rank (expert parallelism); the
-    attention projections and the router are replicated."""
+    attention projections and the router are replicated.  Decode modes for world > 1:
+      "replicated" (default)  every rank carries the rows of ALL tokens of the step through the replicated
+                   dense blocks (a decode mat-vec streams the same weights for 1 or 8 rows), runs its own
+                   experts on them and one all-reduce per layer adds the partial sums;
+      "gathered"   every rank carries its own rows; all-gather before, reduce-scatter after the experts."""
 
     def __init__(self, layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, inter=768, topk=8,
-                 expert_bits=2, attn_bits=6, gs=64, device="cuda", rank=0, world=1, seed=0, group=None):
+                 expert_bits=2, attn_bits=6, gs=64, device="cuda", rank=0, world=1, seed=0, group=None,
+                 ep_mode="replicated"):
         self.L, self.H, self.E, self.I, self.k = layers, hidden, experts, inter, topk
         self.world, self.rank, self.group = world, rank, group
+        self.ep_mode = ep_mode
         self.e_local = experts // world
         self.base = rank * self.e_local
         dq, dkv = q_heads * head_dim, kv_heads * head_dim
@@ -87,6 +93,10 @@ class MoEDecodeStack:
                 continue
             if self.world == 1:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True, all_local=True)
+            elif self.ep_mode == "replicated":
+                y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], expert_base=self.base, out_f32=True,
+                                  static_weights=True, few_token_path=T <= 16)
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
             else:
                 y = moe_ep.gathered_tokens(x, idx, w, moe_ep.partial_experts_fn(lay["gate"], lay["up"], lay["down"],
                                                                                 self.base), group=self.group)
