@@ -299,4 +299,40 @@ __host__ __device__ __forceinline__ uint32_t make_b(const uint32_t (&xr)[8]) {
     return prmt(xr[JL / 2], xr[JH / 2], SEL);
 }
 
+// ---- activation limbs for the integer mat-vec kernels ---------------------------------------------
+// A fixed-point activation xi (|xi| <= 2^22) is fed to the integer MMAs as three signed 8-bit digits,
+// xi = l0 + 256*l1 + 65536*l2 with l in [-128, 127].  With u = xi + 0x8080 the bytes of u ^ 0x8080 are
+// the two's-complement digits: adding 128 at every digit position turns the signed digits into plain
+// base-256 digits, the xor takes the 128 off again.
+// store_limbs8 writes the digits of 8 consecutive activations (half `hf` of a 16-code unit) into the
+// unit's 16 bytes of the three limb rows, in the byte order the kernels unpack codes in:
+//   8-bit: natural;  4-bit: per 8 codes the even ones, then the odd ones;
+//   2-bit: code j of the unit is byte j >> 2 of word j & 3.
+template <int BITS>
+__device__ __forceinline__ void store_limbs8(uint8_t* d0, uint8_t* d1, uint8_t* d2, int hf, const int (&xi)[8]) {
+    uint32_t t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = ((uint32_t)xi[j] + 0x8080u) ^ 0x8080u;
+    uint8_t* const d[3] = {d0, d1, d2};
+#pragma unroll
+    for (int L = 0; L < 3; ++L) {
+        const uint32_t sel = (uint32_t)(((4 + L) << 4) | L);          // (x.byteL, y.byteL) -> result bytes 0, 1
+        if constexpr (BITS == 2) {
+            uint16_t* d16 = reinterpret_cast<uint16_t*>(d[L]) + hf;
+            d16[0] = (uint16_t)prmt(t[0], t[4], sel);
+            d16[2] = (uint16_t)prmt(t[1], t[5], sel);
+            d16[4] = (uint16_t)prmt(t[2], t[6], sel);
+            d16[6] = (uint16_t)prmt(t[3], t[7], sel);
+        } else if constexpr (BITS == 4) {
+            const uint32_t w0 = prmt(prmt(t[0], t[2], sel), prmt(t[4], t[6], sel), 0x5410);
+            const uint32_t w1 = prmt(prmt(t[1], t[3], sel), prmt(t[5], t[7], sel), 0x5410);
+            *reinterpret_cast<uint2*>(d[L] + 8 * hf) = make_uint2(w0, w1);
+        } else {
+            const uint32_t w0 = prmt(prmt(t[0], t[1], sel), prmt(t[2], t[3], sel), 0x5410);
+            const uint32_t w1 = prmt(prmt(t[4], t[5], sel), prmt(t[6], t[7], sel), 0x5410);
+            *reinterpret_cast<uint2*>(d[L] + 8 * hf) = make_uint2(w0, w1);
+        }
+    }
+}
+
 }  // namespace jq

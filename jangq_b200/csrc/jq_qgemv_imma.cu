@@ -222,31 +222,8 @@ qgemv_imma_kernel(const GemvArgs a, const GemvBatch bt) {
 #pragma unroll
                 for (int d = 1; d < LPG; d <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
                 const int u = ko >> 1, hf = ko & 1;      // 16-code unit of the row, which half of it
-                int l0[8], l1[8], l2[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int r1 = (xi[j] + 128) >> 8;
-                    l0[j] = xi[j] & 255; l1[j] = r1 & 255; l2[j] = ((r1 + 128) >> 8) & 255;
-                }
-                auto put = [&](int n, const int (&b)[8]) {   // byte order of to_bytes()
-                    uint8_t* dst = limbs + (size_t)n * LS + u * 16;
-                    if constexpr (BITS == 8) {
-                        *reinterpret_cast<uint2*>(dst + 8 * hf) =
-                            make_uint2(b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24, b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24);
-                    } else if constexpr (BITS == 4) {
-                        *reinterpret_cast<uint2*>(dst + 8 * hf) =
-                            make_uint2(b[0] | b[2] << 8 | b[4] << 16 | b[6] << 24, b[1] | b[3] << 8 | b[5] << 16 | b[7] << 24);
-                    } else {
-                        uint16_t* d16 = reinterpret_cast<uint16_t*>(dst) + hf;
-                        d16[0] = (uint16_t)(b[0] | b[4] << 8);
-                        d16[2] = (uint16_t)(b[1] | b[5] << 8);
-                        d16[4] = (uint16_t)(b[2] | b[6] << 8);
-                        d16[6] = (uint16_t)(b[3] | b[7] << 8);
-                    }
-                };
-                put(3 * m, l0);
-                put(3 * m + 1, l1);
-                put(3 * m + 2, l2);
+                uint8_t* dst = limbs + (size_t)(3 * m) * LS + u * 16;     // the unit in limb row 0 of this activation row
+                store_limbs8<BITS>(dst, dst + LS, dst + 2 * LS, hf, xi);
                 if ((ko & (LPG - 1)) == 0) tab[(ko / LPG) * 2 + m] = make_float2(e, (float)sum);
             }
         }

@@ -350,34 +350,12 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                     const int u = ko >> 1, hf = ko & 1;      // 16-code unit of the slice, which half of it
                     const int t = u >> 3, c = u & 7;         // tile of the slice, 16-byte chunk of its 128-byte row
                     uint8_t* tile = sB + (size_t)t * (NCOL * 128);
-                    int l0[8], l1[8], l2[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int r1 = (xi[j] + 128) >> 8;
-                        l0[j] = xi[j] & 255; l1[j] = r1 & 255; l2[j] = ((r1 + 128) >> 8) & 255;
-                    }
-                    // The order of the 16 codes inside a 16-byte unit of A is whatever is cheapest to unpack:
-                    // 8-bit: natural; 4-bit: per 8 codes the even ones, then the odd ones; 2-bit: code j of
-                    // the unit is byte j >> 2 of word j & 3.  The limbs follow the same order.
-                    auto put = [&](int n, const int (&b)[8]) {
-                        uint8_t* dst = tile + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4);
-                        if constexpr (BITS == 8) {
-                            *reinterpret_cast<uint2*>(dst + 8 * hf) =
-                                make_uint2(b[0] | b[1] << 8 | b[2] << 16 | b[3] << 24, b[4] | b[5] << 8 | b[6] << 16 | b[7] << 24);
-                        } else if constexpr (BITS == 4) {
-                            *reinterpret_cast<uint2*>(dst + 8 * hf) =
-                                make_uint2(b[0] | b[2] << 8 | b[4] << 16 | b[6] << 24, b[1] | b[3] << 8 | b[5] << 16 | b[7] << 24);
-                        } else {
-                            uint16_t* d16 = reinterpret_cast<uint16_t*>(dst) + hf;
-                            d16[0] = (uint16_t)(b[0] | b[4] << 8);
-                            d16[2] = (uint16_t)(b[1] | b[5] << 8);
-                            d16[4] = (uint16_t)(b[2] | b[6] << 8);
-                            d16[6] = (uint16_t)(b[3] | b[7] << 8);
-                        }
+                    // The order of the 16 codes inside a 16-byte unit of A is whatever is cheapest to unpack;
+                    // the limbs follow the same order (store_limbs8).
+                    auto unit = [&](int n) {
+                        return tile + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4);
                     };
-                    put(3 * m, l0);
-                    put(3 * m + 1, l1);
-                    put(3 * m + 2, l2);
+                    store_limbs8<BITS>(unit(3 * m), unit(3 * m + 1), unit(3 * m + 2), hf, xi);
                     if ((ko & (LPG - 1)) == 0) tab[(ko / LPG) * 8 + m] = make_float2(e, (float)sum);
                 }
             }
