@@ -396,6 +396,7 @@ static int gemv_kernel_choice() {
     if (e[0] == 'm') return 1;
     if (e[0] == 'i') return 2;      // integer warp-MMA kernel wherever the shape fits it
     if (e[0] == 't') return 3;
+    if (e[0] == 'p') return 4;      // persistent integer warp-MMA kernel wherever the shape fits it
     return 0;
 }
 
@@ -543,17 +544,22 @@ int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, con
         bool launched = false;
         int rc = JQ_OK;
         // Measured choice on B200 (CUDA events, overlapped launches, working set >> L2):
+        //   2- and 4-bit, M <= 2: persistent integer warp-MMA kernel (22016x4096 2-bit: 12.0 us against 16.2 us
+        //          for the per-tile integer kernel; 14336x4096 4-bit: 10.2 us against 14.1 us for the
+        //          tensor-memory kernel);
         //   8-bit: tensor-memory kernel, except launches of at most ~6K rows with M <= 2, where the integer
         //          warp-MMA kernel has the lower fixed latency (4096x4096: 6.4 us vs 7.7 us);
-        //   4-bit: tensor-memory kernel;
-        //   2-bit: integer warp-MMA kernel for M <= 2 once the grid fills the machine (>= 2 row tiles of 16
-        //          per SM: 11008x4096 8.3 us vs 8.8 us), else the bf16 warp-MMA kernel;
+        //   4-bit, M > 2: tensor-memory kernel;
         //   3/6-bit, M > 2 with 2-bit: bf16 warp-MMA kernel.
         int64_t rows = 0;
         for (int i = 0; i < bt.count; ++i) rows += bt.N[i];
         const bool small8 = bits == 8 && a.M <= 2 && rows <= 6144;
-        const bool big2 = bits == 2 && a.M <= 2 && rows >= (int64_t)32 * sm_count() && K <= 8192;
-        if (fast && (kern == 2 || (kern == 0 && (small8 || big2)))) {
+        const bool narrow = (bits == 2 || bits == 4) && a.M <= 2;
+        if (fast && (kern == 4 || (kern == 0 && narrow))) {
+            rc = launch_pint_kernel(a, bt, x_dtype, bits, gs, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (fast && !launched && (kern == 2 || (kern == 0 && small8))) {
             rc = launch_imma_kernel(a, bt, x_dtype, bits, gs, st, &launched);
             if (rc != JQ_OK) return rc;
         }

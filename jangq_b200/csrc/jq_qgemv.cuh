@@ -131,6 +131,11 @@ constexpr int GEMV_MAX_NBUF = 3;   // deepest per-warp stage pipeline of the war
 int launch_imma_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
                        bool* launched);
 
+// persistent integer warp-MMA kernel (jq_qgemv_pint.cu), dense mat-vecs of 2- and 4-bit codes with at most 2
+// activation rows; same convention
+int launch_pint_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
+                       bool* launched);
+
 // tensor-memory kernel (jq_qgemv_tc.cu), dense mat-vecs only; *launched stays false when the shape does
 // not fit it and the caller should use the warp-MMA kernel instead
 int launch_tc_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,

@@ -221,9 +221,9 @@ def test_plan_groups_fuse_and_match_ungrouped():
 
 
 # ---- every fast kernel, selected explicitly ------------------------------------------------------------------
-@pytest.mark.parametrize("kernel", ("tc", "imma", "mma"))
+@pytest.mark.parametrize("kernel", ("tc", "imma", "mma", "pint"))
 @pytest.mark.parametrize("bits,N,K,M", ((8, 4096, 4096, 1), (2, 5000, 4096, 1), (4, 300, 11008, 2), (8, 130, 2048, 2),
-                                        (2, 96, 512, 1), (4, 4100, 1024, 1)))
+                                        (2, 96, 512, 1), (4, 4100, 1024, 1), (2, 4096, 11008, 2)))
 def test_each_kernel_against_oracle(monkeypatch, kernel, bits, N, K, M):
     """The dispatcher picks a kernel per shape from measurements; JANGQ_GEMV_KERNEL forces one (where the
     shape fits it), so every kernel is checked on shapes it would not get by default: ragged row blocks,
@@ -238,11 +238,28 @@ def test_each_kernel_against_oracle(monkeypatch, kernel, bits, N, K, M):
 def test_nonfinite_activation_poisons_only_its_outputs(monkeypatch):
     """An infinite activation must not turn into a finite garbage value: the integer kernels mark the group's
     exponent NaN, so every output row of that activation row is NaN, the other activation row is untouched."""
-    for kernel in ("tc", "imma"):
+    for kernel, bits in (("tc", 8), ("imma", 8), ("pint", 4), ("pint", 2)):
         monkeypatch.setenv("JANGQ_GEMV_KERNEL", kernel)
-        x, wq, s, b = make_case(256, 1024, 8, 64, 2, torch.bfloat16, seed=5)
-        ref = reference(x, wq, s, b, 8, 64)
+        x, wq, s, b = make_case(256, 1024, bits, 64, 2, torch.bfloat16, seed=5)
+        ref = reference(x, wq, s, b, bits, 64)
         x[1, 77] = float("inf")
-        y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=8).float().cpu().numpy()
+        y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=bits).float().cpu().numpy()
         assert np.all(np.isnan(y[1]))
         assert np.abs(y[0] - ref[0]).max() <= 1e-2 * np.abs(ref[0]).max()
+
+
+@pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (4, 64), (4, 128)))
+def test_persistent_integer_kernel_extremes(monkeypatch, bits, gs):
+    """Largest codes against largest limbs (every code the maximum in most positions, every activation the
+    same value just under a power of two), a fused launch of two matrices with ragged row counts, and f16."""
+    monkeypatch.setenv("JANGQ_GEMV_KERNEL", "pint")
+    K = 2048
+    for dtype in (torch.bfloat16, torch.float16):
+        g = torch.Generator(device="cuda").manual_seed(bits * 131 + gs)
+        w = (torch.rand(333, K, device="cuda", generator=g) > 0.2).to(dtype)
+        w[:, ::gs] = 0
+        wq, s, b = jq.quantize(w, group_size=gs, bits=bits)
+        x = torch.full((1, K), 1.9921875, device="cuda", dtype=dtype)
+        y = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
+        check(y, reference(x, wq, s, b, bits, gs), dtype)
+    _lib.check(_lib.load().jq_device_status())
