@@ -312,7 +312,7 @@ def run_cuda(args):
                              "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650",
                              "traffic": traffic, "traffic_note": "bytes per 225-launch step, scaled from two ncu captures in which "
                              "per-launch DRAM bytes equalled the algorithmic bytes (profiles/bench_launch_list.md)",
-                             "kernel": "qgemv_mma_kernel (225 launches per step, averaged)"},
+                             "kernel": "qgemv_pint_kernel (225 matrices in 129 launches per step, averaged)"},
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": plan.h2d_bytes,
                         "d2h_bytes_per_step": plan.d2h_bytes, "ms_per_step": e2e_ms / K},
                 "gpu_launches": plan.launches_per_run * K, "clocks": clk.summary()}

@@ -544,22 +544,17 @@ int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, con
         bool launched = false;
         int rc = JQ_OK;
         // Measured choice on B200 (CUDA events, overlapped launches, working set >> L2):
-        //   2- and 4-bit, M <= 2: persistent integer warp-MMA kernel (22016x4096 2-bit: 12.0 us against 16.2 us
-        //          for the per-tile integer kernel; 14336x4096 4-bit: 10.2 us against 14.1 us for the
-        //          tensor-memory kernel);
-        //   8-bit: tensor-memory kernel, except launches of at most ~6K rows with M <= 2, where the integer
-        //          warp-MMA kernel has the lower fixed latency (4096x4096: 6.4 us vs 7.7 us);
-        //   4-bit, M > 2: tensor-memory kernel;
+        //   2-, 4- and 8-bit, M <= 2: persistent integer warp-MMA kernel (22016x4096 2-bit: 12.0 us against
+        //          16.2 us for the per-tile integer kernel; 14336x4096 4-bit: 10.2 us and 32000x4096 8-bit:
+        //          24.1 us against 14.1 us and 31.1 us for the tensor-memory kernel);
+        //   4- and 8-bit, M > 2: tensor-memory kernel;
         //   3/6-bit, M > 2 with 2-bit: bf16 warp-MMA kernel.
-        int64_t rows = 0;
-        for (int i = 0; i < bt.count; ++i) rows += bt.N[i];
-        const bool small8 = bits == 8 && a.M <= 2 && rows <= 6144;
-        const bool narrow = (bits == 2 || bits == 4) && a.M <= 2;
+        const bool narrow = (bits == 2 || bits == 4 || bits == 8) && a.M <= 2;
         if (fast && (kern == 4 || (kern == 0 && narrow))) {
             rc = launch_pint_kernel(a, bt, x_dtype, bits, gs, st, &launched);
             if (rc != JQ_OK) return rc;
         }
-        if (fast && !launched && (kern == 2 || (kern == 0 && small8))) {
+        if (fast && !launched && kern == 2) {
             rc = launch_imma_kernel(a, bt, x_dtype, bits, gs, st, &launched);
             if (rc != JQ_OK) return rc;
         }

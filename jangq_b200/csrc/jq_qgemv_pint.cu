@@ -1,5 +1,5 @@
 // K2, persistent integer warp-MMA form: decode-shaped quantized mat-vec  y[M,N] = x[M,K] . deq(W)[N,K]^T
-// for 2- and 4-bit codes, M <= 2.
+// for 2-, 4- and 8-bit codes, M <= 2.
 //
 // Bound: HBM bandwidth on paper; in practice the instruction issue rate.  Algorithmic bytes per launch =
 //     N*K*bits/8 (codes) + N*(K/gs)*2*2 (scales, biases) + M*K*2 + M*N*2.
@@ -66,26 +66,30 @@ __device__ __forceinline__ void cp_async_wait_dyn(int pending) {   // pending in
 // shifts.  Register i, byte t holds code elem(i, t) times 2^shift(i).
 template <int BITS>
 __device__ __forceinline__ void to_bytes(const uint32_t (&u)[Unit<BITS>::WORDS], uint32_t (&r)[4]) {
-    if constexpr (BITS == 4) {
+    if constexpr (BITS == 8) {
+        r[0] = u[0]; r[1] = u[1]; r[2] = u[2]; r[3] = u[3];
+    } else if constexpr (BITS == 4) {
         r[0] = u[0] & 0x0F0F0F0Fu; r[1] = u[0] & 0xF0F0F0F0u;
         r[2] = u[1] & 0x0F0F0F0Fu; r[3] = u[1] & 0xF0F0F0F0u;
     } else {
-        static_assert(BITS == 2, "widths of this kernel: 2, 4");
+        static_assert(BITS == 2, "widths of this kernel: 2, 4, 8");
         r[0] = u[0] & 0x03030303u; r[1] = u[0] & 0x0C0C0C0Cu;
         r[2] = u[0] & 0x30303030u; r[3] = u[0] & 0xC0C0C0C0u;
     }
 }
 template <int BITS> __host__ __device__ constexpr int elem(int i, int t) {
-    return BITS == 2 ? i + 4 * t : 8 * (i >> 1) + (i & 1) + 2 * t;
+    return BITS == 2 ? i + 4 * t : BITS == 4 ? 8 * (i >> 1) + (i & 1) + 2 * t : 4 * i + t;
 }
 // log2 of the factor the code of element j carries inside its byte
-template <int BITS> __host__ __device__ constexpr int code_shift(int j) { return BITS == 2 ? 2 * (j & 3) : 4 * (j & 1); }
+template <int BITS> __host__ __device__ constexpr int code_shift(int j) {
+    return BITS == 2 ? 2 * (j & 3) : BITS == 4 ? 4 * (j & 1) : 0;
+}
 
 template <int BITS, int GS> struct Geom {
-    static constexpr int KT = BITS == 2 ? 512 : 256;      // codes per row and stage: 128 bytes
+    static constexpr int KT = BITS == 2 ? 512 : 256;      // codes per row and stage: 128 bytes (256 for 8-bit codes)
     static constexpr int NBLK = KT / 64;                  // 64-code blocks per stage
-    static constexpr int ROWB = KT * BITS / 8;            // 128
-    static constexpr int RSB = ROWB + (BITS == 2 ? 16 : 32);   // padded row stride: conflict-free unit loads
+    static constexpr int ROWB = KT * BITS / 8;
+    static constexpr int RSB = ROWB + (BITS == 2 ? 16 : BITS == 4 ? 32 : 64);   // padded row stride: conflict-free unit loads
     static constexpr int NG = KT / GS;                    // groups per stage: 8, 4 or 2
     static constexpr int SCB = NG * 2;                    // bytes of scales (or biases) per row and stage
     static constexpr int SC_OFF = 16 * RSB;               // scales [16 rows][NG] (2-byte), then biases [16][NG]
@@ -158,7 +162,7 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
     __syncthreads();
 
     // copies of one item (tile lt, stage st): 16 code rows of 128 bytes + 16 x SCB bytes of scales and of biases
-    constexpr int CPR = ROWB / 16, RPI = 32 / CPR;       // 8 lanes per row, 4 rows per instruction
+    constexpr int CPR = ROWB / 16, RPI = 32 / CPR;       // 8 (16) lanes per row, 4 (2) rows per instruction
     const int crow = lane / CPR, ccol = lane % CPR;
     const int64_t lane_src = (int64_t)crow * rowbytes + ccol * 16;
     const int lane_dst = crow * RSB + ccol * 16;
@@ -434,18 +438,18 @@ static int launch_shape(const GemvArgs& a, GemvBatch bt, cudaStream_t st, bool* 
 }  // namespace pint
 
 // Dense mat-vecs (one launch for all matrices of `bt`) on the persistent integer warp-MMA kernel;
-// *launched stays false when the shape does not fit it (widths other than 2/4, more than 2 activation rows).
+// *launched stays false when the shape does not fit it (widths other than 2/4/8, more than 2 activation rows).
 int launch_pint_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
                        bool* launched) {
     *launched = false;
-    if (!(bits == 2 || bits == 4) || a.M > 2 || a.K % (4 * gs) != 0) return JQ_OK;
+    if (!(bits == 2 || bits == 4 || bits == 8) || a.M > 2 || a.K % (4 * gs) != 0) return JQ_OK;
     int rc = JQ_OK;
 #define JQ_PINT_CASE(B, GSZ)                                                                          \
     if (bits == B && gs == GSZ) {                                                                     \
         rc = (act_dtype == JQ_BF16) ? pint::launch_shape<__nv_bfloat16, B, GSZ>(a, bt, st, launched)  \
                                     : pint::launch_shape<__half, B, GSZ>(a, bt, st, launched);        \
     }
-    JQ_PINT_CASE(2, 64) JQ_PINT_CASE(4, 64) JQ_PINT_CASE(2, 128) JQ_PINT_CASE(4, 128)
+    JQ_PINT_CASE(2, 64) JQ_PINT_CASE(4, 64) JQ_PINT_CASE(8, 64) JQ_PINT_CASE(2, 128) JQ_PINT_CASE(4, 128) JQ_PINT_CASE(8, 128)
 #undef JQ_PINT_CASE
     return rc;
 }

@@ -238,7 +238,7 @@ def test_each_kernel_against_oracle(monkeypatch, kernel, bits, N, K, M):
 def test_nonfinite_activation_poisons_only_its_outputs(monkeypatch):
     """An infinite activation must not turn into a finite garbage value: the integer kernels mark the group's
     exponent NaN, so every output row of that activation row is NaN, the other activation row is untouched."""
-    for kernel, bits in (("tc", 8), ("imma", 8), ("pint", 4), ("pint", 2)):
+    for kernel, bits in (("tc", 8), ("imma", 8), ("pint", 8), ("pint", 4), ("pint", 2)):
         monkeypatch.setenv("JANGQ_GEMV_KERNEL", kernel)
         x, wq, s, b = make_case(256, 1024, bits, 64, 2, torch.bfloat16, seed=5)
         ref = reference(x, wq, s, b, bits, 64)
@@ -248,7 +248,7 @@ def test_nonfinite_activation_poisons_only_its_outputs(monkeypatch):
         assert np.abs(y[0] - ref[0]).max() <= 1e-2 * np.abs(ref[0]).max()
 
 
-@pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (4, 64), (4, 128)))
+@pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (4, 64), (4, 128), (8, 64), (8, 128)))
 def test_persistent_integer_kernel_extremes(monkeypatch, bits, gs):
     """Largest codes against largest limbs (every code the maximum in most positions, every activation the
     same value just under a power of two), a fused launch of two matrices with ragged row counts, and f16."""
