@@ -113,7 +113,7 @@ __host__ __device__ inline int head_bytes(int K, int G, int M, int tpc, int nw) 
     return 64 + tpc * 64 + G * 16 + ((3 * M * limb_stride(K) + 127) / 128) * 128 + nw * M * tpc * 64;
 }
 
-template <typename AT, int BITS, int GS, int NW>
+template <typename AT, int BITS, int GS, int NW, bool M1>
 __global__ void __launch_bounds__(NW * 32, 1)
 qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
     using A = Act<AT>;
@@ -264,7 +264,14 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
                     *reinterpret_cast<uint4*>(limbs + (size_t)(3 * m + L) * LS + (size_t)U * 16) =
                         make_uint4(wd[0], wd[1], wd[2], wd[3]);
                 }
-                if ((U & (LPG - 1)) == 0) tab[(U / LPG) * 2 + m] = make_float2(e, xs);
+                if ((U & (LPG - 1)) == 0) {
+                    if constexpr (M1) {
+                        tab[(U / LPG) * 2] = make_float2(e, 0.f);
+                        tab[(U / LPG) * 2 + 1] = make_float2(0.f, xs);
+                    } else {
+                        tab[(U / LPG) * 2 + m] = make_float2(e, xs);
+                    }
+                }
             }
         }
     }
@@ -274,11 +281,14 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
     const int bm = g >> 2, bl = g & 3;
     const bool bvalid = bl < 3 && bm < M;
     const uint8_t* brow = bvalid ? limbs + (size_t)(3 * bm + bl) * LS + tig * 16 : zero + tig * 16;
-    // a lane's columns: even tig (l0, l1) -> D0 + 256 D1; odd tig (l2, none) -> D2, weighed 65536 at the end;
-    // both belong to activation row tig >> 1
+    // A lane's columns: even tig (l0, l1) -> D0 + 256 D1; odd tig (l2, none) -> D2, weighed 65536 at the end;
+    // both belong to activation row tig >> 1.  With one activation row (M1) the lanes tig >= 2 have no
+    // columns (their D is 0) and carry the bias term instead: a lane computes  acc += f * (D * el + xl)
+    // with (f, el, xl) = (scale, e, 0) for tig < 2 and (bias, 0, sum x) for tig >= 2 -- the same two FMAs.
     const int am = tig >> 1;
-    const float wl = (tig & 1) ? 65536.f : 1.f;
-    const float2* tabm = tab + (am < M ? am : 0);
+    const float wl = M1 ? (tig == 1 ? 65536.f : tig == 3 ? 0.f : 1.f) : ((tig & 1) ? 65536.f : 1.f);
+    const float2* tabm = tab + (M1 ? am : (am < M ? am : 0));
+    const int sc_mine = Geo::SC_OFF + (M1 ? am * 16 * SCB : 0);       // M1: scales for tig < 2, biases for tig >= 2
 
     int b = 0;
     while (lt < ntile) {
@@ -286,68 +296,85 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
         cp_async_wait_dyn(nbuf - 1);                     // this item's copies have landed
         __syncwarp();
 
-        const int nblk = min(KT, K - st * KT) >> 6;
         const uint32_t* c_lo = reinterpret_cast<const uint32_t*>(buf + g * RSB);
         const uint32_t* c_hi = reinterpret_cast<const uint32_t*>(buf + (g + 8) * RSB);
         uint32_t sc_lo[NG / 2], sc_hi[NG / 2], bi_lo[NG / 2], bi_hi[NG / 2];     // packed 2-byte pairs
-        {
-            const uint32_t* p0 = reinterpret_cast<const uint32_t*>(buf + Geo::SC_OFF + g * SCB);
-            const uint32_t* p1 = reinterpret_cast<const uint32_t*>(buf + Geo::SC_OFF + (g + 8) * SCB);
-            const uint32_t* p2 = reinterpret_cast<const uint32_t*>(buf + Geo::SC_OFF + 16 * SCB + g * SCB);
-            const uint32_t* p3 = reinterpret_cast<const uint32_t*>(buf + Geo::SC_OFF + 16 * SCB + (g + 8) * SCB);
+        auto load_pairs = [&](const uint8_t* p, uint32_t (&d)[NG / 2]) {
             if constexpr (NG == 8) {
-                const uint4 v0 = *reinterpret_cast<const uint4*>(p0), v1 = *reinterpret_cast<const uint4*>(p1);
-                const uint4 v2 = *reinterpret_cast<const uint4*>(p2), v3 = *reinterpret_cast<const uint4*>(p3);
-                sc_lo[0] = v0.x; sc_lo[1] = v0.y; sc_lo[2] = v0.z; sc_lo[3] = v0.w;
-                sc_hi[0] = v1.x; sc_hi[1] = v1.y; sc_hi[2] = v1.z; sc_hi[3] = v1.w;
-                bi_lo[0] = v2.x; bi_lo[1] = v2.y; bi_lo[2] = v2.z; bi_lo[3] = v2.w;
-                bi_hi[0] = v3.x; bi_hi[1] = v3.y; bi_hi[2] = v3.z; bi_hi[3] = v3.w;
+                const uint4 v = *reinterpret_cast<const uint4*>(p);
+                d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
             } else if constexpr (NG == 4) {
-                const uint2 v0 = *reinterpret_cast<const uint2*>(p0), v1 = *reinterpret_cast<const uint2*>(p1);
-                const uint2 v2 = *reinterpret_cast<const uint2*>(p2), v3 = *reinterpret_cast<const uint2*>(p3);
-                sc_lo[0] = v0.x; sc_lo[1] = v0.y; sc_hi[0] = v1.x; sc_hi[1] = v1.y;
-                bi_lo[0] = v2.x; bi_lo[1] = v2.y; bi_hi[0] = v3.x; bi_hi[1] = v3.y;
+                const uint2 v = *reinterpret_cast<const uint2*>(p);
+                d[0] = v.x; d[1] = v.y;
             } else {
-                sc_lo[0] = *p0; sc_hi[0] = *p1; bi_lo[0] = *p2; bi_hi[0] = *p3;
+                d[0] = *reinterpret_cast<const uint32_t*>(p);
             }
+        };
+        load_pairs(buf + sc_mine + g * SCB, sc_lo);
+        load_pairs(buf + sc_mine + (g + 8) * SCB, sc_hi);
+        if constexpr (!M1) {
+            load_pairs(buf + Geo::SC_OFF + 16 * SCB + g * SCB, bi_lo);
+            load_pairs(buf + Geo::SC_OFF + 16 * SCB + (g + 8) * SCB, bi_hi);
         }
         const uint8_t* bp = brow + (bvalid ? st * KT : 0);
+        const int bstep = bvalid ? 64 : 0;
         const float2* tp = tabm + (size_t)(st * NG) * 2;
         float acc_lo = 0.f, acc_hi = 0.f, accb_lo = 0.f, accb_hi = 0.f;
         int cg[4];
-#pragma unroll
-        for (int blk = 0; blk < NBLK; ++blk) {
-            if (blk < nblk) {                            // warp-uniform: only a short last stage skips blocks
-                const uint4 bq = *reinterpret_cast<const uint4*>(bp + (bvalid ? blk * 64 : 0));
-                uint32_t ulo[UW], uhi[UW], rl[4], rh[4];
-                load_unit<BITS>(c_lo, blk, tig, ulo);
-                load_unit<BITS>(c_hi, blk, tig, uhi);
-                to_bytes<BITS>(ulo, rl);
-                to_bytes<BITS>(uhi, rh);
-                if (blk % BPG == 0) imma0(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
-                else imma(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
-                imma(cg, rl[2], rh[2], rl[3], rh[3], bq.z, bq.w);
-                if (blk % BPG == BPG - 1) {
-                    const int gi = blk / BPG;
-                    const float2 tx = tp[gi * 2];        // (e, sum x) of the group and activation row
-                    const float s_lo = (gi & 1) ? A::hi_f32(sc_lo[gi >> 1]) : A::lo_f32(sc_lo[gi >> 1]);
-                    const float s_hi = (gi & 1) ? A::hi_f32(sc_hi[gi >> 1]) : A::lo_f32(sc_hi[gi >> 1]);
+        auto block = [&](const int blk) {
+            const uint4 bq = *reinterpret_cast<const uint4*>(bp + blk * bstep);
+            uint32_t ulo[UW], uhi[UW], rl[4], rh[4];
+            load_unit<BITS>(c_lo, blk, tig, ulo);
+            load_unit<BITS>(c_hi, blk, tig, uhi);
+            to_bytes<BITS>(ulo, rl);
+            to_bytes<BITS>(uhi, rh);
+            if (blk % BPG == 0) imma0(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
+            else imma(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
+            imma(cg, rl[2], rh[2], rl[3], rh[3], bq.z, bq.w);
+            if (blk % BPG == BPG - 1) {
+                const int gi = blk / BPG;
+                const float2 tx = tp[gi * 2];
+                const float s_lo = (gi & 1) ? A::hi_f32(sc_lo[gi >> 1]) : A::lo_f32(sc_lo[gi >> 1]);
+                const float s_hi = (gi & 1) ? A::hi_f32(sc_hi[gi >> 1]) : A::lo_f32(sc_hi[gi >> 1]);
+                const float d_lo = (float)(cg[0] + 256 * cg[1]);
+                const float d_hi = (float)(cg[2] + 256 * cg[3]);
+                if constexpr (M1) {                      // tx = (e, 0) or (0, sum x)
+                    acc_lo = fmaf(s_lo, fmaf(d_lo, tx.x, tx.y), acc_lo);
+                    acc_hi = fmaf(s_hi, fmaf(d_hi, tx.x, tx.y), acc_hi);
+                } else {                                 // tx = (e, sum x) of the group and activation row
                     const float b_lo = (gi & 1) ? A::hi_f32(bi_lo[gi >> 1]) : A::lo_f32(bi_lo[gi >> 1]);
                     const float b_hi = (gi & 1) ? A::hi_f32(bi_hi[gi >> 1]) : A::lo_f32(bi_hi[gi >> 1]);
-                    const float d_lo = (float)(cg[0] + 256 * cg[1]);
-                    const float d_hi = (float)(cg[2] + 256 * cg[3]);
                     acc_lo = fmaf(s_lo * tx.x, d_lo, acc_lo);
                     acc_hi = fmaf(s_hi * tx.x, d_hi, acc_hi);
                     accb_lo = fmaf(b_lo, tx.y, accb_lo);
                     accb_hi = fmaf(b_hi, tx.y, accb_hi);
                 }
             }
+        };
+        // only the last stage of 2-bit rows with 64-code groups can be short, and then it is half a stage
+        constexpr bool TAIL = BITS == 2 && GS == 64;
+        constexpr int HEAD_BLKS = TAIL ? NBLK / 2 : NBLK;
+#pragma unroll
+        for (int blk = 0; blk < HEAD_BLKS; ++blk) block(blk);
+        if constexpr (TAIL) {
+            if (K - st * KT >= KT) {
+#pragma unroll
+                for (int blk = HEAD_BLKS; blk < NBLK; ++blk) block(blk);
+            }
         }
-        {   // add the item to this warp's row sums: lanes tig, tig^1 hold the two halves of one (row, activation row)
+        {   // add the item to this warp's row sums
             float p_lo = wl * acc_lo, p_hi = wl * acc_hi;
             p_lo += __shfl_xor_sync(0xFFFFFFFFu, p_lo, 1);
             p_hi += __shfl_xor_sync(0xFFFFFFFFu, p_hi, 1);
-            if ((tig & 1) == 0 && am < M) {
+            if constexpr (M1) {
+                p_lo += __shfl_xor_sync(0xFFFFFFFFu, p_lo, 2);
+                p_hi += __shfl_xor_sync(0xFFFFFFFFu, p_hi, 2);
+                if (tig == 0) {
+                    float* yp = myy + lt * 16 + g;
+                    yp[0] += p_lo;
+                    yp[8] += p_hi;
+                }
+            } else if ((tig & 1) == 0 && am < M) {
                 float* yp = myy + (size_t)am * TPC * 16 + lt * 16 + g;
                 yp[0] += p_lo + accb_lo;
                 yp[8] += p_hi + accb_hi;
@@ -372,8 +399,8 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
     }
 }
 
-template <typename AT, int BITS, int GS, int NW>
-static int launch_cfg(GemvArgs a, GemvBatch bt, int nbuf, int tpc, int grid, cudaStream_t st, bool* launched) {
+template <typename AT, int BITS, int GS, int NW, bool M1>
+static int launch_cfg_m(GemvArgs a, GemvBatch bt, int nbuf, int tpc, int grid, cudaStream_t st, bool* launched) {
     using Geo = Geom<BITS, GS>;
     *launched = false;
     a.nbuf = nbuf;
@@ -383,7 +410,7 @@ static int launch_cfg(GemvArgs a, GemvBatch bt, int nbuf, int tpc, int grid, cud
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_pint_kernel<AT, BITS, GS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemv_pint_kernel<AT, BITS, GS, NW, M1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         MAX_SMEM));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -397,9 +424,15 @@ static int launch_cfg(GemvArgs a, GemvBatch bt, int nbuf, int tpc, int grid, cud
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_pint_kernel<AT, BITS, GS, NW>, a, bt));
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemv_pint_kernel<AT, BITS, GS, NW, M1>, a, bt));
     *launched = true;
     return JQ_OK;
+}
+
+template <typename AT, int BITS, int GS, int NW>
+static int launch_cfg(const GemvArgs& a, const GemvBatch& bt, int nbuf, int tpc, int grid, cudaStream_t st, bool* launched) {
+    if (a.M == 1) return launch_cfg_m<AT, BITS, GS, NW, true>(a, bt, nbuf, tpc, grid, st, launched);
+    return launch_cfg_m<AT, BITS, GS, NW, false>(a, bt, nbuf, tpc, grid, st, launched);
 }
 
 static int env_int(const char* name, int dflt) {
