@@ -204,28 +204,40 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
     };
     while (it_st >= nst) { it_st -= nst; ++it_lt; }
     int lt = it_lt, st = it_st;                   // (tile, stage) of the next item to compute
-    for (int i = 0; i < nbuf; ++i) {
+    issue(it_lt, it_st, 0);
+    cp_async_commit();
+    advance(it_lt, it_st);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- activations -> limbs + per-group (e, sum x), once per CTA --------------------------------------
+    // The first load of x is issued here and the rest of the ring is filled while it is in flight.
+    constexpr int LPG = GS / 16;                         // sixteen activations per lane, LPG lanes per group
+    const int per_row = K / 16;                          // a multiple of LPG
+    const int units = M * per_row;
+    auto load_x = [&](int it, uint4& r0, uint4& r1) {
+        r0 = make_uint4(0u, 0u, 0u, 0u);
+        r1 = r0;
+        if (it < units) {
+            const int m = it / per_row;
+            const uint4* p = reinterpret_cast<const uint4*>(xs16 + (int64_t)m * a.ldx + (size_t)(it - m * per_row) * 16);
+            r0 = p[0]; r1 = p[1];
+        }
+    };
+    uint4 xr0, xr1;
+    load_x(warp * 32 + lane, xr0, xr1);
+    for (int i = 1; i < nbuf; ++i) {
         issue(it_lt, it_st, i);
         cp_async_commit();
         advance(it_lt, it_st);
     }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    // ---- activations -> limbs + per-group (e, sum x), once per CTA --------------------------------------
     {
-        constexpr int LPG = GS / 16;                     // sixteen activations per lane, LPG lanes per group
-        const int per_row = K / 16;                      // a multiple of LPG
-        const int units = M * per_row;
         for (int base = warp * 32; base < units; base += THREADS) {
             const int it = base + lane;
             const bool live = it < units;
             const int m = live ? it / per_row : 0;
             const int U = it - m * per_row;              // 16-code unit of the row
-            uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
-            if (live) {
-                const uint4* p = reinterpret_cast<const uint4*>(xs16 + (int64_t)m * a.ldx + (size_t)U * 16);
-                r0 = p[0]; r1 = p[1];
-            }
+            const uint4 r0 = xr0, r1 = xr1;
+            if (base + THREADS < units) load_x(it + THREADS, xr0, xr1);
             const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
             float v[16];
 #pragma unroll
@@ -454,7 +466,9 @@ static int launch_shape(const GemvArgs& a, GemvBatch bt, cudaStream_t st, bool* 
     const int tpc = (int)((tiles + sms - 1) / sms);
     const int grid = (int)((tiles + tpc - 1) / tpc);
     if (tpc > 64) return JQ_OK;
-    int nw = env_int("JANGQ_PINT_NW", 20);
+    // 20 warps by default; 24 when that saves a round of items (short runs: the slowest warp sets the time)
+    const int64_t items = (int64_t)tpc * ((a.K + Geo::KT - 1) / Geo::KT);
+    int nw = env_int("JANGQ_PINT_NW", (items + 23) / 24 < (items + 19) / 20 ? 24 : 20);
     int nbuf = env_int("JANGQ_PINT_NBUF", 3);
     nw = nw >= 24 ? 24 : nw >= 20 ? 20 : 16;
     nbuf = nbuf < 2 ? 2 : nbuf > 4 ? 4 : nbuf;
