@@ -332,7 +332,14 @@ def run_moe(args, device, world, rank, barrier):
     import torch
     import torch.distributed as dist
     from jangq_b200.stacks import MoEDecodeStack
-    stack = MoEDecodeStack(device=device, rank=rank, world=world)
+    ep_mode = os.environ.get("JANGQ_EP_MODE", "peer")
+    try:
+        stack = MoEDecodeStack(device=device, rank=rank, world=world, ep_mode=ep_mode)
+    except Exception as e:                                # no symmetric memory on this box: NCCL all-reduce instead
+        if rank == 0:
+            print(f"# peer exchange not available ({type(e).__name__}: {e}); using the NCCL all-reduce", file=sys.stderr)
+        ep_mode = "replicated"
+        stack = MoEDecodeStack(device=device, rank=rank, world=world, ep_mode=ep_mode)
     g = torch.Generator(device=device)
     g.manual_seed(11)
     # one token per GPU and step; with N > 1 every rank carries the rows of all N tokens (same seed everywhere)
@@ -407,10 +414,12 @@ def run_moe(args, device, world, rank, barrier):
     gbs = stack.bytes_per_token / (ms * 1e-3) / 1e9
     return {"prefill": prefill, "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
             "per_gpu_GBps": gbs, "hbm_frac": gbs / peak, "graph": graph is not None, "finite": finite,
+            "ep_mode": ep_mode if world > 1 else None,
             "workload": "config3 MoE stack, batch-1 decode per GPU: 48 layers x [q,k,v,o @6b + bf16 router + top-8 of "
                         "128 experts (768x2048 gate/up, 2048x768 down) @2b], group 64; experts sharded E/N per GPU, "
                         "N>1: every rank runs the replicated dense blocks on the N tokens of the step, its own experts on "
-                        "them, one NCCL all-reduce of the partial sums per layer; attention core not run"}
+                        "them, and the partial sums are added per layer over NVLink peer loads inside the residual+norm "
+                        "kernel (ep_mode peer) or by one NCCL all-reduce (ep_mode replicated); attention core not run"}
 
 
 def main():

@@ -244,6 +244,23 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
 int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k, int64_t T, int64_t H,
                         float eps, void* out, int act_dtype, jq_stream_t stream);
 
+/* Expert-parallel decode: sum of the ranks' partial expert outputs over NVLink peer memory fused with
+ * the residual and the RMS norm that consume it (one launch per layer instead of an all-reduce plus
+ * jq_residual_rmsnorm).  The reference runs on one device (its gather_qmm call sites,
+ * jang_tools/dsv41/model.py:1205-1230, sum the k expert outputs of a token locally); this is the same sum with
+ * the experts spread over `world` GPUs.  Every rank calls it with the same x[T,H] and its own y[T*k,H]
+ * (rows of pairs owned by other ranks zero, as jq_gather_qgemv2 leaves them).  peer_bufs: host array of
+ * `world` device addresses, entry p = rank p's exchange buffer of jq_ep_buffer_bytes(tcap, H) bytes,
+ * zero-filled once before the first call and mapped for peer access (entry `rank` is the caller's own).
+ * counters: tcap zero-initialised int32 on the device, private to the rank.  The wait for the peers is bounded
+ * (2 s); when it runs out the call's result is undefined and jq_device_status() returns JQ_ETIMEOUT.
+ * emulate_ranks = world (with rank = 0) runs every rank in one cooperative launch on one GPU: x, y, out and
+ * counters then hold the ranks' arrays back to back (testing without a second GPU). */
+size_t jq_ep_buffer_bytes(int64_t tcap, int64_t H);
+int jq_ep_combine_residual_rmsnorm(const void* x, const void* y, int k, int64_t T, int64_t H, float eps, void* out,
+                                   int act_dtype, const uint64_t* peer_bufs, int rank, int world, int64_t tcap,
+                                   int32_t* counters, int emulate_ranks, jq_stream_t stream);
+
 /* Reads the device-side status word (synchronises the device).  JQ_ETIMEOUT when a
  * kernel's bounded wait on a copy in flight ran out since the library was loaded.
  * No counterpart in the reference: its Metal path has no device-side waits. */

@@ -5,7 +5,8 @@ expert), with exactly one exchange each way:
 
   replicated tokens (batch-1 / small-batch decode: every rank holds the same rows):
       each rank runs its own experts on all rows (pairs of other ranks' experts are skipped by the
-      kernels) and the partial sums are added with one all-reduce over NVLink;
+      kernels) and the partial sums are added over NVLink: by `peer_combine_residual_rmsnorm` (peer loads
+      inside the kernel that also does the residual and the norm) or with one NCCL all-reduce;
   sharded tokens (prefill / large batches: every rank holds its own rows):
       dispatch  = all_to_all_single of the (row, local expert id, routing weight) triples, ordered by
                   destination rank, split sizes from a histogram of the top-k ids;
@@ -18,10 +19,13 @@ device-agnostic so that it is tested with gloo on CPU ranks.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Callable
 
 import torch
 import torch.distributed as dist
+
+from . import _lib
 
 
 def validate_splits(send_counts: torch.Tensor, recv_counts: torch.Tensor, n_pairs: int) -> None:
@@ -122,3 +126,61 @@ def partial_experts_fn(gate, up, down, expert_base: int, swiglu_limit: float = 0
     def fn(x, idx, w):
         return moe_layer(x, idx, w, gate, up, down, swiglu_limit=swiglu_limit, expert_base=expert_base, out_f32=True)
     return fn
+
+
+class PeerExchange:
+    """Exchange buffers for `peer_combine_residual_rmsnorm`: one buffer per rank, every rank holding the device
+    addresses of all of them.  `PeerExchange.connect(group, tcap, H, device)` allocates this rank's buffer in
+    torch's symmetric memory (which maps the peers' buffers for plain loads and stores over NVLink) and
+    exchanges the addresses; `PeerExchange.emulated(world, tcap, H, device)` puts every rank's buffer on one
+    GPU for the single-launch emulation used by the tests."""
+
+    def __init__(self, buffers, ptrs, rank, world, tcap, H, device, handle=None):
+        self.buffers, self.ptrs, self.rank, self.world, self.tcap, self.H = buffers, ptrs, rank, world, tcap, H
+        self.device, self.handle = device, handle
+        self.counters = torch.zeros((world if rank < 0 else 1) * tcap, dtype=torch.int32, device=device)
+        self._ptr_array = (ctypes.c_uint64 * world)(*ptrs)
+
+    @staticmethod
+    def nbytes(tcap: int, H: int) -> int:
+        return int(_lib.load().jq_ep_buffer_bytes(tcap, H))
+
+    @classmethod
+    def connect(cls, group, tcap: int, H: int, device) -> "PeerExchange":
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        n = cls.nbytes(tcap, H) // 4
+        buf = symm_mem.empty(n, dtype=torch.float32, device=device)
+        buf.zero_()
+        handle = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)          # every rank's buffer is zero before anyone signals into it
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        return cls([buf], ptrs, dist.get_rank(group), dist.get_world_size(group), tcap, H, device, handle)
+
+    @classmethod
+    def emulated(cls, world: int, tcap: int, H: int, device) -> "PeerExchange":
+        n = cls.nbytes(tcap, H) // 4
+        bufs = [torch.zeros(n, dtype=torch.float32, device=device) for _ in range(world)]
+        return cls(bufs, [b.data_ptr() for b in bufs], -1, world, tcap, H, device)
+
+
+def peer_combine_residual_rmsnorm(x: torch.Tensor, y: torch.Tensor, k: int, ex: PeerExchange,
+                                  eps: float | None = None) -> torch.Tensor:
+    """rms_norm(x + sum over ranks and slots of y): x [T, H] (the same on every rank), y [T*k, H] this rank's
+    expert outputs (zero rows for pairs owned elsewhere).  One launch; the ranks' partial sums cross NVLink
+    as peer loads inside it.  With an emulated exchange x and y carry a leading rank dimension."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, y)
+    emul = ex.rank < 0
+    T, H = x.shape[-2], x.shape[-1]
+    x, y = x.contiguous(), y.contiguous()
+    if eps is None:
+        eps = torch.finfo(x.dtype).eps
+    out = torch.empty_like(x)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_ep_combine_residual_rmsnorm(
+            x.data_ptr(), y.data_ptr(), k, T, H, float(eps), out.data_ptr(), _lib.dtype_id(x.dtype), ex._ptr_array,
+            0 if emul else ex.rank, ex.world, ex.tcap, ex.counters.data_ptr(), ex.world if emul else 0,
+            _lib.stream_ptr(dev)))
+    return out

@@ -36,6 +36,8 @@ class MoEDecodeStack:
       "replicated" (default)  every rank carries the rows of ALL tokens of the step through the replicated
                    dense blocks (a decode mat-vec streams the same weights for 1 or 8 rows), runs its own
                    experts on them and one all-reduce per layer adds the partial sums;
+      "peer"       as "replicated", but the partial sums cross NVLink as peer loads inside the kernel that also
+                   does the residual and the norm (moe_ep.peer_combine_residual_rmsnorm): no library collective;
       "gathered"   every rank carries its own rows; all-gather before, reduce-scatter after the experts."""
 
     def __init__(self, layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, inter=768, topk=8,
@@ -45,6 +47,9 @@ class MoEDecodeStack:
         self.world, self.rank, self.group = world, rank, group
         self.ep_mode = ep_mode
         self.e_local = experts // world
+        self.exchange = None
+        if world > 1 and ep_mode == "peer":
+            self.exchange = moe_ep.PeerExchange.connect(group, 16, hidden, device)
         self.base = rank * self.e_local
         dq, dkv = q_heads * head_dim, kv_heads * head_dim
         self.layers = []
@@ -93,7 +98,12 @@ class MoEDecodeStack:
                 continue
             if self.world == 1:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True, all_local=True)
-            elif self.ep_mode == "replicated":
+            elif self.ep_mode == "peer" and T <= self.exchange.tcap:
+                y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], expert_base=self.base,
+                                  return_slots=True, static_weights=True, few_token_path=True)
+                x = moe_ep.peer_combine_residual_rmsnorm(x, y, self.k, self.exchange)
+                continue
+            elif self.ep_mode in ("replicated", "peer"):
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], expert_base=self.base, out_f32=True,
                                   static_weights=True, few_token_path=T <= 16)
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)

@@ -254,3 +254,25 @@ def test_decode_stack_step_is_finite_and_deterministic():
 def test_device_status_clean_after_moe():
     torch.cuda.synchronize()
     assert _lib.load().jq_device_status() == 0
+
+
+# ---- expert-parallel exchange fused with residual + norm, every rank emulated in one cooperative launch --------
+@pytest.mark.parametrize("world,T,k,H", ((1, 3, 8, 2048), (2, 8, 8, 2048), (4, 4, 2, 1024), (8, 8, 8, 2048)))
+def test_peer_combine_residual_rmsnorm_emulated(world, T, k, H):
+    """out[r] = rms_norm(x + sum over ranks and slots of y[r]) for every rank r, repeated launches (sequence
+    numbers and the double buffer advance), against torch in f32.  All ranks must produce the same bits."""
+    from jangq_b200 import moe_ep
+    ex = moe_ep.PeerExchange.emulated(world, 8, H, DEV)
+    g = torch.Generator(device=DEV).manual_seed(world * 100 + T)
+    for rep in range(5):
+        x1 = torch.randn((T, H), device=DEV, generator=g).to(torch.bfloat16)
+        x = x1.unsqueeze(0).repeat(world, 1, 1).contiguous()
+        y = (torch.randn((world, T * k, H), device=DEV, generator=g) * 0.3).to(torch.bfloat16)
+        out = moe_ep.peer_combine_residual_rmsnorm(x, y, k, ex)
+        torch.cuda.synchronize()
+        tot = x1.float() + y.float().reshape(world, T, k, H).sum(dim=2).sum(dim=0)
+        ref = tot * torch.rsqrt((tot * tot).mean(dim=-1, keepdim=True) + torch.finfo(torch.bfloat16).eps)
+        for r in range(world):
+            assert torch.equal(out[r], out[0])
+        assert (out[0].float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max()
+    _lib.check(_lib.load().jq_device_status())
