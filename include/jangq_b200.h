@@ -253,7 +253,8 @@ int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k,
  * `world` device addresses, entry p = rank p's exchange buffer of jq_ep_buffer_bytes(tcap, H) bytes,
  * zero-filled once before the first call and mapped for peer access (entry `rank` is the caller's own).
  * counters: tcap zero-initialised int32 on the device, private to the rank.  The wait for the peers is bounded
- * (2 s); when it runs out the call's result is undefined and jq_device_status() returns JQ_ETIMEOUT.
+ * (2 s, or JANGQ_EP_WAIT_MS milliseconds); when it runs out the call's result is undefined, jq_device_status()
+ * returns JQ_ETIMEOUT and later calls do not wait again until jq_device_status_clear().
  * emulate_ranks = world (with rank = 0) runs every rank in one cooperative launch on one GPU: x, y, out and
  * counters then hold the ranks' arrays back to back (testing without a second GPU). */
 size_t jq_ep_buffer_bytes(int64_t tcap, int64_t H);
@@ -265,6 +266,10 @@ int jq_ep_combine_residual_rmsnorm(const void* x, const void* y, int k, int64_t 
  * kernel's bounded wait on a copy in flight ran out since the library was loaded.
  * No counterpart in the reference: its Metal path has no device-side waits. */
 int jq_device_status(void);
+
+/* Clears the status word (synchronises the device): for a caller that has handled a JQ_ETIMEOUT, e.g. by
+ * rebuilding its process group after a rank was lost.  No counterpart in the reference. */
+int jq_device_status_clear(void);
 
 #ifdef __cplusplus
 }

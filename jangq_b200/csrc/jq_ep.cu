@@ -18,13 +18,15 @@
 //
 // The peers' buffers are plain device pointers (obtained by the caller, e.g. from torch's symmetric
 // memory rendezvous); there is no TMA and no multicast in this file.
+#include <cstdlib>
+
 #include "jq_common.cuh"
 
 namespace jq {
 
 constexpr int EP_MAX_WORLD = 16;
 constexpr int EP_PER = 4;                                // columns per thread (H <= 4096)
-constexpr unsigned long long EP_WAIT_NS = 2000000000ull; // 2 s
+constexpr unsigned long long EP_WAIT_NS = 2000000000ull; // 2 s unless JANGQ_EP_WAIT_MS says otherwise
 
 struct EpPeers {
     float* buf[EP_MAX_WORLD];                            // [2][tcap][H] f32, then flags [tcap][EP_MAX_WORLD] u32
@@ -56,7 +58,8 @@ template <typename AT>
 __global__ void __launch_bounds__(1024)
 ep_combine_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, int k, int H, float eps,
                           AT* __restrict__ out, EpPeers peers, int rank0, int world, int tcap, int32_t* counters,
-                          int64_t x_rank_stride, int64_t y_rank_stride, int64_t ctr_rank_stride, int* status) {
+                          int64_t x_rank_stride, int64_t y_rank_stride, int64_t ctr_rank_stride, int* status,
+                          unsigned long long wait_ns) {
     __shared__ float part[32];
     __shared__ uint32_t seq_sh;
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -95,7 +98,7 @@ ep_combine_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, in
         bool ok = *reinterpret_cast<volatile int*>(status) == 0;   // after one timeout nobody waits again
         while (ok && (int32_t)(ep_load_acquire_sys(own) - s) < 0) {
             __nanosleep(100);
-            if (ep_now_ns() - t0 > EP_WAIT_NS) ok = false;
+            if (ep_now_ns() - t0 > wait_ns) ok = false;
         }
         if (!ok) atomicExch(status, 1);
     }
@@ -160,6 +163,11 @@ int jq_ep_combine_residual_rmsnorm(const void* x, const void* y, int k, int64_t 
     const int ranks = emulate_ranks ? world : 1;
     const int k_i = k, H_i = (int)H, rank_i = rank, world_i = world, tcap_i = (int)tcap;
     const int64_t xs = emulate_ranks ? T * H : 0, ys = emulate_ranks ? T * k * H : 0, cs = emulate_ranks ? tcap : 0;
+    unsigned long long wait_ns = EP_WAIT_NS;
+    if (const char* e = getenv("JANGQ_EP_WAIT_MS")) {
+        const long ms = atol(e);
+        if (ms > 0 && ms <= 60000) wait_ns = (unsigned long long)ms * 1000000ull;
+    }
     int rc = JQ_OK;
     JQ_DISPATCH_DTYPE16(act_dtype, AT, {
         const AT* xp = (const AT*)x;
@@ -167,7 +175,7 @@ int jq_ep_combine_residual_rmsnorm(const void* x, const void* y, int k, int64_t 
         AT* op = (AT*)out;
         void* args[] = {(void*)&xp, (void*)&yp, (void*)&k_i, (void*)&H_i, (void*)&eps, (void*)&op, (void*)&peers,
                         (void*)&rank_i, (void*)&world_i, (void*)&tcap_i, (void*)&counters, (void*)&xs, (void*)&ys,
-                        (void*)&cs, (void*)&status};
+                        (void*)&cs, (void*)&status, (void*)&wait_ns};
         const dim3 grid((unsigned)T, (unsigned)ranks);
         if (emulate_ranks) {
             // the ranks' CTAs wait on one another: a cooperative launch guarantees that they are co-resident

@@ -722,4 +722,11 @@ int jq_device_status(void) {
     return JQ_OK;
 }
 
+int jq_device_status_clear(void) {
+    const int v = 0;
+    if (cudaMemcpyToSymbol(jq::g_timeout_flag, &v, sizeof(int)) != cudaSuccess)
+        return jq::fail(JQ_ECUDA, "could not clear the device status word");
+    return JQ_OK;
+}
+
 }  // extern "C"

@@ -276,3 +276,29 @@ def test_peer_combine_residual_rmsnorm_emulated(world, T, k, H):
             assert torch.equal(out[r], out[0])
         assert (out[0].float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max()
     _lib.check(_lib.load().jq_device_status())
+
+
+def test_peer_exchange_missing_rank_times_out(monkeypatch):
+    """Failure detection without a fault: rank 0 of a world of 2 runs alone, nobody sets rank 1's flags, the
+    bounded wait runs out (20 ms here), the kernel returns, the status word reports it and can be cleared."""
+    from jangq_b200 import moe_ep
+    monkeypatch.setenv("JANGQ_EP_WAIT_MS", "20")
+    lib = _lib.load()
+    T, k, H = 2, 2, 1024
+    ex = moe_ep.PeerExchange.emulated(2, 8, H, DEV)
+    ex.rank = 0                                            # a real rank 0 whose peer never shows up
+    x = torch.randn((T, H), device=DEV).to(torch.bfloat16)
+    y = torch.randn((T * k, H), device=DEV).to(torch.bfloat16)
+    out = moe_ep.peer_combine_residual_rmsnorm(x, y, k, ex)
+    torch.cuda.synchronize()
+    assert out.shape == x.shape
+    with pytest.raises(jq.JangqError) as err:
+        _lib.check(lib.jq_device_status())
+    assert err.value.status == _lib.JQ_ETIMEOUT
+    _lib.check(lib.jq_device_status_clear())
+    _lib.check(lib.jq_device_status())
+    # the context is still usable
+    ex1 = moe_ep.PeerExchange.emulated(1, 8, H, DEV)
+    moe_ep.peer_combine_residual_rmsnorm(x.unsqueeze(0), y.unsqueeze(0), k, ex1)
+    torch.cuda.synchronize()
+    _lib.check(lib.jq_device_status())
