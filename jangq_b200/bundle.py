@@ -1,0 +1,325 @@
+"""JANG v2 bundle directories: read, write, and turn into the torch modules of this package.
+
+A v2 bundle (jang_tools/format/writer.py:30-193) is a directory with
+  config.json                    the model config plus a "quantization" block: default group_size/bits/mode
+                                 and one {"group_size", "bits", "mode"[, "storage_bits"]} entry per module whose
+                                 width differs (what mlx-lm's quantization predicate reads);
+  jang_config.json               {"format": "jang", "format_version": "2.0", "quantization": {"bit_widths_used",
+                                 "block_size", "tensor_quantization_manifest": {module: {bits, group_size, ...}}}};
+  model-XXXXX-of-YYYYY.safetensors   shards with metadata {"format": "mlx"}; a quantized module `m` is stored as
+                                 m.weight uint32 [.., N, K*bits/32], m.scales / m.biases float16 [.., N, K/gs];
+                                 a module's tensors never straddle shards;
+  model.safetensors.index.json   {"metadata": {"format", "format_version", "total_size"}, "weight_map"}.
+The bit width of a module is not stored with the tensor: it follows from the shapes,
+bits = w_cols * 32 / (s_cols * group_size) (jang_tools/loader.py:1922-1975), with the config's entry as the hint
+for the group size.  One-bit storage (jang_tools/affine.py:402-416) expands to two-bit codes on load.
+
+Host-side only: numpy + safetensors, no GPU needed until `load_modules` moves tensors to a device.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import numpy as np
+
+FORMAT_NAME = "jang"
+FORMAT_VERSION = "2.0"
+CONFIG_FILENAMES = ("jang_config.json", "jjqf_config.json", "jang_cfg.json", "mxq_config.json")   # loader.py:34
+INDEX_FILENAME = "model.safetensors.index.json"
+ALLOWED_BITS = (2, 3, 4, 5, 6, 8)
+ALLOWED_STORAGE_BITS = (1,) + ALLOWED_BITS
+
+
+class BundleError(ValueError):
+    pass
+
+
+def find_config_path(path) -> Path | None:
+    """The bundle's JANG config file, or None (jang_tools/loader.py:116-121)."""
+    p = Path(path)
+    for name in CONFIG_FILENAMES:
+        if (p / name).exists():
+            return p / name
+    return None
+
+
+def is_jang_model(path) -> bool:
+    """jang_tools/loader.py:149-151."""
+    return find_config_path(path) is not None
+
+
+def is_v2_model(path) -> bool:
+    """v2 = MLX-native safetensors (jang_tools/loader.py:154-181): an index file, or standard shards without
+    *.jang.safetensors ones, or format_version >= 2 in the JANG config.  A corrupt config reads as "not v2"."""
+    p = Path(path)
+    if (p / INDEX_FILENAME).exists():
+        return True
+    if any(p.glob("model-*.safetensors")) and not any(p.glob("*.jang.safetensors")):
+        return True
+    cfg = find_config_path(p)
+    if cfg is not None:
+        try:
+            version = str(json.loads(cfg.read_text()).get("format_version", "1.0"))
+            return int(version.split(".")[0]) >= 2
+        except (OSError, ValueError, AttributeError):
+            return False
+    return False
+
+
+def infer_bits_group_size(w_cols: int, s_cols: int, group_size_hint: int = 64, in_features: int | None = None,
+                          is_router: bool = False) -> tuple[int, int]:
+    """(bits, group_size) of a quantized tensor from its last dimensions: w_cols*32/bits == s_cols*gs.
+
+    Several pairs can satisfy the equation; the candidates are tried in the reference's order
+    (jang_tools/loader.py:1922-1975): with a known logical input width the group sizes that reproduce it come
+    first; router/gate tensors prefer 64; everything else prefers the hint (the module's configured group
+    size), then 64, 128.  Raises BundleError when no allowed width fits."""
+    hint = int(group_size_hint)
+    if in_features:
+        cands = [g for g in (hint, 64, 128, 32) if in_features % g == 0 and s_cols * g == in_features]
+        cands = list(dict.fromkeys(cands))
+        cands += [g for g in (hint, 64, 128, 32) if g not in cands]
+    elif is_router:
+        cands = list(dict.fromkeys([64, hint, 128]))
+    else:
+        cands = list(dict.fromkeys([hint, 64, 128]))
+    for gs in cands:
+        in_dim = s_cols * gs
+        if in_dim <= 0 or (w_cols * 32) % in_dim != 0:
+            continue
+        bits = (w_cols * 32) // in_dim
+        if bits in ALLOWED_BITS and (not in_features or in_dim == in_features):
+            return bits, gs
+    in_dim = s_cols * hint
+    if in_dim > 0 and (w_cols * 32) // in_dim in ALLOWED_BITS and (w_cols * 32) % in_dim == 0:
+        return (w_cols * 32) // in_dim, hint
+    raise BundleError(f"no (bits, group_size) fits weight columns {w_cols} and scale columns {s_cols}")
+
+
+def expand_1bit_to_2bit(packed: np.ndarray) -> np.ndarray:
+    """uint32-packed 1-bit codes -> uint32-packed 2-bit codes with the same values
+    (jang_tools/affine.py:402-416): bit i of a word becomes the 2-bit field i of the pair of output words."""
+    src = np.ascontiguousarray(packed, dtype=np.uint32)
+    bits = ((src[..., None] >> np.arange(32, dtype=np.uint32)) & np.uint32(1)).astype(np.uint32)   # [.., W, 32]
+    shifts = (2 * np.arange(16, dtype=np.uint32))
+    low = (bits[..., :16] << shifts).sum(axis=-1, dtype=np.uint64).astype(np.uint32)
+    high = (bits[..., 16:] << shifts).sum(axis=-1, dtype=np.uint64).astype(np.uint32)
+    out = np.empty(src.shape[:-1] + (src.shape[-1] * 2,), dtype=np.uint32)
+    out[..., 0::2] = low
+    out[..., 1::2] = high
+    return out
+
+
+@dataclass
+class QuantSpec:
+    bits: int
+    group_size: int
+    storage_bits: int | None = None
+
+
+@dataclass
+class Bundle:
+    """An opened bundle: configs, the tensor -> shard map, and lazy tensor reads."""
+    path: Path
+    config: dict
+    jang_config: dict
+    weight_map: dict[str, str]
+    _handles: dict = field(default_factory=dict, repr=False)
+
+    def names(self) -> list[str]:
+        return list(self.weight_map)
+
+    def tensor(self, name: str) -> np.ndarray:
+        from safetensors import safe_open
+        shard = self.weight_map.get(name)
+        if shard is None:
+            raise KeyError(name)
+        h = self._handles.get(shard)
+        if h is None:
+            h = self._handles[shard] = safe_open(str(self.path / shard), framework="np")
+        return h.get_tensor(name)
+
+    def quantized_modules(self) -> list[str]:
+        """Module paths that have .weight (uint32), .scales and .biases."""
+        names = set(self.weight_map)
+        return sorted(n[:-len(".scales")] for n in names
+                      if n.endswith(".scales") and n[:-len(".scales")] + ".weight" in names
+                      and n[:-len(".scales")] + ".biases" in names)
+
+    def default_group_size(self) -> int:
+        q = self.config.get("quantization") or {}
+        return int(q.get("group_size", (self.jang_config.get("quantization") or {}).get("block_size", 64)))
+
+    def quant_spec(self, module: str, w_shape=None, s_shape=None) -> QuantSpec:
+        """The module's (bits, group_size): shapes are authoritative (a config entry can be stale after a
+        loader-side repack), the config's per-module entry or default only supplies the group-size hint."""
+        q = self.config.get("quantization") or {}
+        entry = q.get(module) if isinstance(q.get(module), dict) else {}
+        manifest = (self.jang_config.get("quantization") or {}).get("tensor_quantization_manifest") or {}
+        m = manifest.get(module) if isinstance(manifest.get(module), dict) else {}
+        hint = int(entry.get("group_size", m.get("group_size", self.default_group_size())))
+        storage = entry.get("storage_bits", m.get("storage_bits"))
+        if w_shape is None:
+            w_shape = self.tensor(module + ".weight").shape
+        if s_shape is None:
+            s_shape = self.tensor(module + ".scales").shape
+        w_cols = int(w_shape[-1]) * (2 if storage == 1 else 1)
+        name_lower = module.lower()
+        is_router = ".gate." in name_lower or name_lower.endswith(".gate") or "shared_expert_gate" in name_lower
+        bits, gs = infer_bits_group_size(w_cols, int(s_shape[-1]), hint, is_router=is_router)
+        return QuantSpec(bits, gs, int(storage) if isinstance(storage, int) else None)
+
+    def close(self):
+        self._handles.clear()
+
+
+def _read_json(path: Path, what: str) -> dict:
+    try:
+        data = json.loads(path.read_text())
+    except (OSError, ValueError) as e:
+        raise BundleError(f"cannot read {what} {path}: {e}") from e
+    if not isinstance(data, dict):
+        raise BundleError(f"{what} {path} is not a JSON object")
+    return data
+
+
+def open_bundle(path) -> Bundle:
+    """Open a v2 bundle directory.  Without an index file the shards are listed and scanned."""
+    from safetensors import safe_open
+    p = Path(path)
+    cfg_path = find_config_path(p)
+    if cfg_path is None:
+        raise BundleError(f"{p} is not a JANG bundle (none of {', '.join(CONFIG_FILENAMES)})")
+    if not is_v2_model(p):
+        raise BundleError(f"{p} is a v1 bundle (*.jang.safetensors); repack it to v2 first")
+    jang_config = _read_json(cfg_path, "JANG config")
+    config = _read_json(p / "config.json", "model config") if (p / "config.json").exists() else {}
+    if (p / INDEX_FILENAME).exists():
+        weight_map = _read_json(p / INDEX_FILENAME, "index").get("weight_map")
+        if not isinstance(weight_map, dict):
+            raise BundleError(f"{p / INDEX_FILENAME} has no weight_map")
+        missing = sorted({s for s in weight_map.values() if not (p / s).exists()})
+        if missing:
+            raise BundleError(f"shards named by the index are missing: {missing[:3]}")
+    else:
+        weight_map = {}
+        for shard in sorted(p.glob("model*.safetensors")):
+            with safe_open(str(shard), framework="np") as f:
+                for k in f.keys():
+                    weight_map[k] = shard.name
+    return Bundle(p, config, jang_config, dict(weight_map))
+
+
+def _shard(tensors: dict[str, np.ndarray], max_bytes: int) -> list[list[str]]:
+    """Greedy shards in insertion order; the tensors of one module (same name up to the last dot) stay
+    together (jang_tools/format/writer.py:271-303)."""
+    groups: dict[str, list[str]] = {}
+    for name in tensors:
+        groups.setdefault(name.rsplit(".", 1)[0], []).append(name)
+    shards, cur, size = [], [], 0
+    for names in groups.values():
+        g = sum(tensors[n].nbytes for n in names)
+        if cur and size + g > max_bytes:
+            shards.append(cur)
+            cur, size = [], 0
+        cur.extend(names)
+        size += g
+    if cur:
+        shards.append(cur)
+    return shards
+
+
+def _write_json(path: Path, obj: dict) -> None:
+    path.write_text(json.dumps(obj, indent=2) + "\n")
+
+
+def write_bundle(path, tensors: dict[str, np.ndarray], model_config: dict, jang_config: dict,
+                 max_shard_bytes: int = 5 * 1024 ** 3) -> None:
+    """Write a v2 bundle the reference's loader reads (jang_tools/format/writer.py:30-193): config.json with the
+    quantization block (default = the narrowest width used, one entry per manifest module), jang_config.json
+    stamped format/format_version, shards with metadata {"format": "mlx"}, the index with total_size = bytes
+    of the shard files.  `tensors` holds MLX-layout arrays: m.weight uint32, m.scales / m.biases float16."""
+    from safetensors.numpy import save_file
+    p = Path(path)
+    p.mkdir(parents=True, exist_ok=True)
+    jq = jang_config.get("quantization") or {}
+    widths = jq.get("bit_widths_used") or [4]
+    block = int(jq.get("block_size", 64))
+    quantization = {"group_size": block, "bits": int(min(widths)), "mode": "affine"}
+    manifest = jq.get("tensor_quantization_manifest")
+    if isinstance(manifest, dict):
+        for module, spec in manifest.items():
+            if not isinstance(module, str) or not isinstance(spec, dict):
+                continue
+            bits, gs = spec.get("bits"), spec.get("group_size")
+            if isinstance(bits, int) and isinstance(gs, int):
+                entry = {"group_size": gs, "bits": bits, "mode": "affine"}
+                storage = spec.get("storage_bits")
+                if isinstance(storage, int):
+                    if isinstance(storage, bool) or storage not in ALLOWED_STORAGE_BITS:
+                        raise BundleError(f"invalid storage bit width {storage} for {module}")
+                    entry["storage_bits"] = storage
+                quantization[module] = entry
+    cfg_out = dict(model_config)
+    cfg_out["quantization"] = quantization
+    _write_json(p / "config.json", cfg_out)
+    jc = dict(jang_config)
+    jc.setdefault("format", FORMAT_NAME)
+    jc["format_version"] = FORMAT_VERSION
+    _write_json(p / CONFIG_FILENAMES[0], jc)
+    for name, arr in tensors.items():
+        if name.endswith(".weight") and name[:-len(".weight")] + ".scales" in tensors and arr.dtype != np.uint32:
+            raise BundleError(f"{name}: packed codes must be uint32, got {arr.dtype}")
+    shards = _shard(tensors, max_shard_bytes)
+    weight_map = {}
+    for i, names in enumerate(shards):
+        shard_name = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file({n: np.ascontiguousarray(tensors[n]) for n in names}, str(p / shard_name), metadata={"format": "mlx"})
+        for n in names:
+            weight_map[n] = shard_name
+    total = sum((p / s).stat().st_size for s in set(weight_map.values()))
+    _write_json(p / INDEX_FILENAME, {"metadata": {"format": FORMAT_NAME, "format_version": FORMAT_VERSION,
+                                                  "total_size": total}, "weight_map": weight_map})
+
+
+def load_modules(path, device="cuda", sidecar_dtype=None, only=None) -> dict:
+    """The bundle's quantized modules as this package's torch modules: {module path: JANGLinear} for 2-D
+    tensors, {module path: ExpertBank} for stacked experts [E, N, Kp].  Sidecars keep the stored float16
+    unless `sidecar_dtype` asks for a cast (the reference's runtime modules use bfloat16,
+    jangrt/linear.py:35-38).  One-bit storage is expanded to two-bit codes.  `only` filters module paths."""
+    import torch
+
+    from . import moe
+    from .linear import JANGLinear
+    b = open_bundle(path)
+    out = {}
+    for m in b.quantized_modules():
+        if only is not None and not only(m):
+            continue
+        w = b.tensor(m + ".weight")
+        s = b.tensor(m + ".scales")
+        bi = b.tensor(m + ".biases")
+        if w.dtype != np.uint32:
+            continue                                      # a float module that happens to have scales
+        spec = b.quant_spec(m, w.shape, s.shape)
+        if spec.storage_bits == 1:
+            w = expand_1bit_to_2bit(w)
+        dt = sidecar_dtype or torch.float16
+        wt = torch.from_numpy(w.view(np.int32)).to(device)
+        st = torch.from_numpy(np.ascontiguousarray(s)).to(device).to(dt)
+        bt = torch.from_numpy(np.ascontiguousarray(bi)).to(device).to(dt)
+        if w.ndim == 2:
+            n, k = w.shape[0], s.shape[-1] * spec.group_size
+            lin = JANGLinear(k, n, spec.bits, spec.group_size, bias=(m + ".bias") in b.weight_map, device=device, dtype=dt)
+            lin.weight, lin.scales, lin.biases = wt, st, bt
+            if lin.bias is not None:
+                lin.bias = torch.from_numpy(np.ascontiguousarray(b.tensor(m + ".bias"))).to(device).to(dt)
+            out[m] = lin
+        elif w.ndim == 3:
+            out[m] = moe.ExpertBank(wt, st, bt, spec.bits, spec.group_size)
+        else:
+            raise BundleError(f"{m}.weight has {w.ndim} dimensions")
+    b.close()
+    return out

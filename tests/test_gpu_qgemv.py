@@ -263,3 +263,26 @@ def test_persistent_integer_kernel_extremes(monkeypatch, bits, gs):
         y = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
         check(y, reference(x, wq, s, b, bits, gs), dtype)
     _lib.check(_lib.load().jq_device_status())
+
+
+def test_modules_loaded_from_a_reference_bundle():
+    """A bundle written by the reference's writer (tests/golden/bundle_v2) loads into JANGLinear / ExpertBank
+    with the widths inferred from the shapes, and the modules compute what the oracle computes from the files."""
+    import os
+    from jangq_b200 import bundle as B, moe
+    gold = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bundle_v2")
+    mods = B.load_modules(gold, device=DEV)
+    b = B.open_bundle(gold)
+    rng = np.random.default_rng(3)
+    for name in ("model.layers.0.self_attn.q_proj", "model.layers.0.mlp.gate_proj", "lm_head"):
+        lin = mods[name]
+        spec = b.quant_spec(name)
+        assert (lin.bits, lin.group_size) == (spec.bits, spec.group_size)
+        x = torch.from_numpy(rng.standard_normal((2, lin.in_features)).astype(np.float32)).to(DEV).to(torch.float16)
+        y = lin(x)
+        ref = jo.qmatmul(x.float().cpu().numpy(), b.tensor(name + ".weight"), b.tensor(name + ".scales").astype(np.float32),
+                         b.tensor(name + ".biases").astype(np.float32), spec.bits, spec.group_size)
+        check(y, ref, torch.float16)
+    bank = mods["model.layers.0.mlp.switch_mlp.up_proj"]
+    assert isinstance(bank, moe.ExpertBank) and bank.expert_bits == [3] * 4 and (bank.E, bank.N, bank.K) == (4, 16, 128)
+    b.close()
