@@ -244,6 +244,14 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
 int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k, int64_t T, int64_t H,
                         float eps, void* out, int act_dtype, jq_stream_t stream);
 
+/* Quantized embedding lookup, out[t, :] = dequantize(row ids[t]) with jq_dequantize's arithmetic (two
+ * roundings, q*s then +b).  Stands in for nn.QuantizedEmbedding's mx.dequantize(weight[ids], scales[ids],
+ * biases[ids]) and for jang-runtime/Metal/JANGEmbedding.metal:57-98 (jang_embedding_dequant).  ids: T int32
+ * on the device; an id outside [0, rows) yields a row of zeros.  out: [T, K] f32/f16/bf16, 16-byte aligned. */
+int jq_embedding(const int32_t* ids, int64_t T, const uint32_t* codes, const void* scales, const void* biases,
+                 int sidecar_dtype, int64_t rows, int64_t K, int bits, int group_size, void* out, int out_dtype,
+                 jq_stream_t stream);
+
 /* Expert-parallel decode: sum of the ranks' partial expert outputs over NVLink peer memory fused with
  * the residual and the RMS norm that consume it (one launch per layer instead of an all-reduce plus
  * jq_residual_rmsnorm).  The reference runs on one device (its gather_qmm call sites,

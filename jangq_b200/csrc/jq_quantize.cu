@@ -250,6 +250,55 @@ dequantize_kernel(const uint32_t* __restrict__ codes, const S* __restrict__ scal
     }
 }
 
+// Quantized embedding lookup: out[t] = dequantize(row ids[t]).  Same arithmetic and thread mapping as
+// dequantize_kernel, rows taken through ids; an id outside [0, rows) gives a row of zeros.
+template <typename S, typename O, int BITS>
+__global__ void __launch_bounds__(256)
+embedding_kernel(const uint32_t* __restrict__ codes, const S* __restrict__ scales, const S* __restrict__ biases,
+                 const int32_t* __restrict__ ids, O* __restrict__ out, int64_t n_oct, int oct_per_row, int words_per_row,
+                 int groups_per_row, int64_t rows, int gs_shift) {
+    const int64_t oct = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (oct >= n_oct) return;
+    const int64_t t = oct / oct_per_row;
+    const int o = (int)(oct - t * oct_per_row);
+    const int64_t row = ids[t];
+    float r[8];
+    if (row < 0 || row >= rows) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = 0.f;
+    } else {
+        const uint32_t* cr = codes + row * words_per_row;
+        const int byte0 = o * BITS;
+        const int w0 = byte0 >> 2;
+        const int sh = (byte0 & 3) * 8;
+        const uint32_t a = __ldg(cr + w0);
+        const uint32_t b = (w0 + 1 < words_per_row) ? __ldg(cr + w0 + 1) : 0u;
+        const uint32_t c = (BITS > 4 && w0 + 2 < words_per_row) ? __ldg(cr + w0 + 2) : 0u;
+        const uint32_t lo = __funnelshift_r(a, b, sh);
+        const uint32_t hi = __funnelshift_r(b, c, sh);
+        const unsigned long long bitsv = ((unsigned long long)hi << 32) | lo;
+        const int64_t g = row * groups_per_row + (o >> gs_shift);
+        const float s = Elt<S>::to_f32(scales[g]);
+        const float bs = Elt<S>::to_f32(biases[g]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t qv = (uint32_t)(bitsv >> (j * BITS)) & ((1u << BITS) - 1u);
+            r[j] = __fadd_rn(__fmul_rn((float)qv, s), bs);
+        }
+    }
+    O* op = out + oct * 8;
+    if constexpr (sizeof(O) == 4) {
+        float4* o4 = reinterpret_cast<float4*>(op);
+        o4[0] = make_float4(r[0], r[1], r[2], r[3]);
+        o4[1] = make_float4(r[4], r[5], r[6], r[7]);
+    } else {
+        O tmp[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tmp[j] = Elt<O>::from_f32(r[j]);
+        *reinterpret_cast<uint4*>(op) = *reinterpret_cast<const uint4*>(tmp);
+    }
+}
+
 }  // namespace jq
 
 extern "C" {
@@ -288,6 +337,32 @@ int jq_dequantize(const uint32_t* codes, const void* scales, const void* biases,
                 (dequantize_kernel<S, O, B><<<(unsigned)blocks, threads, 0, st>>>(
                     codes, (const S*)scales, (const S*)biases, (O*)out, n_oct, n_words, gs_shift)))))
     return check_launch("dequantize");
+}
+
+int jq_embedding(const int32_t* ids, int64_t T, const uint32_t* codes, const void* scales, const void* biases,
+                 int sidecar_dtype, int64_t rows, int64_t K, int bits, int group_size, void* out, int out_dtype,
+                 jq_stream_t stream) {
+    using namespace jq;
+    int rc = check_quant_shape(rows, K, bits, group_size);
+    if (rc != JQ_OK) return rc;
+    JQ_REQUIRE(valid_dtype(sidecar_dtype) && valid_dtype(out_dtype), JQ_EINVAL, "bad dtype");
+    JQ_REQUIRE(T >= 0, JQ_EINVAL, "bad token count");
+    if (T == 0 || K == 0) return JQ_OK;
+    JQ_REQUIRE(ids && codes && scales && biases && out, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(aligned(out, 16) && aligned(codes, 4) && K < (1ll << 31), JQ_EINVAL, "out must be 16-byte aligned");
+    const int64_t n_oct = T * (K / 8);
+    const int threads = 256;
+    const int64_t blocks = (n_oct + threads - 1) / threads;
+    JQ_REQUIRE(blocks < (1ll << 31), JQ_EUNSUPPORTED, "too many tokens for one launch");
+    const int gs_shift = group_size == 32 ? 2 : group_size == 64 ? 3 : 4;
+    cudaStream_t st = (cudaStream_t)stream;
+    JQ_DISPATCH_DTYPE(sidecar_dtype, S,
+        JQ_DISPATCH_DTYPE(out_dtype, O,
+            JQ_DISPATCH_BITS(bits, B,
+                (embedding_kernel<S, O, B><<<(unsigned)blocks, threads, 0, st>>>(
+                    codes, (const S*)scales, (const S*)biases, ids, (O*)out, n_oct, (int)(K / 8), (int)(K * bits / 32),
+                    (int)(K / group_size), rows, gs_shift)))))
+    return check_launch("embedding");
 }
 
 }  // extern "C"

@@ -105,6 +105,27 @@ def dequantize(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, gro
     return out.reshape(lead + (K,))
 
 
+def embedding(ids: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,
+              bits: int = 4, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Rows of a quantized table: out[.., :] = dequantize(wq[ids], scales[ids], biases[ids]) in one launch
+    (nn.QuantizedEmbedding.__call__; jang-runtime/Metal/JANGEmbedding.metal:57-98).  ids: integer tensor of
+    any shape on the table's device; ids outside the table give rows of zeros."""
+    dev = _lib.require_cuda(wq, scales, biases, ids)
+    lib = _lib.load()
+    wq = _as_i32(wq)
+    K = _check_triple(wq, scales, biases, bits, group_size)
+    if wq.dim() != 2:
+        raise JangqError(_lib.JQ_EINVAL, f"embedding table must be [rows, K*bits/32], got {tuple(wq.shape)}")
+    wq, scales, biases = wq.contiguous(), scales.contiguous(), biases.contiguous()
+    flat = ids.reshape(-1).to(torch.int32).contiguous()
+    out = torch.empty((flat.numel(), K), dtype=dtype or scales.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_embedding(flat.data_ptr(), flat.numel(), wq.data_ptr(), scales.data_ptr(), biases.data_ptr(),
+                                    _lib.dtype_id(scales.dtype), wq.shape[0], K, bits, group_size, out.data_ptr(),
+                                    _lib.dtype_id(out.dtype), _lib.stream_ptr(dev)))
+    return out.reshape(tuple(ids.shape) + (K,))
+
+
 def _qgemv(x2: torch.Tensor, wq, scales, biases, K, bits, group_size, out: torch.Tensor, flags: int = 0):
     lib = _lib.load()
     dev = x2.device

@@ -164,3 +164,26 @@ def test_shape_errors():
         jq.quantize(torch.zeros((4, 128), dtype=torch.float16, device=dev()), 64, 7)
     with pytest.raises(jq.JangqError):
         jq.quantize(torch.zeros((4, 128), dtype=torch.float16, device=dev()), 48, 4)
+
+
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+@pytest.mark.parametrize("gs,dtype", ((64, torch.bfloat16), (128, torch.float16), (32, torch.float32)))
+def test_embedding_rows_equal_dequantize(bits, gs, dtype):
+    """Row lookup = the same rows of the full dequantization, bit for bit; ids of any shape, repeated ids,
+    ids outside the table give zeros; the oracle's dequantizer agrees."""
+    rows, K = 301, 512
+    g = torch.Generator(device="cuda").manual_seed(bits * 7 + gs)
+    w = (torch.randn((rows, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    sd = torch.bfloat16 if dtype == torch.float32 else dtype
+    wq, s, b = jq.quantize(w.to(sd), gs, bits)
+    full = jq.dequantize(wq, s, b, gs, bits, dtype=dtype)
+    ids = torch.tensor([[0, 300, 17, 17], [5, -1, 301, 299]], device="cuda")
+    out = jq.embedding(ids, wq, s, b, gs, bits, dtype=dtype)
+    assert out.shape == (2, 4, K) and out.dtype == dtype
+    valid = (ids >= 0) & (ids < rows)
+    assert torch.equal(out[valid], full[ids[valid]])
+    assert torch.count_nonzero(out[~valid]) == 0
+    ref = jo.dequantize_affine(wq.cpu().numpy().view(np.uint32), s.float().cpu().numpy(), b.float().cpu().numpy(), bits, gs)
+    assert np.array_equal(out[0, 1].float().cpu().numpy(), ref[300].astype(np.float32) if dtype == torch.float32
+                          else torch.from_numpy(ref[300]).to(dtype).float().numpy())
+    assert jq.embedding(torch.zeros((0,), dtype=torch.int64, device="cuda"), wq, s, b, gs, bits).shape == (0, K)
