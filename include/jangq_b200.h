@@ -244,6 +244,17 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
 int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k, int64_t T, int64_t H,
                         float eps, void* out, int act_dtype, jq_stream_t stream);
 
+/* Activation-weighted affine quantizer: per group, `iterations` rounds of weighted least squares for scale and
+ * bias (weights importance[k] ~ E[x_k^2]) and re-rounding of the codes, float64 arithmetic, float16 sidecars,
+ * final codes from the stored sidecars.  Bit-identical to quantize_imatrix_affine_numpy
+ * (jang_tools/affine.py:279-399) for the same float32 weights and the same FLOORED importance vector (the
+ * caller applies the median floor of affine.py:310-312 on the host: it is a K-vector).  w: [rows, K] f32, f16 or
+ * bf16 (read as float32); importance: K float32 > 0; codes: uint32 [rows, K*bits/32]; scales, biases: float16
+ * [rows, K/group_size].  The reference's fourth return value (relative weighted error) is not computed. */
+int jq_quantize_imatrix(const void* w, int w_dtype, const float* importance, int64_t rows, int64_t K, int bits,
+                        int group_size, int iterations, uint32_t* codes, void* scales_f16, void* biases_f16,
+                        jq_stream_t stream);
+
 /* Quantized embedding lookup, out[t, :] = dequantize(row ids[t]) with jq_dequantize's arithmetic (two
  * roundings, q*s then +b).  Stands in for nn.QuantizedEmbedding's mx.dequantize(weight[ids], scales[ids],
  * biases[ids]) and for jang-runtime/Metal/JANGEmbedding.metal:57-98 (jang_embedding_dequant).  ids: T int32

@@ -105,6 +105,41 @@ def dequantize(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, gro
     return out.reshape(lead + (K,))
 
 
+def quantize_imatrix(w: torch.Tensor, importance, group_size: int = 64, bits: int = 4, iterations: int = 6):
+    """Activation-weighted affine fit (jang_tools/affine.py:279-399): importance[k] ~ E[x_k^2] of the input the
+    matrix consumes.  w [rows, K] (or [E, rows, K]) on the GPU, any float dtype (read as float32); returns
+    (wq uint32-as-int32, scales f16, biases f16) in the layout quantized_matmul / gather_qmm consume,
+    bit-identical to the reference.  The importance floor (1e-4 of the median positive value) is applied here
+    on the host."""
+    import numpy as np
+    dev = _lib.require_cuda(w)
+    lib = _lib.load()
+    if bits not in ALLOWED_BITS or group_size not in ALLOWED_GROUP_SIZES:
+        raise JangqError(_lib.JQ_EUNSUPPORTED, f"bits={bits}, group_size={group_size} not supported")
+    K = w.shape[-1]
+    imp = np.asarray(importance.detach().float().cpu().numpy() if isinstance(importance, torch.Tensor) else importance,
+                     dtype=np.float32)
+    if imp.shape != (K,):
+        raise JangqError(_lib.JQ_EINVAL, f"importance must have shape {(K,)}, got {imp.shape}")
+    if not np.isfinite(imp).all() or np.any(imp < 0):
+        raise JangqError(_lib.JQ_EINVAL, "importance values must be finite and nonnegative")
+    positive = imp[imp > 0]
+    floor = float(np.median(positive)) * 1e-4 if positive.size else 1.0
+    imp = np.maximum(imp, max(floor, 1e-12)).astype(np.float32)
+    lead = tuple(w.shape[:-1])
+    w2 = w.reshape(-1, K).contiguous()
+    rows = w2.shape[0]
+    wq = torch.empty((rows, K * bits // 32), dtype=torch.int32, device=dev)
+    s = torch.empty((rows, K // group_size), dtype=torch.float16, device=dev)
+    b = torch.empty_like(s)
+    impd = torch.from_numpy(imp).to(dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_quantize_imatrix(w2.data_ptr(), _lib.dtype_id(w2.dtype), impd.data_ptr(), rows, K, bits,
+                                           group_size, iterations, wq.data_ptr(), s.data_ptr(), b.data_ptr(),
+                                           _lib.stream_ptr(dev)))
+    return wq.reshape(lead + (wq.shape[-1],)), s.reshape(lead + (s.shape[-1],)), b.reshape(lead + (b.shape[-1],))
+
+
 def embedding(ids: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,
               bits: int = 4, dtype: torch.dtype | None = None) -> torch.Tensor:
     """Rows of a quantized table: out[.., :] = dequantize(wq[ids], scales[ids], biases[ids]) in one launch

@@ -324,3 +324,73 @@ def moe_layer(x, idx, w, gate, up, down, *, swiglu_limit: float = 0.0, act_dtype
         h2 = round_to((_silu(g2) * u2).astype(np.float32), act_dtype)
         out = out + round_to(qmatmul(h2, *sd), act_dtype)
     return out.astype(np.float32)
+
+
+# ---- importance-weighted affine fit (jang_tools/affine.py:279-399) ---------------------------------------------
+F16_TINY = np.float32(np.finfo(np.float16).smallest_normal)
+
+
+def to_f16_nonzero(scale: np.ndarray) -> np.ndarray:
+    """float16 cast of a scale that must not become zero (jang_tools/affine.py:44-51): magnitudes below the
+    smallest normal float16 become +-that value (a zero counts as positive)."""
+    scale = np.asarray(scale)
+    safe = np.where(np.abs(scale) < F16_TINY, np.copysign(F16_TINY, np.where(scale == 0, 1.0, scale)), scale)
+    return safe.astype(np.float16)
+
+
+def floor_importance(importance: np.ndarray) -> np.ndarray:
+    """jang_tools/affine.py:310-312: importance below 1e-4 of the median positive value (and below 1e-12) is
+    raised to that floor, so that no column is ignored entirely."""
+    imp = np.asarray(importance, dtype=np.float32)
+    positive = imp[imp > 0]
+    floor = float(np.median(positive)) * 1e-4 if positive.size else 1.0
+    return np.maximum(imp, max(floor, 1e-12))
+
+
+def quantize_imatrix_affine_codes(w: np.ndarray, importance: np.ndarray, bits: int, group_size: int,
+                                  iterations: int = 6):
+    """Activation-weighted affine fit, jang_tools/affine.py:279-399: per group, start from the min/max grid,
+    then `iterations` rounds of (weighted least squares for scale and bias given the codes; re-round the
+    codes), all in float64 with sums over the group in numpy's order; store float16 sidecars (scale kept
+    non-zero) and derive the final codes from the STORED sidecars in float32.  Returns (codes uint8 [rows, K],
+    scales f16 [rows, G], biases f16 [rows, G], relative weighted error)."""
+    matrix = np.asarray(w, dtype=np.float32)
+    rows, K = matrix.shape
+    G = K // group_size
+    imp = floor_importance(importance)
+    h = imp.reshape(1, G, group_size).astype(np.float64)
+    bins = float((1 << bits) - 1)
+    grouped = matrix.reshape(rows, G, group_size)
+    low = grouped.min(axis=-1).astype(np.float64)
+    high = grouped.max(axis=-1).astype(np.float64)
+    scale = np.maximum((high - low) / bins, 1e-8)
+    bias = low
+    codes = np.clip(np.rint((grouped - bias[..., None]) / scale[..., None]), 0, bins).astype(np.float64)
+    values = grouped.astype(np.float64)
+    sum_h = np.sum(h, axis=-1)
+    sum_hw = np.sum(h * values, axis=-1)
+    for _ in range(iterations):
+        sum_hq = np.sum(h * codes, axis=-1)
+        sum_hq2 = np.sum(h * codes * codes, axis=-1)
+        sum_hqw = np.sum(h * codes * values, axis=-1)
+        det = sum_h * sum_hq2 - sum_hq * sum_hq
+        fitted_scale = np.divide(sum_h * sum_hqw - sum_hq * sum_hw, det, out=scale.copy(), where=np.abs(det) > 1e-20)
+        fitted_bias = (sum_hw - fitted_scale * sum_hq) / sum_h
+        valid = np.isfinite(fitted_scale) & (np.abs(fitted_scale) >= 1e-8)
+        scale = np.where(valid, fitted_scale, scale)
+        bias = np.where(valid, fitted_bias, bias)
+        codes = np.clip(np.rint((values - bias[..., None]) / scale[..., None]), 0, bins)
+    scale_f16 = to_f16_nonzero(scale)
+    bias_f16 = bias.astype(np.float16)
+    ss, sb = scale_f16.astype(np.float32), bias_f16.astype(np.float32)
+    codes_u8 = np.clip(np.rint((grouped - sb[..., None]) / ss[..., None]), 0, bins).astype(np.uint8)
+    rec = codes_u8.astype(np.float32) * ss[..., None] + sb[..., None]
+    err = float(np.sum(h * np.square(rec - grouped), dtype=np.float64))
+    ref = float(np.sum(h * np.square(grouped), dtype=np.float64))
+    return codes_u8.reshape(rows, K), scale_f16, bias_f16, float(np.sqrt(err / max(ref, 1e-30)))
+
+
+def quantize_imatrix_affine(w, importance, bits, group_size, iterations: int = 6):
+    """Packed form: (uint32 [rows, K*bits/32], scales f16, biases f16, relative weighted error)."""
+    codes, s, b, e = quantize_imatrix_affine_codes(w, importance, bits, group_size, iterations)
+    return pack_rows(codes, bits), s, b, e

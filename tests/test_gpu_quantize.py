@@ -187,3 +187,41 @@ def test_embedding_rows_equal_dequantize(bits, gs, dtype):
     assert np.array_equal(out[0, 1].float().cpu().numpy(), ref[300].astype(np.float32) if dtype == torch.float32
                           else torch.from_numpy(ref[300]).to(dtype).float().numpy())
     assert jq.embedding(torch.zeros((0,), dtype=torch.int64, device="cuda"), wq, s, b, gs, bits).shape == (0, K)
+
+
+@pytest.mark.parametrize("gs", (32, 64, 128))
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+def test_imatrix_fit_bit_exact_against_reference_vectors(golden_dir, bits, gs):
+    """jq_quantize_imatrix against the reference's own outputs (tests/golden/imatrix_ref.npz): packed codes and
+    float16 sidecars bit for bit, including the corner groups (all-zero, constant, outlier, exact grid,
+    below the scale floor) and zero-importance columns."""
+    z = np.load(os.path.join(golden_dir, "imatrix_ref.npz"))
+    k = f"b{bits}_g{gs}"
+    w = torch.from_numpy(z[k + "_w"]).cuda()
+    wq, s, b = jq.quantize_imatrix(w, z[k + "_imp"], gs, bits)
+    assert np.array_equal(wq.cpu().numpy().view(np.uint32), z[k + "_packed"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), z[k + "_scales"].view(np.uint16))
+    assert np.array_equal(b.cpu().numpy().view(np.uint16), z[k + "_biases"].view(np.uint16))
+
+
+def test_imatrix_fit_iterations_shapes_and_oracle(golden_dir):
+    z = np.load(os.path.join(golden_dir, "imatrix_ref.npz"))
+    wq, s, b = jq.quantize_imatrix(torch.from_numpy(z["it2_w"]).cuda(), z["it2_imp"], 64, 3, iterations=2)
+    assert np.array_equal(wq.cpu().numpy().view(np.uint32), z["it2_packed"])
+    assert np.array_equal(s.cpu().numpy(), z["it2_scales"]) and np.array_equal(b.cpu().numpy(), z["it2_biases"])
+    # a larger seeded case against the oracle, stacked experts, a row count that leaves a partial block
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((3, 37, 1024)) * 0.02).astype(np.float32)
+    imp = (rng.standard_normal(1024) ** 2).astype(np.float32)
+    wq, s, b = jq.quantize_imatrix(torch.from_numpy(w).cuda(), torch.from_numpy(imp).cuda(), 64, 4)
+    pk, so, bo, _ = jo.quantize_imatrix_affine(w.reshape(-1, 1024), imp, 4, 64)
+    assert wq.shape == (3, 37, 128) and s.shape == (3, 37, 16)
+    assert np.array_equal(wq.cpu().numpy().view(np.uint32).reshape(pk.shape), pk)
+    assert np.array_equal(s.cpu().numpy().reshape(so.shape), so) and np.array_equal(b.cpu().numpy().reshape(bo.shape), bo)
+    # the fit lowers the importance-weighted error of the plain min/max quantizer
+    wq0, s0, b0 = jq.quantize(torch.from_numpy(w).cuda().half(), 64, 4)
+    d_fit = jq.dequantize(wq, s, b, 64, 4, dtype=torch.float32).cpu().numpy()
+    d_mm = jq.dequantize(wq0, s0, b0, 64, 4, dtype=torch.float32).cpu().numpy()
+    assert (imp * (d_fit - w) ** 2).sum() < (imp * (d_mm - w) ** 2).sum()
+    with pytest.raises(jq.JangqError):
+        jq.quantize_imatrix(torch.from_numpy(w).cuda(), imp[:-1], 64, 4)

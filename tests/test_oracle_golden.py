@@ -125,3 +125,19 @@ def test_moe_sort_and_naive_layer():
             u = x[t] @ deq[1][e].T
             ref[t] += w[t, j] * (((g / (1 + np.exp(-g))) * u) @ deq[2][e].T)
     assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-4
+
+
+def test_imatrix_affine_fit_matches_reference(golden_dir):
+    """oracle.quantize_imatrix_affine against the reference's quantize_imatrix_affine_numpy
+    (tests/golden/imatrix_ref.npz, made by make_golden_imatrix.py): codes, sidecars and the error bit for bit."""
+    z = _load(golden_dir, "imatrix_ref.npz")
+    for gs in (32, 64, 128):
+        for bits in (2, 3, 4, 5, 6, 8):
+            k = f"b{bits}_g{gs}"
+            packed, s, b, err = jo.quantize_imatrix_affine(z[k + "_w"], z[k + "_imp"], bits, gs)
+            assert np.array_equal(packed, z[k + "_packed"]), k
+            assert np.array_equal(s.view(np.uint16), z[k + "_scales"].view(np.uint16)), k
+            assert np.array_equal(b.view(np.uint16), z[k + "_biases"].view(np.uint16)), k
+            assert err == float(z[k + "_err"]), k
+    packed, s, b, _ = jo.quantize_imatrix_affine(z["it2_w"], z["it2_imp"], 3, 64, iterations=2)
+    assert np.array_equal(packed, z["it2_packed"]) and np.array_equal(s, z["it2_scales"]) and np.array_equal(b, z["it2_biases"])
