@@ -106,6 +106,19 @@ def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="q
             for w in wsrc:
                 ops.quantize(w, gs, bits)
         alg = per + bytes_w(N, K, bits, gs)
+    elif op == "quantize_imatrix":
+        # the C entry point directly: the Python wrapper floors the importance vector on the host
+        lib = _lib.load()
+        imp = (torch.randn((K,), generator=g, device=dev) ** 2 + 1e-3).float()
+        outs = [(torch.empty((N, K * bits // 32), dtype=torch.int32, device=dev),
+                 torch.empty((N, K // gs), dtype=torch.float16, device=dev),
+                 torch.empty((N, K // gs), dtype=torch.float16, device=dev)) for _ in wsrc]
+
+        def fn():
+            for w, (q, s, b) in zip(wsrc, outs):
+                _lib.check(lib.jq_quantize_imatrix(w.data_ptr(), _lib.dtype_id(w.dtype), imp.data_ptr(), N, K, bits, gs, 6,
+                                                   q.data_ptr(), s.data_ptr(), b.data_ptr(), _lib.stream_ptr(dev)))
+        alg = per + bytes_w(N, K, bits, gs)
     else:
         trip = [ops.quantize(w, gs, bits) for w in wsrc]
         del wsrc
@@ -121,7 +134,7 @@ def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="q
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "dequantize"))
+    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_imatrix", "dequantize"))
     ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small", "qgemm"))
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
