@@ -16,8 +16,9 @@
 // code (jang_tools/affine.py:227-252).  The per-weight division has a fast
 // path: t*rcp(scale) differs from the correctly rounded quotient by less than
 // 2^-23*|q| <= 3.1e-5 for |q| <= 257, so rint() of both agree unless the
-// quotient lies within that distance of a half-integer; such values (fewer than
-// 1 in 50) are recomputed with the exact division.
+// quotient lies within that distance of a half-integer; values within 1e-3 of one
+// (1 in 500; one warp instruction in 16 has such a lane) are recomputed with the
+// exact division.
 #include "jq_common.cuh"
 
 namespace jq {
@@ -155,10 +156,18 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __rest
         for (int j = 0; j < 16; ++j) {
             const float t = __fsub_rn(v[j], bias);
             const float qa = __fmul_rn(t, rcp);
-            float r = rintf(qa);
-            if (!(fabsf(qa - r) < 0.49f)) r = rintf(__fdiv_rn(t, scale));
-            r = fmaxf(fminf(r, bins), 0.0f);      // NaN -> 0
-            q[j] = (uint32_t)(int)r;
+            // rint() and the float->int conversion as one full-rate add: qa + 1.5*2^23 rounds qa to the nearest
+            // even-on-ties integer in the low mantissa bits (|qa| < 2^22)
+            const float shifted = __fadd_rn(qa, 12582912.0f);
+            const float ra = __fsub_rn(shifted, 12582912.0f);
+            if (fabsf(qa - ra) < 0.499f) {
+                const int qi = __float_as_int(shifted) - 0x4B400000;
+                q[j] = (uint32_t)min(max(qi, 0), (int)bins);
+            } else {
+                float r = rintf(__fdiv_rn(t, scale));
+                r = fmaxf(fminf(r, bins), 0.0f);  // NaN -> 0
+                q[j] = (uint32_t)(int)r;
+            }
         }
         if ((flags & JQ_QUANT_F16_TINY_GUARD) && Elt<S>::id == JQ_F16) {
             const float tiny = 6.103515625e-05f;  // smallest normal float16 (affine.py:43)
