@@ -255,6 +255,15 @@ int jq_quantize_imatrix(const void* w, int w_dtype, const float* importance, int
                         int group_size, int iterations, uint32_t* codes, void* scales_f16, void* biases_f16,
                         jq_stream_t stream);
 
+/* Randomized Hadamard rotation of rows: out[r] = H * diag(signs) * x[r], applied per power-of-two block of
+ * the row (K = 11008 -> blocks 8192, 2048, 512, 256), each block normalised by 1/sqrt(block), float32
+ * arithmetic in the reference's order.  Stands in for hadamard_rotate (jang_tools/turboquant/rotation.py:86-113):
+ * weights before quantization (jang_tools/convert.py:1496-1512, rows of W along K) and the input of every rotated
+ * linear layer at inference (jang_tools/loader.py:1763-1767).  signs: K float32 values +-1
+ * (numpy default_rng(seed).choice, rotation.py:43-59).  x, out: [rows, K] f32/f16/bf16 with leading dimensions. */
+int jq_hadamard_rotate(const void* x, int x_dtype, int64_t ldx, int64_t rows, int64_t K, const float* signs,
+                       void* out, int out_dtype, int64_t ldo, jq_stream_t stream);
+
 /* Quantized embedding lookup, out[t, :] = dequantize(row ids[t]) with jq_dequantize's arithmetic (two
  * roundings, q*s then +b).  Stands in for nn.QuantizedEmbedding's mx.dequantize(weight[ids], scales[ids],
  * biases[ids]) and for jang-runtime/Metal/JANGEmbedding.metal:57-98 (jang_embedding_dequant).  ids: T int32

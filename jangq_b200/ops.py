@@ -140,6 +140,41 @@ def quantize_imatrix(w: torch.Tensor, importance, group_size: int = 64, bits: in
     return wq.reshape(lead + (wq.shape[-1],)), s.reshape(lead + (s.shape[-1],)), b.reshape(lead + (b.shape[-1],))
 
 
+_SIGNS_CACHE: dict = {}
+
+
+def hadamard_signs(dim: int, seed: int = 42, device="cuda") -> torch.Tensor:
+    """The +-1 vector of the randomized Hadamard transform (jang_tools/turboquant/rotation.py:43-59; the
+    converter and the loader both use seed 42), float32 on `device`, cached."""
+    import numpy as np
+    key = (int(dim), int(seed), str(torch.device(device)))
+    t = _SIGNS_CACHE.get(key)
+    if t is None:
+        s = np.random.default_rng(seed).choice([-1.0, 1.0], size=dim).astype(np.float32)
+        t = _SIGNS_CACHE[key] = torch.from_numpy(s).to(device)
+    return t
+
+
+def hadamard_rotate(x: torch.Tensor, signs: torch.Tensor | None = None, seed: int = 42,
+                    dtype: torch.dtype | None = None) -> torch.Tensor:
+    """H * diag(signs) * x along the last axis, per power-of-two block (rotation.py:86-113).  The reference
+    returns float32 (its signs are float32); `dtype` defaults to x's dtype so that the result can feed the
+    decode mat-vec directly, pass torch.float32 for the reference's type."""
+    dev = _lib.require_cuda(x)
+    lib = _lib.load()
+    K = x.shape[-1]
+    if signs is None:
+        signs = hadamard_signs(K, seed, dev)
+    if signs.shape != (K,) or signs.dtype != torch.float32:
+        raise JangqError(_lib.JQ_EINVAL, f"signs must be float32 [{K}], got {signs.dtype} {tuple(signs.shape)}")
+    x2 = x.reshape(-1, K).contiguous()
+    out = torch.empty((x2.shape[0], K), dtype=dtype or x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_hadamard_rotate(x2.data_ptr(), _lib.dtype_id(x2.dtype), K, x2.shape[0], K, signs.data_ptr(),
+                                          out.data_ptr(), _lib.dtype_id(out.dtype), K, _lib.stream_ptr(dev)))
+    return out.reshape(tuple(x.shape[:-1]) + (K,))
+
+
 def embedding(ids: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,
               bits: int = 4, dtype: torch.dtype | None = None) -> torch.Tensor:
     """Rows of a quantized table: out[.., :] = dequantize(wq[ids], scales[ids], biases[ids]) in one launch

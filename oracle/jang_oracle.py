@@ -394,3 +394,57 @@ def quantize_imatrix_affine(w, importance, bits, group_size, iterations: int = 6
     """Packed form: (uint32 [rows, K*bits/32], scales f16, biases f16, relative weighted error)."""
     codes, s, b, e = quantize_imatrix_affine_codes(w, importance, bits, group_size, iterations)
     return pack_rows(codes, bits), s, b, e
+
+
+# ---- randomized Hadamard rotation (jang_tools/turboquant/rotation.py:17-113) ----------------------------------
+# The reference module needs MLX to import, so this restatement is checked against an explicit Hadamard matrix
+# (scipy) and the rotation's defining property instead of reference outputs: parity unpinned for the bit
+# pattern of the float32 results, pinned for the mathematics.
+def pow2_blocks(dim: int) -> list[int]:
+    """dim as a sum of distinct powers of two, largest first (rotation.py:26-40): 192 -> [128, 64]."""
+    blocks, rem = [], int(dim)
+    while rem > 0:
+        p = 1 << (rem.bit_length() - 1)
+        blocks.append(p)
+        rem -= p
+    return blocks
+
+
+def hadamard_signs(dim: int, seed: int = 0) -> np.ndarray:
+    """+-1 signs of the randomized transform (rotation.py:43-59): numpy's default_rng(seed).choice."""
+    return np.random.default_rng(seed).choice([-1.0, 1.0], size=dim).astype(np.float32)
+
+
+def _fwht_f32(x: np.ndarray) -> np.ndarray:
+    """Unnormalised Walsh-Hadamard butterflies along the last axis in float32, block size h = 1, 2, 4, ...:
+    (a, b) -> (a + b, a - b) for the two halves of every run of 2h elements, then * float32(1/sqrt(d))
+    (rotation.py:62-83)."""
+    x = np.array(x, dtype=np.float32)
+    d = x.shape[-1]
+    h = 1
+    while h < d:
+        y = x.reshape(x.shape[:-1] + (d // (2 * h), 2, h))
+        a, b = y[..., 0, :], y[..., 1, :]
+        x = np.concatenate([a + b, a - b], axis=-1).reshape(x.shape[:-1] + (d,))
+        h *= 2
+    return x * np.float32(1.0 / (d ** 0.5))
+
+
+def hadamard_rotate(x: np.ndarray, signs: np.ndarray) -> np.ndarray:
+    """H * diag(signs) * x per power-of-two block of the last axis (rotation.py:86-113), float32."""
+    x = np.asarray(x, dtype=np.float32)
+    parts, off = [], 0
+    for b in pow2_blocks(x.shape[-1]):
+        parts.append(_fwht_f32(x[..., off:off + b] * signs[off:off + b]))
+        off += b
+    return np.concatenate(parts, axis=-1)
+
+
+def hadamard_inverse(y: np.ndarray, signs: np.ndarray) -> np.ndarray:
+    """signs * H * y per block (rotation.py:116-140)."""
+    y = np.asarray(y, dtype=np.float32)
+    parts, off = [], 0
+    for b in pow2_blocks(y.shape[-1]):
+        parts.append(_fwht_f32(y[..., off:off + b]) * signs[off:off + b])
+        off += b
+    return np.concatenate(parts, axis=-1)

@@ -225,3 +225,28 @@ def test_imatrix_fit_iterations_shapes_and_oracle(golden_dir):
     assert (imp * (d_fit - w) ** 2).sum() < (imp * (d_mm - w) ** 2).sum()
     with pytest.raises(jq.JangqError):
         jq.quantize_imatrix(torch.from_numpy(w).cuda(), imp[:-1], 64, 4)
+
+
+@pytest.mark.parametrize("K", (64, 192, 4096, 11008, 14336))
+def test_hadamard_rotation_matches_oracle_bit_for_bit(K):
+    """The GPU butterflies do the float32 operations of the restated reference in the same order: equal bits
+    in float32; bf16 input/output rounds once at the end; the rotation cancels in a rotated mat-vec."""
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((3, K)).astype(np.float32)
+    s = jo.hadamard_signs(K, seed=42)
+    ref = jo.hadamard_rotate(x, s)
+    out = jq.hadamard_rotate(torch.from_numpy(x).cuda(), dtype=torch.float32)
+    assert np.array_equal(out.cpu().numpy(), ref)
+    assert np.array_equal(jq.hadamard_signs(K).cpu().numpy(), s)
+    xb = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    outb = jq.hadamard_rotate(xb)
+    refb = torch.from_numpy(jo.hadamard_rotate(xb.float().cpu().numpy(), s)).to(torch.bfloat16)
+    assert outb.dtype == torch.bfloat16 and torch.equal(outb.cpu(), refb)
+    # rotated weights, rotated input: the same product (a rotated bundle, loader.py:1763-1767)
+    if K % 64 == 0 and K <= 4096:
+        w = (rng.standard_normal((128, K)) * 0.02).astype(np.float32)
+        wr = jq.hadamard_rotate(torch.from_numpy(w).cuda(), dtype=torch.float32)
+        wq, sc, bi = jq.quantize(wr.to(torch.bfloat16), 64, 8)
+        y = jq.quantized_matmul(jq.hadamard_rotate(xb), wq, sc, bi, group_size=64, bits=8).float().cpu().numpy()
+        plain = xb.float().cpu().numpy() @ w.T
+        assert np.abs(y - plain).max() <= 2e-2 * np.abs(plain).max()

@@ -141,3 +141,23 @@ def test_imatrix_affine_fit_matches_reference(golden_dir):
             assert err == float(z[k + "_err"]), k
     packed, s, b, _ = jo.quantize_imatrix_affine(z["it2_w"], z["it2_imp"], 3, 64, iterations=2)
     assert np.array_equal(packed, z["it2_packed"]) and np.array_equal(s, z["it2_scales"]) and np.array_equal(b, z["it2_biases"])
+
+
+def test_hadamard_rotation_oracle_properties():
+    """The restated rotation against an explicit Hadamard matrix, and its defining properties."""
+    from scipy.linalg import hadamard
+    rng = np.random.default_rng(1)
+    assert jo.pow2_blocks(192) == [128, 64] and jo.pow2_blocks(11008) == [8192, 2048, 512, 256] and jo.pow2_blocks(64) == [64]
+    s = jo.hadamard_signs(64, seed=42)
+    assert set(np.unique(s)) <= {-1.0, 1.0} and np.array_equal(s, jo.hadamard_signs(64, seed=42))
+    x = rng.standard_normal((3, 64)).astype(np.float32)
+    ref = (x * s).astype(np.float64) @ hadamard(64).astype(np.float64) / 8.0
+    assert np.abs(jo.hadamard_rotate(x, s) - ref).max() < 1e-5
+    for dim in (192, 4096, 11008):
+        s = jo.hadamard_signs(dim, seed=42)
+        x = rng.standard_normal((2, dim)).astype(np.float32)
+        w = rng.standard_normal((5, dim)).astype(np.float32)
+        xr, wr = jo.hadamard_rotate(x, s), jo.hadamard_rotate(w, s)
+        assert np.abs(np.linalg.norm(xr, axis=-1) - np.linalg.norm(x, axis=-1)).max() < 1e-3
+        assert np.abs(xr @ wr.T - x @ w.T).max() < 2e-3 * np.abs(x @ w.T).max() + 1e-3      # the rotation cancels
+        assert np.abs(jo.hadamard_inverse(xr, s) - x).max() < 1e-4
