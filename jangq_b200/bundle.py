@@ -1,4 +1,5 @@
-"""JANG v2 bundle directories: read, write, and turn into the torch modules of this package.
+"""JANG bundle directories: read and write v2, repack v1 to v2, and turn a bundle into the torch modules of this
+package.
 
 A v2 bundle (jang_tools/format/writer.py:30-193) is a directory with
   config.json                    the model config plus a "quantization" block: default group_size/bits/mode
@@ -193,7 +194,7 @@ def open_bundle(path) -> Bundle:
     if cfg_path is None:
         raise BundleError(f"{p} is not a JANG bundle (none of {', '.join(CONFIG_FILENAMES)})")
     if not is_v2_model(p):
-        raise BundleError(f"{p} is a v1 bundle (*.jang.safetensors); repack it to v2 first")
+        raise BundleError(f"{p} is a v1 bundle (*.jang.safetensors); repack it with repack_v1_to_v2 first")
     jang_config = _read_json(cfg_path, "JANG config")
     config = _read_json(p / "config.json", "model config") if (p / "config.json").exists() else {}
     if (p / INDEX_FILENAME).exists():
@@ -323,3 +324,137 @@ def load_modules(path, device="cuda", sidecar_dtype=None, only=None) -> dict:
             raise BundleError(f"{m}.weight has {w.ndim} dimensions")
     b.close()
     return out
+
+
+V1_INDEX_NAMES = ("model.jang.index.json", "model.jjqf.index.json", "model.mxq.index.json")
+V1_SHARD_GLOBS = ("*.jang.safetensors", "*.jjqf.safetensors", "*.mxq.safetensors")
+V1_SUFFIXES = (".qweight", ".scales", ".zeros", ".biases", ".bit_map", ".block_offsets", ".shape", ".bits")
+
+
+def read_v1_tensors(path) -> dict[str, np.ndarray]:
+    """The tensors of a v1 bundle repacked into the v2 (MLX) layout, as jang_tools/loader.py:1326-1655 does on
+    load: for every quantized base `b` (b.qweight uint8 stream, b.scales, b.biases or b.zeros, b.bits or
+    b.bit_map, b.shape)
+      codes   = the byte stream padded to whole words, viewed uint32, cut to out*ceil(in*bits/32) words and
+                shaped [out, words] (stacked experts: [E, out, words]);
+      biases  = stored biases, or -scales*zeros for the oldest files, zeros if neither exists;
+      scales/biases are padded with 1.0 / 0.0 to out*ceil(in/block) groups and shaped like the codes;
+      a missing width means 4 bits; a missing shape means [n_blocks, block_size];
+      names   = b.weight / b.scales / b.biases; a stacked `...experts.gate_up_proj` is split along `out` into
+                `...switch_mlp.gate_proj` and `...switch_mlp.up_proj` (loader.py:1591-1606).
+    Sidecars come back as float16 when they were stored so (the repack is then lossless), float32 when biases
+    had to be computed from zero points.  Other tensors pass through unchanged."""
+    from safetensors import safe_open
+    p = Path(path)
+    cfg_path = find_config_path(p)
+    if cfg_path is None:
+        raise BundleError(f"{p} is not a JANG bundle")
+    block = int((_read_json(cfg_path, "JANG config").get("quantization") or {}).get("block_size", 64))
+    shards = []
+    for name in V1_INDEX_NAMES:
+        if (p / name).exists():
+            wm = _read_json(p / name, "index").get("weight_map") or {}
+            shards = [p / s for s in sorted(set(wm.values()))]
+            break
+    if not shards:
+        for pat in V1_SHARD_GLOBS:
+            shards.extend(sorted(p.glob(pat)))
+    if not shards:
+        raise BundleError(f"no v1 weight files in {p}")
+    raw = {}
+    for s in shards:
+        with safe_open(str(s), framework="np") as f:
+            for k in f.keys():
+                raw[k] = f.get_tensor(k)
+    bases = sorted({k[:-len(suf)] for k in raw for suf in V1_SUFFIXES if k.endswith(suf)})
+    quant_keys = {b + suf for b in bases for suf in V1_SUFFIXES}
+    out: dict[str, np.ndarray] = {}
+    for b in bases:
+        if b + ".qweight" not in raw or b + ".scales" not in raw:
+            raise BundleError(f"{b}: qweight or scales missing")
+        scales = raw[b + ".scales"]
+        keep_f16 = scales.dtype == np.float16
+        sc = scales.astype(np.float32).reshape(-1)
+        if b + ".biases" in raw:
+            keep_f16 = keep_f16 and raw[b + ".biases"].dtype == np.float16
+            bi = raw[b + ".biases"].astype(np.float32).reshape(-1)
+        elif b + ".zeros" in raw:
+            bi = -sc * raw[b + ".zeros"].astype(np.float32).reshape(-1)
+            keep_f16 = False
+        else:
+            bi = np.zeros_like(sc)
+        if b + ".bits" in raw:
+            bits = int(raw[b + ".bits"].reshape(-1)[0])
+        elif b + ".bit_map" in raw:
+            bits = int(raw[b + ".bit_map"].reshape(-1)[0])
+        else:
+            bits = 4
+        if bits not in ALLOWED_STORAGE_BITS:
+            raise BundleError(f"{b}: invalid bit width {bits}")
+        n_blocks = sc.shape[0]
+        shape = tuple(int(x) for x in raw[b + ".shape"].reshape(-1)) if b + ".shape" in raw else (n_blocks, block)
+        if len(shape) >= 3:
+            experts, e_out, in_dim = shape[0], int(np.prod(shape[1:-1])), shape[-1]
+            out_dim = experts * e_out
+        elif len(shape) == 2:
+            experts, e_out = 0, 0
+            out_dim, in_dim = shape
+        else:
+            raise BundleError(f"{b}: shape {shape} is not a matrix")
+        data = raw[b + ".qweight"].astype(np.uint8, copy=False).tobytes()
+        data += b"\x00" * ((4 - len(data) % 4) % 4)
+        words = np.frombuffer(data, dtype=np.uint32)
+        per_row = (in_dim * bits + 31) // 32
+        need = out_dim * per_row
+        if words.shape[0] < need:
+            words = np.pad(words, (0, need - words.shape[0]))
+        words = words[:need]
+        groups_row = (in_dim + block - 1) // block
+        need_g = out_dim * groups_row
+        if n_blocks < need_g:
+            sc = np.pad(sc, (0, need_g - n_blocks), constant_values=1.0)
+            bi = np.pad(bi, (0, need_g - n_blocks), constant_values=0.0)
+        lead = (experts, e_out) if experts else (out_dim,)
+        wq = words.reshape(lead + (per_row,))
+        dt = np.float16 if keep_f16 else np.float32
+        s2 = sc[:need_g].reshape(lead + (groups_row,)).astype(dt)
+        b2 = bi[:need_g].reshape(lead + (groups_row,)).astype(dt)
+        if experts and "gate_up_proj" in b:
+            mid = e_out // 2
+            prefix = b.replace("experts.gate_up_proj", "switch_mlp")
+            for nm, sl in (("gate_proj", slice(0, mid)), ("up_proj", slice(mid, e_out))):
+                out[f"{prefix}.{nm}.weight"] = np.ascontiguousarray(wq[:, sl, :])
+                out[f"{prefix}.{nm}.scales"] = np.ascontiguousarray(s2[:, sl, :])
+                out[f"{prefix}.{nm}.biases"] = np.ascontiguousarray(b2[:, sl, :])
+        else:
+            out[b + ".weight"], out[b + ".scales"], out[b + ".biases"] = wq, s2, b2
+    for k, v in raw.items():
+        if k not in quant_keys:
+            out[k] = v
+    return out
+
+
+def repack_v1_to_v2(src, dst, max_shard_bytes: int = 5 * 1024 ** 3) -> None:
+    """Rewrite a v1 bundle directory as a v2 bundle: tensors through `read_v1_tensors`, a manifest with the
+    width of every module (from the shapes), configs carried over."""
+    src = Path(src)
+    tensors = read_v1_tensors(src)
+    cfg_path = find_config_path(src)
+    jang_config = _read_json(cfg_path, "JANG config")
+    model_config = _read_json(src / "config.json", "model config") if (src / "config.json").exists() else {}
+    model_config.pop("quantization", None)
+    block = int((jang_config.get("quantization") or {}).get("block_size", 64))
+    manifest, widths = {}, set()
+    for name in tensors:
+        if name.endswith(".scales") and name[:-7] + ".weight" in tensors and tensors[name[:-7] + ".weight"].dtype == np.uint32:
+            m = name[:-7]
+            bits, gs = infer_bits_group_size(tensors[m + ".weight"].shape[-1], tensors[name].shape[-1], block)
+            widths.add(bits)
+            manifest[m] = {"bits": bits, "group_size": gs, "weight_key": m + ".weight", "scales_key": m + ".scales",
+                           "biases_key": m + ".biases", "weight_shape": list(tensors[m + ".weight"].shape),
+                           "scales_shape": list(tensors[name].shape), "biases_shape": list(tensors[m + ".biases"].shape)}
+    jc = {k: v for k, v in jang_config.items() if k != "format_version"}
+    q = dict(jc.get("quantization") or {})
+    q.update({"bit_widths_used": sorted(widths) or [4], "block_size": block, "tensor_quantization_manifest": manifest})
+    jc["quantization"] = q
+    write_bundle(dst, tensors, model_config, jc, max_shard_bytes)

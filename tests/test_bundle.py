@@ -130,3 +130,37 @@ def test_expand_1bit_known_answer():
     # values survive: the 2-bit codes of y are the bits of x
     ref = ((x[..., None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(1, -1)
     assert np.array_equal(jo.unpack_rows(y, 2, 128).reshape(1, -1), ref)
+
+
+GOLD_V1 = os.path.join(HERE, "golden", "bundle_v1")
+
+
+def test_v1_repack_dequantizes_to_the_reference_values(tmp_path):
+    """A v1 bundle written by the reference's legacy writer (tests/golden/bundle_v1), repacked to v2 and
+    dequantized by the oracle, gives the reference's own dequantize_tensor values bit for bit; the stacked
+    gate_up_proj experts are split into switch_mlp.gate_proj / up_proj."""
+    assert B.is_jang_model(GOLD_V1) and not B.is_v2_model(GOLD_V1)
+    exp = np.load(os.path.join(HERE, "golden", "bundle_v1_expected.npz"))
+    t = B.read_v1_tensors(GOLD_V1)
+    assert t["model.norm.weight"].dtype == np.float16 and t["model.norm.weight"].shape == (128,)
+    for name, bits in (("model.layers.0.self_attn.q_proj", 4), ("model.layers.0.mlp.down_proj", 3)):
+        wq, s, b = t[name + ".weight"], t[name + ".scales"], t[name + ".biases"]
+        assert wq.dtype == np.uint32 and s.dtype == np.float16
+        assert B.infer_bits_group_size(wq.shape[-1], s.shape[-1], 64) == (bits, 64)
+        deq = jo.dequantize_affine(wq, s.astype(np.float32), b.astype(np.float32), bits, 64)
+        assert np.array_equal(deq, exp[name])
+    full = exp["model.layers.0.mlp.experts.gate_up_proj"]                # [3, 8, 64]
+    for nm, sl in (("gate_proj", slice(0, 4)), ("up_proj", slice(4, 8))):
+        base = "model.layers.0.mlp.switch_mlp." + nm
+        wq, s, b = t[base + ".weight"], t[base + ".scales"], t[base + ".biases"]
+        assert wq.shape == (3, 4, 4)
+        deq = jo.dequantize_affine(wq.reshape(12, 4), s.astype(np.float32).reshape(12, 1), b.astype(np.float32).reshape(12, 1), 2, 64)
+        assert np.array_equal(deq.reshape(3, 4, 64), full[:, sl, :])
+    out = tmp_path / "v2"
+    B.repack_v1_to_v2(GOLD_V1, out)
+    b2 = B.open_bundle(out)
+    assert B.is_v2_model(out) and b2.jang_config["format_version"] == "2.0"
+    assert b2.quant_spec("model.layers.0.mlp.down_proj").bits == 3
+    assert b2.config["quantization"]["model.layers.0.mlp.switch_mlp.up_proj"] == {"group_size": 64, "bits": 2, "mode": "affine"}
+    assert np.array_equal(b2.tensor("model.layers.0.self_attn.q_proj.weight"), t["model.layers.0.self_attn.q_proj.weight"])
+    b2.close()
