@@ -3,7 +3,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py [--ref /path/to/reference]
+    python tests/golden/make_golden.py --ref /path/to/reference
 
 It imports the reference's own numpy code (jang-tools/jang_tools/affine.py,
 pack.py, quantize.py) and reads the reference's MLX-generated fixture
@@ -45,7 +45,8 @@ def adversarial_matrix(rng, rows, K, gs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("JANGQ_REF", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("JANGQ_REF"), required="JANGQ_REF" not in os.environ,
+                    help="root of the reference source tree (or set JANGQ_REF)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "jang-tools"))
     from jang_tools.affine import dequantize_affine_numpy, quantize_native_affine_numpy

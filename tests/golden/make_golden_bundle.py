@@ -3,7 +3,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden_bundle.py [--ref /path/to/reference]
+    python tests/golden/make_golden_bundle.py --ref /path/to/reference
 
 It quantizes four small seeded matrices with jang_tools.affine.quantize_native_affine_numpy (8-bit q_proj,
 2-bit gate_proj, 3-bit stacked experts, 6-bit lm_head with group size 128), adds one float tensor, and writes
@@ -24,7 +24,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("JANGQ_REF"), required="JANGQ_REF" not in os.environ,
+                    help="root of the reference source tree (or set JANGQ_REF)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "jang-tools"))
     from jang_tools.affine import quantize_native_affine_numpy

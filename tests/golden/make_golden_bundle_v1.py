@@ -3,7 +3,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden_bundle_v1.py [--ref /path/to/reference]
+    python tests/golden/make_golden_bundle_v1.py --ref /path/to/reference
 
 Quantizes three seeded tensors with jang_tools.quantize.quantize_tensor(method="rtn") (a 4-bit 2-D matrix, a
 3-bit matrix, a 2-bit stacked expert tensor [E, out, in] named ...experts.gate_up_proj), writes them with
@@ -24,7 +24,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("JANGQ_REF"), required="JANGQ_REF" not in os.environ,
+                    help="root of the reference source tree (or set JANGQ_REF)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "jang-tools"))
     from jang_tools.format.writer import write_jang_model

@@ -3,7 +3,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden_imatrix.py [--ref /path/to/reference]
+    python tests/golden/make_golden_imatrix.py --ref /path/to/reference
 
 Calls jang_tools.affine.quantize_imatrix_affine_numpy on seeded matrices (every width, group sizes 32/64/128,
 with hand-made corner groups and importance vectors that include zeros and a wide dynamic range) and stores
@@ -35,7 +35,8 @@ def case(rng, rows, K, gs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("JANGQ_REF"), required="JANGQ_REF" not in os.environ,
+                    help="root of the reference source tree (or set JANGQ_REF)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "jang-tools"))
     from jang_tools.affine import quantize_imatrix_affine_numpy
