@@ -235,6 +235,13 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
                  int num_experts, int k, int renorm, float scale, int32_t* idx_out, float* w_out,
                  int32_t* counters, float* logits_ws, jq_stream_t stream);
 
+/* jq_moe_route with the residual + RMS norm in front of it folded in: x_out = rms_norm(x + res) (no weight, f32
+ * arithmetic, rounded to the activation type; x, res, x_out: [T, H] contiguous, H <= 4096), then the router on
+ * x_out.  One launch instead of jq_residual_rmsnorm + jq_moe_route in the synthetic decode stacks. */
+int jq_moe_route_norm(const void* x, const void* res, int act_dtype, int64_t T, int64_t H, float eps, void* x_out,
+                      const void* router_w, int num_experts, int k, int renorm, float scale, int32_t* idx_out,
+                      float* w_out, int32_t* counters, float* logits_ws, jq_stream_t stream);
+
 /* out[t, :] = v / sqrt(mean(v^2) + eps) with v = x[t, :] + sum_{j<k} y[t*k + j, :], f32 arithmetic,
  * activation type out; y is f32 when y_f32 != NULL (then k = 1), else of the activation type.  With k > 1
  * it is also the unweighted combine of the routed experts' k slot rows (their routing weights are applied

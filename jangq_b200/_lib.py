@@ -65,6 +65,8 @@ SIGNATURES = {
     "jq_gather_qgemv2": (C.c_int, [_p, _i32, _i64, _i32, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i64, _i64,
                                    _i32, _i32, _p, _p, _i64, _i32, _i32, _p]),
     "jq_moe_route": (C.c_int, [_p, _i32, _i64, _i64, _i64, _p, _i32, _i32, _i32, C.c_float, _p, _p, _p, _p, _p]),
+    "jq_moe_route_norm": (C.c_int, [_p, _p, _i32, _i64, _i64, C.c_float, _p, _p, _i32, _i32, _i32, C.c_float, _p, _p, _p,
+                                    _p, _p]),
     "jq_residual_rmsnorm": (C.c_int, [_p, _p, _p, _i32, _i64, _i64, C.c_float, _p, _i32, _p]),
     "jq_device_status_clear": (C.c_int, []),
     "jq_hadamard_rotate": (C.c_int, [_p, _i32, _i64, _i64, _i64, _p, _p, _i32, _i64, _p]),

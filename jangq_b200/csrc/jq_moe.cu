@@ -184,20 +184,57 @@ __global__ void combine_kernel(const AT* __restrict__ y, int64_t ldy, const int3
 // id), w = p / (sum p + 1e-20) * scale  (dots3/ops.py:149-162; the plain softmax-top-k of the mlx-lm
 // switch layers).  One CTA per token; warps split the experts, warp 0 selects.
 constexpr int ROUTE_MAX_E = 1024;
-template <typename AT>
+// FUSED: the token is first formed as rms_norm(x + res) (no weight, f32, rounded to the activation type:
+// residual_rmsnorm_kernel's arithmetic up to the order of the sum of squares), kept in shared memory for the
+// dot products, and written to x_out by the CTAs of expert block 0 -- the residual + norm launch in front of
+// the router disappears.
+template <typename AT, bool FUSED>
 __global__ void __launch_bounds__(256)
 route_kernel(const AT* __restrict__ x, int64_t ldx, const AT* __restrict__ wr, int H, int E, int k, int renorm,
              float scale, int32_t* __restrict__ idx_out, float* __restrict__ w_out, float* __restrict__ ws_logits,
-             int* __restrict__ ws_count) {
+             int* __restrict__ ws_count, const AT* __restrict__ res, float eps, AT* __restrict__ x_out) {
     // grid (T, ceil(E / 8)): warp w of CTA (t, b) computes the logit of expert 8b + w; the CTA that finishes
     // last for its token (a counter, no waiting) runs the selection over all E logits
     __shared__ float p[ROUTE_MAX_E];
     __shared__ int is_last;
+    __shared__ __align__(16) AT xn[FUSED ? 4096 : 8];
+    __shared__ float part[8];
     pdl_enter();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.y * 8 + warp;
+    if constexpr (FUSED) {                                 // H <= 4096: 16 columns per thread
+        float v[16];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = threadIdx.x + i * 256;
+            v[i] = 0.f;
+            if (c < H) {
+                v[i] = Elt<AT>::to_f32(x[(int64_t)t * ldx + c]) + Elt<AT>::to_f32(res[(int64_t)t * H + c]);
+                ss = fmaf(v[i], v[i], ss);
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
+        if (lane == 0) part[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot += part[i];
+        const float r = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = threadIdx.x + i * 256;
+            if (c < H) {
+                const AT o = Elt<AT>::from_f32(v[i] * r);
+                xn[c] = o;
+                if (blockIdx.y == 0) x_out[(int64_t)t * H + c] = o;
+            }
+        }
+        __syncthreads();
+    }
     if (e < E) {
-        const AT* xr = x + (int64_t)t * ldx;
+        const AT* xr = FUSED ? xn : x + (int64_t)t * ldx;
         const AT* wrow = wr + (int64_t)e * H;
         float acc = 0.f;
         for (int c = lane * 8; c < H; c += 256) {          // H % 8 == 0, 16-byte loads
@@ -333,9 +370,29 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
     JQ_REQUIRE(T <= 65535, JQ_EUNSUPPORTED, "jq_moe_route is the few-token path");
     const dim3 grid((unsigned)T, (unsigned)((num_experts + 7) / 8));
     JQ_DISPATCH_DTYPE16(act_dtype, AT,
-        JQ_CUDA_OK(launch_pdl(route_kernel<AT>, grid, dim3(256), 0, (cudaStream_t)stream, (const AT*)x, ldx,
+        JQ_CUDA_OK(launch_pdl(route_kernel<AT, false>, grid, dim3(256), 0, (cudaStream_t)stream, (const AT*)x, ldx,
                               (const AT*)router_w, (int)H, num_experts, k, renorm, scale, idx_out, w_out, logits_ws,
-                              (int*)counters)))
+                              (int*)counters, (const AT*)nullptr, 0.f, (AT*)nullptr)))
+    return JQ_OK;
+}
+
+int jq_moe_route_norm(const void* x, const void* res, int act_dtype, int64_t T, int64_t H, float eps, void* x_out,
+                      const void* router_w, int num_experts, int k, int renorm, float scale, int32_t* idx_out,
+                      float* w_out, int32_t* counters, float* logits_ws, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(T >= 0 && H > 0 && H % 8 == 0 && H <= 4096, JQ_EINVAL, "jq_moe_route_norm needs H %% 8 == 0, H <= 4096");
+    JQ_REQUIRE(num_experts > 0 && num_experts <= ROUTE_MAX_E, JQ_EUNSUPPORTED, "jq_moe_route_norm takes at most %d experts",
+               ROUTE_MAX_E);
+    JQ_REQUIRE(k > 0 && k <= num_experts, JQ_EINVAL, "k must be in [1, num_experts]");
+    if (T == 0) return JQ_OK;
+    JQ_REQUIRE(x && res && x_out && router_w && idx_out && w_out && counters && logits_ws, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(aligned(router_w, 16), JQ_EINVAL, "the router weights must be 16-byte aligned");
+    JQ_REQUIRE(T <= 65535, JQ_EUNSUPPORTED, "jq_moe_route_norm is the few-token path");
+    const dim3 grid((unsigned)T, (unsigned)((num_experts + 7) / 8));
+    JQ_DISPATCH_DTYPE16(act_dtype, AT,
+        JQ_CUDA_OK(launch_pdl(route_kernel<AT, true>, grid, dim3(256), 0, (cudaStream_t)stream, (const AT*)x, H,
+                              (const AT*)router_w, (int)H, num_experts, k, renorm, scale, idx_out, w_out, logits_ws,
+                              (int*)counters, (const AT*)res, eps, (AT*)x_out)))
     return JQ_OK;
 }
 

@@ -275,6 +275,29 @@ def route_from_hidden(x: torch.Tensor, router_w: torch.Tensor, k: int, renorm: b
     return idx, w
 
 
+def route_norm_from_hidden(x: torch.Tensor, res: torch.Tensor, router_w: torch.Tensor, k: int, renorm: bool = True,
+                           scale: float = 1.0, eps: float | None = None):
+    """(rms_norm(x + res), idx, w): residual_rmsnorm followed by route_from_hidden in one launch."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x, res, router_w)
+    if x.dtype != router_w.dtype or x.dtype != res.dtype or x.dtype not in (torch.bfloat16, torch.float16):
+        raise JangqError(_lib.JQ_EINVAL, "route_norm_from_hidden: x, res and router_w must share a 16-bit dtype")
+    T, H = x.shape
+    E = router_w.shape[0]
+    x, res, router_w = x.contiguous(), res.contiguous(), router_w.contiguous()
+    if eps is None:
+        eps = torch.finfo(x.dtype).eps
+    xo = torch.empty_like(x)
+    idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+    w = torch.empty((T, k), dtype=torch.float32, device=dev)
+    cnt, ws = _route_workspace(dev, T, E)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_moe_route_norm(x.data_ptr(), res.data_ptr(), _lib.dtype_id(x.dtype), T, H, float(eps),
+                                         xo.data_ptr(), router_w.data_ptr(), E, k, 1 if renorm else 0, float(scale),
+                                         idx.data_ptr(), w.data_ptr(), cnt.data_ptr(), ws.data_ptr(), _lib.stream_ptr(dev)))
+    return xo, idx, w
+
+
 _ROUTE_WS = {}
 
 

@@ -89,8 +89,11 @@ class MoEDecodeStack:
                 q = lay["q"](x)
                 lay["k"](x)
                 lay["v"](x)
-            x = moe.residual_rmsnorm(x, lay["o"](q))
-            idx, w = moe.route_from_hidden(x, lay["router"], self.k)
+            if T <= 16 and self.H <= 4096:       # residual + norm folded into the router launch
+                x, idx, w = moe.route_norm_from_hidden(x, lay["o"](q), lay["router"], self.k)
+            else:
+                x = moe.residual_rmsnorm(x, lay["o"](q))
+                idx, w = moe.route_from_hidden(x, lay["router"], self.k)
             if self.world == 1 and T * self.k < moe.SORT_THRESHOLD:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], all_local=True, return_slots=True,
                                   static_weights=True)

@@ -302,3 +302,21 @@ def test_peer_exchange_missing_rank_times_out(monkeypatch):
     moe_ep.peer_combine_residual_rmsnorm(x.unsqueeze(0), y.unsqueeze(0), k, ex1)
     torch.cuda.synchronize()
     _lib.check(lib.jq_device_status())
+
+
+@pytest.mark.parametrize("T,H,E,k", ((1, 2048, 128, 8), (8, 2048, 128, 8), (3, 4096, 64, 6), (5, 1024, 512, 10)))
+def test_route_with_folded_residual_norm(T, H, E, k):
+    """route_norm_from_hidden = residual_rmsnorm then route_from_hidden: the normalised rows agree to one
+    rounding of the activation type and, fed the fused kernel's own rows, the unfused router returns the
+    same experts and weights."""
+    from jangq_b200 import moe
+    g = torch.Generator(device=DEV).manual_seed(T * 31 + H)
+    x = torch.randn((T, H), device=DEV, generator=g).to(torch.bfloat16)
+    res = torch.randn((T, H), device=DEV, generator=g).to(torch.bfloat16)
+    wr = (torch.randn((E, H), device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    xo, idx, w = moe.route_norm_from_hidden(x, res, wr, k)
+    ref = moe.residual_rmsnorm(x, res)
+    assert (xo.float() - ref.float()).abs().max() <= 2.0 ** -7 * ref.float().abs().max()
+    idx2, w2 = moe.route_from_hidden(xo, wr, k)
+    torch.cuda.synchronize()
+    assert torch.equal(idx, idx2) and torch.equal(w, w2)
