@@ -425,7 +425,7 @@ def run_moe(args, device, world, rank, barrier):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
