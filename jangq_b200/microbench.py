@@ -132,9 +132,25 @@ def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="q
             "bytes": alg, "copies": copies}
 
 
+def bench_moe_decode(layers, T, iters):
+    """Few-token decode through `layers` layers of the config-3 MoE stack (stacks.MoEDecodeStack, one GPU): one
+    eager pass (plain launches, what a launch-list capture sees), then the median time of a graph replay."""
+    from .stacks import MoEDecodeStack
+    dev = torch.device("cuda")
+    stack = MoEDecodeStack(layers=layers, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    x = torch.randn((T, stack.H), generator=g, device=dev).to(torch.bfloat16)
+    stack.step(x)
+    torch.cuda.synchronize()
+    ms = _time_graph(lambda: stack.step(x), iters)
+    return {"op": "moe_decode", "layers": layers, "T": T, "us_per_layer": ms * 1e3 / layers, "ms_per_step": ms,
+            "bytes_per_token": stack.bytes_per_token}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_imatrix", "dequantize"))
+    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_imatrix", "dequantize", "moe_decode"))
     ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small", "qgemm"))
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -143,6 +159,7 @@ def main():
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--rotate-mb", type=float, default=512.0)
+    ap.add_argument("--layers", type=int, default=4, help="moe_decode: layers of the stack")
     ap.add_argument("--pdl", action="store_true", help="launch with JQ_GEMV_STATIC_WEIGHTS (overlapped launches)")
     a = ap.parse_args()
     _lib.load()
@@ -163,7 +180,9 @@ def main():
                         for M in (1, 8):
                             print(json.dumps(bench_qgemv(N, K, bits, gs, M, a.iters, a.rotate_mb, flags=flags)), flush=True)
         return
-    if a.op == "qgemv":
+    if a.op == "moe_decode":
+        print(json.dumps(bench_moe_decode(a.layers, a.M, a.iters)))
+    elif a.op == "qgemv":
         print(json.dumps(bench_qgemv(a.N, a.K, a.bits, a.gs, a.M, a.iters, a.rotate_mb, flags=flags)))
     elif a.op == "qgemm":
         print(json.dumps(bench_qgemm(a.N, a.K, a.bits, a.gs, a.M, a.iters)))
