@@ -202,6 +202,16 @@ route_kernel(const AT* __restrict__ x, int64_t ldx, const AT* __restrict__ wr, i
     pdl_enter();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.y * 8 + warp;
+    uint4 wpre[FUSED ? 16 : 1];                            // FUSED: the expert's router row, requested before the norm
+    if constexpr (FUSED) {
+        if (e < E) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int c = lane * 8 + 256 * i;
+                if (c < H) wpre[i] = __ldg(reinterpret_cast<const uint4*>(wr + (int64_t)e * H + c));
+            }
+        }
+    }
     if constexpr (FUSED) {                                 // H <= 4096: 16 columns per thread
         float v[16];
         float ss = 0.f;
@@ -237,13 +247,21 @@ route_kernel(const AT* __restrict__ x, int64_t ldx, const AT* __restrict__ wr, i
         const AT* xr = FUSED ? xn : x + (int64_t)t * ldx;
         const AT* wrow = wr + (int64_t)e * H;
         float acc = 0.f;
-        for (int c = lane * 8; c < H; c += 256) {          // H % 8 == 0, 16-byte loads
-            const uint4 xv = *reinterpret_cast<const uint4*>(xr + c);
-            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + c));
+        auto dot8 = [&](const uint4& xv, const uint4& wv) {
             const AT* xa = reinterpret_cast<const AT*>(&xv);
             const AT* wa = reinterpret_cast<const AT*>(&wv);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc = fmaf(Elt<AT>::to_f32(xa[j]), Elt<AT>::to_f32(wa[j]), acc);
+        };
+        if constexpr (FUSED) {                             // H % 8 == 0, 16-byte loads
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int c = lane * 8 + 256 * i;
+                if (c < H) dot8(*reinterpret_cast<const uint4*>(xr + c), wpre[i]);
+            }
+        } else {
+            for (int c = lane * 8; c < H; c += 256)
+                dot8(*reinterpret_cast<const uint4*>(xr + c), __ldg(reinterpret_cast<const uint4*>(wrow + c)));
         }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
