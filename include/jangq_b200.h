@@ -179,6 +179,8 @@ int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t l
  * The first call on a device looks the array's device address up; make that call during
  * start-up, before any stream capture.  All calls share the one array and every call rewrites
  * it, so two calls whose kernels may overlap on the GPU (different streams) race: serialise them.
+ * Every call puts one small launch in front of the GEMM (one CTA, a thread per expert and a block-wide
+ * scan) that rebuilds the tile list; jq_moe_gemm reuses the list jq_moe_sort made and has no such launch.
  * Same inputs and outputs as jq_moe_gemm otherwise; it calls no cudaMalloc/cudaFree. */
 int jq_moe_gemm_static(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx,
                        const int32_t* expert_offsets, int num_experts,
@@ -200,6 +202,14 @@ int jq_moe_swiglu(const void* gate, const void* up, int64_t ld_in, const float* 
 int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T,
                    int k, int64_t D, void* out, int64_t ldo, float* out_f32, int dtype,
                    jq_stream_t stream);
+
+/* jq_moe_combine plus the always-on (shared) expert: after the slot sum, shared_y[t, :] (activation dtype,
+ * [T, D] with leading dimension ld_shared; NULL: none) is added in f32 and the result rounded once --
+ * `y + se.w2(...)` of jang_tools/dsv41/model.py:1237-1245, where the fused decode kernels treat the shared
+ * expert as one more slot (dsv41/metal_decode.py:376-421). */
+int jq_moe_combine_shared(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T,
+                          int k, int64_t D, const void* shared_y, int64_t ld_shared, void* out, int64_t ldo,
+                          float* out_f32, int dtype, jq_stream_t stream);
 
 /* Unsorted gather mat-vec for few pairs (the reference's path below its sort threshold of 64,
  * dsv41/model.py:1206, and its fused decode kernels): y[p, :] = deq(W[pair_expert[p]]) .
@@ -237,7 +247,9 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
 
 /* jq_moe_route with the residual + RMS norm in front of it folded in: x_out = rms_norm(x + res) (no weight, f32
  * arithmetic, rounded to the activation type; x, res, x_out: [T, H] contiguous, H <= 4096), then the router on
- * x_out.  One launch instead of jq_residual_rmsnorm + jq_moe_route in the synthetic decode stacks. */
+ * x_out.  One launch instead of jq_residual_rmsnorm + jq_moe_route in the synthetic decode stacks.
+ * x_out must not overlap x or res (the CTAs of a token read both while one of them writes x_out): JQ_EINVAL.
+ * counters and logits_ws belong to one stream at a time: calls on different streams need their own. */
 int jq_moe_route_norm(const void* x, const void* res, int act_dtype, int64_t T, int64_t H, float eps, void* x_out,
                       const void* router_w, int num_experts, int k, int renorm, float scale, int32_t* idx_out,
                       float* w_out, int32_t* counters, float* logits_ws, jq_stream_t stream);
@@ -290,6 +302,8 @@ int jq_embedding(const int32_t* ids, int64_t T, const uint32_t* codes, const voi
  * counters: tcap zero-initialised int32 on the device, private to the rank.  The wait for the peers is bounded
  * (2 s, or JANGQ_EP_WAIT_MS milliseconds); when it runs out the call's result is undefined, jq_device_status()
  * returns JQ_ETIMEOUT and later calls do not wait again until jq_device_status_clear().
+ * CTA t of every rank waits for CTA t of its peers, so all T CTAs (1024 threads each) must be resident at
+ * once: T above what one GPU holds (one or two per SM) is refused with JQ_EUNSUPPORTED.
  * emulate_ranks = world (with rank = 0) runs every rank in one cooperative launch on one GPU: x, y, out and
  * counters then hold the ranks' arrays back to back (testing without a second GPU). */
 size_t jq_ep_buffer_bytes(int64_t tcap, int64_t H);

@@ -4,12 +4,12 @@ Host side: torch tensors + ctypes into libjangq_b200.so (hand-written sm_100a
 kernels).  The op names follow the MLX calls the reference makes.
 """
 from ._lib import JangqError
-from .linear import JANGLinear
+from .linear import JANGEmbedding, JANGLinear, JANGSwitchLinear
 from .ops import ALLOWED_BITS, ALLOWED_GROUP_SIZES, dequantize, embedding, hadamard_rotate, hadamard_signs, quantize, quantize_imatrix, quantized_matmul
 from .moe import ExpertBank, gather_qmm, moe_layer, route_softmax_topk
 from .plan import GemvPlan
-from .bundle import is_jang_model, load_modules as load_jang_modules, open_bundle, repack_v1_to_v2, write_bundle
+from .bundle import is_jang_model, load_jang_model, load_modules as load_jang_modules, open_bundle, repack_v1_to_v2, write_bundle
 
 __all__ = ["JangqError", "ALLOWED_BITS", "ALLOWED_GROUP_SIZES", "quantize", "quantize_imatrix", "dequantize", "embedding", "hadamard_rotate", "hadamard_signs", "quantized_matmul",
-           "JANGLinear", "GemvPlan", "ExpertBank", "gather_qmm", "moe_layer", "route_softmax_topk",
-           "is_jang_model", "open_bundle", "load_jang_modules", "write_bundle", "repack_v1_to_v2"]
+           "JANGLinear", "JANGSwitchLinear", "JANGEmbedding", "GemvPlan", "ExpertBank", "gather_qmm", "moe_layer", "route_softmax_topk",
+           "is_jang_model", "load_jang_model", "open_bundle", "load_jang_modules", "write_bundle", "repack_v1_to_v2"]

@@ -25,16 +25,16 @@ GROUP_SIZES = (128, 64, 32)
 
 
 class Tier(enum.Enum):
-    CRITICAL = "critical"      # full attention, routers, shared experts: breaks first at low bits
-    IMPORTANT = "important"    # embeddings, lm_head, linear-attention projections
+    CRITICAL = "critical"      # full attention, output head, routers, shared experts: breaks first at low bits
+    IMPORTANT = "important"    # embeddings, linear-attention projections
     COMPRESS = "compress"      # MLP / routed-expert projections: the bulk of the bytes
 
 
 # (substring, tier); order matters — the first match wins, exactly as in the reference
 _RULES = (
-    ("shared_expert_gate", Tier.CRITICAL), ("shared_expert", Tier.CRITICAL),
+    ("lm_head", Tier.CRITICAL), ("shared_expert_gate", Tier.CRITICAL), ("shared_expert", Tier.CRITICAL),
     ("q_proj", Tier.CRITICAL), ("k_proj", Tier.CRITICAL), ("v_proj", Tier.CRITICAL), ("o_proj", Tier.CRITICAL),
-    ("qkv_proj", Tier.CRITICAL), ("lm_head", Tier.IMPORTANT),
+    ("qkv_proj", Tier.CRITICAL),
     ("embed_tokens", Tier.IMPORTANT), ("wte", Tier.IMPORTANT), ("word_embeddings", Tier.IMPORTANT),
     ("router.proj", Tier.CRITICAL), ("router", Tier.CRITICAL),
     ("gate_up_proj", Tier.COMPRESS), ("gate_proj", Tier.COMPRESS), ("up_proj", Tier.COMPRESS),
@@ -128,3 +128,94 @@ def infer_bits_and_group_size(weight_cols: int, scales_cols: int, group_size: in
         raise ValueError(f"no (bits, group_size) pair gives bits*group_size = {product}")
     cands.sort(key=lambda c: c[0], reverse=prefer_high_bits)
     return cands[0]
+
+
+def _step(bits: int, up: bool) -> int | None:
+    """Neighbouring allowed width (2 -> 3 -> 4 -> 5 -> 6 -> 8), None at either end."""
+    i = ALLOWED_BITS.index(bits) + (1 if up else -1)
+    return ALLOWED_BITS[i] if 0 <= i < len(ALLOWED_BITS) else None
+
+
+def _routed_expert_part(low: str) -> str | None:
+    """The MLP projection a routed-expert tensor name carries (None for anything else)."""
+    if "shared_expert" in low or "expert" not in low:
+        return None
+    for part in ("gate_up_proj", "gate_proj", "up_proj", "down_proj", "w1", "w2", "w3"):
+        if part in low:
+            return part
+    return None
+
+
+def _asymmetry_floor(name: str, bits: int, num_experts: int, base_bits: int = 0) -> int:
+    """Lowest width a routed-expert projection may get in a model with >= 256 experts: the namesake
+    width for 4-bit-and-up budgets, else gate 4 / down 3 (jang_tools/allocate.py:427-474)."""
+    low = name.lower()
+    if num_experts < _MLP_FLOOR_MIN_EXPERTS or "shared_expert" in low:
+        return bits
+    if base_bits >= 4 and any(p in low for p in ("gate_proj", "gate_up_proj", "w1", "up_proj", "w3", "down_proj", "w2")):
+        return max(bits, base_bits)
+    for part, floor in _MLP_FLOORS.items():
+        if part in low:
+            return max(bits, floor)
+    return bits
+
+
+def _layer_index(name: str) -> int | None:
+    parts = name.split(".")
+    for i, p in enumerate(parts[:-1]):
+        if p == "layers":
+            try:
+                return int(parts[i + 1])
+            except ValueError:
+                return None
+    return None
+
+
+def allocate_bits_budget(tensor_info: Iterable[tuple[str, int]], target_bits: float = 4.0, num_experts: int = 0,
+                         has_shared_mlp: bool = False) -> dict[str, int]:
+    """Budget-neutral per-tensor map (jang_tools/allocate.py:1127-1221, allocate_bits_budget_compact):
+    tensor_info = [(name, number of 64-weight blocks)]; the result averages about `target_bits` per weight.
+
+    Every tensor starts at the largest allowed width not above the target.  CRITICAL tensors climb up to
+    four steps (two when they make up 5 % or more of the model), tensors of the first and last two layers one
+    more step (routed experts of a 2-bit budget excepted), and the overspend is paid back by moving
+    COMPRESS tensors, smallest first, one step down wherever the expert floors allow it."""
+    info = list(tensor_info)
+    total = sum(n for _, n in info)
+    base = max((b for b in ALLOWED_BITS if b <= target_bits), default=2)
+    tier = {name: classify_tensor(name, num_experts, has_shared_mlp) for name, _ in info}
+    bits = {name: base for name, _ in info}
+
+    critical = sum(n for name, n in info if tier[name] is Tier.CRITICAL)
+    steps = 4 if (critical / total if total else 0.0) < 0.05 else 2
+    for name, _ in info:
+        if tier[name] is Tier.CRITICAL:
+            for _ in range(steps):
+                nxt = _step(bits[name], True)
+                if nxt is None:
+                    break
+                bits[name] = nxt
+
+    layer = {name: _layer_index(name) for name, _ in info}
+    known = [l for l in layer.values() if l is not None]
+    n_layers = max(known) + 1 if known else 1
+    for name, _ in info:
+        l = layer[name]
+        if l is None or (base == 2 and _routed_expert_part(name.lower()) is not None):
+            continue
+        if l < 2 or l >= n_layers - 2:
+            nxt = _step(bits[name], True)
+            if nxt is not None:
+                bits[name] = nxt
+
+    over = sum(bits[name] * n for name, n in info) - target_bits * total
+    lower = _step(base, False)
+    if over > 0 and lower is not None:
+        for name, n in sorted(((name, n) for name, n in info if tier[name] is Tier.COMPRESS), key=lambda t: t[1]):
+            if over <= 0:
+                break
+            if _asymmetry_floor(name, lower, num_experts, base) > lower:
+                continue
+            bits[name] = lower
+            over -= (base - lower) * n
+    return bits

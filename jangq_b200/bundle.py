@@ -458,3 +458,111 @@ def repack_v1_to_v2(src, dst, max_shard_bytes: int = 5 * 1024 ** 3) -> None:
     q.update({"bit_widths_used": sorted(widths) or [4], "block_size": block, "tensor_quantization_manifest": manifest})
     jc["quantization"] = q
     write_bundle(dst, tensors, model_config, jc, max_shard_bytes)
+
+
+# ---- load_jang_model -------------------------------------------------------------------------------
+def _tree_set(root, dotted: str, leaf) -> None:
+    """Hang `leaf` into nested torch containers under its dotted path (numeric parts included)."""
+    import torch
+    parts = dotted.split(".")
+    node = root
+    for p in parts[:-1]:
+        if p not in node._modules:
+            node.add_module(p, torch.nn.Module())
+        node = node._modules[p]
+    if isinstance(leaf, torch.nn.Module):
+        node.add_module(parts[-1], leaf)
+    else:
+        node.register_buffer(parts[-1], leaf)
+
+
+def load_jang_model(model_path, device="cuda", sidecar_dtype=None, float_dtype=None):
+    """(model, tokenizer) of a JANG bundle, the call shape of jang_tools/loader.py:1078.
+
+    The reference returns an mlx-lm network; here `model` is a torch module tree that follows the bundle's
+    tensor names: every quantized module is a JANGLinear (2-D weight), a JANGSwitchLinear (stacked experts
+    [E, out, packed]) or a JANGEmbedding (names ending in embed_tokens / wte / word_embeddings), every other
+    tensor a buffer at its dotted path, so `model.get_submodule("model.layers.0.self_attn.q_proj")(x)` runs the
+    quantized product and `model.state_dict()` carries the bundle's names.  `model.config` and
+    `model.jang_config` hold the two JSON files.  The network's own forward (attention, norms, sampling) is
+    outside the quantized path and is not built.  v1 bundles are repacked in memory first, as the reference
+    does on load.  `tokenizer` comes from transformers.AutoTokenizer when the directory has tokenizer files,
+    else None."""
+    import torch
+
+    from .linear import JANGEmbedding, JANGLinear, JANGSwitchLinear
+    p = Path(model_path)
+    cfg_path = find_config_path(p)
+    if cfg_path is None:
+        raise FileNotFoundError(f"No JANG config found in {p}")
+    jang_cfg = _read_json(cfg_path, "JANG config")
+    if not jang_cfg.get("format"):
+        raise ValueError(f"JANG config {cfg_path.name} is missing 'format' field")
+    dt = sidecar_dtype or torch.float16
+    model = torch.nn.Module()
+    model.jang_config = jang_cfg
+    model.config = _read_json(p / "config.json", "model config") if (p / "config.json").exists() else {}
+
+    if is_v2_model(p):
+        b = open_bundle(p)
+        names = b.names()
+        get = b.tensor
+        spec_of = lambda m, ws, ss: b.quant_spec(m, ws, ss)          # noqa: E731
+        closer = b.close
+    else:
+        tensors = read_v1_tensors(p)
+        names = sorted(tensors)
+        get = tensors.__getitem__
+        block = int((jang_cfg.get("quantization") or {}).get("block_size", 64))
+
+        def spec_of(m, ws, ss):
+            bits, gs = infer_bits_group_size(ws[-1], ss[-1], block)
+            return QuantSpec(bits, gs, bits)
+        closer = lambda: None                                          # noqa: E731
+
+    quantized = {n[:-len(".scales")] for n in names if n.endswith(".scales") and n[:-len(".scales")] + ".weight" in names}
+    done = set()
+    for m in sorted(quantized):
+        w, s = get(m + ".weight"), get(m + ".scales")
+        if w.dtype != np.uint32:
+            continue
+        bi = get(m + ".biases")
+        spec = spec_of(m, w.shape, s.shape)
+        if spec.storage_bits == 1:
+            w = expand_1bit_to_2bit(w)
+        wt = torch.from_numpy(np.ascontiguousarray(w).view(np.int32)).to(device)
+        st = torch.from_numpy(np.ascontiguousarray(s)).to(device).to(dt)
+        bt = torch.from_numpy(np.ascontiguousarray(bi)).to(device).to(dt)
+        k = s.shape[-1] * spec.group_size
+        if w.ndim == 3:
+            leaf = JANGSwitchLinear(w.shape[0], k, w.shape[1], spec.bits, spec.group_size, device=device, dtype=dt)
+        elif m.rsplit(".", 1)[-1] in ("embed_tokens", "wte", "word_embeddings"):
+            leaf = JANGEmbedding(w.shape[0], k, spec.bits, spec.group_size, device=device, dtype=dt)
+        elif w.ndim == 2:
+            has_bias = (m + ".bias") in names
+            leaf = JANGLinear(k, w.shape[0], spec.bits, spec.group_size, bias=has_bias, device=device, dtype=dt)
+            if has_bias:
+                leaf.bias = torch.from_numpy(np.ascontiguousarray(get(m + ".bias"))).to(device).to(dt)
+                done.add(m + ".bias")
+        else:
+            raise BundleError(f"{m}.weight has {w.ndim} dimensions")
+        leaf.weight, leaf.scales, leaf.biases = wt, st, bt
+        _tree_set(model, m, leaf)
+        done.update((m + ".weight", m + ".scales", m + ".biases"))
+    for n in names:
+        if n in done:
+            continue
+        t = torch.from_numpy(np.ascontiguousarray(get(n)))
+        if float_dtype is not None and t.is_floating_point():
+            t = t.to(float_dtype)
+        _tree_set(model, n, t.to(device))
+    closer()
+
+    tokenizer = None
+    if any((p / f).exists() for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
+        try:
+            from transformers import AutoTokenizer
+            tokenizer = AutoTokenizer.from_pretrained(str(p))
+        except Exception:            # a bundle without usable tokenizer files still loads its weights
+            tokenizer = None
+    return model, tokenizer

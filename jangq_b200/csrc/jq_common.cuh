@@ -43,8 +43,13 @@ int check_quant_shape(int64_t rows, int64_t K, int bits, int group_size);
 // cached per-device attributes (SM count); mutex-guarded, filled on first use
 int sm_count();
 
-// device address of the library's status word on the current device (nullptr on failure);
-// kernels with bounded waits set it to 1 when a wait runs out, jq_device_status() reads it
+// device address of the library's status word on the current device (nullptr on failure).
+// Kernels with bounded waits OR a bit into it when a wait runs out; jq_device_status() reads it.
+//   JQ_STATUS_LOCAL_WAIT  a wait inside one kernel's own pipeline (mbarrier, grid barrier) ran out
+//   JQ_STATUS_PEER_WAIT   a rank of the expert-parallel exchange did not arrive; only this bit makes
+//                         later exchange launches skip their cross-rank wait
+constexpr int JQ_STATUS_LOCAL_WAIT = 1;
+constexpr int JQ_STATUS_PEER_WAIT = 2;
 int* status_word();
 
 // ---- device-side scalar conversion -------------------------------------------

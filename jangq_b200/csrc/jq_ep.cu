@@ -95,12 +95,13 @@ ep_combine_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, in
         ep_store_release_sys(theirs, s);
         const uint32_t* own = reinterpret_cast<const uint32_t*>(peers.buf[rank] + flags_off) + (size_t)t * EP_MAX_WORLD + p;
         const unsigned long long t0 = ep_now_ns();
-        bool ok = *reinterpret_cast<volatile int*>(status) == 0;   // after one timeout nobody waits again
+        // after a peer failed to arrive once, no launch waits for peers again until the word is cleared
+        bool ok = (*reinterpret_cast<volatile int*>(status) & JQ_STATUS_PEER_WAIT) == 0;
         while (ok && (int32_t)(ep_load_acquire_sys(own) - s) < 0) {
             __nanosleep(100);
             if (ep_now_ns() - t0 > wait_ns) ok = false;
         }
-        if (!ok) atomicExch(status, 1);
+        if (!ok) atomicOr(status, JQ_STATUS_PEER_WAIT);
     }
     __syncthreads();
     // 4. sum in rank order + residual + RMS norm
@@ -183,6 +184,13 @@ int jq_ep_combine_residual_rmsnorm(const void* x, const void* y, int k, int64_t 
             JQ_CUDA_OK(cudaLaunchCooperativeKernel((const void*)ep_combine_rmsnorm_kernel<AT>, grid, dim3(1024), args, 0,
                                                    (cudaStream_t)stream));
         } else {
+            // CTA t waits for CTA t of every peer: all T CTAs must be resident at once on every rank, or the
+            // order in which the ranks' GPUs start their blocks decides whether the waits can finish
+            int per_sm = 0;
+            JQ_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ep_combine_rmsnorm_kernel<AT>, 1024, 0));
+            JQ_REQUIRE(T <= (int64_t)per_sm * sm_count(), JQ_EUNSUPPORTED,
+                       "T=%lld exceeds the %lld CTAs of this kernel one GPU holds at a time", (long long)T,
+                       (long long)per_sm * sm_count());
             JQ_CUDA_OK(cudaLaunchKernel((const void*)ep_combine_rmsnorm_kernel<AT>, grid, dim3(1024), args, 0,
                                         (cudaStream_t)stream));
         }

@@ -160,11 +160,12 @@ __global__ void swiglu_kernel(const AT* __restrict__ g, const AT* __restrict__ u
 }
 
 // out[t, :] = sum_j (w ? w[t*k+j] : 1) * y[inv ? inv[t*k+j] : t*k+j, :]  in f32, slots in order
-// (dsv41/model.py:1230-1234); pairs with inv < 0 (experts of another rank) are skipped.
+// (dsv41/model.py:1230-1234); pairs with inv < 0 (experts of another rank) are skipped.  `shared`
+// (optional, [T, D]) is the always-on expert's output, added to the routed sum in f32 (model.py:1237-1245).
 template <typename AT>
 __global__ void combine_kernel(const AT* __restrict__ y, int64_t ldy, const int32_t* __restrict__ inv,
                                const float* __restrict__ w, int T, int k, int D, AT* __restrict__ out, int64_t ldo,
-                               float* __restrict__ out_f32) {
+                               float* __restrict__ out_f32, const AT* __restrict__ shared, int64_t ld_shared) {
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
         for (int c = threadIdx.x; c < D; c += blockDim.x) {
             float acc = 0.f;
@@ -172,6 +173,7 @@ __global__ void combine_kernel(const AT* __restrict__ y, int64_t ldy, const int3
                 const int p = inv ? inv[t * k + j] : t * k + j;
                 if (p >= 0) acc = fmaf(w ? w[t * k + j] : 1.0f, Elt<AT>::to_f32(y[(int64_t)p * ldy + c]), acc);
             }
+            if (shared) acc += Elt<AT>::to_f32(shared[(int64_t)t * ld_shared + c]);
             if (out_f32) out_f32[(int64_t)t * D + c] = acc;
             else out[(int64_t)t * ldo + c] = Elt<AT>::from_f32(acc);
         }
@@ -406,6 +408,15 @@ int jq_moe_route_norm(const void* x, const void* res, int act_dtype, int64_t T, 
     JQ_REQUIRE(x && res && x_out && router_w && idx_out && w_out && counters && logits_ws, JQ_EINVAL, "null pointer");
     JQ_REQUIRE(aligned(router_w, 16), JQ_EINVAL, "the router weights must be 16-byte aligned");
     JQ_REQUIRE(T <= 65535, JQ_EUNSUPPORTED, "jq_moe_route_norm is the few-token path");
+    {   // every CTA of a token re-reads x and res while the first one already writes x_out: no in-place update
+        const char* o0 = (const char*)x_out;
+        const char* o1 = o0 + (size_t)T * H * 2;
+        const char* x0 = (const char*)x;
+        const char* r0 = (const char*)res;
+        const size_t nb = (size_t)T * H * 2;
+        JQ_REQUIRE((o1 <= x0 || x0 + nb <= o0) && (o1 <= r0 || r0 + nb <= o0), JQ_EINVAL,
+                   "jq_moe_route_norm: x_out must not overlap x or res");
+    }
     const dim3 grid((unsigned)T, (unsigned)((num_experts + 7) / 8));
     JQ_DISPATCH_DTYPE16(act_dtype, AT,
         JQ_CUDA_OK(launch_pdl(route_kernel<AT, true>, grid, dim3(256), 0, (cudaStream_t)stream, (const AT*)x, H,
@@ -487,17 +498,25 @@ int jq_moe_swiglu(const void* gate, const void* up, int64_t ld_in, const float* 
     return JQ_OK;
 }
 
-int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T, int k, int64_t D,
-                   void* out, int64_t ldo, float* out_f32, int dtype, jq_stream_t stream) {
+int jq_moe_combine_shared(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T, int k,
+                          int64_t D, const void* shared_y, int64_t ld_shared, void* out, int64_t ldo, float* out_f32,
+                          int dtype, jq_stream_t stream) {
     using namespace jq;
     JQ_REQUIRE(T >= 0 && k > 0 && D >= 0, JQ_EINVAL, "bad argument");
     if (T == 0 || D == 0) return JQ_OK;
     JQ_REQUIRE(y && (out || out_f32), JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(shared_y == nullptr || ld_shared >= D, JQ_EINVAL, "leading dimension of the shared expert's rows too small");
     const int blocks = (int)(T < 8 * 148 ? T : 8 * 148);
     JQ_DISPATCH_DTYPE16(dtype, A,
         (combine_kernel<A><<<blocks, 256, 0, (cudaStream_t)stream>>>((const A*)y, ldy, inv, weights, (int)T, k, (int)D,
-                                                                      (A*)out, ldo, out_f32)))
+                                                                      (A*)out, ldo, out_f32, (const A*)shared_y,
+                                                                      ld_shared)))
     return check_launch("moe_combine");
+}
+
+int jq_moe_combine(const void* y, int64_t ldy, const int32_t* inv, const float* weights, int64_t T, int k, int64_t D,
+                   void* out, int64_t ldo, float* out_f32, int dtype, jq_stream_t stream) {
+    return jq_moe_combine_shared(y, ldy, inv, weights, T, k, D, nullptr, 0, out, ldo, out_f32, dtype, stream);
 }
 
 }  // extern "C"

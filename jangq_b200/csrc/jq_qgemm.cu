@@ -21,6 +21,7 @@
 // MLX's qmm feeds its matrix units), products are accumulated in f32.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "jq_mma.cuh"
@@ -435,7 +436,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
             }
         }
     }
-    if (!ok) atomicExch(a.status, 1);
+    if (!ok) atomicOr(a.status, JQ_STATUS_LOCAL_WAIT);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -538,13 +539,11 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     if (m_tiles == 0) return JQ_OK;
     JQ_REQUIRE(m_tiles < 65536, JQ_EUNSUPPORTED, "too many row tiles for one launch (%lld)", (long long)m_tiles);
     // 256-wide tiles reuse every activation tile twice as often; narrow outputs keep 128
-    const bool wide = N >= 256 && !getenv("JANGQ_GEMM_BN128");
-    const bool dpr2 = getenv("JANGQ_GEMM_DPR2") != nullptr;      // tuning knob: two dequantizer threads per row
+    const bool wide = N >= 256;
 #define JQ_GEMM_CASE(B)                                                                                  \
     if (bits == B) {                                                                                     \
         if (x_dtype == JQ_BF16)                                                                          \
-            return wide ? (dpr2 ? launch_gemm<__nv_bfloat16, B, 256, 2>(xmap, a, m_tiles, st)            \
-                                : launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st))           \
+            return wide ? launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st)                    \
                         : launch_gemm<__nv_bfloat16, B, 128, 1>(xmap, a, m_tiles, st);                   \
         return launch_gemm<__half, B, 128, 1>(xmap, a, m_tiles, st);                                     \
     }
@@ -564,40 +563,60 @@ constexpr int STATIC_MAX_TILES = (int)(STATIC_MAX_ROWS / GEMM_BM) + STATIC_MAX_E
 constexpr int STATIC_HDR = 64;     // word 0 = number of tiles; the lists start 256 bytes in
 static __device__ __align__(256) int32_t g_static_tiles[STATIC_HDR + 2 * STATIC_MAX_TILES];
 
-// One thread rewrites the whole list on every call (count first reset, then the tiles), so nothing
-// of an earlier call survives into this one.
-__global__ void build_tiles_kernel(const int32_t* __restrict__ offsets, int E, int tile_m, int32_t* __restrict__ out) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// One CTA of STATIC_MAX_EXPERTS threads rewrites the whole list on every call, so nothing of an earlier
+// call survives into this one: thread e counts the tiles of expert e, a block-wide exclusive scan gives
+// the position of its first tile, and it writes its own tiles (experts ascending, rows ascending: the
+// order jq_moe_sort emits).  Tiles past STATIC_MAX_TILES are dropped (offsets beyond the stated rows).
+__global__ void __launch_bounds__(STATIC_MAX_EXPERTS)
+build_tiles_kernel(const int32_t* __restrict__ offsets, int E, int tile_m, int32_t* __restrict__ out) {
+    __shared__ int warp_sum[32];
     int32_t* tile_expert = out + STATIC_HDR;
     int32_t* tile_row0 = out + STATIC_HDR + STATIC_MAX_TILES;
-    int tiles = 0;
-    out[0] = 0;
-    for (int e = 0; e < E; ++e) {
-        const int lo = offsets[e], hi = offsets[e + 1];
-        for (int r = lo; r < hi && tiles < STATIC_MAX_TILES; r += tile_m) {
-            tile_expert[tiles] = e;
-            tile_row0[tiles] = r;
-            ++tiles;
-        }
+    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+    int lo = 0, hi = 0;
+    if (e < E) { lo = offsets[e]; hi = offsets[e + 1]; }
+    const int mine = hi > lo ? (hi - lo + tile_m - 1) / tile_m : 0;
+    int incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += v;
     }
-    out[0] = tiles;
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_sum[lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xFFFFFFFFu, w, d);
+            if (lane >= d) w += v;
+        }
+        warp_sum[lane] = w;            // inclusive sums of the warps
+    }
+    __syncthreads();
+    int pos = incl - mine + (warp > 0 ? warp_sum[warp - 1] : 0);
+    for (int r = lo; r < hi && pos < STATIC_MAX_TILES; r += tile_m, ++pos) {
+        tile_expert[pos] = e;
+        tile_row0[pos] = r;
+    }
+    if (e == 0) out[0] = min(warp_sum[31], STATIC_MAX_TILES);
 }
 
 // Device address of the array on the current device.  In host code the array's name is only a
 // host-side handle, never a device address, so it is resolved with cudaGetSymbolAddress once per
 // device (with that device current) and the pointer is what the kernels receive.
 static int static_tiles_ptr(int32_t** out) {
-    static int32_t* cached[64] = {};
+    static std::atomic<int32_t*> cached[64];      // zero-initialised; host threads may race on the first call
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     JQ_REQUIRE(dev >= 0 && dev < 64, JQ_EUNSUPPORTED, "device ordinal %d out of range", dev);
-    if (!cached[dev]) {
-        int32_t* p = nullptr;
+    int32_t* p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
         JQ_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_static_tiles));
         JQ_REQUIRE(p != nullptr, JQ_ECUDA, "cudaGetSymbolAddress returned a null address");
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = p;
     return JQ_OK;
 }
 
@@ -621,7 +640,7 @@ int jq_moe_gemm_static(const void* x_sorted, int act_dtype, int64_t max_rows, in
     int32_t* tiles = nullptr;
     int rc = static_tiles_ptr(&tiles);
     if (rc != JQ_OK) return rc;
-    build_tiles_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(expert_offsets, num_experts, GEMM_BM, tiles);
+    build_tiles_kernel<<<1, STATIC_MAX_EXPERTS, 0, (cudaStream_t)stream>>>(expert_offsets, num_experts, GEMM_BM, tiles);
     rc = check_launch("build_tiles");
     if (rc != JQ_OK) return rc;
     GroupedArgs g;

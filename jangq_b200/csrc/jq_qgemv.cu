@@ -388,13 +388,12 @@ static bool force_simple() {
 }
 
 // JANGQ_GEMV_KERNEL selects the fast-path kernel: unset = per-width default, "tc" = tensor-memory
-// kernel wherever the shape fits it, "imma" = integer warp-MMA kernel wherever it fits, "mma" = the
-// warp-MMA kernel of this file.  A tuning and comparison knob.
+// kernel wherever the shape fits it, "pint" = persistent integer warp-MMA kernel wherever it fits,
+// "mma" = the warp-MMA kernel of this file.  The parity tests force every kernel with it.
 static int gemv_kernel_choice() {
     const char* e = getenv("JANGQ_GEMV_KERNEL");
     if (!e) return 0;
     if (e[0] == 'm') return 1;
-    if (e[0] == 'i') return 2;      // integer warp-MMA kernel wherever the shape fits it
     if (e[0] == 't') return 3;
     if (e[0] == 'p') return 4;      // persistent integer warp-MMA kernel wherever the shape fits it
     return 0;
@@ -453,22 +452,11 @@ static int launch_mma(const GemvArgs& a, const GemvBatch& bt, int pairs, cudaStr
     tiles16 *= pairs;
     constexpr int KT = GemvGeom<BITS, GS, 1>::KT;
     const int nst = (int)((a.K + KT - 1) / KT);
-    int mt = (tiles16 >= (int64_t)4 * sms && tiles16 < (int64_t)12 * sms) ? 2 : 1;
+    const int mt = (tiles16 >= (int64_t)4 * sms && tiles16 < (int64_t)12 * sms) ? 2 : 1;
     int nw = (mt == 1 && tiles16 <= (int64_t)2 * sms && nst >= 16) ? 8 : 4;
-    if (const char* e = getenv("JANGQ_GEMV_MT")) {            // tuning knobs for experiments
-        if (e[0] == '1') mt = 1;
-        if (e[0] == '2') mt = 2;
-    }
-    if (const char* e = getenv("JANGQ_GEMV_NW")) {
-        if (e[0] == '4') nw = 4;
-        if (e[0] == '8') nw = 8;
-    }
     if (mt == 2) nw = 4;
     const int sb = mt == 2 ? GemvGeom<BITS, GS, 2>::stage_bytes(a.M) : GemvGeom<BITS, GS, 1>::stage_bytes(a.M);
-    int nbuf = (nw == 8 && nst >= 20 && nw * 3 * sb <= 200 * 1024) ? 3 : 2;
-    if (const char* e = getenv("JANGQ_GEMV_NBUF")) {
-        if (e[0] == '2' || e[0] == '3') nbuf = e[0] - '0';
-    }
+    const int nbuf = (nw == 8 && nst >= 20 && nw * 3 * sb <= 200 * 1024) ? 3 : 2;
     if (mt == 2) return launch_mma_cfg<AT, BITS, GS, 2, 4>(a, bt, pairs, nbuf, st, launched);
     if (nw == 8) return launch_mma_cfg<AT, BITS, GS, 1, 8>(a, bt, pairs, nbuf, st, launched);
     return launch_mma_cfg<AT, BITS, GS, 1, 4>(a, bt, pairs, nbuf, st, launched);
@@ -552,10 +540,6 @@ int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, con
         const bool narrow = (bits == 2 || bits == 4 || bits == 8) && a.M <= 2;
         if (fast && (kern == 4 || (kern == 0 && narrow))) {
             rc = launch_pint_kernel(a, bt, x_dtype, bits, gs, st, &launched);
-            if (rc != JQ_OK) return rc;
-        }
-        if (fast && !launched && kern == 2) {
-            rc = launch_imma_kernel(a, bt, x_dtype, bits, gs, st, &launched);
             if (rc != JQ_OK) return rc;
         }
         if (fast && !launched && (kern == 3 || (kern == 0 && bits != 2))) {
@@ -718,7 +702,10 @@ int jq_device_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, jq::g_timeout_flag, sizeof(int)) != cudaSuccess)
         return jq::fail(JQ_ECUDA, "could not read the device status word");
-    if (v != 0) return jq::fail(JQ_ETIMEOUT, "a bounded device-side wait ran out");
+    if (v != 0)
+        return jq::fail(JQ_ETIMEOUT, "a bounded device-side wait ran out:%s%s",
+                        (v & jq::JQ_STATUS_LOCAL_WAIT) ? " a kernel's own pipeline or grid barrier" : "",
+                        (v & jq::JQ_STATUS_PEER_WAIT) ? " a rank of the expert-parallel exchange did not arrive" : "");
     return JQ_OK;
 }
 

@@ -6,7 +6,7 @@
 // A 64-code block of 16 rows is 256 bytes of 2-bit codes; to stream them at the HBM rate an SM may spend
 // about 34 warp instructions on it, so this kernel is written against an instruction budget.
 //
-// Arithmetic: the one of the integer warp-MMA kernel (jq_qgemv_imma.cu): per quantization group the
+// Arithmetic: per quantization group the
 // activations are  x[k] ~ e * xi[k]  (e a power of two) with xi in three signed 8-bit limbs, the codes
 // are the unsigned operand of mma.sync.m16n8k32 (u8 x s8 -> s32), the limb sums are exact integers and
 //     acc += e * s * (D0 + 256 D1 + 65536 D2) + b * sum_k x[k].
@@ -23,8 +23,6 @@
 // codes) plus the raw 2-byte scales and biases, copied by cp.async into a private ring of `nbuf` stages
 // per warp: no register staging, no CTA barrier.  A warp adds the item's result to its own row sums in
 // shared memory; one CTA barrier at the end, then the warps' sums are added and stored.
-#include <cstdlib>
-
 #include "jq_mma.cuh"
 #include "jq_qgemv.cuh"
 
@@ -447,11 +445,6 @@ static int launch_cfg(const GemvArgs& a, const GemvBatch& bt, int nbuf, int tpc,
     return launch_cfg_m<AT, BITS, GS, NW, false>(a, bt, nbuf, tpc, grid, st, launched);
 }
 
-static int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return (e && e[0] >= '0' && e[0] <= '9') ? atoi(e) : dflt;
-}
-
 // One CTA per SM; every CTA gets the same number of 16-row tiles (the last one the remainder).  The warp
 // count and the ring depth are the largest that fit the shared memory next to the limbs.
 template <typename AT, int BITS, int GS>
@@ -468,10 +461,8 @@ static int launch_shape(const GemvArgs& a, GemvBatch bt, cudaStream_t st, bool* 
     if (tpc > 64) return JQ_OK;
     // 20 warps by default; 24 when that saves a round of items (short runs: the slowest warp sets the time)
     const int64_t items = (int64_t)tpc * ((a.K + Geo::KT - 1) / Geo::KT);
-    int nw = env_int("JANGQ_PINT_NW", (items + 23) / 24 < (items + 19) / 20 ? 24 : 20);
-    int nbuf = env_int("JANGQ_PINT_NBUF", 3);
-    nw = nw >= 24 ? 24 : nw >= 20 ? 20 : 16;
-    nbuf = nbuf < 2 ? 2 : nbuf > 4 ? 4 : nbuf;
+    int nw = (items + 23) / 24 < (items + 19) / 20 ? 24 : 20;
+    int nbuf = 3;
     while ((size_t)head_bytes((int)a.K, a.G, a.M, tpc, nw) + (size_t)nw * nbuf * Geo::STAGE > (size_t)MAX_SMEM) {
         if (nbuf > 2) --nbuf;
         else if (nw > 16) nw -= 4;

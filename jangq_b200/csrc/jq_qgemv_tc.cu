@@ -37,8 +37,6 @@
 // the limbs of x are written in the same order.
 // Every mbarrier wait is bounded: a wait that runs out sets the library's status word and the
 // CTA runs on to the common exit without waiting again.
-#include <cstdlib>
-
 #include "jq_mma.cuh"
 #include "jq_qgemv.cuh"
 #include "jq_tc.cuh"
@@ -46,16 +44,6 @@
 namespace jq {
 
 namespace tcv {
-
-// Optional cycle accounting of the waits of every role (compiled in with -DJQ_TC_PROFILE only).
-#ifdef JQ_TC_PROFILE
-__device__ unsigned long long g_tc_prof[32];
-#define JQ_PROF_DECL(v) long long v = clock64()
-#define JQ_PROF_ADD(cond, idx, t0) do { if (cond) atomicAdd(&g_tc_prof[idx], (unsigned long long)(clock64() - (t0))); } while (0)
-#else
-#define JQ_PROF_DECL(v) do { } while (0)
-#define JQ_PROF_ADD(cond, idx, t0) do { } while (0)
-#endif
 
 constexpr int ROWS = 128;        // weight rows per CTA
 constexpr int TK = 128;          // k per tile = bytes of one A row per tile
@@ -173,7 +161,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
     uint16_t* y16 = reinterpret_cast<uint16_t*>(bt.y[mi]);
 
     // ---- set-up: barriers, tensor memory, first weight copies (static data) -----------------------------
-    JQ_PROF_DECL(t_start);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     auto produce = [&](int st) {       // one lane: stage st of the slice
         const int s = st % NS;
@@ -199,7 +186,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
     const uint32_t tmem_a = tmem_base, tmem_d = tmem_base + RG::A_COLS;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;   // tensor-memory lane quarter = warp id mod 4
     bool ok = true;
-    JQ_PROF_ADD(tid == 0, 0, t_start);                 // 0: set-up
 
     float acc[MMAX];
 #pragma unroll
@@ -211,16 +197,13 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
         if constexpr (BITS != 8) {
             // ---------------- unpackers: packed codes -> one byte per code -> tensor memory ----------------
             // They depend on the weights only, so they start before the activations are ready.
-            JQ_PROF_DECL(t_roles);
             static_assert(BITS == 2 || BITS == 4 || BITS == 8, "widths of this kernel");
             constexpr int NCH = TILE_B / 16;                          // 16-byte chunks of one row and tile
             const int half = (warp - W_UNP) >> 2;                     // tiles of a stage alternate between two warp sets
             const uint32_t row_off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
             for (int st = 0; st < nstages && ok; ++st) {
                 const int s = st % NS;
-                JQ_PROF_DECL(t0);
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(raw_full + s, (uint32_t)(st / NS) & 1u, POLLS));
-                JQ_PROF_ADD(warp == W_UNP && lane == 0, 9, t0);       // 9: unpacker waits for packed codes
                 if (!ok) break;
                 const uint8_t* rowp = sRaw + (size_t)s * STAGE_BYTES + row_off;
 #pragma unroll
@@ -248,13 +231,11 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                             }
                         }
                     }
-                    JQ_PROF_DECL(t1);
                     if (pr >= RP) {    // the MMAs of pair pr - RP have read this A slot
                         ok = __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(d_full + pi, (uint32_t)((pr / RP) - 1) & 1u, POLLS));
                         if (!ok) break;
                         tc_fence_after();
                     }
-                    JQ_PROF_ADD(warp == W_UNP && lane == 0, 10, t1);  // 10: unpacker waits for a free A tile
                     tmem_st32(tmem_a + lane_base + (uint32_t)((2 * pi + (t & 1)) * 32), v);
                     tmem_st_wait();
                     tc_fence_before();
@@ -264,7 +245,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                 __syncwarp();                                         // every lane has read its row of the stage
                 if (lane == 0) mbar_arrive(raw_empty + s);
             }
-            JQ_PROF_ADD(warp == W_UNP && lane == 0, 12, t_roles);     // 12: unpacker loop, total
         }
     } else {
         // ---- warps 0..10: activations of the slice -> limbs (B operand) + per-group (e, sum xi) ---------------
@@ -298,7 +278,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
             }
         }
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        JQ_PROF_DECL(t_prep);
         {
             // eight consecutive activations per lane; GS/8 adjacent lanes form a quantization group.
             // The loads of all PF rounds are issued together, so their latency is paid once.
@@ -316,10 +295,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                         rawv[i] = *reinterpret_cast<const uint4*>(xs16 + (int64_t)m * a.ldx + k_begin + (it - m * per_row) * 8);
                     }
                 }
-#ifdef JQ_TC_PROFILE
-                { uint32_t sink; asm volatile("mov.u32 %0, %1;" : "=r"(sink) : "r"(rawv[0].x)); (void)sink; }
-                JQ_PROF_ADD(tid == 0 && base0 == 0, 16, t_prep);   // 16: first activation load has arrived
-#endif
 #pragma unroll
                 for (int i = 0; i < PF; ++i) {
                     const int it = base0 + i * PREP + lane;
@@ -362,16 +337,12 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes of B -> tensor-core reads
         asm volatile("bar.sync 1, %0;" ::"n"(PREP) : "memory");
-        JQ_PROF_ADD(tid == 0, 1, t_prep);                  // 1: activation limbs
-        JQ_PROF_DECL(t_roles);
 
         if (warp == 0) {
             // ---------------- TMA producer (the first NS stages are already in flight) ----------------
             if (lane == 0) {
                 for (int st = NS; st < nstages; ++st) {
-                    JQ_PROF_DECL(t0);
                     ok = mbar_wait_relaxed(raw_empty + st % NS, (uint32_t)((st / NS) - 1) & 1u, POLLS);
-                    JQ_PROF_ADD(true, 2, t0);                  // 2: producer waits for a free stage
                     if (!ok) break;
                     produce(st);
                 }
@@ -384,13 +355,9 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                 const int npairs_ = ntiles / 2;
                 for (int pr = warp - W_MMA; pr < npairs_ && ok; pr += 2) {
                     const int pi = pr % RP, s = pr % NS;
-                    JQ_PROF_DECL(t0);
                     if constexpr (BITS == 8) ok = mbar_wait(raw_full + s, (uint32_t)(pr / NS) & 1u, POLLS);
                     else ok = mbar_wait(a_full + pi, (uint32_t)(pr / RP) & 1u, POLLS);
-                    JQ_PROF_ADD(warp == W_MMA, 3, t0);         // 3: MMA waits for its A operand
-                    JQ_PROF_DECL(t1);
                     if (ok && pr >= RP) ok = mbar_wait(d_empty + pi, (uint32_t)((pr / RP) - 1) & 1u, POLLS);
-                    JQ_PROF_ADD(warp == W_MMA, 4, t1);         // 4: MMA waits for a free accumulator
                     if (!ok) break;
                     tc_fence_after();
                     // descriptors: one 32-bit add per operand and MMA (the issuing thread is the scarce resource)
@@ -414,25 +381,20 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                     umma_commit(d_full + pi);      // sums ready; for narrow codes also: the A slots are free again
                     if constexpr (BITS == 8) { if (pr + NS < npairs_) umma_commit(raw_empty + s); }   // the stage is free again
                 }
-                JQ_PROF_ADD(warp == W_MMA, 5, t_roles);        // 5: MMA loop, total
             }
         } else {
             // ---------------- epilogue: one weight row per thread, two tiles per step ----------------
             for (int i = 0; i < my_pairs && ok; ++i) {
-                JQ_PROF_DECL(t0);
                 issue_sc(i + SQ - 1);
                 cp_async_wait<SQ - 1>();                              // sidecars of this pair have landed
-                JQ_PROF_ADD(warp == W_EPI && lane == 0, 6, t0);       // 6: epilogue waits for sidecars
                 const uint4 cell = *reinterpret_cast<const uint4*>(my_sc + ((size_t)(i % SQ) * ROWS + row) * 16);
                 const uint32_t sw[2] = {cell.x, cell.y}, bw[2] = {cell.z, cell.w};
                 const int pair = 2 * i + eset;
                 const int t0i = 2 * pair;                             // first tile of the pair
                 const int g0 = t0i * GPT;                             // its first group (of the slice)
                 const int gq0 = GS == 64 ? 0 : 2 * (pair & 1);        // ... and that group's place in the sidecar quad
-                JQ_PROF_DECL(t1);
                 const int pi = pair % RP;
                 ok = mbar_wait_warp(d_full + pi, (uint32_t)(pair / RP) & 1u, POLLS, true);   // one lane polls
-                JQ_PROF_ADD(warp == W_EPI && lane == 0, 7, t1);       // 7: epilogue waits for sums
                 if (!ok) break;
                 tc_fence_after();
                 if (NCOL == 16 && M == 1) {
@@ -484,7 +446,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
                 }
             }
             cp_async_wait<0>();
-            JQ_PROF_ADD(warp == W_EPI && lane == 0, 8, t_roles);      // 8: epilogue loop, total
             // the two sets add their partial sums: set 1 -> shared memory -> set 0
             if (eset == 1) {
 #pragma unroll
@@ -497,7 +458,7 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
             }
         }
     }
-    if (!ok) atomicExch(a.status, 1);
+    if (!ok) atomicOr(a.status, JQ_STATUS_LOCAL_WAIT);
 
     // ---- results: direct store, or partial sums to rank 0 through distributed shared memory -----------------
     const bool owner = warp >= W_EPI && warp < W_EPI + 4;             // set 0 holds the CTA's sums
@@ -529,15 +490,6 @@ qgemv_tc_kernel(const __grid_constant__ TcMaps maps, const GemvArgs a, const Gem
         tc_fence_after();
         tmem_dealloc(tmem_base, RG::TMEM_COLS);
     }
-    JQ_PROF_ADD(tid == 0, 14, t_start);                           // 14: whole CTA
-#ifdef JQ_TC_PROFILE
-    if (tid == 0) atomicAdd(&g_tc_prof[15], 1ull);                 // 15: CTA count
-#endif
-}
-
-static int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return (e && e[0] >= '0' && e[0] <= '9') ? atoi(e) : dflt;
 }
 
 template <typename AT, int BITS, int GS, int NCOL>
@@ -625,25 +577,14 @@ static int launch_shape(const TcMaps& maps, const GemvArgs& a, const GemvBatch& 
     // the limbs of a long slice can crowd out the ring: split K further while fewer than 4 stages fit
     while (S < 8 && S < nquads && fit_ns(S) * RG::STAGE_BYTES < 4 * BOX_BYTES &&
            make_map(NCOL, ((nquads + S - 1) / S) * TPQ, 0, 4, BOX_BYTES).total + 1024 > 227 * 1024) ++S;
-    S = env_int("JANGQ_TC_S", S);
     if (S < 1 || S > 8 || S > nquads) return JQ_OK;
-    int ns = env_int("JANGQ_TC_NS", fit_ns(S));
+    const int ns = fit_ns(S);
     if (ns < 2 || ns > RG::MAX_STAGES || (BITS == 8 && (ns & 1))) return JQ_OK;
     return launch_cfg<AT, BITS, GS, NCOL>(maps, a, bt, S, ns, st, launched);
 }
 
 }  // namespace tcv
 
-#ifdef JQ_TC_PROFILE
-extern "C" int jq_tc_profile_read(unsigned long long* out, int reset) {
-    if (cudaMemcpyFromSymbol(out, tcv::g_tc_prof, sizeof(tcv::g_tc_prof)) != cudaSuccess) return 1;
-    if (reset) {
-        unsigned long long z[32] = {};
-        if (cudaMemcpyToSymbol(tcv::g_tc_prof, z, sizeof(z)) != cudaSuccess) return 1;
-    }
-    return 0;
-}
-#endif
 
 // Dense mat-vecs (one launch for all matrices of `bt`) on the tensor-memory kernel; *launched stays
 // false when the shape does not fit it.

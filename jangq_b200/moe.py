@@ -302,9 +302,9 @@ _ROUTE_WS = {}
 
 
 def _route_workspace(dev, T: int, E: int):
-    """(counters, logits scratch) of the router kernel, kept per device: calls on one stream follow each
-    other, and the kernel leaves the counters at zero."""
-    key = (dev.type, dev.index)
+    """(counters, logits scratch) of the router kernel, kept per device and stream: calls on one stream
+    follow each other, and the kernel leaves the counters at zero."""
+    key = (dev.type, dev.index, torch.cuda.current_stream(dev).cuda_stream)
     cnt, ws = _ROUTE_WS.get(key, (None, None))
     if cnt is None or cnt.numel() < T:
         cnt = torch.zeros(max(T, 1024), dtype=torch.int32, device=dev)
@@ -332,6 +332,31 @@ def residual_rmsnorm(x: torch.Tensor, y: torch.Tensor, eps: float | None = None,
         _lib.check(lib.jq_residual_rmsnorm(x.data_ptr(), None if yf else y.data_ptr(), y.data_ptr() if yf else None, k, T, H,
                                            float(eps), out.data_ptr(), _lib.dtype_id(x.dtype), _lib.stream_ptr(dev)))
     return out
+
+
+def _shared_expert(x: torch.Tensor, shared, swiglu_limit: float) -> torch.Tensor:
+    """down(silu(gate x) * up x) of the always-on expert (`_shared`, dsv41/model.py:1237-1245): gate and up
+    as one fused mat-vec launch for few rows, the SwiGLU kernel without routing weights, then down.  All three
+    products run in libjangq_b200.so."""
+    lib = _lib.load()
+    sg, su, sd = shared
+    T = x.shape[0]
+    dev = x.device
+    same = (sg.in_features == su.in_features and sg.out_features == su.out_features and sg.bits == su.bits and
+            sg.group_size == su.group_size)
+    if T <= _lib.QGEMV_MAX_M and same and sg.scales.dtype == x.dtype and su.scales.dtype == x.dtype:
+        gu = torch.empty((2, T, sg.out_features), dtype=x.dtype, device=dev)
+        flags = _lib.JQ_GEMV_STATIC_WEIGHTS if (getattr(sg, "static_weights", False) and
+                                                getattr(su, "static_weights", False)) else 0
+        ops.qgemv_fused(x, [sg, su], [gu[0], gu[1]], flags)
+        g2, u2 = gu[0], gu[1]
+    else:
+        g2, u2 = sg(x), su(x)
+    I2 = g2.shape[1]
+    h2 = torch.empty((T, I2), dtype=x.dtype, device=dev)
+    _lib.check(lib.jq_moe_swiglu(g2.data_ptr(), u2.data_ptr(), g2.stride(0), None, None, None, h2.data_ptr(),
+                                 h2.stride(0), I2, T, float(swiglu_limit), _lib.dtype_id(x.dtype), _lib.stream_ptr(dev)))
+    return sd(h2)
 
 
 def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertBank, up: ExpertBank,
@@ -385,19 +410,12 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
                 return y        # [T*k, H]: the caller sums the k rows of a token (routing weights already applied)
             # pairs of other ranks' experts were skipped by the kernels and their rows stay zero
             inv_ptr = None
-        need_f32 = out_f32 or shared is not None
-        acc = torch.empty((T, H), dtype=torch.float32, device=dev) if need_f32 else None
-        out = None if need_f32 else torch.empty((T, H), dtype=x.dtype, device=dev)
-        _lib.check(lib.jq_moe_combine(y.data_ptr(), y.stride(0), inv_ptr, None, T, k, H,
-                                      out.data_ptr() if out is not None else None, H,
-                                      acc.data_ptr() if acc is not None else None, dt, st))
-        if shared is not None:
-            sg, su, sd = shared
-            g2, u2 = sg(x).float(), su(x).float()
-            if swiglu_limit > 0:
-                u2 = u2.clamp(-swiglu_limit, swiglu_limit)
-                g2 = g2.clamp(max=swiglu_limit)
-            acc = acc + sd((torch.nn.functional.silu(g2) * u2).to(x.dtype)).float()
-        if need_f32:
-            return acc if out_f32 else acc.to(x.dtype)
-        return out
+        ys = _shared_expert(x, shared, swiglu_limit) if shared is not None else None
+        acc = torch.empty((T, H), dtype=torch.float32, device=dev) if out_f32 else None
+        out = None if out_f32 else torch.empty((T, H), dtype=x.dtype, device=dev)
+        _lib.check(lib.jq_moe_combine_shared(y.data_ptr(), y.stride(0), inv_ptr, None, T, k, H,
+                                             ys.data_ptr() if ys is not None else None,
+                                             ys.stride(0) if ys is not None else 0,
+                                             out.data_ptr() if out is not None else None, H,
+                                             acc.data_ptr() if acc is not None else None, dt, st))
+        return acc if out_f32 else out

@@ -19,11 +19,14 @@ def _rand_linear(out_f, in_f, bits, gs, device, seed):
     return JANGLinear.from_float(w, bits=bits, group_size=gs)
 
 
-def _rand_bank(E, out_f, in_f, bits, gs, device, seed):
+def _rand_bank(E, out_f, in_f, bits, gs, device, seed, e0=0, e1=None):
+    """Experts [e0, e1) of a bank of E random experts.  The whole bank is drawn from one seed and then cut, so
+    the experts a rank holds are the same tensors whatever the number of ranks."""
     from .ops import quantize
+    e1 = E if e1 is None else e1
     g = torch.Generator(device=device)
     g.manual_seed(seed)
-    w = (torch.randn((E, out_f, in_f), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    w = (torch.randn((E, out_f, in_f), generator=g, device=device, dtype=torch.float32)[e0:e1] * 0.02).to(torch.bfloat16)
     wq, s, b = quantize(w, gs, bits)
     return moe.ExpertBank(wq, s, b, bits, gs)
 
@@ -62,9 +65,9 @@ class MoEDecodeStack:
                 "o": _rand_linear(hidden, dq, attn_bits, gs, device, s0 + 4),
                 "router": (torch.randn((experts, hidden), device=device,
                                        generator=torch.Generator(device=device).manual_seed(s0 + 5)) * 0.02).to(torch.bfloat16),
-                "gate": _rand_bank(self.e_local, inter, hidden, expert_bits, gs, device, s0 + 10 + rank),
-                "up": _rand_bank(self.e_local, inter, hidden, expert_bits, gs, device, s0 + 30 + rank),
-                "down": _rand_bank(self.e_local, hidden, inter, expert_bits, gs, device, s0 + 50 + rank),
+                "gate": _rand_bank(experts, inter, hidden, expert_bits, gs, device, s0 + 10, self.base, self.base + self.e_local),
+                "up": _rand_bank(experts, inter, hidden, expert_bits, gs, device, s0 + 30, self.base, self.base + self.e_local),
+                "down": _rand_bank(experts, hidden, inter, expert_bits, gs, device, s0 + 50, self.base, self.base + self.e_local),
             }
             self.layers.append(lay)
         torch.cuda.synchronize(device)
@@ -76,10 +79,21 @@ class MoEDecodeStack:
         per_expert = 3 * (inter * hidden * expert_bits // 8 + (inter * hidden // gs) * 2 * e)
         self.bytes_per_token = layers * (attn + topk * per_expert + experts * hidden * 2)
 
-    def step(self, x: torch.Tensor) -> torch.Tensor:
-        """One token per row of x ([T, H] bf16) through every layer's quantized matmuls."""
+    def check_status(self):
+        """Raise JangqError(JQ_ETIMEOUT) if a bounded device-side wait ran out since the last check (a rank of
+        the exchange that never arrived): the outputs of that step are undefined.  Reads the device status
+        word, which synchronises the device; call it between graph replays in a serving loop."""
+        from . import _lib
+        _lib.check(_lib.load().jq_device_status())
+
+    def step(self, x: torch.Tensor, trace: list | None = None) -> torch.Tensor:
+        """One token per row of x ([T, H] bf16) through every layer's quantized matmuls.  With several ranks
+        and outside stream capture, the step first checks that the previous one did not time out.  `trace`
+        (a list) receives every layer's routing decision (idx, w), for checks against a reference walk."""
         from .ops import qgemv_fused
         T = x.shape[0]
+        if self.world > 1 and not torch.cuda.is_current_stream_capturing():
+            self.check_status()
         for lay in self.layers:
             if T <= 16:     # q/k/v read the same activations: one fused launch
                 outs = [torch.empty((T, lay[n].out_features), dtype=x.dtype, device=x.device) for n in "qkv"]
@@ -94,6 +108,8 @@ class MoEDecodeStack:
             else:
                 x = moe.residual_rmsnorm(x, lay["o"](q))
                 idx, w = moe.route_from_hidden(x, lay["router"], self.k)
+            if trace is not None:
+                trace.append((idx, w))
             if self.world == 1 and T * self.k < moe.SORT_THRESHOLD:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], all_local=True, return_slots=True,
                                   static_weights=True)

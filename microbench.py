@@ -1,8 +1,8 @@
 """Single-op micro-benchmark with an HBM-resident working set.
 
-    python -m jangq_b200.microbench --op qgemv --N 4096 --K 4096 --bits 4 --gs 64 --M 1
-    python -m jangq_b200.microbench --op quantize --N 8192 --K 8192 --bits 4
-    python -m jangq_b200.microbench --sweep qgemv        # BASELINE config-4 small-M sweep
+    python microbench.py --op qgemv --N 4096 --K 4096 --bits 4 --gs 64 --M 1
+    python microbench.py --op quantize --N 8192 --K 8192 --bits 4
+    python microbench.py --sweep qgemv        # BASELINE config-4 small-M sweep
 
 Distinct copies of the weights are rotated so that the bytes touched between
 two uses of the same copy exceed `--rotate-mb` (default 512 MB, 4x the L2), and
@@ -14,9 +14,13 @@ from __future__ import annotations
 import argparse
 import json
 
+import os
+import sys
+
 import torch
 
-from . import _lib, ops
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from jangq_b200 import _lib, ops  # noqa: E402
 
 
 def _time_graph(fn, iters: int, warmup: int = 3) -> float:
@@ -74,7 +78,7 @@ def bench_qgemv(N, K, bits, gs, M, iters, rotate_mb, dtype=torch.bfloat16, flags
 
 def bench_qgemm(N, K, bits, gs, M, iters, dtype=torch.bfloat16):
     """Prefill GEMM: TFLOP/s = 2*M*N*K / time (activations and weights stay L2/HBM resident as they fall)."""
-    from .gemm import qgemm
+    from jangq_b200.gemm import qgemm
     dev = torch.device("cuda")
     g = torch.Generator(device=dev)
     g.manual_seed(0)
@@ -135,7 +139,7 @@ def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="q
 def bench_moe_decode(layers, T, iters):
     """Few-token decode through `layers` layers of the config-3 MoE stack (stacks.MoEDecodeStack, one GPU): one
     eager pass (plain launches, what a launch-list capture sees), then the median time of a graph replay."""
-    from .stacks import MoEDecodeStack
+    from jangq_b200.stacks import MoEDecodeStack
     dev = torch.device("cuda")
     stack = MoEDecodeStack(layers=layers, device=dev)
     g = torch.Generator(device=dev)

@@ -320,3 +320,162 @@ def test_route_with_folded_residual_norm(T, H, E, k):
     idx2, w2 = moe.route_from_hidden(xo, wr, k)
     torch.cuda.synchronize()
     assert torch.equal(idx, idx2) and torch.equal(w, w2)
+
+
+# ---- the BASELINE MoE configurations at their real layer shapes ------------------------------------------------
+def _bank_from_seed(E, N, K, bits, gs, seed):
+    """A bank of E random experts quantized on the GPU, and its packed tensors on the host for the oracle."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    w = (torch.randn((E, N, K), generator=g, device=DEV, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    wq, s, b = jq.quantize(w, gs, bits)
+    del w
+    return jq.ExpertBank(wq, s, b, bits, gs), (wq.cpu().numpy().view(np.uint32), s.float().cpu().numpy(),
+                                               b.float().cpu().numpy(), bits, gs)
+
+
+def _linear_from_seed(N, K, bits, gs, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    w = (torch.randn((N, K), generator=g, device=DEV, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    lin = jq.JANGLinear.from_float(w, bits=bits, group_size=gs)
+    return lin, (lin.weight.cpu().numpy().view(np.uint32), lin.scales.float().cpu().numpy(),
+                 lin.biases.float().cpu().numpy(), bits, gs)
+
+
+@pytest.mark.parametrize("name,E,k,H,I,shared_bits,Ts", (("config3", 128, 8, 2048, 768, 0, (1, 8, 2048)),
+                                                         ("config5", 512, 10, 4096, 1024, 8, (1, 32, 4096))))
+def test_moe_layer_at_baseline_shapes(name, E, k, H, I, shared_bits, Ts):
+    """One routed layer of BASELINE config 3 (128 experts, top-8, hidden 2048, intermediate 768, 2-bit) and of
+    config 5 (512 experts, top-10, hidden 4096, intermediate 1024, 2-bit experts plus one 8-bit shared expert)
+    through moe_layer -- the few-token gather path at batch 1 / 8 / 32 and the sorted tensor-core path at the
+    prefill sizes -- against the oracle.  Tokens are independent, so the oracle walks a sample of them
+    (all of them for the small batches); every GPU row outside the sample is still checked for finiteness."""
+    gate, qg = _bank_from_seed(E, I, H, 2, 64, 101)
+    up, qu = _bank_from_seed(E, I, H, 2, 64, 102)
+    down, qd = _bank_from_seed(E, H, I, 2, 64, 103)
+    shared = shared_q = None
+    if shared_bits:
+        mods = [_linear_from_seed(I, H, shared_bits, 64, 104), _linear_from_seed(I, H, shared_bits, 64, 105),
+                _linear_from_seed(H, I, shared_bits, 64, 106)]
+        shared, shared_q = tuple(m for m, _ in mods), tuple(q for _, q in mods)
+    for T in Ts:
+        g = torch.Generator(device=DEV).manual_seed(T)
+        x = torch.randn((T, H), generator=g, device=DEV).to(torch.bfloat16)
+        logits = torch.randn((T, E), generator=g, device=DEV)
+        idx, w = jq.route_softmax_topk(logits, k)
+        out = jq.moe_layer(x, idx, w, gate, up, down, shared=shared)
+        torch.cuda.synchronize()
+        assert out.shape == (T, H) and bool(torch.isfinite(out.float()).all())
+        sample = np.arange(T) if T <= 32 else np.random.default_rng(T).choice(T, 24, replace=False)
+        ref = jo.moe_layer(x.float().cpu().numpy()[sample], idx.cpu().numpy()[sample], w.cpu().numpy()[sample],
+                           qg, qu, qd, act_dtype="bf16", shared=shared_q)
+        close(out.float().cpu().numpy()[sample], ref)
+    _lib.check(_lib.load().jq_device_status())
+
+
+def test_moe_layer_shared_expert_small():
+    """The always-on expert through the CUDA path (fused gate/up mat-vec, SwiGLU kernel, down, added in f32
+    inside the combine) with and without the clamp, few tokens and many, against the oracle's `shared=`."""
+    E, k, H, I = 8, 2, 256, 128
+    gate, qg = make_bank(E, I, H, 4, 64, seed=31)
+    up, qu = make_bank(E, I, H, 4, 64, seed=32)
+    down, qd = make_bank(E, H, I, 4, 64, seed=33)
+    mods = [_linear_from_seed(I, H, 8, 64, 34), _linear_from_seed(I, H, 8, 64, 35), _linear_from_seed(H, I, 8, 64, 36)]
+    shared, shared_q = tuple(m for m, _ in mods), tuple(q for _, q in mods)
+    rng = np.random.default_rng(5)
+    for T in (1, 5, 200):
+        x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+        idx, w = jq.route_softmax_topk(torch.from_numpy(rng.standard_normal((T, E)).astype(np.float32)).to(DEV), k)
+        for lim in (0.0, 0.4):
+            out = jq.moe_layer(x, idx, w, gate, up, down, swiglu_limit=lim, shared=shared)
+            ref = jo.moe_layer(x.float().cpu().numpy(), idx.cpu().numpy(), w.cpu().numpy(), qg, qu, qd,
+                               swiglu_limit=lim, act_dtype="bf16", shared=shared_q)
+            close(out.float().cpu().numpy(), ref)
+
+
+def _rms(v):
+    v = v.astype(np.float64)
+    return (v / np.sqrt((v * v).mean(axis=-1, keepdims=True) + float(torch.finfo(torch.bfloat16).eps))).astype(np.float32)
+
+
+@pytest.mark.parametrize("T", (1, 4))
+def test_decode_stack_two_layers_against_numpy_walk(T):
+    """MoEDecodeStack (what bench.py times for MoE decode) at config-3 layer shapes, two layers, against a
+    numpy walk of the same layers through the oracle: fused q/k/v, o, residual + norm folded into the router,
+    top-8 of 128 experts through the gate/up gather, SwiGLU, down gather, combine + residual + norm.  The walk
+    recomputes the router logits itself and accepts the GPU's choice of experts only where it agrees with them
+    (or where the k-th and (k+1)-th logits are within one rounding step of the activation type)."""
+    from jangq_b200.stacks import MoEDecodeStack
+    st = MoEDecodeStack(layers=2, device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(100 + T)
+    x0 = torch.randn((T, st.H), generator=g, device=DEV).to(torch.bfloat16)
+    trace = []
+    out = st.step(x0, trace=trace)
+    torch.cuda.synchronize()
+
+    def host(lin):
+        return (lin.weight.cpu().numpy().view(np.uint32), lin.scales.float().cpu().numpy(),
+                lin.biases.float().cpu().numpy(), lin.bits, lin.group_size)
+
+    def bank(b):
+        return (b.weight.cpu().numpy().view(np.uint32), b.scales.float().cpu().numpy(), b.biases.float().cpu().numpy(),
+                b.expert_bits[0], b.group_size)
+
+    x = x0.float().cpu().numpy()
+    for lay, (idx_g, _) in zip(st.layers, trace):
+        q = jo.round_to(jo.qmatmul(x, *host(lay["q"])), "bf16")
+        o = jo.round_to(jo.qmatmul(q, *host(lay["o"])), "bf16")
+        x = jo.round_to(_rms(x + o), "bf16")
+        logits = jo.round_to((x.astype(np.float64) @ lay["router"].float().cpu().numpy().astype(np.float64).T)
+                             .astype(np.float32), "bf16")
+        idx_ref, _ = jo.route_softmax_topk(logits, st.k)
+        idx_g = idx_g.cpu().numpy()
+        for t in range(T):
+            srt = np.sort(logits[t])[::-1]
+            if srt[st.k - 1] - srt[st.k] > 2.0 ** -7 * max(1.0, abs(srt[st.k - 1])):
+                assert set(idx_g[t].tolist()) == set(idx_ref[t].tolist())
+        # routing weights of the experts the GPU chose, from the walk's own logits
+        z = logits - logits.max(axis=-1, keepdims=True)
+        p = np.exp(z) / np.exp(z).sum(axis=-1, keepdims=True)
+        w = np.take_along_axis(p, idx_g.astype(np.int64), axis=-1)
+        w = (w / (w.sum(axis=-1, keepdims=True) + 1e-20)).astype(np.float32)
+        y = jo.moe_layer(x, idx_g, w, bank(lay["gate"]), bank(lay["up"]), bank(lay["down"]), act_dtype="bf16")
+        x = jo.round_to(_rms(x + y), "bf16")
+    close(out.float().cpu().numpy(), x)
+    _lib.check(_lib.load().jq_device_status())
+
+
+def test_switch_linear_module_matches_gather_qmm():
+    """JANGSwitchLinear with SwitchProj's call shapes (jang_tools/dsv41/model.py:1207-1230): x [T,1,1,D] with
+    idx [T,k] below the sort threshold, x [R,1,D] with a sorted idx [R] above it."""
+    E, N, K, bits = 8, 96, 256, 4
+    rng = np.random.default_rng(12)
+    w = torch.from_numpy((rng.standard_normal((E, N, K)) * 0.05).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    mod = jq.JANGSwitchLinear.from_float(w, bits=bits, group_size=64)
+    pk = (mod.weight.cpu().numpy().view(np.uint32), mod.scales.float().cpu().numpy(), mod.biases.float().cpu().numpy())
+    T, k = 5, 3
+    x = torch.from_numpy(rng.standard_normal((T, K)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    idx = torch.from_numpy(rng.integers(0, E, (T, k)).astype(np.int32)).to(DEV)
+    y = mod(x[:, None, None, :], idx, False)
+    assert y.shape == (T, k, 1, N)
+    ref = jo.gather_qmm(x.float().cpu().numpy(), *pk, idx.cpu().numpy().reshape(-1), bits, 64, np.repeat(np.arange(T), k))
+    close(y.float().cpu().numpy().reshape(T * k, N), ref)
+    R = 100
+    xr = torch.from_numpy(rng.standard_normal((R, K)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    e_idx = torch.sort(torch.from_numpy(rng.integers(0, E, R).astype(np.int32)).to(DEV)).values
+    y2 = mod(xr[:, None, :], e_idx, True)
+    assert y2.shape == (R, 1, N)
+    close(y2.float().cpu().numpy().reshape(R, N), jo.gather_qmm(xr.float().cpu().numpy(), *pk, e_idx.cpu().numpy(), bits, 64))
+
+
+def test_route_norm_rejects_in_place_output():
+    from jangq_b200 import moe
+    lib = _lib.load()
+    x = torch.randn((2, 1024), device=DEV).to(torch.bfloat16)
+    res = torch.randn((2, 1024), device=DEV).to(torch.bfloat16)
+    wr = torch.randn((16, 1024), device=DEV).to(torch.bfloat16)
+    idx = torch.empty((2, 4), dtype=torch.int32, device=DEV)
+    w = torch.empty((2, 4), dtype=torch.float32, device=DEV)
+    cnt, ws = moe._route_workspace(x.device, 2, 16)
+    rc = lib.jq_moe_route_norm(x.data_ptr(), res.data_ptr(), _lib.JQ_BF16, 2, 1024, 1e-3, x.data_ptr(), wr.data_ptr(), 16, 4,
+                               1, 1.0, idx.data_ptr(), w.data_ptr(), cnt.data_ptr(), ws.data_ptr(), _lib.stream_ptr())
+    assert rc == _lib.JQ_EINVAL and b"must not overlap" in lib.jq_last_error()

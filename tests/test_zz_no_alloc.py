@@ -58,3 +58,36 @@ def test_static_grouped_gemm_rejects_sizes_beyond_its_array():
     rc = lib.jq_moe_gemm_static(z.data_ptr(), _lib.JQ_BF16, 70000, 64, z.data_ptr(), 4, z.data_ptr(), z.data_ptr(),
                                 z.data_ptr(), None, _lib.JQ_BF16, 64, 64, 4, 64, z.data_ptr(), 64, None)
     assert rc == _lib.JQ_EUNSUPPORTED and b"at most 65536 rows" in lib.jq_last_error()
+
+
+def test_static_grouped_gemm_mixed_widths_and_dropped_pairs():
+    """A bank with two code widths (one launch per width, experts of the other width skipped) and a routing in
+    which some pairs belong to experts outside the bank, so fewer rows are kept than the call's row bound:
+    two calls in a row, each identical to the entry point that takes caller buffers."""
+    lib = _lib.load()
+    E, N, K, gs, base = 6, 128, 256, 64, 4
+    widths = (4, 8, 4, 8, 8, 4)
+    rng = np.random.default_rng(77)
+    experts = []
+    for e in range(E):
+        w = torch.from_numpy((rng.standard_normal((N, K)) * 0.05).astype(np.float32)).to(DEV).to(torch.bfloat16)
+        wq, s, b = jq.quantize(w, gs, widths[e])
+        experts.append((wq, s, b, widths[e]))
+    bank = jq.ExpertBank.from_experts(experts, gs)
+    for T, k in ((140, 3), (33, 2)):
+        x = torch.from_numpy(rng.standard_normal((T, K)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+        idx = torch.from_numpy(rng.integers(0, base + E + 3, T * k).astype(np.int32)).to(DEV)   # some ids outside the bank
+        sp = SortedPairs(idx, E, base)
+        xs = _gather_rows(x, sp, k)
+        ref = _moe_gemm(xs, sp, bank)
+        y = torch.zeros_like(ref)
+        for bits in bank.distinct_bits:
+            _lib.check(lib.jq_moe_gemm_static(xs.data_ptr(), _lib.JQ_BF16, sp.n, xs.stride(0), sp.offsets.data_ptr(), E,
+                                              bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
+                                              bank.biases_tab.data_ptr(), bank.bits_tab.data_ptr(), _lib.JQ_BF16, N, K,
+                                              bits, gs, y.data_ptr(), y.stride(0), _lib.stream_ptr()))
+        torch.cuda.synchronize()
+        kept = int(sp.offsets[E])
+        assert 0 < kept < T * k
+        assert torch.equal(y[:kept], ref[:kept])
+    assert lib.jq_device_status() == 0
