@@ -75,9 +75,36 @@ CONFIG = {"workload": "config2 dense decoder, batch-1 decode weight stream: 225 
 
 
 # --------------------------------------------------------------------------------------
-# CPU arm: the reference's numpy path (dequantize_affine_numpy(...) @ x), restated in
-# oracle/jang_oracle.py, on all host threads, on a bounded sample of the workload
+# CPU arm: the reference's numpy path, dequantize_affine_numpy(...) @ x (jang_tools/affine.py:445-463), on a
+# bounded sample of the workload, row chunks spread over one worker process per host core with the BLAS
+# library held to one thread per worker (no oversubscription).  The reference's own function is used where
+# its tree can be imported ($JANGQ_REF or /root/reference; widths 2/4/8 -- its 3/5/6-bit unpack is a
+# per-element Python loop); elsewhere, and for the 6-bit rows, the restatement in oracle/jang_oracle.py.
 # --------------------------------------------------------------------------------------
+_CPU = {}
+
+
+def _cpu_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def _reference_dequant():
+    for root in (os.environ.get("JANGQ_REF", ""), "/root/reference"):
+        pkg = os.path.join(root, "jang-tools")
+        if root and os.path.isdir(os.path.join(pkg, "jang_tools")):
+            if pkg not in sys.path:
+                sys.path.insert(0, pkg)
+            try:
+                from jang_tools.affine import dequantize_affine_numpy
+                return dequantize_affine_numpy
+            except Exception:
+                pass
+    return None
+
+
 def cpu_sample_setup():
     from oracle import jang_oracle as jo
     rng = np.random.default_rng(0)
@@ -91,60 +118,77 @@ def cpu_sample_setup():
     return sample
 
 
-def cpu_sample_step(sample, threads):
-    from concurrent.futures import ThreadPoolExecutor
+def _cpu_worker_init():
+    try:
+        from threadpoolctl import threadpool_limits
+        _CPU["limit"] = threadpool_limits(limits=1)
+    except Exception:
+        pass
+
+
+def _cpu_part(job):
+    i, r0, r1 = job
+    _, packed, s, b, x, bits, _, _ = _CPU["sample"][i]
+    ref = _CPU["ref"]
+    if ref is not None and bits in (2, 4, 8):
+        W = ref(packed[r0:r1], s[r0:r1], b[r0:r1], bits=bits, group_size=GS)
+        return float((x.astype(np.float32) @ W.T).sum())
     from oracle import jang_oracle as jo
+    return float(jo.qmatmul(x, packed[r0:r1], s[r0:r1], b[r0:r1], bits, GS, acc=np.float32).sum())
 
-    def part(args):
-        packed, s, b, x, bits = args
-        return jo.qmatmul(x, packed, s, b, bits, GS, acc=np.float32)
 
+def cpu_arm(steps, warmup):
+    """Times the sample; returns (GB/s, ms per step, description).  Worker processes are forked after the
+    sample exists, so they share it without copies; this process holds no CUDA context."""
+    import multiprocessing as mp
+    cores = _cpu_cores()
+    _CPU["sample"] = cpu_sample_setup()
+    _CPU["ref"] = _reference_dequant()
     jobs = []
-    for _, packed, s, b, x, bits, N, K in sample:
-        chunk = (N + threads - 1) // threads
-        for r0 in range(0, N, chunk):
-            jobs.append((packed[r0:r0 + chunk], s[r0:r0 + chunk], b[r0:r0 + chunk], x, bits))
-    with ThreadPoolExecutor(threads) as ex:
-        list(ex.map(part, jobs))
-    return sum(alg_bytes(N, K, bits) for _, _, _, _, _, bits, N, K in sample)
-
-
-def cpu_baseline(steps=2, warmup=1):
-    threads = os.cpu_count() or 1
-    sample = cpu_sample_setup()
-    for _ in range(warmup):
-        cpu_sample_step(sample, threads)
-    t0 = time.perf_counter()
-    nbytes = 0
-    for _ in range(steps):
-        nbytes += cpu_sample_step(sample, threads)
-    dt = time.perf_counter() - t0
-    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": "per step: one q_proj 4096x4096@8b + one gate_proj 11008x4096@2b + 4096 rows of lm_head@6b "
-                      "(dequantize + f32 mat-vec, numpy restatement of jang_tools/affine.py:445-463)",
+    for i, (_, _, _, _, _, _, N, _) in enumerate(_CPU["sample"]):
+        chunk = max(64, (N + 2 * cores - 1) // (2 * cores))
+        jobs += [(i, r0, min(N, r0 + chunk)) for r0 in range(0, N, chunk)]
+    nbytes = sum(alg_bytes(N, K, bits) for _, _, _, _, _, bits, N, K in _CPU["sample"])
+    with mp.get_context("fork").Pool(cores, initializer=_cpu_worker_init) as pool:
+        for _ in range(max(warmup, 1)):
+            pool.map(_cpu_part, jobs)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            pool.map(_cpu_part, jobs)
+        dt = time.perf_counter() - t0
+    kind = "reference" if _CPU["ref"] is not None else "port"
+    desc = {"value": nbytes * steps / dt / 1e9, "unit": UNIT, "cores": cores, "blas_threads_per_worker": 1,
+            "workers": cores, "kind": kind,
+            "sample": "per step: one q_proj 4096x4096@8b + one gate_proj 11008x4096@2b + 4096 rows of lm_head@6b; "
+                      "dequantize + f32 mat-vec in numpy, row chunks over one process per core"
+                      + ("; jang_tools.affine.dequantize_affine_numpy for the 2/8-bit matrices, its restatement for "
+                         "the 6-bit rows" if kind == "reference" else "; numpy restatement of jang_tools/affine.py:445-463"),
             "ms_per_step": dt / steps * 1e3}
+    return desc
+
+
+def cpu_baseline(steps=3, warmup=1):
+    """The CPU arm in a process of its own (this one holds a CUDA context; workers are forked)."""
+    import subprocess
+    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", str(steps),
+                          "--warmup", str(warmup)], capture_output=True, text=True, timeout=900,
+                         env={k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")})
+    for line in out.stdout.splitlines():
+        if line.startswith("{"):
+            return json.loads(line)["cpu_baseline"]
+    return {"error": (out.stderr or out.stdout)[-300:]}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    sample = cpu_sample_setup()
-    for _ in range(max(args.warmup, 0)):
-        cpu_sample_step(sample, threads)
-    t0 = time.perf_counter()
-    nbytes = 0
-    for _ in range(args.steps):
-        nbytes += cpu_sample_step(sample, threads)
-    dt = time.perf_counter() - t0
-    v = nbytes / dt / 1e9
+    desc = cpu_arm(args.steps, args.warmup)
+    v = desc["value"]
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": desc["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": CONFIG,
-            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                             "sample": "per step: one q_proj 4096x4096@8b + one gate_proj 11008x4096@2b + 4096 rows "
-                                       "of lm_head@6b, numpy dequantize + f32 mat-vec on all host threads"},
+            "cpu_baseline": desc,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -238,7 +282,8 @@ def run_cuda(args):
         torch.cuda.synchronize()
 
     linears = build_stack(device)
-    plan = jq.GemvPlan(linears, m=1, dtype=torch.bfloat16, device=device, groups=stack_groups())
+    plan = jq.GemvPlan(linears, m=1, dtype=torch.bfloat16, device=device, groups=stack_groups(),
+                       persistent=not args.no_persistent)
     g = torch.Generator(device=device)
     g.manual_seed(7)
     for buf in plan._xbuf.values():
@@ -318,6 +363,11 @@ def run_cuda(args):
                 "gpu_launches": plan.launches_per_run * K, "clocks": clk.summary()}
         if moe_res is not None:
             line["moe_decode"] = moe_res
+        if world == 1 and not args.no_extras:
+            try:
+                line["other_configs"] = run_extras(peaks, quick=args.quick_extras)
+            except Exception as e:                        # the headline stands without the side measurements
+                line["other_configs"] = {"error": f"{type(e).__name__}: {e}"}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
@@ -412,7 +462,8 @@ def run_moe(args, device, world, rank, barrier):
                "note": "router + sort + gather + gate/up/down grouped GEMMs + SwiGLU + combine of one layer; "
                        "N>1: all-to-all dispatch/combine of the rank's 2048 tokens (host-synchronised split sizes)"}
     gbs = stack.bytes_per_token / (ms * 1e-3) / 1e9
-    return {"prefill": prefill, "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
+    parity = moe_parity(stack, x, xp, device, world, rank) if world > 1 else None
+    return {"parity": parity, "prefill": prefill, "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
             "per_gpu_GBps": gbs, "hbm_frac": gbs / peak, "graph": graph is not None, "finite": finite,
             "ep_mode": ep_mode if world > 1 else None,
             "workload": "config3 MoE stack, batch-1 decode per GPU: 48 layers x [q,k,v,o @6b + bf16 router + top-8 of "
@@ -420,6 +471,95 @@ def run_moe(args, device, world, rank, barrier):
                         "N>1: every rank runs the replicated dense blocks on the N tokens of the step, its own experts on "
                         "them, and the partial sums are added per layer over NVLink peer loads inside the residual+norm "
                         "kernel (ep_mode peer) or by one NCCL all-reduce (ep_mode replicated); attention core not run"}
+
+
+def run_extras(peaks, quick=False):
+    """The other BASELINE configurations on one GPU, as sub-records of the bench line (CUDA events, graph
+    replay, weights rotated over more than twice the L2 where a case would fit it):
+      config1   4096x4096 bf16 weight: quantize at 4 bits (GB/s) and the batch-1 mat-vec over it;
+      qgemm     the prefill GEMM at the config-2 layer shapes with M = 512, and 4096 x 14336 x 4096 at 4 bits;
+      sweep     config 4: K in {2048,4096,8192} x N in {4096,14336,28672} x bits {2,3,4,6,8} x group {64,128},
+                M in {1,8} as GB/s against the HBM peak, M in {64,512,4096} as TFLOP/s against the bf16 peak;
+                per width the minimum and the median fraction over the 18 (K, N, group) cases."""
+    import torch
+    import microbench as mb
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    tf_burst = float(peaks.get("bf16_tflops", 1590.0))
+    tf_sus = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops_burst": tf_burst, "bf16_tflops_sustained": tf_sus,
+                     "source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback"}}
+    q = mb.bench_quantize(4096, 4096, 4, 64, 5, 300)
+    v = mb.bench_qgemv(4096, 4096, 4, 64, 1, 5, 300, flags=1)
+    out["config1"] = {"quantize_GBps": q["GBps"], "quantize_us": q["us"], "quantize_frac_hbm": q["GBps"] / hbm,
+                      "qgemv_GBps": v["GBps"], "qgemv_us": v["us"], "qgemv_frac_hbm": v["GBps"] / hbm,
+                      "note": "HBM-resident: rotating copies; the 9.45 MB mat-vec alone would sit in L2"}
+    torch.cuda.empty_cache()
+    layer = []
+    flops = us = 0.0
+    for name, N, K, bits, cnt in (("q/k/v/o", 4096, 4096, 8, 4), ("gate/up", 11008, 4096, 2, 2), ("down", 4096, 11008, 2, 1)):
+        r = mb.bench_qgemm(N, K, bits, 64, 512, 3)
+        layer.append({"name": name, "M": 512, "N": N, "K": K, "bits": bits, "TFLOPs": r["TFLOPs"], "us": r["us"]})
+        flops += cnt * 2.0 * 512 * N * K
+        us += cnt * r["us"]
+    big = mb.bench_qgemm(14336, 4096, 4, 64, 4096, 3)
+    out["qgemm"] = {"config2_prefill512_layer": layer, "layer_TFLOPs": flops / (us * 1e-6) / 1e12,
+                    "layer_frac_burst": flops / (us * 1e-6) / 1e12 / tf_burst,
+                    "layer_frac_sustained": flops / (us * 1e-6) / 1e12 / tf_sus,
+                    "M4096_N14336_K4096_4bit_TFLOPs": big["TFLOPs"], "frac_burst": big["TFLOPs"] / tf_burst,
+                    "frac_sustained": big["TFLOPs"] / tf_sus}
+    torch.cuda.empty_cache()
+    Ks, Ns = ((4096,), (4096, 14336)) if quick else ((2048, 4096, 8192), (4096, 14336, 28672))
+    sweep = {}
+    for bits in (2, 3, 4, 6, 8):
+        small, large, worst_s, worst_l = {1: [], 8: []}, {64: [], 512: [], 4096: []}, None, None
+        for gs in (64, 128):
+            for K in Ks:
+                for N in Ns:
+                    for M in (1, 8):
+                        r = mb.bench_qgemv(N, K, bits, gs, M, 3, 256, flags=1)
+                        f = r["GBps"] / hbm
+                        small[M].append(f)
+                        if worst_s is None or f < worst_s[0]:
+                            worst_s = (f, f"M={M} N={N} K={K} gs={gs}")
+                    for M in (64, 512, 4096):
+                        r = mb.bench_qgemm(N, K, bits, gs, M, 2)
+                        f = r["TFLOPs"] / tf_burst
+                        large[M].append(f)
+                        if worst_l is None or f < worst_l[0]:
+                            worst_l = (f, f"M={M} N={N} K={K} gs={gs}")
+                    torch.cuda.empty_cache()
+        sweep[str(bits)] = {
+            **{f"M{M}_hbm_frac_min_med": [min(v), statistics.median(v)] for M, v in small.items()},
+            **{f"M{M}_bf16_burst_frac_min_med": [min(v), statistics.median(v)] for M, v in large.items()},
+            "worst_small": worst_s[1], "worst_large": worst_l[1]}
+    out["config4_sweep"] = {"cases_per_width": len(Ks) * len(Ns) * 2, "by_bits": sweep,
+                            "note": "fractions of the measured HBM copy rate (M = 1, 8) and of the measured bf16 burst "
+                                    "rate (M = 64, 512, 4096); [minimum, median] over K x N x group size"}
+    return out
+
+
+def moe_parity(stack, x, xp, device, world, rank):
+    """Outside the timed region, with several ranks: two layers of the expert-parallel decode step and one
+    expert-parallel prefill layer against the same layers computed on rank 0 alone from all experts (a
+    one-rank stack with the same seeds: experts are drawn by global id, so it is the same model).
+    Returns max |y - ref| / max |ref| and the cosine of both comparisons (north-star bar 1e-2 / 0.9999)."""
+    import torch
+    from jangq_b200.stacks import MoEDecodeStack
+    y_ep = stack.step(x, n_layers=2).float()
+    p_ep = stack.prefill_layer(xp, 0).float()
+    torch.cuda.synchronize()
+    if rank != 0:
+        return None
+    ref = MoEDecodeStack(layers=2, device=device, rank=0, world=1)
+    y_ref = ref.step(x).float()
+    p_ref = ref.prefill_layer(xp, 0).float()
+    torch.cuda.synchronize()
+
+    def cmp(a, b):
+        return {"max_rel": float((a - b).abs().max() / b.abs().max()),
+                "cos": float((a * b).sum() / (a.norm() * b.norm()))}
+    return {"decode_2_layers": cmp(y_ep, y_ref), "prefill_layer_0": cmp(p_ep, p_ref),
+            "reference": "the same layers on rank 0 alone with all 128 experts", "tokens": int(x.shape[0])}
 
 
 def main():
@@ -430,6 +570,10 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the config-3 MoE decode measurement")
+    ap.add_argument("--no-extras", action="store_true", help="skip the config-1 / prefill GEMM / config-4 sweep sub-records")
+    ap.add_argument("--quick-extras", action="store_true", help="a reduced config-4 sweep (K=4096, two N)")
+    ap.add_argument("--no-persistent", action="store_true",
+                    help="one launch per group of matrices instead of the one persistent launch per step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

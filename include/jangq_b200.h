@@ -120,6 +120,50 @@ int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtyp
 int jq_qgemv_batched_ex(const JqGemvDesc* descs, int count, int64_t M, int act_dtype,
                         int sidecar_dtype, int flags, jq_stream_t stream);
 
+/* A whole decode step's dependent mat-vecs in ONE persistent launch.  The reference measured its decode
+ * as dispatch-bound and fused its dispatches by hand (jang_tools/dsv41/DECODE_DSPARK_METHODS.md:90-128, driver
+ * dsv41/metal_decode.py:464-497); on CUDA the same effect needs the boundary between two dependent mat-vecs
+ * to be cheaper than a kernel boundary.  A program is an ordered list of ops; op j computes, for each of its
+ * 1..4 matrices (they share x, K, the bit width and the group size -- q/k/v, or gate/up),
+ *     y_i[N_i] = deq(W_i)[N_i, K] . x[K]            (jq_qgemv's arithmetic, one activation row),
+ * and op j + 1 starts only after every output of op j is complete: a grid barrier inside the kernel,
+ * across which the next op's weights are already streaming.  x of an op may be any buffer written before
+ * the launch or by an op at least two places earlier, or exactly one whole output y_i of the op directly
+ * before it (with K == N_i); any other overlap with the previous op's outputs is refused (JQ_EINVAL).
+ * Limits: bits 2, 4 or 8; group_size 64 or 128 with K / group_size a multiple of 4; activations, scales,
+ * biases and outputs all of act_dtype (f16 or bf16); codes 16-byte, scales/biases 8-byte, x 16-byte
+ * aligned; an op whose rows would make one CTA touch more than 16 row tiles (about 35 000 rows at K = 4096)
+ * is refused with JQ_EUNSUPPORTED: split it by rows.  Weights must not be written while a program that names
+ * them runs.
+ *
+ * jq_qgemv_stream_workspace_bytes: device bytes a program needs (op table, float32 accumulators, counters).
+ * jq_qgemv_stream_prepare: validates the ops (a HOST array), writes the op table into the 256-byte aligned
+ *   device workspace and zeroes its counters; synchronises `stream`; call it once, outside stream capture,
+ *   and again after jq_device_status() has reported a timeout.  Fills *program (host memory, caller-owned).
+ * jq_qgemv_stream_run: one cooperative launch (one CTA per SM) on `stream`; may be captured in a CUDA graph
+ *   and replayed.  Two runs of the same program must not overlap (they share the workspace).  Every wait
+ *   inside is bounded (0.5 s); if one runs out, jq_device_status() returns JQ_ETIMEOUT and the outputs of that
+ *   run are undefined. */
+typedef struct JqStreamOp {
+    const void*     x;            /* [K] activations of the op                     */
+    const uint32_t* codes[4];     /* [N_i, K*bits/32]                              */
+    const void*     scales[4];    /* [N_i, K/group_size]                           */
+    const void*     biases[4];
+    void*           y[4];         /* [N_i]                                         */
+    int64_t         N[4];
+    int64_t         K;
+    int32_t         count;        /* matrices of the op: 1..4                      */
+    int32_t         bits, group_size;
+} JqStreamOp;
+typedef struct JqStreamProgram {  /* filled by jq_qgemv_stream_prepare, read by jq_qgemv_stream_run */
+    void*   workspace;
+    int32_t n_ops, act_dtype, kmax, maxrows, warps, grid;
+} JqStreamProgram;
+size_t jq_qgemv_stream_workspace_bytes(const JqStreamOp* ops, int n_ops);
+int jq_qgemv_stream_prepare(const JqStreamOp* ops, int n_ops, int act_dtype, void* workspace,
+                            size_t workspace_bytes, JqStreamProgram* program, jq_stream_t stream);
+int jq_qgemv_stream_run(const JqStreamProgram* program, jq_stream_t stream);
+
 /* K3. Prefill-shaped quantized GEMM: the same mx.quantized_matmul call with many
  * activation rows (MLX switches from qmv to its tiled qmm there; the reference's only
  * statement of that kernel is the tile shape at jang_tools/jangh/kernels.py:34,273-277).

@@ -37,6 +37,17 @@ class JqGemvDesc(C.Structure):
                 ("bits", C.c_int32), ("group_size", C.c_int32)]
 
 
+class JqStreamOp(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("codes", C.c_void_p * 4), ("scales", C.c_void_p * 4), ("biases", C.c_void_p * 4),
+                ("y", C.c_void_p * 4), ("N", C.c_int64 * 4), ("K", C.c_int64), ("count", C.c_int32), ("bits", C.c_int32),
+                ("group_size", C.c_int32)]
+
+
+class JqStreamProgram(C.Structure):
+    _fields_ = [("workspace", C.c_void_p), ("n_ops", C.c_int32), ("act_dtype", C.c_int32), ("kmax", C.c_int32),
+                ("maxrows", C.c_int32), ("warps", C.c_int32), ("grid", C.c_int32)]
+
+
 _i64, _i32, _p = C.c_int64, C.c_int, C.c_void_p
 
 # name -> (restype, argtypes); every symbol include/jangq_b200.h declares
@@ -52,6 +63,9 @@ SIGNATURES = {
     "jq_qgemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_batched": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _p]),
     "jq_qgemv_batched_ex": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _i32, _p]),
+    "jq_qgemv_stream_workspace_bytes": (C.c_size_t, [C.POINTER(JqStreamOp), _i32]),
+    "jq_qgemv_stream_prepare": (C.c_int, [C.POINTER(JqStreamOp), _i32, _i32, _p, C.c_size_t, C.POINTER(JqStreamProgram), _p]),
+    "jq_qgemv_stream_run": (C.c_int, [C.POINTER(JqStreamProgram), _p]),
     "jq_device_status": (C.c_int, []),
     "jq_moe_sort_max_tiles": (C.c_size_t, [_i64, _i32, _i32]),
     "jq_moe_sort": (C.c_int, [_p, _i64, _i32, _i32, _p, _p, _p, _i32, _p, _p, _p, _p]),

@@ -1,0 +1,89 @@
+// Building blocks of the integer warp-MMA mat-vec kernels (jq_qgemv_pint.cu, jq_qgemv_stream.cu):
+// the u8 x s8 -> s32 m16n8k32 MMA wrappers, small cp.async forms and the shift-free unpack of 2-, 4- and
+// 8-bit codes into byte operands.
+//
+// Shift-free unpack: a code stays at its bit position p inside its byte, A = word & (mask << p) = 2^p * q,
+// and the activation that meets it is scaled by 2^-p before it is cut into limbs (exact: a power of two).
+// A 32-bit word of codes costs one AND per operand register.
+#pragma once
+
+#include "jq_mma.cuh"
+
+namespace jq {
+namespace imma_ops {
+
+__device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                     uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// same with a zero accumulator input (starts a new sum without clearing registers)
+__device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                      uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+// The lane's 16 codes of a 64-code block (u[], code j at bit j*BITS) -> 4 registers of 4 bytes, without
+// shifts.  Register i, byte t holds code elem(i, t) times 2^code_shift(elem(i, t)).
+template <int BITS>
+__device__ __forceinline__ void to_bytes(const uint32_t (&u)[Unit<BITS>::WORDS], uint32_t (&r)[4]) {
+    if constexpr (BITS == 8) {
+        r[0] = u[0]; r[1] = u[1]; r[2] = u[2]; r[3] = u[3];
+    } else if constexpr (BITS == 4) {
+        r[0] = u[0] & 0x0F0F0F0Fu; r[1] = u[0] & 0xF0F0F0F0u;
+        r[2] = u[1] & 0x0F0F0F0Fu; r[3] = u[1] & 0xF0F0F0F0u;
+    } else {
+        static_assert(BITS == 2, "widths of the integer kernels: 2, 4, 8");
+        r[0] = u[0] & 0x03030303u; r[1] = u[0] & 0x0C0C0C0Cu;
+        r[2] = u[0] & 0x30303030u; r[3] = u[0] & 0xC0C0C0C0u;
+    }
+}
+template <int BITS> __host__ __device__ constexpr int elem(int i, int t) {
+    return BITS == 2 ? i + 4 * t : BITS == 4 ? 8 * (i >> 1) + (i & 1) + 2 * t : 4 * i + t;
+}
+// log2 of the factor the code of element j carries inside its byte
+template <int BITS> __host__ __device__ constexpr int code_shift(int j) {
+    return BITS == 2 ? 2 * (j & 3) : BITS == 4 ? 4 * (j & 1) : 0;
+}
+
+// Sixteen consecutive activations v[] of one quantization group -> the unit's 16 bytes of the three limb
+// rows (byte order = the order to_bytes leaves the codes in).  `scale` = 2^(21 - E) with E the exponent of
+// the group's largest magnitude, so that |v * scale| < 2^22; element j is further divided by the factor
+// 2^code_shift(j) its code carries.  The limbs are the signed base-256 digits of the rounded value:
+// with u = xi + 0x8080 the bytes of u ^ 0x8080 are the two's-complement digits.
+template <int BITS>
+__device__ __forceinline__ void limbs16(const float (&v)[16], float scale, uint8_t* l0, uint8_t* l1, uint8_t* l2) {
+    uint32_t t[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float sj = scale * (1.f / (float)(1 << code_shift<BITS>(j)));
+        t[j] = ((uint32_t)__float2int_rn(v[j] * sj) + 0x8080u) ^ 0x8080u;
+    }
+    uint8_t* const d[3] = {l0, l1, l2};
+#pragma unroll
+    for (int L = 0; L < 3; ++L) {
+        const uint32_t sel = ((4u + L) << 4) | L;            // byte L of both sources
+        uint32_t wd[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            wd[i] = __byte_perm(__byte_perm(t[elem<BITS>(i, 0)], t[elem<BITS>(i, 1)], sel),
+                                __byte_perm(t[elem<BITS>(i, 2)], t[elem<BITS>(i, 3)], sel), 0x5410);
+        *reinterpret_cast<uint4*>(d[L]) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+    }
+}
+
+}  // namespace imma_ops
+}  // namespace jq

@@ -23,7 +23,7 @@
 // codes) plus the raw 2-byte scales and biases, copied by cp.async into a private ring of `nbuf` stages
 // per warp: no register staging, no CTA barrier.  A warp adds the item's result to its own row sums in
 // shared memory; one CTA barrier at the end, then the warps' sums are added and stored.
-#include "jq_mma.cuh"
+#include "jq_imma.cuh"
 #include "jq_qgemv.cuh"
 
 namespace jq {
@@ -32,55 +32,12 @@ namespace pint {
 
 constexpr int MAX_SMEM = 227 * 1024;
 
-__device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                     uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                      uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
-}
+using namespace imma_ops;
+
 __device__ __forceinline__ void cp_async_wait_dyn(int pending) {   // pending in 1..3
     if (pending == 1) cp_async_wait<1>();
     else if (pending == 2) cp_async_wait<2>();
     else cp_async_wait<3>();
-}
-
-// The lane's 16 codes of a 64-code block (u[], code j at bit j*BITS) -> 4 registers of 4 bytes, without
-// shifts.  Register i, byte t holds code elem(i, t) times 2^shift(i).
-template <int BITS>
-__device__ __forceinline__ void to_bytes(const uint32_t (&u)[Unit<BITS>::WORDS], uint32_t (&r)[4]) {
-    if constexpr (BITS == 8) {
-        r[0] = u[0]; r[1] = u[1]; r[2] = u[2]; r[3] = u[3];
-    } else if constexpr (BITS == 4) {
-        r[0] = u[0] & 0x0F0F0F0Fu; r[1] = u[0] & 0xF0F0F0F0u;
-        r[2] = u[1] & 0x0F0F0F0Fu; r[3] = u[1] & 0xF0F0F0F0u;
-    } else {
-        static_assert(BITS == 2, "widths of this kernel: 2, 4, 8");
-        r[0] = u[0] & 0x03030303u; r[1] = u[0] & 0x0C0C0C0Cu;
-        r[2] = u[0] & 0x30303030u; r[3] = u[0] & 0xC0C0C0C0u;
-    }
-}
-template <int BITS> __host__ __device__ constexpr int elem(int i, int t) {
-    return BITS == 2 ? i + 4 * t : BITS == 4 ? 8 * (i >> 1) + (i & 1) + 2 * t : 4 * i + t;
-}
-// log2 of the factor the code of element j carries inside its byte
-template <int BITS> __host__ __device__ constexpr int code_shift(int j) {
-    return BITS == 2 ? 2 * (j & 3) : BITS == 4 ? 4 * (j & 1) : 0;
 }
 
 template <int BITS, int GS> struct Geom {

@@ -10,6 +10,12 @@ last output.  Linears named in one inner list of `groups` read the same
 activations (q/k/v, or gate/up, of a decoder layer) and go out through
 jq_qgemv_batched_ex, which makes one launch of every run that shares K, the
 bit width and the group size.
+
+`persistent=True` goes one step further (the reference's hand-fused dispatches,
+dsv41/metal_decode.py:464-497): every run of consecutive groups the streamed
+program takes (one activation row, 2-/4-/8-bit codes) becomes ONE cooperative
+launch, jq_qgemv_stream_run, whose op boundaries are grid barriers inside the
+kernel; groups it does not take (other widths) keep their own launch.
 """
 from __future__ import annotations
 
@@ -30,7 +36,7 @@ class GemvPlan:
 
     def __init__(self, linears: Sequence[JANGLinear], m: int = 1, dtype: torch.dtype = torch.bfloat16,
                  device=None, share_inputs: bool = True, static_weights: bool = True,
-                 groups: Sequence[Sequence[int]] | None = None):
+                 groups: Sequence[Sequence[int]] | None = None, persistent: bool = False):
         if m < 1 or m > _lib.QGEMV_MAX_M:
             raise _lib.JangqError(_lib.JQ_EINVAL, f"GemvPlan takes 1..{_lib.QGEMV_MAX_M} rows")
         self.linears = list(linears)
@@ -56,6 +62,24 @@ class GemvPlan:
             if any(self.x[i] is not self.x[g[0]] for i in g):
                 raise _lib.JangqError(_lib.JQ_EINVAL, "the linears of a group must read the same input buffer")
         self.launches_per_run = sum(self._launches_of(g) for g in self.groups) * ((m + 7) // 8)
+        # persistent: segments = ("program", StreamProgram) or ("groups", [group, ...]) in execution order
+        self.persistent = bool(persistent) and m == 1
+        self._segments = None
+        if self.persistent:
+            self._segments, launches, run = [], 0, []
+            for g in self.groups + [None]:
+                if g is not None and self._streamable(g):
+                    run.append(g)
+                    continue
+                if run:
+                    self._segments.append(("program", StreamProgram(
+                        [(self.x[r[0]], [self.linears[i] for i in r], [self.y[i] for i in r]) for r in run], dtype)))
+                    launches += 1
+                    run = []
+                if g is not None:
+                    self._segments.append(("groups", [g]))
+                    launches += self._launches_of(g)
+            self.launches_per_run = launches
         self._graph = None
         self._host_in = {k: torch.zeros(v.shape, dtype=dtype).pin_memory() for k, v in self._xbuf.items()}
         self._host_out = torch.zeros(self.y[-1].shape, dtype=dtype).pin_memory()
@@ -78,9 +102,25 @@ class GemvPlan:
             run += 1
         return n
 
+    def _streamable(self, group) -> bool:
+        lins = [self.linears[i] for i in group]
+        l0 = lins[0]
+        return (len(lins) <= 4 and l0.bits in (2, 4, 8) and l0.group_size in (64, 128) and
+                l0.in_features % (4 * l0.group_size) == 0 and
+                all(l.bits == l0.bits and l.group_size == l0.group_size and l.in_features == l0.in_features and
+                    l.scales.dtype == self.dtype and l.bias is None for l in lins))
+
     def _enqueue(self):
         from .ops import qgemv_fused
         flags = _lib.JQ_GEMV_STATIC_WEIGHTS if self.static_weights else 0
+        if self._segments is not None:
+            for kind, what in self._segments:
+                if kind == "program":
+                    what.run()
+                else:
+                    for g in what:
+                        qgemv_fused(self.x[g[0]], [self.linears[i] for i in g], [self.y[i] for i in g], flags)
+            return
         for g in self.groups:
             qgemv_fused(self.x[g[0]], [self.linears[i] for i in g], [self.y[i] for i in g], flags)
 
@@ -124,3 +164,54 @@ class GemvPlan:
     @property
     def d2h_bytes(self) -> int:
         return self._host_out.numel() * self._host_out.element_size()
+
+
+class StreamProgram:
+    """A prepared program of dependent one-row mat-vecs for jq_qgemv_stream_run: `ops` is a list of
+    (x [1, K] or [K], [linear, ...], [y, ...]) in execution order; the linears of an op share x, K, the bit
+    width (2, 4 or 8) and the group size.  An op with more rows than one op of a program may have is cut
+    into row ranges (consecutive ops over slices of the same tensors).  The program keeps references to the
+    tensors it names; run() enqueues the one launch on the current stream."""
+
+    MAX_TILES_PER_CTA = 14          # row tiles per SM an op may have (the kernel's limit of 16 minus both ends)
+
+    def __init__(self, ops, dtype: torch.dtype = torch.bfloat16):
+        import ctypes as C
+        lib = _lib.load()
+        self._keep = ops
+        first = ops[0][0]
+        self.device = first.device
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        flat = []
+        for x, lins, ys in ops:
+            l0 = lins[0]
+            tiles = sum((l.out_features + 15) // 16 for l in lins)
+            parts = max(1, -(-tiles // (self.MAX_TILES_PER_CTA * sms)))
+            if parts == 1:
+                flat.append((x, [(l.weight, l.scales, l.biases, y.reshape(-1)) for l, y in zip(lins, ys)], l0))
+                continue
+            for l, y in zip(lins, ys):          # too many rows: every matrix on its own, in row chunks
+                n = l.out_features
+                chunk = -(-n // (parts * 16)) * 16
+                for r0 in range(0, n, chunk):
+                    r1 = min(n, r0 + chunk)
+                    flat.append((x, [(l.weight[r0:r1], l.scales[r0:r1], l.biases[r0:r1], y.reshape(-1)[r0:r1])], l0))
+        self.n_ops = len(flat)
+        arr = (_lib.JqStreamOp * self.n_ops)()
+        for d, (x, mats, l0) in zip(arr, flat):
+            d.x = x.data_ptr()
+            d.K, d.bits, d.group_size, d.count = l0.in_features, l0.bits, l0.group_size, len(mats)
+            for i, (w, s, b, y) in enumerate(mats):
+                d.codes[i], d.scales[i], d.biases[i], d.y[i], d.N[i] = (w.data_ptr(), s.data_ptr(), b.data_ptr(),
+                                                                          y.data_ptr(), w.shape[0])
+        nbytes = int(lib.jq_qgemv_stream_workspace_bytes(arr, self.n_ops))
+        self.workspace = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=self.device)
+        self.program = _lib.JqStreamProgram()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.jq_qgemv_stream_prepare(arr, self.n_ops, _lib.dtype_id(dtype), self.workspace.data_ptr(),
+                                                   self.workspace.numel(), C.byref(self.program),
+                                                   _lib.stream_ptr(self.device)))
+
+    def run(self):
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().jq_qgemv_stream_run(self.program, _lib.stream_ptr(self.device)))

@@ -86,15 +86,16 @@ class MoEDecodeStack:
         from . import _lib
         _lib.check(_lib.load().jq_device_status())
 
-    def step(self, x: torch.Tensor, trace: list | None = None) -> torch.Tensor:
+    def step(self, x: torch.Tensor, trace: list | None = None, n_layers: int | None = None) -> torch.Tensor:
         """One token per row of x ([T, H] bf16) through every layer's quantized matmuls.  With several ranks
         and outside stream capture, the step first checks that the previous one did not time out.  `trace`
-        (a list) receives every layer's routing decision (idx, w), for checks against a reference walk."""
+        (a list) receives every layer's routing decision (idx, w), for checks against a reference walk;
+        `n_layers` stops after the first layers."""
         from .ops import qgemv_fused
         T = x.shape[0]
         if self.world > 1 and not torch.cuda.is_current_stream_capturing():
             self.check_status()
-        for lay in self.layers:
+        for lay in self.layers[:n_layers]:
             if T <= 16:     # q/k/v read the same activations: one fused launch
                 outs = [torch.empty((T, lay[n].out_features), dtype=x.dtype, device=x.device) for n in "qkv"]
                 qgemv_fused(x, [lay[n] for n in "qkv"], outs, 1)

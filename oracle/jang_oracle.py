@@ -83,17 +83,28 @@ def pack_rows(codes: np.ndarray, bits: int) -> np.ndarray:
 
 
 def unpack_rows(packed: np.ndarray, bits: int, K: int | None = None) -> np.ndarray:
-    """Inverse of pack_rows -> uint8 [rows, K] (pack.py:85-149, vectorised for
-    every width; the reference's 3/5/6-bit branch is a per-element loop)."""
+    """Inverse of pack_rows -> uint8 [rows, K] (pack.py:85-149), vectorised for every width: the stream is
+    cut into units of lcm(bits, 8) bits (1 byte for 2/4/8-bit codes, 3 bytes for 3/6-bit, 5 bytes for 5-bit),
+    each unit is read as one little-endian integer and its codes are shifted out.  (The reference's own
+    3/5/6-bit branch is a per-element loop.)"""
     packed = np.ascontiguousarray(packed, dtype="<u4")
     rows, words = packed.shape
     if K is None:
         K = words * 32 // bits
-    stream = np.unpackbits(packed.view(np.uint8).reshape(rows, words * 4), axis=1,
-                           bitorder="little")
-    bitplane = stream[:, : K * bits].reshape(rows, K, bits)
-    weights = (1 << np.arange(bits)).astype(np.uint8)
-    return (bitplane * weights).sum(axis=2, dtype=np.uint8)
+    unit_bytes = {2: 1, 4: 1, 8: 1, 3: 3, 6: 3, 5: 5}[bits]
+    per_unit = unit_bytes * 8 // bits
+    if K % per_unit:
+        raise ValueError(f"K={K} is not a multiple of {per_unit} codes")
+    stream = packed.view(np.uint8).reshape(rows, words * 4)[:, : K * bits // 8].reshape(rows, -1, unit_bytes)
+    if unit_bytes == 1:
+        unit = stream[:, :, 0]
+    else:
+        unit = np.zeros(stream.shape[:2], dtype=np.uint64)
+        for i in range(unit_bytes):
+            unit |= stream[:, :, i].astype(np.uint64) << np.uint64(8 * i)
+    shifts = (np.arange(per_unit) * bits).astype(unit.dtype)
+    codes = (unit[:, :, None] >> shifts) & unit.dtype.type((1 << bits) - 1)
+    return codes.astype(np.uint8).reshape(rows, K)
 
 
 # --------------------------------------------------------------------------
