@@ -130,7 +130,7 @@ int jq_qgemv_batched_ex(const JqGemvDesc* descs, int count, int64_t M, int act_d
  * across which the next op's weights are already streaming.  x of an op may be any buffer written before
  * the launch or by an op at least two places earlier, or exactly one whole output y_i of the op directly
  * before it (with K == N_i); any other overlap with the previous op's outputs is refused (JQ_EINVAL).
- * Limits: bits 2, 4 or 8; group_size 64 or 128 with K / group_size a multiple of 4; activations, scales,
+ * Limits: bits 2, 4, 6 or 8; group_size 64 or 128 with K / group_size a multiple of 4; activations, scales,
  * biases and outputs all of act_dtype (f16 or bf16); codes 16-byte, scales/biases 8-byte, x 16-byte
  * aligned; an op whose rows would make one CTA touch more than 16 row tiles (about 35 000 rows at K = 4096)
  * is refused with JQ_EUNSUPPORTED: split it by rows.  Weights must not be written while a program that names

@@ -45,8 +45,18 @@ __device__ __forceinline__ void to_bytes(const uint32_t (&u)[Unit<BITS>::WORDS],
     } else if constexpr (BITS == 4) {
         r[0] = u[0] & 0x0F0F0F0Fu; r[1] = u[0] & 0xF0F0F0F0u;
         r[2] = u[1] & 0x0F0F0F0Fu; r[3] = u[1] & 0xF0F0F0F0u;
+    } else if constexpr (BITS == 6) {
+        // 16 codes = 96 bits = four groups of 24 bits (4 codes each).  A group g = c0 | c1 << 6 | c2 << 12 |
+        // c3 << 18 becomes the bytes (c0, c1, c2, c3) in two steps: the upper pair moves to the high half,
+        // then the odd code of each half moves up by two bits.  Bits above the group's 24 fall out in the masks.
+        const uint32_t grp[4] = {u[0], funnel_r(u[0], u[1], 24), funnel_r(u[1], u[2], 16), u[2] >> 8};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t h = (grp[i] & 0x0000FFFFu) | ((grp[i] << 4) & 0xFFFF0000u);
+            r[i] = (h & 0x003F003Fu) | ((h << 2) & 0x3F003F00u);
+        }
     } else {
-        static_assert(BITS == 2, "widths of the integer kernels: 2, 4, 8");
+        static_assert(BITS == 2, "widths of the integer kernels: 2, 4, 6, 8");
         r[0] = u[0] & 0x03030303u; r[1] = u[0] & 0x0C0C0C0Cu;
         r[2] = u[0] & 0x30303030u; r[3] = u[0] & 0xC0C0C0C0u;
     }
@@ -57,32 +67,6 @@ template <int BITS> __host__ __device__ constexpr int elem(int i, int t) {
 // log2 of the factor the code of element j carries inside its byte
 template <int BITS> __host__ __device__ constexpr int code_shift(int j) {
     return BITS == 2 ? 2 * (j & 3) : BITS == 4 ? 4 * (j & 1) : 0;
-}
-
-// Sixteen consecutive activations v[] of one quantization group -> the unit's 16 bytes of the three limb
-// rows (byte order = the order to_bytes leaves the codes in).  `scale` = 2^(21 - E) with E the exponent of
-// the group's largest magnitude, so that |v * scale| < 2^22; element j is further divided by the factor
-// 2^code_shift(j) its code carries.  The limbs are the signed base-256 digits of the rounded value:
-// with u = xi + 0x8080 the bytes of u ^ 0x8080 are the two's-complement digits.
-template <int BITS>
-__device__ __forceinline__ void limbs16(const float (&v)[16], float scale, uint8_t* l0, uint8_t* l1, uint8_t* l2) {
-    uint32_t t[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float sj = scale * (1.f / (float)(1 << code_shift<BITS>(j)));
-        t[j] = ((uint32_t)__float2int_rn(v[j] * sj) + 0x8080u) ^ 0x8080u;
-    }
-    uint8_t* const d[3] = {l0, l1, l2};
-#pragma unroll
-    for (int L = 0; L < 3; ++L) {
-        const uint32_t sel = ((4u + L) << 4) | L;            // byte L of both sources
-        uint32_t wd[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            wd[i] = __byte_perm(__byte_perm(t[elem<BITS>(i, 0)], t[elem<BITS>(i, 1)], sel),
-                                __byte_perm(t[elem<BITS>(i, 2)], t[elem<BITS>(i, 3)], sel), 0x5410);
-        *reinterpret_cast<uint4*>(d[L]) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
-    }
 }
 
 }  // namespace imma_ops

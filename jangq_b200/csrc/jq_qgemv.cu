@@ -389,6 +389,7 @@ static bool force_simple() {
 
 // JANGQ_GEMV_KERNEL selects the fast-path kernel: unset = per-width default, "tc" = tensor-memory
 // kernel wherever the shape fits it, "pint" = persistent integer warp-MMA kernel wherever it fits,
+// "one" = item-streaming integer kernel (one activation row) wherever it fits,
 // "mma" = the warp-MMA kernel of this file.  The parity tests force every kernel with it.
 static int gemv_kernel_choice() {
     const char* e = getenv("JANGQ_GEMV_KERNEL");
@@ -396,6 +397,7 @@ static int gemv_kernel_choice() {
     if (e[0] == 'm') return 1;
     if (e[0] == 't') return 3;
     if (e[0] == 'p') return 4;      // persistent integer warp-MMA kernel wherever the shape fits it
+    if (e[0] == 'o') return 5;      // item-streaming integer kernel (one activation row) wherever the shape fits it
     return 0;
 }
 
@@ -538,7 +540,15 @@ int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, con
         //   4- and 8-bit, M > 2: tensor-memory kernel;
         //   3/6-bit, M > 2 with 2-bit: bf16 warp-MMA kernel.
         const bool narrow = (bits == 2 || bits == 4 || bits == 8) && a.M <= 2;
-        if (fast && (kern == 4 || (kern == 0 && narrow))) {
+        //   one activation row, 2-, 4-, 6- and 8-bit: item-streaming integer kernel.  6-bit 32000x4096: 25.5 us
+        //          against 38 us for the bf16 warp-MMA kernel; on the other widths it ties with the persistent
+        //          kernel (12288x4096 8-bit 11.9 / 11.4 us, 22016x4096 2-bit 11.3 / 11.0 us, 14336x4096 4-bit
+        //          9.8 / 10.2 us; the whole config-2 decode stream 1.105 / 1.108 ms)
+        if (fast && (kern == 5 || (kern == 0 && a.M == 1))) {
+            rc = launch_one_kernel(a, bt, x_dtype, bits, gs, st, &launched);
+            if (rc != JQ_OK) return rc;
+        }
+        if (fast && !launched && (kern == 4 || (kern == 0 && narrow))) {
             rc = launch_pint_kernel(a, bt, x_dtype, bits, gs, st, &launched);
             if (rc != JQ_OK) return rc;
         }

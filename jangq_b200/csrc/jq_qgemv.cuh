@@ -127,6 +127,11 @@ __device__ __forceinline__ void gemv_stage_blocks(const uint32_t* __restrict__ c
 
 constexpr int GEMV_MAX_NBUF = 3;   // deepest per-warp stage pipeline of the warp-MMA kernels
 
+// item-streaming integer warp-MMA kernel (jq_qgemv_one.cu), dense mat-vecs of 2-, 4-, 6- and 8-bit codes with one
+// activation row; same convention
+int launch_one_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
+                      bool* launched);
+
 // persistent integer warp-MMA kernel (jq_qgemv_pint.cu), dense mat-vecs of 2- and 4-bit codes with at most 2
 // activation rows; same convention
 int launch_pint_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,

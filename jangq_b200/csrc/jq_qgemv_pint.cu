@@ -23,8 +23,8 @@
 // codes) plus the raw 2-byte scales and biases, copied by cp.async into a private ring of `nbuf` stages
 // per warp: no register staging, no CTA barrier.  A warp adds the item's result to its own row sums in
 // shared memory; one CTA barrier at the end, then the warps' sums are added and stored.
-#include "jq_imma.cuh"
 #include "jq_qgemv.cuh"
+#include "jq_stream_dev.cuh"
 
 namespace jq {
 
@@ -179,13 +179,21 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
         }
     };
     uint4 xr0, xr1;
-    load_x(warp * 32 + lane, xr0, xr1);
+    if constexpr (M1) {
+        // one activation row: 8 activations per thread (one 16-byte load, requested before the ring is filled)
+        xr0 = tid < K / 8 ? stream::ld_cg16(xs16 + (size_t)tid * 8) : make_uint4(0u, 0u, 0u, 0u);
+        xr1 = xr0;
+    } else {
+        load_x(warp * 32 + lane, xr0, xr1);
+    }
     for (int i = 1; i < nbuf; ++i) {
         issue(it_lt, it_st, i);
         cp_async_commit();
         advance(it_lt, it_st);
     }
-    {
+    if constexpr (M1) {
+        stream::prep_limbs<AT, BITS, GS>(xs16, nullptr, K, limbs, tab, LS, tid, THREADS, true, xr0);
+    } else {
         for (int base = warp * 32; base < units; base += THREADS) {
             const int it = base + lane;
             const bool live = it < units;

@@ -13,7 +13,7 @@ bit width and the group size.
 
 `persistent=True` goes one step further (the reference's hand-fused dispatches,
 dsv41/metal_decode.py:464-497): every run of consecutive groups the streamed
-program takes (one activation row, 2-/4-/8-bit codes) becomes ONE cooperative
+program takes (one activation row, 2-/4-/6-/8-bit codes) becomes ONE cooperative
 launch, jq_qgemv_stream_run, whose op boundaries are grid barriers inside the
 kernel; groups it does not take (other widths) keep their own launch.
 """
@@ -105,7 +105,7 @@ class GemvPlan:
     def _streamable(self, group) -> bool:
         lins = [self.linears[i] for i in group]
         l0 = lins[0]
-        return (len(lins) <= 4 and l0.bits in (2, 4, 8) and l0.group_size in (64, 128) and
+        return (len(lins) <= 4 and l0.bits in (2, 4, 6, 8) and l0.group_size in (64, 128) and
                 l0.in_features % (4 * l0.group_size) == 0 and
                 all(l.bits == l0.bits and l.group_size == l0.group_size and l.in_features == l0.in_features and
                     l.scales.dtype == self.dtype and l.bias is None for l in lins))
@@ -169,7 +169,7 @@ class GemvPlan:
 class StreamProgram:
     """A prepared program of dependent one-row mat-vecs for jq_qgemv_stream_run: `ops` is a list of
     (x [1, K] or [K], [linear, ...], [y, ...]) in execution order; the linears of an op share x, K, the bit
-    width (2, 4 or 8) and the group size.  An op with more rows than one op of a program may have is cut
+    width (2, 4, 6 or 8) and the group size.  An op with more rows than one op of a program may have is cut
     into row ranges (consecutive ops over slices of the same tensors).  The program keeps references to the
     tensors it names; run() enqueues the one launch on the current stream."""
 

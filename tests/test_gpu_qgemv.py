@@ -221,7 +221,7 @@ def test_plan_groups_fuse_and_match_ungrouped():
 
 
 # ---- every fast kernel, selected explicitly ------------------------------------------------------------------
-@pytest.mark.parametrize("kernel", ("tc", "mma", "pint"))
+@pytest.mark.parametrize("kernel", ("tc", "mma", "pint", "one"))
 @pytest.mark.parametrize("bits,N,K,M", ((8, 4096, 4096, 1), (2, 5000, 4096, 1), (4, 300, 11008, 2), (8, 130, 2048, 2),
                                         (2, 96, 512, 1), (4, 4100, 1024, 1), (2, 4096, 11008, 2)))
 def test_each_kernel_against_oracle(monkeypatch, kernel, bits, N, K, M):
@@ -255,7 +255,7 @@ def test_bench_stream_launches_against_oracle(names, N, K, bits):
     _lib.check(_lib.load().jq_device_status())
 
 
-@pytest.mark.parametrize("kernel", ("pint", "tc", "mma"))
+@pytest.mark.parametrize("kernel", ("pint", "tc", "mma", "one"))
 @pytest.mark.parametrize("bits", (2, 4, 8))
 def test_wide_dynamic_range_group(monkeypatch, kernel, bits):
     """One 1e4 outlier among N(0,1) activations in a group: the integer kernels cut the group's activations to
@@ -281,6 +281,43 @@ def test_nonfinite_activation_poisons_only_its_outputs(monkeypatch):
         y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=bits).float().cpu().numpy()
         assert np.all(np.isnan(y[1]))
         assert np.abs(y[0] - ref[0]).max() <= 1e-2 * np.abs(ref[0]).max()
+    # the one-row integer kernel (the default for a single activation row): every output becomes NaN
+    for bits in (2, 4, 6, 8):
+        monkeypatch.setenv("JANGQ_GEMV_KERNEL", "one")
+        x, wq, s, b = make_case(256, 1024, bits, 64, 1, torch.bfloat16, seed=6)
+        x[0, 300] = float("-inf")
+        y = jq.quantized_matmul(x, wq, s, b, group_size=64, bits=bits).float().cpu().numpy()
+        assert np.all(np.isnan(y))
+
+
+@pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (4, 64), (4, 128), (6, 64), (6, 128), (8, 64), (8, 128)))
+def test_one_row_integer_kernel_shapes_and_extremes(monkeypatch, bits, gs):
+    """The item-streaming integer kernel (one activation row): ragged row counts, rows shorter than one
+    256-byte stage, rows whose last stage is short, a fused launch of three matrices, largest codes against
+    largest limbs, f16."""
+    from jangq_b200.ops import qgemv_fused
+    monkeypatch.setenv("JANGQ_GEMV_KERNEL", "one")
+    for N, K in ((333, 2048), (17, 256), (5000, 1280), (40, 11008)):
+        if K % (4 * gs):
+            continue
+        x, wq, s, b = make_case(N, K, bits, gs, 1, torch.bfloat16, seed=bits + gs + N)
+        check(jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits), reference(x, wq, s, b, bits, gs), torch.bfloat16)
+    for dtype in (torch.bfloat16, torch.float16):
+        g = torch.Generator(device="cuda").manual_seed(bits * 131 + gs)
+        w = (torch.rand(333, 2048, device="cuda", generator=g) > 0.2).to(dtype)
+        w[:, ::gs] = 0
+        wq, s, b = jq.quantize(w, group_size=gs, bits=bits)
+        x = torch.full((1, 2048), 1.9921875, device="cuda", dtype=dtype)
+        check(jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits), reference(x, wq, s, b, bits, gs), dtype)
+    lins = [jq.JANGLinear.from_float((torch.randn(n, 1024, device=DEV) * 0.02).to(torch.bfloat16), bits=bits, group_size=gs)
+            for n in (96, 33, 2500)]
+    x = torch.randn(1, 1024, device=DEV).to(torch.bfloat16)
+    outs = [torch.empty((1, l.out_features), dtype=torch.bfloat16, device=DEV) for l in lins]
+    qgemv_fused(x, lins, outs, _lib.JQ_GEMV_STATIC_WEIGHTS)
+    torch.cuda.synchronize()
+    for lin, out in zip(lins, outs):
+        check(out, reference(x, lin.weight, lin.scales, lin.biases, bits, gs), torch.bfloat16)
+    _lib.check(_lib.load().jq_device_status())
 
 
 @pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (4, 64), (4, 128), (8, 64), (8, 128)))

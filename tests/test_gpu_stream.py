@@ -48,7 +48,8 @@ def test_small_program_every_width_and_ragged_shapes(dtype):
     16-row tile, rows shorter than one 256-byte stage, rows whose last stage is short, a fused op of three
     matrices; fewer tiles than SMs (one or two CTAs per tile)."""
     shapes = ((8, 64, 176, 1024), (2, 64, 100, 768), (4, 64, 333, 1280), (2, 128, 64, 2048), (4, 128, 40, 1024),
-              (8, 128, 17, 512), (2, 64, 300, 11008), (8, 64, 1, 256))
+              (8, 128, 17, 512), (2, 64, 300, 11008), (8, 64, 1, 256), (6, 64, 200, 1024), (6, 128, 77, 2048),
+              (6, 64, 50, 1280))
     ops, lins, xs = [], [], []
     for i, (bits, gs, N, K) in enumerate(shapes):
         lin = make_linear(N, K, bits, gs, 10 + i, dtype)
@@ -161,11 +162,12 @@ def test_decoder_layer_shapes_match_separate_launches():
 
 
 def test_plan_with_a_width_the_program_does_not_take():
-    """A 6-bit head after streamable groups: the program covers the run before it, the head keeps its launch."""
-    lins = [make_linear(512, 1024, 8, 64, 601), make_linear(512, 1024, 8, 64, 602), make_linear(1024, 1024, 2, 64, 603),
-            make_linear(2000, 1024, 6, 64, 604)]
+    """A 3-bit matrix between streamable groups: programs cover the runs around it, it keeps its own launch;
+    the 6-bit head rides in the second program."""
+    lins = [make_linear(512, 1024, 8, 64, 601), make_linear(512, 1024, 8, 64, 602), make_linear(1024, 1024, 3, 64, 603),
+            make_linear(5000, 1024, 6, 64, 604)]
     plan = jq.GemvPlan(lins, m=1, device=DEV, groups=[[0, 1], [2], [3]], persistent=True)
-    assert plan.launches_per_run == 2
+    assert plan.launches_per_run == 3
     for k, buf in plan._xbuf.items():
         buf.copy_(rand_x(k, 77))
     plan.capture()
@@ -197,7 +199,7 @@ def test_program_validation():
                                            ctypes.byref(prog), _lib.stream_ptr())
 
     assert prepare([op(x.data_ptr(), y.data_ptr())]) == _lib.JQ_OK
-    assert prepare([op(x.data_ptr(), y.data_ptr(), bits=6)]) == _lib.JQ_EUNSUPPORTED
+    assert prepare([op(x.data_ptr(), y.data_ptr(), bits=3)]) == _lib.JQ_EUNSUPPORTED
     assert prepare([op(x.data_ptr(), y.data_ptr())], nbytes=512) == _lib.JQ_EWORKSPACE
     # the second op reads the middle of the first op's output: refused
     assert prepare([op(x.data_ptr(), y.data_ptr()), op(y.data_ptr() + 32, x.data_ptr(), K=512)]) == _lib.JQ_EINVAL
