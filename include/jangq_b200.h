@@ -335,6 +335,36 @@ int jq_embedding(const int32_t* ids, int64_t T, const uint32_t* codes, const voi
                  int sidecar_dtype, int64_t rows, int64_t K, int bits, int group_size, void* out, int out_dtype,
                  jq_stream_t stream);
 
+/* JANGTQ: rotated codebook weights (jang_tools/turboquant/linear.py:24-200; kernels
+ * jang-runtime/Sources/JANGCoreMetal/JANGTQMatmul.metal:154-363).  Storage per stacked tensor: packed uint32
+ * [E, N, ceil(K / (32 / bits))] holding 32 / bits codebook indices per word, LSB first (3-bit words hold 10 and
+ * leave 2 bits unused: not the affine codec's continuous bitstream); norms float16 [E, N]; one codebook of
+ * 2^bits float32 centroids per (K, bits); bits 2, 3 or 4.  Activations arrive already rotated,
+ * x_rot = H diag(signs) x in float32 (jq_hadamard_rotate with out_dtype JQ_F32), outputs are float32, as in the
+ * reference's kernels.
+ *
+ * jq_tq_gather_matmul (jangtq_gather_tq_matmul, metal:281-363):
+ *     out[p, n] = norms[e, n] * sum_i codebook[idx[e, n, i]] * x_rot[p / x_div, i],   e = rhs_indices[p]
+ *   x_div = 1: every pair has its own activation row (the down projection); x_div = k: the k pairs of a token
+ *   share its row.  rhs_indices NULL: expert 0 for every pair (a plain TurboQuantLinear with E = 1).  Pairs whose
+ *   expert is outside [0, num_experts) get a row of zeros.
+ * jq_tq_fused_gate_up_swiglu (jangtq_fused_gate_up_swiglu, metal:154-262): gate and up of the same expert in one
+ *   pass, out_act[p, n] = silu(min(g, limit)) * clip(u, +-limit) (limit <= 0: no clamp).
+ * jq_tq_quantize (tq_quantize_weight, linear.py:137-178, after the rotation): per row of w_rot [rows, K] float32
+ *   the L2 norm (float16 out, floored at 1e-10 for the division) and for every element the number of
+ *   boundaries (midpoints of neighbouring centroids, 2^bits - 1 floats on the device) its normalised value
+ *   exceeds, packed as above. */
+int jq_tq_gather_matmul(const float* x_rot, int64_t ldx, int x_div, const int32_t* rhs_indices, int64_t pairs,
+                        const uint32_t* packed, const void* norms, const float* codebook, int num_experts,
+                        int64_t N, int64_t K, int bits, float* out, int64_t ldo, jq_stream_t stream);
+int jq_tq_fused_gate_up_swiglu(const float* x_rot, int64_t ldx, int x_div, const int32_t* rhs_indices,
+                               int64_t pairs, const uint32_t* packed_gate, const void* norms_gate,
+                               const uint32_t* packed_up, const void* norms_up, const float* codebook,
+                               int num_experts, int64_t N, int64_t K, int bits, float swiglu_limit,
+                               float* out_act, int64_t ldo, jq_stream_t stream);
+int jq_tq_quantize(const float* w_rot, int64_t rows, int64_t K, int bits, const float* boundaries,
+                   uint32_t* packed, void* norms, jq_stream_t stream);
+
 /* Expert-parallel decode: sum of the ranks' partial expert outputs over NVLink peer memory fused with
  * the residual and the RMS norm that consume it (one launch per layer instead of an all-reduce plus
  * jq_residual_rmsnorm).  The reference runs on one device (its gather_qmm call sites,

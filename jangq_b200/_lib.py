@@ -87,6 +87,10 @@ SIGNATURES = {
     "jq_hadamard_rotate": (C.c_int, [_p, _i32, _i64, _i64, _i64, _p, _p, _i32, _i64, _p]),
     "jq_quantize_imatrix": (C.c_int, [_p, _i32, _p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p]),
     "jq_embedding": (C.c_int, [_p, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _p]),
+    "jq_tq_gather_matmul": (C.c_int, [_p, _i64, _i32, _p, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _p, _i64, _p]),
+    "jq_tq_fused_gate_up_swiglu": (C.c_int, [_p, _i64, _i32, _p, _i64, _p, _p, _p, _p, _p, _i32, _i64, _i64, _i32,
+                                             C.c_float, _p, _i64, _p]),
+    "jq_tq_quantize": (C.c_int, [_p, _i64, _i64, _i32, _p, _p, _p, _p]),
     "jq_ep_buffer_bytes": (C.c_size_t, [_i64, _i64]),
     "jq_ep_combine_residual_rmsnorm": (C.c_int, [_p, _p, _i32, _i64, _i64, C.c_float, _p, _i32, _p, _i32, _i32, _i64,
                                                  _p, _i32, _p]),

@@ -459,3 +459,116 @@ def hadamard_inverse(y: np.ndarray, signs: np.ndarray) -> np.ndarray:
         parts.append(_fwht_f32(y[..., off:off + b]) * signs[off:off + b])
         off += b
     return np.concatenate(parts, axis=-1)
+
+
+# ---- JANGTQ: rotated codebook weights (jang_tools/turboquant/linear.py:24-60,137-200, codebook.py:27-102,
+#      pipeline.py:32-53; kernels jang-runtime/Sources/JANGCoreMetal/JANGTQMatmul.metal:154-363) -------------
+# Storage: packed uint32 [.., out, in / (32 // bits)] holding 32 // bits codebook indices per word, LSB first
+# (3-bit: 10 per word, the top 2 bits unused -- NOT the affine codec's continuous bitstream), one float16 norm
+# per row, one codebook of 2^bits float32 centroids per (in_features, bits), one +-1 sign vector per
+# in_features.  y[out] = norm[out] * sum_i codebook[idx[out, i]] * rot(x)[i],  rot = H * diag(signs).
+# Parity unpinned for everything that runs through MLX in the reference (rotation, norms, index choice);
+# compute_codebook is plain numpy there and is pinned by tests/golden/tq_codebooks.json.
+def tq_codebook(dim: int, bits: int, n_iter: int = 200) -> np.ndarray:
+    """Lloyd-Max centroids for a coordinate of a random unit vector in `dim` dimensions
+    (codebook.py:27-102): density (1 - x^2)^((dim - 3) / 2) on a 10000-point grid over [-1, 1], centroids
+    started uniformly on +-3/sqrt(dim), conditional means by the trapezoid rule until they move < 1e-10."""
+    import math
+    if bits < 1:
+        return np.array([0.0])
+    n = 1 << bits
+    grid = np.linspace(-1.0, 1.0, 10000)
+    if dim <= 2:
+        pdf = np.ones_like(grid) * 0.5
+    else:
+        logc = math.lgamma(dim / 2.0) - 0.5 * math.log(math.pi) - math.lgamma((dim - 1) / 2.0)
+        pdf = np.exp(logc + (dim - 3) / 2.0 * np.log(np.maximum(1.0 - grid ** 2, 1e-30)))
+    trap = getattr(np, "trapezoid", getattr(np, "trapz", None))
+    total = trap(pdf, grid)
+    if total > 0:
+        pdf = pdf / total
+    cent = np.linspace(-3.0 / np.sqrt(max(dim, 1)), 3.0 / np.sqrt(max(dim, 1)), n)
+    for _ in range(n_iter):
+        edges = np.concatenate([[-1.0], (cent[:-1] + cent[1:]) / 2.0, [1.0]])
+        new = np.zeros(n)
+        for i in range(n):
+            m = (grid >= edges[i]) & ((grid <= edges[i + 1]) if i == n - 1 else (grid < edges[i + 1]))
+            if m.sum() <= 1:
+                new[i] = cent[i]
+                continue
+            new[i] = trap(grid[m] * pdf[m], grid[m]) / max(trap(pdf[m], grid[m]), 1e-10)
+        if np.allclose(cent, new, atol=1e-10):
+            break
+        cent = new
+    return np.array(sorted(cent.tolist()))
+
+
+def tq_pack(idx: np.ndarray, bits: int) -> np.ndarray:
+    """[rows, K] indices -> uint32 [rows, K / (32 // bits)] (pipeline.py:32-53; K a multiple of 32 // bits)."""
+    per = 32 // bits
+    rows, K = idx.shape
+    v = idx.astype(np.uint32).reshape(rows, K // per, per)
+    out = np.zeros((rows, K // per), np.uint32)
+    for i in range(per):
+        out |= v[:, :, i] << np.uint32(i * bits)
+    return out
+
+
+def tq_unpack(packed: np.ndarray, bits: int, K: int) -> np.ndarray:
+    per = 32 // bits
+    p = np.asarray(packed, dtype=np.uint32)
+    shifts = (np.arange(per) * bits).astype(np.uint32)
+    idx = (p[..., None] >> shifts) & np.uint32((1 << bits) - 1)
+    return idx.reshape(p.shape[:-1] + (-1,))[..., :K].astype(np.uint8)
+
+
+def tq_quantize(w: np.ndarray, bits: int, seed: int = 42):
+    """(packed, norms float16, codebook float32, signs float32) of a [out, in] matrix
+    (linear.py:137-178): rotate the rows, take their L2 norms (floored at 1e-10), normalise, and count for every
+    element the boundaries (midpoints of neighbouring centroids) it exceeds.  float32 throughout."""
+    w = np.asarray(w, dtype=np.float32)
+    K = w.shape[1]
+    signs = np.random.default_rng(seed).choice([-1.0, 1.0], size=K).astype(np.float32)
+    wr = hadamard_rotate(w, signs)
+    norms = np.sqrt((wr * wr).sum(axis=1, keepdims=True, dtype=np.float32))
+    wn = wr / np.maximum(norms, np.float32(1e-10))
+    cb = tq_codebook(K, bits).astype(np.float32)
+    edges = ((cb[:-1] + cb[1:]) / np.float32(2.0)).astype(np.float32)
+    idx = np.zeros(wn.shape, np.uint8)
+    for e in edges:
+        idx += (wn > e).astype(np.uint8)
+    return tq_pack(idx, bits), norms[:, 0].astype(np.float16), cb, signs
+
+
+def tq_dequantize(packed, norms, codebook, signs, bits: int) -> np.ndarray:
+    """The float32 matrix TurboQuantLinear multiplies by (linear.py:51-56): codebook[idx] * norm, rotated back."""
+    K = signs.shape[0]
+    w = np.asarray(codebook, np.float32)[tq_unpack(packed, bits, K)] * np.asarray(norms, np.float32)[:, None]
+    return hadamard_inverse(w, signs)
+
+
+def tq_matmul_rotated(x_rot, packed, norms, codebook, bits: int) -> np.ndarray:
+    """y[m, out] = norm[out] * sum_i codebook[idx[out, i]] * x_rot[m, i] in float64 (JANGTQMatmul.metal:18-30)."""
+    x_rot = np.atleast_2d(np.asarray(x_rot, np.float64))
+    K = x_rot.shape[1]
+    W = np.asarray(codebook, np.float64)[tq_unpack(packed, bits, K)]
+    return ((x_rot @ W.T) * np.asarray(norms, np.float64)[None, :]).astype(np.float32)
+
+
+def tq_gather_matmul(x_rot, packed, norms, codebook, rhs, bits: int, x_div: int = 1) -> np.ndarray:
+    """out[p] = tq_matmul_rotated(x_rot[p // x_div], expert rhs[p]) (jangtq_gather_tq_matmul, metal:281-363)."""
+    rhs = np.asarray(rhs).reshape(-1)
+    return np.stack([tq_matmul_rotated(x_rot[p // x_div], packed[e], norms[e], codebook, bits)[0]
+                     for p, e in enumerate(rhs)])
+
+
+def tq_fused_gate_up_swiglu(x_rot, packed_g, norms_g, packed_u, norms_u, codebook, rhs, bits: int, topk: int,
+                            swiglu_limit: float = 0.0) -> np.ndarray:
+    """out[t * k + j] = silu(min(g, lim)) * clip(u, +-lim) with g, u the gate / up products of token t and its
+    j-th expert (jangtq_fused_gate_up_swiglu, metal:154-262)."""
+    g = tq_gather_matmul(x_rot, packed_g, norms_g, codebook, rhs, bits, topk).astype(np.float32)
+    u = tq_gather_matmul(x_rot, packed_u, norms_u, codebook, rhs, bits, topk).astype(np.float32)
+    if swiglu_limit > 0:
+        g = np.minimum(g, np.float32(swiglu_limit))
+        u = np.clip(u, -np.float32(swiglu_limit), np.float32(swiglu_limit))
+    return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)

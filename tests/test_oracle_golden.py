@@ -161,3 +161,37 @@ def test_hadamard_rotation_oracle_properties():
         assert np.abs(np.linalg.norm(xr, axis=-1) - np.linalg.norm(x, axis=-1)).max() < 1e-3
         assert np.abs(xr @ wr.T - x @ w.T).max() < 2e-3 * np.abs(x @ w.T).max() + 1e-3      # the rotation cancels
         assert np.abs(jo.hadamard_inverse(xr, s) - x).max() < 1e-4
+
+
+# ---- JANGTQ codebook weights ----------------------------------------------------------------------------------
+def test_tq_codebooks_match_the_reference():
+    """Oracle and package codebooks against centroids the reference's compute_codebook produced
+    (tests/golden/tq_codebooks.json, written by tests/golden/make_golden_tq.py): exact, they are format data."""
+    import json
+    from jangq_b200 import turboquant as tq
+    gold = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tq_codebooks.json")))
+    assert len(gold) == 21
+    for key, want in gold.items():
+        d, b = (int(v) for v in key.split("x"))
+        assert np.array_equal(jo.tq_codebook(d, b), np.array(want)), key
+        assert list(tq.compute_codebook(d, b)) == want, key
+
+
+def test_tq_pack_and_products_agree():
+    """Packing (10 three-bit indices per word), and the two forms of the product: rotated activations against
+    norm * codebook[idx] (the kernels) equals x against the de-rotated matrix (TurboQuantLinear.__call__)."""
+    rng = np.random.default_rng(2)
+    for bits, K in ((2, 256), (3, 320), (4, 192)):
+        idx = rng.integers(0, 1 << bits, (7, K)).astype(np.uint8)
+        p = jo.tq_pack(idx, bits)
+        assert p.shape == (7, K // (32 // bits)) and np.array_equal(jo.tq_unpack(p, bits, K), idx)
+        if bits == 3:
+            assert np.all((p >> np.uint32(30)) == 0)            # the top two bits of a 3-bit word stay empty
+        w = (rng.standard_normal((24, K)) * 0.05).astype(np.float32)
+        packed, norms, cb, signs = jo.tq_quantize(w, bits, seed=7)
+        deq = jo.tq_dequantize(packed, norms, cb, signs, bits)
+        assert np.abs(deq - w).max() < {2: 0.12, 3: 0.07, 4: 0.05}[bits]
+        x = rng.standard_normal((3, K)).astype(np.float32)
+        a = jo.tq_matmul_rotated(jo.hadamard_rotate(x, signs), packed, norms, cb, bits)
+        b = x.astype(np.float64) @ deq.astype(np.float64).T
+        assert np.abs(a - b).max() <= 1e-4 * np.abs(b).max()
