@@ -283,7 +283,7 @@ def run_cuda(args):
 
     linears = build_stack(device)
     plan = jq.GemvPlan(linears, m=1, dtype=torch.bfloat16, device=device, groups=stack_groups(),
-                       persistent=not args.no_persistent)
+                       persistent=args.persistent)
     g = torch.Generator(device=device)
     g.manual_seed(7)
     for buf in plan._xbuf.values():
@@ -343,9 +343,12 @@ def run_cuda(args):
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         per_gpu = value / world
+        # DRAM bytes of one step = sum over the step's five launch shapes of (bytes ncu counted for one launch of
+        # that shape) x (launches of that shape per step); the captures are per kernel, not of this run
         traffic = None
         try:
-            traffic = json.load(open(os.path.join(ROOT, "profiles", "qgemv_traffic.json"))).get("dram_bytes_per_step_scaled")
+            shapes = json.load(open(os.path.join(ROOT, "profiles", "qgemv_one_dram_bytes.json")))["launch_shapes"]
+            traffic = sum(int(v["dram_bytes"]) * int(v["launches_per_step"]) for v in shapes.values())
         except Exception:
             pass
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -355,9 +358,12 @@ def run_cuda(args):
                 "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                              "frac": per_gpu / peak,
                              "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650",
-                             "traffic": traffic, "traffic_note": "bytes per 225-launch step, scaled from two ncu captures in which "
-                             "per-launch DRAM bytes equalled the algorithmic bytes (profiles/bench_launch_list.md)",
-                             "kernel": "qgemv_pint_kernel (225 matrices in 129 launches per step, averaged)"},
+                             "traffic": traffic,
+                             "traffic_note": "ESTIMATED: per step, the sum over the five launch shapes of one captured launch's "
+                             "dram__bytes_read + dram__bytes_write (ncu, per kernel) x launches per step "
+                             "(profiles/qgemv_one_dram_bytes.json); not a capture of this run",
+                             "kernel": ("qgemv_stream_kernel (the step as one persistent launch)" if args.persistent else
+                                        "qgemv_one_kernel (225 matrices in 129 launches per step, averaged)")},
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": plan.h2d_bytes,
                         "d2h_bytes_per_step": plan.d2h_bytes, "ms_per_step": e2e_ms / K},
                 "gpu_launches": plan.launches_per_run * K, "clocks": clk.summary()}
@@ -572,8 +578,9 @@ def main():
     ap.add_argument("--no-moe", action="store_true", help="skip the config-3 MoE decode measurement")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-1 / prefill GEMM / config-4 sweep sub-records")
     ap.add_argument("--quick-extras", action="store_true", help="a reduced config-4 sweep (K=4096, two N)")
-    ap.add_argument("--no-persistent", action="store_true",
-                    help="one launch per group of matrices instead of the one persistent launch per step")
+    ap.add_argument("--persistent", action="store_true",
+                    help="the whole step as one persistent launch (jq_qgemv_stream_run) instead of one launch per group of "
+                         "matrices; measured slower on B200 (1.5 ms against 1.1 ms per step), kept for comparison")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

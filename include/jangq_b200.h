@@ -278,6 +278,21 @@ int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const
                      int bits, int group_size, void* y, void* y2, int64_t ldy, int expert_base, int flags,
                      jq_stream_t stream);
 
+/* The down projection of the routed experts with the SwiGLU in front of it folded in (few pairs): the
+ * reference's second fused decode dispatch, dsv41_moe_dn, reads the activations the first one wrote
+ * (jang_tools/dsv41/metal_decode.py:334-421); here the two gather launches stay and the SwiGLU between them
+ * disappears: y[p, :] = deq(W[pair_expert[p] - expert_base]) . h[p, :] with
+ * h[p, :] = silu(min(g[p, :], limit)) * clip(u[p, :], +-limit) * weights[p], rounded to the activation type --
+ * jq_moe_swiglu followed by jq_gather_qgemv2 with x_div = 1.  gate/up: [pairs, K] of the activation type, leading
+ * dimension ld_in.  Up to 16 pairs of one width (2, 4, 6 or 8 bits, bits_tab NULL) run as one launch and need no
+ * scratch; any other case runs the two launches through h_scratch ([pairs, K], activation type; JQ_EWORKSPACE when
+ * it is needed and NULL). */
+int jq_gather_qgemv_swiglu(const void* gate, const void* up, int act_dtype, int64_t ld_in, const float* weights,
+                           float limit, const int32_t* pair_expert, int64_t pairs, const uint32_t* const* codes_tab,
+                           const void* const* scales_tab, const void* const* biases_tab, const int32_t* bits_tab,
+                           int num_experts, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size,
+                           void* y, int64_t ldy, int expert_base, int flags, void* h_scratch, jq_stream_t stream);
+
 /* Router of the few-token (decode) path, one launch: logits = x . router_w^T (f32 accumulation,
  * rounded to the activation type), softmax over the experts in f32, the k largest scores with ties
  * to the lower expert id (jang_tools/dsv41/metal_decode.py:1141), weights p / (sum p + 1e-20) * scale

@@ -79,6 +79,8 @@ SIGNATURES = {
     "jq_moe_combine_shared": (C.c_int, [_p, _i64, _p, _p, _i64, _i32, _i64, _p, _i64, _p, _i64, _p, _i32, _p]),
     "jq_gather_qgemv2": (C.c_int, [_p, _i32, _i64, _i32, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i64, _i64,
                                    _i32, _i32, _p, _p, _i64, _i32, _i32, _p]),
+    "jq_gather_qgemv_swiglu": (C.c_int, [_p, _p, _i32, _i64, _p, C.c_float, _p, _i64, _p, _p, _p, _p, _i32, _i32, _i64, _i64,
+                                         _i32, _i32, _p, _i64, _i32, _i32, _p, _p]),
     "jq_moe_route": (C.c_int, [_p, _i32, _i64, _i64, _i64, _p, _i32, _i32, _i32, C.c_float, _p, _p, _p, _p, _p]),
     "jq_moe_route_norm": (C.c_int, [_p, _p, _i32, _i64, _i64, C.c_float, _p, _p, _i32, _i32, _i32, C.c_float, _p, _p, _p,
                                     _p, _p]),

@@ -620,7 +620,15 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
     const bool fast = !force_simple() && (gs == 64 || gs == 128) && act_dtype != JQ_F32 && sidecar_dtype == act_dtype &&
                       ((K * bits / 8) % 16 == 0) && aligned(x, 16) && (ldx % 8 == 0) && ((K / gs) % 4 == 0) && bits != 5;
     bool launched = false;
-    if (fast) {
+    // One token's pairs (they share its row, or each has its own): the item-streaming integer kernel, all
+    // matrices in one launch.  Other cases (several tokens, per-expert widths): the bf16 warp-MMA kernel.
+    if (fast && !bits_tab && pairs <= 16 && (x_div == pairs || x_div == 1) && gemv_kernel_choice() != 1) {
+        rc = launch_gather_one(x, nullptr, nullptr, 0.f, ldx, (x_div == 1 && pairs > 1) ? 1 : 0, pair_expert, (int)pairs,
+                               codes_tab2 ? 2 : 1, codes_tab, scales_tab, biases_tab, codes_tab2, scales_tab2, biases_tab2,
+                               num_experts, expert_base, act_dtype, N, K, bits, gs, y, y2, ldy, a.pdl != 0, st, &launched);
+        if (rc != JQ_OK) return rc;
+    }
+    if (fast && !launched) {
         rc = launch_mma_any(a, bt, act_dtype, bits, gs, (int)pairs, st, &launched);
         if (rc != JQ_OK) return rc;
     }
@@ -682,6 +690,39 @@ int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const
     return jq::gather_qgemv_dispatch(x, act_dtype, ldx, x_div, pair_expert, pairs, codes_tab, scales_tab, biases_tab,
                                      bits_tab, num_experts, sidecar_dtype, N, K, bits, group_size, y, ldy,
                                      (cudaStream_t)stream, codes_tab2, scales_tab2, biases_tab2, y2, flags, expert_base);
+}
+
+int jq_gather_qgemv_swiglu(const void* gate, const void* up, int act_dtype, int64_t ld_in, const float* weights,
+                           float limit, const int32_t* pair_expert, int64_t pairs, const uint32_t* const* codes_tab,
+                           const void* const* scales_tab, const void* const* biases_tab, const int32_t* bits_tab,
+                           int num_experts, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y,
+                           int64_t ldy, int expert_base, int flags, void* h_scratch, jq_stream_t stream) {
+    using namespace jq;
+    int rc = check_quant_shape(N, K, bits, group_size);
+    if (rc != JQ_OK) return rc;
+    JQ_REQUIRE(act_dtype == JQ_BF16 || act_dtype == JQ_F16, JQ_EINVAL, "16-bit activations only");
+    JQ_REQUIRE(pairs >= 0 && pairs < 65536, JQ_EINVAL, "fewer than 65536 pairs");
+    if (pairs == 0 || N == 0) return JQ_OK;
+    JQ_REQUIRE(gate && up && pair_expert && codes_tab && scales_tab && biases_tab && y, JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(ld_in >= K && ldy >= N, JQ_EINVAL, "leading dimension too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool fast = (group_size == 64 || group_size == 128) && sidecar_dtype == act_dtype && !bits_tab &&
+                      aligned(gate, 16) && aligned(up, 16) && (ld_in % 8 == 0) && gemv_kernel_choice() != 1;
+    bool launched = false;
+    if (fast && pairs <= 16) {
+        rc = launch_gather_one(gate, up, weights, limit, ld_in, 1, pair_expert, (int)pairs, 1, codes_tab, scales_tab,
+                               biases_tab, nullptr, nullptr, nullptr, num_experts, expert_base, act_dtype, N, K, bits,
+                               group_size, y, nullptr, ldy, (flags & JQ_GEMV_STATIC_WEIGHTS) != 0, st, &launched);
+        if (rc != JQ_OK) return rc;
+    }
+    if (launched) return JQ_OK;
+    JQ_REQUIRE(h_scratch != nullptr, JQ_EWORKSPACE,
+               "this shape takes the two-launch path: pass h_scratch, [pairs, K] of the activation type");
+    rc = jq_moe_swiglu(gate, up, ld_in, weights, nullptr, nullptr, h_scratch, K, K, pairs, limit, act_dtype, stream);
+    if (rc != JQ_OK) return rc;
+    return gather_qgemv_dispatch(h_scratch, act_dtype, K, 1, pair_expert, pairs, codes_tab, scales_tab, biases_tab, bits_tab,
+                                 num_experts, sidecar_dtype, N, K, bits, group_size, y, ldy, st, nullptr, nullptr, nullptr,
+                                 nullptr, flags, expert_base);
 }
 
 int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes, const void* scales,

@@ -28,7 +28,7 @@ struct GemvArgs {
     const void* const* scales_tab2;
     const void* const* biases_tab2;
     void* y2;
-    int ksplit;   // tensor-memory kernel: CTAs of a cluster that split K
+    int ksplit;   // tensor-memory kernel: CTAs of a cluster that split K; one-row kernel: row tiles per CTA
     int* status;  // device status word, set to 1 when a bounded wait ran out (tensor-memory kernel)
 };
 
@@ -131,6 +131,15 @@ constexpr int GEMV_MAX_NBUF = 3;   // deepest per-warp stage pipeline of the war
 // activation row; same convention
 int launch_one_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
                       bool* launched);
+
+// routed-expert gather for one token on the item-streaming integer kernel (jq_qgemv_one.cu): `banks` x `pairs`
+// matrices in one launch, optionally with the activations formed as silu(gate) * up * weight on the fly
+int launch_gather_one(const void* x, const void* up, const float* wts, float limit, int64_t ldx, int x_per_pair,
+                      const int32_t* pair_expert, int pairs, int banks, const uint32_t* const* codes_tab,
+                      const void* const* scales_tab, const void* const* biases_tab, const uint32_t* const* codes_tab2,
+                      const void* const* scales_tab2, const void* const* biases_tab2, int num_experts, int expert_base,
+                      int act_dtype, int64_t N, int64_t K, int bits, int gs, void* y, void* y2, int64_t ldy, bool pdl,
+                      cudaStream_t st, bool* launched);
 
 // persistent integer warp-MMA kernel (jq_qgemv_pint.cu), dense mat-vecs of 2- and 4-bit codes with at most 2
 // activation rows; same convention

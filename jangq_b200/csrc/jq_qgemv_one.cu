@@ -61,7 +61,7 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
         ti.scales = reinterpret_cast<const uint16_t*>(bt.scales[mi]) + row0 * G;
         ti.biases = reinterpret_cast<const uint16_t*>(bt.biases[mi]) + row0 * G;
         ti.rows_valid = (int)min((int64_t)16, bt.N[mi] - row0);
-        ti.pad = 0;
+        ti.xsel = 0;
         tiles[tid] = ti;
     }
     for (int i = tid; i < ZERO_BYTES / 4; i += THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
@@ -93,9 +93,11 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
     request(0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint16_t* xs = reinterpret_cast<const uint16_t*>(a.x);
-    const uint4 xpre = tid < K / 8 ? ld_cg16(xs + (size_t)tid * 8) : make_uint4(0u, 0u, 0u, 0u);
+    PrepSrc src;
+    src.xs = xs; src.have_pre = true;
+    src.pre = tid < K / 8 ? ld_cg16(xs + (size_t)tid * 8) : make_uint4(0u, 0u, 0u, 0u);
     request(1);
-    prep_limbs<AT, BITS, GS>(xs, nullptr, K, limbs, tab, LS, tid, THREADS, true, xpre);
+    prep_limbs<AT, BITS, GS>(src, K, limbs, tab, LS, 0, tid, THREADS);
     __syncthreads();
 
     WarpCtx w;
@@ -170,6 +172,190 @@ static int launch_shape(const GemvArgs& a, GemvBatch bt, cudaStream_t st, bool* 
     return JQ_OK;                                                 // K too long: another kernel
 }
 
+// ---- routed-expert gather for one token (decode): every (token, slot) pair multiplies its own expert ---------
+// One launch covers `banks` x `pairs` matrices of N x K (gate and up of the k routed experts, or their down
+// projections).  Pair p uses expert pair_expert[p] - expert_base of the bank's pointer tables; pairs whose
+// expert belongs to another rank get zero rows.  Activations: one shared row (gate/up of one token), one row
+// per pair (down), or -- SWIGLU -- one row per pair formed on the fly as silu(g) * u * weight from the gate
+// and up products, so that the separate SwiGLU launch between the two gathers disappears.
+struct GatherArgs {
+    const void* x;                    // activation rows, or the gate products when `up` is set
+    const void* up;                   // SwiGLU source: up products [pairs, K]; nullptr otherwise
+    const float* wts;                 // SwiGLU source: routing weight per pair (nullptr: 1)
+    const int32_t* pair_expert;
+    const uint32_t* const* codes_tab[2];
+    const void* const* scales_tab[2];
+    const void* const* biases_tab[2];
+    void* y[2];
+    int64_t ldx, ldy;
+    float limit;
+    int pairs, banks, num_experts, expert_base;
+    int N, K, G;
+    int x_per_pair;                   // 0: every pair reads row 0; 1: pair p reads row p
+    int tpc;                          // 16-row tiles per CTA
+};
+
+__host__ __device__ inline size_t gather_head_bytes(int K, int nx, int nw) {
+    const size_t limbs = ((size_t)nx * 3 * limb_stride(K) + 127) / 128 * 128;
+    return HEAD0 + MAXT * sizeof(TileInfo) + MAXT * sizeof(void*) + 16 + (size_t)nx * (K / 64) * 16 + limbs +
+           (size_t)nw * MAXT * 16 * sizeof(float);
+}
+
+template <typename AT, int BITS, int GS, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+gather_one_kernel(const GatherArgs a) {
+    using A = Act<AT>;
+    constexpr int THREADS = NW * 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = a.K, G = a.G, N = a.N;
+    const int LS = limb_stride(K);
+    constexpr int RB = rowb_of(BITS);
+    const int rowbytes = K * BITS / 8;
+    const int nst = (rowbytes + RB - 1) / RB;
+    const int nx = a.x_per_pair ? a.pairs : 1;
+    const int tpm = (N + 15) / 16;                                   // tiles per matrix
+    const int total = a.banks * a.pairs * tpm;
+
+    uint8_t* zero = smem;
+    TileInfo* tiles = reinterpret_cast<TileInfo*>(smem + HEAD0);                          // [MAXT], live tiles only
+    uint16_t** ytile = reinterpret_cast<uint16_t**>(tiles + MAXT);                        // [MAXT] first output of the tile
+    int* nlive_s = reinterpret_cast<int*>(ytile + MAXT);
+    float2* tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(ytile + MAXT) + 16);   // [nx][K / 64][2]
+    uint8_t* limbs = reinterpret_cast<uint8_t*>(tab) + (size_t)nx * (K / 64) * 16;         // [nx][3][LS]
+    float* ysum = reinterpret_cast<float*>(limbs + ((size_t)nx * 3 * LS + 127) / 128 * 128);
+    uint8_t* ring = smem + gather_head_bytes(K, nx, NW) + (size_t)warp * 2 * SLOT;
+    float* myy = ysum + (size_t)warp * MAXT * 16;
+
+    for (int i = tid; i < ZERO_BYTES / 4; i += THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // the routing decision comes from the launch before: nothing can be requested ahead of it
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int tile0 = (int)blockIdx.x * a.tpc;
+    const int ntile = min(a.tpc, total - tile0);
+    if (warp == 0) {
+        bool live = false;
+        TileInfo ti = {};
+        uint16_t* yp = nullptr;
+        if (lane < ntile) {
+            const int gt = tile0 + lane;
+            const int j = gt / tpm, tm = gt - j * tpm;               // matrix (bank-major), tile inside it
+            const int b = j / a.pairs, p = j - b * a.pairs;
+            const int e = a.pair_expert[p] - a.expert_base;
+            const int row0 = tm * 16;
+            const int rows_valid = min(16, N - row0);
+            yp = reinterpret_cast<uint16_t*>(a.y[b]) + (int64_t)p * a.ldy + row0;
+            if (e >= 0 && e < a.num_experts) {
+                live = true;
+                ti.codes = reinterpret_cast<const uint8_t*>(a.codes_tab[b][e]) + (int64_t)row0 * rowbytes;
+                ti.scales = reinterpret_cast<const uint16_t*>(a.scales_tab[b][e]) + (int64_t)row0 * G;
+                ti.biases = reinterpret_cast<const uint16_t*>(a.biases_tab[b][e]) + (int64_t)row0 * G;
+                ti.rows_valid = rows_valid;
+                ti.xsel = a.x_per_pair ? p : 0;
+            } else {
+                for (int r = 0; r < rows_valid; ++r) yp[r] = 0;     // an expert of another rank: zero rows
+            }
+        }
+        const unsigned mask = __ballot_sync(0xFFFFFFFFu, live);
+        if (live) {
+            const int pos = __popc(mask & ((1u << lane) - 1u));
+            tiles[pos] = ti;
+            ytile[pos] = yp;
+        }
+        if (lane == 0) *nlive_s = __popc(mask);
+    }
+    __syncthreads();
+    const int nlive = *nlive_s;
+    for (int i = lane; i < nlive * 16; i += 32) myy[i] = 0.f;
+
+    OpGeo ge;
+    ge.rowbytes = rowbytes; ge.G = G; ge.rowb = RB; ge.rsb = rsb_of(BITS);
+    ge.grpb = BITS * GS / 8; ge.ngb = 2 * (RB / (BITS * GS / 8)); ge.bits = BITS; ge.gs = GS;
+    const int cnt = nlive * nst;
+    int slot = 0, npre = 0;
+    for (int k = 0; k < 2; ++k) {
+        const int pos = warp + k * NW;
+        if (pos < cnt) {
+            const int lt = pos / nst;
+            issue_item(ring + k * SLOT, tiles[lt], pos - lt * nst, ge, lane);
+            cp_async_commit();
+            npre = k + 1;
+        }
+    }
+    const int xtab_stride = (K / 64) * 2;                               // float2 entries of one activation set
+    {
+        PrepSrc src;
+        src.xs = reinterpret_cast<const uint16_t*>(a.x);
+        src.up = reinterpret_cast<const uint16_t*>(a.up);
+        src.wts = a.up ? a.wts : nullptr;
+        src.limit = a.limit; src.ldx = a.ldx; src.nx = nx;
+        prep_limbs<AT, BITS, GS>(src, K, limbs, tab, LS, xtab_stride, tid, THREADS);
+    }
+    __syncthreads();
+
+    WarpCtx w;
+    w.tl = tiles; w.ge = ge; w.cnt = cnt; w.nst = nst; w.stage0 = 0;
+    w.tl1 = tiles; w.ge1 = ge; w.lt1 = w.st1 = w.lt1b = w.st1b = 0; w.next_n = 0;
+    run_op<AT, BITS, GS, NW, true>(w, ring, limbs, LS, zero, tab, myy, warp, lane, slot, npre, xtab_stride);
+    cp_async_wait<0>();
+    __syncthreads();
+
+    for (int t = tid; t < nlive * 16; t += THREADS) {
+        float part[NW];
+#pragma unroll
+        for (int ww = 0; ww < NW; ++ww) part[ww] = ysum[(size_t)ww * MAXT * 16 + t];
+        float v = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < NW; ++ww) v += part[ww];             // always in warp order
+        if ((t & 15) < tiles[t >> 4].rows_valid) ytile[t >> 4][t & 15] = A::from_f32(v);
+    }
+}
+
+template <typename AT, int BITS, int GS, int NW>
+static int launch_gather_cfg(const GatherArgs& a, int nx, int grid, bool pdl, cudaStream_t st, bool* launched) {
+    const size_t smem = gather_head_bytes(a.K, nx, NW) + (size_t)NW * 2 * SLOT;
+    static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
+    int dev = 0;
+    JQ_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        JQ_CUDA_OK(cudaFuncSetAttribute(gather_one_kernel<AT, BITS, GS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        MAX_SMEM));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, gather_one_kernel<AT, BITS, GS, NW>, a));
+    *launched = true;
+    return JQ_OK;
+}
+
+template <typename AT, int BITS, int GS>
+static int launch_gather_shape(GatherArgs a, bool pdl, cudaStream_t st, bool* launched) {
+    const int sms = sm_count();
+    const int nx = a.x_per_pair ? a.pairs : 1;
+    const int64_t tiles = (int64_t)a.banks * a.pairs * ((a.N + 15) / 16);
+    const int tpc = (int)((tiles + sms - 1) / sms);
+    if (tpc > MAXT) return JQ_OK;
+    a.tpc = tpc;
+    const int grid = (int)((tiles + tpc - 1) / tpc);
+    for (int nw : {16, 12, 8}) {
+        if (gather_head_bytes(a.K, nx, nw) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
+        if (nw == 16) return launch_gather_cfg<AT, BITS, GS, 16>(a, nx, grid, pdl, st, launched);
+        if (nw == 12) return launch_gather_cfg<AT, BITS, GS, 12>(a, nx, grid, pdl, st, launched);
+        return launch_gather_cfg<AT, BITS, GS, 8>(a, nx, grid, pdl, st, launched);
+    }
+    return JQ_OK;
+}
+
 }  // namespace one
 
 // Dense mat-vecs with one activation row (one launch for all matrices of `bt`) on the item-streaming integer
@@ -188,6 +374,42 @@ int launch_one_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int
     JQ_ONE_CASE(2, 64) JQ_ONE_CASE(4, 64) JQ_ONE_CASE(6, 64) JQ_ONE_CASE(8, 64)
     JQ_ONE_CASE(2, 128) JQ_ONE_CASE(4, 128) JQ_ONE_CASE(6, 128) JQ_ONE_CASE(8, 128)
 #undef JQ_ONE_CASE
+    return rc;
+}
+
+}  // namespace jq
+
+namespace jq {
+
+// Routed-expert gather for one token on the item-streaming integer kernel (see GatherArgs); *launched stays false
+// when the shape does not fit (more than 16 pairs, other widths, K / gs not a multiple of 4, too many tiles).
+int launch_gather_one(const void* x, const void* up, const float* wts, float limit, int64_t ldx, int x_per_pair,
+                      const int32_t* pair_expert, int pairs, int banks, const uint32_t* const* codes_tab,
+                      const void* const* scales_tab, const void* const* biases_tab, const uint32_t* const* codes_tab2,
+                      const void* const* scales_tab2, const void* const* biases_tab2, int num_experts, int expert_base,
+                      int act_dtype, int64_t N, int64_t K, int bits, int gs, void* y, void* y2, int64_t ldy, bool pdl,
+                      cudaStream_t st, bool* launched) {
+    *launched = false;
+    if (!(bits == 2 || bits == 4 || bits == 6 || bits == 8) || !(gs == 64 || gs == 128) || K % (4 * gs) != 0 ||
+        pairs < 1 || pairs > 16 || N < 1 || N >= (1 << 24) || K >= (1 << 22))
+        return JQ_OK;
+    one::GatherArgs a = {};
+    a.x = x; a.up = up; a.wts = wts; a.limit = limit; a.ldx = ldx; a.x_per_pair = x_per_pair;
+    a.pair_expert = pair_expert; a.pairs = pairs; a.banks = banks;
+    a.codes_tab[0] = codes_tab; a.scales_tab[0] = scales_tab; a.biases_tab[0] = biases_tab;
+    a.codes_tab[1] = codes_tab2; a.scales_tab[1] = scales_tab2; a.biases_tab[1] = biases_tab2;
+    a.y[0] = y; a.y[1] = y2; a.ldy = ldy;
+    a.num_experts = num_experts; a.expert_base = expert_base;
+    a.N = (int)N; a.K = (int)K; a.G = (int)(K / gs);
+    int rc = JQ_OK;
+#define JQ_GATHER_CASE(B, GSZ)                                                                               \
+    if (bits == B && gs == GSZ) {                                                                            \
+        rc = (act_dtype == JQ_BF16) ? one::launch_gather_shape<__nv_bfloat16, B, GSZ>(a, pdl, st, launched)  \
+                                    : one::launch_gather_shape<__half, B, GSZ>(a, pdl, st, launched);        \
+    }
+    JQ_GATHER_CASE(2, 64) JQ_GATHER_CASE(4, 64) JQ_GATHER_CASE(6, 64) JQ_GATHER_CASE(8, 64)
+    JQ_GATHER_CASE(2, 128) JQ_GATHER_CASE(4, 128) JQ_GATHER_CASE(6, 128) JQ_GATHER_CASE(8, 128)
+#undef JQ_GATHER_CASE
     return rc;
 }
 

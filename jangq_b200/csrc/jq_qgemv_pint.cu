@@ -192,7 +192,9 @@ qgemv_pint_kernel(const GemvArgs a, const GemvBatch bt) {
         advance(it_lt, it_st);
     }
     if constexpr (M1) {
-        stream::prep_limbs<AT, BITS, GS>(xs16, nullptr, K, limbs, tab, LS, tid, THREADS, true, xr0);
+        stream::PrepSrc src;
+        src.xs = xs16; src.have_pre = true; src.pre = xr0;
+        stream::prep_limbs<AT, BITS, GS>(src, K, limbs, tab, LS, 0, tid, THREADS);
     } else {
         for (int base = warp * 32; base < units; base += THREADS) {
             const int it = base + lane;

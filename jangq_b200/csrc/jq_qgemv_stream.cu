@@ -87,15 +87,17 @@ qgemv_stream_kernel(const DevOp* __restrict__ ops, int n_ops, float* __restrict_
             ti.scales = od->scales[mi] + row0 * od->G;
             ti.biases = od->biases[mi] + row0 * od->G;
             ti.rows_valid = (int)min((int64_t)16, (int64_t)od->N[mi] - row0);
-            ti.pad = 0;
+            ti.xsel = 0;
             tiles_s[(j & 1) * MAXT + lane] = ti;
         }
         __syncwarp();
     };
     auto prep = [&](const DevOp& o1, const float* acc) {
         const int nth = THREADS;
+        PrepSrc src;
+        src.xs = o1.x; src.acc = acc;
 #define JQ_STREAM_PREP(B, GSZ) \
-        if (o1.bits == B && o1.gs == GSZ) prep_limbs<AT, B, GSZ>(o1.x, acc, o1.K, limbs, tab, LS, tid, nth);
+        if (o1.bits == B && o1.gs == GSZ) prep_limbs<AT, B, GSZ>(src, o1.K, limbs, tab, LS, 0, tid, nth);
         JQ_STREAM_PREP(2, 64) JQ_STREAM_PREP(4, 64) JQ_STREAM_PREP(6, 64) JQ_STREAM_PREP(8, 64)
         JQ_STREAM_PREP(2, 128) JQ_STREAM_PREP(4, 128) JQ_STREAM_PREP(6, 128) JQ_STREAM_PREP(8, 128)
 #undef JQ_STREAM_PREP

@@ -58,7 +58,7 @@ struct TileInfo {                     // one tile of the CTA's run (32 bytes)
     const uint16_t* scales;
     const uint16_t* biases;
     int rows_valid;
-    int pad;
+    int xsel;                         // which set of activation limbs the tile multiplies (0 for a dense op)
 };
 
 struct OpCtx {                        // this CTA's share of one op, precomputed by the warp that builds the tables
@@ -207,45 +207,61 @@ __device__ __forceinline__ void issue_item(uint8_t* buf, const TileInfo& ti, int
     }
 }
 
-// Activations of an op -> limbs + per-group (e, sum x), by the first `nthreads` threads of the CTA (whole
-// warps).  Source: xs (activation type) or, when acc != nullptr, the previous op's float32 accumulator,
-// rounded to the activation type first (the value the output conversion stores).  A thread takes 8
-// consecutive activations (one 16-byte load), GS / 8 lanes share a quantization group: this step sits on
-// the critical path between two dependent mat-vecs, so it is spread over as many threads as K allows.
-// `pre`: the thread's first 16 bytes of xs (half-unit tid), when the caller requested them ahead of time
-// (have_pre), so that other work overlaps the load.
+// Where the activations of an op come from.
+struct PrepSrc {
+    const uint16_t* xs = nullptr;     // rows of the activation type (or the gate products when `up` is set)
+    const float* acc = nullptr;       // instead of xs: the previous op's float32 accumulator (one row)
+    const uint16_t* up = nullptr;     // SwiGLU source: up products, same layout as xs
+    const float* wts = nullptr;       // SwiGLU source: one routing weight per row (nullptr: 1)
+    float limit = 0.f;                // SwiGLU clamp (<= 0: none)
+    int64_t ldx = 0;                  // elements between rows of xs / up
+    int nx = 1;                       // rows (sets of limbs)
+    bool have_pre = false;            // `pre` holds the thread's first 16 bytes of row 0 (requested ahead of time)
+    uint4 pre = {0u, 0u, 0u, 0u};
+};
+
+// Activations -> limbs + per-group (e, sum x), by the first `nthreads` threads of the CTA (whole warps).
+// Set s of the limbs starts at limbs + s * 3 * LS, its table at tab + s * xtab_stride.  Sources: rows of the
+// activation type; the previous op's float32 accumulator, rounded to the activation type first (the value
+// the output conversion stores); or gate and up products turned into h = silu(g) * u * weight on the fly.
+// A thread takes 8 consecutive activations (one 16-byte load), GS / 8 lanes share a quantization group: this
+// step sits on the critical path between two dependent mat-vecs, so it is spread over as many threads as K
+// allows, and all of a thread's loads go out before its first conversion.
 template <typename AT, int BITS, int GS>
-__device__ __forceinline__ void prep_limbs(const uint16_t* __restrict__ xs, const float* __restrict__ acc, int K,
-                                           uint8_t* limbs, float2* tab, int LS, int tid, int nthreads,
-                                           bool have_pre = false, uint4 pre = make_uint4(0u, 0u, 0u, 0u)) {
+__device__ __forceinline__ void prep_limbs(const PrepSrc& src, int K, uint8_t* limbs, float2* tab, int LS,
+                                           int xtab_stride, int tid, int nthreads) {
     using A = Act<AT>;
     constexpr int LPG = GS / 8;                          // lanes per group: 8 or 16
     const int lane = tid & 31;
-    const int halves = K / 8;                            // a multiple of LPG
-    // all of the thread's loads go out before the first conversion (long rows take several rounds, and a
-    // round-trip to the L2 per round would add up on the critical path)
+    const int halves = K / 8;                            // per row; a multiple of 32 (K is a multiple of 4 GS)
+    const int total = halves * src.nx;
     constexpr int PRE = 4;
     uint4 xq[PRE];
-    if (!acc) {
+    if (!src.acc) {
 #pragma unroll
         for (int i = 0; i < PRE; ++i) {
-            const int H = tid + i * nthreads;
+            const int idx = tid + i * nthreads;
             xq[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (H < halves) xq[i] = (i == 0 && have_pre) ? pre : ld_cg16(xs + (size_t)H * 8);
+            if (idx < total) {
+                const int sx = idx / halves, H = idx - sx * halves;
+                xq[i] = (i == 0 && src.have_pre) ? src.pre : ld_cg16(src.xs + sx * src.ldx + (size_t)H * 8);
+            }
         }
     }
     int round = 0;
-    for (int base = (tid >> 5) * 32; base < halves; base += nthreads, ++round) {
-        const int H = base + lane;                       // half-unit: activations [8 H, 8 H + 8)
-        const bool live = H < halves;
+    for (int base = (tid >> 5) * 32; base < total; base += nthreads, ++round) {
+        const int idx = base + lane;
+        const bool live = idx < total;
+        const int sx = live ? idx / halves : 0;
+        const int H = idx - sx * halves;                 // half-unit of the row: activations [8 H, 8 H + 8)
         float v[8];
         if (!live) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.f;
-        } else if (acc) {
+        } else if (src.acc) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint4 r = ld_cg16(acc + (size_t)H * 8 + h * 4);
+                const uint4 r = ld_cg16(src.acc + (size_t)H * 8 + h * 4);
                 const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) v[h * 4 + j] = A::to_f32(A::from_f32(__uint_as_float(w[j])));
@@ -256,10 +272,26 @@ __device__ __forceinline__ void prep_limbs(const uint16_t* __restrict__ xs, cons
             else if (round == 1) r = xq[1];
             else if (round == 2) r = xq[2];
             else if (round == 3) r = xq[3];
-            else r = ld_cg16(xs + (size_t)H * 8);
+            else r = ld_cg16(src.xs + sx * src.ldx + (size_t)H * 8);
             const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) { v[2 * j] = A::lo_f32(w[j]); v[2 * j + 1] = A::hi_f32(w[j]); }
+            if (src.up) {
+                // xs holds the gate products: h = silu(min(g, limit)) * clip(u, +-limit) * weight, rounded to
+                // the activation type (what a separate SwiGLU launch would store)
+                const uint4 ru = ld_cg16(src.up + sx * src.ldx + (size_t)H * 8);
+                const uint32_t wu[4] = {ru.x, ru.y, ru.z, ru.w};
+                const float wt = src.wts ? src.wts[sx] : 1.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float gv = v[j], uv = (j & 1) ? A::hi_f32(wu[j >> 1]) : A::lo_f32(wu[j >> 1]);
+                    if (src.limit > 0.f) {
+                        gv = fminf(gv, src.limit);
+                        uv = fminf(fmaxf(uv, -src.limit), src.limit);
+                    }
+                    v[j] = A::to_f32(A::from_f32((gv / (1.0f + __expf(-gv))) * uv * wt));
+                }
+            }
         }
         uint32_t amax = 0u;                              // largest magnitude, as bits (NaN/inf sort highest)
         float xsum = 0.f;
@@ -283,11 +315,12 @@ __device__ __forceinline__ void prep_limbs(const uint16_t* __restrict__ xs, cons
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 xi[j] = __float2int_rn(v[j] * (scale * (1.f / (float)(1 << code_shift<BITS>(j)))));
-            uint8_t* u0 = limbs + (size_t)(H >> 1) * 16;
+            uint8_t* u0 = limbs + (size_t)sx * 3 * LS + (size_t)(H >> 1) * 16;
             store_limbs8<BITS == 6 ? 8 : BITS>(u0, u0 + LS, u0 + 2 * LS, H & 1, xi);
             if ((H & (LPG - 1)) == 0) {
-                tab[(H / LPG) * 2] = make_float2(e, 0.f);            // lanes that carry scales: D * e
-                tab[(H / LPG) * 2 + 1] = make_float2(0.f, xsum);     // lanes that carry biases: sum x
+                float2* t = tab + (size_t)sx * xtab_stride + (H / LPG) * 2;
+                t[0] = make_float2(e, 0.f);                          // lanes that carry scales: D * e
+                t[1] = make_float2(0.f, xsum);                       // lanes that carry biases: sum x
             }
         }
     }
@@ -395,10 +428,12 @@ struct WarpCtx {
 // when there is nothing to request), so "all but the newest group" always covers the current item.
 // Behind its last item of the op the warp requests its first two items of the next op, so that both of its
 // slots are in flight while the CTA sits in the op boundary.
-template <typename AT, int BITS, int GS, int NW>
+// XSETS: the tiles name their set of activation limbs (TileInfo::xsel; set s starts at limbs + s * 3 * LS and
+// tab + s * xtab_stride): the routed-expert gather, where every (token, slot) pair may bring its own row.
+template <typename AT, int BITS, int GS, int NW, bool XSETS = false>
 __device__ __forceinline__ void run_op(const WarpCtx& w, uint8_t* ring, const uint8_t* limbs, int LS,
                                        const uint8_t* zero, const float2* tab, float* myy, int warp, int lane, int& slot,
-                                       int& npre) {
+                                       int& npre, int xtab_stride = 0) {
     constexpr int RB = rowb_of(BITS), KT = RB * 8 / BITS, NBLK = KT / 64, NG = KT / GS;
     const int g = lane >> 2, tig = lane & 3;
     const bool bvalid = g < 3;
@@ -451,6 +486,11 @@ __device__ __forceinline__ void run_op(const WarpCtx& w, uint8_t* ring, const ui
         const int nblk = kc * 8 / (BITS * 64);
         const uint8_t* bp = brow + (bvalid ? st * KT : 0);
         const float2* tp = tabm + (size_t)(st * NG) * 2;
+        if constexpr (XSETS) {
+            const int xs_ = w.tl[lt].xsel;
+            if (bvalid) bp += (size_t)xs_ * 3 * LS;
+            tp += (size_t)xs_ * xtab_stride;
+        }
         float a_lo = 0.f, a_hi = 0.f;
         if (nblk == NBLK) compute_item<AT, BITS, GS, true>(buf, bp, tp, nblk, g, tig, a_lo, a_hi);
         else compute_item<AT, BITS, GS, false>(buf, bp, tp, nblk, g, tig, a_lo, a_hi);

@@ -402,10 +402,22 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
         else:
             flags = _lib.JQ_GEMV_STATIC_WEIGHTS if static_weights else 0
             g, u = _gather_qgemv_pair(x, k, idx32, gate, up, flags, expert_base)
-            h = torch.empty((P, I), dtype=x.dtype, device=dev)
-            _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), None, None,
-                                         h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
-            y = _gather_qgemv(h, 1, idx32, down, flags, expert_base)
+            if len(down.distinct_bits) == 1 and down.bits_tab is None:
+                # SwiGLU folded into the down gather (one launch for up to 16 pairs, two through h otherwise)
+                dn = down._sidecars_as(x.dtype)
+                y = torch.empty((P, dn.N), dtype=x.dtype, device=dev)
+                h = torch.empty((P, I), dtype=x.dtype, device=dev)     # only shapes off the one-launch path touch it
+                _lib.check(lib.jq_gather_qgemv_swiglu(g.data_ptr(), u.data_ptr(), dt, g.stride(0), wf.data_ptr(),
+                                                      float(swiglu_limit), idx32.data_ptr(), P, dn.codes_tab.data_ptr(),
+                                                      dn.scales_tab.data_ptr(), dn.biases_tab.data_ptr(), None, dn.E,
+                                                      _lib.dtype_id(dn.sidecar_dtype), dn.N, dn.K, dn.distinct_bits[0],
+                                                      dn.group_size, y.data_ptr(), y.stride(0), expert_base, flags,
+                                                      h.data_ptr(), st))
+            else:
+                h = torch.empty((P, I), dtype=x.dtype, device=dev)
+                _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), wf.data_ptr(), None, None,
+                                             h.data_ptr(), h.stride(0), I, P, float(swiglu_limit), dt, st))
+                y = _gather_qgemv(h, 1, idx32, down, flags, expert_base)
             if return_slots and shared is None:
                 return y        # [T*k, H]: the caller sums the k rows of a token (routing weights already applied)
             # pairs of other ranks' experts were skipped by the kernels and their rows stay zero

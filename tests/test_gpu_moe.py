@@ -479,3 +479,97 @@ def test_route_norm_rejects_in_place_output():
     rc = lib.jq_moe_route_norm(x.data_ptr(), res.data_ptr(), _lib.JQ_BF16, 2, 1024, 1e-3, x.data_ptr(), wr.data_ptr(), 16, 4,
                                1, 1.0, idx.data_ptr(), w.data_ptr(), cnt.data_ptr(), ws.data_ptr(), _lib.stream_ptr())
     assert rc == _lib.JQ_EINVAL and b"must not overlap" in lib.jq_last_error()
+
+
+def _np_swiglu(g, u, w, limit):
+    g = g.astype(np.float32)
+    u = u.astype(np.float32)
+    if limit > 0:
+        g = np.minimum(g, limit)
+        u = np.clip(u, -limit, limit)
+    h = g / (1.0 + np.exp(-g)) * u * w[:, None]
+    return jo.round_to(h, "bf16")
+
+
+@pytest.mark.parametrize("bits,gs,N,K", ((2, 64, 768, 2048), (4, 64, 200, 1024), (6, 64, 334, 1280), (8, 128, 40, 2048),
+                                         (2, 128, 2048, 768), (6, 64, 2048, 768)))
+@pytest.mark.parametrize("P,x_div", ((8, 8), (1, 1), (6, 1), (16, 16)))
+def test_one_token_gather_on_the_item_kernel(bits, gs, N, K, P, x_div, monkeypatch):
+    """Up to 16 pairs of one token (a shared row, or one row per pair) take the item-streaming integer kernel:
+    against the oracle, against the warp-MMA kernel forced by the environment switch, pairs outside the bank
+    written as zero rows, an expert named twice, and the two-bank form."""
+    from jangq_b200.moe import _gather_qgemv, _gather_qgemv_pair
+    E, base = 6, 10
+    a, ref_a = make_bank(E, N, K, bits, gs, seed=31)
+    b, ref_b = make_bank(E, N, K, bits, gs, seed=32)
+    rng = np.random.default_rng(P * 7 + bits)
+    rows = P // x_div
+    x = torch.from_numpy(rng.standard_normal((rows, K)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    pe_np = rng.integers(base, base + E, size=P).astype(np.int32)
+    if P >= 6:
+        pe_np[1], pe_np[4], pe_np[5] = 3, pe_np[0], base + E       # below the bank, a repeat, above the bank
+    pe = torch.from_numpy(pe_np).to(DEV)
+    y = _gather_qgemv(x, x_div, pe, a, 0, base)
+    ya, yb = _gather_qgemv_pair(x, x_div, pe, a, b, 0, base)
+    # same arithmetic, another split of a row's stages over the warps: one output rounding step
+    assert (y.float() - ya.float()).abs().max() <= 2.0 ** -7 * ya.float().abs().max()
+    local = (pe_np >= base) & (pe_np < base + E)
+    lhs = np.arange(P) // x_div
+    for out, ref in ((ya, ref_a), (yb, ref_b)):
+        want = np.zeros((P, N), np.float32)
+        want[local] = jo.gather_qmm(x.float().cpu().numpy(), ref[0], ref[1], ref[2], pe_np[local] - base, bits, gs,
+                                    lhs_indices=lhs[local])
+        close(out.float().cpu().numpy(), want)
+        assert torch.count_nonzero(out[torch.from_numpy(~local).to(DEV)]) == 0
+    monkeypatch.setenv("JANGQ_GEMV_KERNEL", "mma")
+    ym = _gather_qgemv(x, x_div, pe, a, 0, base)
+    monkeypatch.delenv("JANGQ_GEMV_KERNEL")
+    assert (y.float() - ym.float()).abs().max() <= 2.0 ** -6 * ym.float().abs().max()
+    _lib.check(_lib.load().jq_device_status())
+
+
+@pytest.mark.parametrize("bits,N,K", ((2, 2048, 768), (6, 2048, 768), (4, 300, 1024), (8, 64, 512), (3, 256, 512)))
+@pytest.mark.parametrize("P", (1, 8, 16, 24))
+@pytest.mark.parametrize("limit", (0.0, 1.5))
+def test_gather_with_folded_swiglu(bits, N, K, P, limit):
+    """jq_gather_qgemv_swiglu against the oracle's SwiGLU followed by its gather, and against the two library
+    calls it replaces; 3-bit banks and more than 16 pairs take the two-launch route through h_scratch, which
+    is refused when the scratch is missing."""
+    lib = _lib.load()
+    E, base = 5, 3
+    bank, ref = make_bank(E, N, K, bits, 64, seed=41)
+    bank = bank._sidecars_as(torch.bfloat16)
+    rng = np.random.default_rng(P + bits)
+    g = torch.from_numpy(rng.standard_normal((P, K)).astype(np.float32) * 2).to(DEV).to(torch.bfloat16)
+    u = torch.from_numpy(rng.standard_normal((P, K)).astype(np.float32) * 2).to(DEV).to(torch.bfloat16)
+    w = torch.from_numpy(rng.random(P).astype(np.float32) + 0.1).to(DEV)
+    pe_np = rng.integers(base, base + E, size=P).astype(np.int32)
+    if P >= 8:
+        pe_np[2] = 0                                               # not in the bank: a zero row
+    pe = torch.from_numpy(pe_np).to(DEV)
+    y = torch.full((P, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    h = torch.empty((P, K), dtype=torch.bfloat16, device=DEV)
+
+    def call(scratch):
+        return lib.jq_gather_qgemv_swiglu(g.data_ptr(), u.data_ptr(), _lib.JQ_BF16, g.stride(0), w.data_ptr(), limit,
+                                          pe.data_ptr(), P, bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
+                                          bank.biases_tab.data_ptr(), None, E, _lib.JQ_BF16, N, K, bits, 64, y.data_ptr(),
+                                          y.stride(0), base, 0, scratch, _lib.stream_ptr())
+
+    two_launch = bits == 3 or P > 16
+    if two_launch:
+        assert call(None) == _lib.JQ_EWORKSPACE
+    _lib.check(call(h.data_ptr() if two_launch else None))
+    local = (pe_np >= base) & (pe_np < base + E)
+    hn = _np_swiglu(g.float().cpu().numpy(), u.float().cpu().numpy(), w.cpu().numpy(), limit)
+    want = np.zeros((P, N), np.float32)
+    want[local] = jo.gather_qmm(hn[local], ref[0], ref[1], ref[2], pe_np[local] - base, bits, 64)
+    close(y.float().cpu().numpy(), want)
+    assert torch.count_nonzero(y[torch.from_numpy(~local).to(DEV)]) == 0
+    # the two calls it replaces
+    _lib.check(lib.jq_moe_swiglu(g.data_ptr(), u.data_ptr(), g.stride(0), w.data_ptr(), None, None, h.data_ptr(), K, K, P,
+                                 limit, _lib.JQ_BF16, _lib.stream_ptr()))
+    from jangq_b200.moe import _gather_qgemv
+    y2 = _gather_qgemv(h, 1, pe, bank, 0, base)
+    assert (y.float() - y2.float()).abs().max() <= 2.0 ** -6 * y2.float().abs().max()
+    _lib.check(lib.jq_device_status())
