@@ -120,6 +120,19 @@ int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtyp
 int jq_qgemv_batched_ex(const JqGemvDesc* descs, int count, int64_t M, int act_dtype,
                         int sidecar_dtype, int flags, jq_stream_t stream);
 
+/* jq_qgemv_batched_ex for one activation row that does not exist yet: the row is
+ *     x_out = rms_norm(res + sum_{j<k} y[j, :])      (jq_residual_rmsnorm's arithmetic for T = 1, up to the order
+ *                                                     in which the squares are added),
+ * formed inside the mat-vec launch: every CTA builds the row in registers on its way to the integer limbs, and
+ * one CTA stores it at x_out for the residual path.  With k > 1 this is also the unweighted combine of the routed
+ * experts' slot rows, so a decode layer's "combine + residual + norm" launch disappears into the next layer's
+ * q/k/v launch.  res [K], y [k, ldy], x_out [K] of the activation type; every descs[i].x must be x_out and every
+ * descs[i].K the same K <= 4096.  Widths and shapes the one-row kernel does not take run jq_residual_rmsnorm as a
+ * launch of its own first (y rows contiguous then).  x_out must not alias res or y. */
+int jq_qgemv_batched_norm(const void* res, const void* y, int64_t ldy, int k, float eps, void* x_out,
+                          const JqGemvDesc* descs, int count, int act_dtype, int sidecar_dtype, int flags,
+                          jq_stream_t stream);
+
 /* A whole decode step's dependent mat-vecs in ONE persistent launch.  The reference measured its decode
  * as dispatch-bound and fused its dispatches by hand (jang_tools/dsv41/DECODE_DSPARK_METHODS.md:90-128, driver
  * dsv41/metal_decode.py:464-497); on CUDA the same effect needs the boundary between two dependent mat-vecs

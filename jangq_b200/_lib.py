@@ -63,6 +63,7 @@ SIGNATURES = {
     "jq_qgemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_batched": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _p]),
     "jq_qgemv_batched_ex": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _i32, _p]),
+    "jq_qgemv_batched_norm": (C.c_int, [_p, _p, _i64, _i32, C.c_float, _p, C.POINTER(JqGemvDesc), _i32, _i32, _i32, _i32, _p]),
     "jq_qgemv_stream_workspace_bytes": (C.c_size_t, [C.POINTER(JqStreamOp), _i32]),
     "jq_qgemv_stream_prepare": (C.c_int, [C.POINTER(JqStreamOp), _i32, _i32, _p, C.c_size_t, C.POINTER(JqStreamProgram), _p]),
     "jq_qgemv_stream_run": (C.c_int, [C.POINTER(JqStreamProgram), _p]),

@@ -489,8 +489,11 @@ struct GemvItems {
     int64_t N[GEMV_MAX_FUSE], ldy[GEMV_MAX_FUSE];
 };
 
+// ns (optional, M == 1): the activation row does not exist yet; it is rms_norm(ns->res + sum of ns->k rows of ns->y)
+// and belongs at x (== ns->out).  The one-row kernel forms it inside its launch; for any other kernel the norm
+// goes out as its own launch first.
 int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, const GemvItems& it, int sidecar_dtype,
-                         int64_t K, int bits, int gs, int y_dtype, int flags, cudaStream_t st) {
+                         int64_t K, int bits, int gs, int y_dtype, int flags, cudaStream_t st, const NormSrc* ns = nullptr) {
     JQ_REQUIRE(it.count >= 1 && it.count <= GEMV_MAX_FUSE, JQ_EINVAL, "bad item count %d", it.count);
     JQ_REQUIRE(valid_dtype(x_dtype) && valid_dtype(sidecar_dtype) && valid_dtype(y_dtype), JQ_EINVAL, "bad dtype");
     JQ_REQUIRE(M >= 0 && M <= JQ_QGEMV_MAX_M, JQ_EINVAL, "qgemv takes 0 <= M <= %d rows, got %lld", JQ_QGEMV_MAX_M,
@@ -545,7 +548,13 @@ int qgemv_dispatch_items(const void* x, int x_dtype, int64_t M, int64_t ldx, con
         //          kernel (12288x4096 8-bit 11.9 / 11.4 us, 22016x4096 2-bit 11.3 / 11.0 us, 14336x4096 4-bit
         //          9.8 / 10.2 us; the whole config-2 decode stream 1.105 / 1.108 ms)
         if (fast && (kern == 5 || (kern == 0 && a.M == 1))) {
+            if (ns) { a.norm_res = ns->res; a.norm_y = ns->y; a.norm_ldy = ns->ldy; a.norm_k = ns->k; a.norm_eps = ns->eps; }
             rc = launch_one_kernel(a, bt, x_dtype, bits, gs, st, &launched);
+            if (rc != JQ_OK) return rc;
+            a.norm_res = nullptr;
+        }
+        if (ns && !launched) {
+            rc = jq_residual_rmsnorm(ns->res, ns->y, nullptr, ns->k, 1, K, ns->eps, ns->out, x_dtype, (jq_stream_t)st);
             if (rc != JQ_OK) return rc;
         }
         if (fast && !launched && (kern == 4 || (kern == 0 && narrow))) {
@@ -645,7 +654,7 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
 // Fused form of several mat-vecs: consecutive entries that share x, K, the bit width and the group size
 // become one launch (at most GEMV_MAX_FUSE matrices each).
 int qgemv_dispatch_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtype, int sidecar_dtype, int flags,
-                           cudaStream_t st) {
+                           cudaStream_t st, const NormSrc* ns = nullptr) {
     JQ_REQUIRE(count >= 0 && count <= JQ_QGEMV_MAX_BATCH, JQ_EINVAL, "count must be in [0, %d]", JQ_QGEMV_MAX_BATCH);
     JQ_REQUIRE(count == 0 || descs, JQ_EINVAL, "null descriptor table");
     int i = 0;
@@ -662,7 +671,7 @@ int qgemv_dispatch_batched(const JqGemvDesc* descs, int count, int64_t M, int ac
             ++j;
         }
         int rc = qgemv_dispatch_items(d0.x, act_dtype, M, d0.ldx, it, sidecar_dtype, d0.K, d0.bits, d0.group_size,
-                                      act_dtype, flags, st);
+                                      act_dtype, flags, st, i == 0 ? ns : nullptr);
         if (rc != JQ_OK) return rc;
         i = j;
     }
@@ -747,6 +756,26 @@ int jq_qgemv_batched(const JqGemvDesc* descs, int count, int64_t M, int act_dtyp
 int jq_qgemv_batched_ex(const JqGemvDesc* descs, int count, int64_t M, int act_dtype, int sidecar_dtype, int flags,
                         jq_stream_t stream) {
     return jq::qgemv_dispatch_batched(descs, count, M, act_dtype, sidecar_dtype, flags, (cudaStream_t)stream);
+}
+
+int jq_qgemv_batched_norm(const void* res, const void* y, int64_t ldy, int k, float eps, void* x_out,
+                          const JqGemvDesc* descs, int count, int act_dtype, int sidecar_dtype, int flags,
+                          jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(count >= 1 && count <= JQ_QGEMV_MAX_BATCH && descs, JQ_EINVAL, "count must be in [1, %d]", JQ_QGEMV_MAX_BATCH);
+    JQ_REQUIRE(act_dtype == JQ_BF16 || act_dtype == JQ_F16, JQ_EINVAL, "16-bit activations only");
+    JQ_REQUIRE(res && y && x_out && k >= 1, JQ_EINVAL, "null pointer or k < 1");
+    const int64_t K = descs[0].K;
+    JQ_REQUIRE(K > 0 && K <= 4096 && K % 8 == 0 && ldy >= K && ldy % 8 == 0, JQ_EUNSUPPORTED,
+               "rows of at most 4096 elements, a multiple of 8, ldy %% 8 == 0");
+    JQ_REQUIRE(aligned(res, 16) && aligned(y, 16) && aligned(x_out, 16), JQ_EINVAL, "res, y and x_out must be 16-byte aligned");
+    for (int i = 0; i < count; ++i)
+        JQ_REQUIRE(descs[i].x == x_out && descs[i].K == K, JQ_EINVAL, "every entry reads x_out (desc %d does not)", i);
+    JQ_REQUIRE(x_out != res && x_out != y, JQ_EINVAL, "x_out must not overlap res or y (every CTA reads them)");
+    // the separate norm launch (other widths) reads contiguous rows; only the fused read takes a leading dimension
+    JQ_REQUIRE(k == 1 || ldy == K, JQ_EUNSUPPORTED, "y rows must be contiguous (ldy == K) when k > 1");
+    NormSrc ns = {res, y, ldy, k, eps, x_out};
+    return qgemv_dispatch_batched(descs, count, 1, act_dtype, sidecar_dtype, flags, (cudaStream_t)stream, &ns);
 }
 
 int jq_device_status(void) {

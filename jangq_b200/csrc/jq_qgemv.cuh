@@ -29,6 +29,13 @@ struct GemvArgs {
     const void* const* biases_tab2;
     void* y2;
     int ksplit;   // tensor-memory kernel: CTAs of a cluster that split K; one-row kernel: row tiles per CTA
+    // one-row kernel, optional: the activation row is formed in the launch as rms_norm(norm_res + sum of the
+    // norm_k rows of norm_y) (no weight, f32, rounded to the activation type) and CTA 0 writes it to x
+    const void* norm_res;
+    const void* norm_y;
+    int64_t norm_ldy;
+    int norm_k;
+    float norm_eps;
     int* status;  // device status word, set to 1 when a bounded wait ran out (tensor-memory kernel)
 };
 
@@ -131,6 +138,15 @@ constexpr int GEMV_MAX_NBUF = 3;   // deepest per-warp stage pipeline of the war
 // activation row; same convention
 int launch_one_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
                       bool* launched);
+// Where the one activation row of a launch comes from when it is formed inside the launch (GemvArgs::norm_*).
+struct NormSrc {
+    const void* res;
+    const void* y;
+    int64_t ldy;
+    int k;
+    float eps;
+    void* out;
+};
 
 // routed-expert gather for one token on the item-streaming integer kernel (jq_qgemv_one.cu): `banks` x `pairs`
 // matrices in one launch, optionally with the activations formed as silu(gate) * up * weight on the fly

@@ -24,7 +24,7 @@ using namespace stream;
 
 __host__ __device__ inline size_t one_head_bytes(int K, int nw) {
     const size_t limbs = ((size_t)3 * limb_stride(K) + 127) / 128 * 128;
-    return HEAD0 + MAXT * sizeof(TileInfo) + (size_t)(K / 64) * 16 + limbs + (size_t)nw * MAXT * 16 * sizeof(float);
+    return HEAD0 + MAXT * sizeof(TileInfo) + 128 + (size_t)(K / 64) * 16 + limbs + (size_t)nw * MAXT * 16 * sizeof(float);
 }
 
 template <typename AT, int BITS, int GS, int NW>
@@ -42,7 +42,8 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
 
     uint8_t* zero = smem;
     TileInfo* tiles = reinterpret_cast<TileInfo*>(smem + HEAD0);                        // [MAXT]
-    float2* tab = reinterpret_cast<float2*>(tiles + MAXT);                              // [K / 64][2]
+    float* part = reinterpret_cast<float*>(tiles + MAXT);                               // [32] sums of squares per warp
+    float2* tab = reinterpret_cast<float2*>(part + 32);                                 // [K / 64][2]
     uint8_t* limbs = reinterpret_cast<uint8_t*>(tab) + (size_t)(K / 64) * 16;           // [3][LS]
     float* ysum = reinterpret_cast<float*>(limbs + ((size_t)3 * LS + 127) / 128 * 128);  // [NW][MAXT * 16]
     uint8_t* ring = smem + one_head_bytes(K, NW) + (size_t)warp * 2 * SLOT;
@@ -95,8 +96,58 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
     const uint16_t* xs = reinterpret_cast<const uint16_t*>(a.x);
     PrepSrc src;
     src.xs = xs; src.have_pre = true;
-    src.pre = tid < K / 8 ? ld_cg16(xs + (size_t)tid * 8) : make_uint4(0u, 0u, 0u, 0u);
-    request(1);
+    if (a.norm_res == nullptr) {
+        src.pre = tid < K / 8 ? ld_cg16(xs + (size_t)tid * 8) : make_uint4(0u, 0u, 0u, 0u);
+        request(1);
+    } else {
+        // The row is rms_norm(res + sum_j y[j]) (K <= 8 * THREADS: a thread holds its 8 columns in registers
+        // from the loads to the limbs).  Every CTA forms the whole row -- (k + 1) * 2 K bytes out of L2 -- which
+        // costs less than the launch it replaces; CTA 0 stores the row for whoever needs it next.
+        const uint16_t* res = reinterpret_cast<const uint16_t*>(a.norm_res);
+        const uint16_t* ys = reinterpret_cast<const uint16_t*>(a.norm_y);
+        const bool mine = tid < K / 8;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        if (mine) {
+            const uint4 r0 = ld_cg16(res + (size_t)tid * 8);
+            const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { v[2 * j] = A::lo_f32(w0[j]); v[2 * j + 1] = A::hi_f32(w0[j]); }
+            for (int j0 = 0; j0 < a.norm_k; j0 += 4) {           // four rows' loads in flight at a time
+                uint4 rr[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    rr[q] = j0 + q < a.norm_k ? ld_cg16(ys + (size_t)(j0 + q) * a.norm_ldy + (size_t)tid * 8)
+                                              : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {                     // slot order; rows past k add +0
+                    const uint32_t wq[4] = {rr[q].x, rr[q].y, rr[q].z, rr[q].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { v[2 * j] += A::lo_f32(wq[j]); v[2 * j + 1] += A::hi_f32(wq[j]); }
+                }
+            }
+        }
+        request(1);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
+        if (lane == 0) part[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < NW; ++i) tot += part[i];
+        const float rn = rsqrtf(tot / (float)K + a.norm_eps);
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            o[j] = (uint32_t)A::from_f32(v[2 * j] * rn) | ((uint32_t)A::from_f32(v[2 * j + 1] * rn) << 16);
+        src.pre = make_uint4(o[0], o[1], o[2], o[3]);
+        if (blockIdx.x == 0 && mine)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(const_cast<void*>(a.x)) + (size_t)tid * 8) = src.pre;
+    }
     prep_limbs<AT, BITS, GS>(src, K, limbs, tab, LS, 0, tid, THREADS);
     __syncthreads();
 
@@ -165,6 +216,7 @@ static int launch_shape(const GemvArgs& a, GemvBatch bt, cudaStream_t st, bool* 
     if (tpc > MAXT) return JQ_OK;                                 // too many rows for one launch of this kernel
     for (int nw : {16, 12, 8}) {
         if (one_head_bytes((int)a.K, nw) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
+        if (a.norm_res != nullptr && a.K > 8 * 32 * nw) return JQ_OK;     // the row must fit the CTA's registers
         if (nw == 16) return launch_cfg<AT, BITS, GS, 16>(a, bt, tpc, grid, st, launched);
         if (nw == 12) return launch_cfg<AT, BITS, GS, 12>(a, bt, tpc, grid, st, launched);
         return launch_cfg<AT, BITS, GS, 8>(a, bt, tpc, grid, st, launched);

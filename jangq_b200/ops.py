@@ -231,6 +231,31 @@ def qgemv_fused(x2: torch.Tensor, linears, outs, flags: int = 0):
                                        _lib.dtype_id(linears[0].scales.dtype), flags, _lib.stream_ptr(x2.device)))
 
 
+def qgemv_fused_norm(res: torch.Tensor, y: torch.Tensor, k: int, linears, outs, flags: int = 0,
+                     eps: float | None = None) -> torch.Tensor:
+    """x = rms_norm(res + sum of the k rows of y) (one token: res [1, K], y [k, K]) and the mat-vecs of `linears`
+    over x in one launch (jq_qgemv_batched_norm); returns x [1, K]."""
+    lib = _lib.load()
+    n = len(linears)
+    K = res.shape[-1]
+    if res.shape[0] != 1 or tuple(y.shape) != (k, K) or n < 1 or n > _lib.QGEMV_MAX_BATCH:
+        raise JangqError(_lib.JQ_EINVAL, f"qgemv_fused_norm: one token, y [{k}, {K}], 1..{_lib.QGEMV_MAX_BATCH} linears")
+    if eps is None:
+        eps = torch.finfo(res.dtype).eps
+    res, y = res.contiguous(), y.contiguous()
+    x = torch.empty_like(res)
+    descs = (_lib.JqGemvDesc * n)()
+    for d, lin, out in zip(descs, linears, outs):
+        d.x, d.codes, d.scales, d.biases, d.y = (x.data_ptr(), lin.weight.data_ptr(), lin.scales.data_ptr(),
+                                                 lin.biases.data_ptr(), out.data_ptr())
+        d.N, d.K, d.ldx, d.ldy = lin.weight.shape[0], lin.in_features, x.stride(0), out.stride(0)
+        d.bits, d.group_size = lin.bits, lin.group_size
+    _lib.check(lib.jq_qgemv_batched_norm(res.data_ptr(), y.data_ptr(), y.stride(0), k, float(eps), x.data_ptr(), descs, n,
+                                         _lib.dtype_id(res.dtype), _lib.dtype_id(linears[0].scales.dtype), flags,
+                                         _lib.stream_ptr(res.device)))
+    return x
+
+
 def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
                      transpose: bool = True, group_size: int = 64, bits: int = 4,
                      static_weights: bool = False) -> torch.Tensor:

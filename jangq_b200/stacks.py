@@ -91,14 +91,19 @@ class MoEDecodeStack:
         and outside stream capture, the step first checks that the previous one did not time out.  `trace`
         (a list) receives every layer's routing decision (idx, w), for checks against a reference walk;
         `n_layers` stops after the first layers."""
-        from .ops import qgemv_fused
+        from .ops import qgemv_fused, qgemv_fused_norm
         T = x.shape[0]
         if self.world > 1 and not torch.cuda.is_current_stream_capturing():
             self.check_status()
+        pending = None      # (x, slot rows) of a layer whose combine + residual + norm rides in the next q/k/v launch
         for lay in self.layers[:n_layers]:
             if T <= 16:     # q/k/v read the same activations: one fused launch
                 outs = [torch.empty((T, lay[n].out_features), dtype=x.dtype, device=x.device) for n in "qkv"]
-                qgemv_fused(x, [lay[n] for n in "qkv"], outs, 1)
+                if pending is not None:
+                    x = qgemv_fused_norm(pending[0], pending[1], self.k, [lay[n] for n in "qkv"], outs, 1)
+                    pending = None
+                else:
+                    qgemv_fused(x, [lay[n] for n in "qkv"], outs, 1)
                 q = outs[0]
             else:
                 q = lay["q"](x)
@@ -114,7 +119,10 @@ class MoEDecodeStack:
             if self.world == 1 and T * self.k < moe.SORT_THRESHOLD:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], all_local=True, return_slots=True,
                                   static_weights=True)
-                x = moe.residual_rmsnorm(x, y, k=self.k)     # combine + residual + norm in one launch
+                if T == 1 and self.H <= 4096:
+                    pending = (x, y)
+                else:
+                    x = moe.residual_rmsnorm(x, y, k=self.k)     # combine + residual + norm in one launch
                 continue
             if self.world == 1:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True, all_local=True)
@@ -131,6 +139,8 @@ class MoEDecodeStack:
                 y = moe_ep.gathered_tokens(x, idx, w, moe_ep.partial_experts_fn(lay["gate"], lay["up"], lay["down"],
                                                                                 self.base), group=self.group)
             x = moe.residual_rmsnorm(x, y)
+        if pending is not None:
+            x = moe.residual_rmsnorm(pending[0], pending[1], k=self.k)
         return x
 
 

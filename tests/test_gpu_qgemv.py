@@ -358,3 +358,61 @@ def test_modules_loaded_from_a_reference_bundle():
     bank = mods["model.layers.0.mlp.switch_mlp.up_proj"]
     assert isinstance(bank, moe.ExpertBank) and bank.expert_bits == [3] * 4 and (bank.E, bank.N, bank.K) == (4, 16, 128)
     b.close()
+
+
+@pytest.mark.parametrize("bits,K,k,shapes", ((6, 2048, 8, (4096, 512, 512)), (8, 4096, 1, (256,)), (2, 1024, 3, (300, 100)),
+                                             (4, 768, 8, (64,)), (3, 1024, 4, (128, 128)), (8, 2048, 16, (1000,))))
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+def test_row_formed_in_the_launch_as_residual_rmsnorm(bits, K, k, shapes, dtype):
+    """jq_qgemv_batched_norm: x = rms_norm(res + sum of k rows) formed inside the mat-vec launch equals the separate
+    norm launch to one rounding step of the activation type, and the products match the oracle applied to the row
+    the launch stored; 3-bit takes the two-launch route."""
+    from jangq_b200.ops import qgemv_fused_norm
+    from jangq_b200.moe import residual_rmsnorm
+    rng = np.random.default_rng(bits * 100 + k)
+    res = torch.from_numpy(rng.standard_normal((1, K)).astype(np.float32)).to(DEV).to(dtype)
+    y = torch.from_numpy(rng.standard_normal((k, K)).astype(np.float32) * 0.5).to(DEV).to(dtype)
+    lins = []
+    for i, N in enumerate(shapes):
+        _, wq, s, b = make_case(N, K, bits, 64, 1, dtype, seed=400 + i)
+        lin = jq.JANGLinear(K, N, bits, 64, dtype=dtype, device=DEV)
+        lin.weight.copy_(wq); lin.scales.copy_(s); lin.biases.copy_(b)
+        lins.append(lin)
+    outs = [torch.full((1, n), float("nan"), dtype=dtype, device=DEV) for n in shapes]
+    x = qgemv_fused_norm(res, y, k, lins, outs, _lib.JQ_GEMV_STATIC_WEIGHTS)
+    want = residual_rmsnorm(res, y, k=k)
+    torch.cuda.synchronize()
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    assert ((x.float() - want.float()).abs() <= ulp * want.float().abs() + 1e-6).all()
+    v = res.float().cpu().numpy().astype(np.float64) + y.float().cpu().numpy().astype(np.float64).sum(0, keepdims=True)
+    ref_x = v / np.sqrt((v * v).mean() + float(torch.finfo(dtype).eps))
+    assert np.abs(x.float().cpu().numpy() - ref_x).max() <= 2 * ulp * np.abs(ref_x).max()
+    for lin, out in zip(lins, outs):
+        check(out, reference(x, lin.weight, lin.scales, lin.biases, bits, 64), dtype)
+    _lib.check(_lib.load().jq_device_status())
+
+
+def test_row_formed_in_the_launch_validation():
+    lib = _lib.load()
+    K = 1024
+    _, wq, s, b = make_case(64, K, 4, 64, 1, torch.bfloat16)
+    res = torch.zeros((1, K), dtype=torch.bfloat16, device=DEV)
+    y = torch.zeros((2, K), dtype=torch.bfloat16, device=DEV)
+    x = torch.zeros((1, K), dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros((1, 64), dtype=torch.bfloat16, device=DEV)
+    d = (_lib.JqGemvDesc * 1)()
+    d[0].x, d[0].codes, d[0].scales, d[0].biases, d[0].y = x.data_ptr(), wq.data_ptr(), s.data_ptr(), b.data_ptr(), out.data_ptr()
+    d[0].N, d[0].K, d[0].ldx, d[0].ldy, d[0].bits, d[0].group_size = 64, K, K, 64, 4, 64
+
+    def call(xo, yy=y, ldy=K):
+        return lib.jq_qgemv_batched_norm(res.data_ptr(), yy.data_ptr(), ldy, 2, 1e-6, xo, d, 1, _lib.JQ_BF16, _lib.JQ_BF16, 0,
+                                         _lib.stream_ptr())
+
+    assert call(x.data_ptr()) == _lib.JQ_OK
+    assert call(res.data_ptr()) == _lib.JQ_EINVAL            # entries do not read x_out / aliasing
+    d[0].x = res.data_ptr()
+    assert call(res.data_ptr()) == _lib.JQ_EINVAL
+    assert b"must not overlap" in lib.jq_last_error()
+    d[0].x = x.data_ptr()
+    assert call(x.data_ptr(), ldy=K + 8) == _lib.JQ_EUNSUPPORTED
+    torch.cuda.synchronize()
