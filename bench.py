@@ -449,15 +449,21 @@ def run_moe(args, device, world, rank, barrier):
     Tp = 2048
     xp = torch.randn((Tp, stack.H), generator=g, device=device).to(torch.bfloat16)
     nl = min(4, stack.L)
+    layer_fn = stack.prefill_layer
     for l in range(nl):
-        stack.prefill_layer(xp, l)
+        layer_fn(xp, l)
+    if stack.prefill_overflowed():       # a destination got more rows than its slots hold: the exact exchange instead
+        layer_fn = stack.prefill_layer_exact
     barrier()
     ev0.record()
     for _ in range(3):
         for l in range(nl):
-            stack.prefill_layer(xp, l)
+            layer_fn(xp, l)
     ev1.record()
     barrier()
+    exchange = "one GPU" if world == 1 else ("fixed-capacity slots, two equal-split all_to_all_single, no host read-back"
+                                             if layer_fn == stack.prefill_layer and not stack.prefill_overflowed()
+                                             else "exact split sizes (host read-back per layer): slots overflowed")
     tp = torch.tensor([ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tp, op=dist.ReduceOp.MAX)
@@ -466,7 +472,7 @@ def run_moe(args, device, world, rank, barrier):
     prefill = {"tokens_per_gpu": Tp, "ms_per_layer": ms_layer, "tok_s_per_layer": world * Tp / (ms_layer * 1e-3),
                "expert_TFLOPs_per_gpu": flops_layer / (ms_layer * 1e-3) / 1e12,
                "note": "router + sort + gather + gate/up/down grouped GEMMs + SwiGLU + combine of one layer; "
-                       "N>1: all-to-all dispatch/combine of the rank's 2048 tokens (host-synchronised split sizes)"}
+                       "N>1: all-to-all dispatch/combine of the rank's 2048 tokens", "exchange": exchange}
     gbs = stack.bytes_per_token / (ms * 1e-3) / 1e9
     parity = moe_parity(stack, x, xp, device, world, rank) if world > 1 else None
     return {"parity": parity, "prefill": prefill, "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,

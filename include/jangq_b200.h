@@ -317,6 +317,14 @@ int jq_moe_route(const void* x, int act_dtype, int64_t ldx, int64_t T, int64_t H
                  int num_experts, int k, int renorm, float scale, int32_t* idx_out, float* w_out,
                  int32_t* counters, float* logits_ws, jq_stream_t stream);
 
+/* The selection half of the router for many tokens, where the logits come from a GEMM: softmax over the experts
+ * in f32, the k largest scores with ties to the lower expert id, weights p / (sum p + 1e-20) * scale when
+ * renorm != 0, else p * scale (dots3/ops.py:149-162; tie rule of jang_tools/dsv41/metal_decode.py:1141).
+ * logits [T, ld >= num_experts], f32 or a 16-bit type; idx_out int32 [T, k], w_out f32 [T, k]; one warp per
+ * token, one launch.  num_experts <= 1024. */
+int jq_moe_topk(const void* logits, int logits_dtype, int64_t ld, int64_t T, int num_experts, int k, int renorm,
+                float scale, int32_t* idx_out, float* w_out, jq_stream_t stream);
+
 /* jq_moe_route with the residual + RMS norm in front of it folded in: x_out = rms_norm(x + res) (no weight, f32
  * arithmetic, rounded to the activation type; x, res, x_out: [T, H] contiguous, H <= 4096), then the router on
  * x_out.  One launch instead of jq_residual_rmsnorm + jq_moe_route in the synthetic decode stacks.
@@ -392,6 +400,20 @@ int jq_tq_fused_gate_up_swiglu(const float* x_rot, int64_t ldx, int x_div, const
                                float* out_act, int64_t ldo, jq_stream_t stream);
 int jq_tq_quantize(const float* w_rot, int64_t rows, int64_t K, int bits, const float* boundaries,
                    uint32_t* packed, void* norms, jq_stream_t stream);
+
+/* Expert-parallel prefill, dispatch side: the rows of this rank's (token, slot) pairs packed into fixed-capacity
+ * slots per destination rank, ready for ONE equal-split all-to-all (the reference runs on one device; this is the
+ * exchange step in front of its gather_qmm call sites, dots3/ops.py:168-192, when the experts are sharded
+ * E / world per GPU).  send: [world * capacity] slot rows of H * 2 + 16 bytes -- H values of the activation type,
+ * then int32 local expert id (-1: empty slot), float32 routing weight, 8 spare bytes.  Pair p = t * k + j goes to
+ * rank idx[p] / (num_experts / world); slot_of_pair[p] receives its slot (dest * capacity + position) or -1 when
+ * that destination was already full, in which case *overflow (device int32) becomes 1 -- read it after the step
+ * and repeat the step with exact split sizes.  Which slot of its destination a pair gets depends on the launch;
+ * no result does (slot rows are computed independently and added per token in slot order by jq_moe_combine with
+ * inv = slot_of_pair).  counters: world device int32 of scratch.  Two launches, no host read-back. */
+int jq_ep_pack_slots(const void* x, int64_t ldx, const int32_t* idx, const float* w, int64_t T, int k, int64_t H,
+                     int num_experts, int world, int64_t capacity, void* send, int32_t* slot_of_pair,
+                     int32_t* counters, int32_t* overflow, jq_stream_t stream);
 
 /* Expert-parallel decode: sum of the ranks' partial expert outputs over NVLink peer memory fused with
  * the residual and the RMS norm that consume it (one launch per layer instead of an all-reduce plus

@@ -63,6 +63,7 @@ SIGNATURES = {
     "jq_qgemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),
     "jq_qgemv_batched": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _p]),
     "jq_qgemv_batched_ex": (C.c_int, [C.POINTER(JqGemvDesc), _i32, _i64, _i32, _i32, _i32, _p]),
+    "jq_ep_pack_slots": (C.c_int, [_p, _i64, _p, _p, _i64, _i32, _i64, _i32, _i32, _i64, _p, _p, _p, _p, _p]),
     "jq_qgemv_batched_norm": (C.c_int, [_p, _p, _i64, _i32, C.c_float, _p, C.POINTER(JqGemvDesc), _i32, _i32, _i32, _i32, _p]),
     "jq_qgemv_stream_workspace_bytes": (C.c_size_t, [C.POINTER(JqStreamOp), _i32]),
     "jq_qgemv_stream_prepare": (C.c_int, [C.POINTER(JqStreamOp), _i32, _i32, _p, C.c_size_t, C.POINTER(JqStreamProgram), _p]),
@@ -82,6 +83,7 @@ SIGNATURES = {
                                    _i32, _i32, _p, _p, _i64, _i32, _i32, _p]),
     "jq_gather_qgemv_swiglu": (C.c_int, [_p, _p, _i32, _i64, _p, C.c_float, _p, _i64, _p, _p, _p, _p, _i32, _i32, _i64, _i64,
                                          _i32, _i32, _p, _i64, _i32, _i32, _p, _p]),
+    "jq_moe_topk": (C.c_int, [_p, _i32, _i64, _i64, _i32, _i32, _i32, C.c_float, _p, _p, _p]),
     "jq_moe_route": (C.c_int, [_p, _i32, _i64, _i64, _i64, _p, _i32, _i32, _i32, C.c_float, _p, _p, _p, _p, _p]),
     "jq_moe_route_norm": (C.c_int, [_p, _p, _i32, _i64, _i64, C.c_float, _p, _p, _i32, _i32, _i32, C.c_float, _p, _p, _p,
                                     _p, _p]),

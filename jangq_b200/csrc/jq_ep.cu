@@ -134,9 +134,75 @@ ep_combine_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, in
     }
 }
 
+// ---- sharded-token dispatch: rows into fixed-capacity slots per destination rank ------------------------------
+// Slot row layout (row_bytes = H * 2 + 16): the H activation values, then int32 local expert id (-1: empty slot),
+// float32 routing weight, 8 spare bytes.  ep_fill marks every slot empty and clears the per-destination
+// counters; ep_pack gives pair p (token p / k, slot p % k) the next free slot of its destination rank
+// (an atomic counter: the order of the slots inside a destination is whatever the launch makes it, which no
+// result depends on -- every slot row is computed on its own and each token adds its k slots in slot order) and
+// copies the row there; a pair that finds its destination full sets the overflow word and gets slot -1.
+__global__ void ep_fill_kernel(uint8_t* __restrict__ send, int64_t row_bytes, int64_t slots, int H2,
+                               int32_t* __restrict__ counters, int world, int32_t* __restrict__ overflow) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < slots) *reinterpret_cast<int32_t*>(send + i * row_bytes + H2) = -1;
+    if (i < world) counters[i] = 0;
+    if (i == 0) *overflow = 0;
+}
+
+__global__ void __launch_bounds__(256)
+ep_pack_kernel(const uint8_t* __restrict__ x, int64_t x_row_bytes, const int32_t* __restrict__ idx,
+               const float* __restrict__ w, int64_t P, int k, int H2, int e_local, int world, int cap,
+               uint8_t* __restrict__ send, int64_t row_bytes, int32_t* __restrict__ counters,
+               int32_t* __restrict__ slot_of_pair, int32_t* __restrict__ overflow) {
+    const int lane = threadIdx.x & 31;
+    const int64_t p = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;      // one warp per pair
+    if (p >= P) return;
+    const int e = idx[p];
+    int dest = e / e_local;
+    dest = dest < 0 ? 0 : (dest >= world ? world - 1 : dest);
+    int s = 0;
+    if (lane == 0) {
+        s = atomicAdd(counters + dest, 1);
+        if (s >= cap) { atomicExch(overflow, 1); s = -1; }
+        slot_of_pair[p] = s < 0 ? -1 : dest * cap + s;
+    }
+    s = __shfl_sync(0xFFFFFFFFu, s, 0);
+    if (s < 0) return;
+    uint8_t* dst = send + ((int64_t)dest * cap + s) * row_bytes;
+    const uint8_t* src = x + (p / k) * x_row_bytes;
+    for (int c = lane * 16; c < H2; c += 512) *reinterpret_cast<uint4*>(dst + c) = __ldg(reinterpret_cast<const uint4*>(src + c));
+    if (lane == 0) {
+        *reinterpret_cast<int32_t*>(dst + H2) = e - dest * e_local;
+        *reinterpret_cast<float*>(dst + H2 + 4) = w[p];
+    }
+}
+
 }  // namespace jq
 
 extern "C" {
+
+int jq_ep_pack_slots(const void* x, int64_t ldx, const int32_t* idx, const float* w, int64_t T, int k, int64_t H,
+                     int num_experts, int world, int64_t capacity, void* send, int32_t* slot_of_pair,
+                     int32_t* counters, int32_t* overflow, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(T >= 0 && k >= 1 && H > 0 && H % 8 == 0 && ldx >= H && ldx % 8 == 0, JQ_EINVAL,
+               "rows of a multiple of 8 16-bit values");
+    JQ_REQUIRE(world >= 1 && num_experts >= world && num_experts % world == 0, JQ_EINVAL, "experts must shard evenly");
+    JQ_REQUIRE(capacity >= 1 && capacity * world < (1ll << 31) && T * k < (1ll << 31), JQ_EINVAL, "bad capacity");
+    JQ_REQUIRE(send && slot_of_pair && counters && overflow && (T == 0 || (x && idx && w)), JQ_EINVAL, "null pointer");
+    JQ_REQUIRE(aligned(x, 16) && aligned(send, 16), JQ_EINVAL, "x and the send buffer must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t slots = capacity * world, row_bytes = H * 2 + 16, P = T * k;
+    ep_fill_kernel<<<(unsigned)((slots + 255) / 256), 256, 0, st>>>((uint8_t*)send, row_bytes, slots, (int)(H * 2), counters,
+                                                                    world, overflow);
+    int rc = check_launch("ep_fill");
+    if (rc != JQ_OK || P == 0) return rc;
+    ep_pack_kernel<<<(unsigned)((P * 32 + 255) / 256), 256, 0, st>>>((const uint8_t*)x, ldx * 2, idx, w, P, k, (int)(H * 2),
+                                                                     num_experts / world, world, (int)capacity,
+                                                                     (uint8_t*)send, row_bytes, counters, slot_of_pair,
+                                                                     overflow);
+    return check_launch("ep_pack");
+}
 
 size_t jq_ep_buffer_bytes(int64_t tcap, int64_t H) {
     if (tcap <= 0 || H <= 0) return 0;

@@ -328,6 +328,70 @@ route_kernel(const AT* __restrict__ x, int64_t ldx, const AT* __restrict__ wr, i
     for (int j = lane; j < k; j += 32) w_out[(int64_t)t * k + j] *= norm;
 }
 
+// Router for many tokens (prefill): the logits come from a GEMM; one warp per token turns its row of logits
+// (f32, or the activation type) into the softmax over the experts in f32, the k largest scores (ties to the
+// lower id) and w = p / (sum p + 1e-20) * scale -- route_kernel's selection, one launch instead of the five or
+// six of an eager softmax / top-k / normalise chain.  E <= 1024: a lane holds up to 32 logits in registers.
+template <typename LT>
+__global__ void __launch_bounds__(256)
+topk_rows_kernel(const LT* __restrict__ logits, int64_t ld, int T, int E, int k, int renorm, float scale,
+                 int32_t* __restrict__ idx_out, float* __restrict__ w_out) {
+    const int lane = threadIdx.x & 31;
+    const int t = (int)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    if (t >= T) return;
+    constexpr int PER = ROUTE_MAX_E / 32;
+    float p[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = lane + 32 * i;
+        p[i] = -INFINITY;
+        if (e < E) {
+            if constexpr (sizeof(LT) == 4) p[i] = (float)logits[(int64_t)t * ld + e];
+            else p[i] = Elt<LT>::to_f32(logits[(int64_t)t * ld + e]);
+            mx = fmaxf(mx, p[i]);
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = lane + 32 * i;
+        p[i] = e < E ? __expf(p[i] - mx) : -1.f;
+        if (e < E) sum += p[i];
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+    const float inv_sum = 1.0f / sum;
+    float top_sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+        float bv = -1.f;
+        int bi = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (p[i] > bv) { bv = p[i]; bi = lane + 32 * i; }       // ascending ids: the first maximum is the lowest id
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, d);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, d);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (bi == lane + 32 * i) p[i] = -1.f;                   // taken
+        const float pv = bv * inv_sum;
+        top_sum += pv;
+        if (lane == 0) {
+            idx_out[(int64_t)t * k + j] = bi;
+            w_out[(int64_t)t * k + j] = pv;                         // raw p: normalised below
+        }
+    }
+    __syncwarp();
+    const float norm = renorm ? scale / (top_sum + 1e-20f) : scale;
+    for (int j = lane; j < k; j += 32) w_out[(int64_t)t * k + j] *= norm;
+}
+
 // out[t, :] = rms_norm(x[t, :] + sum_j y[t*k + j, :]) without weight, in f32: v / sqrt(mean(v^2) + eps), rounded
 // to the activation type; the k rows are added in slot order (k = 1: a plain residual).  Glue of the
 // synthetic decode stacks (residual + norm between the quantized blocks; with k > 1 also the unweighted
@@ -423,6 +487,29 @@ int jq_moe_route_norm(const void* x, const void* res, int act_dtype, int64_t T, 
                               (const AT*)router_w, (int)H, num_experts, k, renorm, scale, idx_out, w_out, logits_ws,
                               (int*)counters, (const AT*)res, eps, (AT*)x_out)))
     return JQ_OK;
+}
+
+int jq_moe_topk(const void* logits, int logits_dtype, int64_t ld, int64_t T, int num_experts, int k, int renorm, float scale,
+                int32_t* idx_out, float* w_out, jq_stream_t stream) {
+    using namespace jq;
+    JQ_REQUIRE(num_experts > 0 && num_experts <= ROUTE_MAX_E, JQ_EUNSUPPORTED, "jq_moe_topk takes at most %d experts", ROUTE_MAX_E);
+    JQ_REQUIRE(k > 0 && k <= num_experts && T >= 0 && ld >= num_experts, JQ_EINVAL, "k in [1, num_experts], ld >= num_experts");
+    JQ_REQUIRE(T < (1ll << 26), JQ_EUNSUPPORTED, "too many rows");
+    if (T == 0) return JQ_OK;
+    JQ_REQUIRE(logits && idx_out && w_out, JQ_EINVAL, "null pointer");
+    const unsigned blocks = (unsigned)((T * 32 + 255) / 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (logits_dtype == JQ_F32)
+        topk_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)logits, ld, (int)T, num_experts, k, renorm, scale, idx_out, w_out);
+    else if (logits_dtype == JQ_BF16)
+        topk_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, (int)T, num_experts, k, renorm,
+                                                               scale, idx_out, w_out);
+    else if (logits_dtype == JQ_F16)
+        topk_rows_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)logits, ld, (int)T, num_experts, k, renorm, scale, idx_out,
+                                                        w_out);
+    else
+        return fail(JQ_EINVAL, "logits must be f32, f16 or bf16");
+    return check_launch("moe_topk");
 }
 
 int jq_residual_rmsnorm(const void* x, const void* y, const float* y_f32, int k, int64_t T, int64_t H, float eps, void* out,

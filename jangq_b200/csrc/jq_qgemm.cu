@@ -32,7 +32,7 @@ namespace jq {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_SA = 3;     // activation stages
+constexpr int GEMM_SMEM = 227 * 1024;   // dynamic shared memory of one CTA
 constexpr int GEMM_SB = 2;     // dequantized-weight stages
 
 struct GemmArgs {
@@ -135,22 +135,52 @@ __device__ __forceinline__ uint4 dequant_chunk(const uint32_t (&u)[2 * BITS], ui
                       dequant_pair<AT, BITS, 8 * C + 6>(u, sp2, b2, s, bias));
 }
 
-template <typename AT, int BITS, int BN, int DPR>
+// Code staging of one CTA: k-blocks per stage, bytes per row and stage, row pitch.  With two row tiles per CTA
+// the activation stages take twice the room, so the code stages shrink: rows of 128 bytes lose their padding
+// (their 16-byte chunks are XOR-swizzled by the row instead) and the wide odd widths stage fewer k-blocks.
+// Rows of 128 bytes are not padded there: their 16-byte chunks are XOR-swizzled by the row instead, so that the
+// eight rows a quarter-warp reads together fall into eight different 16-byte bank groups.
+// Measured on 4096x14336x4096 (B200, 4-bit): three activation stages with these code stages run at 961 TFLOP/s;
+// halving the code stages to make room for a fourth activation stage runs at 830 -- the pace is set by the
+// dequantizer warps and their per-stage synchronisation, not by the depth of the TMA pipeline; two threads per
+// weight row (twice the dequantizer warps) run at 840.
+template <int BITS, int BN, int MT> struct CodeStage {
+    static constexpr int CKB = MT == 1 ? (BITS == 2 ? 8 : (BITS == 8 ? 2 : 4))
+                                       : (BITS == 2 ? 8 : (BITS == 3 || BITS == 4) ? 4 : 2);
+    static constexpr int RB = CKB * 8 * BITS;
+    static constexpr bool SWZ = MT == 2 && RB == 128;
+    static constexpr int RBP = SWZ ? RB : RB + 16;
+    static constexpr int SA = 3;                                    // activation stages
+    static constexpr size_t SMEM = 1024 + 256 + (size_t)SA * MT * GEMM_BM * GEMM_BK * 2 + GEMM_SB * BN * GEMM_BK * 2 +
+                                   2 * BN * RBP;
+};
+
+// MT: 128-row tiles of the activations per CTA (1 or 2).  With 2 every dequantized weight tile feeds two
+// accumulators (2 x BN columns of tensor memory), which halves the dequantizer work per flop: the kernel is
+// bound by the dequantizer warps, not by the tensor pipe, with one.
+template <typename AT, int BITS, int BN, int DPR, int MT>
 __global__ void __launch_bounds__(64 + BN * DPR)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     using A = Act<AT>;
+    using CS = CodeStage<BITS, BN, MT>;
+    constexpr int GEMM_SA = CS::SA;
     constexpr int NDW = BN / 32 * DPR;                  // dequantizer warps (DPR threads share a weight row)
     constexpr int NDT = NDW * 32;
-    constexpr int A_STAGE = GEMM_BM * GEMM_BK * 2;      // 16 KB
+    constexpr int A_TILE = GEMM_BM * GEMM_BK * 2;       // 16 KB
+    constexpr int A_STAGE = MT * A_TILE;
     constexpr int B_STAGE = BN * GEMM_BK * 2;
     constexpr int UW = 2 * BITS;                        // words of one row's 64 codes
     // packed codes are staged through shared memory, CKB k-blocks at a time, so that the global
     // reads are coalesced 16-byte chunks (8+ lanes per row) instead of one sector per thread
-    constexpr int CKB = BITS == 2 ? 8 : (BITS == 8 ? 2 : 4);
-    constexpr int RB = CKB * 8 * BITS;                  // bytes per row and code stage (96..192)
-    constexpr int RBP = RB + 16;                        // padded pitch: conflict-free row reads
+    constexpr int CKB = CS::CKB;
+    constexpr int RB = CS::RB;                          // bytes per row and code stage (80..192)
+    constexpr int RBP = CS::RBP;                        // padded pitch (or swizzled chunks): conflict-free row reads
+    constexpr bool SWZ = CS::SWZ;
     constexpr int CPR = RB / 16;                        // 16-byte chunks per row
     constexpr int C_STAGE = BN * RBP;
+    static_assert(MT * BN <= 512, "tensor memory holds 512 columns");
+    // swizzle of a staged 128-byte code row (8 chunks): by the row
+    auto swz_of = [](int row) { return row & 7; };
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // the dynamic shared-memory base is only guaranteed 16-byte aligned: realign to 1024
@@ -168,7 +198,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t n0 = (int64_t)blockIdx.x * BN;
-    int64_t m0 = (int64_t)blockIdx.y * GEMM_BM, m_end = a.M;
+    int64_t m0 = (int64_t)blockIdx.y * (GEMM_BM * MT), m_end = a.M;
     const uint32_t* codes_g = a.codes;
     const void* scales_g = a.scales;
     const void* biases_g = a.biases;
@@ -191,7 +221,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         mbar_init(accfull, 1);
         mbar_fence_init();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    if (warp == 1) tmem_alloc(tmem_slot, MT * BN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -206,7 +236,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                 if (kb >= GEMM_SA) ok = mbar_wait(xempty + s, (uint32_t)((kb / GEMM_SA) - 1) & 1u, 1u << 18);
                 if (!ok) break;
                 mbar_expect_tx(xfull + s, A_STAGE);
-                tma_load_2d(sA + s * A_STAGE, &xmap, kb * GEMM_BK, (int)m0, xfull + s);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)      // rows past M read as zeros
+                    tma_load_2d(sA + s * A_STAGE + mt * A_TILE, &xmap, kb * GEMM_BK, (int)m0 + mt * GEMM_BM, xfull + s);
             }
         }
     } else if (warp == 1) {
@@ -222,8 +254,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                 const uint32_t a_addr = smem_u32(sA + s * A_STAGE), b_addr = smem_u32(sB + t * B_STAGE);
 #pragma unroll
                 for (int k = 0; k < GEMM_BK / 16; ++k)
-                    umma_f16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+                        umma_f16(tmem_base + (uint32_t)(mt * BN), umma_desc_sw128(a_addr + mt * A_TILE + k * 32),
+                                 umma_desc_sw128(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                 umma_commit(xempty + s);
                 umma_commit(bempty + t);
             }
@@ -254,7 +288,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                 for (int c = dt; c < BN * CPR; c += NDT) {
                     const int row = c / CPR, col = c - row * CPR;
                     if (col * 16 < rem)
-                        cp_async16(dstb + row * RBP + col * 16,
+                        cp_async16(dstb + row * RBP + (SWZ ? (col ^ swz_of(row)) : col) * 16,
                                    cbytes + min(n0 + row, a.N - 1) * rowbytes + off + col * 16);
                 }
             }
@@ -329,10 +363,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                 uint32_t cur[UW];
                 if constexpr (DPR == 1) {
                     if constexpr ((8 * BITS) % 16 == 0) {
-                        const uint4* cp = reinterpret_cast<const uint4*>(crow + kbi * 8 * BITS);
+                        const uint4* cp = reinterpret_cast<const uint4*>(crow + (SWZ ? 0 : kbi * 8 * BITS));
 #pragma unroll
                         for (int i = 0; i < UW / 4; ++i) {
-                            const uint4 v = cp[i];
+                            const uint4 v = SWZ ? cp[(kbi * (UW / 4) + i) ^ swz_of(r)] : cp[i];
                             cur[4 * i] = v.x; cur[4 * i + 1] = v.y; cur[4 * i + 2] = v.z; cur[4 * i + 3] = v.w;
                         }
                     } else {
@@ -345,15 +379,19 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                     }
                 } else {
                     // this thread's 32 codes are BITS whole words; the other half stays zero
-                    const uint32_t* cp = reinterpret_cast<const uint32_t*>(crow + kbi * 8 * BITS) + half * BITS;
+                    auto cword = [&](int off) {      // word at byte `off` of the staged row
+                        const int phys = SWZ ? ((((off >> 4) ^ swz_of(r)) << 4) | (off & 15)) : off;
+                        return *reinterpret_cast<const uint32_t*>(crow + phys);
+                    };
+                    const int off0 = kbi * 8 * BITS + half * BITS * 4;
 #pragma unroll
                     for (int i = 0; i < UW; ++i) cur[i] = 0u;
                     if (half == 0) {
 #pragma unroll
-                        for (int i = 0; i < BITS; ++i) cur[i] = cp[i];
+                        for (int i = 0; i < BITS; ++i) cur[i] = cword(off0 + 4 * i);
                     } else {
 #pragma unroll
-                        for (int i = 0; i < BITS; ++i) cur[BITS + i] = cp[i];
+                        for (int i = 0; i < BITS; ++i) cur[BITS + i] = cword(off0 + 4 * i);
                     }
                 }
                 if (sc_vec) {
@@ -410,12 +448,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
             const int q = warp & 3;                               // TMEM lane quarter this warp may read
             const int part = (warp - 2) / 4;                      // the NDW/4 warps of a quarter split the columns
             constexpr int COLS_PER_WARP = BN / (NDW / 4);
-            const int64_t m = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int mt = 0; mt < MT; ++mt) {
+            const int64_t m = m0 + mt * GEMM_BM + q * 32 + lane;
             uint16_t* yrow = reinterpret_cast<uint16_t*>(a.y) + m * a.ldy + n0;
 #pragma unroll 1
             for (int c0 = part * COLS_PER_WARP; c0 < (part + 1) * COLS_PER_WARP; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + c0), v);
                 if (m < m_end) {
                     if (a.y_vec_ok && n0 + c0 + 32 <= a.N) {
 #pragma unroll
@@ -434,6 +474,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                     }
                 }
             }
+            }
         }
     }
     if (!ok) atomicOr(a.status, JQ_STATUS_LOCAL_WAIT);
@@ -441,7 +482,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, MT * BN);
     }
 }
 
@@ -459,21 +500,20 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-template <typename AT, int BITS, int BN, int DPR>
+template <typename AT, int BITS, int BN, int DPR, int MT = 1>
 static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, int64_t m_tiles, cudaStream_t st) {
-    constexpr int CKB = BITS == 2 ? 8 : (BITS == 8 ? 2 : 4);
-    constexpr size_t smem = 1024 + GEMM_SA * GEMM_BM * GEMM_BK * 2 + GEMM_SB * BN * GEMM_BK * 2 +
-                            2 * BN * (CKB * 8 * BITS + 16) + 256;
+    constexpr size_t smem = CodeStage<BITS, BN, MT>::SMEM;
+    static_assert(smem <= GEMM_SMEM, "shared memory of one CTA");
     static bool attr_done[64] = {};
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN, DPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN, DPR, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)m_tiles);
-    qgemm_tc_kernel<AT, BITS, BN, DPR><<<grid, 64 + BN * DPR, smem, st>>>(xmap, a);
+    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)((m_tiles + MT - 1) / MT));
+    qgemm_tc_kernel<AT, BITS, BN, DPR, MT><<<grid, 64 + BN * DPR, smem, st>>>(xmap, a);
     return check_launch("qgemm");
 }
 
@@ -538,13 +578,17 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     const int64_t m_tiles = grp ? grp->max_tiles : (M + GEMM_BM - 1) / GEMM_BM;
     if (m_tiles == 0) return JQ_OK;
     JQ_REQUIRE(m_tiles < 65536, JQ_EUNSUPPORTED, "too many row tiles for one launch (%lld)", (long long)m_tiles);
-    // 256-wide tiles reuse every activation tile twice as often; narrow outputs keep 128
+    // 256-wide tiles reuse every activation tile twice as often; narrow outputs keep 128.  Two row tiles per CTA
+    // (dense only: the grouped tile lists are per 128 rows) when that still leaves a CTA for most SMs.
     const bool wide = N >= 256;
+    const bool two = !grp && wide && ((N + 255) / 256) * ((m_tiles + 1) / 2) >= (int64_t)sm_count() * 3 / 4;
 #define JQ_GEMM_CASE(B)                                                                                  \
     if (bits == B) {                                                                                     \
-        if (x_dtype == JQ_BF16)                                                                          \
+        if (x_dtype == JQ_BF16) {                                                                        \
+            if (two) return launch_gemm<__nv_bfloat16, B, 256, 1, 2>(xmap, a, m_tiles, st);              \
             return wide ? launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st)                    \
                         : launch_gemm<__nv_bfloat16, B, 128, 1>(xmap, a, m_tiles, st);                   \
+        }                                                                                                \
         return launch_gemm<__half, B, 128, 1>(xmap, a, m_tiles, st);                                     \
     }
     JQ_GEMM_CASE(2) JQ_GEMM_CASE(3) JQ_GEMM_CASE(4) JQ_GEMM_CASE(5) JQ_GEMM_CASE(6) JQ_GEMM_CASE(8)

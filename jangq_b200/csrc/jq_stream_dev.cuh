@@ -373,7 +373,9 @@ __device__ __forceinline__ void compute_item(const uint8_t* buf, const uint8_t* 
         load_pairs(sp_hi, s_hi);
         int cg[4];
         auto block = [&](const int blk) {
-            const uint4 bq = *reinterpret_cast<const uint4*>(bp + blk * 64);
+            // only the lanes of the three limb columns load; the other columns are zero without touching memory
+            uint4 bq = make_uint4(0u, 0u, 0u, 0u);
+            if (g < 3) bq = *reinterpret_cast<const uint4*>(bp + blk * 64);
             uint32_t ulo[UW], uhi[UW], rl[4], rh[4];
             load_unit<BITS>(c_lo, blk, tig, ulo);
             load_unit<BITS>(c_hi, blk, tig, uhi);

@@ -248,6 +248,19 @@ def gather_qmm(x: torch.Tensor, w, scales: torch.Tensor | None = None, biases: t
 def route_softmax_topk(logits: torch.Tensor, k: int, renorm: bool = True, scale: float = 1.0):
     """(idx int32 [T, k], w float32 [T, k]): softmax over experts in f32, top-k by score (ties to
     the lower id, as jang_tools/dsv41/metal_decode.py:1141), w / (sum w + 1e-20) * scale."""
+    if logits.is_cuda and logits.dim() == 2 and logits.shape[1] <= 1024 and \
+            logits.dtype in (torch.float32, torch.bfloat16, torch.float16):
+        lib = _lib.load()
+        if logits.stride(1) != 1:
+            logits = logits.contiguous()
+        T, E = logits.shape
+        idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+        wts = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+        with torch.cuda.device(logits.device):
+            _lib.check(lib.jq_moe_topk(logits.data_ptr(), _lib.dtype_id(logits.dtype), logits.stride(0), T, E, k,
+                                       1 if renorm else 0, float(scale), idx.data_ptr(), wts.data_ptr(),
+                                       _lib.stream_ptr(logits.device)))
+        return idx, wts
     p = torch.softmax(logits.float(), dim=-1)
     w, idx = torch.topk(p, k, dim=-1, sorted=True)
     if renorm:
@@ -383,7 +396,10 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
     P = T * k
     idx32 = idx.reshape(-1).to(torch.int32).contiguous()
     wf = w.reshape(-1).float().contiguous()
-    x = x.contiguous()
+    # rows with a leading dimension are taken as they are (the slot rows of the expert-parallel exchange carry
+    # 16 bytes of routing data behind each row); anything else is made contiguous
+    if not (x.dim() == 2 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+        x = x.contiguous()
     dt = _lib.dtype_id(x.dtype)
     st = _lib.stream_ptr(dev)
     I = gate.N

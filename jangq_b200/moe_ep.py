@@ -76,6 +76,114 @@ def dispatch_combine(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, num_ex
     return out
 
 
+def slot_capacity(n_pairs: int, world: int, factor: float = 1.25) -> int:
+    """Slots per (source, destination) pair of ranks for dispatch_combine_slots: the mean share of a rank's
+    pairs times `factor`, plus slack for small batches, a multiple of 8, never more than all pairs."""
+    c = int(n_pairs / world * factor) + 32
+    return min(max(n_pairs, 8), (c + 7) // 8 * 8)
+
+
+def dispatch_combine_slots(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, num_experts: int, local_fn: Callable,
+                           capacity: int, group=None):
+    """Sharded-token expert parallelism without a host read-back: every (source, destination) pair of ranks owns
+    `capacity` row slots (the same number on every rank), so both exchanges are equal-split all_to_all_single calls
+    of fixed size and no split table ever reaches the host.  A row travels with its local expert id and routing
+    weight packed behind its H values (16 bytes), so the dispatch is ONE collective; empty slots carry expert id
+    -1 and local_fn ignores them (the CUDA kernels drop pairs whose expert is outside the bank).  The return trip
+    sends the slot rows back and each token adds its k slots in slot order.
+
+    Returns (out [T, H] float32, overflow): `overflow` is a 0-dim bool tensor on x's device, true when some
+    destination got more than `capacity` pairs -- their rows are missing from `out`; the caller reads it after
+    the step (not in its middle) and repeats the step with dispatch_combine or a larger capacity."""
+    world = dist.get_world_size(group)
+    if num_experts % world:
+        raise ValueError(f"{num_experts} experts do not shard over {world} ranks")
+    e_local = num_experts // world
+    T, H = x.shape
+    k = idx.shape[1]
+    P, C = T * k, int(capacity)
+    es = x.element_size()
+    if C < 1 or (H * es) % 4:
+        raise ValueError("capacity must be positive and rows a multiple of 4 bytes")
+    dev = x.device
+    Hp = H + 16 // es                                               # row + 16 bytes: expert id, weight, 8 spare
+    mcol = H * es // 4                                              # int32 / float32 column of the expert id
+    if x.is_cuda and es == 2 and H % 8 == 0:
+        return _dispatch_combine_slots_cuda(x, idx, w, num_experts, local_fn, C, group, world, Hp, mcol)
+    flat = idx.reshape(-1).to(torch.int64)
+    dest = torch.div(flat, e_local, rounding_mode="floor").clamp_(0, world - 1)
+    order = torch.sort(dest, stable=True).indices                  # pairs grouped by destination rank
+    counts = torch.zeros(world, dtype=torch.int64, device=dev).scatter_add_(0, dest, torch.ones_like(dest))
+    first = torch.cumsum(counts, 0) - counts
+    sdest = dest[order]
+    pos = torch.arange(P, device=dev) - first[sdest]               # position among the pairs of its destination
+    valid = pos < C
+    slot = torch.where(valid, sdest * C + pos, torch.full_like(pos, world * C))   # row world*C: never sent
+    overflow = (counts > C).any()
+
+    send = torch.empty((world * C + 1, Hp), dtype=x.dtype, device=dev)
+    send_i, send_f = send.view(torch.int32), send.view(torch.float32)
+    send_i[:, mcol] = -1
+    send[:, :H].index_copy_(0, slot, x.index_select(0, torch.div(order, k, rounding_mode="floor")))
+    send_i[:, mcol].index_copy_(0, slot, (flat[order] % e_local).to(torch.int32))
+    send_f[:, mcol + 1].index_copy_(0, slot, w.reshape(-1).to(torch.float32)[order])
+    recv = torch.empty((world * C, Hp), dtype=x.dtype, device=dev)
+    dist.all_to_all_single(recv, send[:world * C], group=group)
+
+    y_recv = local_fn(recv[:, :H], recv.view(torch.int32)[:, mcol], recv.view(torch.float32)[:, mcol + 1])
+    y_recv = y_recv.to(x.dtype).contiguous()
+    y_back = torch.empty_like(y_recv)
+    dist.all_to_all_single(y_back, y_recv, group=group)
+
+    slot_of_pair = torch.empty(P, dtype=torch.int32, device=dev)
+    slot_of_pair.index_copy_(0, order, torch.where(valid, slot, torch.full_like(slot, -1)).to(torch.int32))
+    out = torch.empty((T, y_back.shape[1]), dtype=torch.float32, device=dev)
+    if x.is_cuda:
+        lib = _lib.load()
+        with torch.cuda.device(dev):
+            _lib.check(lib.jq_moe_combine(y_back.data_ptr(), y_back.stride(0), slot_of_pair.data_ptr(), None, T, k,
+                                          y_back.shape[1], None, y_back.shape[1], out.data_ptr(),
+                                          _lib.dtype_id(x.dtype), _lib.stream_ptr(dev)))
+    else:
+        sp = slot_of_pair.long().reshape(T, k)
+        rows = y_back.float()[sp.clamp(min=0)]                     # [T, k, D]; slot -1 (dropped) reads row 0: masked
+        rows = torch.where((sp >= 0)[..., None], rows, torch.zeros((), dtype=rows.dtype))
+        out = rows.sum(1) if T else out
+    return out, overflow
+
+
+def _dispatch_combine_slots_cuda(x, idx, w, num_experts, local_fn, C, group, world, Hp, mcol):
+    """dispatch_combine_slots on a GPU: the slot rows are packed by jq_ep_pack_slots (two launches), the k slots of
+    a token are added by jq_moe_combine; in between only the two collectives and local_fn."""
+    lib = _lib.load()
+    T, H = x.shape
+    k = idx.shape[1]
+    dev = x.device
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    idx32 = idx.reshape(-1).to(torch.int32).contiguous()
+    wf = w.reshape(-1).to(torch.float32).contiguous()
+    send = torch.empty((world * C, Hp), dtype=x.dtype, device=dev)
+    recv = torch.empty_like(send)
+    slot_of_pair = torch.empty(max(T * k, 1), dtype=torch.int32, device=dev)
+    scratch = torch.empty(world + 1, dtype=torch.int32, device=dev)           # counters, then the overflow word
+    st = _lib.stream_ptr(dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.jq_ep_pack_slots(x.data_ptr(), x.stride(0), idx32.data_ptr(), wf.data_ptr(), T, k, H, num_experts,
+                                        world, C, send.data_ptr(), slot_of_pair.data_ptr(), scratch.data_ptr(),
+                                        scratch[world:].data_ptr(), st))
+        dist.all_to_all_single(recv, send, group=group)
+        y_recv = local_fn(recv[:, :H], recv.view(torch.int32)[:, mcol], recv.view(torch.float32)[:, mcol + 1])
+        y_recv = y_recv.to(x.dtype).contiguous()
+        y_back = torch.empty_like(y_recv)
+        dist.all_to_all_single(y_back, y_recv, group=group)
+        D = y_back.shape[1]
+        out = torch.empty((T, D), dtype=torch.float32, device=dev)
+        _lib.check(lib.jq_moe_combine(y_back.data_ptr(), y_back.stride(0), slot_of_pair.data_ptr(), None, T, k, D, None, D,
+                                      out.data_ptr(), _lib.dtype_id(x.dtype), st))
+    return out, scratch[world] != 0
+
+
 def replicated_tokens(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, partial_fn: Callable, group=None) -> torch.Tensor:
     """Replicated-token expert parallelism: partial_fn(x, idx, w) -> f32 [T, H] over this rank's experts
     only; one all-reduce adds the ranks' partial sums."""
@@ -107,15 +215,16 @@ def gathered_tokens(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, partial
     return out
 
 
-def local_experts_fn(gate, up, down, swiglu_limit: float = 0.0):
-    """local_fn for dispatch_combine on a GPU: rows with one (local) expert and weight each."""
+def local_experts_fn(gate, up, down, swiglu_limit: float = 0.0, out_f32: bool = True):
+    """local_fn for dispatch_combine / dispatch_combine_slots on a GPU: rows with one (local) expert and weight
+    each; rows whose expert id is outside the bank (the empty slots, id -1) give zero rows."""
     from .moe import moe_layer
 
     def fn(x_rows, e_local, w_rows):
         if x_rows.shape[0] == 0:
             return torch.zeros_like(x_rows, dtype=torch.float32)
         return moe_layer(x_rows, e_local[:, None], w_rows[:, None], gate, up, down, swiglu_limit=swiglu_limit,
-                         out_f32=True)
+                         out_f32=out_f32)
     return fn
 
 

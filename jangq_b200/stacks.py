@@ -47,6 +47,7 @@ class MoEDecodeStack:
                  expert_bits=2, attn_bits=6, gs=64, device="cuda", rank=0, world=1, seed=0, group=None,
                  ep_mode="replicated"):
         self.L, self.H, self.E, self.I, self.k = layers, hidden, experts, inter, topk
+        self.slot_factor, self._overflow = 1.25, None
         self.world, self.rank, self.group = world, rank, group
         self.ep_mode = ep_mode
         self.e_local = experts // world
@@ -148,13 +149,41 @@ class MoEDecodeStack:
         """The routed-expert block of one layer over many tokens (sorted tensor-core path); with
         world > 1 the tokens of this rank are dispatched to the expert owners and combined back."""
         lay = self.layers[layer]
-        logits = torch.matmul(x, lay["router"].t()).float()
+        logits = torch.matmul(x, lay["router"].t())          # library GEMM; the selection is jq_moe_topk (one launch)
+        idx, w = moe.route_softmax_topk(logits, self.k)
+        if self.world == 1:
+            return moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"])
+        # fixed-capacity slots: two equal-split collectives, nothing read back by the host inside the layer; the
+        # overflow flags of a step are OR-ed on the device and read by prefill_overflowed() after it
+        cap = moe_ep.slot_capacity(x.shape[0] * self.k, self.world, self.slot_factor)
+        y, over = moe_ep.dispatch_combine_slots(x, idx, w, self.E,
+                                                moe_ep.local_experts_fn(lay["gate"], lay["up"], lay["down"], out_f32=False),
+                                                cap, group=self.group)
+        self._overflow = over if self._overflow is None else (self._overflow | over)
+        return y.to(x.dtype)
+
+    def prefill_layer_exact(self, x: torch.Tensor, layer: int = 0) -> torch.Tensor:
+        """prefill_layer with exact split sizes (a host read-back per layer): the route to repeat a step on whose
+        slots overflowed."""
+        lay = self.layers[layer]
+        logits = torch.matmul(x, lay["router"].t())          # library GEMM; the selection is jq_moe_topk (one launch)
         idx, w = moe.route_softmax_topk(logits, self.k)
         if self.world == 1:
             return moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"])
         y = moe_ep.dispatch_combine(x, idx, w, self.E, moe_ep.local_experts_fn(lay["gate"], lay["up"], lay["down"]),
                                     group=self.group)
         return y.to(x.dtype)
+
+    def prefill_overflowed(self) -> bool:
+        """True when a prefill_layer call since the last check ran out of slots on any rank (one host read; the
+        ranks agree through one all-reduce, so that they repeat the step together)."""
+        if self._overflow is None:
+            return False
+        flag = self._overflow.to(torch.int32).reshape(1)
+        self._overflow = None
+        if self.world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        return bool(flag.item())
 
 
 def moe_bytes(lin: JANGLinear) -> int:

@@ -152,9 +152,36 @@ def bench_moe_decode(layers, T, iters):
             "bytes_per_token": stack.bytes_per_token}
 
 
+def bench_moe_prefill(tokens, iters):
+    """The routed-expert block of one config-3 layer over `tokens` tokens (router, sort, gather, grouped GEMMs,
+    SwiGLU, combine), timed as eager launches with CUDA events (its tile counts live on the device, so it is not
+    graph-captured)."""
+    from jangq_b200.stacks import MoEDecodeStack
+    dev = torch.device("cuda")
+    stack = MoEDecodeStack(layers=1, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(12)
+    x = torch.randn((tokens, stack.H), generator=g, device=dev).to(torch.bfloat16)
+    for _ in range(3):
+        stack.prefill_layer(x)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stack.prefill_layer(x)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    ms = times[len(times) // 2]
+    flops = 2.0 * tokens * stack.k * 3 * stack.I * stack.H
+    return {"op": "moe_prefill", "tokens": tokens, "ms_per_layer": ms, "expert_TFLOPs": flops / (ms * 1e-3) / 1e12}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_imatrix", "dequantize", "moe_decode"))
+    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_imatrix", "dequantize", "moe_decode", "moe_prefill"))
     ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small", "qgemm"))
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -186,6 +213,8 @@ def main():
         return
     if a.op == "moe_decode":
         print(json.dumps(bench_moe_decode(a.layers, a.M, a.iters)))
+    elif a.op == "moe_prefill":
+        print(json.dumps(bench_moe_prefill(a.M if a.M > 1 else 2048, a.iters)))
     elif a.op == "qgemv":
         print(json.dumps(bench_qgemv(a.N, a.K, a.bits, a.gs, a.M, a.iters, a.rotate_mb, flags=flags)))
     elif a.op == "qgemm":

@@ -41,7 +41,11 @@ def _worker(rank, world, port, mode, ret):
         lo = rank * e_local
 
         def local_fn(x_rows, e_loc, w_rows):
-            return _dense_moe(x_rows, (e_loc.long() + lo)[:, None], w_rows[:, None], Wg, Wu, Wd)
+            live = e_loc >= 0                                     # empty slots of the fixed-capacity exchange: id -1
+            # empty slots hold whatever the buffer held: compute on zeros there, never multiply garbage by 0
+            xr = torch.where(live[:, None], x_rows, torch.zeros(()))
+            wr = torch.where(live, w_rows, torch.zeros(()))
+            return _dense_moe(xr, (e_loc.long().clamp(min=0) + lo)[:, None], wr[:, None], Wg, Wu, Wd)
 
         if mode == "sharded":
             T = 5 + 3 * rank                                     # ragged: ranks hold different row counts
@@ -53,6 +57,28 @@ def _worker(rank, world, port, mode, ret):
             w = torch.rand(T, k, generator=gr)
             out = moe_ep.dispatch_combine(x, idx, w, E, local_fn)
             ref = _dense_moe(x, idx, w, Wg, Wu, Wd)
+        elif mode in ("slots", "slots_overflow"):
+            T = 6                                                # capacity is a contract: the same on every rank
+            gr = torch.Generator().manual_seed(200 + rank)
+            x = torch.randn(T, H, generator=gr)
+            idx = torch.randint(0, E, (T, k), generator=gr)
+            if rank == 0:
+                idx[:] = torch.tensor([6, 7])                    # all 12 pairs of rank 0 go to rank 1
+            else:
+                idx[:] = torch.tensor([1, 5])                    # rank 1: six pairs each way
+            w = torch.rand(T, k, generator=gr)
+            cap = 12 if mode == "slots" else 8
+            out, over = moe_ep.dispatch_combine_slots(x, idx, w, E, local_fn, cap)
+            ref = _dense_moe(x, idx, w, Wg, Wu, Wd)
+            if mode == "slots_overflow":
+                # rank 0 loses its pairs past the 8th slot (sorted by destination, then pair order) and says so
+                assert bool(over) == (rank == 0)
+                if rank == 0:
+                    keep = torch.zeros(T * k, dtype=torch.bool)
+                    keep[:8] = True
+                    ref = _dense_moe(x, idx, w * keep.reshape(T, k), Wg, Wu, Wd)
+            else:
+                assert not bool(over)
         elif mode == "empty":
             x = torch.zeros(0, H)
             idx = torch.zeros(0, k, dtype=torch.long)
@@ -86,7 +112,7 @@ def _worker(rank, world, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ("sharded", "replicated", "gathered", "empty"))
+@pytest.mark.parametrize("mode", ("sharded", "replicated", "gathered", "empty", "slots", "slots_overflow"))
 def test_expert_parallel_two_ranks(mode):
     world, port = 2, _free_port()
     ret = mp.Manager().dict()

@@ -573,3 +573,62 @@ def test_gather_with_folded_swiglu(bits, N, K, P, limit):
     y2 = _gather_qgemv(h, 1, pe, bank, 0, base)
     assert (y.float() - y2.float()).abs().max() <= 2.0 ** -6 * y2.float().abs().max()
     _lib.check(lib.jq_device_status())
+
+
+@pytest.mark.parametrize("world,C", ((2, 40), (4, 16), (8, 64), (2, 7)))
+def test_ep_slot_packing_covers_every_pair_once(world, C):
+    """jq_ep_pack_slots: every pair lands in exactly one slot of its destination rank with its row, local expert id
+    and weight; empty slots carry id -1; a destination with more pairs than slots drops the surplus, reports them
+    as -1 and sets the overflow word."""
+    lib = _lib.load()
+    T, k, H, E = 9, 4, 256, 16
+    rng = np.random.default_rng(world * 100 + C)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    idx = torch.from_numpy(rng.integers(0, E, size=(T, k)).astype(np.int32)).to(DEV)
+    w = torch.from_numpy(rng.random((T, k)).astype(np.float32)).to(DEV)
+    Hp = H + 8
+    send = torch.full((world * C, Hp), 7.0, dtype=torch.bfloat16, device=DEV)
+    sop = torch.full((T * k,), -5, dtype=torch.int32, device=DEV)
+    scratch = torch.full((world + 1,), 99, dtype=torch.int32, device=DEV)
+    _lib.check(lib.jq_ep_pack_slots(x.data_ptr(), H, idx.data_ptr(), w.data_ptr(), T, k, H, E, world, C, send.data_ptr(),
+                                    sop.data_ptr(), scratch.data_ptr(), scratch[world:].data_ptr(), _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    e_local = E // world
+    dest = idx.cpu().numpy().reshape(-1) // e_local
+    counts = np.bincount(dest, minlength=world)
+    assert scratch[:world].cpu().numpy().tolist() == counts.tolist()
+    assert bool(scratch[world]) == bool((counts > C).any())
+    sop_h = sop.cpu().numpy()
+    ids = send.view(torch.int32)[:, H // 2].cpu().numpy()
+    wts = send.view(torch.float32)[:, H // 2 + 1].cpu().numpy()
+    rows = send[:, :H].float().cpu().numpy()
+    used = sop_h[sop_h >= 0]
+    assert len(set(used.tolist())) == used.size                       # no slot twice
+    for r in range(world):
+        assert ((sop_h >= r * C) & (sop_h < (r + 1) * C)).sum() == min(counts[r], C)
+    xh, wh, ih = x.float().cpu().numpy(), w.cpu().numpy().reshape(-1), idx.cpu().numpy().reshape(-1)
+    for p, s in enumerate(sop_h):
+        if s < 0:
+            assert counts[dest[p]] > C
+            continue
+        assert s // C == dest[p] and ids[s] == ih[p] - dest[p] * e_local and wts[s] == wh[p]
+        assert np.array_equal(rows[s], xh[p // k])
+    free = np.setdiff1d(np.arange(world * C), used)
+    assert (ids[free] == -1).all()
+
+
+@pytest.mark.parametrize("T,E,k,dtype", ((2048, 128, 8, torch.bfloat16), (33, 1000, 32, torch.float32), (5, 7, 7, torch.float16),
+                                         (300, 512, 10, torch.bfloat16)))
+def test_topk_over_logit_rows(T, E, k, dtype):
+    """jq_moe_topk (one warp per token) against the oracle's softmax / top-k: ids bit-exact including ties (16-bit
+    logits collide often: ties go to the lower id), weights to f32 rounding; a padded leading dimension."""
+    rng = np.random.default_rng(T + E)
+    full = torch.from_numpy(rng.standard_normal((T, E + 8)).astype(np.float32)).to(DEV).to(dtype)
+    logits = full[:, :E]
+    idx, w = jq.route_softmax_topk(logits, k)
+    idx_ref, w_ref = jo.route_softmax_topk(logits.float().cpu().numpy(), k)
+    assert np.array_equal(idx.cpu().numpy(), idx_ref)
+    assert np.allclose(w.cpu().numpy(), w_ref, rtol=2e-5, atol=1e-7)
+    idx2, w2 = jq.route_softmax_topk(logits, k, renorm=False, scale=2.5)
+    _, w_ref2 = jo.route_softmax_topk(logits.float().cpu().numpy(), k, renorm=False, scale=2.5)
+    assert np.array_equal(idx2.cpu().numpy(), idx_ref) and np.allclose(w2.cpu().numpy(), w_ref2, rtol=2e-5, atol=1e-7)

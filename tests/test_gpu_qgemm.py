@@ -110,3 +110,26 @@ def test_qgemm_unsupported_row_lengths():
 def test_device_status_clean_after_gemm():
     torch.cuda.synchronize()
     assert _lib.load().jq_device_status() == 0
+
+
+@pytest.mark.parametrize("gs", (64, 128))
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+def test_qgemm_two_row_tiles_per_cta(bits, gs):
+    """Shapes large enough for the two-accumulator form (256 rows of the activations per CTA): a ragged last
+    row tile whose second half is empty, a ragged last column tile, every width and code-stage layout."""
+    M, N, K = 1160, 7300, 384
+    x, wq, s, b = make_case(M, N, K, bits, gs, torch.bfloat16, seed=bits + gs)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
+    check(y, x, wq, s, b, bits, gs, torch.bfloat16)
+    _lib.check(_lib.load().jq_device_status())
+
+
+def test_qgemm_two_row_tiles_equal_one_row_tile_results():
+    """The same rows through the one- and the two-accumulator form (a small N keeps one tile per CTA) are
+    bit-identical: the accumulation order along K is the same."""
+    M, K, bits, gs = 1024, 512, 4, 64
+    x, wq, s, b = make_case(M, 8192, K, bits, gs, torch.bfloat16, seed=5)
+    y2 = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)                  # 32 x 4 CTAs: two tiles each
+    y1 = jq.quantized_matmul(x, wq[:512].contiguous(), s[:512].contiguous(), b[:512].contiguous(), group_size=gs,
+                             bits=bits)                                               # 2 x 8 CTAs: one tile each
+    assert torch.equal(y2[:, :512], y1)
