@@ -460,8 +460,12 @@ static int launch_mma(const GemvArgs& a, const GemvBatch& bt, int pairs, cudaStr
     const int sb = mt == 2 ? GemvGeom<BITS, GS, 2>::stage_bytes(a.M) : GemvGeom<BITS, GS, 1>::stage_bytes(a.M);
     const int nbuf = (nw == 8 && nst >= 20 && nw * 3 * sb <= 200 * 1024) ? 3 : 2;
     if (mt == 2) return launch_mma_cfg<AT, BITS, GS, 2, 4>(a, bt, pairs, nbuf, st, launched);
-    if (nw == 8) return launch_mma_cfg<AT, BITS, GS, 1, 8>(a, bt, pairs, nbuf, st, launched);
-    return launch_mma_cfg<AT, BITS, GS, 1, 4>(a, bt, pairs, nbuf, st, launched);
+    if (nw == 8) {
+        // eight warps' stages may not fit the shared memory (several activation rows, wide codes): four warps then
+        const int rc = launch_mma_cfg<AT, BITS, GS, 1, 8>(a, bt, pairs, nbuf, st, launched);
+        if (rc != JQ_OK || *launched) return rc;
+    }
+    return launch_mma_cfg<AT, BITS, GS, 1, 4>(a, bt, pairs, 2, st, launched);
 }
 
 static int launch_mma_any(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, int pairs,
@@ -629,10 +633,10 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
     const bool fast = !force_simple() && (gs == 64 || gs == 128) && act_dtype != JQ_F32 && sidecar_dtype == act_dtype &&
                       ((K * bits / 8) % 16 == 0) && aligned(x, 16) && (ldx % 8 == 0) && ((K / gs) % 4 == 0) && bits != 5;
     bool launched = false;
-    // One token's pairs (they share its row, or each has its own): the item-streaming integer kernel, all
-    // matrices in one launch.  Other cases (several tokens, per-expert widths): the bf16 warp-MMA kernel.
-    if (fast && !bits_tab && pairs <= 16 && (x_div == pairs || x_div == 1) && gemv_kernel_choice() != 1) {
-        rc = launch_gather_one(x, nullptr, nullptr, 0.f, ldx, (x_div == 1 && pairs > 1) ? 1 : 0, pair_expert, (int)pairs,
+    // Up to 16 pairs (one or two tokens of a top-8 model; a row per x_div pairs): the item-streaming integer kernel,
+    // all matrices in one launch.  Other cases (more pairs, per-expert widths): the bf16 warp-MMA kernel.
+    if (fast && !bits_tab && pairs <= 16 && x_div >= 1 && gemv_kernel_choice() != 1) {
+        rc = launch_gather_one(x, nullptr, nullptr, 0.f, ldx, x_div, pair_expert, (int)pairs,
                                codes_tab2 ? 2 : 1, codes_tab, scales_tab, biases_tab, codes_tab2, scales_tab2, biases_tab2,
                                num_experts, expert_base, act_dtype, N, K, bits, gs, y, y2, ldy, a.pdl != 0, st, &launched);
         if (rc != JQ_OK) return rc;

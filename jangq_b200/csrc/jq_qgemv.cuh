@@ -150,7 +150,7 @@ struct NormSrc {
 
 // routed-expert gather for one token on the item-streaming integer kernel (jq_qgemv_one.cu): `banks` x `pairs`
 // matrices in one launch, optionally with the activations formed as silu(gate) * up * weight on the fly
-int launch_gather_one(const void* x, const void* up, const float* wts, float limit, int64_t ldx, int x_per_pair,
+int launch_gather_one(const void* x, const void* up, const float* wts, float limit, int64_t ldx, int x_div,
                       const int32_t* pair_expert, int pairs, int banks, const uint32_t* const* codes_tab,
                       const void* const* scales_tab, const void* const* biases_tab, const uint32_t* const* codes_tab2,
                       const void* const* scales_tab2, const void* const* biases_tab2, int num_experts, int expert_base,

@@ -243,7 +243,7 @@ struct GatherArgs {
     float limit;
     int pairs, banks, num_experts, expert_base;
     int N, K, G;
-    int x_per_pair;                   // 0: every pair reads row 0; 1: pair p reads row p
+    int x_div;                        // pair p reads activation row p / x_div (pairs: one shared row; 1: a row per pair)
     int tpc;                          // 16-row tiles per CTA
 };
 
@@ -265,7 +265,7 @@ gather_one_kernel(const GatherArgs a) {
     constexpr int RB = rowb_of(BITS);
     const int rowbytes = K * BITS / 8;
     const int nst = (rowbytes + RB - 1) / RB;
-    const int nx = a.x_per_pair ? a.pairs : 1;
+    const int nx = (a.pairs + a.x_div - 1) / a.x_div;
     const int tpm = (N + 15) / 16;                                   // tiles per matrix
     const int total = a.banks * a.pairs * tpm;
 
@@ -304,7 +304,7 @@ gather_one_kernel(const GatherArgs a) {
                 ti.scales = reinterpret_cast<const uint16_t*>(a.scales_tab[b][e]) + (int64_t)row0 * G;
                 ti.biases = reinterpret_cast<const uint16_t*>(a.biases_tab[b][e]) + (int64_t)row0 * G;
                 ti.rows_valid = rows_valid;
-                ti.xsel = a.x_per_pair ? p : 0;
+                ti.xsel = p / a.x_div;
             } else {
                 for (int r = 0; r < rows_valid; ++r) yp[r] = 0;     // an expert of another rank: zero rows
             }
@@ -393,7 +393,7 @@ static int launch_gather_cfg(const GatherArgs& a, int nx, int grid, bool pdl, cu
 template <typename AT, int BITS, int GS>
 static int launch_gather_shape(GatherArgs a, bool pdl, cudaStream_t st, bool* launched) {
     const int sms = sm_count();
-    const int nx = a.x_per_pair ? a.pairs : 1;
+    const int nx = (a.pairs + a.x_div - 1) / a.x_div;
     const int64_t tiles = (int64_t)a.banks * a.pairs * ((a.N + 15) / 16);
     const int tpc = (int)((tiles + sms - 1) / sms);
     if (tpc > MAXT) return JQ_OK;
@@ -435,7 +435,7 @@ namespace jq {
 
 // Routed-expert gather for one token on the item-streaming integer kernel (see GatherArgs); *launched stays false
 // when the shape does not fit (more than 16 pairs, other widths, K / gs not a multiple of 4, too many tiles).
-int launch_gather_one(const void* x, const void* up, const float* wts, float limit, int64_t ldx, int x_per_pair,
+int launch_gather_one(const void* x, const void* up, const float* wts, float limit, int64_t ldx, int x_div,
                       const int32_t* pair_expert, int pairs, int banks, const uint32_t* const* codes_tab,
                       const void* const* scales_tab, const void* const* biases_tab, const uint32_t* const* codes_tab2,
                       const void* const* scales_tab2, const void* const* biases_tab2, int num_experts, int expert_base,
@@ -443,10 +443,10 @@ int launch_gather_one(const void* x, const void* up, const float* wts, float lim
                       cudaStream_t st, bool* launched) {
     *launched = false;
     if (!(bits == 2 || bits == 4 || bits == 6 || bits == 8) || !(gs == 64 || gs == 128) || K % (4 * gs) != 0 ||
-        pairs < 1 || pairs > 16 || N < 1 || N >= (1 << 24) || K >= (1 << 22))
+        pairs < 1 || pairs > 16 || x_div < 1 || N < 1 || N >= (1 << 24) || K >= (1 << 22))
         return JQ_OK;
     one::GatherArgs a = {};
-    a.x = x; a.up = up; a.wts = wts; a.limit = limit; a.ldx = ldx; a.x_per_pair = x_per_pair;
+    a.x = x; a.up = up; a.wts = wts; a.limit = limit; a.ldx = ldx; a.x_div = x_div;
     a.pair_expert = pair_expert; a.pairs = pairs; a.banks = banks;
     a.codes_tab[0] = codes_tab; a.scales_tab[0] = scales_tab; a.biases_tab[0] = biases_tab;
     a.codes_tab[1] = codes_tab2; a.scales_tab[1] = scales_tab2; a.biases_tab[1] = biases_tab2;

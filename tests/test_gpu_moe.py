@@ -493,7 +493,7 @@ def _np_swiglu(g, u, w, limit):
 
 @pytest.mark.parametrize("bits,gs,N,K", ((2, 64, 768, 2048), (4, 64, 200, 1024), (6, 64, 334, 1280), (8, 128, 40, 2048),
                                          (2, 128, 2048, 768), (6, 64, 2048, 768)))
-@pytest.mark.parametrize("P,x_div", ((8, 8), (1, 1), (6, 1), (16, 16)))
+@pytest.mark.parametrize("P,x_div", ((8, 8), (1, 1), (6, 1), (16, 16), (16, 8), (12, 4)))
 def test_one_token_gather_on_the_item_kernel(bits, gs, N, K, P, x_div, monkeypatch):
     """Up to 16 pairs of one token (a shared row, or one row per pair) take the item-streaming integer kernel:
     against the oracle, against the warp-MMA kernel forced by the environment switch, pairs outside the bank
