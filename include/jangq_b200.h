@@ -224,6 +224,16 @@ int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t l
                 const void* const* scales_tab, const void* const* biases_tab, const int32_t* bits_tab,
                 int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y_sorted,
                 int64_t ldy, jq_stream_t stream);
+/* jq_moe_gemm over a tile list of tile_m rows per entry (the tile_m given to jq_moe_sort): 128, or 256 -- one CTA
+ * then carries two 128-row accumulators and every dequantized weight tile feeds both, which pays once experts hold
+ * more than 128 rows (bf16 activations and N >= 256 only; JQ_EUNSUPPORTED otherwise). */
+int jq_moe_gemm_tiled(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx,
+                      const int32_t* expert_offsets, const int32_t* tile_expert, const int32_t* tile_row0,
+                      const int32_t* num_tiles, int64_t max_tiles, int tile_m, const uint32_t* const* codes_tab,
+                      const void* const* scales_tab, const void* const* biases_tab, const int32_t* bits_tab,
+                      int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size, void* y_sorted,
+                      int64_t ldy, jq_stream_t stream);
+
 
 /* jq_moe_gemm without any workspace.  No counterpart in the reference (MLX allocates inside
  * gather_qmm); it exists for callers that must not allocate device memory on the request path:

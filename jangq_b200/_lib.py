@@ -74,6 +74,8 @@ SIGNATURES = {
     "jq_gather_rows": (C.c_int, [_p, _i64, _p, _p, _i32, _p, _i64, _i64, _i64, _i32, _p]),
     "jq_moe_gemm": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _i32, _i64, _i64, _i32, _i32,
                               _p, _i64, _p]),
+    "jq_moe_gemm_tiled": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, _p, _i32, _i64, _i64, _i32,
+                                    _i32, _p, _i64, _p]),
     "jq_moe_gemm_static": (C.c_int, [_p, _i32, _i64, _i64, _p, _i32, _p, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p,
                                      _i64, _p]),
     "jq_moe_swiglu": (C.c_int, [_p, _p, _i64, _p, _p, _p, _p, _i64, _i64, _i64, C.c_float, _i32, _p]),

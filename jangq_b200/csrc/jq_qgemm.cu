@@ -500,6 +500,8 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// m_tiles: 128-row tiles of a dense GEMM (MT of them per CTA), or entries of a grouped GEMM's tile list (one CTA
+// each, whatever MT)
 template <typename AT, int BITS, int BN, int DPR, int MT = 1>
 static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, int64_t m_tiles, cudaStream_t st) {
     constexpr size_t smem = CodeStage<BITS, BN, MT>::SMEM;
@@ -512,7 +514,7 @@ static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, int64_t m_til
                                         (int)smem));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)((m_tiles + MT - 1) / MT));
+    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)(a.tile_expert ? m_tiles : (m_tiles + MT - 1) / MT));
     qgemm_tc_kernel<AT, BITS, BN, DPR, MT><<<grid, 64 + BN * DPR, smem, st>>>(xmap, a);
     return check_launch("qgemm");
 }
@@ -523,6 +525,7 @@ struct GroupedArgs {
     const void* const* scales_tab;
     const void* const* biases_tab;
     int64_t max_tiles;
+    int tile_m;       // rows per entry of the tile list: 128, or 256 (two accumulators per CTA)
 };
 
 // Dense when grp == nullptr (codes/scales/biases of one matrix); grouped otherwise (x holds the M
@@ -581,7 +584,10 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     // 256-wide tiles reuse every activation tile twice as often; narrow outputs keep 128.  Two row tiles per CTA
     // (dense only: the grouped tile lists are per 128 rows) when that still leaves a CTA for most SMs.
     const bool wide = N >= 256;
-    const bool two = !grp && wide && ((N + 255) / 256) * ((m_tiles + 1) / 2) >= (int64_t)sm_count() * 3 / 4;
+    JQ_REQUIRE(!grp || grp->tile_m == 128 || (grp->tile_m == 256 && wide && x_dtype == JQ_BF16), JQ_EUNSUPPORTED,
+               "tile lists of 256 rows need bf16 activations and N >= 256 (128 otherwise)");
+    const bool two = grp ? grp->tile_m == 256
+                         : wide && ((N + 255) / 256) * ((m_tiles + 1) / 2) >= (int64_t)sm_count() * 3 / 4;
 #define JQ_GEMM_CASE(B)                                                                                  \
     if (bits == B) {                                                                                     \
         if (x_dtype == JQ_BF16) {                                                                        \
@@ -694,6 +700,7 @@ int jq_moe_gemm_static(const void* x_sorted, int act_dtype, int64_t max_rows, in
     g.expert_offsets = expert_offsets;
     g.bits_tab = bits_tab; g.codes_tab = codes_tab; g.scales_tab = scales_tab; g.biases_tab = biases_tab;
     g.max_tiles = max_rows / GEMM_BM + num_experts;
+    g.tile_m = 128;
     return qgemm_dispatch(x_sorted, act_dtype, max_rows, ldx, nullptr, nullptr, nullptr, sidecar_dtype, N, K, bits,
                           group_size, y_sorted, act_dtype, ldy, &g, (cudaStream_t)stream);
 }
@@ -710,7 +717,18 @@ int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t l
                 const uint32_t* const* codes_tab, const void* const* scales_tab, const void* const* biases_tab,
                 const int32_t* bits_tab, int sidecar_dtype, int64_t N, int64_t K, int bits, int group_size,
                 void* y_sorted, int64_t ldy, jq_stream_t stream) {
+    return jq_moe_gemm_tiled(x_sorted, act_dtype, max_rows, ldx, expert_offsets, tile_expert, tile_row0, num_tiles,
+                             max_tiles, 128, codes_tab, scales_tab, biases_tab, bits_tab, sidecar_dtype, N, K, bits,
+                             group_size, y_sorted, ldy, stream);
+}
+
+int jq_moe_gemm_tiled(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t ldx, const int32_t* expert_offsets,
+                      const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* num_tiles, int64_t max_tiles,
+                      int tile_m, const uint32_t* const* codes_tab, const void* const* scales_tab,
+                      const void* const* biases_tab, const int32_t* bits_tab, int sidecar_dtype, int64_t N, int64_t K,
+                      int bits, int group_size, void* y_sorted, int64_t ldy, jq_stream_t stream) {
     using namespace jq;
+    JQ_REQUIRE(tile_m == 128 || tile_m == 256, JQ_EINVAL, "tile_m must be 128 or 256");
     JQ_REQUIRE(expert_offsets && tile_expert && tile_row0 && num_tiles && codes_tab && scales_tab && biases_tab,
                JQ_EINVAL, "null pointer");
     JQ_REQUIRE(max_tiles >= 0, JQ_EINVAL, "negative max_tiles");
@@ -718,6 +736,7 @@ int jq_moe_gemm(const void* x_sorted, int act_dtype, int64_t max_rows, int64_t l
     g.tile_expert = tile_expert; g.tile_row0 = tile_row0; g.num_tiles = num_tiles; g.expert_offsets = expert_offsets;
     g.bits_tab = bits_tab; g.codes_tab = codes_tab; g.scales_tab = scales_tab; g.biases_tab = biases_tab;
     g.max_tiles = max_tiles;
+    g.tile_m = tile_m;
     return qgemm_dispatch(x_sorted, act_dtype, max_rows, ldx, nullptr, nullptr, nullptr, sidecar_dtype, N, K, bits,
                           group_size, y_sorted, act_dtype, ldy, &g, (cudaStream_t)stream);
 }

@@ -115,12 +115,13 @@ class ExpertBank:
 class SortedPairs:
     """Result of jq_moe_sort for one routing decision; reused by gate, up and down."""
 
-    def __init__(self, idx_flat: torch.Tensor, num_experts: int, expert_base: int = 0):
+    def __init__(self, idx_flat: torch.Tensor, num_experts: int, expert_base: int = 0, tile_m: int | None = None):
         lib = _lib.load()
         dev = idx_flat.device
         n = idx_flat.numel()
         self.n, self.E = n, num_experts
-        self.max_tiles = int(lib.jq_moe_sort_max_tiles(n, num_experts, _lib.MOE_TILE_M))
+        self.tile_m = tile_m or _lib.MOE_TILE_M
+        self.max_tiles = int(lib.jq_moe_sort_max_tiles(n, num_experts, self.tile_m))
         i32 = dict(dtype=torch.int32, device=dev)
         self.order = torch.empty(max(n, 1), **i32)
         self.inv = torch.empty(max(n, 1), **i32)
@@ -129,7 +130,7 @@ class SortedPairs:
         self.tile_row0 = torch.empty(max(self.max_tiles, 1), **i32)
         self.num_tiles = torch.empty(1, **i32)
         _lib.check(lib.jq_moe_sort(idx_flat.data_ptr(), n, num_experts, expert_base, self.order.data_ptr(),
-                                   self.inv.data_ptr(), self.offsets.data_ptr(), _lib.MOE_TILE_M,
+                                   self.inv.data_ptr(), self.offsets.data_ptr(), self.tile_m,
                                    self.tile_expert.data_ptr(), self.tile_row0.data_ptr(), self.num_tiles.data_ptr(),
                                    _lib.stream_ptr(dev)))
         self.count_ptr = self.offsets.data_ptr() + 4 * num_experts      # device address of the kept-pair count
@@ -148,13 +149,13 @@ def _moe_gemm(x_sorted: torch.Tensor, sp: SortedPairs, bank: ExpertBank) -> torc
     bank = bank._sidecars_as(x_sorted.dtype)
     y = torch.empty((x_sorted.shape[0], bank.N), dtype=x_sorted.dtype, device=x_sorted.device)
     for bits in bank.distinct_bits:
-        _lib.check(lib.jq_moe_gemm(x_sorted.data_ptr(), _lib.dtype_id(x_sorted.dtype), sp.n, x_sorted.stride(0),
-                                   sp.offsets.data_ptr(), sp.tile_expert.data_ptr(), sp.tile_row0.data_ptr(),
-                                   sp.num_tiles.data_ptr(), sp.max_tiles, bank.codes_tab.data_ptr(),
-                                   bank.scales_tab.data_ptr(), bank.biases_tab.data_ptr(),
-                                   bank.bits_tab.data_ptr() if bank.bits_tab is not None else None,
-                                   _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
-                                   y.data_ptr(), y.stride(0), _lib.stream_ptr(x_sorted.device)))
+        _lib.check(lib.jq_moe_gemm_tiled(x_sorted.data_ptr(), _lib.dtype_id(x_sorted.dtype), sp.n, x_sorted.stride(0),
+                                         sp.offsets.data_ptr(), sp.tile_expert.data_ptr(), sp.tile_row0.data_ptr(),
+                                         sp.num_tiles.data_ptr(), sp.max_tiles, sp.tile_m, bank.codes_tab.data_ptr(),
+                                         bank.scales_tab.data_ptr(), bank.biases_tab.data_ptr(),
+                                         bank.bits_tab.data_ptr() if bank.bits_tab is not None else None,
+                                         _lib.dtype_id(bank.sidecar_dtype), bank.N, bank.K, bits, bank.group_size,
+                                         y.data_ptr(), y.stride(0), _lib.stream_ptr(x_sorted.device)))
     return y
 
 
@@ -406,7 +407,10 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
     with torch.cuda.device(dev):
         use_sorted = P >= SORT_THRESHOLD if few_token_path is None else not few_token_path
         if use_sorted and gate.gemm_ok and up.gemm_ok and down.gemm_ok:
-            sp = SortedPairs(idx32, gate.E, expert_base)
+            # experts with more than 128 rows on average: 256-row tiles, two accumulators per CTA share every
+            # dequantized weight tile (bf16, all three projections at least 256 wide)
+            big = (x.dtype == torch.bfloat16 and min(gate.N, up.N, down.N) >= 256 and P >= 96 * gate.E)
+            sp = SortedPairs(idx32, gate.E, expert_base, tile_m=256 if big else 128)
             xs = _gather_rows(x, sp, k)
             g = _moe_gemm(xs, sp, gate)
             u = _moe_gemm(xs, sp, up)
