@@ -40,11 +40,21 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ unsigned long long wall_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// A wait gives up only when BOTH its poll budget is spent AND this much wall time has passed since its first
+// clock reading: a poll count alone runs out under a profiler or time-slicing although nothing is wrong.
+constexpr unsigned long long MBAR_WAIT_NS = 1000000000ull;
+
 // Bounded wait on a phase parity.  Returns false when the limit ran out (the
 // caller records an error and leaves instead of spinning for ever).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t max_polls = (1u << 20)) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < max_polls; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -54,8 +64,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+        if ((i & 1023u) == 1023u) {
+            const unsigned long long now = wall_ns();
+            if (t0 == 0) t0 = now;
+            else if (i >= max_polls && now - t0 > MBAR_WAIT_NS) return false;
+        }
     }
-    return false;
 }
 
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.

@@ -56,14 +56,25 @@ moe_sort_kernel(const int32_t* __restrict__ idx, int n, int E, int base, int32_t
         const int e = idx[i] - base;
         return (e >= 0 && e < E) ? e : E;
     };
-    // pass 1: per-chunk histogram
-    for (int i0 = lo; i0 < hi; i0 += 32) {
-        const int i = i0 + lane;
-        const bool act = i < hi;
-        const int b = act ? bucket(i) : -1;
-        const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
-        if (act && (peers & ((1u << lane) - 1u)) == 0) cnt[warp * EB + b] += __popc(peers);
-        __syncwarp();
+    // pass 1: per-chunk histogram.  The ids of 16 steps are loaded up front (one round trip to memory instead
+    // of sixteen dependent ones: the loop below synchronises the warp every step).
+    constexpr int SORT_BATCH = 16;
+    for (int j0 = lo; j0 < hi; j0 += 32 * SORT_BATCH) {
+        int bk[SORT_BATCH];
+#pragma unroll
+        for (int q = 0; q < SORT_BATCH; ++q) {
+            const int i = j0 + q * 32 + lane;
+            bk[q] = i < hi ? bucket(i) : -1;
+        }
+#pragma unroll
+        for (int q = 0; q < SORT_BATCH; ++q) {
+            if (j0 + q * 32 >= hi) break;
+            const int b = bk[q];
+            const bool act = b >= 0;
+            const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
+            if (act && (peers & ((1u << lane) - 1u)) == 0) cnt[warp * EB + b] += __popc(peers);
+            __syncwarp();
+        }
     }
     __syncthreads();
     // totals per bucket and exclusive scan over buckets (thread 0 .. E: serial scan is fine for E <= 1024)
@@ -73,23 +84,51 @@ moe_sort_kernel(const int32_t* __restrict__ idx, int n, int E, int base, int32_t
         start[b] = tot;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0, tiles = 0;
-        for (int b = 0; b < EB; ++b) {
-            const int c = start[b];
-            start[b] = run;
+    // Exclusive scan over the buckets of (pairs, tiles), 1024 buckets at a time with a carry: thread b owns bucket
+    // b, a shuffle scan inside the warps and one over the warps' sums give its first position and its first tile;
+    // every thread then writes the tiles of its own expert.
+    {
+        __shared__ int wsum_c[SORT_WARPS], wsum_t[SORT_WARPS], carry[2];
+        if (threadIdx.x == 0) carry[0] = carry[1] = 0;
+        __syncthreads();
+        for (int b0 = 0; b0 < EB; b0 += SORT_THREADS) {
+            const int b = b0 + threadIdx.x;
+            const int c = b < EB ? start[b] : 0;
+            const int tl = b < E ? (c + tile_m - 1) / tile_m : 0;
+            int ic = c, it = tl;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int vc = __shfl_up_sync(0xFFFFFFFFu, ic, d), vt = __shfl_up_sync(0xFFFFFFFFu, it, d);
+                if (lane >= d) { ic += vc; it += vt; }
+            }
+            if (lane == 31) { wsum_c[warp] = ic; wsum_t[warp] = it; }
+            __syncthreads();
+            if (warp == 0) {
+                int vc = wsum_c[lane], vt = wsum_t[lane];
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int uc = __shfl_up_sync(0xFFFFFFFFu, vc, d), ut = __shfl_up_sync(0xFFFFFFFFu, vt, d);
+                    if (lane >= d) { vc += uc; vt += ut; }
+                }
+                wsum_c[lane] = vc; wsum_t[lane] = vt;      // inclusive over the warps
+            }
+            __syncthreads();
+            const int run = carry[0] + (warp > 0 ? wsum_c[warp - 1] : 0) + ic - c;
+            int tile = carry[1] + (warp > 0 ? wsum_t[warp - 1] : 0) + it - tl;
+            if (b < EB) start[b] = run;
             if (b < E) {
                 offsets[b] = run;
-                for (int r = 0; r < c; r += tile_m) {
-                    tile_expert[tiles] = b;
-                    tile_row0[tiles] = run + r;
-                    ++tiles;
+                for (int r = 0; r < c; r += tile_m, ++tile) {
+                    tile_expert[tile] = b;
+                    tile_row0[tile] = run + r;
                 }
             }
-            run += c;
+            if (b == E) offsets[E] = run;
+            __syncthreads();
+            if (threadIdx.x == 0) { carry[0] += wsum_c[SORT_WARPS - 1]; carry[1] += wsum_t[SORT_WARPS - 1]; }
+            __syncthreads();
         }
-        offsets[E] = start[E];
-        *num_tiles = tiles;
+        if (threadIdx.x == 0) *num_tiles = carry[1];
     }
     __syncthreads();
     // per-chunk base positions: start[b] + counts of earlier chunks
@@ -103,25 +142,152 @@ moe_sort_kernel(const int32_t* __restrict__ idx, int n, int E, int base, int32_t
     }
     __syncthreads();
     // pass 2: stable placement
-    for (int i0 = lo; i0 < hi; i0 += 32) {
-        const int i = i0 + lane;
-        const bool act = i < hi;
-        const int b = act ? bucket(i) : -1;
+    for (int j0 = lo; j0 < hi; j0 += 32 * SORT_BATCH) {
+        int bk[SORT_BATCH];
+#pragma unroll
+        for (int q = 0; q < SORT_BATCH; ++q) {
+            const int i = j0 + q * 32 + lane;
+            bk[q] = i < hi ? bucket(i) : -1;
+        }
+#pragma unroll
+        for (int q = 0; q < SORT_BATCH; ++q) {
+            if (j0 + q * 32 >= hi) break;
+            const int i = j0 + q * 32 + lane;
+            const int b = bk[q];
+            const bool act = b >= 0;
+            const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
+            const int rank = __popc(peers & ((1u << lane) - 1u));
+            int pos = 0;
+            if (act) pos = cnt[warp * EB + b] + rank;
+            __syncwarp();
+            if (act && rank == 0) cnt[warp * EB + b] += __popc(peers);
+            __syncwarp();
+            if (act) {
+                if (b < E) {
+                    order[pos] = i;
+                    inv[i] = pos;
+                } else {
+                    inv[i] = -1;
+                }
+            }
+        }
+    }
+}
+
+// ---- the same sort over several CTAs (n >= 2048 pairs, at most 1023 experts) ---------------------------------------
+// One CTA's cost is its __match_any_sync steps (one per 32 pairs and pass, and a step costs about as many
+// iterations as the warp holds distinct experts): 16384 pairs keep one SM busy for 40 us.  Here chunk c =
+// pairs [1024 c, 1024 (c + 1)) (the last chunk also takes the remainder, so it holds 1024..2047 pairs) belongs to
+// CTA c: (A) counts per bucket, (B) one CTA turns the counts into first positions per (chunk, bucket), offsets and
+// the tile list, (C) stable placement inside the chunk.  The per-chunk tables live in the chunk's own stretch of
+// `inv` (1024 entries >= buckets), which CTA c reads into shared memory before it writes its inv entries.
+__device__ __forceinline__ int sort_bucket(const int32_t* idx, int i, int base, int E) {
+    const int e = idx[i] - base;
+    return (e >= 0 && e < E) ? e : E;
+}
+
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_count_kernel(const int32_t* __restrict__ idx, int n, int E, int base, int chunks, int32_t* __restrict__ inv) {
+    extern __shared__ int32_t sm[];                   // [E + 1]
+    const int EB = E + 1, c = blockIdx.x, lane = threadIdx.x & 31;
+    const int lo = c * SORT_THREADS, hi = c == chunks - 1 ? n : lo + SORT_THREADS;
+    for (int b = threadIdx.x; b < EB; b += SORT_THREADS) sm[b] = 0;
+    __syncthreads();
+    for (int i0 = lo; i0 < hi; i0 += SORT_THREADS) {
+        const int i = i0 + threadIdx.x;
+        const int b = i < hi ? sort_bucket(idx, i, base, E) : -1;
+        const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
+        if (b >= 0 && (peers & ((1u << lane) - 1u)) == 0) atomicAdd(sm + b, __popc(peers));
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < EB; b += SORT_THREADS) inv[lo + b] = sm[b];
+}
+
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_scan_kernel(int E, int chunks, int32_t* __restrict__ inv, int32_t* __restrict__ offsets, int tile_m,
+                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0, int32_t* __restrict__ num_tiles) {
+    __shared__ int wsum_c[SORT_WARPS], wsum_t[SORT_WARPS];
+    const int EB = E + 1, b = threadIdx.x, warp = b >> 5, lane = b & 31;       // EB <= SORT_THREADS
+    int c = 0;
+    if (b < EB)
+        for (int ch = 0; ch < chunks; ++ch) c += inv[ch * SORT_THREADS + b];
+    const int tl = b < E ? (c + tile_m - 1) / tile_m : 0;
+    int ic = c, it = tl;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int vc = __shfl_up_sync(0xFFFFFFFFu, ic, d), vt = __shfl_up_sync(0xFFFFFFFFu, it, d);
+        if (lane >= d) { ic += vc; it += vt; }
+    }
+    if (lane == 31) { wsum_c[warp] = ic; wsum_t[warp] = it; }
+    __syncthreads();
+    if (warp == 0) {
+        int vc = wsum_c[lane], vt = wsum_t[lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int uc = __shfl_up_sync(0xFFFFFFFFu, vc, d), ut = __shfl_up_sync(0xFFFFFFFFu, vt, d);
+            if (lane >= d) { vc += uc; vt += ut; }
+        }
+        wsum_c[lane] = vc; wsum_t[lane] = vt;
+    }
+    __syncthreads();
+    int run = (warp > 0 ? wsum_c[warp - 1] : 0) + ic - c;
+    int tile = (warp > 0 ? wsum_t[warp - 1] : 0) + it - tl;
+    if (b < E) {
+        offsets[b] = run;
+        for (int r = 0; r < c; r += tile_m, ++tile) {
+            tile_expert[tile] = b;
+            tile_row0[tile] = run + r;
+        }
+    }
+    if (b == E) offsets[E] = run;
+    if (b == SORT_THREADS - 1) *num_tiles = wsum_t[SORT_WARPS - 1];
+    if (b < EB)
+        for (int ch = 0; ch < chunks; ++ch) {          // counts -> first position of (chunk, bucket)
+            const int v = inv[ch * SORT_THREADS + b];
+            inv[ch * SORT_THREADS + b] = run;
+            run += v;
+        }
+}
+
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_place_kernel(const int32_t* __restrict__ idx, int n, int E, int base, int chunks, int32_t* __restrict__ order,
+                      int32_t* __restrict__ inv) {
+    extern __shared__ int32_t sm[];                   // [SORT_WARPS + 1][E + 1]
+    const int EB = E + 1, c = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int32_t* wpos = sm;                               // per warp of the round: count, then first position
+    int32_t* next = sm + SORT_WARPS * EB;             // first free position of the bucket in this chunk
+    const int lo = c * SORT_THREADS, hi = c == chunks - 1 ? n : lo + SORT_THREADS;
+    for (int b = threadIdx.x; b < EB; b += SORT_THREADS) next[b] = inv[lo + b];
+    __syncthreads();                                  // the chunk's table is read before its inv entries are written
+    for (int i0 = lo; i0 < hi; i0 += SORT_THREADS) {
+        for (int j = threadIdx.x; j < SORT_WARPS * EB; j += SORT_THREADS) wpos[j] = 0;
+        __syncthreads();
+        const int i = i0 + threadIdx.x;
+        const int b = i < hi ? sort_bucket(idx, i, base, E) : -1;
         const unsigned peers = __match_any_sync(0xFFFFFFFFu, b);
         const int rank = __popc(peers & ((1u << lane) - 1u));
-        int pos = 0;
-        if (act) pos = cnt[warp * EB + b] + rank;
-        __syncwarp();
-        if (act && rank == 0) cnt[warp * EB + b] += __popc(peers);
-        __syncwarp();
-        if (act) {
+        if (b >= 0 && rank == 0) wpos[warp * EB + b] = __popc(peers);
+        __syncthreads();
+        for (int bb = threadIdx.x; bb < EB; bb += SORT_THREADS) {
+            int run = next[bb];
+            for (int w = 0; w < SORT_WARPS; ++w) {
+                const int v = wpos[w * EB + bb];
+                wpos[w * EB + bb] = run;
+                run += v;
+            }
+            next[bb] = run;
+        }
+        __syncthreads();
+        if (b >= 0) {
             if (b < E) {
+                const int pos = wpos[warp * EB + b] + rank;
                 order[pos] = i;
                 inv[i] = pos;
             } else {
                 inv[i] = -1;
             }
         }
+        __syncthreads();
     }
 }
 
@@ -145,8 +311,33 @@ __global__ void swiglu_kernel(const AT* __restrict__ g, const AT* __restrict__ u
                               float lim) {
     pdl_enter();
     const int n = count ? min(*count, max_rows) : max_rows;
+    // rows of whole 16-byte vectors (the grouped-GEMM outputs): 8 elements per thread and step, same arithmetic
+    const bool vec = (cols % 8 == 0) && (ld_in % 8 == 0) && (ld_out % 8 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(h)) % 16 == 0);
     for (int p = blockIdx.x; p < n; p += gridDim.x) {
         const float wt = w ? w[order ? order[p] : p] : 1.0f;
+        if (vec) {
+            for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+                const uint4 gq = __ldg(reinterpret_cast<const uint4*>(g + p * ld_in + c));
+                const uint4 uq = __ldg(reinterpret_cast<const uint4*>(u + p * ld_in + c));
+                const AT* ga = reinterpret_cast<const AT*>(&gq);
+                const AT* ua = reinterpret_cast<const AT*>(&uq);
+                uint4 hq;
+                AT* ha = reinterpret_cast<AT*>(&hq);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float gv = Elt<AT>::to_f32(ga[j]), uv = Elt<AT>::to_f32(ua[j]);
+                    if (lim > 0.f) {
+                        gv = fminf(gv, lim);
+                        uv = fminf(fmaxf(uv, -lim), lim);
+                    }
+                    const float sv = gv / (1.0f + __expf(-gv));
+                    ha[j] = Elt<AT>::from_f32(sv * uv * wt);
+                }
+                *reinterpret_cast<uint4*>(h + p * ld_out + c) = hq;
+            }
+            continue;
+        }
         for (int c = threadIdx.x; c < cols; c += blockDim.x) {
             float gv = Elt<AT>::to_f32(g[p * ld_in + c]), uv = Elt<AT>::to_f32(u[p * ld_in + c]);
             if (lim > 0.f) {
@@ -166,7 +357,46 @@ template <typename AT>
 __global__ void combine_kernel(const AT* __restrict__ y, int64_t ldy, const int32_t* __restrict__ inv,
                                const float* __restrict__ w, int T, int k, int D, AT* __restrict__ out, int64_t ldo,
                                float* __restrict__ out_f32, const AT* __restrict__ shared, int64_t ld_shared) {
+    // rows of whole 16-byte vectors: 8 columns per thread, the same sums in the same (slot) order
+    const bool vec = (D % 8 == 0) && (ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0) &&
+                     (out_f32 ? reinterpret_cast<uintptr_t>(out_f32) % 16 == 0
+                              : (ldo % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0)) &&
+                     (!shared || (ld_shared % 8 == 0 && reinterpret_cast<uintptr_t>(shared) % 16 == 0));
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        if (vec) {
+            for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+                float acc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                for (int j = 0; j < k; ++j) {
+                    const int p = inv ? inv[t * k + j] : t * k + j;
+                    if (p < 0) continue;
+                    const float wj = w ? w[t * k + j] : 1.0f;
+                    const uint4 q = __ldg(reinterpret_cast<const uint4*>(y + (int64_t)p * ldy + c));
+                    const AT* ya = reinterpret_cast<const AT*>(&q);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, Elt<AT>::to_f32(ya[i]), acc[i]);
+                }
+                if (shared) {
+                    const uint4 q = __ldg(reinterpret_cast<const uint4*>(shared + (int64_t)t * ld_shared + c));
+                    const AT* sa = reinterpret_cast<const AT*>(&q);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] += Elt<AT>::to_f32(sa[i]);
+                }
+                if (out_f32) {
+                    float4* o = reinterpret_cast<float4*>(out_f32 + (int64_t)t * D + c);
+                    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+                } else {
+                    uint4 oq;
+                    AT* oa = reinterpret_cast<AT*>(&oq);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) oa[i] = Elt<AT>::from_f32(acc[i]);
+                    *reinterpret_cast<uint4*>(out + (int64_t)t * ldo + c) = oq;
+                }
+            }
+            continue;
+        }
         for (int c = threadIdx.x; c < D; c += blockDim.x) {
             float acc = 0.f;
             for (int j = 0; j < k; ++j) {
@@ -549,6 +779,23 @@ int jq_moe_sort(const int32_t* topk_idx, int64_t n_pairs, int num_experts, int e
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         JQ_CUDA_OK(cudaFuncSetAttribute(moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    if (n_pairs >= 2 * SORT_THREADS && num_experts + 1 <= SORT_THREADS) {
+        // several CTAs: count, scan, place
+        static bool attr2_done[64] = {};
+        if (dev < 0 || dev >= 64 || !attr2_done[dev]) {
+            JQ_CUDA_OK(cudaFuncSetAttribute(moe_sort_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            if (dev >= 0 && dev < 64) attr2_done[dev] = true;
+        }
+        const int chunks = (int)(n_pairs / SORT_THREADS);
+        cudaStream_t st = (cudaStream_t)stream;
+        moe_sort_count_kernel<<<chunks, SORT_THREADS, (size_t)(num_experts + 1) * sizeof(int32_t), st>>>(
+            topk_idx, (int)n_pairs, num_experts, expert_base, chunks, inv);
+        moe_sort_scan_kernel<<<1, SORT_THREADS, 0, st>>>(num_experts, chunks, inv, expert_offsets, tile_m, tile_expert,
+                                                         tile_row0, num_tiles);
+        moe_sort_place_kernel<<<chunks, SORT_THREADS, smem, st>>>(topk_idx, (int)n_pairs, num_experts, expert_base, chunks,
+                                                                  order, inv);
+        return check_launch("moe_sort");
     }
     moe_sort_kernel<<<1, SORT_THREADS, smem, (cudaStream_t)stream>>>(topk_idx, (int)n_pairs, num_experts, expert_base,
                                                                       order, inv, expert_offsets, tile_m, tile_expert,

@@ -479,8 +479,12 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     }
     if (!ok) atomicOr(a.status, JQ_STATUS_LOCAL_WAIT);
     tc_fence_before();
-    __syncthreads();
+    const int gave_up = __syncthreads_or(ok ? 0 : 1);
     if (warp == 1) {
+        // after a wait that gave up, copies and MMAs of this CTA may still be in flight: give them a millisecond
+        // to land before the tensor memory goes back and the CTA's shared memory is reused
+        if (gave_up)
+            for (int i = 0; i < 1000; ++i) __nanosleep(1000);
         tc_fence_after();
         tmem_dealloc(tmem_base, MT * BN);
     }

@@ -111,7 +111,8 @@ __host__ __device__ constexpr uint32_t umma_idesc_i8(int n) {
 // issue slots a hot polling loop takes from the MMA-issuing warps of the same SM.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t max_polls) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < max_polls; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -122,8 +123,12 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
             : "memory");
         if (done) return true;
         __nanosleep(64);
+        if ((i & 255u) == 255u) {
+            const unsigned long long now = wall_ns();
+            if (t0 == 0) t0 = now;
+            else if (i >= max_polls && now - t0 > MBAR_WAIT_NS) return false;
+        }
     }
-    return false;
 }
 
 // Warp-wide bounded wait: lane 0 polls, the outcome is broadcast (32 lanes polling the same mbarrier

@@ -407,9 +407,9 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
     with torch.cuda.device(dev):
         use_sorted = P >= SORT_THRESHOLD if few_token_path is None else not few_token_path
         if use_sorted and gate.gemm_ok and up.gemm_ok and down.gemm_ok:
-            # experts with more than 128 rows on average: 256-row tiles, two accumulators per CTA share every
+            # experts with at least 256 rows on average: 256-row tiles, two accumulators per CTA share every
             # dequantized weight tile (bf16, all three projections at least 256 wide)
-            big = (x.dtype == torch.bfloat16 and min(gate.N, up.N, down.N) >= 256 and P >= 96 * gate.E)
+            big = (x.dtype == torch.bfloat16 and min(gate.N, up.N, down.N) >= 256 and P >= 256 * gate.E)
             sp = SortedPairs(idx32, gate.E, expert_base, tile_m=256 if big else 128)
             xs = _gather_rows(x, sp, k)
             g = _moe_gemm(xs, sp, gate)

@@ -23,6 +23,11 @@ def main():
     g = torch.Generator(device=dev).manual_seed(5)              # x: the same on every rank
     gy = torch.Generator(device=dev).manual_seed(100 + rank)    # y: the rank's own
     eps = torch.finfo(torch.bfloat16).eps
+    failures = []       # recorded, not raised: every rank runs the same sequence of collectives to the end
+
+    def expect(cond, what):
+        if not bool(cond):
+            failures.append(what)
 
     def reference(x, y):
         part = y.float().reshape(T, k, H).sum(dim=1)
@@ -35,10 +40,10 @@ def main():
         y = (torch.randn((T * k, H), device=dev, generator=gy) * 0.3).to(torch.bfloat16)
         out = moe_ep.peer_combine_residual_rmsnorm(x, y, k, ex)
         ref = reference(x, y)
-        assert (out.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max(), (rank, rep)
+        expect((out.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max(), f"eager exchange, rep {rep}")
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
-        assert all(torch.equal(gathered[0], o) for o in gathered), "ranks disagree bit-wise"
+        expect(all(torch.equal(gathered[0], o) for o in gathered), "ranks disagree bit-wise")
     # the same call replayed from a CUDA graph
     x = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
     y = (torch.randn((T * k, H), device=dev, generator=gy) * 0.3).to(torch.bfloat16)
@@ -55,7 +60,7 @@ def main():
     for _ in range(5):
         gr.replay()
     torch.cuda.synchronize()
-    assert (out.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max()
+    expect((out.float() - ref).abs().max() <= 2.0 ** -7 * ref.abs().max(), "graph replay")
     # the decode stack: peer mode against the NCCL mode, two layers
     xs = torch.randn((world, H), device=dev, generator=g).to(torch.bfloat16)
     outs = {}
@@ -63,12 +68,18 @@ def main():
         st = MoEDecodeStack(layers=2, device=dev, rank=rank, world=world, ep_mode=mode)
         outs[mode] = st.step(xs).float()
     torch.cuda.synchronize()
-    assert (outs["peer"] - outs["replicated"]).abs().max() <= 2.0 ** -5 * outs["replicated"].abs().max()
-    _lib.check(_lib.load().jq_device_status())
-    dist.barrier()
-    if rank == 0:
+    expect((outs["peer"] - outs["replicated"]).abs().max() <= 2.0 ** -5 * outs["replicated"].abs().max(),
+           "decode stack: peer against replicated")
+    expect(_lib.load().jq_device_status() == _lib.JQ_OK, "device status word set")
+    # the ranks agree on the verdict between steps, with nothing in flight, and all leave through the same door
+    bad = torch.tensor([len(failures)], device=dev, dtype=torch.int32)
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if failures:
+        print(f"EP_PEER_FAIL rank {rank}: {failures}", flush=True)
+    if rank == 0 and int(bad.item()) == 0:
         print("EP_PEER_OK")
     dist.destroy_process_group()
+    sys.exit(1 if int(bad.item()) else 0)
 
 
 if __name__ == "__main__":
