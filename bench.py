@@ -443,6 +443,39 @@ def run_moe(args, device, world, rank, barrier):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / K
     finite = bool(torch.isfinite(out.float()).all())
+    # strong scaling: ONE token per step on all N GPUs (every rank runs the dense blocks on it, its own experts, one
+    # exchange per layer): the batch-1 latency the path is named for, next to the weak-scaling throughput above
+    strong = None
+    if world > 1:
+        try:
+            x1 = x[:1].contiguous()
+            stack.step(x1)
+            torch.cuda.synchronize()
+            s1 = torch.cuda.Stream()
+            s1.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s1):
+                stack.step(x1)
+            torch.cuda.current_stream().wait_stream(s1)
+            torch.cuda.synchronize()
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1):
+                stack.step(x1)
+            for _ in range(W):
+                g1.replay()
+            barrier()
+            ev0.record()
+            for _ in range(K):
+                g1.replay()
+            ev1.record()
+            barrier()
+            t1 = torch.tensor([ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
+            dist.all_reduce(t1, op=dist.ReduceOp.MAX)
+            ms1 = float(t1.item()) / K
+            strong = {"tokens_per_step": 1, "ms_per_step": ms1, "tok_s": 1.0 / (ms1 * 1e-3),
+                      "note": "one token on all N GPUs: per-token latency; the dense half is replicated, so N GPUs buy no "
+                              "latency on this path"}
+        except Exception as e:
+            strong = {"error": f"{type(e).__name__}: {e}"}
     peak = 6464.6
     try:
         peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
@@ -478,7 +511,8 @@ def run_moe(args, device, world, rank, barrier):
                        "N>1: all-to-all dispatch/combine of the rank's 2048 tokens", "exchange": exchange}
     gbs = stack.bytes_per_token / (ms * 1e-3) / 1e9
     parity = moe_parity(stack, x, xp, device, world, rank) if world > 1 else None
-    return {"parity": parity, "prefill": prefill, "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
+    return {"parity": parity, "prefill": prefill, "strong_scaling": strong, "scaling_of_tok_s": "weak (one token per GPU and step)",
+            "tok_s": world / (ms * 1e-3), "ms_per_step": ms, "tokens_per_step": world, "bytes_per_token": stack.bytes_per_token,
             "per_gpu_GBps": gbs, "hbm_frac": gbs / peak, "graph": graph is not None, "finite": finite,
             "ep_mode": ep_mode if world > 1 else None,
             "workload": "config3 MoE stack, batch-1 decode per GPU: 48 layers x [q,k,v,o @6b + bf16 router + top-8 of "
