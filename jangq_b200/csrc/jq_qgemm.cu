@@ -155,10 +155,27 @@ template <int BITS, int BN, int MT> struct CodeStage {
                                    2 * BN * RBP;
 };
 
+__device__ __forceinline__ void gemm_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f32x4(const float* own, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(own)), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+constexpr int KS_PITCH = 256 + 4;     // floats per staged accumulator row: 16 bytes of skew keep 16-byte accesses apart
+
 // MT: 128-row tiles of the activations per CTA (1 or 2).  With 2 every dequantized weight tile feeds two
 // accumulators (2 x BN columns of tensor memory), which halves the dequantizer work per flop: the kernel is
 // bound by the dequantizer warps, not by the tensor pipe, with one.
-template <typename AT, int BITS, int BN, int DPR, int MT>
+// KS: CTAs of a cluster (along blockIdx.z) that split K, for grids that would leave most SMs idle: every CTA
+// accumulates its share of the k-blocks in its own tensor memory; the others stage their accumulators as float32
+// in their (by then idle) shared memory, and CTA 0 of the cluster adds them through distributed shared memory
+// in rank order and stores the tile.  Both cluster barriers are reached by every thread on every path.
+template <typename AT, int BITS, int BN, int DPR, int MT, int KS = 1>
 __global__ void __launch_bounds__(64 + BN * DPR)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     using A = Act<AT>;
@@ -213,7 +230,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         scales_g = a.scales_tab[e];
         biases_g = a.biases_tab[e];
     }
-    const int nkb = (int)(a.K / GEMM_BK);
+    // this CTA's k-blocks [kb0, kb1): all of them, or its share (whole code stages) of a split K
+    const int nkb_all = (int)(a.K / GEMM_BK);
+    int kb0 = 0, kb1 = nkb_all;
+    const int ks_rank = KS > 1 ? (int)blockIdx.z : 0;
+    if constexpr (KS > 1) {
+        kb0 = (ks_rank * nkb_all / KS) / CKB * CKB;
+        kb1 = ks_rank == KS - 1 ? nkb_all : ((ks_rank + 1) * nkb_all / KS) / CKB * CKB;
+    }
+    const int nkb = kb1 - kb0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < GEMM_SA; ++i) { mbar_init(xfull + i, 1); mbar_init(xempty + i, 1); }
@@ -231,21 +256,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % GEMM_SA;
-                if (kb >= GEMM_SA) ok = mbar_wait(xempty + s, (uint32_t)((kb / GEMM_SA) - 1) & 1u, 1u << 18);
+            for (int lk = 0; lk < nkb && ok; ++lk) {
+                const int s = lk % GEMM_SA;
+                if (lk >= GEMM_SA) ok = mbar_wait(xempty + s, (uint32_t)((lk / GEMM_SA) - 1) & 1u, 1u << 18);
                 if (!ok) break;
                 mbar_expect_tx(xfull + s, A_STAGE);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)      // rows past M read as zeros
-                    tma_load_2d(sA + s * A_STAGE + mt * A_TILE, &xmap, kb * GEMM_BK, (int)m0 + mt * GEMM_BM, xfull + s);
+                    tma_load_2d(sA + s * A_STAGE + mt * A_TILE, &xmap, (kb0 + lk) * GEMM_BK, (int)m0 + mt * GEMM_BM,
+                                xfull + s);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc<AT, BN>();
-            for (int kb = 0; kb < nkb && ok; ++kb) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {      // kb: local index
                 const int s = kb % GEMM_SA, t = kb % GEMM_SB;
                 ok = mbar_wait(xfull + s, (uint32_t)(kb / GEMM_SA) & 1u, 1u << 18) &&
                      mbar_wait(bfull + t, (uint32_t)(kb / GEMM_SB) & 1u, 1u << 18);
@@ -276,7 +302,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
         const uint32_t sw = (uint32_t)(r & 7);
         const int gs = a.gs;
-        const int nstage = (nkb + CKB - 1) / CKB;
+        const int st0 = kb0 / CKB, nstage = (kb1 + CKB - 1) / CKB;     // code stages [st0, nstage) (absolute)
 
         // all dequantizer threads copy code stage `st` together: consecutive lanes take consecutive
         // 16-byte chunks of a row; always one commit so that group counting stays uniform
@@ -340,26 +366,28 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         };
         uint16_t s0h = 0, b0h = 0, s1h = 0, b1h = 0, s0n = 0, b0n = 0, s1n = 0, b1n = 0;
         if (sc_vec) {
-            load_sc_stage(0, scw, bcw);
+            load_sc_stage(st0, scw, bcw);
         } else {
-            s0h = __ldg(srow); b0h = __ldg(brow);
+            const int g0 = kb0 * GEMM_BK / gs;
+            s0h = __ldg(srow + g0); b0h = __ldg(brow + g0);
             s1h = s0h; b1h = b0h;
-            if (gs == 32) { s1h = __ldg(srow + 1); b1h = __ldg(brow + 1); }
+            if (gs == 32) { s1h = __ldg(srow + g0 + 1); b1h = __ldg(brow + g0 + 1); }
         }
-        issue_codes(0, 0);
+        issue_codes(st0, 0);
         // After a timed-out wait the warp keeps walking the loops (copies and the named barrier
         // only), so that no other dequantizer warp is left waiting at the barrier.
-        for (int st = 0; st < nstage; ++st) {
+        for (int st = st0; st < nstage; ++st) {
             cp_async_wait<0>();
             asm volatile("bar.sync 1, %0;" ::"n"(NDT) : "memory");  // stage st landed; stage st-1 fully consumed
-            issue_codes(st + 1, (st + 1) & 1);
+            issue_codes(st + 1, (st + 1 - st0) & 1);
             if (sc_vec && st + 1 < nstage) load_sc_stage(st + 1, scn, bcn);
-            const uint8_t* crow = sC + (st & 1) * C_STAGE + r * RBP;
+            const uint8_t* crow = sC + ((st - st0) & 1) * C_STAGE + r * RBP;
 #pragma unroll
             for (int kbi = 0; kbi < CKB; ++kbi) {
-                const int kb = st * CKB + kbi;
-                if (kb >= nkb) break;
-                const int t = kb % GEMM_SB;
+                const int kb = st * CKB + kbi;             // absolute k-block; lk: its index in this CTA's share
+                if (kb >= kb1) break;
+                const int lk = kb - kb0;
+                const int t = lk % GEMM_SB;
                 uint32_t cur[UW];
                 if constexpr (DPR == 1) {
                     if constexpr ((8 * BITS) % 16 == 0) {
@@ -400,7 +428,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                     s0h = (uint16_t)((gi & 1) ? (swd >> 16) : (swd & 0xFFFFu));
                     b0h = (uint16_t)((gi & 1) ? (bwd >> 16) : (bwd & 0xFFFFu));
                     s1h = s0h; b1h = b0h;
-                } else if (kb + 1 < nkb) {        // scalar path: sidecars of the next k-block
+                } else if (kb + 1 < kb1) {        // scalar path: sidecars of the next k-block
                     const int k1 = (kb + 1) * GEMM_BK;
                     const int g0 = k1 / gs;
                     s0n = __ldg(srow + g0); b0n = __ldg(brow + g0);
@@ -413,8 +441,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                 // s * 2^-TGT is exact (power-of-two scaling) unless it underflows the 16-bit type
                 const uint32_t sp0 = A::pack_hi(s0 * POST, s0 * POST), sp1 = A::pack_hi(s1 * POST, s1 * POST);
                 const uint32_t bb0 = (uint32_t)b0h * 0x00010001u, bb1 = (uint32_t)b1h * 0x00010001u;
-                if (ok && kb >= GEMM_SB)   // warp-uniform outcome
-                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(bempty + t, (uint32_t)((kb / GEMM_SB) - 1) & 1u, 1u << 18));
+                if (ok && lk >= GEMM_SB)   // warp-uniform outcome
+                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(bempty + t, (uint32_t)((lk / GEMM_SB) - 1) & 1u, 1u << 18));
                 if (ok) {
                     uint8_t* dst = sB + t * B_STAGE + row_off;
 #define JQ_CHUNK(C, SP, BB, S, BI) \
@@ -443,7 +471,28 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
 
         // ---------------- epilogue: TMEM -> registers -> Y ----------------
         if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(accfull, 0, 1u << 18));
-        if (ok) {
+        if constexpr (KS > 1) {
+            // split K: the accumulator is complete, so nothing reads this CTA's stages any more; the CTAs behind
+            // rank 0 leave theirs as float32 rows at the start of their shared memory (rank 0 stores after the
+            // cluster barrier below)
+            if (ok && ks_rank != 0) {
+                tc_fence_after();
+                const int q = warp & 3, part = (warp - 2) / 4;
+                constexpr int COLS_PER_WARP = BN / (NDW / 4);
+                float* srow_f = reinterpret_cast<float*>(smem) + (size_t)(q * 32 + lane) * KS_PITCH;
+#pragma unroll 1
+                for (int c0 = part * COLS_PER_WARP; c0 < (part + 1) * COLS_PER_WARP; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(srow_f + c0 + 4 * j) =
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                }
+            }
+        }
+        if (KS == 1 && ok) {
             tc_fence_after();
             const int q = warp & 3;                               // TMEM lane quarter this warp may read
             const int part = (warp - 2) / 4;                      // the NDW/4 warps of a quarter split the columns
@@ -477,6 +526,51 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
             }
         }
     }
+    if constexpr (KS > 1) {
+        static_assert(KS == 1 || (MT == 1 && BN == 256), "split K: one 128 x 256 accumulator per CTA");
+        gemm_cluster_sync();                               // the staged accumulators are complete
+        if (warp >= 2 && ks_rank == 0 && ok) {
+            tc_fence_after();
+            const int q = warp & 3, part = (warp - 2) / 4;
+            constexpr int COLS_PER_WARP = BN / (NDW / 4);
+            const float* srow_f = reinterpret_cast<const float*>(smem) + (size_t)(q * 32 + lane) * KS_PITCH;
+            const int64_t m = m0 + q * 32 + lane;
+            uint16_t* yrow = reinterpret_cast<uint16_t*>(a.y) + m * a.ldy + n0;
+#pragma unroll 1
+            for (int c0 = part * COLS_PER_WARP; c0 < (part + 1) * COLS_PER_WARP; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                float f[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                for (int rk = 1; rk < KS; ++rk) {           // rank order: the same sum whatever the timing
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 t = ld_cluster_f32x4(srow_f + c0 + 4 * j, (uint32_t)rk);
+                        f[4 * j] += t.x; f[4 * j + 1] += t.y; f[4 * j + 2] += t.z; f[4 * j + 3] += t.w;
+                    }
+                }
+                if (m < m_end) {
+                    if (a.y_vec_ok && n0 + c0 + 32 <= a.N) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 o;
+                            o.x = A::pack_hi(f[8 * j + 0], f[8 * j + 1]);
+                            o.y = A::pack_hi(f[8 * j + 2], f[8 * j + 3]);
+                            o.z = A::pack_hi(f[8 * j + 4], f[8 * j + 5]);
+                            o.w = A::pack_hi(f[8 * j + 6], f[8 * j + 7]);
+                            *reinterpret_cast<uint4*>(yrow + c0 + 8 * j) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c0 + j < a.N) yrow[c0 + j] = A::from_f32(f[j]);
+                    }
+                }
+            }
+        }
+        gemm_cluster_sync();                               // the others keep their shared memory until rank 0 has read it
+    }
     if (!ok) atomicOr(a.status, JQ_STATUS_LOCAL_WAIT);
     tc_fence_before();
     const int gave_up = __syncthreads_or(ok ? 0 : 1);
@@ -506,20 +600,35 @@ EncodeTiledFn encode_tiled_fn() {
 
 // m_tiles: 128-row tiles of a dense GEMM (MT of them per CTA), or entries of a grouped GEMM's tile list (one CTA
 // each, whatever MT)
-template <typename AT, int BITS, int BN, int DPR, int MT = 1>
+template <typename AT, int BITS, int BN, int DPR, int MT = 1, int KS = 1>
 static int launch_gemm(const CUtensorMap& xmap, const GemmArgs& a, int64_t m_tiles, cudaStream_t st) {
     constexpr size_t smem = CodeStage<BITS, BN, MT>::SMEM;
     static_assert(smem <= GEMM_SMEM, "shared memory of one CTA");
+    static_assert(KS == 1 || 1024 + 128 * KS_PITCH * sizeof(float) <= smem - 512, "staged accumulator fits the stages");
     static bool attr_done[64] = {};
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN, DPR, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JQ_CUDA_OK(cudaFuncSetAttribute(qgemm_tc_kernel<AT, BITS, BN, DPR, MT, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)(a.tile_expert ? m_tiles : (m_tiles + MT - 1) / MT));
-    qgemm_tc_kernel<AT, BITS, BN, DPR, MT><<<grid, 64 + BN * DPR, smem, st>>>(xmap, a);
+    dim3 grid((unsigned)((a.N + BN - 1) / BN), (unsigned)(a.tile_expert ? m_tiles : (m_tiles + MT - 1) / MT), KS);
+    if constexpr (KS > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(64 + BN * DPR);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = KS;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, qgemm_tc_kernel<AT, BITS, BN, DPR, MT, KS>, xmap, a));
+        return JQ_OK;
+    }
+    qgemm_tc_kernel<AT, BITS, BN, DPR, MT, KS><<<grid, 64 + BN * DPR, smem, st>>>(xmap, a);
     return check_launch("qgemm");
 }
 
@@ -590,12 +699,34 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
     const bool wide = N >= 256;
     JQ_REQUIRE(!grp || grp->tile_m == 128 || (grp->tile_m == 256 && wide && x_dtype == JQ_BF16), JQ_EUNSUPPORTED,
                "tile lists of 256 rows need bf16 activations and N >= 256 (128 otherwise)");
-    const bool two = grp ? grp->tile_m == 256
-                         : wide && ((N + 255) / 256) * ((m_tiles + 1) / 2) >= (int64_t)sm_count() * 3 / 4;
+    // Dense GEMMs pick the form with the shortest estimated time.  A CTA walks a k-block in about 1.1 us with one
+    // accumulator and 1.3 us with two (measured; the dequantizer warps set the pace), whatever the grid, so what
+    // counts is the number of waves and the k-blocks per CTA:
+    //   one accumulator            waves(tiles)      * nkb * 1.1
+    //   two accumulators (MT = 2)  waves(tiles / 2)  * nkb * 1.3     (every weight tile dequantized once for two)
+    //   split K over S CTAs        waves(tiles * S)  * (nkb / S * 1.1 + 8)   (8 us: staging and adding the accumulators)
+    bool two = grp ? grp->tile_m == 256 : false;
+    int ksplit = 1;
+    if (!grp && wide && x_dtype == JQ_BF16) {
+        const int64_t sms = sm_count(), ncol = (N + 255) / 256, nkb_all = K / GEMM_BK;
+        auto waves = [&](int64_t ctas) { return (double)((ctas + sms - 1) / sms); };
+        double best = waves(ncol * m_tiles) * nkb_all * 1.1;
+        if (m_tiles >= 2) {
+            const double t2 = waves(ncol * ((m_tiles + 1) / 2)) * nkb_all * 1.3;
+            if (t2 < best) { best = t2; two = true; }
+        }
+        for (int S : {2, 4}) {
+            if (nkb_all / S < 16) continue;
+            const double ts = waves(ncol * m_tiles * S) * ((double)nkb_all / S * 1.1 + 8.0);
+            if (ts < best) { best = ts; two = false; ksplit = S; }
+        }
+    }
 #define JQ_GEMM_CASE(B)                                                                                  \
     if (bits == B) {                                                                                     \
         if (x_dtype == JQ_BF16) {                                                                        \
             if (two) return launch_gemm<__nv_bfloat16, B, 256, 1, 2>(xmap, a, m_tiles, st);              \
+            if (ksplit == 4) return launch_gemm<__nv_bfloat16, B, 256, 1, 1, 4>(xmap, a, m_tiles, st);  \
+            if (ksplit == 2) return launch_gemm<__nv_bfloat16, B, 256, 1, 1, 2>(xmap, a, m_tiles, st);  \
             return wide ? launch_gemm<__nv_bfloat16, B, 256, 1>(xmap, a, m_tiles, st)                    \
                         : launch_gemm<__nv_bfloat16, B, 128, 1>(xmap, a, m_tiles, st);                   \
         }                                                                                                \

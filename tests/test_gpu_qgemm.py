@@ -133,3 +133,18 @@ def test_qgemm_two_row_tiles_equal_one_row_tile_results():
     y1 = jq.quantized_matmul(x, wq[:512].contiguous(), s[:512].contiguous(), b[:512].contiguous(), group_size=gs,
                              bits=bits)                                               # 2 x 8 CTAs: one tile each
     assert torch.equal(y2[:, :512], y1)
+
+
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+@pytest.mark.parametrize("M,N,K,gs", ((200, 1000, 2048, 64), (130, 520, 4096, 128), (512, 4096, 4096, 64), (40, 300, 4480, 64)))
+def test_qgemm_split_k_over_a_cluster(bits, M, N, K, gs):
+    """Grids far below the SM count split K over a cluster of 2 or 4 CTAs whose accumulators meet in distributed
+    shared memory: ragged rows and columns, K shares that are not equal (4480 = 70 k-blocks), every width."""
+    if bits in (3, 5) and K % 128:
+        K += 64
+    x, wq, s, b = make_case(M, N, K, bits, gs, torch.bfloat16, seed=bits * 7 + M)
+    y = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
+    check(y, x, wq, s, b, bits, gs, torch.bfloat16)
+    y2 = jq.quantized_matmul(x, wq, s, b, group_size=gs, bits=bits)
+    assert torch.equal(y, y2)                                  # the partial sums are added in rank order
+    _lib.check(_lib.load().jq_device_status())
