@@ -307,7 +307,7 @@ int jq_gather_qgemv2(const void* x, int act_dtype, int64_t ldx, int x_div, const
  * disappears: y[p, :] = deq(W[pair_expert[p] - expert_base]) . h[p, :] with
  * h[p, :] = silu(min(g[p, :], limit)) * clip(u[p, :], +-limit) * weights[p], rounded to the activation type --
  * jq_moe_swiglu followed by jq_gather_qgemv2 with x_div = 1.  gate/up: [pairs, K] of the activation type, leading
- * dimension ld_in.  Up to 16 pairs of one width (2, 4, 6 or 8 bits, bits_tab NULL) run as one launch and need no
+ * dimension ld_in.  Up to 16 pairs of one width (2, 3, 4, 6 or 8 bits, bits_tab NULL) run as one launch and need no
  * scratch; any other case runs the two launches through h_scratch ([pairs, K], activation type; JQ_EWORKSPACE when
  * it is needed and NULL). */
 int jq_gather_qgemv_swiglu(const void* gate, const void* up, int act_dtype, int64_t ld_in, const float* weights,

@@ -61,12 +61,25 @@ __device__ __forceinline__ void to_bytes(const uint32_t (&u)[Unit<BITS>::WORDS],
         r[2] = u[0] & 0x30303030u; r[3] = u[0] & 0xC0C0C0C0u;
     }
 }
+// 3-bit codes: the lane's 16 codes are two units of 8 codes = 24 bits.  Inside a unit six codes sit whole inside
+// one of its three bytes (c0, c1 in byte 0; c3, c4 in byte 1; c6, c7 in byte 2) and are taken with one AND each
+// way; the two that straddle a byte boundary (c2, c5) need one shift of the unit.  A unit thus becomes three
+// operand registers with the bytes (c0, 2 c3, 4 c6, 0), (8 c1, 16 c4, 32 c7, 0), (c2, 2 c5, 0, 0): 8 codes on 12 byte
+// positions, so a 64-code block takes three MMAs instead of two; the activation limbs leave the same gaps.
+__device__ __forceinline__ void to_bytes3(const uint32_t (&u)[2], uint32_t (&r)[6]) {
+    const uint32_t g0 = u[0], g1 = funnel_r(u[0], u[1], 24);
+    r[0] = g0 & 0x001C0E07u; r[1] = g0 & 0x00E07038u; r[2] = (g0 >> 6) & 0x00000E07u;
+    r[3] = g1 & 0x001C0E07u; r[4] = g1 & 0x00E07038u; r[5] = (g1 >> 6) & 0x00000E07u;
+}
 template <int BITS> __host__ __device__ constexpr int elem(int i, int t) {
     return BITS == 2 ? i + 4 * t : BITS == 4 ? 8 * (i >> 1) + (i & 1) + 2 * t : 4 * i + t;
 }
 // log2 of the factor the code of element j carries inside its byte
 template <int BITS> __host__ __device__ constexpr int code_shift(int j) {
-    return BITS == 2 ? 2 * (j & 3) : BITS == 4 ? 4 * (j & 1) : 0;
+    return BITS == 2 ? 2 * (j & 3) : BITS == 4 ? 4 * (j & 1)
+         : BITS == 3 ? ((j & 7) == 1 ? 3 : (j & 7) == 3 ? 1 : (j & 7) == 4 ? 4 : (j & 7) == 5 ? 1 : (j & 7) == 6 ? 2
+                        : (j & 7) == 7 ? 5 : 0)
+         : 0;
 }
 
 }  // namespace imma_ops

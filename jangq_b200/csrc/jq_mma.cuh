@@ -349,4 +349,21 @@ __device__ __forceinline__ void store_limbs8(uint8_t* d0, uint8_t* d1, uint8_t* 
     }
 }
 
+// The same for a unit of 8 three-bit codes: 12 bytes per limb row, (x0, x3, x6, 0), (x1, x4, x7, 0), (x2, x5, 0, 0)
+// -- the byte positions the 3-bit unpack of the integer kernels leaves its codes at.
+__device__ __forceinline__ void store_limbs3(uint8_t* d0, uint8_t* d1, uint8_t* d2, const int (&xi)[8]) {
+    uint32_t t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = ((uint32_t)xi[j] + 0x8080u) ^ 0x8080u;
+    uint8_t* const d[3] = {d0, d1, d2};
+#pragma unroll
+    for (int L = 0; L < 3; ++L) {
+        const uint32_t sel = (uint32_t)(((4 + L) << 4) | L);
+        uint32_t* o = reinterpret_cast<uint32_t*>(d[L]);
+        o[0] = prmt(prmt(t[0], t[3], sel), prmt(t[6], 0u, sel), 0x5410);
+        o[1] = prmt(prmt(t[1], t[4], sel), prmt(t[7], 0u, sel), 0x5410);
+        o[2] = prmt(prmt(t[2], t[5], sel), 0u, 0x5410);
+    }
+}
+
 }  // namespace jq

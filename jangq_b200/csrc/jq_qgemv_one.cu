@@ -22,8 +22,8 @@ namespace one {
 
 using namespace stream;
 
-__host__ __device__ inline size_t one_head_bytes(int K, int nw) {
-    const size_t limbs = ((size_t)3 * limb_stride(K) + 127) / 128 * 128;
+__host__ __device__ inline size_t one_head_bytes(int K, int nw, int bits = 8) {
+    const size_t limbs = ((size_t)3 * limb_stride_bits(K, bits) + 127) / 128 * 128;
     return HEAD0 + MAXT * sizeof(TileInfo) + 128 + (size_t)(K / 64) * 16 + limbs + (size_t)nw * MAXT * 16 * sizeof(float);
 }
 
@@ -35,7 +35,7 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = (int)a.K, G = a.G, TPC = a.ksplit;          // ksplit: 16-row tiles per CTA in this kernel
-    const int LS = limb_stride(K);
+    const int LS = limb_stride_bits(K, BITS);
     constexpr int RB = rowb_of(BITS);
     const int rowbytes = K * BITS / 8;
     const int nst = (rowbytes + RB - 1) / RB;
@@ -46,7 +46,7 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
     float2* tab = reinterpret_cast<float2*>(part + 32);                                 // [K / 64][2]
     uint8_t* limbs = reinterpret_cast<uint8_t*>(tab) + (size_t)(K / 64) * 16;           // [3][LS]
     float* ysum = reinterpret_cast<float*>(limbs + ((size_t)3 * LS + 127) / 128 * 128);  // [NW][MAXT * 16]
-    uint8_t* ring = smem + one_head_bytes(K, NW) + (size_t)warp * 2 * SLOT;
+    uint8_t* ring = smem + one_head_bytes(K, NW, BITS) + (size_t)warp * 2 * SLOT;
     float* myy = ysum + (size_t)warp * MAXT * 16;
 
     // tiles of all matrices of the launch are numbered consecutively; blk_end[i] = first tile after matrix i
@@ -176,7 +176,7 @@ qgemv_one_kernel(const GemvArgs a, const GemvBatch bt) {
 
 template <typename AT, int BITS, int GS, int NW>
 static int launch_cfg(GemvArgs a, const GemvBatch& bt, int tpc, int grid, cudaStream_t st, bool* launched) {
-    const size_t smem = one_head_bytes((int)a.K, NW) + (size_t)NW * 2 * SLOT;
+    const size_t smem = one_head_bytes((int)a.K, NW, BITS) + (size_t)NW * 2 * SLOT;
     static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
@@ -215,7 +215,7 @@ static int launch_shape(const GemvArgs& a, GemvBatch bt, cudaStream_t st, bool* 
     const int grid = (int)((tiles + tpc - 1) / tpc);
     if (tpc > MAXT) return JQ_OK;                                 // too many rows for one launch of this kernel
     for (int nw : {16, 12, 8}) {
-        if (one_head_bytes((int)a.K, nw) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
+        if (one_head_bytes((int)a.K, nw, BITS) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
         if (a.norm_res != nullptr && a.K > 8 * 32 * nw) return JQ_OK;     // the row must fit the CTA's registers
         if (nw == 16) return launch_cfg<AT, BITS, GS, 16>(a, bt, tpc, grid, st, launched);
         if (nw == 12) return launch_cfg<AT, BITS, GS, 12>(a, bt, tpc, grid, st, launched);
@@ -247,8 +247,8 @@ struct GatherArgs {
     int tpc;                          // 16-row tiles per CTA
 };
 
-__host__ __device__ inline size_t gather_head_bytes(int K, int nx, int nw) {
-    const size_t limbs = ((size_t)nx * 3 * limb_stride(K) + 127) / 128 * 128;
+__host__ __device__ inline size_t gather_head_bytes(int K, int nx, int nw, int bits = 8) {
+    const size_t limbs = ((size_t)nx * 3 * limb_stride_bits(K, bits) + 127) / 128 * 128;
     return HEAD0 + MAXT * sizeof(TileInfo) + MAXT * sizeof(void*) + 16 + (size_t)nx * (K / 64) * 16 + limbs +
            (size_t)nw * MAXT * 16 * sizeof(float);
 }
@@ -261,7 +261,7 @@ gather_one_kernel(const GatherArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = a.K, G = a.G, N = a.N;
-    const int LS = limb_stride(K);
+    const int LS = limb_stride_bits(K, BITS);
     constexpr int RB = rowb_of(BITS);
     const int rowbytes = K * BITS / 8;
     const int nst = (rowbytes + RB - 1) / RB;
@@ -276,7 +276,7 @@ gather_one_kernel(const GatherArgs a) {
     float2* tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(ytile + MAXT) + 16);   // [nx][K / 64][2]
     uint8_t* limbs = reinterpret_cast<uint8_t*>(tab) + (size_t)nx * (K / 64) * 16;         // [nx][3][LS]
     float* ysum = reinterpret_cast<float*>(limbs + ((size_t)nx * 3 * LS + 127) / 128 * 128);
-    uint8_t* ring = smem + gather_head_bytes(K, nx, NW) + (size_t)warp * 2 * SLOT;
+    uint8_t* ring = smem + gather_head_bytes(K, nx, NW, BITS) + (size_t)warp * 2 * SLOT;
     float* myy = ysum + (size_t)warp * MAXT * 16;
 
     for (int i = tid; i < ZERO_BYTES / 4; i += THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
@@ -366,7 +366,7 @@ gather_one_kernel(const GatherArgs a) {
 
 template <typename AT, int BITS, int GS, int NW>
 static int launch_gather_cfg(const GatherArgs& a, int nx, int grid, bool pdl, cudaStream_t st, bool* launched) {
-    const size_t smem = gather_head_bytes(a.K, nx, NW) + (size_t)NW * 2 * SLOT;
+    const size_t smem = gather_head_bytes(a.K, nx, NW, BITS) + (size_t)NW * 2 * SLOT;
     static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
     int dev = 0;
     JQ_CUDA_OK(cudaGetDevice(&dev));
@@ -400,7 +400,7 @@ static int launch_gather_shape(GatherArgs a, bool pdl, cudaStream_t st, bool* la
     a.tpc = tpc;
     const int grid = (int)((tiles + tpc - 1) / tpc);
     for (int nw : {16, 12, 8}) {
-        if (gather_head_bytes(a.K, nx, nw) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
+        if (gather_head_bytes(a.K, nx, nw, BITS) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
         if (nw == 16) return launch_gather_cfg<AT, BITS, GS, 16>(a, nx, grid, pdl, st, launched);
         if (nw == 12) return launch_gather_cfg<AT, BITS, GS, 12>(a, nx, grid, pdl, st, launched);
         return launch_gather_cfg<AT, BITS, GS, 8>(a, nx, grid, pdl, st, launched);
@@ -416,15 +416,17 @@ static int launch_gather_shape(GatherArgs a, bool pdl, cudaStream_t st, bool* la
 int launch_one_kernel(const GemvArgs& a, const GemvBatch& bt, int act_dtype, int bits, int gs, cudaStream_t st,
                       bool* launched) {
     *launched = false;
-    if (!(bits == 2 || bits == 4 || bits == 6 || bits == 8) || a.M != 1 || a.K % (4 * gs) != 0 || a.K >= (1 << 24)) return JQ_OK;
+    if (!(bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8) || a.M != 1 || a.K % (4 * gs) != 0 ||
+        a.K >= (1 << 24))
+        return JQ_OK;
     int rc = JQ_OK;
 #define JQ_ONE_CASE(B, GSZ)                                                                          \
     if (bits == B && gs == GSZ) {                                                                    \
         rc = (act_dtype == JQ_BF16) ? one::launch_shape<__nv_bfloat16, B, GSZ>(a, bt, st, launched)  \
                                     : one::launch_shape<__half, B, GSZ>(a, bt, st, launched);        \
     }
-    JQ_ONE_CASE(2, 64) JQ_ONE_CASE(4, 64) JQ_ONE_CASE(6, 64) JQ_ONE_CASE(8, 64)
-    JQ_ONE_CASE(2, 128) JQ_ONE_CASE(4, 128) JQ_ONE_CASE(6, 128) JQ_ONE_CASE(8, 128)
+    JQ_ONE_CASE(2, 64) JQ_ONE_CASE(3, 64) JQ_ONE_CASE(4, 64) JQ_ONE_CASE(6, 64) JQ_ONE_CASE(8, 64)
+    JQ_ONE_CASE(2, 128) JQ_ONE_CASE(3, 128) JQ_ONE_CASE(4, 128) JQ_ONE_CASE(6, 128) JQ_ONE_CASE(8, 128)
 #undef JQ_ONE_CASE
     return rc;
 }
@@ -442,7 +444,7 @@ int launch_gather_one(const void* x, const void* up, const float* wts, float lim
                       int act_dtype, int64_t N, int64_t K, int bits, int gs, void* y, void* y2, int64_t ldy, bool pdl,
                       cudaStream_t st, bool* launched) {
     *launched = false;
-    if (!(bits == 2 || bits == 4 || bits == 6 || bits == 8) || !(gs == 64 || gs == 128) || K % (4 * gs) != 0 ||
+    if (!(bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8) || !(gs == 64 || gs == 128) || K % (4 * gs) != 0 ||
         pairs < 1 || pairs > 16 || x_div < 1 || N < 1 || N >= (1 << 24) || K >= (1 << 22))
         return JQ_OK;
     one::GatherArgs a = {};
@@ -459,8 +461,8 @@ int launch_gather_one(const void* x, const void* up, const float* wts, float lim
         rc = (act_dtype == JQ_BF16) ? one::launch_gather_shape<__nv_bfloat16, B, GSZ>(a, pdl, st, launched)  \
                                     : one::launch_gather_shape<__half, B, GSZ>(a, pdl, st, launched);        \
     }
-    JQ_GATHER_CASE(2, 64) JQ_GATHER_CASE(4, 64) JQ_GATHER_CASE(6, 64) JQ_GATHER_CASE(8, 64)
-    JQ_GATHER_CASE(2, 128) JQ_GATHER_CASE(4, 128) JQ_GATHER_CASE(6, 128) JQ_GATHER_CASE(8, 128)
+    JQ_GATHER_CASE(2, 64) JQ_GATHER_CASE(3, 64) JQ_GATHER_CASE(4, 64) JQ_GATHER_CASE(6, 64) JQ_GATHER_CASE(8, 64)
+    JQ_GATHER_CASE(2, 128) JQ_GATHER_CASE(3, 128) JQ_GATHER_CASE(4, 128) JQ_GATHER_CASE(6, 128) JQ_GATHER_CASE(8, 128)
 #undef JQ_GATHER_CASE
     return rc;
 }

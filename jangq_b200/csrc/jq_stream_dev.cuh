@@ -20,13 +20,17 @@ constexpr int MAX_SMEM = 227 * 1024;
 constexpr int MAX_FUSE = 4;          // matrices of one op (they share x, K, the width and the group size)
 constexpr int MAXT = 16;             // 16-row tiles one CTA may touch in one op
 // bytes of packed codes per row and item: whole 64-code blocks, 256 bytes (192 for 6-bit codes: 4 blocks of 48)
-__host__ __device__ constexpr int rowb_of(int bits) { return bits == 6 ? 192 : 256; }
+__host__ __device__ constexpr int rowb_of(int bits) { return bits == 6 || bits == 3 ? 192 : 256; }
 constexpr int ZERO_BYTES = 1024 + 64;
 constexpr int HEAD0 = ZERO_BYTES;      // zeros, then each kernel's own tables
 constexpr unsigned long long WAIT_NS = 500ull * 1000 * 1000;
 
 // Shared-memory row stride of an item's code rows: conflict-free unit loads for each width
-__host__ __device__ constexpr int rsb_of(int bits) { return rowb_of(bits) + (bits == 2 || bits == 6 ? 16 : bits == 4 ? 32 : 64); }
+__host__ __device__ constexpr int rsb_of(int bits) {
+    return rowb_of(bits) + (bits == 2 || bits == 6 || bits == 3 ? 16 : bits == 4 ? 32 : 64);
+}
+// limb bytes of one 64-code block and limb row: one byte per code, except 3-bit (8 codes on 12 byte positions)
+__host__ __device__ constexpr int limb_block_bytes(int bits) { return bits == 3 ? 96 : 64; }
 // bytes of one item: 16 code rows at the width's stride, then scales [16][NG] and biases [16][NG] (2-byte)
 __host__ __device__ constexpr int item_bytes(int bits, int gs) { return 16 * rsb_of(bits) + 2 * 16 * 2 * ((rowb_of(bits) * 8 / bits) / gs); }
 constexpr int SLOT = 5376;
@@ -77,6 +81,7 @@ struct Sync {                         // head of the workspace
 static_assert(sizeof(Sync) == 256, "the op table starts 256 bytes in");
 
 __host__ __device__ inline int limb_stride(int K) { return K + 64; }
+__host__ __device__ inline int limb_stride_bits(int K, int bits) { return K / 64 * limb_block_bytes(bits) + 64; }
 __host__ __device__ inline size_t head_bytes(int kmax, int nw) {
     const size_t limbs = ((size_t)3 * limb_stride(kmax) + 127) / 128 * 128;
     return HEAD0 + 3 * sizeof(DevOp) + 4 * sizeof(OpCtx) + 2 * MAXT * sizeof(TileInfo) + (size_t)(kmax / 64) * 16 + limbs +
@@ -315,8 +320,13 @@ __device__ __forceinline__ void prep_limbs(const PrepSrc& src, int K, uint8_t* l
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 xi[j] = __float2int_rn(v[j] * (scale * (1.f / (float)(1 << code_shift<BITS>(j)))));
-            uint8_t* u0 = limbs + (size_t)sx * 3 * LS + (size_t)(H >> 1) * 16;
-            store_limbs8<BITS == 6 ? 8 : BITS>(u0, u0 + LS, u0 + 2 * LS, H & 1, xi);
+            if constexpr (BITS == 3) {
+                uint8_t* u0 = limbs + (size_t)sx * 3 * LS + (size_t)H * 12;
+                store_limbs3(u0, u0 + LS, u0 + 2 * LS, xi);
+            } else {
+                uint8_t* u0 = limbs + (size_t)sx * 3 * LS + (size_t)(H >> 1) * 16;
+                store_limbs8<BITS == 6 ? 8 : BITS>(u0, u0 + LS, u0 + 2 * LS, H & 1, xi);
+            }
             if ((H & (LPG - 1)) == 0) {
                 float2* t = tab + (size_t)sx * xtab_stride + (H / LPG) * 2;
                 t[0] = make_float2(e, 0.f);                          // lanes that carry scales: D * e
@@ -374,16 +384,32 @@ __device__ __forceinline__ void compute_item(const uint8_t* buf, const uint8_t* 
         int cg[4];
         auto block = [&](const int blk) {
             // only the lanes of the three limb columns load; the other columns are zero without touching memory
-            uint4 bq = make_uint4(0u, 0u, 0u, 0u);
-            if (g < 3) bq = *reinterpret_cast<const uint4*>(bp + blk * 64);
-            uint32_t ulo[UW], uhi[UW], rl[4], rh[4];
+            uint32_t ulo[UW], uhi[UW];
             load_unit<BITS>(c_lo, blk, tig, ulo);
             load_unit<BITS>(c_hi, blk, tig, uhi);
-            to_bytes<BITS>(ulo, rl);
-            to_bytes<BITS>(uhi, rh);
-            if (blk % BPG == 0) imma0(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
-            else imma(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
-            imma(cg, rl[2], rh[2], rl[3], rh[3], bq.z, bq.w);
+            if constexpr (BITS == 3) {
+                uint2 b0 = make_uint2(0u, 0u), b1 = b0, b2 = b0;
+                if (g < 3) {
+                    const uint2* bb = reinterpret_cast<const uint2*>(bp + blk * 96);
+                    b0 = bb[0]; b1 = bb[1]; b2 = bb[2];
+                }
+                uint32_t rl[6], rh[6];
+                to_bytes3(ulo, rl);
+                to_bytes3(uhi, rh);
+                if (blk % BPG == 0) imma0(cg, rl[0], rh[0], rl[1], rh[1], b0.x, b0.y);
+                else imma(cg, rl[0], rh[0], rl[1], rh[1], b0.x, b0.y);
+                imma(cg, rl[2], rh[2], rl[3], rh[3], b1.x, b1.y);
+                imma(cg, rl[4], rh[4], rl[5], rh[5], b2.x, b2.y);
+            } else {
+                uint4 bq = make_uint4(0u, 0u, 0u, 0u);
+                if (g < 3) bq = *reinterpret_cast<const uint4*>(bp + blk * 64);
+                uint32_t rl[4], rh[4];
+                to_bytes<BITS>(ulo, rl);
+                to_bytes<BITS>(uhi, rh);
+                if (blk % BPG == 0) imma0(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
+                else imma(cg, rl[0], rh[0], rl[1], rh[1], bq.x, bq.y);
+                imma(cg, rl[2], rh[2], rl[3], rh[3], bq.z, bq.w);
+            }
             if (blk % BPG == BPG - 1) {
                 const int gi = blk / BPG;
                 const float2 tx = tp[gi * 2];
@@ -405,7 +431,7 @@ __device__ __forceinline__ void compute_item(const uint8_t* buf, const uint8_t* 
         }
         c_lo += RUN * 2 * BITS;
         c_hi += RUN * 2 * BITS;
-        bp += RUN * 64;
+        bp += RUN * limb_block_bytes(BITS);
         tp += RG * 2;
         sp_lo += RG * 2;
         sp_hi += RG * 2;
@@ -439,7 +465,8 @@ __device__ __forceinline__ void run_op(const WarpCtx& w, uint8_t* ring, const ui
     constexpr int RB = rowb_of(BITS), KT = RB * 8 / BITS, NBLK = KT / 64, NG = KT / GS;
     const int g = lane >> 2, tig = lane & 3;
     const bool bvalid = g < 3;
-    const uint8_t* brow = bvalid ? limbs + (size_t)g * LS + tig * 16 : zero + tig * 16;
+    constexpr int LBB = limb_block_bytes(BITS);              // limb bytes per block: a quarter of them per tig
+    const uint8_t* brow = bvalid ? limbs + (size_t)g * LS + tig * (LBB / 4) : zero + tig * 16;
     const float wl = tig == 1 ? 65536.f : tig == 3 ? 0.f : 1.f;
     const float2* tabm = tab + (tig >> 1);
     int il = warp;
@@ -486,7 +513,7 @@ __device__ __forceinline__ void run_op(const WarpCtx& w, uint8_t* ring, const ui
         const uint8_t* buf = ring + slot * SLOT;
         const int kc = min(RB, w.ge.rowbytes - st * RB);
         const int nblk = kc * 8 / (BITS * 64);
-        const uint8_t* bp = brow + (bvalid ? st * KT : 0);
+        const uint8_t* bp = brow + (bvalid ? st * (KT / 64 * LBB) : 0);
         const float2* tp = tabm + (size_t)(st * NG) * 2;
         if constexpr (XSETS) {
             const int xs_ = w.tl[lt].xsel;

@@ -492,7 +492,7 @@ def _np_swiglu(g, u, w, limit):
 
 
 @pytest.mark.parametrize("bits,gs,N,K", ((2, 64, 768, 2048), (4, 64, 200, 1024), (6, 64, 334, 1280), (8, 128, 40, 2048),
-                                         (2, 128, 2048, 768), (6, 64, 2048, 768)))
+                                         (2, 128, 2048, 768), (6, 64, 2048, 768), (3, 64, 336, 1280), (3, 128, 96, 2048)))
 @pytest.mark.parametrize("P,x_div", ((8, 8), (1, 1), (6, 1), (16, 16), (16, 8), (12, 4)))
 def test_one_token_gather_on_the_item_kernel(bits, gs, N, K, P, x_div, monkeypatch):
     """Up to 16 pairs of one token (a shared row, or one row per pair) take the item-streaming integer kernel:
@@ -528,12 +528,12 @@ def test_one_token_gather_on_the_item_kernel(bits, gs, N, K, P, x_div, monkeypat
     _lib.check(_lib.load().jq_device_status())
 
 
-@pytest.mark.parametrize("bits,N,K", ((2, 2048, 768), (6, 2048, 768), (4, 300, 1024), (8, 64, 512), (3, 256, 512)))
+@pytest.mark.parametrize("bits,N,K", ((2, 2048, 768), (6, 2048, 768), (4, 300, 1024), (8, 64, 512), (3, 256, 512), (5, 256, 512)))
 @pytest.mark.parametrize("P", (1, 8, 16, 24))
 @pytest.mark.parametrize("limit", (0.0, 1.5))
 def test_gather_with_folded_swiglu(bits, N, K, P, limit):
     """jq_gather_qgemv_swiglu against the oracle's SwiGLU followed by its gather, and against the two library
-    calls it replaces; 3-bit banks and more than 16 pairs take the two-launch route through h_scratch, which
+    calls it replaces; 5-bit banks and more than 16 pairs take the two-launch route through h_scratch, which
     is refused when the scratch is missing."""
     lib = _lib.load()
     E, base = 5, 3
@@ -556,7 +556,7 @@ def test_gather_with_folded_swiglu(bits, N, K, P, limit):
                                           bank.biases_tab.data_ptr(), None, E, _lib.JQ_BF16, N, K, bits, 64, y.data_ptr(),
                                           y.stride(0), base, 0, scratch, _lib.stream_ptr())
 
-    two_launch = bits == 3 or P > 16
+    two_launch = bits == 5 or P > 16
     if two_launch:
         assert call(None) == _lib.JQ_EWORKSPACE
     _lib.check(call(h.data_ptr() if two_launch else None))

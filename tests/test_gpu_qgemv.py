@@ -290,7 +290,8 @@ def test_nonfinite_activation_poisons_only_its_outputs(monkeypatch):
         assert np.all(np.isnan(y))
 
 
-@pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (4, 64), (4, 128), (6, 64), (6, 128), (8, 64), (8, 128)))
+@pytest.mark.parametrize("bits,gs", ((2, 64), (2, 128), (3, 64), (3, 128), (4, 64), (4, 128), (6, 64), (6, 128), (8, 64),
+                                     (8, 128)))
 def test_one_row_integer_kernel_shapes_and_extremes(monkeypatch, bits, gs):
     """The item-streaming integer kernel (one activation row): ragged row counts, rows shorter than one
     256-byte stage, rows whose last stage is short, a fused launch of three matrices, largest codes against
