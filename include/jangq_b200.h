@@ -94,6 +94,11 @@ int jq_qgemv(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t*
  * decode step (the reference measured its decode as dispatch-bound,
  * jang_tools/dsv41/DECODE_DSPARK_METHODS.md:90-93). */
 #define JQ_GEMV_STATIC_WEIGHTS 1
+/* For the gather mat-vecs (jq_gather_qgemv2, jq_gather_qgemv_swiglu): most pairs name experts outside this bank
+ * (expert-parallel decode: about pairs / world are local).  Up to 128 pairs then run on the integer gather, which
+ * compacts the local pairs and walks them 16 at a time; without the flag more than 16 pairs take the bf16 warp-MMA
+ * gather, which is faster when most pairs are local. */
+#define JQ_GATHER_FEW_LOCAL 2
 int jq_qgemv_ex(const void* x, int x_dtype, int64_t M, int64_t ldx, const uint32_t* codes,
                 const void* scales, const void* biases, int sidecar_dtype, int64_t N, int64_t K,
                 int bits, int group_size, void* y, int y_dtype, int64_t ldy, int flags,

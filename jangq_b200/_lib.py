@@ -18,6 +18,7 @@ JQ_OK, JQ_EINVAL, JQ_EUNSUPPORTED, JQ_EWORKSPACE, JQ_ECUDA, JQ_ETIMEOUT = range(
 JQ_F32, JQ_F16, JQ_BF16 = 0, 1, 2
 JQ_QUANT_F16_TINY_GUARD = 1
 JQ_GEMV_STATIC_WEIGHTS = 1
+JQ_GATHER_FEW_LOCAL = 2
 QGEMV_MAX_M = 16
 QGEMV_MAX_BATCH = 8
 MOE_TILE_M = 128

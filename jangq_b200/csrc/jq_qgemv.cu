@@ -635,10 +635,12 @@ int gather_qgemv_dispatch(const void* x, int act_dtype, int64_t ldx, int x_div, 
     bool launched = false;
     // Up to 16 pairs (one or two tokens of a top-8 model; a row per x_div pairs): the item-streaming integer kernel,
     // all matrices in one launch.  Other cases (more pairs, per-expert widths): the bf16 warp-MMA kernel.
-    if (fast && !bits_tab && pairs <= 16 && x_div >= 1 && gemv_kernel_choice() != 1) {
+    const bool sparse = (flags & JQ_GATHER_FEW_LOCAL) != 0;
+    if (fast && !bits_tab && (pairs <= 16 || sparse) && x_div >= 1 && gemv_kernel_choice() != 1) {
         rc = launch_gather_one(x, nullptr, nullptr, 0.f, ldx, x_div, pair_expert, (int)pairs,
                                codes_tab2 ? 2 : 1, codes_tab, scales_tab, biases_tab, codes_tab2, scales_tab2, biases_tab2,
-                               num_experts, expert_base, act_dtype, N, K, bits, gs, y, y2, ldy, a.pdl != 0, st, &launched);
+                               num_experts, expert_base, act_dtype, N, K, bits, gs, y, y2, ldy, a.pdl != 0, st, &launched,
+                               sparse);
         if (rc != JQ_OK) return rc;
     }
     if (fast && !launched) {
@@ -722,10 +724,11 @@ int jq_gather_qgemv_swiglu(const void* gate, const void* up, int act_dtype, int6
     const bool fast = (group_size == 64 || group_size == 128) && sidecar_dtype == act_dtype && !bits_tab &&
                       aligned(gate, 16) && aligned(up, 16) && (ld_in % 8 == 0) && gemv_kernel_choice() != 1;
     bool launched = false;
-    if (fast && pairs <= 16) {
+    const bool sparse = (flags & JQ_GATHER_FEW_LOCAL) != 0;
+    if (fast && (pairs <= 16 || sparse)) {
         rc = launch_gather_one(gate, up, weights, limit, ld_in, 1, pair_expert, (int)pairs, 1, codes_tab, scales_tab,
                                biases_tab, nullptr, nullptr, nullptr, num_experts, expert_base, act_dtype, N, K, bits,
-                               group_size, y, nullptr, ldy, (flags & JQ_GEMV_STATIC_WEIGHTS) != 0, st, &launched);
+                               group_size, y, nullptr, ldy, (flags & JQ_GEMV_STATIC_WEIGHTS) != 0, st, &launched, sparse);
         if (rc != JQ_OK) return rc;
     }
     if (launched) return JQ_OK;

@@ -155,7 +155,7 @@ int launch_gather_one(const void* x, const void* up, const float* wts, float lim
                       const void* const* scales_tab, const void* const* biases_tab, const uint32_t* const* codes_tab2,
                       const void* const* scales_tab2, const void* const* biases_tab2, int num_experts, int expert_base,
                       int act_dtype, int64_t N, int64_t K, int bits, int gs, void* y, void* y2, int64_t ldy, bool pdl,
-                      cudaStream_t st, bool* launched);
+                      cudaStream_t st, bool* launched, bool sparse = false);
 
 // persistent integer warp-MMA kernel (jq_qgemv_pint.cu), dense mat-vecs of 2- and 4-bit codes with at most 2
 // activation rows; same convention

@@ -408,6 +408,210 @@ static int launch_gather_shape(GatherArgs a, bool pdl, cudaStream_t st, bool* la
     return JQ_OK;
 }
 
+// ---- the same for more pairs of which few are local (expert-parallel decode) -------------------------------------
+// With the experts sharded over the ranks every rank sees the pairs of all tokens of the step (up to 128) but owns
+// the experts of only about pairs / world of them.  Every CTA first compacts the local pairs (ballots over the
+// pair list), then the launch walks them in rounds of up to 16: a round is the one-token gather above over the
+// round's pairs -- tile list, requests, limbs, items, row sums.  Rows of the other pairs are written as zeros, pair p
+// by CTA p mod grid.  Limbs: one set per activation row when pairs share rows (gate/up: prepared once), else one set
+// per pair that this CTA's tiles of the round touch (down: a CTA's tiles lie in one or two pairs).
+constexpr int SPARSE_MAX_PAIRS = 128;
+
+__host__ __device__ inline size_t sparse_head_bytes(int K, int nsets, int nw, int bits) {
+    const size_t limbs = ((size_t)nsets * 3 * limb_stride_bits(K, bits) + 127) / 128 * 128;
+    return HEAD0 + MAXT * sizeof(TileInfo) + MAXT * sizeof(void*) + 64 + SPARSE_MAX_PAIRS * 4 + SPARSE_MAX_PAIRS + MAXT * 4 +
+           (size_t)nsets * (K / 64) * 16 + limbs + (size_t)nw * MAXT * 16 * sizeof(float);
+}
+
+template <typename AT, int BITS, int GS, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+gather_sparse_kernel(const GatherArgs a, const int nsets) {
+    using A = Act<AT>;
+    constexpr int THREADS = NW * 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = a.K, G = a.G, N = a.N;
+    const int LS = limb_stride_bits(K, BITS);
+    constexpr int RB = rowb_of(BITS);
+    const int rowbytes = K * BITS / 8;
+    const int nst = (rowbytes + RB - 1) / RB;
+    const int tpm = (N + 15) / 16;
+    const bool per_pair = a.x_div == 1;                               // a row (and a set of limbs) per pair
+    const int nrows = (a.pairs + a.x_div - 1) / a.x_div;
+
+    uint8_t* zero = smem;
+    TileInfo* tiles = reinterpret_cast<TileInfo*>(smem + HEAD0);                          // [MAXT]
+    uint16_t** ytile = reinterpret_cast<uint16_t**>(tiles + MAXT);                        // [MAXT]
+    int* misc = reinterpret_cast<int*>(ytile + MAXT);                                     // [16]: 0 = local pairs, 1 = sets
+    int* lp = misc + 16;                                                                  // [128] local pairs, ascending
+    uint8_t* lflag = reinterpret_cast<uint8_t*>(lp + SPARSE_MAX_PAIRS);                   // [128] pair is local
+    int* rowmap = reinterpret_cast<int*>(lflag + SPARSE_MAX_PAIRS);                       // [MAXT] set -> pair
+    float2* tab = reinterpret_cast<float2*>(rowmap + MAXT);                               // [nsets][K / 64][2]
+    uint8_t* limbs = reinterpret_cast<uint8_t*>(tab) + (size_t)nsets * (K / 64) * 16;     // [nsets][3][LS]
+    float* ysum = reinterpret_cast<float*>(limbs + ((size_t)nsets * 3 * LS + 127) / 128 * 128);
+    uint8_t* ring = smem + sparse_head_bytes(K, nsets, NW, BITS) + (size_t)warp * 2 * SLOT;
+    float* myy = ysum + (size_t)warp * MAXT * 16;
+
+    for (int i = tid; i < ZERO_BYTES / 4; i += THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp == 0) {
+        int nl = 0;
+        for (int p0 = 0; p0 < a.pairs; p0 += 32) {
+            const int p = p0 + lane;
+            bool live = false;
+            if (p < a.pairs) {
+                const int e = a.pair_expert[p] - a.expert_base;
+                live = e >= 0 && e < a.num_experts;
+                lflag[p] = live ? 1 : 0;
+            }
+            const unsigned mask = __ballot_sync(0xFFFFFFFFu, live);
+            if (live) lp[nl + __popc(mask & ((1u << lane) - 1u))] = p;
+            nl += __popc(mask);
+        }
+        if (lane == 0) misc[0] = nl;
+    }
+    __syncthreads();
+    const int nl = misc[0];
+    // zero rows of the pairs whose expert lives on another rank
+    for (int p = (int)blockIdx.x; p < a.pairs; p += (int)gridDim.x) {
+        if (lflag[p]) continue;
+        for (int b = 0; b < a.banks; ++b) {
+            uint16_t* yr = reinterpret_cast<uint16_t*>(a.y[b]) + (int64_t)p * a.ldy;
+            for (int c = tid; c < N; c += THREADS) yr[c] = 0;
+        }
+    }
+    OpGeo ge;
+    ge.rowbytes = rowbytes; ge.G = G; ge.rowb = RB; ge.rsb = rsb_of(BITS);
+    ge.grpb = BITS * GS / 8; ge.ngb = 2 * (RB / (BITS * GS / 8)); ge.bits = BITS; ge.gs = GS;
+    const int xtab_stride = (K / 64) * 2;
+    PrepSrc src;
+    src.xs = reinterpret_cast<const uint16_t*>(a.x);
+    src.up = reinterpret_cast<const uint16_t*>(a.up);
+    src.wts = a.up ? a.wts : nullptr;
+    src.limit = a.limit; src.ldx = a.ldx;
+    if (!per_pair && nl > 0) {                                        // shared rows: all sets once
+        src.nx = nrows;
+        prep_limbs<AT, BITS, GS>(src, K, limbs, tab, LS, xtab_stride, tid, THREADS);
+    }
+    for (int q0 = 0; q0 < nl; q0 += 16) {
+        const int nq = min(16, nl - q0);
+        const int tiles_r = a.banks * nq * tpm;
+        const int tpc = (tiles_r + (int)gridDim.x - 1) / (int)gridDim.x;      // <= MAXT (checked by the host)
+        const int tile0 = (int)blockIdx.x * tpc;
+        const int ntile = max(0, min(tpc, tiles_r - tile0));
+        if (warp == 0) {
+            int qi = -1;
+            if (lane < ntile) {
+                const int gt = tile0 + lane;
+                const int j = gt / tpm, tm = gt - j * tpm;
+                const int b = j / nq;
+                qi = j - b * nq;
+                const int p = lp[q0 + qi];
+                const int e = a.pair_expert[p] - a.expert_base;
+                const int row0 = tm * 16;
+                TileInfo ti;
+                ti.codes = reinterpret_cast<const uint8_t*>(a.codes_tab[b][e]) + (int64_t)row0 * rowbytes;
+                ti.scales = reinterpret_cast<const uint16_t*>(a.scales_tab[b][e]) + (int64_t)row0 * G;
+                ti.biases = reinterpret_cast<const uint16_t*>(a.biases_tab[b][e]) + (int64_t)row0 * G;
+                ti.rows_valid = min(16, N - row0);
+                ti.xsel = p / a.x_div;
+                tiles[lane] = ti;
+                ytile[lane] = reinterpret_cast<uint16_t*>(a.y[b]) + (int64_t)p * a.ldy + row0;
+            }
+            if (per_pair) {
+                // sets of this CTA and round: the distinct pairs of its tiles, numbered by first appearance
+                const unsigned peers = __match_any_sync(0xFFFFFFFFu, qi);
+                const bool leader = qi >= 0 && (peers & ((1u << lane) - 1u)) == 0;
+                const unsigned leaders = __ballot_sync(0xFFFFFFFFu, leader);
+                const int first = __ffs(peers) - 1;
+                const int set = __popc(leaders & ((1u << first) - 1u));
+                if (qi >= 0) tiles[lane].xsel = set;
+                if (leader) rowmap[set] = lp[q0 + qi];
+                if (lane == 0) misc[1] = __popc(leaders);
+            }
+        }
+        __syncthreads();
+        for (int i = lane; i < ntile * 16; i += 32) myy[i] = 0.f;
+        const int cnt = ntile * nst;
+        int slot = 0, npre = 0;
+        for (int k = 0; k < 2; ++k) {
+            const int pos = warp + k * NW;
+            if (pos < cnt) {
+                const int lt = pos / nst;
+                issue_item(ring + k * SLOT, tiles[lt], pos - lt * nst, ge, lane);
+                cp_async_commit();
+                npre = k + 1;
+            }
+        }
+        if (per_pair && ntile > 0) {
+            src.nx = misc[1];
+            src.rowmap = rowmap;
+            prep_limbs<AT, BITS, GS>(src, K, limbs, tab, LS, xtab_stride, tid, THREADS);
+        }
+        __syncthreads();
+        WarpCtx w;
+        w.tl = tiles; w.ge = ge; w.cnt = cnt; w.nst = nst; w.stage0 = 0;
+        w.tl1 = tiles; w.ge1 = ge; w.lt1 = w.st1 = w.lt1b = w.st1b = 0; w.next_n = 0;
+        run_op<AT, BITS, GS, NW, true>(w, ring, limbs, LS, zero, tab, myy, warp, lane, slot, npre, xtab_stride);
+        cp_async_wait<0>();
+        __syncthreads();
+        for (int t = tid; t < ntile * 16; t += THREADS) {
+            float v = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < NW; ++ww) v += ysum[(size_t)ww * MAXT * 16 + t];      // always in warp order
+            if ((t & 15) < tiles[t >> 4].rows_valid) ytile[t >> 4][t & 15] = A::from_f32(v);
+        }
+        __syncthreads();                                                // the lists are rebuilt by the next round
+    }
+}
+
+template <typename AT, int BITS, int GS, int NW>
+static int launch_sparse_cfg(const GatherArgs& a, int nsets, int grid, bool pdl, cudaStream_t st, bool* launched) {
+    const size_t smem = sparse_head_bytes(a.K, nsets, NW, BITS) + (size_t)NW * 2 * SLOT;
+    static bool attr_done[64] = {};        // per device; benign race: the attribute call is idempotent
+    int dev = 0;
+    JQ_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        JQ_CUDA_OK(cudaFuncSetAttribute(gather_sparse_kernel<AT, BITS, GS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        MAX_SMEM));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, gather_sparse_kernel<AT, BITS, GS, NW>, a, nsets));
+    *launched = true;
+    return JQ_OK;
+}
+
+template <typename AT, int BITS, int GS>
+static int launch_sparse_shape(GatherArgs a, bool pdl, cudaStream_t st, bool* launched) {
+    const int grid = sm_count();
+    const int tpm = (a.N + 15) / 16;
+    const int64_t round_tiles = (int64_t)a.banks * 16 * tpm;                       // a full round of 16 pairs
+    const int tpc = (int)((round_tiles + grid - 1) / grid);
+    if (tpc > MAXT) return JQ_OK;
+    // limb sets: the activation rows (shared rows), or the pairs one CTA's tiles of a round can lie in
+    const int nsets = a.x_div == 1 ? std::min(16, (tpc + tpm - 1) / tpm + 1) : (a.pairs + a.x_div - 1) / a.x_div;
+    if (nsets > 16) return JQ_OK;
+    for (int nw : {16, 12, 8}) {
+        if (sparse_head_bytes(a.K, nsets, nw, BITS) + (size_t)nw * 2 * SLOT > (size_t)MAX_SMEM) continue;
+        if (nw == 16) return launch_sparse_cfg<AT, BITS, GS, 16>(a, nsets, grid, pdl, st, launched);
+        if (nw == 12) return launch_sparse_cfg<AT, BITS, GS, 12>(a, nsets, grid, pdl, st, launched);
+        return launch_sparse_cfg<AT, BITS, GS, 8>(a, nsets, grid, pdl, st, launched);
+    }
+    return JQ_OK;
+}
+
 }  // namespace one
 
 // Dense mat-vecs with one activation row (one launch for all matrices of `bt`) on the item-streaming integer
@@ -442,11 +646,13 @@ int launch_gather_one(const void* x, const void* up, const float* wts, float lim
                       const void* const* scales_tab, const void* const* biases_tab, const uint32_t* const* codes_tab2,
                       const void* const* scales_tab2, const void* const* biases_tab2, int num_experts, int expert_base,
                       int act_dtype, int64_t N, int64_t K, int bits, int gs, void* y, void* y2, int64_t ldy, bool pdl,
-                      cudaStream_t st, bool* launched) {
+                      cudaStream_t st, bool* launched, bool sparse) {
     *launched = false;
     if (!(bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8) || !(gs == 64 || gs == 128) || K % (4 * gs) != 0 ||
-        pairs < 1 || pairs > 16 || x_div < 1 || N < 1 || N >= (1 << 24) || K >= (1 << 22))
+        pairs < 1 || x_div < 1 || N < 1 || N >= (1 << 24) || K >= (1 << 22))
         return JQ_OK;
+    // more than 16 pairs: only when the caller says that few of them are local, and whole rows per x_div pairs
+    if (pairs > 16 && (!sparse || pairs > one::SPARSE_MAX_PAIRS || pairs % x_div != 0)) return JQ_OK;
     one::GatherArgs a = {};
     a.x = x; a.up = up; a.wts = wts; a.limit = limit; a.ldx = ldx; a.x_div = x_div;
     a.pair_expert = pair_expert; a.pairs = pairs; a.banks = banks;
@@ -458,8 +664,12 @@ int launch_gather_one(const void* x, const void* up, const float* wts, float lim
     int rc = JQ_OK;
 #define JQ_GATHER_CASE(B, GSZ)                                                                               \
     if (bits == B && gs == GSZ) {                                                                            \
-        rc = (act_dtype == JQ_BF16) ? one::launch_gather_shape<__nv_bfloat16, B, GSZ>(a, pdl, st, launched)  \
-                                    : one::launch_gather_shape<__half, B, GSZ>(a, pdl, st, launched);        \
+        if (pairs > 16)                                                                                      \
+            rc = (act_dtype == JQ_BF16) ? one::launch_sparse_shape<__nv_bfloat16, B, GSZ>(a, pdl, st, launched)  \
+                                        : one::launch_sparse_shape<__half, B, GSZ>(a, pdl, st, launched);    \
+        else                                                                                                 \
+            rc = (act_dtype == JQ_BF16) ? one::launch_gather_shape<__nv_bfloat16, B, GSZ>(a, pdl, st, launched)  \
+                                        : one::launch_gather_shape<__half, B, GSZ>(a, pdl, st, launched);    \
     }
     JQ_GATHER_CASE(2, 64) JQ_GATHER_CASE(3, 64) JQ_GATHER_CASE(4, 64) JQ_GATHER_CASE(6, 64) JQ_GATHER_CASE(8, 64)
     JQ_GATHER_CASE(2, 128) JQ_GATHER_CASE(3, 128) JQ_GATHER_CASE(4, 128) JQ_GATHER_CASE(6, 128) JQ_GATHER_CASE(8, 128)

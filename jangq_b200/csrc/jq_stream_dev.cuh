@@ -221,6 +221,7 @@ struct PrepSrc {
     float limit = 0.f;                // SwiGLU clamp (<= 0: none)
     int64_t ldx = 0;                  // elements between rows of xs / up
     int nx = 1;                       // rows (sets of limbs)
+    const int* rowmap = nullptr;      // set s reads row rowmap[s] of xs / up / wts (nullptr: row s)
     bool have_pre = false;            // `pre` holds the thread's first 16 bytes of row 0 (requested ahead of time)
     uint4 pre = {0u, 0u, 0u, 0u};
 };
@@ -249,7 +250,8 @@ __device__ __forceinline__ void prep_limbs(const PrepSrc& src, int K, uint8_t* l
             xq[i] = make_uint4(0u, 0u, 0u, 0u);
             if (idx < total) {
                 const int sx = idx / halves, H = idx - sx * halves;
-                xq[i] = (i == 0 && src.have_pre) ? src.pre : ld_cg16(src.xs + sx * src.ldx + (size_t)H * 8);
+                const int row = src.rowmap ? src.rowmap[sx] : sx;
+                xq[i] = (i == 0 && src.have_pre) ? src.pre : ld_cg16(src.xs + row * src.ldx + (size_t)H * 8);
             }
         }
     }
@@ -259,6 +261,7 @@ __device__ __forceinline__ void prep_limbs(const PrepSrc& src, int K, uint8_t* l
         const bool live = idx < total;
         const int sx = live ? idx / halves : 0;
         const int H = idx - sx * halves;                 // half-unit of the row: activations [8 H, 8 H + 8)
+        const int srow = src.rowmap ? src.rowmap[sx] : sx;
         float v[8];
         if (!live) {
 #pragma unroll
@@ -277,16 +280,16 @@ __device__ __forceinline__ void prep_limbs(const PrepSrc& src, int K, uint8_t* l
             else if (round == 1) r = xq[1];
             else if (round == 2) r = xq[2];
             else if (round == 3) r = xq[3];
-            else r = ld_cg16(src.xs + sx * src.ldx + (size_t)H * 8);
+            else r = ld_cg16(src.xs + srow * src.ldx + (size_t)H * 8);
             const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) { v[2 * j] = A::lo_f32(w[j]); v[2 * j + 1] = A::hi_f32(w[j]); }
             if (src.up) {
                 // xs holds the gate products: h = silu(min(g, limit)) * clip(u, +-limit) * weight, rounded to
                 // the activation type (what a separate SwiGLU launch would store)
-                const uint4 ru = ld_cg16(src.up + sx * src.ldx + (size_t)H * 8);
+                const uint4 ru = ld_cg16(src.up + srow * src.ldx + (size_t)H * 8);
                 const uint32_t wu[4] = {ru.x, ru.y, ru.z, ru.w};
-                const float wt = src.wts ? src.wts[sx] : 1.f;
+                const float wt = src.wts ? src.wts[srow] : 1.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     float gv = v[j], uv = (j & 1) ? A::hi_f32(wu[j >> 1]) : A::lo_f32(wu[j >> 1]);

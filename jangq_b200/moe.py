@@ -376,7 +376,7 @@ def _shared_expert(x: torch.Tensor, shared, swiglu_limit: float) -> torch.Tensor
 def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertBank, up: ExpertBank,
               down: ExpertBank, swiglu_limit: float = 0.0, shared=None, expert_base: int = 0,
               out_f32: bool = False, all_local: bool | None = None, return_slots: bool = False,
-              static_weights: bool = False, few_token_path: bool | None = None) -> torch.Tensor:
+              static_weights: bool = False, few_token_path: bool | None = None, few_local: bool = False) -> torch.Tensor:
     """Routed SwiGLU experts: out[t] = sum_j down_e( silu(gate_e x_t) * up_e x_t * w[t, j] ), e = idx[t, j].
 
     x [T, H] bf16/f16; idx [T, k] int; w [T, k] f32.  Follows dsv41/model.py:1206-1245.  With
@@ -387,7 +387,8 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
     themselves).  return_slots=True
     (few-token path only) returns the [T*k, H] rows before the combine, for a caller that fuses the sum.
     static_weights=True promises that the expert weights are not written by earlier work on the stream, so
-    the few-token mat-vecs may prefetch them while their predecessor still runs.  few_token_path forces
+    the few-token mat-vecs may prefetch them while their predecessor still runs.  few_local says that most
+    pairs name experts of other ranks (up to 128 pairs then stay on the integer gather).  few_token_path forces
     (True) or forbids (False) the unsorted gather mat-vec path; default: below 64 pairs, as the reference.
     """
     lib = _lib.load()
@@ -421,6 +422,8 @@ def moe_layer(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: ExpertB
             inv_ptr = sp.inv.data_ptr()
         else:
             flags = _lib.JQ_GEMV_STATIC_WEIGHTS if static_weights else 0
+            if few_local:        # experts sharded over ranks: most pairs are other ranks' (JQ_GATHER_FEW_LOCAL)
+                flags |= _lib.JQ_GATHER_FEW_LOCAL
             g, u = _gather_qgemv_pair(x, k, idx32, gate, up, flags, expert_base)
             if len(down.distinct_bits) == 1 and down.bits_tab is None:
                 # SwiGLU folded into the down gather (one launch for up to 16 pairs, two through h otherwise)

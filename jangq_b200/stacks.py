@@ -129,12 +129,12 @@ class MoEDecodeStack:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], out_f32=True, all_local=True)
             elif self.ep_mode == "peer" and T <= self.exchange.tcap:
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], expert_base=self.base,
-                                  return_slots=True, static_weights=True, few_token_path=True)
+                                  return_slots=True, static_weights=True, few_token_path=True, few_local=True)
                 x = moe_ep.peer_combine_residual_rmsnorm(x, y, self.k, self.exchange)
                 continue
             elif self.ep_mode in ("replicated", "peer"):
                 y = moe.moe_layer(x, idx, w, lay["gate"], lay["up"], lay["down"], expert_base=self.base, out_f32=True,
-                                  static_weights=True, few_token_path=T <= 16)
+                                  static_weights=True, few_token_path=T <= 16, few_local=True)
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
             else:
                 y = moe_ep.gathered_tokens(x, idx, w, moe_ep.partial_experts_fn(lay["gate"], lay["up"], lay["down"],

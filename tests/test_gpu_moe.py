@@ -632,3 +632,73 @@ def test_topk_over_logit_rows(T, E, k, dtype):
     idx2, w2 = jq.route_softmax_topk(logits, k, renorm=False, scale=2.5)
     _, w_ref2 = jo.route_softmax_topk(logits.float().cpu().numpy(), k, renorm=False, scale=2.5)
     assert np.array_equal(idx2.cpu().numpy(), idx_ref) and np.allclose(w2.cpu().numpy(), w_ref2, rtol=2e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("bits,N,K", ((2, 768, 2048), (6, 200, 1024), (3, 96, 1280), (8, 2048, 768)))
+@pytest.mark.parametrize("P,x_div,E,base,E_all", ((64, 8, 16, 32, 128), (32, 1, 4, 8, 16), (128, 8, 8, 0, 16), (40, 1, 16, 0, 16),
+                                                   (24, 8, 2, 6, 64)))
+def test_gather_of_many_pairs_few_of_them_local(bits, N, K, P, x_div, E, base, E_all):
+    """JQ_GATHER_FEW_LOCAL: up to 128 pairs on the integer gather, the local ones compacted and walked 16 at a time
+    (the (40, 1, 16, 0, 16) case has every pair local: three rounds; (24, 8, 2, 6, 64) usually has none), rows shared
+    by x_div pairs or one per pair, two banks; against the oracle and the bf16 warp-MMA gather."""
+    lib = _lib.load()
+    a, ref_a = make_bank(E, N, K, bits, 64, seed=51)
+    b, ref_b = make_bank(E, N, K, bits, 64, seed=52)
+    a, b = a._sidecars_as(torch.bfloat16), b._sidecars_as(torch.bfloat16)
+    rng = np.random.default_rng(P + bits + E)
+    rows = P // x_div
+    x = torch.from_numpy(rng.standard_normal((rows, K)).astype(np.float32)).to(DEV).to(torch.bfloat16)
+    pe_np = rng.integers(0, E_all, size=P).astype(np.int32)
+    pe = torch.from_numpy(pe_np).to(DEV)
+
+    def run(flags):
+        y = torch.full((2, P, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        _lib.check(lib.jq_gather_qgemv2(x.data_ptr(), _lib.JQ_BF16, x.stride(0), x_div, pe.data_ptr(), P, a.codes_tab.data_ptr(),
+                                        a.scales_tab.data_ptr(), a.biases_tab.data_ptr(), b.codes_tab.data_ptr(),
+                                        b.scales_tab.data_ptr(), b.biases_tab.data_ptr(), None, E, _lib.JQ_BF16, N, K, bits, 64,
+                                        y[0].data_ptr(), y[1].data_ptr(), y.stride(1), base, flags, _lib.stream_ptr()))
+        return y
+
+    ys = run(_lib.JQ_GATHER_FEW_LOCAL | _lib.JQ_GEMV_STATIC_WEIGHTS)
+    ym = run(0)
+    torch.cuda.synchronize()
+    local = (pe_np >= base) & (pe_np < base + E)
+    lhs = np.arange(P) // x_div
+    for i, ref in enumerate((ref_a, ref_b)):
+        want = np.zeros((P, N), np.float32)
+        if local.any():
+            want[local] = jo.gather_qmm(x.float().cpu().numpy(), ref[0], ref[1], ref[2], pe_np[local] - base, bits, 64,
+                                        lhs_indices=lhs[local])
+            close(ys[i].float().cpu().numpy(), want)
+        assert torch.count_nonzero(ys[i][torch.from_numpy(~local).to(DEV)]) == 0
+        assert not torch.isnan(ys[i].float()).any()
+        assert (ys[i].float() - ym[i].float()).abs().max() <= 2.0 ** -6 * max(float(ym[i].float().abs().max()), 1e-6)
+    _lib.check(lib.jq_device_status())
+
+
+@pytest.mark.parametrize("P,E,base,E_all", ((64, 16, 16, 128), (48, 8, 0, 8)))
+def test_swiglu_gather_of_many_pairs_few_of_them_local(P, E, base, E_all):
+    """jq_gather_qgemv_swiglu with JQ_GATHER_FEW_LOCAL: one set of limbs per local pair a CTA's tiles touch."""
+    lib = _lib.load()
+    N, K, bits = 2048, 768, 2
+    bank, ref = make_bank(E, N, K, bits, 64, seed=61)
+    bank = bank._sidecars_as(torch.bfloat16)
+    rng = np.random.default_rng(P)
+    g = torch.from_numpy(rng.standard_normal((P, K)).astype(np.float32) * 2).to(DEV).to(torch.bfloat16)
+    u = torch.from_numpy(rng.standard_normal((P, K)).astype(np.float32) * 2).to(DEV).to(torch.bfloat16)
+    w = torch.from_numpy(rng.random(P).astype(np.float32) + 0.1).to(DEV)
+    pe_np = rng.integers(0, E_all, size=P).astype(np.int32)
+    pe = torch.from_numpy(pe_np).to(DEV)
+    y = torch.full((P, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.jq_gather_qgemv_swiglu(g.data_ptr(), u.data_ptr(), _lib.JQ_BF16, g.stride(0), w.data_ptr(), 0.0,
+                                          pe.data_ptr(), P, bank.codes_tab.data_ptr(), bank.scales_tab.data_ptr(),
+                                          bank.biases_tab.data_ptr(), None, E, _lib.JQ_BF16, N, K, bits, 64, y.data_ptr(),
+                                          y.stride(0), base, _lib.JQ_GATHER_FEW_LOCAL, None, _lib.stream_ptr()))
+    torch.cuda.synchronize()
+    local = (pe_np >= base) & (pe_np < base + E)
+    hn = _np_swiglu(g.float().cpu().numpy(), u.float().cpu().numpy(), w.cpu().numpy(), 0.0)
+    want = np.zeros((P, N), np.float32)
+    want[local] = jo.gather_qmm(hn[local], ref[0], ref[1], ref[2], pe_np[local] - base, bits, 64)
+    close(y.float().cpu().numpy(), want)
+    assert torch.count_nonzero(y[torch.from_numpy(~local).to(DEV)]) == 0
+    _lib.check(lib.jq_device_status())
