@@ -558,6 +558,153 @@ route_kernel(const AT* __restrict__ x, int64_t ldx, const AT* __restrict__ wr, i
     for (int j = lane; j < k; j += 32) w_out[(int64_t)t * k + j] *= norm;
 }
 
+// The fused router for up to 128 experts as ONE thread-block cluster per token (up to 8 CTAs x 16 experts): the
+// logits meet in the shared memory of the cluster's first CTA (st.shared::cluster) and a cluster barrier replaces
+// the fence + counter + re-read from global memory of route_kernel, whose hand-over costs about 2.5 us on a path
+// that is a chain of dependent launches.  The router rows are requested before the dependency wait (static
+// weights); x and res are read 16 bytes per thread.  Same arithmetic as route_kernel<AT, true>.
+template <typename AT>
+__global__ void __launch_bounds__(256)
+route_cluster_kernel(const AT* __restrict__ x, const AT* __restrict__ wr, int H, int E, int k, int renorm, float scale,
+                     int32_t* __restrict__ idx_out, float* __restrict__ w_out, const AT* __restrict__ res, float eps,
+                     AT* __restrict__ x_out) {
+    __shared__ float p[128];
+    __shared__ __align__(16) AT xn[4096];
+    __shared__ float part[8];
+    const int t = blockIdx.x, rank = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // two experts per warp: their router rows, 8 columns per lane and 256-column step (H <= 4096: 16 steps)
+    const int e0 = rank * 16 + warp * 2;
+    uint4 wa[16], wb[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int c = lane * 8 + 256 * i;
+        wa[i] = wb[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < H) {
+            if (e0 < E) wa[i] = __ldg(reinterpret_cast<const uint4*>(wr + (int64_t)e0 * H + c));
+            if (e0 + 1 < E) wb[i] = __ldg(reinterpret_cast<const uint4*>(wr + (int64_t)(e0 + 1) * H + c));
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the token: rms_norm(x + res); thread j owns columns [8 j, 8 j + 8) and, for H > 2048, [2048 + 8 j, ...)
+    float v[16];
+    float ss = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int c = h * 2048 + threadIdx.x * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[h * 8 + j] = 0.f;
+        if (c < H) {
+            const uint4 xq = *reinterpret_cast<const uint4*>(x + (int64_t)t * H + c);
+            const uint4 rq = *reinterpret_cast<const uint4*>(res + (int64_t)t * H + c);
+            const AT* xa = reinterpret_cast<const AT*>(&xq);
+            const AT* ra = reinterpret_cast<const AT*>(&rq);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[h * 8 + j] = Elt<AT>::to_f32(xa[j]) + Elt<AT>::to_f32(ra[j]);
+                ss = fmaf(v[h * 8 + j], v[h * 8 + j], ss);
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += part[i];
+    const float r = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int c = h * 2048 + threadIdx.x * 8;
+        if (c < H) {
+            uint4 oq;
+            AT* oa = reinterpret_cast<AT*>(&oq);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) oa[j] = Elt<AT>::from_f32(v[h * 8 + j] * r);
+            *reinterpret_cast<uint4*>(xn + c) = oq;
+            if (rank == 0) *reinterpret_cast<uint4*>(x_out + (int64_t)t * H + c) = oq;
+        }
+    }
+    __syncthreads();
+    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int c = lane * 8 + 256 * i;
+        if (c < H) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xn + c);
+            const AT* xa = reinterpret_cast<const AT*>(&xv);
+            const AT* a0 = reinterpret_cast<const AT*>(&wa[i]);
+            const AT* a1 = reinterpret_cast<const AT*>(&wb[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float xf = Elt<AT>::to_f32(xa[j]);
+                acc0 = fmaf(xf, Elt<AT>::to_f32(a0[j]), acc0);
+                acc1 = fmaf(xf, Elt<AT>::to_f32(a1[j]), acc1);
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, d);
+        acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, d);
+    }
+    if (lane < 2 && e0 + lane < E) {
+        // the logit, rounded to the activation type, into p[] of the cluster's first CTA
+        const float lv = Elt<AT>::to_f32(Elt<AT>::from_f32(lane == 0 ? acc0 : acc1));
+        uint32_t local = (uint32_t)__cvta_generic_to_shared(p + e0 + lane), remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(lv) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank != 0 || warp != 0) return;
+    float mx = -INFINITY;
+    for (int i = lane; i < E; i += 32) mx = fmaxf(mx, p[i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float pv = __expf(p[i] - mx);
+        p[i] = pv;
+        sum += pv;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+    const float inv_sum = 1.0f / sum;
+    __syncwarp();
+    float top_sum = 0.f, my_w = 0.f;
+    int my_idx = 0;
+    for (int j = 0; j < k; ++j) {
+        float bv = -1.f;
+        int bi = 0x7FFFFFFF;
+        for (int i = lane; i < E; i += 32) {
+            const float pv = p[i];
+            if (pv > bv) { bv = pv; bi = i; }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, d);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, d);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) p[bi] = -1.f;
+        __syncwarp();
+        const float pv = bv * inv_sum;
+        top_sum += pv;
+        if (lane == j % 32) { my_w = pv; my_idx = bi; }
+        if (j % 32 == 31 || j == k - 1) {
+            const int j0 = j - (j % 32);
+            if (lane <= j - j0) {
+                idx_out[(int64_t)t * k + j0 + lane] = my_idx;
+                w_out[(int64_t)t * k + j0 + lane] = my_w;
+            }
+        }
+    }
+    __syncwarp();
+    const float norm = renorm ? scale / (top_sum + 1e-20f) : scale;
+    for (int j = lane; j < k; j += 32) w_out[(int64_t)t * k + j] *= norm;
+}
+
 // Router for many tokens (prefill): the logits come from a GEMM; one warp per token turns its row of logits
 // (f32, or the activation type) into the softmax over the experts in f32, the k largest scores (ties to the
 // lower id) and w = p / (sum p + 1e-20) * scale -- route_kernel's selection, one launch instead of the five or
@@ -710,6 +857,26 @@ int jq_moe_route_norm(const void* x, const void* res, int act_dtype, int64_t T, 
         const size_t nb = (size_t)T * H * 2;
         JQ_REQUIRE((o1 <= x0 || x0 + nb <= o0) && (o1 <= r0 || r0 + nb <= o0), JQ_EINVAL,
                    "jq_moe_route_norm: x_out must not overlap x or res");
+    }
+    if (num_experts <= 128 && aligned(x, 16) && aligned(res, 16) && aligned(x_out, 16)) {
+        // one cluster of ceil(E / 16) <= 8 CTAs per token
+        const unsigned cl = (unsigned)((num_experts + 15) / 16);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)T, cl);
+        cfg.blockDim = dim3(256);
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1; attr[1].val.clusterDim.y = cl; attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        const int Hi = (int)H;
+        JQ_DISPATCH_DTYPE16(act_dtype, AT,
+            JQ_CUDA_OK(cudaLaunchKernelEx(&cfg, route_cluster_kernel<AT>, (const AT*)x, (const AT*)router_w, Hi, num_experts, k,
+                                          renorm, scale, idx_out, w_out, (const AT*)res, eps, (AT*)x_out)))
+        return JQ_OK;
     }
     const dim3 grid((unsigned)T, (unsigned)((num_experts + 7) / 8));
     JQ_DISPATCH_DTYPE16(act_dtype, AT,
