@@ -459,7 +459,11 @@ static int launch_mma(const GemvArgs& a, const GemvBatch& bt, int pairs, cudaStr
     if (mt == 2) nw = 4;
     const int sb = mt == 2 ? GemvGeom<BITS, GS, 2>::stage_bytes(a.M) : GemvGeom<BITS, GS, 1>::stage_bytes(a.M);
     const int nbuf = (nw == 8 && nst >= 20 && nw * 3 * sb <= 200 * 1024) ? 3 : 2;
-    if (mt == 2) return launch_mma_cfg<AT, BITS, GS, 2, 4>(a, bt, pairs, nbuf, st, launched);
+    if (mt == 2) {
+        // 32-row tiles may not fit either (wide codes, several activation rows, long groups): 16-row tiles then
+        const int rc = launch_mma_cfg<AT, BITS, GS, 2, 4>(a, bt, pairs, nbuf, st, launched);
+        if (rc != JQ_OK || *launched) return rc;
+    }
     if (nw == 8) {
         // eight warps' stages may not fit the shared memory (several activation rows, wide codes): four warps then
         const int rc = launch_mma_cfg<AT, BITS, GS, 1, 8>(a, bt, pairs, nbuf, st, launched);
