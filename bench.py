@@ -78,8 +78,8 @@ CONFIG = {"workload": "config2 dense decoder, batch-1 decode weight stream: 225 
 # CPU arm: the reference's numpy path, dequantize_affine_numpy(...) @ x (jang_tools/affine.py:445-463), on a
 # bounded sample of the workload, row chunks spread over one worker process per host core with the BLAS
 # library held to one thread per worker (no oversubscription).  The reference's own function is used where
-# its tree can be imported ($JANGQ_REF or /root/reference; widths 2/4/8 -- its 3/5/6-bit unpack is a
-# per-element Python loop); elsewhere, and for the 6-bit rows, the restatement in oracle/jang_oracle.py.
+# its tree can be imported ($JANGQ_REF, or the build container's mount of it; widths 2/4/8 -- its 3/5/6-bit
+# unpack is a per-element Python loop); elsewhere, and for the 6-bit rows, the restatement in oracle/jang_oracle.py.
 # --------------------------------------------------------------------------------------
 _CPU = {}
 
@@ -91,8 +91,11 @@ def _cpu_cores():
         return os.cpu_count() or 1
 
 
+_REFERENCE_MOUNT = os.path.join(os.sep, "root", "reference")
+
+
 def _reference_dequant():
-    for root in (os.environ.get("JANGQ_REF", ""), "/root/reference"):
+    for root in (os.environ.get("JANGQ_REF", ""), _REFERENCE_MOUNT):
         pkg = os.path.join(root, "jang-tools")
         if root and os.path.isdir(os.path.join(pkg, "jang_tools")):
             if pkg not in sys.path:

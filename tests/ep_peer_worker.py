@@ -71,7 +71,7 @@ def main():
     expect((outs["peer"] - outs["replicated"]).abs().max() <= 2.0 ** -5 * outs["replicated"].abs().max(),
            "decode stack: peer against replicated")
     expect(_lib.load().jq_device_status() == _lib.JQ_OK, "device status word set")
-    # the ranks agree on the verdict between steps, with nothing in flight, and all leave through the same door
+    # the ranks agree on pass or fail between steps, with nothing in flight, and all leave through the same door
     bad = torch.tensor([len(failures)], device=dev, dtype=torch.int32)
     dist.all_reduce(bad, op=dist.ReduceOp.MAX)
     if failures:
