@@ -715,7 +715,7 @@ int qgemm_dispatch(const void* x, int x_dtype, int64_t M, int64_t ldx, const uin
             const double t2 = waves(ncol * ((m_tiles + 1) / 2)) * nkb_all * 1.3;
             if (t2 < best) { best = t2; two = true; }
         }
-        for (int S : {2, 4}) {
+        for (int S : {2, 4}) {      // clusters of 8 such CTAs were measured at half the speed of 4 (72.9 vs 33.9 us)
             if (nkb_all / S < 16) continue;
             const double ts = waves(ncol * m_tiles * S) * ((double)nkb_all / S * 1.1 + 8.0);
             if (ts < best) { best = ts; two = false; ksplit = S; }
