@@ -58,6 +58,8 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
     if w.dim() < 2:
         raise JangqError(_lib.JQ_EINVAL, f"affine quantization expects a matrix, got {tuple(w.shape)}")
     K = w.shape[-1]
+    if K == 0:
+        raise JangqError(_lib.JQ_EINVAL, "affine quantization expects rows of at least one group")
     lead = tuple(w.shape[:-1])
     w2 = w.reshape(-1, K).contiguous()
     rows = w2.shape[0]
