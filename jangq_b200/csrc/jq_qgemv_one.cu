@@ -247,10 +247,16 @@ struct GatherArgs {
     int tpc;                          // 16-row tiles per CTA
 };
 
+// The per-expert pointer tables are static: up to GATHER_TAB_EXPERTS experts' entries are copied into shared memory
+// before the dependency wait, which takes one dependent round trip to memory (expert id -> pointer) off the path
+// between the routing decision and the first weight bytes.
+constexpr int GATHER_TAB_EXPERTS = 128;
+constexpr size_t GATHER_TAB_BYTES = (size_t)2 * 3 * GATHER_TAB_EXPERTS * sizeof(void*);
+
 __host__ __device__ inline size_t gather_head_bytes(int K, int nx, int nw, int bits = 8) {
     const size_t limbs = ((size_t)nx * 3 * limb_stride_bits(K, bits) + 127) / 128 * 128;
-    return HEAD0 + MAXT * sizeof(TileInfo) + MAXT * sizeof(void*) + 16 + (size_t)nx * (K / 64) * 16 + limbs +
-           (size_t)nw * MAXT * 16 * sizeof(float);
+    return HEAD0 + MAXT * sizeof(TileInfo) + MAXT * sizeof(void*) + 16 + GATHER_TAB_BYTES + (size_t)nx * (K / 64) * 16 +
+           limbs + (size_t)nw * MAXT * 16 * sizeof(float);
 }
 
 template <typename AT, int BITS, int GS, int NW>
@@ -273,7 +279,8 @@ gather_one_kernel(const GatherArgs a) {
     TileInfo* tiles = reinterpret_cast<TileInfo*>(smem + HEAD0);                          // [MAXT], live tiles only
     uint16_t** ytile = reinterpret_cast<uint16_t**>(tiles + MAXT);                        // [MAXT] first output of the tile
     int* nlive_s = reinterpret_cast<int*>(ytile + MAXT);
-    float2* tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(ytile + MAXT) + 16);   // [nx][K / 64][2]
+    const void** ptab = reinterpret_cast<const void**>(reinterpret_cast<uint8_t*>(ytile + MAXT) + 16);   // [2][3][128]
+    float2* tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(ptab) + GATHER_TAB_BYTES);       // [nx][K / 64][2]
     uint8_t* limbs = reinterpret_cast<uint8_t*>(tab) + (size_t)nx * (K / 64) * 16;         // [nx][3][LS]
     float* ysum = reinterpret_cast<float*>(limbs + ((size_t)nx * 3 * LS + 127) / 128 * 128);
     uint8_t* ring = smem + gather_head_bytes(K, nx, NW, BITS) + (size_t)warp * 2 * SLOT;
@@ -281,8 +288,19 @@ gather_one_kernel(const GatherArgs a) {
 
     for (int i = tid; i < ZERO_BYTES / 4; i += THREADS) reinterpret_cast<uint32_t*>(zero)[i] = 0u;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // the routing decision comes from the launch before: nothing can be requested ahead of it
+    // the routing decision comes from the launch before: no weights can be requested ahead of it, but the pointer
+    // tables can be read
+    const bool tab_cached = a.num_experts <= GATHER_TAB_EXPERTS;
+    if (tab_cached) {
+        for (int i = tid; i < a.banks * 3 * a.num_experts; i += THREADS) {
+            const int b = i / (3 * a.num_experts), r = i - b * 3 * a.num_experts;
+            const int which = r / a.num_experts, e = r - which * a.num_experts;
+            const void* v = which == 0 ? (const void*)a.codes_tab[b][e] : which == 1 ? a.scales_tab[b][e] : a.biases_tab[b][e];
+            ptab[(b * 3 + which) * GATHER_TAB_EXPERTS + e] = v;
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
 
     const int tile0 = (int)blockIdx.x * a.tpc;
     const int ntile = min(a.tpc, total - tile0);
@@ -300,9 +318,12 @@ gather_one_kernel(const GatherArgs a) {
             yp = reinterpret_cast<uint16_t*>(a.y[b]) + (int64_t)p * a.ldy + row0;
             if (e >= 0 && e < a.num_experts) {
                 live = true;
-                ti.codes = reinterpret_cast<const uint8_t*>(a.codes_tab[b][e]) + (int64_t)row0 * rowbytes;
-                ti.scales = reinterpret_cast<const uint16_t*>(a.scales_tab[b][e]) + (int64_t)row0 * G;
-                ti.biases = reinterpret_cast<const uint16_t*>(a.biases_tab[b][e]) + (int64_t)row0 * G;
+                const void* pc = tab_cached ? ptab[(b * 3 + 0) * GATHER_TAB_EXPERTS + e] : (const void*)a.codes_tab[b][e];
+                const void* ps = tab_cached ? ptab[(b * 3 + 1) * GATHER_TAB_EXPERTS + e] : a.scales_tab[b][e];
+                const void* pb = tab_cached ? ptab[(b * 3 + 2) * GATHER_TAB_EXPERTS + e] : a.biases_tab[b][e];
+                ti.codes = reinterpret_cast<const uint8_t*>(pc) + (int64_t)row0 * rowbytes;
+                ti.scales = reinterpret_cast<const uint16_t*>(ps) + (int64_t)row0 * G;
+                ti.biases = reinterpret_cast<const uint16_t*>(pb) + (int64_t)row0 * G;
                 ti.rows_valid = rows_valid;
                 ti.xsel = p / a.x_div;
             } else {
