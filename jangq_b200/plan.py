@@ -147,6 +147,12 @@ class GemvPlan:
             self._graph.replay()
         return self.y
 
+    def check_status(self):
+        """Raise JangqError(JQ_ETIMEOUT) if a bounded device-side wait of a launch ran out since the last check (the
+        outputs of that run are undefined).  Reads the device status word, which synchronises the device: call it at
+        step boundaries of a serving loop, not between launches."""
+        _lib.check(_lib.load().jq_device_status())
+
     def run_host(self, host_inputs: dict | None = None) -> torch.Tensor:
         """One step from host memory: pinned inputs -> device, replay, last output -> pinned host."""
         src = host_inputs if host_inputs is not None else self._host_in
