@@ -4,17 +4,19 @@
 // Every rank holds the same tokens x[T,H] (replicated decode, jangq_b200/stacks.py) and the outputs of
 // its own experts for them, y[T*k,H] (rows of pairs routed to other ranks' experts are zero).  CTA t of
 // rank r:
-//   1. sums its k slot rows of token t in f32 and stores the row into its own symmetric buffer
-//      (half s & 1 of a double buffer, s = the launch's sequence number from a device counter);
+//   1. sums its k slot rows of token t in f32 and PUSHES the row into row [t][r] of every rank's symmetric
+//      buffer, its own included (plain stores over NVLink, posted; half s & 1 of a double buffer, s = the
+//      launch's sequence number from a device counter);
 //   2. release: writes s into flag [t][r] of every peer's buffer (st.release.sys after a system fence);
 //   3. acquire: waits until its own flags [t][0..world) are >= s (ld.acquire.sys, bounded by a wall-clock
 //      limit, after which the library's status word is set, the CTA carries on without hanging and no
 //      later launch waits again);
-//   4. reads row t of every rank's buffer with plain peer loads in rank order (the same order on every
-//      rank, so the replicated x stays bit-identical), adds x, normalises, writes out[t].
-// Double buffering needs no second barrier: a rank overwrites half s & 1 only in launch s + 2, which it
-// enters after launch s + 1, whose flags every peer sends only after it finished reading in launch s.
-// Bytes over NVLink per rank and layer: (world - 1) * T * H * 4 read + (world - 1) * T * 4 of flags.
+//   4. reads rows [t][0..world) of its OWN buffer in rank order (the same order on every rank, so the
+//      replicated x stays bit-identical), adds x, normalises, writes out[t].  The exchange crosses NVLink once
+//      (stores and flags one way) instead of twice (flags, then loads and their replies).
+// Double buffering needs no second barrier: a rank writes into half s & 1 of its peers only in launch s + 2,
+// which it enters after launch s + 1, whose flags every peer sends only after it finished reading in launch s.
+// Bytes over NVLink per rank and layer: (world - 1) * T * H * 4 written + (world - 1) * T * 4 of flags.
 //
 // The peers' buffers are plain device pointers (obtained by the caller, e.g. from torch's symmetric
 // memory rendezvous); there is no TMA and no multicast in this file.
@@ -29,7 +31,7 @@ constexpr int EP_PER = 4;                                // columns per thread (
 constexpr unsigned long long EP_WAIT_NS = 2000000000ull; // 2 s unless JANGQ_EP_WAIT_MS says otherwise
 
 struct EpPeers {
-    float* buf[EP_MAX_WORLD];                            // [2][tcap][H] f32, then flags [tcap][EP_MAX_WORLD] u32
+    float* buf[EP_MAX_WORLD];       // [2][tcap][EP_MAX_WORLD][H] f32 (row of token t from rank r), then flags [tcap][EP_MAX_WORLD] u32
 };
 
 __device__ __forceinline__ unsigned long long ep_now_ns() {
@@ -72,18 +74,19 @@ ep_combine_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, in
     if (threadIdx.x == 0) seq_sh = (uint32_t)(++counters[t]);   // only this CTA touches counters[t]; launches are stream-ordered
     __syncthreads();
     const uint32_t s = seq_sh;
-    const size_t half = (size_t)(s & 1u) * tcap * H;
-    const size_t flags_off = (size_t)2 * tcap * H;       // in floats
+    const size_t half = (size_t)(s & 1u) * tcap * EP_MAX_WORLD * H;
+    const size_t flags_off = (size_t)2 * tcap * EP_MAX_WORLD * H;       // in floats
 
-    // 1. this rank's partial row
-    float* mine = peers.buf[rank] + half + (size_t)t * H;
+    // 1. this rank's partial row, PUSHED into every rank's buffer (plain stores over NVLink, posted): the readers
+    //    then find all rows in their own memory and the exchange costs one NVLink crossing instead of two
+    const size_t my_row = half + ((size_t)t * EP_MAX_WORLD + rank) * H;
 #pragma unroll
     for (int i = 0; i < EP_PER; ++i) {
         const int c = threadIdx.x + i * 1024;
         if (c < H) {
             float a = 0.f;
             for (int j = 0; j < k; ++j) a += Elt<AT>::to_f32(y[((int64_t)t * k + j) * H + c]);
-            mine[c] = a;
+            for (int p = 0; p < world; ++p) peers.buf[p][my_row + c] = a;
         }
     }
     __syncthreads();
@@ -112,8 +115,9 @@ ep_combine_rmsnorm_kernel(const AT* __restrict__ x, const AT* __restrict__ y, in
         const int c = threadIdx.x + i * 1024;
         v[i] = 0.f;
         if (c < H) {
-            float a = 0.f;
-            for (int p = 0; p < world; ++p) a += ep_load_peer(peers.buf[p] + half + (size_t)t * H + c);
+            float a = 0.f;                                 // rank order: the same x on every rank, bit for bit
+            for (int p = 0; p < world; ++p)
+                a += ep_load_peer(peers.buf[rank] + half + ((size_t)t * EP_MAX_WORLD + p) * H + c);
             a += Elt<AT>::to_f32(x[(int64_t)t * H + c]);
             v[i] = a;
             ss = fmaf(a, a, ss);
@@ -206,7 +210,7 @@ int jq_ep_pack_slots(const void* x, int64_t ldx, const int32_t* idx, const float
 
 size_t jq_ep_buffer_bytes(int64_t tcap, int64_t H) {
     if (tcap <= 0 || H <= 0) return 0;
-    return (size_t)2 * tcap * H * sizeof(float) + (size_t)tcap * jq::EP_MAX_WORLD * sizeof(uint32_t);
+    return (size_t)2 * tcap * jq::EP_MAX_WORLD * H * sizeof(float) + (size_t)tcap * jq::EP_MAX_WORLD * sizeof(uint32_t);
 }
 
 int jq_ep_combine_residual_rmsnorm(const void* x, const void* y, int k, int64_t T, int64_t H, float eps, void* out,

@@ -5,7 +5,7 @@ expert), with exactly one exchange each way:
 
   replicated tokens (batch-1 / small-batch decode: every rank holds the same rows):
       each rank runs its own experts on all rows (pairs of other ranks' experts are skipped by the
-      kernels) and the partial sums are added over NVLink: by `peer_combine_residual_rmsnorm` (peer loads
+      kernels) and the partial sums are added over NVLink: by `peer_combine_residual_rmsnorm` (peer stores
       inside the kernel that also does the residual and the norm) or with one NCCL all-reduce;
   sharded tokens (prefill / large batches: every rank holds its own rows):
       dispatch  = all_to_all_single of the (row, local expert id, routing weight) triples, ordered by
@@ -278,7 +278,7 @@ def peer_combine_residual_rmsnorm(x: torch.Tensor, y: torch.Tensor, k: int, ex: 
                                   eps: float | None = None) -> torch.Tensor:
     """rms_norm(x + sum over ranks and slots of y): x [T, H] (the same on every rank), y [T*k, H] this rank's
     expert outputs (zero rows for pairs owned elsewhere).  One launch; the ranks' partial sums cross NVLink
-    as peer loads inside it.  With an emulated exchange x and y carry a leading rank dimension."""
+    as peer stores inside it.  With an emulated exchange x and y carry a leading rank dimension."""
     lib = _lib.load()
     dev = _lib.require_cuda(x, y)
     emul = ex.rank < 0
