@@ -125,3 +125,13 @@ def test_split_validation():
         moe_ep.validate_splits(torch.tensor([3, 3]), torch.tensor([1, 2]), 10)
     with pytest.raises(ValueError, match="negative"):
         moe_ep.validate_splits(torch.tensor([11, -1]), torch.tensor([1, 2]), 10)
+
+
+def test_slot_capacity_is_a_multiple_of_8_between_the_mean_share_and_all_pairs():
+    for n_pairs, world in ((16384, 8), (16384, 2), (64, 8), (8, 4), (100000, 3)):
+        c = moe_ep.slot_capacity(n_pairs, world)
+        assert c % 8 == 0 or c == n_pairs
+        assert c <= max(n_pairs, 8)
+        assert c >= min(n_pairs, n_pairs // world)
+    assert moe_ep.slot_capacity(16384, 8) == 2592          # 1.25 x 2048 + 32
+    assert moe_ep.slot_capacity(16384, 8, factor=2.0) == 4128
