@@ -44,6 +44,8 @@ extern "C" {
 /* jq_quantize flags */
 #define JQ_QUANT_F16_TINY_GUARD  1  /* numpy-mirror floor on |scale| for f16 sidecars
                                        (jang_tools/affine.py:46-51); MLX itself has none */
+/* jq_quantize_mse flags */
+#define JQ_QUANT_MSE_EXHAUSTIVE  2  /* evaluate every clip ratio in float64, no float32 screen */
 
 typedef void* jq_stream_t;
 
@@ -65,6 +67,17 @@ int jq_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, i
  * caller convert.py:1564-1592).  Sidecars are float16 as in the reference. */
 int jq_quantize_rtn(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size,
                     int sidecar_dtype, uint32_t* codes, void* scales, void* biases,
+                    jq_stream_t stream);
+
+/* K1c. The same zero-point quantizer with the clip-ratio search that is
+ * quantize_tensor's default, method="mse" (jang_tools/quantize.py:153-191): 20
+ * ratios in [0.7, 1.0] per block, least mean squared error wins; 2-4 bits, wider
+ * codes take the K1b arithmetic as in the reference (:153).  Bit-exact with the
+ * reference under NumPy >= 2, where the search runs in float64.  A float32 pass
+ * first discards the ratios that provably cannot win; JQ_QUANT_MSE_EXHAUSTIVE
+ * evaluates all 20 in float64 instead (same result, for cross-checking). */
+int jq_quantize_mse(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size,
+                    int sidecar_dtype, int flags, uint32_t* codes, void* scales, void* biases,
                     jq_stream_t stream);
 
 /* Dequantizer: mx.dequantize / dequantize_affine_numpy (jang_tools/affine.py:445-463,

@@ -1,4 +1,5 @@
-// K1: affine group quantizer, its zero-point RTN sibling, and the dequantizer.
+// K1: affine group quantizer, its zero-point RTN sibling with and without the clip-ratio search, and the
+// dequantizer.
 //
 // All three are streaming kernels bounded by HBM bandwidth: the quantizer reads
 // sizeof(T) bytes and writes bits/8 + 2*sizeof(S)/group_size bytes per weight.
@@ -219,6 +220,223 @@ static int launch_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, 
     return check_launch("quantize");
 }
 
+// ---- clip-ratio search (quantize_tensor(method="mse"), jang_tools/quantize.py:153-191) ------------
+// For each block the reference tries 20 clip ratios, quantizes the block against the shrunken
+// range and keeps the ratio with the least mean squared error.  Its float32 minima are multiplied
+// by float64 ratios, so (NumPy >= 2 promotion) every step of the search is float64; this kernel
+// does the same arithmetic in the same order, including the order of the error sum, so the winner
+// is the reference's winner bit for bit.
+//
+// Evaluated for all 20 ratios the search is bound by the FP64 pipe (20 x ~10 double operations per
+// weight, 384 us for 4096x4096), so a float32 pass first narrows the ratios to those that can still win
+// (see the bound at the screening pass) and only those are evaluated in float64.
+// Mapping: eight lanes per block, lane k owning the weights i = k (mod 8).  numpy's add.reduce over
+// a contiguous row keeps eight running sums over exactly those residue classes and folds them as
+// ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)), which is a three-step xor butterfly over the eight lanes.
+// The per-ratio scalars (scale, its reciprocal, zero point: two exact divisions) are computed once
+// per block, ratio r by lane r % 8, and handed round by shuffle.  x/scale uses x*rcp(scale) and
+// falls back to the exact division when the sum lands within 1e-4 of a half-integer, the only
+// place where the two could round to different codes.
+// linspace(0.7, 1.0, 20) as numpy produces it (start + i*step, last element set to stop)
+__constant__ double MSE_RATIOS[20] = {
+    0x1.6666666666666p-1, 0x1.6e7bf53896e7cp-1, 0x1.7691840ac7691p-1, 0x1.7ea712dcf7ea7p-1, 0x1.86bca1af286bcp-1,
+    0x1.8ed2308158ed2p-1, 0x1.96e7bf53896e8p-1, 0x1.9efd4e25b9efdp-1, 0x1.a712dcf7ea713p-1, 0x1.af286bca1af28p-1,
+    0x1.b73dfa9c4b73ep-1, 0x1.bf53896e7bf54p-1, 0x1.c7691840ac769p-1, 0x1.cf7ea712dcf7fp-1, 0x1.d79435e50d794p-1,
+    0x1.dfa9c4b73dfaap-1, 0x1.e7bf53896e7c0p-1, 0x1.efd4e25b9efd5p-1, 0x1.f7ea712dcf7eap-1, 0x1.0000000000000p+0};
+
+template <typename T, typename S, int BITS, int GS>
+__global__ void __launch_bounds__(256)
+quantize_mse_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __restrict__ scales,
+                    S* __restrict__ biases, int64_t n_blocks, int64_t n_words, bool screen) {
+    constexpr int EPL = GS / 8;                       // weights per lane
+    constexpr int L = (1 << BITS) - 1;
+    constexpr int WORDS_PER_WARP = 4 * GS * BITS / 32;
+    constexpr int NC = 32 / BITS + 2;                 // codes that can touch one 32-bit word
+    __shared__ __align__(16) uint8_t stage[8][4 * GS + 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane >> 3, k = lane & 7;
+    const int64_t warp_blk = ((int64_t)blockIdx.x * 8 + warp) * 4;
+    const int64_t qb = warp_blk + sub;
+    const bool valid = qb < n_blocks;
+
+    float xf[EPL];
+#pragma unroll
+    for (int t = 0; t < EPL; ++t) xf[t] = valid ? Elt<T>::to_f32(w[qb * GS + t * 8 + k]) : 0.0f;
+    float lo = xf[0], hi = xf[0];
+#pragma unroll
+    for (int t = 1; t < EPL; ++t) { lo = fminf(lo, xf[t]); hi = fmaxf(hi, xf[t]); }
+#pragma unroll
+    for (int d = 1; d < 8; d <<= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+        hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+    }
+    const bool is_const = (hi == lo);                 // quantize.py:151
+
+    // scalars of ratios k, k+8, k+16 (quantize.py:164-172)
+    double sc[3], rc[3];
+    int zp[3];
+#pragma unroll
+    for (int s = 0; s < 3; ++s) {
+        const int r = s * 8 + k;
+        sc[s] = 1.0; rc[s] = 1.0; zp[s] = 0;
+        if (r < 20) {
+            const double ratio = MSE_RATIOS[r];
+            const double c_min = __dmul_rn((double)lo, ratio);
+            const double c_max = __dmul_rn((double)hi, ratio);
+            double c_range = __dsub_rn(c_max, c_min);
+            if (c_range == 0.0) c_range = 1.0;
+            sc[s] = __ddiv_rn(c_range, (double)L);
+            zp[s] = min(max(__double2int_rn(__ddiv_rn(-c_min, sc[s])), 0), L);
+            rc[s] = __drcp_rn(sc[s]);
+        }
+    }
+
+    // Screening pass in float32.  With d = 2^-17 * max|x| the float32 root-mean-square error of a ratio
+    // is within d of the float64 one: the reconstruction (q-z)*scale is at most 2*max|x| and carries three
+    // float32 roundings (2^-21.7 * max|x| together); a code can differ from the float64 code only where the
+    // quotient is within 2^-20 of a tie, which moves |error| by less than 2^-19.5 * max|x|.  So the float64
+    // winner has a float32 rms no larger than the float32 minimum plus 2d, and only ratios inside that
+    // window (plus 1e-4 relative for the float32 summation) need the exact evaluation below; they are
+    // taken in ascending order with the reference's strict comparison.  Blocks whose magnitude would
+    // push float32 squares out of range, or that hold a NaN, skip the screen and evaluate all 20.
+    unsigned cand = is_const ? 0u : 0xFFFFFu;                  // a constant block's result is fixed (:187-189)
+    const float amax = fmaxf(fabsf(lo), fabsf(hi));
+    if (screen) {   // warp-uniform: every lane runs the pass (it shuffles), whether or not its block uses the outcome
+        float scf[3], rcf[3], m32[3];
+#pragma unroll
+        for (int s = 0; s < 3; ++s) { scf[s] = (float)sc[s]; rcf[s] = (float)rc[s]; m32[s] = 0.0f; }
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                if (s * 8 + kk >= 20) break;
+                const int src = (lane & 24) | kk;
+                const float scale = __shfl_sync(0xFFFFFFFFu, scf[s], src);
+                const float rcp = __shfl_sync(0xFFFFFFFFu, rcf[s], src);
+                const float z = (float)__shfl_sync(0xFFFFFFFFu, zp[s], src);
+                const float cl = -z, ch = (float)L - z;
+                float acc = 0.0f;
+#pragma unroll
+                for (int t = 0; t < EPL; ++t) {
+                    // rint(x/scale) through the 1.5*2^23 add; quotients too large for it clamp correctly anyway
+                    const float r = __fsub_rn(fmaf(xf[t], rcp, 12582912.0f), 12582912.0f);
+                    const float c = fminf(fmaxf(r, cl), ch);
+                    const float e = fmaf(-c, scale, xf[t]);
+                    acc = fmaf(e, e, acc);
+                }
+                acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+                acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+                acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 4);
+                if (kk == k) m32[s] = acc * (1.0f / GS);
+            }
+        }
+        float mn = fminf(m32[0], m32[1]);
+        if (16 + k < 20) mn = fminf(mn, m32[2]);
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, d));
+        const float lim = fmaf(sqrtf(mn), 1.0001f, amax * 1.52587890625e-05f);   // rms_min*(1+1e-4) + 2^-16*max|x|
+        const float thr = lim * lim * 1.00001f;
+        unsigned narrowed = 0u;
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+            const unsigned b = __ballot_sync(0xFFFFFFFFu, (s * 8 + k < 20) && (m32[s] <= thr));
+            narrowed |= ((b >> (lane & 24)) & 0xFFu) << (8 * s);
+        }
+        if (!is_const && amax > 1e-15f && amax < 1e15f) cand = narrowed;
+    }
+
+    double best = __longlong_as_double(0x7FF0000000000000ll);   // +inf
+    double best_scale = 1.0;
+    int best_zero = 0;
+    bool found = false;
+    while (__any_sync(0xFFFFFFFFu, cand != 0u)) {
+        // each group of eight lanes takes its own next candidate; the loop runs for the longest list
+        const bool active = cand != 0u;
+        const int r = active ? __ffs(cand) - 1 : 0;
+        cand &= cand - 1u;
+        const int s = r >> 3, src = (lane & 24) | (r & 7);
+        const double scale = __shfl_sync(0xFFFFFFFFu, s == 0 ? sc[0] : s == 1 ? sc[1] : sc[2], src);
+        const double rcp = __shfl_sync(0xFFFFFFFFu, s == 0 ? rc[0] : s == 1 ? rc[1] : rc[2], src);
+        const int z = __shfl_sync(0xFFFFFFFFu, s == 0 ? zp[0] : s == 1 ? zp[1] : zp[2], src);
+        const double zd = (double)z;
+        double acc = 0.0;
+#pragma unroll
+        for (int t = 0; t < EPL; ++t) {
+            const double x = (double)xf[t];
+            double v = __dadd_rn(__dmul_rn(x, rcp), zd);
+            int qi = __double2int_rn(v);
+            if (fabs(v - (double)qi) > 0.4999) {              // near a tie (or saturated): exact quotient
+                v = __dadd_rn(__ddiv_rn(x, scale), zd);       // quantize.py:174
+                qi = __double2int_rn(v);
+            }
+            qi = min(max(qi, 0), L);                          // :175
+            const double e = __dsub_rn(x, __dmul_rn((double)(qi - z), scale));   // :176
+            acc = __dadd_rn(acc, __dmul_rn(e, e));
+        }
+        acc = __dadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 1));
+        acc = __dadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 2));
+        acc = __dadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 4));
+        const double mse = __dmul_rn(acc, 1.0 / GS);          // :178 (division by a power of two)
+        if (active && mse < best) { best = mse; best_scale = scale; best_zero = z; found = true; }   // :181-185
+    }
+    if (is_const || !found) { best_scale = 1.0; best_zero = 0; }   // :187-189, and the initial values of :158-160
+
+    // codes of the winning ratio, staged so that each lane can assemble whole words
+    uint8_t* st = stage[warp];
+#pragma unroll
+    for (int t = 0; t < EPL; ++t) {
+        int qi = 0;
+        if (!is_const && found) {
+            const double v = __dadd_rn(__ddiv_rn((double)xf[t], best_scale), (double)best_zero);
+            qi = min(max(__double2int_rn(v), 0), L);
+        }
+        st[sub * GS + t * 8 + k] = (uint8_t)qi;
+    }
+    __syncwarp();
+    const int64_t word0 = warp_blk * (GS * BITS / 32);
+    for (int wi = lane; wi < WORDS_PER_WARP; wi += 32) {
+        if (word0 + wi >= n_words) break;
+        const int p = 32 * wi, c = p / BITS, o = p - c * BITS;
+        unsigned long long acc = 0ull;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) acc |= (unsigned long long)st[c + j] << (j * BITS);   // bits past o+32 are dropped
+        codes[word0 + wi] = (uint32_t)(acc >> o);
+    }
+    if (valid && k == 0) {
+        const float sf = __double2float_rn(best_scale);           // :184 (float32 array)
+        scales[qb] = Elt<S>::from_f32(sf);                        // :281-282
+        biases[qb] = Elt<S>::from_f32(__fmul_rn(-sf, (float)best_zero));
+    }
+}
+
+static int launch_quantize_mse(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int gs, int sidecar_dtype,
+                               int flags, uint32_t* codes, void* scales, void* biases, cudaStream_t st) {
+    int rc = check_quant_shape(rows, K, bits, gs);
+    if (rc != JQ_OK) return rc;
+    JQ_REQUIRE(valid_dtype(w_dtype) && valid_dtype(sidecar_dtype), JQ_EINVAL, "bad dtype");
+    JQ_REQUIRE(bits <= 4, JQ_EINVAL, "the clip-ratio search covers 2, 3 and 4 bits");
+    const int64_t n = rows * K;
+    if (n == 0) return JQ_OK;
+    JQ_REQUIRE(w && codes && scales && biases, JQ_EINVAL, "null pointer");
+    const int64_t n_blocks = n / gs, n_words = n * bits / 32;
+    const int64_t ctas = (n_blocks + 31) / 32;
+    JQ_REQUIRE(ctas < (1ll << 31), JQ_EUNSUPPORTED, "tensor too large for one launch (%lld weights)", (long long)n);
+#define JQ_MSE_GS(G)                                                                                        \
+    JQ_DISPATCH_DTYPE(w_dtype, T,                                                                           \
+        JQ_DISPATCH_DTYPE(sidecar_dtype, S,                                                                 \
+            JQ_DISPATCH_BITS(bits, B,                                                                       \
+                if constexpr (B <= 4) {                                                                     \
+                    quantize_mse_kernel<T, S, B, G><<<(unsigned)ctas, 256, 0, st>>>(                        \
+                        (const T*)w, codes, (S*)scales, (S*)biases, n_blocks, n_words,                      \
+                        !(flags & JQ_QUANT_MSE_EXHAUSTIVE));                                                \
+                })))
+    if (gs == 32) { JQ_MSE_GS(32); }
+    else if (gs == 64) { JQ_MSE_GS(64); }
+    else { JQ_MSE_GS(128); }
+#undef JQ_MSE_GS
+    return check_launch("quantize_mse");
+}
+
 // ---- dequantizer ---------------------------------------------------------------
 // One thread produces 8 consecutive weights (BITS bytes of codes, at most 3 words).
 template <typename S, typename O, int BITS>
@@ -322,6 +540,16 @@ int jq_quantize_rtn(const void* w, int w_dtype, int64_t rows, int64_t K, int bit
                     uint32_t* codes, void* scales, void* biases, jq_stream_t stream) {
     return jq::launch_quantize<jq::MODE_RTN>(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, 0, codes, scales,
                                              biases, (cudaStream_t)stream);
+}
+
+int jq_quantize_mse(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size, int sidecar_dtype,
+                    int flags, uint32_t* codes, void* scales, void* biases, jq_stream_t stream) {
+    // quantize.py:153: widths above 4 bits skip the search and take the min/max branch
+    if (bits > 4)
+        return jq::launch_quantize<jq::MODE_RTN>(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, 0, codes, scales,
+                                                 biases, (cudaStream_t)stream);
+    return jq::launch_quantize_mse(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, flags, codes, scales, biases,
+                                   (cudaStream_t)stream);
 }
 
 int jq_dequantize(const uint32_t* codes, const void* scales, const void* biases, int sidecar_dtype, int64_t rows,

@@ -51,7 +51,9 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
     The source dtype of `w` (float32/float16/bfloat16) is the arithmetic's input
     precision, exactly as for mx.quantize; the converter feeds float16
     (convert.py:1550).  Sidecars default to the source dtype.  mode="rtn" runs the
-    converter's zero-point fallback instead (quantize.py:211-289, float16 sidecars).
+    converter's zero-point fallback instead (quantize.py:211-289, float16 sidecars);
+    mode="mse" adds quantize_tensor's clip-ratio search (quantize.py:153-191);
+    mode="mse_exhaustive" is the same search without the float32 screen (a cross-check).
     """
     dev = _lib.require_cuda(w)
     lib = _lib.load()
@@ -63,7 +65,7 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
     lead = tuple(w.shape[:-1])
     w2 = w.reshape(-1, K).contiguous()
     rows = w2.shape[0]
-    if mode == "rtn" and sidecar_dtype is None:
+    if mode in ("rtn", "mse", "mse_exhaustive") and sidecar_dtype is None:
         sidecar_dtype = torch.float16
     sdt = sidecar_dtype or w.dtype
     if bits not in ALLOWED_BITS or group_size not in ALLOWED_GROUP_SIZES or K % group_size or (K * bits) % 32:
@@ -82,6 +84,11 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
         elif mode == "rtn":
             _lib.check(lib.jq_quantize_rtn(w2.data_ptr(), _lib.dtype_id(w2.dtype), rows, K, bits, group_size,
                                            _lib.dtype_id(sdt), wq.data_ptr(), scales.data_ptr(),
+                                           biases.data_ptr(), _lib.stream_ptr(dev)))
+        elif mode in ("mse", "mse_exhaustive"):
+            flags = _lib.JQ_QUANT_MSE_EXHAUSTIVE if mode == "mse_exhaustive" else 0
+            _lib.check(lib.jq_quantize_mse(w2.data_ptr(), _lib.dtype_id(w2.dtype), rows, K, bits, group_size,
+                                           _lib.dtype_id(sdt), flags, wq.data_ptr(), scales.data_ptr(),
                                            biases.data_ptr(), _lib.stream_ptr(dev)))
         else:
             raise JangqError(_lib.JQ_EINVAL, f"unknown quantize mode {mode!r}")

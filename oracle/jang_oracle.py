@@ -205,6 +205,79 @@ def quantize_rtn(w, bits, group_size=64):
 
 
 # --------------------------------------------------------------------------
+# f3: clip-ratio search, quantize_tensor's default method="mse"
+#     (jang_tools/quantize.py:153-191; bits > 4 take the RTN branch, :153,:192)
+# --------------------------------------------------------------------------
+MSE_CLIP_RATIOS = np.linspace(0.7, 1.0, 20)                          # quantize.py:163
+
+
+def _sum_like_numpy(sq: np.ndarray) -> np.ndarray:
+    """Row sums of a float64 [n, gs] array (gs in 8..128) in the order numpy's
+    add.reduce uses along a contiguous axis: eight running sums over the
+    elements i = j (mod 8), folded as ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7))."""
+    n, gs = sq.shape
+    r = sq[:, 0:8].copy()
+    for i in range(8, gs, 8):
+        r = r + sq[:, i:i + 8]
+    return ((r[:, 0] + r[:, 1]) + (r[:, 2] + r[:, 3])) + ((r[:, 4] + r[:, 5]) + (r[:, 6] + r[:, 7]))
+
+
+def quantize_mse_codes(w: np.ndarray, bits: int, group_size: int = 64):
+    """Return (codes, scales, biases), f16-rounded sidecars held in float32.
+
+    The reference multiplies float32 block minima by float64 clip ratios, so
+    under NumPy >= 2 promotion rules the whole search (scale, zero point, codes,
+    squared error) runs in float64 and only the winning scale is rounded to
+    float32 (quantize.py:159,184).  This restatement follows that arithmetic,
+    with the error sum written out in numpy's reduction order.
+    """
+    if bits > 4:
+        return quantize_rtn_codes(w, bits, group_size)
+    w = np.asarray(w, dtype=np.float32)
+    rows, K = w.shape
+    if K % group_size:
+        raise ValueError("K must be a multiple of group_size")
+    L = (1 << bits) - 1
+    blk = w.reshape(-1, group_size)
+    nb = blk.shape[0]
+    wmin = blk.min(axis=1)
+    wmax = blk.max(axis=1)
+    const = wmax == wmin
+    x = blk.astype(np.float64)
+    best_q = np.zeros((nb, group_size), dtype=np.uint8)                  # :158-161
+    best_scale = np.ones(nb, dtype=np.float32)
+    best_zero = np.zeros(nb, dtype=np.float32)
+    best_mse = np.full(nb, np.inf, dtype=np.float64)
+    for ratio in MSE_CLIP_RATIOS:
+        c_min = wmin.astype(np.float64) * ratio                          # :164-165
+        c_max = wmax.astype(np.float64) * ratio
+        c_range = c_max - c_min                                          # :167-168
+        c_range[c_range == 0] = 1.0
+        scale = c_range / L                                              # :170
+        zero = np.clip(np.round(-c_min / scale), 0, L)                   # :171-172
+        q = np.clip(np.round(x / scale[:, None] + zero[:, None]), 0, L)  # :174-175
+        err = x - (q - zero[:, None]) * scale[:, None]                   # :176
+        mse = _sum_like_numpy(err * err) / group_size                    # :178
+        better = mse < best_mse                                          # :181-185
+        best_mse[better] = mse[better]
+        best_q[better] = q[better].astype(np.uint8)
+        best_scale[better] = scale[better]
+        best_zero[better] = zero[better]
+    best_scale[const] = 1.0                                              # :187-189
+    best_zero[const] = 0.0
+    best_q[const] = 0
+    scales = round_to(best_scale, "f16")                                 # :281
+    biases = round_to((-best_scale * best_zero).astype(np.float32), "f16")  # :282
+    G = K // group_size
+    return best_q.reshape(rows, K), scales.reshape(rows, G), biases.reshape(rows, G)
+
+
+def quantize_mse(w, bits, group_size=64):
+    codes, s, b = quantize_mse_codes(w, bits, group_size)
+    return pack_rows(codes, bits), s, b
+
+
+# --------------------------------------------------------------------------
 # a4: dequantizer (jang_tools/affine.py:445-463; docs/adoption/PORTING.md:80-116)
 # --------------------------------------------------------------------------
 def dequantize_affine(packed, scales, biases, bits: int, group_size: int) -> np.ndarray:

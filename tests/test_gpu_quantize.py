@@ -114,6 +114,90 @@ def test_rtn_vs_oracle(bits):
     assert np.array_equal(f32(s), so) and np.array_equal(f32(b), bo)
 
 
+@pytest.mark.parametrize("gs", (64, 128))
+@pytest.mark.parametrize("bits", (2, 3, 4, 6))
+def test_mse_golden(golden_dir, bits, gs):
+    """quantize_tensor(method="mse") vectors made by the reference (quantize.py:153-191)."""
+    z = np.load(os.path.join(golden_dir, "mse_ref.npz"))
+    wq, s, b = jq.quantize(torch.from_numpy(z["w"]).to(dev()), gs, bits, mode="mse")
+    key = f"g{gs}_b{bits}"
+    assert np.array_equal(to_np_u32(wq), z[key + "_packed"])
+    assert np.array_equal(s.cpu().numpy(), z[key + "_scales"])
+    assert np.array_equal(b.cpu().numpy(), z[key + "_biases"])
+
+
+@pytest.mark.parametrize("mode", ("mse", "mse_exhaustive"))
+@pytest.mark.parametrize("src", ("f32", "f16", "bf16"))
+@pytest.mark.parametrize("gs", (32, 64, 128))
+@pytest.mark.parametrize("bits", (2, 3, 4))
+def test_mse_vs_oracle(bits, gs, src, mode):
+    """Clip-ratio search against the oracle: codes and sidecars bit for bit, over magnitudes from 1e-3 to
+    50, with constant and zero blocks, an outlier, and a row count that leaves the last warp and the last
+    CTA partly empty."""
+    rng = np.random.default_rng(100 * bits + gs)
+    w = rng.standard_normal((37, 640)).astype(np.float32)
+    w *= np.exp(rng.uniform(np.log(1e-3), np.log(50.0), size=(37, 1))).astype(np.float32)
+    w[3, 128:256] = -0.125
+    w[4, :128] = 0.0
+    w[5, 77] = 300.0
+    wt = torch.from_numpy(w).to(dev()).to(TORCH_DT[src])
+    wq, s, b = jq.quantize(wt, gs, bits, mode=mode)
+    pk, so, bo = jo.quantize_mse(f32(wt), bits, gs)
+    assert np.array_equal(to_np_u32(wq), pk)
+    assert np.array_equal(f32(s), so) and np.array_equal(f32(b), bo)
+    assert s.dtype == torch.float16
+
+
+@pytest.mark.parametrize("bits", (2, 3, 4))
+def test_mse_screen_never_changes_the_winner(bits):
+    """The float32 screen only discards clip ratios that cannot win: on 8.4 M weights of mixed character
+    the screened search returns what the exhaustive float64 search returns.  The rows cover gaussians at
+    magnitudes from 1e-12 to 1e12, blocks of few distinct values (where several ratios reconstruct almost
+    exactly), a large common offset with a tiny spread (where float32 cannot tell the ratios apart),
+    heavy tails, and magnitudes outside the screen's float32 range."""
+    g = torch.Generator(device=dev())
+    g.manual_seed(bits)
+    R, K = 2048, 4096
+    w = torch.randn((R, K), generator=g, device=dev())
+    mag = torch.exp(torch.empty((R, 1), device=dev()).uniform_(-27.6, 27.6, generator=g))
+    w = w * mag
+    w[100:200] = torch.randint(0, 3, (100, K), generator=g, device=dev()).float() * 0.37 - 0.2
+    w[200:300] = 1000.0 + torch.randn((100, K), generator=g, device=dev()) * 1e-4
+    w[300:400] = torch.randn((100, K), generator=g, device=dev()) ** 5
+    w[400:450] = torch.randn((50, K), generator=g, device=dev()) * 1e-25
+    w[450:500] = torch.randn((50, K), generator=g, device=dev()) * 1e25
+    w[500:600] = torch.randint(-8, 8, (100, K), generator=g, device=dev()).float() / 64
+    for gs in (64, 128):
+        a = jq.quantize(w, gs, bits, mode="mse")
+        e = jq.quantize(w, gs, bits, mode="mse_exhaustive")
+        for x, y in zip(a, e):
+            assert torch.equal(x, y)
+
+
+def test_mse_wide_codes_take_rtn():
+    """quantize.py:153: above 4 bits the search is skipped."""
+    rng = np.random.default_rng(9)
+    w = torch.from_numpy((rng.standard_normal((16, 256)) * 0.02).astype(np.float32)).to(dev())
+    for bits in (5, 6, 8):
+        a = jq.quantize(w, 64, bits, mode="mse")
+        r = jq.quantize(w, 64, bits, mode="rtn")
+        assert all(torch.equal(x, y) for x, y in zip(a, r))
+
+
+def test_mse_full_size_vs_oracle():
+    """A 2048x4096 bf16 matrix at 2 bits: identical to the oracle, and the search lowers the error."""
+    rng = np.random.default_rng(0)
+    wt = torch.from_numpy((rng.standard_normal((2048, 4096)) * 0.02).astype(np.float32)).to(dev()).to(torch.bfloat16)
+    wq, s, b = jq.quantize(wt, 64, 2, mode="mse")
+    pk, so, bo = jo.quantize_mse(f32(wt), 2, 64)
+    assert np.array_equal(to_np_u32(wq), pk)
+    assert np.array_equal(f32(s), so) and np.array_equal(f32(b), bo)
+    wr, sr, br = jq.quantize(wt, 64, 2, mode="rtn")
+    e_mse = (jq.dequantize(wq, s, b, 64, 2, dtype=torch.float32) - wt.float()).square().mean().item()
+    e_rtn = (jq.dequantize(wr, sr, br, 64, 2, dtype=torch.float32) - wt.float()).square().mean().item()
+    assert e_mse < e_rtn
+
+
 def test_config1_full_size_bit_exact():
     """BASELINE config 1: 4096x4096 N(0,0.02) seed 0, 4-bit, group 64, bf16."""
     rng = np.random.default_rng(0)
