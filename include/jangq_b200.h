@@ -41,9 +41,11 @@ extern "C" {
 #define JQ_F16   1
 #define JQ_BF16  2
 
-/* jq_quantize flags */
+/* jq_quantize / jq_quantize_rtn flags */
 #define JQ_QUANT_F16_TINY_GUARD  1  /* numpy-mirror floor on |scale| for f16 sidecars
                                        (jang_tools/affine.py:46-51); MLX itself has none */
+#define JQ_QUANT_IEEE_DIV        4  /* per-weight IEEE division behind a guarded reciprocal instead of the
+                                       reciprocal-and-residual form (same codes; for cross-checking) */
 /* jq_quantize_mse flags */
 #define JQ_QUANT_MSE_EXHAUSTIVE  2  /* evaluate every clip ratio in float64, no float32 screen */
 
@@ -66,7 +68,7 @@ int jq_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, i
  * is missing: quantize_tensor(method="rtn") (jang_tools/quantize.py:211-289,
  * caller convert.py:1564-1592).  Sidecars are float16 as in the reference. */
 int jq_quantize_rtn(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size,
-                    int sidecar_dtype, uint32_t* codes, void* scales, void* biases,
+                    int sidecar_dtype, int flags, uint32_t* codes, void* scales, void* biases,
                     jq_stream_t stream);
 
 /* K1c. The same zero-point quantizer with the clip-ratio search that is

@@ -18,6 +18,7 @@ JQ_OK, JQ_EINVAL, JQ_EUNSUPPORTED, JQ_EWORKSPACE, JQ_ECUDA, JQ_ETIMEOUT = range(
 JQ_F32, JQ_F16, JQ_BF16 = 0, 1, 2
 JQ_QUANT_F16_TINY_GUARD = 1
 JQ_QUANT_MSE_EXHAUSTIVE = 2
+JQ_QUANT_IEEE_DIV = 4
 JQ_GEMV_STATIC_WEIGHTS = 1
 JQ_GATHER_FEW_LOCAL = 2
 QGEMV_MAX_M = 16
@@ -58,7 +59,7 @@ SIGNATURES = {
     "jq_status_string": (C.c_char_p, [_i32]),
     "jq_last_error": (C.c_char_p, []),
     "jq_quantize": (C.c_int, [_p, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _p, _p, _p, _p]),
-    "jq_quantize_rtn": (C.c_int, [_p, _i32, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p]),
+    "jq_quantize_rtn": (C.c_int, [_p, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _p, _p, _p, _p]),
     "jq_quantize_mse": (C.c_int, [_p, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _p, _p, _p, _p]),
     "jq_dequantize": (C.c_int, [_p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _p]),
     "jq_qgemv": (C.c_int, [_p, _i32, _i64, _i64, _p, _p, _p, _i32, _i64, _i64, _i32, _i32, _p, _i32, _i64, _p]),

@@ -71,6 +71,10 @@ __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, fl
 // lane's flat 16-weight chunk index; lanes of an even/odd pair cooperate for odd
 // widths.  All lanes of the warp must call this (it shuffles).
 template <int BITS>
+__device__ __forceinline__ void store_words(uint32_t* __restrict__ codes, int64_t chunk, const uint32_t (&out)[4],
+                                            bool valid);
+
+template <int BITS>
 __device__ __forceinline__ void store_codes(uint32_t* __restrict__ codes, int64_t chunk, const uint32_t (&q)[16],
                                             bool valid) {
     uint32_t out[4] = {0u, 0u, 0u, 0u};
@@ -80,6 +84,13 @@ __device__ __forceinline__ void store_codes(uint32_t* __restrict__ codes, int64_
         out[wd] |= q[j] << sh;
         if (sh + BITS > 32) out[wd + 1] |= q[j] >> (32 - sh);
     }
+    store_words<BITS>(codes, chunk, out, valid);
+}
+
+// The 2*BITS bytes of one lane, already packed LSB-first into out[0..], to memory as whole words.
+template <int BITS>
+__device__ __forceinline__ void store_words(uint32_t* __restrict__ codes, int64_t chunk, const uint32_t (&out)[4],
+                                            bool valid) {
     if constexpr (BITS == 2) {
         if (valid) codes[chunk] = out[0];
     } else if constexpr (BITS == 4) {
@@ -197,6 +208,192 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __rest
     }
 }
 
+// ---- affine and RTN quantizers, lean form ----------------------------------------------------------------
+// The same arithmetic as quantize_kernel in fewer instructions per weight (the kernel is bound by
+// instruction issue, not by HBM).  With 16-bit sources exact rounding ties are common (both the weights and the
+// group edge sit on a coarse grid, so (w - edge) * q0 / edge is often exactly k + 1/2): a guarded fast path takes its
+// exact-division branch in a large share of warp steps.  This form has no guard and no branch:
+//   * y = RN(t/scale) from the correctly rounded reciprocal in three instructions: y0 = RN(t*r), then
+//     y = RN(y0 + RN(t - y0*scale) * r).  The residual is exact in an fma, and with r = RN(1/scale) and y0 within one
+//     ulp of the quotient the corrected value is the correctly rounded quotient (Markstein's theorem); neither
+//     overflow nor underflow can occur here, since |scale| >= 1e-7 up to one rounding and |t| <= hi - lo;
+//   * y + 1.5*2^23 is rint(y) (ties to even) with the integer in the low mantissa bits; clamping those bits to
+//     [0x4B400000, 0x4B400000 + bins] and adding them, shifted, into the output word packs the code, and the
+//     0x4B400000 that every term carries is removed once per word;
+//   * 16-bit sources keep their 16 weights as 8 packed registers; min/max run on pairs (bf16x2 / half2 min and max
+//     are exact), and a weight is widened only where it is used.
+// NaN weights give code `bins`, as the guarded kernel's exact branch does.
+template <typename T> struct Raw16;
+template <> struct Raw16<float> {
+    float v[16];
+    __device__ __forceinline__ void load(const float* p) { load16<float>(p, v); }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    }
+    __device__ __forceinline__ float get(int j) const { return v[j]; }
+    __device__ __forceinline__ void minmax(float& lo, float& hi) const {
+        lo = v[0]; hi = v[0];
+#pragma unroll
+        for (int j = 1; j < 16; ++j) { lo = fminf(lo, v[j]); hi = fmaxf(hi, v[j]); }
+    }
+};
+template <> struct Raw16<__nv_bfloat16> {
+    uint32_t u[8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+        u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w; u[4] = b.x; u[5] = b.y; u[6] = b.z; u[7] = b.w;
+    }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) u[j] = 0u;
+    }
+    __device__ __forceinline__ float get(int j) const {
+        return __uint_as_float((j & 1) ? (u[j >> 1] & 0xFFFF0000u) : (u[j >> 1] << 16));
+    }
+    __device__ __forceinline__ void minmax(float& lo, float& hi) const {
+        __nv_bfloat162 l = *reinterpret_cast<const __nv_bfloat162*>(&u[0]), h = l;
+#pragma unroll
+        for (int j = 1; j < 8; ++j) {
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&u[j]);
+            l = __hmin2(l, x); h = __hmax2(h, x);
+        }
+        lo = fminf(__low2float(l), __high2float(l));
+        hi = fmaxf(__low2float(h), __high2float(h));
+    }
+};
+template <> struct Raw16<__half> {
+    uint32_t u[8];
+    __device__ __forceinline__ void load(const __half* p) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+        u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w; u[4] = b.x; u[5] = b.y; u[6] = b.z; u[7] = b.w;
+    }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) u[j] = 0u;
+    }
+    __device__ __forceinline__ float get(int j) const {
+        const __half2 x = *reinterpret_cast<const __half2*>(&u[j >> 1]);
+        return (j & 1) ? __high2float(x) : __low2float(x);
+    }
+    __device__ __forceinline__ void minmax(float& lo, float& hi) const {
+        __half2 l = *reinterpret_cast<const __half2*>(&u[0]), h = l;
+#pragma unroll
+        for (int j = 1; j < 8; ++j) {
+            const __half2 x = *reinterpret_cast<const __half2*>(&u[j]);
+            l = __hmin2(l, x); h = __hmax2(h, x);
+        }
+        lo = fminf(__low2float(l), __high2float(l));
+        hi = fmaxf(__low2float(h), __high2float(h));
+    }
+};
+
+template <typename T, typename S, int BITS, int MODE>
+__global__ void __launch_bounds__(256)
+quantize_lean_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __restrict__ scales,
+                     S* __restrict__ biases, int64_t n_chunks, int lanes_per_group, int flags) {
+    constexpr int BINS = (1 << BITS) - 1;
+    constexpr float MAGIC = 12582912.0f;              // 1.5 * 2^23; its bit pattern is 0x4B400000
+    constexpr uint32_t MBITS = 0x4B400000u;
+    const int64_t chunk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = chunk < n_chunks;
+    Raw16<T> raw;
+    if (valid) raw.load(w + chunk * 16); else raw.zero();
+    float lo, hi;
+    raw.minmax(lo, hi);
+    for (int d = 1; d < lanes_per_group; d <<= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+        hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+    }
+    // AFFINE: code = clamp(rint((w - bias) / scale));  RTN: code = clamp(rint(w / scale + zero))
+    float scale, bias, zero = 0.0f;
+    bool is_const = false;
+    if constexpr (MODE == MODE_AFFINE) {
+        // jang_tools/affine.py:230-250
+        hi = fmaxf(hi, 0.0f);
+        scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), (float)BINS), 1e-7f);
+        const bool dom_lo = fabsf(lo) > fabsf(hi);
+        scale = dom_lo ? scale : -scale;
+        const float edge = dom_lo ? lo : hi;
+        const float q0 = rintf(__fdiv_rn(edge, scale));
+        bias = 0.0f;
+        if (q0 != 0.0f) { scale = __fdiv_rn(edge, q0); bias = edge; }
+    } else {
+        // jang_tools/quantize.py:148-205 (standard min/max branch)
+        is_const = (hi == lo);
+        scale = __fdiv_rn(is_const ? 1.0f : __fsub_rn(hi, lo), (float)BINS);
+        zero = fminf(fmaxf(rintf(__fdiv_rn(-lo, scale)), 0.0f), (float)BINS);
+        bias = 0.0f;
+    }
+    const float rcp = __frcp_rn(scale);
+
+    uint32_t out[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float t = MODE == MODE_AFFINE ? __fsub_rn(raw.get(j), bias) : raw.get(j);
+        const float y0 = __fmul_rn(t, rcp);
+        float y = __fmaf_rn(__fmaf_rn(-y0, scale, t), rcp, y0);           // = RN(t / scale)
+        if constexpr (MODE == MODE_RTN) y = __fadd_rn(y, zero);
+        const int si = __float_as_int(__fadd_rn(y, MAGIC));               // MBITS + rint(y); order-preserving beyond
+        const uint32_t x = (uint32_t)min(max(si, (int)MBITS), (int)(MBITS + BINS));
+        const int pos = j * BITS, wd = pos >> 5, sh = pos & 31;
+        out[wd] += x << sh;
+        if (sh + BITS > 32) out[wd + 1] += x >> (32 - sh);   // MBITS has 22 low zero bits: (MBITS+q)>>k = (MBITS>>k)+(q>>k)
+    }
+    // remove what the 0x4B400000 of every term added to each word (compile-time constants)
+    {
+        uint32_t c[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int pos = j * BITS, wd = pos >> 5, sh = pos & 31;
+            c[wd] += MBITS << sh;
+            if (sh + BITS > 32) c[wd + 1] += MBITS >> (32 - sh);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] -= c[i];
+    }
+    // A scale whose reciprocal is not a normal float32 with full precision (groups near the ends of the float32
+    // range) is outside what the residual form guarantees: such a lane divides per weight.
+    if (!(fabsf(scale) > 1e-30f && fabsf(scale) < 1e30f) && valid) {
+        const T* src = w + chunk * 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = 0u;
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) {
+            const float v = Elt<T>::to_f32(src[j]);
+            float r = MODE == MODE_AFFINE ? rintf(__fdiv_rn(__fsub_rn(v, bias), scale))
+                                          : rintf(__fadd_rn(__fdiv_rn(v, scale), zero));
+            r = fmaxf(fminf(r, (float)BINS), 0.0f);
+            const uint32_t qv = (uint32_t)(int)r;
+            const int pos = j * BITS, wd = pos >> 5, sh = pos & 31;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (i == wd) out[i] |= qv << sh;
+                if (i == wd + 1 && sh + BITS > 32) out[i] |= qv >> (32 - sh);
+            }
+        }
+    }
+    if constexpr (MODE == MODE_AFFINE) {
+        if ((flags & JQ_QUANT_F16_TINY_GUARD) && Elt<S>::id == JQ_F16) {
+            const float tiny = 6.103515625e-05f;  // smallest normal float16 (affine.py:43)
+            if (fabsf(scale) < tiny) scale = copysignf(tiny, scale == 0.0f ? 1.0f : scale);
+        }
+    } else {
+        if (is_const) {                               // quantize.py:203-205
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[i] = 0u;
+            scale = 1.0f; zero = 0.0f;
+        }
+        bias = __fmul_rn(-scale, zero);               // quantize.py:279
+    }
+    store_words<BITS>(codes, chunk, out, valid);
+    if (valid && (threadIdx.x & (lanes_per_group - 1)) == 0) {
+        const int64_t g = chunk / lanes_per_group;
+        scales[g] = Elt<S>::from_f32(scale);
+        biases[g] = Elt<S>::from_f32(bias);
+    }
+}
+
 template <int MODE>
 static int launch_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int gs, int sidecar_dtype,
                            int flags, uint32_t* codes, void* scales, void* biases, cudaStream_t st) {
@@ -212,6 +409,14 @@ static int launch_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, 
     const int64_t blocks = (n_chunks + threads - 1) / threads;
     JQ_REQUIRE(blocks < (1ll << 31), JQ_EUNSUPPORTED, "tensor too large for one launch (%lld weights)", (long long)n);
     const int lpg = gs / 16;
+    if (!(flags & JQ_QUANT_IEEE_DIV)) {
+        JQ_DISPATCH_DTYPE(w_dtype, T,
+            JQ_DISPATCH_DTYPE(sidecar_dtype, S,
+                JQ_DISPATCH_BITS(bits, B,
+                    (quantize_lean_kernel<T, S, B, MODE><<<(unsigned)blocks, threads, 0, st>>>(
+                        (const T*)w, codes, (S*)scales, (S*)biases, n_chunks, lpg, flags)))))
+        return check_launch("quantize");
+    }
     JQ_DISPATCH_DTYPE(w_dtype, T,
         JQ_DISPATCH_DTYPE(sidecar_dtype, S,
             JQ_DISPATCH_BITS(bits, B,
@@ -537,8 +742,8 @@ int jq_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, i
 }
 
 int jq_quantize_rtn(const void* w, int w_dtype, int64_t rows, int64_t K, int bits, int group_size, int sidecar_dtype,
-                    uint32_t* codes, void* scales, void* biases, jq_stream_t stream) {
-    return jq::launch_quantize<jq::MODE_RTN>(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, 0, codes, scales,
+                    int flags, uint32_t* codes, void* scales, void* biases, jq_stream_t stream) {
+    return jq::launch_quantize<jq::MODE_RTN>(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, flags, codes, scales,
                                              biases, (cudaStream_t)stream);
 }
 
@@ -546,7 +751,7 @@ int jq_quantize_mse(const void* w, int w_dtype, int64_t rows, int64_t K, int bit
                     int flags, uint32_t* codes, void* scales, void* biases, jq_stream_t stream) {
     // quantize.py:153: widths above 4 bits skip the search and take the min/max branch
     if (bits > 4)
-        return jq::launch_quantize<jq::MODE_RTN>(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, 0, codes, scales,
+        return jq::launch_quantize<jq::MODE_RTN>(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, flags, codes, scales,
                                                  biases, (cudaStream_t)stream);
     return jq::launch_quantize_mse(w, w_dtype, rows, K, bits, group_size, sidecar_dtype, flags, codes, scales, biases,
                                    (cudaStream_t)stream);

@@ -53,7 +53,8 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
     (convert.py:1550).  Sidecars default to the source dtype.  mode="rtn" runs the
     converter's zero-point fallback instead (quantize.py:211-289, float16 sidecars);
     mode="mse" adds quantize_tensor's clip-ratio search (quantize.py:153-191);
-    mode="mse_exhaustive" is the same search without the float32 screen (a cross-check).
+    mode="mse_exhaustive" is the same search without the float32 screen, and
+    mode="affine_ieee_div" / "rtn_ieee_div" the quantizers with a per-weight IEEE division (cross-checks).
     """
     dev = _lib.require_cuda(w)
     lib = _lib.load()
@@ -65,7 +66,7 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
     lead = tuple(w.shape[:-1])
     w2 = w.reshape(-1, K).contiguous()
     rows = w2.shape[0]
-    if mode in ("rtn", "mse", "mse_exhaustive") and sidecar_dtype is None:
+    if mode in ("rtn", "rtn_ieee_div", "mse", "mse_exhaustive") and sidecar_dtype is None:
         sidecar_dtype = torch.float16
     sdt = sidecar_dtype or w.dtype
     if bits not in ALLOWED_BITS or group_size not in ALLOWED_GROUP_SIZES or K % group_size or (K * bits) % 32:
@@ -76,14 +77,17 @@ def quantize(w: torch.Tensor, group_size: int = 64, bits: int = 4, *, sidecar_dt
     scales = torch.empty((rows, G), dtype=sdt, device=dev)
     biases = torch.empty((rows, G), dtype=sdt, device=dev)
     with torch.cuda.device(dev):
-        if mode == "affine":
+        if mode in ("affine", "affine_ieee_div"):
             flags = _lib.JQ_QUANT_F16_TINY_GUARD if f16_tiny_guard else 0
+            if mode == "affine_ieee_div":
+                flags |= _lib.JQ_QUANT_IEEE_DIV
             _lib.check(lib.jq_quantize(w2.data_ptr(), _lib.dtype_id(w2.dtype), rows, K, bits, group_size,
                                        _lib.dtype_id(sdt), flags, wq.data_ptr(), scales.data_ptr(),
                                        biases.data_ptr(), _lib.stream_ptr(dev)))
-        elif mode == "rtn":
+        elif mode in ("rtn", "rtn_ieee_div"):
+            flags = _lib.JQ_QUANT_IEEE_DIV if mode == "rtn_ieee_div" else 0
             _lib.check(lib.jq_quantize_rtn(w2.data_ptr(), _lib.dtype_id(w2.dtype), rows, K, bits, group_size,
-                                           _lib.dtype_id(sdt), wq.data_ptr(), scales.data_ptr(),
+                                           _lib.dtype_id(sdt), flags, wq.data_ptr(), scales.data_ptr(),
                                            biases.data_ptr(), _lib.stream_ptr(dev)))
         elif mode in ("mse", "mse_exhaustive"):
             flags = _lib.JQ_QUANT_MSE_EXHAUSTIVE if mode == "mse_exhaustive" else 0

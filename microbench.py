@@ -105,8 +105,8 @@ def bench_quantize(N, K, bits, gs, iters, rotate_mb, dtype=torch.bfloat16, op="q
     g = torch.Generator(device=dev)
     g.manual_seed(0)
     wsrc = [(torch.randn((N, K), generator=g, device=dev) * 0.02).to(dtype) for _ in range(copies)]
-    if op in ("quantize", "quantize_rtn", "quantize_mse", "quantize_mse_exhaustive"):
-        mode = {"quantize": "affine", "quantize_rtn": "rtn", "quantize_mse": "mse",
+    if op in ("quantize", "quantize_ieee_div", "quantize_rtn", "quantize_rtn_ieee_div", "quantize_mse", "quantize_mse_exhaustive"):
+        mode = {"quantize": "affine", "quantize_ieee_div": "affine_ieee_div", "quantize_rtn": "rtn", "quantize_rtn_ieee_div": "rtn_ieee_div", "quantize_mse": "mse",
                 "quantize_mse_exhaustive": "mse_exhaustive"}[op]
 
         def fn():
@@ -184,7 +184,7 @@ def bench_moe_prefill(tokens, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_rtn", "quantize_mse", "quantize_mse_exhaustive", "quantize_imatrix", "dequantize", "moe_decode", "moe_prefill"))
+    ap.add_argument("--op", default="qgemv", choices=("qgemv", "qgemm", "quantize", "quantize_ieee_div", "quantize_rtn", "quantize_rtn_ieee_div", "quantize_mse", "quantize_mse_exhaustive", "quantize_imatrix", "dequantize", "moe_decode", "moe_prefill"))
     ap.add_argument("--sweep", default=None, choices=(None, "qgemv", "qgemv-small", "qgemm"))
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
