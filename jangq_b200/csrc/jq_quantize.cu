@@ -1,26 +1,18 @@
 // K1: affine group quantizer, its zero-point RTN sibling with and without the clip-ratio search, and the
 // dequantizer.
 //
-// All three are streaming kernels bounded by HBM bandwidth: the quantizer reads
-// sizeof(T) bytes and writes bits/8 + 2*sizeof(S)/group_size bytes per weight.
-// Because K % group_size == 0 and K*bits % 32 == 0, groups and packed words
-// never straddle a row, so the kernels walk the tensor as one flat array.
+// Bytes per weight: the quantizers read sizeof(T) and write bits/8 + 2*sizeof(S)/group_size.  Because
+// K % group_size == 0 and K*bits % 32 == 0, groups and packed words never straddle a row, so the kernels walk the
+// tensor as one flat array.  Arithmetic follows the reference line by line with IEEE round-to-nearest intrinsics so
+// that no FMA contraction or approximate division can change a code (jang_tools/affine.py:227-252).
 //
-// Mapping: one thread owns 16 consecutive weights (one or two 16-byte loads per
-// 8 of them), so a group of 32/64/128 weights is 2/4/8 adjacent lanes and the
-// min/max reduction is 1-3 xor-shuffles.  16 codes of `bits` bits are 2*bits
-// bytes: whole words for 2/4/6/8 bits; for 3/5 bits two adjacent lanes exchange
-// 16 bits so that every store is a whole 32-bit word.
-//
-// Arithmetic follows the reference line by line with IEEE round-to-nearest
-// intrinsics so that no FMA contraction or approximate division can change a
-// code (jang_tools/affine.py:227-252).  The per-weight division has a fast
-// path: t*rcp(scale) differs from the correctly rounded quotient by less than
-// 2^-23*|q| <= 3.1e-5 for |q| <= 257, so rint() of both agree unless the
-// quotient lies within that distance of a half-integer; values within 1e-3 of one
-// (1 in 500; one warp instruction in 16 has such a lane) are recomputed with the
-// exact division.
+// quantize_group_kernel is the product path.  quantize_kernel is the earlier form, selected by JQ_QUANT_IEEE_DIV
+// for cross-checks: one thread owns 16 consecutive weights, a group is 2/4/8 adjacent lanes, and the per-weight
+// quotient is t*rcp(scale) with a fallback to the IEEE division within 1e-3 of a rounding tie.
+#include <type_traits>
+
 #include "jq_common.cuh"
+#include "jq_mma.cuh"
 
 namespace jq {
 
@@ -208,103 +200,140 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __rest
     }
 }
 
-// ---- affine and RTN quantizers, lean form ----------------------------------------------------------------
-// The same arithmetic as quantize_kernel in fewer instructions per weight (the kernel is bound by
-// instruction issue, not by HBM).  With 16-bit sources exact rounding ties are common (both the weights and the
-// group edge sit on a coarse grid, so (w - edge) * q0 / edge is often exactly k + 1/2): a guarded fast path takes its
-// exact-division branch in a large share of warp steps.  This form has no guard and no branch:
+// ---- affine and RTN quantizers: one thread per group, branch-free exact quotient -------------------------------
+// The arithmetic of quantize_kernel (above: the form that divides per weight, kept as a cross-check behind
+// JQ_QUANT_IEEE_DIV) in half the instructions; the quantizers are bound by instruction issue, not by HBM.
 //   * y = RN(t/scale) from the correctly rounded reciprocal in three instructions: y0 = RN(t*r), then
 //     y = RN(y0 + RN(t - y0*scale) * r).  The residual is exact in an fma, and with r = RN(1/scale) and y0 within one
-//     ulp of the quotient the corrected value is the correctly rounded quotient (Markstein's theorem); neither
-//     overflow nor underflow can occur here, since |scale| >= 1e-7 up to one rounding and |t| <= hi - lo;
-//   * y + 1.5*2^23 is rint(y) (ties to even) with the integer in the low mantissa bits; clamping those bits to
-//     [0x4B400000, 0x4B400000 + bins] and adding them, shifted, into the output word packs the code, and the
-//     0x4B400000 that every term carries is removed once per word;
-//   * 16-bit sources keep their 16 weights as 8 packed registers; min/max run on pairs (bf16x2 / half2 min and max
-//     are exact), and a weight is widened only where it is used.
-// NaN weights give code `bins`, as the guarded kernel's exact branch does.
-template <typename T> struct Raw16;
-template <> struct Raw16<float> {
-    float v[16];
-    __device__ __forceinline__ void load(const float* p) { load16<float>(p, v); }
-    __device__ __forceinline__ void zero() {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-    }
-    __device__ __forceinline__ float get(int j) const { return v[j]; }
-    __device__ __forceinline__ void minmax(float& lo, float& hi) const {
-        lo = v[0]; hi = v[0];
-#pragma unroll
-        for (int j = 1; j < 16; ++j) { lo = fminf(lo, v[j]); hi = fmaxf(hi, v[j]); }
-    }
-};
-template <> struct Raw16<__nv_bfloat16> {
-    uint32_t u[8];
-    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-        u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w; u[4] = b.x; u[5] = b.y; u[6] = b.z; u[7] = b.w;
-    }
-    __device__ __forceinline__ void zero() {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) u[j] = 0u;
-    }
-    __device__ __forceinline__ float get(int j) const {
-        return __uint_as_float((j & 1) ? (u[j >> 1] & 0xFFFF0000u) : (u[j >> 1] << 16));
-    }
-    __device__ __forceinline__ void minmax(float& lo, float& hi) const {
-        __nv_bfloat162 l = *reinterpret_cast<const __nv_bfloat162*>(&u[0]), h = l;
-#pragma unroll
-        for (int j = 1; j < 8; ++j) {
-            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&u[j]);
-            l = __hmin2(l, x); h = __hmax2(h, x);
-        }
-        lo = fminf(__low2float(l), __high2float(l));
-        hi = fmaxf(__low2float(h), __high2float(h));
+//     ulp of the quotient the corrected value is the correctly rounded quotient (Markstein's theorem).  No guard and
+//     no branch: with 16-bit sources exact rounding ties are common (weights and group edge sit on a coarse grid, so
+//     (w - edge) * q0 / edge is often exactly k + 1/2) and a guarded reciprocal takes its exact-division branch in a
+//     large share of warp steps.  Groups whose scale is outside [1e-30, 1e30], where the reciprocal is not a normal
+//     float32 of full precision, divide per weight instead;
+//   * y * 2^-149 is a subnormal whose bit pattern is rint(y) (ties to even) as an integer, negative for negative y;
+//     for 2-, 4- and 8-bit codes one cvt.pack.sat then clamps two of them and shifts them into the word being built;
+//   * a thread owns a whole group, so the per-group scalars (three IEEE divisions, the reciprocal) are issued once per
+//     group and need no shuffles; with 16 weights per lane they were a third of all instructions, computed by each of
+//     the 2/4/8 lanes sharing a group.  A CTA of 128 threads copies its 128 consecutive groups into shared memory with
+//     coalesced 16-byte asynchronous copies (row pitch = group bytes + 16, an odd number of 16-byte slots, so the
+//     per-thread row reads are conflict-free), then every thread walks its own row twice: min/max (on bf16x2 / half2
+//     pairs for 16-bit sources: exact), then codes in runs of 32 weights (= BITS whole words);
+//   * sidecars leave as consecutive elements of consecutive lanes.
+// NaN weights give code `bins`, as the dividing kernel does.
+// rint(y), ties to even, as an integer: y * 2^-149 lands on the subnormal grid, whose bit pattern is the integer
+// itself (sign in bit 31, so a negative y reads as a negative integer; y >= 2^23 and NaN read as large positive
+// ones).  mul.rn.f32 without .ftz keeps subnormal results whatever the compile flags.
+__device__ __forceinline__ int rint_bits(float y) {
+    int r;
+    asm("{\n\t.reg .f32 t;\n\tmul.rn.f32 t, %1, 0f00000001;\n\tmov.b32 %0, t;\n\t}" : "=r"(r) : "f"(y));
+    return r;
+}
+
+// d = (c << 2*BITS) | sat(a) << BITS | sat(b), each saturated to [0, 2^BITS - 1]
+template <int BITS>
+__device__ __forceinline__ uint32_t pack_sat2(int a, int b, uint32_t c) {
+    uint32_t d;
+    if constexpr (BITS == 8) asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    else if constexpr (BITS == 4) asm("cvt.pack.sat.u4.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    else asm("cvt.pack.sat.u2.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <typename T> struct Vec16;      // 16 bytes of weights
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    template <int E> static __device__ __forceinline__ float get(const uint4& u) {
+        return __uint_as_float(E == 0 ? u.x : E == 1 ? u.y : E == 2 ? u.z : u.w);
     }
 };
-template <> struct Raw16<__half> {
-    uint32_t u[8];
-    __device__ __forceinline__ void load(const __half* p) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-        u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w; u[4] = b.x; u[5] = b.y; u[6] = b.z; u[7] = b.w;
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    template <int E> static __device__ __forceinline__ float get(const uint4& u) {
+        const uint32_t wd = (E >> 1) == 0 ? u.x : (E >> 1) == 1 ? u.y : (E >> 1) == 2 ? u.z : u.w;
+        return __uint_as_float((E & 1) ? (wd & 0xFFFF0000u) : (wd << 16));
     }
-    __device__ __forceinline__ void zero() {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) u[j] = 0u;
-    }
-    __device__ __forceinline__ float get(int j) const {
-        const __half2 x = *reinterpret_cast<const __half2*>(&u[j >> 1]);
-        return (j & 1) ? __high2float(x) : __low2float(x);
-    }
-    __device__ __forceinline__ void minmax(float& lo, float& hi) const {
-        __half2 l = *reinterpret_cast<const __half2*>(&u[0]), h = l;
-#pragma unroll
-        for (int j = 1; j < 8; ++j) {
-            const __half2 x = *reinterpret_cast<const __half2*>(&u[j]);
-            l = __hmin2(l, x); h = __hmax2(h, x);
-        }
-        lo = fminf(__low2float(l), __high2float(l));
-        hi = fmaxf(__low2float(h), __high2float(h));
+};
+template <> struct Vec16<__half> {
+    static constexpr int N = 8;
+    template <int E> static __device__ __forceinline__ float get(const uint4& u) {
+        const uint32_t wd = (E >> 1) == 0 ? u.x : (E >> 1) == 1 ? u.y : (E >> 1) == 2 ? u.z : u.w;
+        const __half2 h = *reinterpret_cast<const __half2*>(&wd);
+        return (E & 1) ? __high2float(h) : __low2float(h);
     }
 };
 
-template <typename T, typename S, int BITS, int MODE>
-__global__ void __launch_bounds__(256)
-quantize_lean_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __restrict__ scales,
-                     S* __restrict__ biases, int64_t n_chunks, int lanes_per_group, int flags) {
-    constexpr int BINS = (1 << BITS) - 1;
-    constexpr float MAGIC = 12582912.0f;              // 1.5 * 2^23; its bit pattern is 0x4B400000
-    constexpr uint32_t MBITS = 0x4B400000u;
-    const int64_t chunk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool valid = chunk < n_chunks;
-    Raw16<T> raw;
-    if (valid) raw.load(w + chunk * 16); else raw.zero();
-    float lo, hi;
-    raw.minmax(lo, hi);
-    for (int d = 1; d < lanes_per_group; d <<= 1) {
-        lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
-        hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+template <typename T>
+__device__ __forceinline__ void row_minmax(const uint8_t* row, int vectors, float& lo, float& hi) {
+    if constexpr (sizeof(T) == 4) {
+        const float4 f0 = *reinterpret_cast<const float4*>(row);
+        lo = fminf(fminf(f0.x, f0.y), fminf(f0.z, f0.w));
+        hi = fmaxf(fmaxf(f0.x, f0.y), fmaxf(f0.z, f0.w));
+#pragma unroll 4
+        for (int i = 1; i < vectors; ++i) {
+            const float4 f = *reinterpret_cast<const float4*>(row + 16 * i);
+            lo = fminf(fminf(lo, f.x), fminf(fminf(f.y, f.z), f.w));
+            hi = fmaxf(fmaxf(hi, f.x), fmaxf(fmaxf(f.y, f.z), f.w));
+        }
+    } else {
+        using P = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+        uint4 u = *reinterpret_cast<const uint4*>(row);
+        P l = __hmin2(__hmin2(*reinterpret_cast<P*>(&u.x), *reinterpret_cast<P*>(&u.y)),
+                      __hmin2(*reinterpret_cast<P*>(&u.z), *reinterpret_cast<P*>(&u.w)));
+        P h = __hmax2(__hmax2(*reinterpret_cast<P*>(&u.x), *reinterpret_cast<P*>(&u.y)),
+                      __hmax2(*reinterpret_cast<P*>(&u.z), *reinterpret_cast<P*>(&u.w)));
+#pragma unroll 4
+        for (int i = 1; i < vectors; ++i) {
+            u = *reinterpret_cast<const uint4*>(row + 16 * i);
+            l = __hmin2(__hmin2(l, *reinterpret_cast<P*>(&u.x)),
+                        __hmin2(__hmin2(*reinterpret_cast<P*>(&u.y), *reinterpret_cast<P*>(&u.z)), *reinterpret_cast<P*>(&u.w)));
+            h = __hmax2(__hmax2(h, *reinterpret_cast<P*>(&u.x)),
+                        __hmax2(__hmax2(*reinterpret_cast<P*>(&u.y), *reinterpret_cast<P*>(&u.z)), *reinterpret_cast<P*>(&u.w)));
+        }
+        lo = fminf(__low2float(l), __high2float(l));
+        hi = fmaxf(__low2float(h), __high2float(h));
     }
+}
+
+template <typename S>
+__device__ __forceinline__ void put_sidecar(void* p, int64_t i, float v) {
+    reinterpret_cast<S*>(p)[i] = Elt<S>::from_f32(v);
+}
+
+template <typename T, int BITS, int GS, int MODE>
+__global__ void __launch_bounds__(128)
+quantize_group_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, void* __restrict__ scales,
+                      void* __restrict__ biases, int sidecar_dtype, int64_t n_groups, int flags) {
+    constexpr int THREADS = 128;
+    constexpr int ROW = GS * (int)sizeof(T);          // bytes of one group
+    constexpr int VPG = ROW / 16;                     // 16-byte vectors per group (a power of two)
+    constexpr int PITCH = ROW + 16;
+    constexpr int WPV = Vec16<T>::N;                  // weights per vector
+    constexpr int VPR = 32 / WPV;                     // vectors per run of 32 weights
+    constexpr int BINS = (1 << BITS) - 1;
+    extern __shared__ __align__(16) uint8_t tile[];
+    const int tid = threadIdx.x;
+    const int64_t g0 = (int64_t)blockIdx.x * THREADS;
+    const int n_here = (int)min((int64_t)THREADS, n_groups - g0);
+
+    {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(w) + g0 * ROW;
+#pragma unroll
+        for (int i = 0; i < VPG; ++i) {
+            const int v = i * THREADS + tid;
+            const int g = v / VPG, c = v % VPG;
+            if (g < n_here) cp_async16(tile + g * PITCH + c * 16, src + (size_t)v * 16);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+    }
+    if (tid >= n_here) return;
+    const uint8_t* row = tile + tid * PITCH;
+    const int64_t grp = g0 + tid;
+
+    float lo, hi;
+    row_minmax<T>(row, VPG, lo, hi);
+
     // AFFINE: code = clamp(rint((w - bias) / scale));  RTN: code = clamp(rint(w / scale + zero))
     float scale, bias, zero = 0.0f;
     bool is_const = false;
@@ -326,72 +355,120 @@ quantize_lean_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* _
         bias = 0.0f;
     }
     const float rcp = __frcp_rn(scale);
+    uint32_t* dst = codes + grp * (GS * BITS / 32);
 
-    uint32_t out[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float t = MODE == MODE_AFFINE ? __fsub_rn(raw.get(j), bias) : raw.get(j);
-        const float y0 = __fmul_rn(t, rcp);
-        float y = __fmaf_rn(__fmaf_rn(-y0, scale, t), rcp, y0);           // = RN(t / scale)
-        if constexpr (MODE == MODE_RTN) y = __fadd_rn(y, zero);
-        const int si = __float_as_int(__fadd_rn(y, MAGIC));               // MBITS + rint(y); order-preserving beyond
-        const uint32_t x = (uint32_t)min(max(si, (int)MBITS), (int)(MBITS + BINS));
-        const int pos = j * BITS, wd = pos >> 5, sh = pos & 31;
-        out[wd] += x << sh;
-        if (sh + BITS > 32) out[wd + 1] += x >> (32 - sh);   // MBITS has 22 low zero bits: (MBITS+q)>>k = (MBITS>>k)+(q>>k)
-    }
-    // remove what the 0x4B400000 of every term added to each word (compile-time constants)
-    {
-        uint32_t c[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int pos = j * BITS, wd = pos >> 5, sh = pos & 31;
-            c[wd] += MBITS << sh;
-            if (sh + BITS > 32) c[wd + 1] += MBITS >> (32 - sh);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[i] -= c[i];
-    }
-    // A scale whose reciprocal is not a normal float32 with full precision (groups near the ends of the float32
-    // range) is outside what the residual form guarantees: such a lane divides per weight.
-    if (!(fabsf(scale) > 1e-30f && fabsf(scale) < 1e30f) && valid) {
-        const T* src = w + chunk * 16;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[i] = 0u;
+    if (!(fabsf(scale) > 1e-30f && fabsf(scale) < 1e30f)) {
+        // A scale whose reciprocal is not a normal float32 of full precision (groups near the ends of the float32
+        // range) is outside what the residual form guarantees: divide per weight, emit words from a bit queue.
+        unsigned long long acc = 0ull;
+        int fill = 0;
+        const T* rw = reinterpret_cast<const T*>(row);
 #pragma unroll 1
-        for (int j = 0; j < 16; ++j) {
-            const float v = Elt<T>::to_f32(src[j]);
+        for (int j = 0; j < GS; ++j) {
+            const float v = Elt<T>::to_f32(rw[j]);
             float r = MODE == MODE_AFFINE ? rintf(__fdiv_rn(__fsub_rn(v, bias), scale))
                                           : rintf(__fadd_rn(__fdiv_rn(v, scale), zero));
             r = fmaxf(fminf(r, (float)BINS), 0.0f);
-            const uint32_t qv = (uint32_t)(int)r;
-            const int pos = j * BITS, wd = pos >> 5, sh = pos & 31;
+            acc |= (unsigned long long)(is_const ? 0u : (uint32_t)(int)r) << fill;
+            fill += BITS;
+            if (fill >= 32) { *dst++ = (uint32_t)acc; acc >>= 32; fill -= 32; }
+        }
+    } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (i == wd) out[i] |= qv << sh;
-                if (i == wd + 1 && sh + BITS > 32) out[i] |= qv >> (32 - sh);
+        for (int run = 0; run < GS / 32; ++run) {
+            uint32_t out[BITS];
+#pragma unroll
+            for (int i = 0; i < BITS; ++i) out[i] = 0u;
+#pragma unroll
+            for (int vv = 0; vv < VPR; ++vv) {
+                const uint4 u = *reinterpret_cast<const uint4*>(row + (run * VPR + vv) * 16);
+                int si[WPV];
+                auto one = [&](float val, int e) {
+                    const float t = MODE == MODE_AFFINE ? __fsub_rn(val, bias) : val;
+                    const float y0 = __fmul_rn(t, rcp);
+                    float y = __fmaf_rn(__fmaf_rn(-y0, scale, t), rcp, y0);       // = RN(t / scale)
+                    if constexpr (MODE == MODE_RTN) y = __fadd_rn(y, zero);
+                    si[e] = rint_bits(y);
+                };
+                one(Vec16<T>::template get<0>(u), 0);
+                one(Vec16<T>::template get<1>(u), 1);
+                one(Vec16<T>::template get<2>(u), 2);
+                one(Vec16<T>::template get<3>(u), 3);
+                if constexpr (WPV == 8) {
+                    one(Vec16<T>::template get<4>(u), 4);
+                    one(Vec16<T>::template get<5>(u), 5);
+                    one(Vec16<T>::template get<6>(u), 6);
+                    one(Vec16<T>::template get<7>(u), 7);
+                }
+                if constexpr (BITS == 2 || BITS == 4 || BITS == 8) {
+                    // two codes per instruction, clamped by its saturation; the last pair goes in first
+                    uint32_t part = 0u;
+#pragma unroll
+                    for (int e = WPV - 2; e >= 0; e -= 2) {
+                        part = pack_sat2<BITS>(si[e + 1], si[e], part);
+                        if (BITS == 8 && (e & 3) == 0) {         // four 8-bit codes fill a word
+                            out[(vv * WPV + e) / 4] = part;
+                            part = 0u;
+                        }
+                    }
+                    if constexpr (BITS != 8) {
+                        constexpr int span = WPV * BITS;         // bits of this vector: 8, 16 or 32
+                        const int pos = vv * span, wd = pos >> 5, sh = pos & 31;
+                        out[wd] |= part << sh;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < WPV; ++e) {
+                        const uint32_t x = (uint32_t)min(max(si[e], 0), BINS);
+                        const int pos = (vv * WPV + e) * BITS, wd = pos >> 5, sh = pos & 31;
+                        out[wd] += x << sh;              // disjoint fields: the sum is the OR, in one shift-add
+                        if (sh + BITS > 32) out[wd + 1] += x >> (32 - sh);
+                    }
+                }
+            }
+            if (is_const) {
+#pragma unroll
+                for (int i = 0; i < BITS; ++i) out[i] = 0u;
+            }
+            uint32_t* p = dst + run * BITS;
+            if constexpr (BITS == 4) {
+                *reinterpret_cast<uint4*>(p) = make_uint4(out[0], out[1], out[2], out[3]);
+            } else if constexpr (BITS == 8) {
+                reinterpret_cast<uint4*>(p)[0] = make_uint4(out[0], out[1], out[2], out[3]);
+                reinterpret_cast<uint4*>(p)[1] = make_uint4(out[4], out[5], out[6], out[7]);
+            } else if constexpr (BITS == 2 || BITS == 6) {
+#pragma unroll
+                for (int i = 0; i < BITS / 2; ++i) reinterpret_cast<uint2*>(p)[i] = make_uint2(out[2 * i], out[2 * i + 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < BITS; ++i) p[i] = out[i];
             }
         }
     }
     if constexpr (MODE == MODE_AFFINE) {
-        if ((flags & JQ_QUANT_F16_TINY_GUARD) && Elt<S>::id == JQ_F16) {
+        if ((flags & JQ_QUANT_F16_TINY_GUARD) && sidecar_dtype == JQ_F16) {
             const float tiny = 6.103515625e-05f;  // smallest normal float16 (affine.py:43)
             if (fabsf(scale) < tiny) scale = copysignf(tiny, scale == 0.0f ? 1.0f : scale);
         }
     } else {
-        if (is_const) {                               // quantize.py:203-205
-#pragma unroll
-            for (int i = 0; i < 4; ++i) out[i] = 0u;
-            scale = 1.0f; zero = 0.0f;
-        }
+        if (is_const) { scale = 1.0f; zero = 0.0f; }  // quantize.py:203-205
         bias = __fmul_rn(-scale, zero);               // quantize.py:279
     }
-    store_words<BITS>(codes, chunk, out, valid);
-    if (valid && (threadIdx.x & (lanes_per_group - 1)) == 0) {
-        const int64_t g = chunk / lanes_per_group;
-        scales[g] = Elt<S>::from_f32(scale);
-        biases[g] = Elt<S>::from_f32(bias);
-    }
+    if (sidecar_dtype == JQ_F16) { put_sidecar<__half>(scales, grp, scale); put_sidecar<__half>(biases, grp, bias); }
+    else if (sidecar_dtype == JQ_BF16) { put_sidecar<__nv_bfloat16>(scales, grp, scale); put_sidecar<__nv_bfloat16>(biases, grp, bias); }
+    else { put_sidecar<float>(scales, grp, scale); put_sidecar<float>(biases, grp, bias); }
+}
+
+template <typename T, int BITS, int GS, int MODE>
+static int launch_group(const void* w, uint32_t* codes, void* scales, void* biases, int sidecar_dtype, int64_t n_groups,
+                        int flags, cudaStream_t st) {
+    constexpr int smem = 128 * (GS * (int)sizeof(T) + 16);
+    auto kern = quantize_group_kernel<T, BITS, GS, MODE>;
+    if (smem > 48 * 1024) JQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int64_t ctas = (n_groups + 127) / 128;
+    JQ_REQUIRE(ctas < (1ll << 31), JQ_EUNSUPPORTED, "tensor too large for one launch");
+    kern<<<(unsigned)ctas, 128, smem, st>>>((const T*)w, codes, scales, biases, sidecar_dtype, n_groups, flags);
+    return JQ_OK;
 }
 
 template <int MODE>
@@ -410,11 +487,14 @@ static int launch_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, 
     JQ_REQUIRE(blocks < (1ll << 31), JQ_EUNSUPPORTED, "tensor too large for one launch (%lld weights)", (long long)n);
     const int lpg = gs / 16;
     if (!(flags & JQ_QUANT_IEEE_DIV)) {
+        const int64_t n_groups = n / gs;
+        int rc2 = JQ_OK;
         JQ_DISPATCH_DTYPE(w_dtype, T,
-            JQ_DISPATCH_DTYPE(sidecar_dtype, S,
-                JQ_DISPATCH_BITS(bits, B,
-                    (quantize_lean_kernel<T, S, B, MODE><<<(unsigned)blocks, threads, 0, st>>>(
-                        (const T*)w, codes, (S*)scales, (S*)biases, n_chunks, lpg, flags)))))
+            JQ_DISPATCH_BITS(bits, B,
+                (rc2 = gs == 32 ? launch_group<T, B, 32, MODE>(w, codes, scales, biases, sidecar_dtype, n_groups, flags, st)
+                     : gs == 64 ? launch_group<T, B, 64, MODE>(w, codes, scales, biases, sidecar_dtype, n_groups, flags, st)
+                                : launch_group<T, B, 128, MODE>(w, codes, scales, biases, sidecar_dtype, n_groups, flags, st))))
+        if (rc2 != JQ_OK) return rc2;
         return check_launch("quantize");
     }
     JQ_DISPATCH_DTYPE(w_dtype, T,
