@@ -723,42 +723,60 @@ static int launch_quantize_mse(const void* w, int w_dtype, int64_t rows, int64_t
 }
 
 // ---- dequantizer ---------------------------------------------------------------
-// One thread produces 8 consecutive weights (BITS bytes of codes, at most 3 words).
+// One thread produces four runs of 8 consecutive weights (BITS bytes of codes, inside two words), 256 runs
+// apart, and issues the loads of all four before it converts any: a thread that reads 4 bytes of codes per
+// 16 bytes it writes keeps too little in flight to cover the read latency (8 KB per SM at full occupancy).
+constexpr int DEQ_UNROLL = 4;
+
 template <typename S, typename O, int BITS>
 __global__ void __launch_bounds__(256)
 dequantize_kernel(const uint32_t* __restrict__ codes, const S* __restrict__ scales, const S* __restrict__ biases,
                   O* __restrict__ out, int64_t n_oct, int64_t n_words, int gs_shift /* log2(gs/8) */) {
-    const int64_t oct = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (oct >= n_oct) return;
-    const int64_t byte0 = oct * BITS;
-    const int64_t w0 = byte0 >> 2;
-    const int sh = (int)(byte0 & 3) * 8;
-    const uint32_t a = __ldg(codes + w0);
-    const uint32_t b = (w0 + 1 < n_words) ? __ldg(codes + w0 + 1) : 0u;
-    const uint32_t c = (BITS > 4 && w0 + 2 < n_words) ? __ldg(codes + w0 + 2) : 0u;
-    // 64 bits of the stream starting at this thread's first code
-    const uint32_t lo = __funnelshift_r(a, b, sh);
-    const uint32_t hi = __funnelshift_r(b, c, sh);
-    const unsigned long long bitsv = ((unsigned long long)hi << 32) | lo;
-    const int64_t g = oct >> gs_shift;
-    const float s = Elt<S>::to_f32(scales[g]);
-    const float bs = Elt<S>::to_f32(biases[g]);
-    float r[8];
+    const int64_t oct0 = (int64_t)blockIdx.x * (256 * DEQ_UNROLL) + threadIdx.x;
+    uint32_t a[DEQ_UNROLL], b[DEQ_UNROLL];
+    float s[DEQ_UNROLL], bs[DEQ_UNROLL];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t qv = (uint32_t)(bitsv >> (j * BITS)) & ((1u << BITS) - 1u);
-        r[j] = __fadd_rn(__fmul_rn((float)qv, s), bs);   // affine.py:457-463: two roundings
+    for (int u = 0; u < DEQ_UNROLL; ++u) {
+        const int64_t oct = oct0 + u * 256;
+        a[u] = b[u] = 0u;
+        s[u] = bs[u] = 0.f;
+        if (oct < n_oct) {
+            const int64_t w0 = (oct * BITS) >> 2;
+            a[u] = __ldg(codes + w0);
+            // the run starts at byte (oct * BITS) & 3 of a[u]; its 8 * BITS bits end inside a[u] for 2 and 4 bits
+            // (start 0 or 2, 16 or 32 bits) and inside b[u] for every other width (at most 24 + 40 bits)
+            if (BITS != 2 && BITS != 4 && w0 + 1 < n_words) b[u] = __ldg(codes + w0 + 1);
+            const int64_t g = oct >> gs_shift;
+            s[u] = Elt<S>::to_f32(scales[g]);
+            bs[u] = Elt<S>::to_f32(biases[g]);
+        }
     }
-    O* o = out + oct * 8;
-    if constexpr (sizeof(O) == 4) {
-        float4* o4 = reinterpret_cast<float4*>(o);
-        o4[0] = make_float4(r[0], r[1], r[2], r[3]);
-        o4[1] = make_float4(r[4], r[5], r[6], r[7]);
-    } else {
-        O tmp[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) tmp[j] = Elt<O>::from_f32(r[j]);
-        *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(tmp);
+    for (int u = 0; u < DEQ_UNROLL; ++u) {
+        const int64_t oct = oct0 + u * 256;
+        if (oct >= n_oct) continue;
+        const int sh = (int)((oct * BITS) & 3) * 8;
+        // 64 bits of the stream starting at this run's first code
+        const uint32_t lo = __funnelshift_r(a[u], b[u], sh);
+        const uint32_t hi = b[u] >> sh;
+        const unsigned long long bitsv = ((unsigned long long)hi << 32) | lo;
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t qv = (uint32_t)(bitsv >> (j * BITS)) & ((1u << BITS) - 1u);
+            r[j] = __fadd_rn(__fmul_rn((float)qv, s[u]), bs[u]);   // affine.py:457-463: two roundings
+        }
+        O* o = out + oct * 8;
+        if constexpr (sizeof(O) == 4) {
+            float4* o4 = reinterpret_cast<float4*>(o);
+            o4[0] = make_float4(r[0], r[1], r[2], r[3]);
+            o4[1] = make_float4(r[4], r[5], r[6], r[7]);
+        } else {
+            O tmp[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tmp[j] = Elt<O>::from_f32(r[j]);
+            *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(tmp);
+        }
     }
 }
 
@@ -849,7 +867,7 @@ int jq_dequantize(const uint32_t* codes, const void* scales, const void* biases,
     JQ_REQUIRE(aligned(out, 16) && aligned(codes, 4), JQ_EINVAL, "out must be 16-byte aligned");
     const int64_t n_oct = n / 8, n_words = n * bits / 32;
     const int threads = 256;
-    const int64_t blocks = (n_oct + threads - 1) / threads;
+    const int64_t blocks = (n_oct + threads * jq::DEQ_UNROLL - 1) / (threads * jq::DEQ_UNROLL);
     JQ_REQUIRE(blocks < (1ll << 31), JQ_EUNSUPPORTED, "tensor too large for one launch");
     const int gs_shift = group_size == 32 ? 2 : group_size == 64 ? 3 : 4;
     cudaStream_t st = (cudaStream_t)stream;
