@@ -9,7 +9,7 @@
 //     running sums over the elements i mod 8, combined as ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)).  Eight lanes
 //     own one group, lane j the elements j, j+8, ...; the combine is an xor-shuffle tree over 1, 2, 4;
 //   * float64 -> float16 is one rounding (__double2half).
-// Bound: float64 arithmetic (about 40 operations per weight and iteration), not HBM: algorithmic bytes are
+// Bound: float64 arithmetic (about 20 operations per weight and iteration), not HBM: algorithmic bytes are
 // rows*K*sizeof(src) read + rows*K*bits/8 + rows*(K/gs)*4 written.
 #include <cuda_fp16.h>
 
@@ -59,10 +59,20 @@ quantize_fit_kernel(const W* __restrict__ w, const float* __restrict__ importanc
     double scale = fmax(__ddiv_rn(__dsub_rn((double)hi, (double)lo), bins), 1e-8);
     double bias = (double)lo;
     double c[PER];
+    // (v - bias) / scale, correctly rounded, in three operations from the correctly rounded reciprocal r: y0 = RN(t*r),
+    // y = RN(y0 + RN(t - y0*scale)*r); the residual is exact in an fma and y0 is within one ulp of the quotient, so y is
+    // the rounded quotient (Markstein's theorem; |scale| >= 1e-8 and |t| < 2^129: no overflow or underflow).  rint by
+    // adding and removing 1.5 * 2^52 (beyond 2^51 the result is still far outside [0, bins] on the right side).
     auto round_codes = [&]() {
+        const double r = __drcp_rn(scale);
 #pragma unroll
-        for (int i = 0; i < PER; ++i)
-            c[i] = fmin(fmax(rint(__ddiv_rn(__dsub_rn((double)v[i], bias), scale)), 0.0), bins);
+        for (int i = 0; i < PER; ++i) {
+            const double t = __dsub_rn((double)v[i], bias);
+            const double y0 = __dmul_rn(t, r);
+            const double y = __fma_rn(__fma_rn(-y0, scale, t), r, y0);
+            const double rq = __dsub_rn(__dadd_rn(y, 6755399441055744.0), 6755399441055744.0);
+            c[i] = fmin(fmax(rq, 0.0), bins);
+        }
     };
     round_codes();
     double a0 = (double)h[0], a1 = __dmul_rn((double)h[0], (double)v[0]);
