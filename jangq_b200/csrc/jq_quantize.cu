@@ -518,16 +518,24 @@ static int launch_quantize(const void* w, int w_dtype, int64_t rows, int64_t K, 
 // Mapping: eight lanes per block, lane k owning the weights i = k (mod 8).  numpy's add.reduce over
 // a contiguous row keeps eight running sums over exactly those residue classes and folds them as
 // ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)), which is a three-step xor butterfly over the eight lanes.
-// The per-ratio scalars (scale, its reciprocal, zero point: two exact divisions) are computed once
-// per block, ratio r by lane r % 8, and handed round by shuffle.  x/scale uses x*rcp(scale) and
-// falls back to the exact division when the sum lands within 1e-4 of a half-integer, the only
-// place where the two could round to different codes.
+// The per-ratio scalars (scale, its reciprocal, zero point) are computed once
+// per block, ratio r by lane r % 8, and handed round by shuffle.  Every quotient (x/scale per weight, the scale and
+// the zero point per ratio) is the correctly rounded one, formed from the correctly rounded reciprocal and one exact
+// residual (div_by_rcp) instead of a division.
 // linspace(0.7, 1.0, 20) as numpy produces it (start + i*step, last element set to stop)
 __constant__ double MSE_RATIOS[20] = {
     0x1.6666666666666p-1, 0x1.6e7bf53896e7cp-1, 0x1.7691840ac7691p-1, 0x1.7ea712dcf7ea7p-1, 0x1.86bca1af286bcp-1,
     0x1.8ed2308158ed2p-1, 0x1.96e7bf53896e8p-1, 0x1.9efd4e25b9efdp-1, 0x1.a712dcf7ea713p-1, 0x1.af286bca1af28p-1,
     0x1.b73dfa9c4b73ep-1, 0x1.bf53896e7bf54p-1, 0x1.c7691840ac769p-1, 0x1.cf7ea712dcf7fp-1, 0x1.d79435e50d794p-1,
     0x1.dfa9c4b73dfaap-1, 0x1.e7bf53896e7c0p-1, 0x1.efd4e25b9efd5p-1, 0x1.f7ea712dcf7eap-1, 0x1.0000000000000p+0};
+
+// RN(a / b) from r = RN(1 / b): y0 = RN(a*r) is within one ulp of the quotient, the residual a - y0*b is exact in an
+// fma, and the corrected value rounds to the correctly rounded quotient (Markstein's theorem; no overflow or underflow
+// for the magnitudes here: b >= 1e-46, |a| < 2^129).
+__device__ __forceinline__ double div_by_rcp(double a, double b, double r) {
+    const double y0 = __dmul_rn(a, r);
+    return __fma_rn(__fma_rn(-y0, b, a), r, y0);
+}
 
 template <typename T, typename S, int BITS, int GS>
 __global__ void __launch_bounds__(256)
@@ -570,9 +578,9 @@ quantize_mse_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __
             const double c_max = __dmul_rn((double)hi, ratio);
             double c_range = __dsub_rn(c_max, c_min);
             if (c_range == 0.0) c_range = 1.0;
-            sc[s] = __ddiv_rn(c_range, (double)L);
-            zp[s] = min(max(__double2int_rn(__ddiv_rn(-c_min, sc[s])), 0), L);
+            sc[s] = div_by_rcp(c_range, (double)L, 1.0 / L);
             rc[s] = __drcp_rn(sc[s]);
+            zp[s] = min(max(__double2int_rn(div_by_rcp(-c_min, sc[s], rc[s])), 0), L);
         }
     }
 
@@ -631,7 +639,7 @@ quantize_mse_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __
     }
 
     double best = __longlong_as_double(0x7FF0000000000000ll);   // +inf
-    double best_scale = 1.0;
+    double best_scale = 1.0, best_rcp = 1.0;
     int best_zero = 0;
     bool found = false;
     while (__any_sync(0xFFFFFFFFu, cand != 0u)) {
@@ -648,13 +656,8 @@ quantize_mse_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __
 #pragma unroll
         for (int t = 0; t < EPL; ++t) {
             const double x = (double)xf[t];
-            double v = __dadd_rn(__dmul_rn(x, rcp), zd);
-            int qi = __double2int_rn(v);
-            if (fabs(v - (double)qi) > 0.4999) {              // near a tie (or saturated): exact quotient
-                v = __dadd_rn(__ddiv_rn(x, scale), zd);       // quantize.py:174
-                qi = __double2int_rn(v);
-            }
-            qi = min(max(qi, 0), L);                          // :175
+            const double v = __dadd_rn(div_by_rcp(x, scale, rcp), zd);   // quantize.py:174
+            const int qi = min(max(__double2int_rn(v), 0), L);           // :175
             const double e = __dsub_rn(x, __dmul_rn((double)(qi - z), scale));   // :176
             acc = __dadd_rn(acc, __dmul_rn(e, e));
         }
@@ -662,9 +665,9 @@ quantize_mse_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __
         acc = __dadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 2));
         acc = __dadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, 4));
         const double mse = __dmul_rn(acc, 1.0 / GS);          // :178 (division by a power of two)
-        if (active && mse < best) { best = mse; best_scale = scale; best_zero = z; found = true; }   // :181-185
+        if (active && mse < best) { best = mse; best_scale = scale; best_rcp = rcp; best_zero = z; found = true; }   // :181-185
     }
-    if (is_const || !found) { best_scale = 1.0; best_zero = 0; }   // :187-189, and the initial values of :158-160
+    if (is_const || !found) { best_scale = 1.0; best_rcp = 1.0; best_zero = 0; }   // :187-189, and the initial values of :158-160
 
     // codes of the winning ratio, staged so that each lane can assemble whole words
     uint8_t* st = stage[warp];
@@ -672,7 +675,7 @@ quantize_mse_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __
     for (int t = 0; t < EPL; ++t) {
         int qi = 0;
         if (!is_const && found) {
-            const double v = __dadd_rn(__ddiv_rn((double)xf[t], best_scale), (double)best_zero);
+            const double v = __dadd_rn(div_by_rcp((double)xf[t], best_scale, best_rcp), (double)best_zero);
             qi = min(max(__double2int_rn(v), 0), L);
         }
         st[sub * GS + t * 8 + k] = (uint8_t)qi;
