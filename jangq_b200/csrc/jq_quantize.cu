@@ -208,8 +208,8 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __rest
 //     ulp of the quotient the corrected value is the correctly rounded quotient (Markstein's theorem).  No guard and
 //     no branch: with 16-bit sources exact rounding ties are common (weights and group edge sit on a coarse grid, so
 //     (w - edge) * q0 / edge is often exactly k + 1/2) and a guarded reciprocal takes its exact-division branch in a
-//     large share of warp steps.  Groups whose scale is outside [1e-30, 1e30], where the reciprocal is not a normal
-//     float32 of full precision, divide per weight instead;
+//     large share of warp steps.  Groups whose scale is outside [1e-25, 1e25], where the reciprocal or a residual may
+//     leave the normal float32 range, divide per weight instead;
 //   * y * 2^-149 is a subnormal whose bit pattern is rint(y) (ties to even) as an integer, negative for negative y;
 //     for 2-, 4- and 8-bit codes one cvt.pack.sat then clamps two of them and shifts them into the word being built;
 //   * a thread owns a whole group, so the per-group scalars (three IEEE divisions, the reciprocal) are issued once per
@@ -336,9 +336,9 @@ __device__ __forceinline__ void quantize_one_group(const uint8_t* row, int64_t g
     const float rcp = __frcp_rn(scale);
     uint32_t* dst = codes + grp * (GS * BITS / 32);
 
-    if (!(fabsf(scale) > 1e-30f && fabsf(scale) < 1e30f)) {
-        // A scale whose reciprocal is not a normal float32 of full precision (groups near the ends of the float32
-        // range) is outside what the residual form guarantees: divide per weight, emit words from a bit queue.
+    if (!(fabsf(scale) > 1e-25f && fabsf(scale) < 1e25f)) {
+        // Near the ends of the float32 range the reciprocal or the residual can be subnormal, which is outside
+        // what the residual form guarantees: divide per weight, emit words from a bit queue.
         unsigned long long acc = 0ull;
         int fill = 0;
         const T* rw = reinterpret_cast<const T*>(row);
