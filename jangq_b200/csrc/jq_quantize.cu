@@ -169,7 +169,7 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ codes, S* __rest
                 q[j] = (uint32_t)min(max(qi, 0), (int)bins);
             } else {
                 float r = rintf(__fdiv_rn(t, scale));
-                r = fmaxf(fminf(r, bins), 0.0f);  // NaN -> 0
+                r = fmaxf(fminf(r, bins), 0.0f);  // NaN -> bins (fminf returns its other operand)
                 q[j] = (uint32_t)(int)r;
             }
         }
