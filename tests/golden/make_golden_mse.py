@@ -3,7 +3,7 @@
 Runs jang_tools.quantize.quantize_tensor(method="mse") (jang_tools/quantize.py:153-191,
 :211-289) on a seeded tensor with a constant block, a zero block and an outlier, at
 2/3/4 bits (the widths the search covers) and 6 bits (which falls through to RTN),
-for 64- and 128-weight blocks.  The fixture records the numpy version: the reference
+for 32-, 64- and 128-weight blocks.  The fixture records the numpy version: the reference
 multiplies float32 minima by float64 clip ratios, so its arithmetic follows that
 version's promotion rules (float64 under NumPy >= 2).
 
@@ -32,7 +32,7 @@ def main():
     w[2, 7] = 0.9                                    # outlier the search clips
     w[3, 300] = -1.1
     out = {"w": w, "numpy_version": np.array(np.__version__)}
-    for gs in (64, 128):
+    for gs in (32, 64, 128):
         for bits in (2, 3, 4, 6):
             qt = quantize_tensor(w, np.full(w.size // gs, bits, np.uint8), block_size=gs, method="mse")
             key = f"g{gs}_b{bits}"

@@ -150,7 +150,7 @@ def test_affine_division_forms_agree(bits, src):
                 assert torch.equal(x, y), (mode, gs)
 
 
-@pytest.mark.parametrize("gs", (64, 128))
+@pytest.mark.parametrize("gs", (32, 64, 128))
 @pytest.mark.parametrize("bits", (2, 3, 4, 6))
 def test_mse_golden(golden_dir, bits, gs):
     """quantize_tensor(method="mse") vectors made by the reference (quantize.py:153-191)."""

@@ -68,7 +68,7 @@ def test_rtn_matches_reference(golden_dir, bits):
     assert np.array_equal(b, z[f"b{bits}_biases"].astype(np.float32))
 
 
-@pytest.mark.parametrize("gs", (64, 128))
+@pytest.mark.parametrize("gs", (32, 64, 128))
 @pytest.mark.parametrize("bits", (2, 3, 4, 6))
 def test_mse_matches_reference(golden_dir, bits, gs):
     """quantize_tensor(method="mse") (quantize.py:153-191): the oracle reproduces the reference's

@@ -44,7 +44,7 @@ def test_rtn_fixture_through_the_mirror(golden_dir, bits):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("gs", (64, 128))
+@pytest.mark.parametrize("gs", (32, 64, 128))
 @pytest.mark.parametrize("bits", (2, 3, 4, 6))
 def test_default_method_is_the_clip_ratio_search(golden_dir, bits, gs):
     z = np.load(os.path.join(golden_dir, "mse_ref.npz"))
